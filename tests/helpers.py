@@ -1,0 +1,94 @@
+"""Shared test helpers: running an operator case through the oracle, tolerances."""
+import os
+
+import numpy as np
+import torch
+
+import cases
+from oracle import bounds_oracle as O
+
+GOLDEN_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+# Per-operator agreement bar on identical seeded inputs, fp32:
+#   |ours - ref| <= ATOL + RTOL * |ref|
+RTOL = 1e-5
+ATOL = 1e-6
+
+
+def load_golden(name):
+    return np.load(os.path.join(GOLDEN_DIR, name))
+
+
+def oracle_bounds(c, t, dtype=torch.float32):
+    return O.OBounds(c["p"], c["eps"], t[0].to(dtype), t[1].to(dtype), t[2].to(dtype), t[3].to(dtype), c["words"])
+
+
+def run_oracle_op(c, dtype=torch.float32):
+    """Runs case `c` (see cases.OP_CASES) through the CPU oracle; returns a dict of tensors."""
+    x_t, ex = cases.case_inputs(c)
+    x = oracle_bounds(c, x_t, dtype)
+    op = c["op"]
+    if op == "concretize":
+        l, u = x.concretize()
+        return {"l": l, "u": u}
+    if op == "relu":
+        r = x.relu()
+    elif op == "tanh":
+        r = x.tanh()
+    elif op == "exp":
+        r = x.exp()
+    elif op == "reciprocal":
+        r = x.reciprocal()
+    elif op == "matmul":
+        r = x.matmul(ex["W"].to(dtype))
+    elif op == "dense":
+        r = x.dense(ex["W"].to(dtype), ex["bias"].to(dtype))
+    elif op == "dot":
+        r = x.dot_product(oracle_bounds(c, ex["y"], dtype))
+    elif op == "context":
+        r = x.context(oracle_bounds(c, ex["y"], dtype))
+    elif op == "mul_bounds":
+        r = x.mul_bounds(oracle_bounds(c, ex["y"], dtype))
+    elif op == "softmax":
+        r = x.softmax()
+    elif op == "layer_norm":
+        r = x.layer_norm(ex["W"].to(dtype), ex["bias"].to(dtype), "no_var")
+    elif op == "scale":
+        r = x.scale(c["c"])
+    elif op == "add":
+        r = x.add(oracle_bounds(c, ex["y"], dtype))
+    else:
+        raise KeyError(op)
+    return {"lw": r.lw, "lb": r.lb, "uw": r.uw, "ub": r.ub}
+
+
+def assert_close(got, ref, what, rtol=RTOL, atol=ATOL):
+    got = torch.as_tensor(np.asarray(got)) if not isinstance(got, torch.Tensor) else got.detach().cpu()
+    ref = torch.as_tensor(np.asarray(ref)) if not isinstance(ref, torch.Tensor) else ref.detach().cpu()
+    assert got.shape == ref.shape, "%s: shape %s vs %s" % (what, tuple(got.shape), tuple(ref.shape))
+    got, ref = got.double(), ref.double()
+    err = (got - ref).abs()
+    bound = atol + rtol * ref.abs()
+    bad = err > bound
+    if bool(bad.any()) or not bool(torch.isfinite(got).all()):
+        i = int(torch.argmax(err - bound))
+        raise AssertionError("%s: %d of %d outside tolerance; worst |d|=%.3e at flat index %d (got %.9g ref %.9g)"
+                             % (what, int(bad.sum()), bad.numel(), float(err.flatten()[i]), i,
+                                float(got.flatten()[i]), float(ref.flatten()[i])))
+
+
+def assert_within_noise(got, ref32, ref64, what, c=4.0, rtol=RTOL, atol=ATOL):
+    """End-to-end criterion.  Over several layers the reference's own fp32 rounding noise is
+    amplified well beyond the per-operator bar (its fp32 and fp64 runs differ by 1e-3 relative
+    after two to three encoder layers), so a whole pass is judged against the fp64 run of the
+    same algorithm: max|got - ref64| <= c * max|ref32 - ref64| + atol + rtol * max|ref64|."""
+    def d(t):
+        t = torch.as_tensor(np.asarray(t)) if not isinstance(t, torch.Tensor) else t.detach().cpu()
+        return t.double()
+    got, ref32, ref64 = d(got), d(ref32), d(ref64)
+    assert got.shape == ref64.shape, "%s: shape %s vs %s" % (what, tuple(got.shape), tuple(ref64.shape))
+    assert bool(torch.isfinite(got).all()), "%s: non-finite values" % what
+    noise = float((ref32 - ref64).abs().max())
+    err = float((got - ref64).abs().max())
+    bound = c * noise + atol + rtol * float(ref64.abs().max())
+    assert err <= bound, "%s: max|got-ref64|=%.3e exceeds %.1f x fp32 noise %.3e (+tol) = %.3e" % (what, err, c, noise, bound)

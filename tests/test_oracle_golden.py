@@ -1,0 +1,63 @@
+"""The CPU oracle against the committed golden vectors (outputs of the reference's own
+Python `Bounds`, see tests/golden/make_golden.py)."""
+import pytest
+import torch
+
+import cases
+import helpers
+from oracle import bounds_oracle as O
+
+
+@pytest.fixture(scope="module")
+def golden_ops():
+    return helpers.load_golden("ops.npz")
+
+
+@pytest.mark.parametrize("name", sorted(cases.OP_CASES))
+def test_op_matches_golden(name, golden_ops):
+    torch.set_num_threads(1)
+    out = helpers.run_oracle_op(cases.OP_CASES[name])
+    for k, v in out.items():
+        helpers.assert_close(v, golden_ops["%s/%s" % (name, k)], "%s/%s" % (name, k))
+
+
+def test_encoder_matches_golden():
+    torch.set_num_threads(1)
+    g = helpers.load_golden("encoder.npz")
+    c = cases.ENCODER_CASE
+    model = O.make_encoder(c["seed"], c["layers"], c["d_model"], c["heads"], c["ffn"], c["std"])
+    emb = cases.encoder_inputs(c)
+    trace, trace64 = [], []
+    l, u = O.encoder_forward(model, emb, [c["index"]], c["p"], c["eps"], trace=trace)
+    l64, u64 = O.encoder_forward(O.model_to(model, torch.float64), emb.double(), [c["index"]], c["p"], c["eps"],
+                                 trace=trace64)
+    # Single operators meet the per-op bar (test above); over a whole pass the fp32 noise of the
+    # reference itself is amplified, so the pass is judged against the fp64 run (see helpers).
+    helpers.assert_within_noise(l, g["l"], l64, "logit lower")
+    helpers.assert_within_noise(u, g["u"], u64, "logit upper")
+    stages, stages64 = dict(trace), dict(trace64)
+    for s in range(c["B"]):
+        for nm in ("embedding", "layer0.scores", "layer0.probs", "layer0.output", "pooled"):
+            bl, bu = stages[nm].concretize()
+            bl64, bu64 = stages64[nm].concretize()
+            heads = c["heads"] if nm in ("layer0.scores", "layer0.probs") else 1
+            sl = slice(s * heads, (s + 1) * heads)
+            helpers.assert_within_noise(bl[sl], g["s%d/%s/l" % (s, nm)], bl64[sl], "s%d %s l" % (s, nm))
+            helpers.assert_within_noise(bu[sl], g["s%d/%s/u" % (s, nm)], bu64[sl], "s%d %s u" % (s, nm))
+
+
+def test_bounds_contain_concrete_forward():
+    """Soundness of the oracle pass: sampled points of the eps-ball map inside [l, u]."""
+    c = cases.ENCODER_CASE
+    model = O.make_encoder(c["seed"], c["layers"], c["d_model"], c["heads"], c["ffn"], c["std"])
+    emb = cases.encoder_inputs(c)[:1]
+    l, u = O.encoder_forward(model, emb, [c["index"]], c["p"], c["eps"])
+    g = torch.Generator().manual_seed(5)
+    n = 512
+    delta = (torch.randint(0, 2, (n, c["d_model"]), generator=g).float() * 2 - 1) * c["eps"]  # vertices
+    delta[: n // 2] *= torch.rand(n // 2, 1, generator=g)
+    x = emb.repeat(n, 1, 1)
+    x[:, c["index"], :] += delta
+    y = O.concrete_forward(model, x)
+    assert float(y.min()) >= float(l[0]) - 1e-5 and float(y.max()) <= float(u[0]) + 1e-5
+    assert float(u[0] - l[0]) < 2.0  # and the bound is finite and of sane width at this eps
