@@ -1,0 +1,86 @@
+"""ctypes binding of libfaith_b200.so (the C ABI declared in include/faith_b200.h).
+
+There is no CPU fallback: if the shared library is missing or a call fails, an exception is
+raised.
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libfaith_b200.so")
+
+FB_P1, FB_P2, FB_PINF = 1, 2, 3
+FB_NATIVE, FB_TRANSPOSED = 0, 1
+FB_RELU, FB_TANH, FB_EXP, FB_RECIPROCAL = 0, 1, 2, 3
+
+_P = ctypes.c_void_p
+_I = ctypes.c_int
+_L = ctypes.c_int64
+_F = ctypes.c_float
+
+
+class EncoderLayer(ctypes.Structure):
+    _fields_ = [(n, _P) for n in ("q_w", "q_b", "k_w", "k_b", "v_w", "v_b", "ao_w", "ao_b", "ln1_g", "ln1_b",
+                                  "f1_w", "f1_b", "f2_w", "f2_b", "ln2_g", "ln2_b")]
+
+
+class Encoder(ctypes.Structure):
+    _fields_ = [("layers", _I), ("d_model", _I), ("heads", _I), ("ffn", _I), ("layer_norm", _I),
+                ("emb_ln_g", _P), ("emb_ln_b", _P), ("layer", ctypes.POINTER(EncoderLayer)),
+                ("pool_w", _P), ("pool_b", _P), ("cls_w", _P), ("cls_b", _P)]
+
+
+# name -> argtypes; every function returns int (fb_status) unless listed in _OTHER_RESTYPE
+SIGNATURES = {
+    "fb_concretize_f32": [_P] * 6 + [_L, _I, _I, _I, _I, _F, _I, _P],
+    "fb_relax_f32": [_I] + [_P] * 8 + [_L, _I, _I, _I, _I, _F, _I, _P, _P],
+    "fb_matmul_f32": [_P] * 10 + [_L, _I, _I, _I, _P],
+    "fb_dot_product_f32": [_P] * 16 + [_I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P],
+    "fb_mul_bounds_f32": [_P] * 12 + [_L, _I, _I, _I, _I, _F, _P],
+    "fb_add_f32": [_P] * 12 + [_L, _I, _I, _P],
+    "fb_scale_f32": [_P] * 8 + [_L, _I, _I, _F, _P],
+    "fb_rowsum_f32": [_P] * 8 + [_L, _I, _I, _P],
+    "fb_layernorm_novar_f32": [_P] * 14 + [_L, _I, _I, _P],
+    "fb_split_heads_f32": [_P] * 4 + [_I] * 6 + [_P],
+    "fb_merge_heads_f32": [_P] * 4 + [_I] * 5 + [_P],
+    "fb_conv2d_f32": [_P] * 10 + [_I] * 10 + [_P],
+    "fb_encoder_workspace_bytes": [ctypes.POINTER(Encoder), _I, _I, _I],
+    "fb_encoder_forward_f32": [ctypes.POINTER(Encoder), _P, _I, _I, ctypes.POINTER(_I), _I, _I, _F, _P, _P, _P, _P, _L, _P],
+    "fb_status_string": [_I],
+    "fb_last_cuda_error": [],
+    "fb_version": [],
+}
+_OTHER_RESTYPE = {"fb_status_string": ctypes.c_char_p, "fb_encoder_workspace_bytes": _L}
+
+_lib = None
+
+
+def load():
+    """Loads the shared library (once) and declares the prototypes."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError("libfaith_b200.so is not built (expected at %s); run `python -m faith_b200.build`. "
+                           "There is no CPU fallback." % LIB_PATH)
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, argtypes in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the symbol is missing
+        fn.argtypes = argtypes
+        fn.restype = _OTHER_RESTYPE.get(name, _I)
+    _lib = lib
+    return lib
+
+
+class FaithError(RuntimeError):
+    pass
+
+
+def check(status, what):
+    if status != 0:
+        lib = load()
+        msg = lib.fb_status_string(status).decode()
+        extra = ""
+        if status == 4:
+            extra = " (cudaError %d)" % lib.fb_last_cuda_error()
+        raise FaithError("%s failed: %s%s" % (what, msg, extra))

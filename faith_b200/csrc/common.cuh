@@ -1,0 +1,191 @@
+// Shared host/device helpers of libfaith_b200 (sm_100a only).
+#pragma once
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+#include "faith_b200.h"
+
+namespace fb {
+
+// ---------------------------------------------------------------- host side
+void set_last_cuda_error(int e);
+
+struct DeviceInfo {
+  int sms;
+  int smem_optin;  // max dynamic shared memory per block (opt-in), bytes
+};
+// Properties of the current device, queried once per device and cached.
+const DeviceInfo& device_info();
+
+#define FB_CUDA_OK(expr)                                   \
+  do {                                                     \
+    cudaError_t fb_e_ = (expr);                            \
+    if (fb_e_ != cudaSuccess) {                            \
+      fb::set_last_cuda_error((int)fb_e_);                 \
+      return FB_ERR_CUDA;                                  \
+    }                                                      \
+  } while (0)
+
+// Launch errors are read without clearing the sticky state of unrelated earlier failures.
+#define FB_LAUNCH_OK() FB_CUDA_OK(cudaGetLastError())
+
+__host__ __device__ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline bool valid_norm(int p) { return p == FB_P1 || p == FB_P2 || p == FB_PINF; }
+inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// -------------------------------------------------------------- device side
+// Scalar arithmetic with the rounding of the reference's PyTorch expressions: one rounding
+// per operation, no contraction into fused multiply-adds.
+__device__ __forceinline__ float fadd(float a, float b) { return __fadd_rn(a, b); }
+__device__ __forceinline__ float fsub(float a, float b) { return __fsub_rn(a, b); }
+__device__ __forceinline__ float fmul(float a, float b) { return __fmul_rn(a, b); }
+__device__ __forceinline__ float fdiv(float a, float b) { return __fdiv_rn(a, b); }
+
+constexpr float kGuard = 1e-12f;  // additive guard of every chord slope (Bounds.py:27)
+
+// Accumulation of the dual norm over dim_in: sum |x| (p = inf), sum x^2 (p = 2), max |x| (p = 1).
+__device__ __forceinline__ float norm_accum(int p, float acc, float x) {
+  if (p == FB_PINF) return acc + fabsf(x);
+  if (p == FB_P2) return fmaf(x, x, acc);
+  return fmaxf(acc, fabsf(x));
+}
+__device__ __forceinline__ float norm_combine(int p, float a, float b) {
+  return (p == FB_P1) ? fmaxf(a, b) : a + b;
+}
+__device__ __forceinline__ float norm_finish(int p, float acc) {
+  return (p == FB_P2) ? sqrtf(acc) : acc;
+}
+
+// Coefficients of one column after a relaxation:
+//   out_lw = c_ll * lw + c_lu * uw      out_lb = nlb
+//   out_uw = c_ul * lw + c_uu * uw      out_ub = nub
+// For every well-formed column (l <= u) exactly one coefficient per line is non-zero, so the
+// rescale is a single rounded product as in the reference.
+struct ColCoef {
+  float c_ll, c_lu, c_ul, c_uu, nlb, nub;
+};
+
+// One call of the reference's add_linear (Bounds.py:362-381) at the level of a column:
+// adds mask * (line with slope k through (x0, y0) applied to the input bound) to the lower
+// (lower = true) or upper output line.  A positive slope keeps the side, any other swaps it.
+__device__ __forceinline__ void add_line(ColCoef& c, float mask, bool lower, float k, float x0, float y0,
+                                         float lb, float ub) {
+  const float kp = (k > 0.f) ? 1.f : 0.f;
+  const float kn = 1.f - kp;
+  const float own_b = lower ? lb : ub;
+  const float oth_b = lower ? ub : lb;
+  const float t_own = fmul(fmul(mask, kp), fadd(fmul(fsub(own_b, x0), k), y0));
+  const float t_oth = fmul(fmul(mask, kn), fadd(fmul(fsub(oth_b, x0), k), y0));
+  const float w_own = fmul(fmul(mask, kp), k);
+  const float w_oth = fmul(fmul(mask, kn), k);
+  if (lower) {
+    c.c_ll = fadd(c.c_ll, w_own);
+    c.c_lu = fadd(c.c_lu, w_oth);
+    c.nlb = fadd(fadd(c.nlb, t_own), t_oth);
+  } else {
+    c.c_uu = fadd(c.c_uu, w_own);
+    c.c_ul = fadd(c.c_ul, w_oth);
+    c.nub = fadd(fadd(c.nub, t_own), t_oth);
+  }
+}
+
+__device__ __forceinline__ float dtanh_ref(float x) {
+  const float ch = coshf(x);
+  return fdiv(1.f, fmul(ch, ch));
+}
+
+// exp continued linearly above 12 (Bounds.py:984-989)
+__device__ __forceinline__ float exp_capped(float x) {
+  const float thres = 12.f;
+  if (x < thres) return expf(fminf(x, thres));
+  return fmul(expf(thres), fadd(fsub(x, thres), 1.f));
+}
+
+// Per-column relaxation: from the concretised range (l, u) and the bias terms (lb, ub) to
+// the column coefficients.  `bad` is set when FB_RECIPROCAL sees l < 1e-12.
+__device__ inline ColCoef relax_column(int op, float l, float u, float lb, float ub, bool& bad) {
+  ColCoef c = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (op == FB_EXP) {  // Bounds.py:982-997; both slopes are applied to the own side
+    const float m = fminf(fmul(fadd(l, u), 0.5f), fadd(l, 0.99f));
+    const float kl = expf(fminf(m, 12.f));
+    const float el = exp_capped(l);
+    const float ku = fdiv(fsub(exp_capped(u), el), fadd(fsub(u, l), kGuard));
+    c.c_ll = kl;
+    c.nlb = fmul(kl, fadd(fsub(lb, m), 1.f));
+    c.c_uu = ku;
+    c.nub = fadd(fsub(fmul(ub, ku), fmul(ku, l)), el);
+    return c;
+  }
+  if (op == FB_RECIPROCAL) {  // Bounds.py:1145-1155; both slopes negative: sides swap
+    if (!(l >= kGuard)) bad = true;
+    const float m = fmul(fadd(l, u), 0.5f);
+    const float kl = fdiv(-1.f, fmul(m, m));
+    const float ku = fdiv(-1.f, fmul(l, u));
+    c.c_lu = kl;
+    c.nlb = fadd(fmul(ub, kl), fdiv(2.f, m));
+    c.c_ul = ku;
+    c.nub = fadd(fsub(fmul(lb, ku), fmul(ku, l)), fdiv(1.f, l));
+    return c;
+  }
+  const float pos = (l > 0.f) ? 1.f : 0.f;
+  const float neg = (u < 0.f) ? 1.f : 0.f;
+  const float both = 1.f - pos - neg;
+  if (op == FB_RELU) {  // Bounds.py:921-963
+    if (pos != 0.f) {
+      add_line(c, pos, true, 1.f, 0.f, 0.f, lb, ub);
+      add_line(c, pos, false, 1.f, 0.f, 0.f, lb, ub);
+    }
+    if (both != 0.f) {
+      const float k_up = fdiv(u, fadd(fsub(u, l), kGuard));
+      add_line(c, both, false, k_up, l, 0.f, lb, ub);
+      const float k_lo = (fabsf(u) > fabsf(l)) ? 1.f : 0.f;
+      add_line(c, both, true, k_lo, 0.f, 0.f, lb, ub);
+    }
+    return c;
+  }
+  // FB_TANH, Bounds.py:1027-1103
+  if (pos != 0.f || neg != 0.f) {
+    const float m = fmul(fadd(l, u), 0.5f);
+    const float k_tan = dtanh_ref(m);
+    const float y_tan = tanhf(m);
+    const float tl = tanhf(l);
+    const float k_chd = fdiv(fsub(tanhf(u), tl), fadd(fsub(u, l), kGuard));
+    if (neg != 0.f) {
+      add_line(c, neg, true, k_tan, m, y_tan, lb, ub);
+      add_line(c, neg, false, k_chd, l, tl, lb, ub);
+    }
+    if (pos != 0.f) {
+      add_line(c, pos, false, k_tan, m, y_tan, lb, ub);
+      add_line(c, pos, true, k_chd, l, tl, lb, ub);
+    }
+  }
+  if (both != 0.f) {
+    const float tu = tanhf(u), tl = tanhf(l);
+    // lower line: tangent point in [l, 0] whose tangent passes through (u, tanh u)
+    float d = fmul(l, 0.5f), lo = l, hi = 0.f;
+#pragma unroll 1
+    for (int t = 0; t < 10; ++t) {
+      const float v = fsub(fdiv(fsub(tu, tanhf(d)), fadd(fsub(u, d), kGuard)), dtanh_ref(d));
+      if (v > 0.f) { lo = d; d = fmul(fadd(d, hi), 0.5f); }
+      else         { hi = d; d = fmul(fadd(d, lo), 0.5f); }
+    }
+    float td = tanhf(d);
+    float k = fdiv(fsub(td, tu), fadd(fsub(d, u), kGuard));
+    add_line(c, both, true, k, d, td, lb, ub);
+    // upper line: tangent point in [0, u] whose tangent passes through (l, tanh l)
+    d = fmul(u, 0.5f); lo = 0.f; hi = u;
+#pragma unroll 1
+    for (int t = 0; t < 10; ++t) {
+      const float v = fsub(fdiv(fsub(tanhf(d), tl), fadd(fsub(d, l), kGuard)), dtanh_ref(d));
+      if (v > 0.f) { hi = d; d = fmul(fadd(d, lo), 0.5f); }
+      else         { lo = d; d = fmul(fadd(d, hi), 0.5f); }
+    }
+    td = tanhf(d);
+    k = fdiv(fsub(td, tl), fadd(fsub(d, l), kGuard));
+    add_line(c, both, false, k, d, td, lb, ub);
+  }
+  return c;
+}
+
+}  // namespace fb

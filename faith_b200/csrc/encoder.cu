@@ -1,0 +1,234 @@
+// Whole-model driver: forward linear-bound propagation through a BERT-style encoder for a batch
+// of sentences, as one chain of kernel launches on the caller's stream (no host synchronisation,
+// no allocation: all intermediates live in a caller-provided arena of four rotating slots).
+//
+// Stage order follows the reference verifier (VerifierForward.py:93-319): input bounds ->
+// embedding layer norm -> per layer [Q,K,V dense -> head split -> scores = Q.K^T / sqrt(d) ->
+// softmax (exp, row sum, reciprocal, McCormick product) -> context = probs . V -> head merge ->
+// dense -> +residual -> layer norm -> dense -> relu -> dense -> +residual -> layer norm] ->
+// first token -> dense -> tanh -> classifier folded to logit0 - logit1 -> concretise.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace fb {
+namespace {
+
+struct BoundSet {
+  float *lw, *uw, *lb, *ub;
+};
+
+inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
+
+struct Plan {
+  int64_t cap_w, cap_b;      // floats per lw (resp. lb) tensor of a slot
+  int64_t slot_bytes;        // one slot: lw, uw, lb, ub
+  int64_t range_floats;      // one operand-range scratch tensor of the dot product
+  int64_t small_bytes;       // folded classifier weight + bias
+  int64_t total;
+};
+
+Plan make_plan(const fb_encoder* e, int S, int L, int words) {
+  Plan p;
+  const int64_t D = e->d_model, F = e->ffn, H = e->heads, Di = (int64_t)words * D;
+  int64_t feat = D > F ? D : F;
+  if (H * L > feat) feat = H * L;
+  p.cap_w = (int64_t)S * L * Di * feat;
+  p.cap_b = (int64_t)S * L * feat;
+  p.slot_bytes = 2 * align_up(p.cap_w * 4, 256) + 2 * align_up(p.cap_b * 4, 256);
+  const int64_t d = D / H;
+  p.range_floats = (int64_t)S * H * (L > d ? L : d) * (L > d ? L : d);
+  p.small_bytes = align_up((D + 1) * 4, 256);
+  p.total = 4 * p.slot_bytes + 4 * align_up(p.range_floats * 4, 256) + p.small_bytes;
+  return p;
+}
+
+BoundSet carve_slot(char* base, const Plan& p) {
+  BoundSet b;
+  b.lw = reinterpret_cast<float*>(base);
+  b.uw = reinterpret_cast<float*>(base + align_up(p.cap_w * 4, 256));
+  b.lb = reinterpret_cast<float*>(base + 2 * align_up(p.cap_w * 4, 256));
+  b.ub = reinterpret_cast<float*>(base + 2 * align_up(p.cap_w * 4, 256) + align_up(p.cap_b * 4, 256));
+  return b;
+}
+
+// lw = uw = identity block at the perturbed positions, lb = ub = embeddings
+// (VerifierForward.py:127-152).  positions are packed into `pos` (up to 4 words).
+struct Positions { int v[4]; };
+
+__global__ void __launch_bounds__(256)
+input_bounds_kernel(const float* __restrict__ emb, float* __restrict__ lw, float* __restrict__ uw,
+                    float* __restrict__ lb, float* __restrict__ ub, int64_t n_w, int64_t n_b, int L, int D, int words,
+                    Positions pos) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const int Di = words * D;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_w; i += stride) {
+    const int j = (int)(i % D);
+    const int m = (int)((i / D) % Di);
+    const int l = (int)((i / ((int64_t)D * Di)) % L);
+    const int w = m / D;
+    const float v = (l == pos.v[w] && (m - w * D) == j) ? 1.f : 0.f;
+    lw[i] = v;
+    uw[i] = v;
+  }
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_b; i += stride) {
+    const float v = emb[i];
+    lb[i] = v;
+    ub[i] = v;
+  }
+}
+
+// classifier folded to one row: w = cls_w[0] - cls_w[1], b = cls_b[0] - cls_b[1]
+// (VerifierForward.py:289-292)
+__global__ void fold_classifier_kernel(const float* __restrict__ cls_w, const float* __restrict__ cls_b,
+                                       float* __restrict__ w, float* __restrict__ b, int D) {
+  for (int j = threadIdx.x; j < D; j += blockDim.x) w[j] = fsub(cls_w[j], cls_w[D + j]);
+  if (threadIdx.x == 0) b[0] = fsub(cls_b[0], cls_b[1]);
+}
+
+#define FB_TRY(expr) do { int rc_ = (expr); if (rc_ != FB_OK) return rc_; } while (0)
+
+int dense(const BoundSet& x, const float* W, const float* bias, const BoundSet& y, int64_t rows, int Di, int Do, int Dy,
+          void* st) {
+  return fb_matmul_f32(x.lw, x.uw, x.lb, x.ub, W, bias, y.lw, y.uw, y.lb, y.ub, rows, Di, Do, Dy, st);
+}
+
+int relax(int op, const BoundSet& x, const BoundSet& y, int64_t rows, int Di, int Do, int words, int p, float eps,
+          int* violation, void* st) {
+  return fb_relax_f32(op, x.lw, x.uw, x.lb, x.ub, y.lw, y.uw, y.lb, y.ub, rows, Di, Do, words, p, eps, FB_NATIVE,
+                      violation, st);
+}
+
+// y = layer_norm(x + r) (mode no_var) or y = x + r (mode "no"); r may be null-valued (no residual)
+int norm_residual(const fb_encoder* e, const BoundSet& x, const BoundSet* r, const float* g, const float* b,
+                  const BoundSet& y, int64_t rows, int Di, int Do, void* st) {
+  if (e->layer_norm == 1) {
+    return fb_layernorm_novar_f32(x.lw, x.uw, x.lb, x.ub, r ? r->lw : nullptr, r ? r->uw : nullptr,
+                                  r ? r->lb : nullptr, r ? r->ub : nullptr, g, b, y.lw, y.uw, y.lb, y.ub, rows, Di, Do, st);
+  }
+  if (r) return fb_add_f32(x.lw, x.uw, x.lb, x.ub, r->lw, r->uw, r->lb, r->ub, y.lw, y.uw, y.lb, y.ub, rows, Di, Do, st);
+  // no norm, no residual: plain copy
+  cudaStream_t s = (cudaStream_t)st;
+  const size_t nw = (size_t)rows * Di * Do * 4, nb = (size_t)rows * Do * 4;
+  FB_CUDA_OK(cudaMemcpyAsync(y.lw, x.lw, nw, cudaMemcpyDeviceToDevice, s));
+  FB_CUDA_OK(cudaMemcpyAsync(y.uw, x.uw, nw, cudaMemcpyDeviceToDevice, s));
+  FB_CUDA_OK(cudaMemcpyAsync(y.lb, x.lb, nb, cudaMemcpyDeviceToDevice, s));
+  FB_CUDA_OK(cudaMemcpyAsync(y.ub, x.ub, nb, cudaMemcpyDeviceToDevice, s));
+  return FB_OK;
+}
+
+}  // namespace
+}  // namespace fb
+
+using namespace fb;
+
+extern "C" int64_t fb_encoder_workspace_bytes(const fb_encoder* enc, int S, int L, int words) {
+  if (!enc || S <= 0 || L <= 0 || words <= 0 || enc->heads <= 0 || enc->d_model % enc->heads != 0) return -1;
+  return make_plan(enc, S, L, words).total;
+}
+
+extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, int S, int L, const int* positions,
+                                      int words, int p, float eps, float* out_l, float* out_u, int* violation,
+                                      void* workspace, int64_t workspace_bytes, void* stream) {
+  if (!enc || !emb || !positions || !out_l || !out_u || !violation || !workspace) return FB_ERR_ARG;
+  if (S <= 0 || L <= 0 || words <= 0 || words > 4 || !valid_norm(p)) return FB_ERR_ARG;
+  if (enc->layers < 0 || enc->heads <= 0 || enc->d_model <= 0 || enc->d_model % enc->heads != 0 || enc->ffn <= 0)
+    return FB_ERR_ARG;
+  if (enc->layer_norm != 0 && enc->layer_norm != 1) return FB_ERR_ARG;
+  for (int w = 0; w < words; ++w)
+    if (positions[w] < 0 || positions[w] >= L) return FB_ERR_ARG;
+  if (!aligned16(workspace)) return FB_ERR_ALIGN;
+  const Plan plan = make_plan(enc, S, L, words);
+  if (workspace_bytes < plan.total) return FB_ERR_WORKSPACE;
+
+  cudaStream_t st = (cudaStream_t)stream;
+  const int D = enc->d_model, H = enc->heads, F = enc->ffn, d = D / H, Di = words * D;
+  const int64_t rows = (int64_t)S * L;
+  char* base = static_cast<char*>(workspace);
+  BoundSet slot[4];
+  for (int i = 0; i < 4; ++i) slot[i] = carve_slot(base + i * plan.slot_bytes, plan);
+  float* range[4];
+  for (int i = 0; i < 4; ++i)
+    range[i] = reinterpret_cast<float*>(base + 4 * plan.slot_bytes + i * align_up(plan.range_floats * 4, 256));
+  float* fold_w = reinterpret_cast<float*>(base + 4 * plan.slot_bytes + 4 * align_up(plan.range_floats * 4, 256));
+  float* fold_b = fold_w + D;
+
+  FB_CUDA_OK(cudaMemsetAsync(violation, 0, sizeof(int), st));
+
+  // slot roles rotate; names follow the walk-through in the file header
+  int A = 0, B = 1, C = 2, Dd = 3;
+  {
+    Positions pos = {{0, 0, 0, 0}};
+    for (int w = 0; w < words; ++w) pos.v[w] = positions[w];
+    const int64_t n_w = rows * Di * D, n_b = rows * D;
+    const int64_t want = ceil_div(n_w, 256), cap = (int64_t)device_info().sms * 16;
+    input_bounds_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, st>>>(emb, slot[B].lw, slot[B].uw, slot[B].lb,
+                                                                             slot[B].ub, n_w, n_b, L, D, words, pos);
+    FB_LAUNCH_OK();
+    FB_TRY(norm_residual(enc, slot[B], nullptr, enc->emb_ln_g, enc->emb_ln_b, slot[A], rows, Di, D, stream));
+  }
+  const float inv_sqrt_d = (float)(1.0 / sqrt((double)d));
+  for (int li = 0; li < enc->layers; ++li) {
+    const fb_encoder_layer& ly = enc->layer[li];
+    const BoundSet &X = slot[A], &T1 = slot[B], &T2 = slot[C], &T3 = slot[Dd];
+    // queries and keys, split into heads: [S*H, L, Di, d]
+    FB_TRY(dense(X, ly.q_w, ly.q_b, T1, rows, Di, D, D, stream));
+    FB_TRY(fb_split_heads_f32(T1.lw, T1.lb, T2.lw, T2.lb, S, L, Di, H, d, 0, stream));
+    FB_TRY(fb_split_heads_f32(T1.uw, T1.ub, T2.uw, T2.ub, S, L, Di, H, d, 0, stream));
+    FB_TRY(dense(X, ly.k_w, ly.k_b, T1, rows, Di, D, D, stream));
+    FB_TRY(fb_split_heads_f32(T1.lw, T1.lb, T3.lw, T3.lb, S, L, Di, H, d, 0, stream));
+    FB_TRY(fb_split_heads_f32(T1.uw, T1.ub, T3.uw, T3.ub, S, L, Di, H, d, 0, stream));
+    // scores [S*H, L, Di, L], scaled by 1/sqrt(d) -> T1
+    FB_TRY(fb_dot_product_f32(T2.lw, T2.uw, T2.lb, T2.ub, T3.lw, T3.uw, T3.lb, T3.ub, T1.lw, T1.uw, T1.lb, T1.ub,
+                              range[0], range[1], range[2], range[3], S * H, L, L, Di, d, words, p, eps, inv_sqrt_d,
+                              FB_NATIVE, stream));
+    const int64_t hrows = (int64_t)S * H * L;
+    // softmax = exp / row sum
+    FB_TRY(relax(FB_EXP, T1, T2, hrows, Di, L, words, p, eps, nullptr, stream));                     // E  -> T2
+    FB_TRY(fb_rowsum_f32(T2.lw, T2.uw, T2.lb, T2.ub, T1.lw, T1.uw, T1.lb, T1.ub, hrows, Di, L, stream));  // sum -> T1
+    FB_TRY(relax(FB_RECIPROCAL, T1, T3, hrows, Di, L, words, p, eps, violation, stream));             // 1/sum -> T3
+    FB_TRY(fb_mul_bounds_f32(T2.lw, T2.uw, T2.lb, T2.ub, T3.lw, T3.uw, T3.lb, T3.ub, T1.lw, T1.uw, T1.lb, T1.ub, hrows,
+                             Di, L, words, p, eps, stream));                                          // probs -> T1
+    // values, split into heads with position/feature swapped: [S*H, d, Di, L]
+    FB_TRY(dense(X, ly.v_w, ly.v_b, T2, rows, Di, D, D, stream));
+    FB_TRY(fb_split_heads_f32(T2.lw, T2.lb, T3.lw, T3.lb, S, L, Di, H, d, 1, stream));
+    FB_TRY(fb_split_heads_f32(T2.uw, T2.ub, T3.uw, T3.ub, S, L, Di, H, d, 1, stream));
+    // context [S*H, L, Di, d] -> T2, merged [S, L, Di, D] -> T1
+    FB_TRY(fb_dot_product_f32(T1.lw, T1.uw, T1.lb, T1.ub, T3.lw, T3.uw, T3.lb, T3.ub, T2.lw, T2.uw, T2.lb, T2.ub,
+                              range[0], range[1], range[2], range[3], S * H, L, d, Di, L, words, p, eps, 1.0f,
+                              FB_NATIVE, stream));
+    FB_TRY(fb_merge_heads_f32(T2.lw, T2.lb, T1.lw, T1.lb, S, L, Di, H, d, stream));
+    FB_TRY(fb_merge_heads_f32(T2.uw, T2.ub, T1.uw, T1.ub, S, L, Di, H, d, stream));
+    // attention output: dense, + residual, layer norm -> T3
+    FB_TRY(dense(T1, ly.ao_w, ly.ao_b, T2, rows, Di, D, D, stream));
+    FB_TRY(norm_residual(enc, T2, &X, ly.ln1_g, ly.ln1_b, T3, rows, Di, D, stream));
+    // feed-forward: dense, relu, dense, + residual, layer norm -> T1
+    FB_TRY(dense(T3, ly.f1_w, ly.f1_b, T1, rows, Di, D, F, stream));
+    FB_TRY(relax(FB_RELU, T1, T2, rows, Di, F, words, p, eps, nullptr, stream));
+    FB_TRY(dense(T2, ly.f2_w, ly.f2_b, T1, rows, Di, F, D, stream));
+    FB_TRY(norm_residual(enc, T1, &T3, ly.ln2_g, ly.ln2_b, T2, rows, Di, D, stream));
+    // the layer output becomes the next layer's input
+    const int newA = C;
+    C = A;
+    A = newA;
+  }
+  {
+    const BoundSet &X = slot[A], &T1 = slot[B], &T2 = slot[C];
+    // first token of every sentence: [S, 1, Di, D]
+    FB_CUDA_OK(cudaMemcpy2DAsync(T1.lw, (size_t)Di * D * 4, X.lw, (size_t)L * Di * D * 4, (size_t)Di * D * 4, S,
+                                 cudaMemcpyDeviceToDevice, st));
+    FB_CUDA_OK(cudaMemcpy2DAsync(T1.uw, (size_t)Di * D * 4, X.uw, (size_t)L * Di * D * 4, (size_t)Di * D * 4, S,
+                                 cudaMemcpyDeviceToDevice, st));
+    FB_CUDA_OK(cudaMemcpy2DAsync(T1.lb, (size_t)D * 4, X.lb, (size_t)L * D * 4, (size_t)D * 4, S,
+                                 cudaMemcpyDeviceToDevice, st));
+    FB_CUDA_OK(cudaMemcpy2DAsync(T1.ub, (size_t)D * 4, X.ub, (size_t)L * D * 4, (size_t)D * 4, S,
+                                 cudaMemcpyDeviceToDevice, st));
+    FB_TRY(dense(T1, enc->pool_w, enc->pool_b, T2, S, Di, D, D, stream));
+    FB_TRY(relax(FB_TANH, T2, T1, S, Di, D, words, p, eps, nullptr, stream));
+    fold_classifier_kernel<<<1, 128, 0, st>>>(enc->cls_w, enc->cls_b, fold_w, fold_b, D);
+    FB_LAUNCH_OK();
+    FB_TRY(dense(T1, fold_w, fold_b, T2, S, Di, D, 1, stream));
+    FB_TRY(fb_concretize_f32(T2.lw, T2.uw, T2.lb, T2.ub, out_l, out_u, S, Di, 1, words, p, eps, FB_NATIVE, stream));
+  }
+  return FB_OK;
+}

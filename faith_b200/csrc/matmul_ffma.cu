@@ -1,0 +1,235 @@
+// Split-sign product of bounds with a constant weight, exact-fp32 path (CUDA-core FFMA).
+//
+//   y_lw = x_lw W+ + x_uw W-        y_uw = x_lw W- + x_uw W+       (Bounds.py:403-412)
+//
+// is evaluated in centre/radius form, which needs half the multiply-adds:
+//   c = (x_lw + x_uw)/2, r = (x_uw - x_lw)/2,  y_c = c W,  y_r = r |W|,
+//   y_lw = y_c - y_r,  y_uw = y_c + y_r.
+// Every product and accumulation is fp32, so the result has the error class of the reference's
+// fp32 GEMMs (different summation order, one extra rounding for c and r).
+//
+// Tiling: 128 x 128 output tile per block, K in steps of 16, 256 threads with an 8 x 8 micro
+// tile and two accumulators (centre, radius) each; global loads of the next K step are issued
+// into registers before the current step is computed (two shared-memory stages).
+#include "common.cuh"
+
+namespace fb {
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 16;
+constexpr int LD = BM + 4;  // padded leading dimension of the k-major shared tiles
+constexpr int kThreads = 256;
+constexpr int kStageFloats = 3 * BK * LD;  // centre, radius, weight
+
+// A: [M, K] row-major (two of them: lower and upper side); W: [N, K] row-major.
+template <bool VEC>
+__global__ void __launch_bounds__(kThreads)
+split_sign_gemm_ffma(const float* __restrict__ a_lo, const float* __restrict__ a_up,
+                     const float* __restrict__ W, const float* __restrict__ bias,
+                     float* __restrict__ c_lo, float* __restrict__ c_up, int64_t M, int N, int K) {
+  extern __shared__ __align__(16) float smem[];
+  const int tid = threadIdx.x;
+  const int tx = tid & 15, ty = tid >> 4;
+  const int64_t m0 = (int64_t)blockIdx.x * BM;
+  const int n0 = blockIdx.y * BN;
+
+  float acc_c[8][8], acc_r[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { acc_c[i][j] = 0.f; acc_r[i][j] = 0.f; }
+
+  // global -> register staging: 2 float4 per thread per operand
+  float4 g_lo[2], g_up[2], g_w[2];
+  auto load_tile = [&](int k0) {
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const int f = tid + kThreads * q;
+      const int r = f >> 2, kk = k0 + (f & 3) * 4;
+      const int64_t m = m0 + r;
+      const int n = n0 + r;
+      float4 lo = make_float4(0.f, 0.f, 0.f, 0.f), up = lo, w = lo;
+      if (VEC) {
+        if (kk < K) {
+          if (m < M) {
+            lo = __ldg(reinterpret_cast<const float4*>(a_lo + m * K + kk));
+            up = __ldg(reinterpret_cast<const float4*>(a_up + m * K + kk));
+          }
+          if (n < N) w = __ldg(reinterpret_cast<const float4*>(W + (int64_t)n * K + kk));
+        }
+      } else {
+        float tl[4] = {0.f, 0.f, 0.f, 0.f}, tu[4] = {0.f, 0.f, 0.f, 0.f}, tw[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          if (kk + e < K) {
+            if (m < M) { tl[e] = __ldg(a_lo + m * K + kk + e); tu[e] = __ldg(a_up + m * K + kk + e); }
+            if (n < N) tw[e] = __ldg(W + (int64_t)n * K + kk + e);
+          }
+        }
+        lo = make_float4(tl[0], tl[1], tl[2], tl[3]);
+        up = make_float4(tu[0], tu[1], tu[2], tu[3]);
+        w = make_float4(tw[0], tw[1], tw[2], tw[3]);
+      }
+      g_lo[q] = lo; g_up[q] = up; g_w[q] = w;
+    }
+  };
+  auto store_tile = [&](int stage) {
+    float* s_c = smem + stage * kStageFloats;
+    float* s_r = s_c + BK * LD;
+    float* s_w = s_r + BK * LD;
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const int f = tid + kThreads * q;
+      const int r = f >> 2, kq = (f & 3) * 4;
+      const float lo[4] = {g_lo[q].x, g_lo[q].y, g_lo[q].z, g_lo[q].w};
+      const float up[4] = {g_up[q].x, g_up[q].y, g_up[q].z, g_up[q].w};
+      const float w[4] = {g_w[q].x, g_w[q].y, g_w[q].z, g_w[q].w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        s_c[(kq + e) * LD + r] = fmul(fadd(lo[e], up[e]), 0.5f);
+        s_r[(kq + e) * LD + r] = fmul(fsub(up[e], lo[e]), 0.5f);
+        s_w[(kq + e) * LD + r] = w[e];
+      }
+    }
+  };
+
+  const int ktiles = (K + BK - 1) / BK;
+  load_tile(0);
+  store_tile(0);
+  __syncthreads();
+  for (int t = 0; t < ktiles; ++t) {
+    const int cur = t & 1;
+    if (t + 1 < ktiles) load_tile((t + 1) * BK);
+    const float* s_c = smem + cur * kStageFloats;
+    const float* s_r = s_c + BK * LD;
+    const float* s_w = s_r + BK * LD;
+#pragma unroll
+    for (int k = 0; k < BK; ++k) {
+      float ac[8], ar[8], w[8], wa[8];
+      *reinterpret_cast<float4*>(ac) = *reinterpret_cast<const float4*>(s_c + k * LD + ty * 4);
+      *reinterpret_cast<float4*>(ac + 4) = *reinterpret_cast<const float4*>(s_c + k * LD + 64 + ty * 4);
+      *reinterpret_cast<float4*>(ar) = *reinterpret_cast<const float4*>(s_r + k * LD + ty * 4);
+      *reinterpret_cast<float4*>(ar + 4) = *reinterpret_cast<const float4*>(s_r + k * LD + 64 + ty * 4);
+      *reinterpret_cast<float4*>(w) = *reinterpret_cast<const float4*>(s_w + k * LD + tx * 4);
+      *reinterpret_cast<float4*>(w + 4) = *reinterpret_cast<const float4*>(s_w + k * LD + 64 + tx * 4);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) wa[j] = fabsf(w[j]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          acc_c[i][j] = fmaf(ac[i], w[j], acc_c[i][j]);
+          acc_r[i][j] = fmaf(ar[i], wa[j], acc_r[i][j]);
+        }
+    }
+    if (t + 1 < ktiles) store_tile(cur ^ 1);
+    __syncthreads();
+  }
+
+  // epilogue: y_lo = centre - radius, y_up = centre + radius (+ bias)
+  const bool vec_out = (N % 4 == 0) && aligned16(c_lo) && aligned16(c_up);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int64_t m = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
+    if (m >= M) continue;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int n = n0 + h * 64 + tx * 4;
+      float lo[4], up[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float b = (bias != nullptr && n + e < N) ? bias[n + e] : 0.f;
+        lo[e] = fsub(acc_c[i][h * 4 + e], acc_r[i][h * 4 + e]);
+        up[e] = fadd(acc_c[i][h * 4 + e], acc_r[i][h * 4 + e]);
+        if (bias != nullptr) { lo[e] = fadd(lo[e], b); up[e] = fadd(up[e], b); }
+      }
+      if (vec_out && n + 3 < N) {
+        *reinterpret_cast<float4*>(c_lo + m * N + n) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+        *reinterpret_cast<float4*>(c_up + m * N + n) = make_float4(up[0], up[1], up[2], up[3]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (n + e < N) { c_lo[m * N + n + e] = lo[e]; c_up[m * N + n + e] = up[e]; }
+      }
+    }
+  }
+}
+
+// Narrow outputs (N <= 16, e.g. a classifier head): one warp per row of A, lanes across K,
+// each lane accumulates all N outputs; HBM-bound on reading A once.
+template <int NMAX>
+__global__ void __launch_bounds__(kThreads)
+split_sign_gemv_rows(const float* __restrict__ a_lo, const float* __restrict__ a_up,
+                     const float* __restrict__ W, const float* __restrict__ bias,
+                     float* __restrict__ c_lo, float* __restrict__ c_up, int64_t M, int N, int K) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * (kThreads / 32);
+  for (int64_t m = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5); m < M; m += warps) {
+    float sc[NMAX], sr[NMAX];
+#pragma unroll
+    for (int n = 0; n < NMAX; ++n) { sc[n] = 0.f; sr[n] = 0.f; }
+    for (int k = lane; k < K; k += 32) {
+      const float lo = __ldg(a_lo + m * K + k), up = __ldg(a_up + m * K + k);
+      const float c = fmul(fadd(lo, up), 0.5f), r = fmul(fsub(up, lo), 0.5f);
+#pragma unroll
+      for (int n = 0; n < NMAX; ++n) {
+        if (n < N) {
+          const float w = __ldg(W + (int64_t)n * K + k);
+          sc[n] = fmaf(c, w, sc[n]);
+          sr[n] = fmaf(r, fabsf(w), sr[n]);
+        }
+      }
+    }
+#pragma unroll
+    for (int n = 0; n < NMAX; ++n) {
+#pragma unroll
+      for (int s = 16; s > 0; s >>= 1) {
+        sc[n] += __shfl_xor_sync(0xffffffffu, sc[n], s);
+        sr[n] += __shfl_xor_sync(0xffffffffu, sr[n], s);
+      }
+    }
+    if (lane == 0) {
+#pragma unroll
+      for (int n = 0; n < NMAX; ++n) {
+        if (n < N) {
+          float lo = fsub(sc[n], sr[n]), up = fadd(sc[n], sr[n]);
+          if (bias != nullptr) { lo = fadd(lo, bias[n]); up = fadd(up, bias[n]); }
+          c_lo[m * N + n] = lo;
+          c_up[m * N + n] = up;
+        }
+      }
+    }
+  }
+}
+
+}  // namespace
+
+// One split-sign GEMM: (a_lo, a_up) [M, K] x W[N, K]^T (+ bias) -> (c_lo, c_up) [M, N].
+int launch_split_sign_ffma(const float* a_lo, const float* a_up, const float* W, const float* bias, float* c_lo,
+                           float* c_up, int64_t M, int N, int K, cudaStream_t st) {
+  if (M == 0 || N == 0) return FB_OK;
+  if (N <= 16) {
+    const int64_t want = ceil_div(M, kThreads / 32);
+    const int64_t cap = (int64_t)device_info().sms * 16;
+    const unsigned blocks = (unsigned)(want < cap ? want : cap);
+    split_sign_gemv_rows<16><<<blocks, kThreads, 0, st>>>(a_lo, a_up, W, bias, c_lo, c_up, M, N, K);
+    FB_LAUNCH_OK();
+    return FB_OK;
+  }
+  const int64_t gm = ceil_div(M, BM);
+  const int gn = (int)ceil_div(N, BN);
+  if (gm > 0x7fffffff || gn > 65535) return FB_ERR_SHAPE;
+  const size_t smem = sizeof(float) * 2 * kStageFloats;
+  const bool vec = K % 4 == 0 && aligned16(a_lo) && aligned16(a_up) && aligned16(W);
+  if (vec) {
+    FB_CUDA_OK(cudaFuncSetAttribute(split_sign_gemm_ffma<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    split_sign_gemm_ffma<true><<<dim3((unsigned)gm, gn), kThreads, smem, st>>>(a_lo, a_up, W, bias, c_lo, c_up, M, N, K);
+  } else {
+    FB_CUDA_OK(cudaFuncSetAttribute(split_sign_gemm_ffma<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    split_sign_gemm_ffma<false><<<dim3((unsigned)gm, gn), kThreads, smem, st>>>(a_lo, a_up, W, bias, c_lo, c_up, M, N, K);
+  }
+  FB_LAUNCH_OK();
+  return FB_OK;
+}
+
+}  // namespace fb

@@ -1,0 +1,230 @@
+"""Thin tensor-level wrappers over the C ABI: argument checks, output allocation, stream.
+
+PyTorch is used only for device memory and the current stream; all arithmetic happens in
+libfaith_b200.so.  Every tensor must be a contiguous float32 CUDA tensor.
+"""
+import math
+
+import torch
+
+from . import _lib
+from ._lib import (FB_EXP, FB_NATIVE, FB_P1, FB_P2, FB_PINF, FB_RECIPROCAL, FB_RELU, FB_TANH, FB_TRANSPOSED,
+                   check, load)
+
+
+def norm_code(p):
+    """Maps the perturbation norm p to the C enum (the dual exponent is implied)."""
+    if p == 1:
+        return FB_P1
+    if p == 2:
+        return FB_P2
+    if p == float("inf") or p >= 10:  # the reference treats p >= 10 as infinity (Verifier.py:17)
+        return FB_PINF
+    raise ValueError("only p in {1, 2, inf} is supported, got %r" % (p,))
+
+
+def _chk(*tensors):
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise _lib.FaithError("faith_b200 operators need CUDA tensors (there is no CPU path)")
+        if t.dtype != torch.float32:
+            raise _lib.FaithError("float32 tensors required, got %s" % t.dtype)
+        if not t.is_contiguous():
+            raise _lib.FaithError("contiguous tensors required")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise _lib.FaithError("all tensors must live on one device")
+    return dev
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t):
+    return None if t is None else t.data_ptr()
+
+
+def concretize(lw, uw, lb, ub, p, eps, words=1, layout=FB_NATIVE):
+    dev = _chk(lw, uw, lb, ub)
+    rows = lb.numel() // lb.shape[-1]
+    Do = lb.shape[-1]
+    Di = lw.shape[-2] if layout == FB_NATIVE else lw.shape[-1]
+    l, u = torch.empty_like(lb), torch.empty_like(ub)
+    with torch.cuda.device(dev):
+        check(load().fb_concretize_f32(_p(lw), _p(uw), _p(lb), _p(ub), _p(l), _p(u), rows, Di, Do, words,
+                                       norm_code(p), eps, layout, _stream()), "fb_concretize_f32")
+    return l, u
+
+
+def relax(op, lw, uw, lb, ub, p, eps, words=1, layout=FB_NATIVE, out=None, violation=None):
+    dev = _chk(lw, uw, lb, ub)
+    rows = lb.numel() // lb.shape[-1]
+    Do = lb.shape[-1]
+    Di = lw.shape[-2] if layout == FB_NATIVE else lw.shape[-1]
+    if out is None:
+        out = (torch.empty_like(lw), torch.empty_like(uw), torch.empty_like(lb), torch.empty_like(ub))
+    o_lw, o_uw, o_lb, o_ub = out
+    _chk(o_lw, o_uw, o_lb, o_ub, violation)
+    with torch.cuda.device(dev):
+        check(load().fb_relax_f32(op, _p(lw), _p(uw), _p(lb), _p(ub), _p(o_lw), _p(o_uw), _p(o_lb), _p(o_ub),
+                                  rows, Di, Do, words, norm_code(p), eps, layout, _p(violation), _stream()),
+              "fb_relax_f32")
+    return o_lw, o_uw, o_lb, o_ub
+
+
+def matmul(lw, uw, lb, ub, W, bias=None):
+    dev = _chk(lw, uw, lb, ub, W, bias)
+    rows = lb.numel() // lb.shape[-1]
+    Di, Do = lw.shape[-2], lw.shape[-1]
+    Dy = W.shape[0]
+    if W.shape[1] != Do:
+        raise _lib.FaithError("weight shape %s does not match feature size %d" % (tuple(W.shape), Do))
+    y_lw = torch.empty(lw.shape[:-1] + (Dy,), device=dev, dtype=torch.float32)
+    y_uw = torch.empty_like(y_lw)
+    y_lb = torch.empty(lb.shape[:-1] + (Dy,), device=dev, dtype=torch.float32)
+    y_ub = torch.empty_like(y_lb)
+    with torch.cuda.device(dev):
+        check(load().fb_matmul_f32(_p(lw), _p(uw), _p(lb), _p(ub), _p(W), _p(bias), _p(y_lw), _p(y_uw), _p(y_lb),
+                                   _p(y_ub), rows, Di, Do, Dy, _stream()), "fb_matmul_f32")
+    return y_lw, y_uw, y_lb, y_ub
+
+
+def dot_product(x, y, p, eps, words=1, out_scale=1.0, layout=FB_NATIVE, scratch=None, out=None):
+    """x, y: (lw, uw, lb, ub).  Returns (z_lw, z_uw, z_lb, z_ub)."""
+    x_lw, x_uw, x_lb, x_ub = x
+    y_lw, y_uw, y_lb, y_ub = y
+    dev = _chk(*x, *y)
+    B, Lx, K = x_lb.shape
+    Ly = y_lb.shape[1]
+    Di = x_lw.shape[2] if layout == FB_NATIVE else x_lw.shape[3]
+    if out is None:
+        zshape = (B, Lx, Di, Ly) if layout == FB_NATIVE else (B, Lx, Ly, Di)
+        out = (torch.empty(zshape, device=dev), torch.empty(zshape, device=dev),
+               torch.empty((B, Lx, Ly), device=dev), torch.empty((B, Lx, Ly), device=dev))
+    if scratch is None:
+        scratch = (torch.empty_like(x_lb), torch.empty_like(x_lb), torch.empty_like(y_lb), torch.empty_like(y_lb))
+    x_l, x_u, y_l, y_u = scratch
+    z_lw, z_uw, z_lb, z_ub = out
+    _chk(*out, *scratch)
+    with torch.cuda.device(dev):
+        check(load().fb_dot_product_f32(_p(x_lw), _p(x_uw), _p(x_lb), _p(x_ub), _p(y_lw), _p(y_uw), _p(y_lb), _p(y_ub),
+                                        _p(z_lw), _p(z_uw), _p(z_lb), _p(z_ub), _p(x_l), _p(x_u), _p(y_l), _p(y_u),
+                                        B, Lx, Ly, Di, K, words, norm_code(p), eps, out_scale, layout, _stream()),
+              "fb_dot_product_f32")
+    return out
+
+
+def mul_bounds(x, y, p, eps, words=1):
+    dev = _chk(*x, *y)
+    x_lw, x_uw, x_lb, x_ub = x
+    rows = x_lb.numel() // x_lb.shape[-1]
+    Di, Do = x_lw.shape[-2], x_lw.shape[-1]
+    out = (torch.empty_like(x_lw), torch.empty_like(x_lw), torch.empty_like(x_lb), torch.empty_like(x_lb))
+    with torch.cuda.device(dev):
+        check(load().fb_mul_bounds_f32(*[_p(t) for t in x], *[_p(t) for t in y], *[_p(t) for t in out],
+                                       rows, Di, Do, words, norm_code(p), eps, _stream()), "fb_mul_bounds_f32")
+    return out
+
+
+def add(x, y):
+    dev = _chk(*x, *y)
+    x_lw, x_uw, x_lb, x_ub = x
+    rows = x_lb.numel() // x_lb.shape[-1]
+    Di, Do = x_lw.shape[-2], x_lw.shape[-1]
+    out = (torch.empty_like(x_lw), torch.empty_like(x_lw), torch.empty_like(x_lb), torch.empty_like(x_lb))
+    with torch.cuda.device(dev):
+        check(load().fb_add_f32(*[_p(t) for t in x], *[_p(t) for t in y], *[_p(t) for t in out], rows, Di, Do,
+                                _stream()), "fb_add_f32")
+    return out
+
+
+def scale(x, c):
+    dev = _chk(*x)
+    x_lw, x_uw, x_lb, x_ub = x
+    rows = x_lb.numel() // x_lb.shape[-1]
+    Di, Do = x_lw.shape[-2], x_lw.shape[-1]
+    out = (torch.empty_like(x_lw), torch.empty_like(x_lw), torch.empty_like(x_lb), torch.empty_like(x_lb))
+    with torch.cuda.device(dev):
+        check(load().fb_scale_f32(*[_p(t) for t in x], *[_p(t) for t in out], rows, Di, Do, float(c), _stream()),
+              "fb_scale_f32")
+    return out
+
+
+def rowsum(x):
+    dev = _chk(*x)
+    x_lw, x_uw, x_lb, x_ub = x
+    rows = x_lb.numel() // x_lb.shape[-1]
+    Di, Do = x_lw.shape[-2], x_lw.shape[-1]
+    out = (torch.empty_like(x_lw), torch.empty_like(x_lw), torch.empty_like(x_lb), torch.empty_like(x_lb))
+    with torch.cuda.device(dev):
+        check(load().fb_rowsum_f32(*[_p(t) for t in x], *[_p(t) for t in out], rows, Di, Do, _stream()),
+              "fb_rowsum_f32")
+    return out
+
+
+def layernorm_novar(x, gamma, beta, residual=None):
+    dev = _chk(*x, gamma, beta, *(residual or ()))
+    x_lw, x_uw, x_lb, x_ub = x
+    rows = x_lb.numel() // x_lb.shape[-1]
+    Di, Do = x_lw.shape[-2], x_lw.shape[-1]
+    out = (torch.empty_like(x_lw), torch.empty_like(x_lw), torch.empty_like(x_lb), torch.empty_like(x_lb))
+    r = [_p(t) for t in residual] if residual is not None else [None] * 4
+    with torch.cuda.device(dev):
+        check(load().fb_layernorm_novar_f32(*[_p(t) for t in x], *r, _p(gamma), _p(beta), *[_p(t) for t in out],
+                                            rows, Di, Do, _stream()), "fb_layernorm_novar_f32")
+    return out
+
+
+def split_heads(x, heads, transpose_ld=False):
+    """(lw, uw, lb, ub) [B, L, Di, H*d] -> [B*H, L, Di, d], or [B*H, d, Di, L] with transpose_ld."""
+    dev = _chk(*x)
+    lw, uw, lb, ub = x
+    B, L, Di, D = lw.shape
+    d = D // heads
+    wshape = (B * heads, d, Di, L) if transpose_ld else (B * heads, L, Di, d)
+    bshape = (B * heads, d, L) if transpose_ld else (B * heads, L, d)
+    out = (torch.empty(wshape, device=dev), torch.empty(wshape, device=dev),
+           torch.empty(bshape, device=dev), torch.empty(bshape, device=dev))
+    with torch.cuda.device(dev):
+        for w, b, ow, ob in ((lw, lb, out[0], out[2]), (uw, ub, out[1], out[3])):
+            check(load().fb_split_heads_f32(_p(w), _p(b), _p(ow), _p(ob), B, L, Di, heads, d, int(transpose_ld),
+                                            _stream()), "fb_split_heads_f32")
+    return out
+
+
+def merge_heads(x, heads):
+    """(lw, uw, lb, ub) [B*H, L, Di, d] -> [B, L, Di, H*d]."""
+    dev = _chk(*x)
+    lw, uw, lb, ub = x
+    BH, L, Di, d = lw.shape
+    B = BH // heads
+    out = (torch.empty((B, L, Di, heads * d), device=dev), torch.empty((B, L, Di, heads * d), device=dev),
+           torch.empty((B, L, heads * d), device=dev), torch.empty((B, L, heads * d), device=dev))
+    with torch.cuda.device(dev):
+        for w, b, ow, ob in ((lw, lb, out[0], out[2]), (uw, ub, out[1], out[3])):
+            check(load().fb_merge_heads_f32(_p(w), _p(b), _p(ow), _p(ob), B, L, Di, heads, d, _stream()),
+                  "fb_merge_heads_f32")
+    return out
+
+
+def conv2d(x, weight, bias, stride, padding):
+    """x: (lw, uw, lb, ub) with lw, uw [B, Di, C, H, W] and lb, ub [B, C, H, W]."""
+    dev = _chk(*x, weight, bias)
+    lw, uw, lb, ub = x
+    B, Di, C, H, W = lw.shape
+    Co, Ci, Kh, Kw = weight.shape
+    if Ci != C:
+        raise _lib.FaithError("conv weight expects %d input channels, bounds have %d" % (Ci, C))
+    Ho = (H + 2 * padding - Kh) // stride + 1
+    Wo = (W + 2 * padding - Kw) // stride + 1
+    out = (torch.empty((B, Di, Co, Ho, Wo), device=dev), torch.empty((B, Di, Co, Ho, Wo), device=dev),
+           torch.empty((B, Co, Ho, Wo), device=dev), torch.empty((B, Co, Ho, Wo), device=dev))
+    with torch.cuda.device(dev):
+        check(load().fb_conv2d_f32(*[_p(t) for t in x], _p(weight), _p(bias), *[_p(t) for t in out],
+                                   B, Di, C, H, W, Co, Kh, Kw, stride, padding, _stream()), "fb_conv2d_f32")
+    return out

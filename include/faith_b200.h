@@ -1,0 +1,191 @@
+/*
+ * faith_b200 -- forward linear-bound propagation operators for NVIDIA B200 (sm_100a).
+ *
+ * C ABI of the shared library libfaith_b200.so.  Every entry point
+ *   - takes plain device pointers (fp32) and sizes, plus a CUDA stream passed as void*
+ *     (a cudaStream_t; NULL = the legacy default stream),
+ *   - enqueues its kernels on that stream and returns without synchronising,
+ *   - never allocates or frees device memory: outputs and scratch belong to the caller,
+ *   - returns an fb_status code instead of aborting.
+ *
+ * A bound object carries four tensors (reference: Transformer_Verification_Code/Verifiers/
+ * Bounds.py:270-297):
+ *     lw, uw : [rows, Di, Do]      rows = batch * length (row-major, Do contiguous)
+ *     lb, ub : [rows, Do]
+ * This is the reference's PyTorch layout ("native").  The reference's pybind entry points
+ * (HandTunedKernels/kernel.cpp:69-241) pass lw/uw transposed, [rows, Do, Di] with Di
+ * contiguous (Bounds.py:1203-1211); entry points that accept it take `layout`.
+ *
+ * The dual norm is selected by `p` (Bounds.py:277): FB_P1 -> max-abs, FB_P2 -> Euclidean,
+ * FB_PINF -> sum-abs.  `words` is the number of perturbed words: the Di axis is split into
+ * `words` equal blocks whose norms are added (Bounds.py:319-326).  `eps` is the perturbation
+ * radius.
+ */
+#ifndef FAITH_B200_H
+#define FAITH_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum fb_status {
+  FB_OK = 0,
+  FB_ERR_ARG = 1,     /* null pointer, negative size, unknown enum value */
+  FB_ERR_SHAPE = 2,   /* sizes the kernels do not support (documented per function) */
+  FB_ERR_ALIGN = 3,   /* pointer not aligned to 16 bytes where the vector path needs it */
+  FB_ERR_CUDA = 4,    /* a CUDA runtime call or launch failed; see fb_last_cuda_error() */
+  FB_ERR_WORKSPACE = 5 /* caller-provided scratch too small */
+};
+
+enum fb_norm { FB_P1 = 1, FB_P2 = 2, FB_PINF = 3 };
+enum fb_layout { FB_NATIVE = 0 /* [rows, Di, Do] */, FB_TRANSPOSED = 1 /* [rows, Do, Di] */ };
+
+/* Relaxation selector of fb_relax_f32. */
+enum fb_relax_op { FB_RELU = 0, FB_TANH = 1, FB_EXP = 2, FB_RECIPROCAL = 3 };
+
+const char* fb_status_string(int status);
+/* cudaError_t (as int) of the most recent FB_ERR_CUDA on the calling thread. */
+int fb_last_cuda_error(void);
+int fb_version(void);
+
+/* l = lb - eps * sum_w ||lw_w||_q,  u = ub + eps * sum_w ||uw_w||_q      (out: [rows, Do]).
+ * Replaces Bounds.concretize (Bounds.py:311-326) and the reference kernel `concretize`
+ * (HandTunedKernels/dot_product_verification.cu:47-105). */
+int fb_concretize_f32(const float* lw, const float* uw, const float* lb, const float* ub,
+                      float* l, float* u,
+                      int64_t rows, int Di, int Do, int words, int p, float eps, int layout,
+                      void* stream);
+
+/* Fused concretise + per-column linear relaxation + column rescale of lw/uw.
+ *   op = FB_RELU        Bounds.ori_relu  (Bounds.py:921-963); kernel.cpp:69-99 c_relu_verification
+ *   op = FB_TANH        Bounds.ori_tanh  (Bounds.py:1027-1103); kernel.cpp:101-131 c_tanh_verification
+ *   op = FB_EXP         Bounds.exp       (Bounds.py:970-1003)
+ *   op = FB_RECIPROCAL  Bounds.reciprocal (Bounds.py:1136-1161)
+ * Outputs have the shape and layout of the inputs and must not alias them.
+ * `violation` (device int, may be NULL) is set to 1 by FB_RECIPROCAL when some concretised
+ * lower bound is below 1e-12, the condition the reference asserts on (Bounds.py:1147); the
+ * caller zeroes it beforehand. */
+int fb_relax_f32(int op,
+                 const float* lw, const float* uw, const float* lb, const float* ub,
+                 float* out_lw, float* out_uw, float* out_lb, float* out_ub,
+                 int64_t rows, int Di, int Do, int words, int p, float eps, int layout,
+                 int* violation, void* stream);
+
+/* Product with a constant weight W [Dy, Do] (nn.Linear layout) and optional bias [Dy]
+ * (NULL = none): y_lw = x_lw W+ + x_uw W-, y_uw = x_lw W- + x_uw W+, same for lb/ub, then
+ * + bias.  Replaces Bounds.ori_matmul / dense (Bounds.py:397-413, 1016-1025) and the
+ * commented-out c_matmul_verification (kernel.cpp:243-266).  Native layout only.
+ * x_lw, x_uw: [rows, Di, Do]; y_lw, y_uw: [rows, Di, Dy]. */
+int fb_matmul_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+                  const float* W, const float* bias,
+                  float* y_lw, float* y_uw, float* y_lb, float* y_ub,
+                  int64_t rows, int Di, int Do, int Dy, void* stream);
+
+/* Bound x bound dot product  z[b,i,j] = sum_k x[b,i,k] * y[b,j,k]  (attention scores and,
+ * with y = transposed values, the attention context).  Replaces Bounds.ori_dot_product
+ * (Bounds.py:710-823) and c_dot_product_verification_QK / _V (kernel.cpp:133-241).
+ *   native:      x_lw,x_uw [B,Lx,Di,K]  y_lw,y_uw [B,Ly,Di,K]  z_lw,z_uw [B,Lx,Di,Ly]
+ *   transposed:  x_lw,x_uw [B,Lx,K,Di]  y_lw,y_uw [B,Ly,K,Di]  z_lw,z_uw [B,Lx,Ly,Di]
+ *   x_lb,x_ub [B,Lx,K]   y_lb,y_ub [B,Ly,K]   z_lb,z_ub [B,Lx,Ly]
+ * x_l,x_u [B,Lx,K] and y_l,y_u [B,Ly,K] are caller-provided scratch that receives the
+ * concretised ranges of the operands (as in the reference, Bounds.py:1274-1277).
+ * Every output is multiplied by `out_scale` (1/sqrt(d) of the attention scores,
+ * VerifierForward.py:232-233; must be > 0; pass 1.0f for the plain operator). */
+int fb_dot_product_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+                       const float* y_lw, const float* y_uw, const float* y_lb, const float* y_ub,
+                       float* z_lw, float* z_uw, float* z_lb, float* z_ub,
+                       float* x_l, float* x_u, float* y_l, float* y_u,
+                       int B, int Lx, int Ly, int Di, int K, int words, int p, float eps,
+                       float out_scale, int layout, void* stream);
+
+/* Elementwise product of two bounded quantities (McCormick planes), fused with the
+ * concretisation of both operands.  Replaces Bounds.multiply(Bounds) (Bounds.py:608-651). */
+int fb_mul_bounds_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+                      const float* y_lw, const float* y_uw, const float* y_lb, const float* y_ub,
+                      float* z_lw, float* z_uw, float* z_lb, float* z_ub,
+                      int64_t rows, int Di, int Do, int words, int p, float eps, void* stream);
+
+/* z = x + y on all four tensors (Bounds.add with a Bounds argument, Bounds.py:383-389).
+ * In-place (z == x) is allowed. */
+int fb_add_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+               const float* y_lw, const float* y_uw, const float* y_lb, const float* y_ub,
+               float* z_lw, float* z_uw, float* z_lb, float* z_ub,
+               int64_t rows, int Di, int Do, void* stream);
+
+/* Multiplication by a scalar; a non-positive scalar swaps the two sides
+ * (Bounds.multiply(float), Bounds.py:594-607).  In-place is NOT allowed. */
+int fb_scale_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+                 float* z_lw, float* z_uw, float* z_lb, float* z_ub,
+                 int64_t rows, int Di, int Do, float c, void* stream);
+
+/* Sum over the feature axis, broadcast back to every feature: the denominator of the softmax
+ * (Bounds.softmax, Bounds.py:1007-1013).  Shapes as the input. */
+int fb_rowsum_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+                  float* z_lw, float* z_uw, float* z_lb, float* z_ub,
+                  int64_t rows, int Di, int Do, void* stream);
+
+/* Layer normalisation without the variance ("no_var", Bounds.py:1111-1131), optionally fused
+ * with a preceding residual add: t = x (+ r); t -= mean over features of the opposite side;
+ * out = t * gamma (split by sign of gamma) + beta on lb/ub.  r_* may all be NULL. */
+int fb_layernorm_novar_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+                           const float* r_lw, const float* r_uw, const float* r_lb, const float* r_ub,
+                           const float* gamma, const float* beta,
+                           float* z_lw, float* z_uw, float* z_lb, float* z_ub,
+                           int64_t rows, int Di, int Do, void* stream);
+
+/* Head split [B, L, Di, H*d] -> [B*H, L, Di, d] (VerifierForward.py:208-229) and its inverse
+ * (VerifierForward.py:253-265).  With transpose_ld != 0 the split additionally swaps the
+ * position and feature axes, giving [B*H, d, Di, L]: the operand `value.t()` of the attention
+ * context (Bounds.py:843-850) in contiguous form. */
+int fb_split_heads_f32(const float* x_w, const float* x_b, float* z_w, float* z_b,
+                       int B, int L, int Di, int H, int d, int transpose_ld, void* stream);
+int fb_merge_heads_f32(const float* x_w, const float* x_b, float* z_w, float* z_b,
+                       int B, int L, int Di, int H, int d, void* stream);
+
+/* Bound of a 2-D convolution with constant weights (split by sign like fb_matmul_f32); dim_in
+ * is the batch axis of the convolution.  Replaces the commented-out
+ * c_convolution_verification (kernel.cpp:268-295).
+ * x_lw,x_uw [B, Di, Cin, H, W]; x_lb,x_ub [B, Cin, H, W]; Wt [Cout, Cin, Kh, Kw]; bias [Cout] or
+ * NULL; y_lw,y_uw [B, Di, Cout, Ho, Wo]; y_lb,y_ub [B, Cout, Ho, Wo]. */
+int fb_conv2d_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+                  const float* Wt, const float* bias,
+                  float* y_lw, float* y_uw, float* y_lb, float* y_ub,
+                  int B, int Di, int Cin, int H, int W, int Cout, int Kh, int Kw,
+                  int stride, int pad, void* stream);
+
+/* ---- whole-model driver: forward bound pass of a BERT-style encoder ---------------------
+ * Follows VerifierForward.verify_safety (VerifierForward.py:93-119) for a batch of S
+ * sentences with one set of perturbed positions; no epsilon search.  Weights are device
+ * pointers in nn.Linear layout. */
+typedef struct fb_encoder_layer {
+  const float *q_w, *q_b, *k_w, *k_b, *v_w, *v_b, *ao_w, *ao_b, *ln1_g, *ln1_b;
+  const float *f1_w, *f1_b, *f2_w, *f2_b, *ln2_g, *ln2_b;
+} fb_encoder_layer;
+
+typedef struct fb_encoder {
+  int layers, d_model, heads, ffn;
+  int layer_norm;                 /* 0 = "no", 1 = "no_var" */
+  const float *emb_ln_g, *emb_ln_b;
+  const fb_encoder_layer* layer;  /* host array of `layers` entries */
+  const float *pool_w, *pool_b;   /* [d_model, d_model], [d_model] */
+  const float *cls_w, *cls_b;     /* [2, d_model], [2] */
+} fb_encoder;
+
+/* Bytes of scratch fb_encoder_forward_f32 needs for S sentences of length L. */
+int64_t fb_encoder_workspace_bytes(const fb_encoder* enc, int S, int L, int words);
+
+/* emb [S, L, d_model] (device); positions[words] (host) = perturbed token indices;
+ * out_l, out_u [S] (device) = concretised bounds of logit0 - logit1;
+ * violation [1] (device int, zeroed by the call): set when a softmax denominator was not
+ * provably positive (the reference's assertion, Bounds.py:1147). */
+int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, int S, int L,
+                           const int* positions, int words, int p, float eps,
+                           float* out_l, float* out_u, int* violation,
+                           void* workspace, int64_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FAITH_B200_H */

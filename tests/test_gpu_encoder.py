@@ -1,0 +1,137 @@
+"""The C++ whole-model driver against the CPU oracle: per-stage noise budget, golden vectors and
+sampled containment of concrete forward passes."""
+import pytest
+import torch
+
+import cases
+import helpers
+from oracle import bounds_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _small():
+    c = cases.ENCODER_CASE
+    model = O.make_encoder(c["seed"], c["layers"], c["d_model"], c["heads"], c["ffn"], c["std"])
+    return c, model, cases.encoder_inputs(c)
+
+
+def test_encoder_driver_matches_oracle_and_golden():
+    import faith_b200
+    c, model, emb = _small()
+    l32, u32 = O.encoder_forward(model, emb, [c["index"]], c["p"], c["eps"])
+    l64, u64 = O.encoder_forward(O.model_to(model, torch.float64), emb.double(), [c["index"]], c["p"], c["eps"])
+    ver = faith_b200.EncoderVerifier(model, DEV)
+    l, u, viol = ver.forward(emb.to(DEV), [c["index"]], c["p"], c["eps"])
+    assert int(viol.item()) == 0
+    helpers.assert_within_noise(l, l32, l64, "logit lower")
+    helpers.assert_within_noise(u, u32, u64, "logit upper")
+    g = helpers.load_golden("encoder.npz")
+    helpers.assert_within_noise(l, g["l"], l64, "logit lower vs golden")
+    helpers.assert_within_noise(u, g["u"], u64, "logit upper vs golden")
+
+
+def test_encoder_stage_by_stage_with_bounds_class():
+    """The same pass through the Python `Bounds` class (one C-ABI call per operator), compared
+    stage by stage with the oracle trace."""
+    import math
+    import types
+    import faith_b200
+    c, model, emb = _small()
+    trace, trace64 = [], []
+    O.encoder_forward(model, emb, [c["index"]], c["p"], c["eps"], trace=trace)
+    O.encoder_forward(O.model_to(model, torch.float64), emb.double(), [c["index"]], c["p"], c["eps"], trace=trace64)
+    st32, st64 = dict(trace), dict(trace64)
+    args = types.SimpleNamespace(method="forward", perturbed_words=1, current_flag=1)
+    ib = O.input_bounds(emb, [c["index"]], c["p"], c["eps"])
+    x = faith_b200.Bounds(args, c["p"], c["eps"], lw=ib.lw.to(DEV), lb=ib.lb.to(DEV), uw=ib.uw.to(DEV), ub=ib.ub.to(DEV))
+
+    def lin(w, b):
+        return types.SimpleNamespace(weight=w.to(DEV), bias=b.to(DEV))
+
+    from faith_b200 import ops
+    heads = model["heads"]
+
+    def split(b, tr=False):
+        o = ops.split_heads(b._t4(), heads, tr)
+        return b._new(o[0], o[1], o[2], o[3])
+
+    def check(name, b):
+        gl, gu = b.concretize()
+        l32, u32 = st32[name].concretize()
+        l64, u64 = st64[name].concretize()
+        helpers.assert_within_noise(gl, l32, l64, name + " l")
+        helpers.assert_within_noise(gu, u32, u64, name + " u")
+
+    x = x.layer_norm(lin(model["emb_ln_g"], model["emb_ln_b"]), "no_var")
+    check("embedding", x)
+    for i, ly in enumerate(model["layers"]):
+        q = split(x.dense(lin(ly["q_w"], ly["q_b"])))
+        k = split(x.dense(lin(ly["k_w"], ly["k_b"])))
+        v = split(x.dense(lin(ly["v_w"], ly["v_b"])))
+        scores = q.dot_product(k).multiply(1.0 / math.sqrt(q.lw.shape[-1]))
+        check("layer%d.scores" % i, scores)
+        probs = scores.softmax()
+        check("layer%d.probs" % i, probs)
+        ctx = probs.context(v)
+        m = ops.merge_heads(ctx._t4(), heads)
+        ctx = ctx._new(m[0], m[1], m[2], m[3])
+        att = ctx.dense(lin(ly["ao_w"], ly["ao_b"])).add(x).layer_norm(lin(ly["ln1_g"], ly["ln1_b"]), "no_var")
+        check("layer%d.attention" % i, att)
+        inter = att.dense(lin(ly["f1_w"], ly["f1_b"])).relu()
+        check("layer%d.intermediate" % i, inter)
+        x = inter.dense(lin(ly["f2_w"], ly["f2_b"])).add(att).layer_norm(lin(ly["ln2_g"], ly["ln2_b"]), "no_var")
+        check("layer%d.output" % i, x)
+
+
+def test_encoder_bounds_contain_sampled_forward_passes():
+    """10 000 concrete forward passes sampled in the eps-ball (half on vertices, half inside)
+    must land inside the interval the driver returns."""
+    import faith_b200
+    c, model, emb = _small()
+    ver = faith_b200.EncoderVerifier(model, DEV)
+    l, u, _ = ver.forward(emb.to(DEV), [c["index"]], c["p"], c["eps"])
+    l, u = l.cpu(), u.cpu()
+    g = torch.Generator().manual_seed(9)
+    n = 10000
+    for s in range(emb.shape[0]):
+        delta = (torch.randint(0, 2, (n, c["d_model"]), generator=g).float() * 2 - 1) * c["eps"]
+        delta[: n // 2] *= torch.rand(n // 2, 1, generator=g)
+        x = emb[s:s + 1].repeat(n, 1, 1)
+        x[:, c["index"], :] += delta
+        y = O.concrete_forward(model, x)
+        assert float(y.min()) >= float(l[s]) - 1e-5, (float(y.min()), float(l[s]))
+        assert float(y.max()) <= float(u[s]) + 1e-5, (float(y.max()), float(u[s]))
+
+
+@pytest.mark.parametrize("p,words,positions", [(2.0, 2, [1, 2]), (1.0, 1, [3])])
+def test_encoder_other_norms_and_two_words(p, words, positions):
+    import faith_b200
+    c, model, emb = _small()
+    l32, u32 = O.encoder_forward(model, emb, positions, p, 5e-4)
+    l64, u64 = O.encoder_forward(O.model_to(model, torch.float64), emb.double(), positions, p, 5e-4)
+    ver = faith_b200.EncoderVerifier(model, DEV)
+    l, u, viol = ver.forward(emb.to(DEV), positions, p, 5e-4)
+    assert int(viol.item()) == 0
+    helpers.assert_within_noise(l, l32, l64, "l")
+    helpers.assert_within_noise(u, u32, u64, "u")
+
+
+def test_encoder_full_size_config_properties():
+    """Configuration of the headline benchmark (3 layers, d_model 128, 4 heads, FFN 512, L 32,
+    one perturbed word, L-inf) on 8 sentences at eps = 1e-3: finite, ordered, contains the
+    unperturbed forward pass, and agrees with the oracle within the fp32 noise budget."""
+    import faith_b200
+    model = O.make_encoder(4)
+    emb = torch.randn(8, 32, 128, generator=torch.Generator().manual_seed(4))
+    ver = faith_b200.EncoderVerifier(model, DEV)
+    l, u, viol = ver.forward(emb.to(DEV), [1], float("inf"), 1e-3)
+    l, u = l.cpu(), u.cpu()
+    assert bool(torch.isfinite(l).all()) and bool(torch.isfinite(u).all())
+    y = O.concrete_forward(model, emb)
+    assert bool((l <= y + 1e-5).all()) and bool((y <= u + 1e-5).all())
+    l32, u32 = O.encoder_forward(model, emb[:2], [1], float("inf"), 1e-3)
+    l64, u64 = O.encoder_forward(O.model_to(model, torch.float64), emb[:2].double(), [1], float("inf"), 1e-3)
+    helpers.assert_within_noise(l[:2], l32, l64, "l")
+    helpers.assert_within_noise(u[:2], u32, u64, "u")

@@ -1,0 +1,324 @@
+"""Parity of the CUDA operators (through the C ABI) with the CPU oracle and the golden vectors."""
+import math
+
+import pytest
+import torch
+
+import cases
+import helpers
+from oracle import bounds_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def gpu_bounds(c, t):
+    import faith_b200
+    return faith_b200.BoundsLite(c["p"], c["eps"], t[0].to(DEV), t[1].to(DEV), t[2].to(DEV), t[3].to(DEV), c["words"])
+
+
+def run_gpu_op(c):
+    import types
+    x_t, ex = cases.case_inputs(c)
+    x = gpu_bounds(c, x_t)
+    op = c["op"]
+    if op == "concretize":
+        l, u = x.concretize()
+        return {"l": l, "u": u}
+    if op in ("relu", "tanh", "exp", "reciprocal", "softmax"):
+        r = getattr(x, op)()
+    elif op == "matmul":
+        r = x.matmul(ex["W"].to(DEV))
+    elif op == "dense":
+        r = x.dense(types.SimpleNamespace(weight=ex["W"].to(DEV), bias=ex["bias"].to(DEV)))
+    elif op == "dot":
+        r = x.dot_product(gpu_bounds(c, ex["y"]))
+    elif op == "context":
+        r = x.context(gpu_bounds(c, ex["y"]))
+    elif op == "mul_bounds":
+        r = x.multiply(gpu_bounds(c, ex["y"]))
+    elif op == "layer_norm":
+        r = x.layer_norm(types.SimpleNamespace(weight=ex["W"].to(DEV), bias=ex["bias"].to(DEV)), "no_var")
+    elif op == "scale":
+        r = x.multiply(c["c"])
+    elif op == "add":
+        r = x.add(gpu_bounds(c, ex["y"]))
+    else:
+        raise KeyError(op)
+    return {"lw": r.lw, "lb": r.lb, "uw": r.uw, "ub": r.ub}
+
+
+@pytest.fixture(scope="module")
+def golden_ops():
+    return helpers.load_golden("ops.npz")
+
+
+@pytest.mark.parametrize("name", sorted(cases.OP_CASES))
+def test_op_matches_oracle_and_golden(name, golden_ops):
+    c = cases.OP_CASES[name]
+    got = run_gpu_op(c)
+    ref = helpers.run_oracle_op(c)
+    for k in ref:
+        helpers.assert_close(got[k], ref[k], "%s/%s vs oracle" % (name, k))
+        helpers.assert_close(got[k], golden_ops["%s/%s" % (name, k)], "%s/%s vs golden" % (name, k))
+
+
+def _pair(seed, B, L, Di, Do, p, eps, words, shift=-0.7, wscale=0.2):
+    import faith_b200
+    t = cases.rand_bounds(seed, B, L, Di, Do, shift, wscale)
+    return (O.OBounds(p, eps, *t, words=words),
+            faith_b200.BoundsLite(p, eps, *[v.to(DEV) for v in t], perturbed_words=words))
+
+
+def _cmp(g, o, what, **kw):
+    for k in ("lw", "uw", "lb", "ub"):
+        helpers.assert_close(getattr(g, k), getattr(o, k), "%s %s" % (what, k), **kw)
+
+
+# shapes of the reference's own sweep (transformer_forward_test_bound.py:725-737), a ragged one,
+# and shapes whose tile does / does not fit in shared memory
+RELAX_SHAPES = [(1, 2, 64, 64), (1, 16, 128, 256), (2, 5, 256, 512), (1, 3, 24, 20), (1, 2, 7, 5),
+                (1, 2, 1024, 96), (3, 1, 64, 1)]
+
+
+@pytest.mark.parametrize("op", ["relu", "tanh", "exp"])
+@pytest.mark.parametrize("shape", RELAX_SHAPES)
+@pytest.mark.parametrize("p,words", [(2.0, 1), (float("inf"), 1), (1.0, 1)])
+def test_relax_shapes(op, shape, p, words):
+    o, g = _pair(101, *shape, p, 0.5, words)
+    _cmp(getattr(g, op)(), getattr(o, op)(), "%s %s p=%s" % (op, shape, p))
+
+
+def test_relax_words_blocks():
+    for words in (2, 4):
+        o, g = _pair(102, 2, 3, 64, 40, 2.0, 0.3, words)
+        _cmp(g.relu(), o.relu(), "relu words=%d" % words)
+        _cmp(g.tanh(), o.tanh(), "tanh words=%d" % words)
+
+
+def test_reciprocal_and_violation_flag():
+    o, g = _pair(103, 2, 4, 64, 48, 2.0, 0.05, 1, shift=1.0)
+    _cmp(g.reciprocal(), o.reciprocal(), "reciprocal")
+    o2, g2 = _pair(103, 2, 4, 64, 48, 2.0, 0.5, 1, shift=-0.5)  # ranges that reach below zero
+    with pytest.raises(AssertionError):
+        o2.reciprocal()
+    with pytest.raises(AssertionError):
+        g2.reciprocal()
+
+
+def test_relu_all_three_column_kinds_present():
+    o, g = _pair(104, 1, 4, 64, 128, 2.0, 0.5, 1)
+    l, u = o.concretize()
+    assert bool((l > 0).any()) and bool((u < 0).any()) and bool(((l <= 0) & (u >= 0)).any())
+    gl, gu = g.concretize()
+    helpers.assert_close(gl, l, "concretize l")
+    helpers.assert_close(gu, u, "concretize u")
+
+
+def test_empty_batch_is_a_no_op():
+    import faith_b200
+    z4 = torch.zeros(0, 3, 8, 8, device=DEV)
+    z3 = torch.zeros(0, 3, 8, device=DEV)
+    r = faith_b200.BoundsLite(2, 0.1, z4, z3, z4.clone(), z3.clone()).relu()
+    assert r.lw.shape == (0, 3, 8, 8)
+
+
+def test_unwritten_outputs_are_detected():
+    """Outputs pre-filled with NaN must be fully overwritten (catches unwritten tails)."""
+    from faith_b200 import ops
+    from faith_b200._lib import FB_RELU
+    t = [v.to(DEV) for v in cases.rand_bounds(105, 2, 3, 24, 20, -0.7, 0.2)]
+    out = tuple(torch.full_like(v, float("nan")) for v in (t[0], t[2], t[1], t[3]))
+    ops.relax(FB_RELU, t[0], t[2], t[1], t[3], 2.0, 0.5, out=out)
+    for v in out:
+        assert bool(torch.isfinite(v).all())
+
+
+# ------------------------------------------------------------------ matmul
+@pytest.mark.parametrize("shape,Dy", [((1, 2, 64, 64), 64), ((1, 16, 64, 64), 128), ((2, 8, 128, 256), 512),
+                                      ((1, 3, 24, 20), 7), ((1, 5, 33, 130), 129), ((1, 4, 64, 128), 2),
+                                      ((1, 1, 128, 512), 128)])
+def test_matmul_shapes(shape, Dy):
+    import types
+    B, L, Di, Do = shape
+    g0 = torch.Generator().manual_seed(7)
+    t = cases.rand_bounds(201, B, L, Di, Do, 0.0, 1.0)
+    # weights with the spread of a trained layer: variance 1/fan_in
+    W = torch.randn(Dy, Do, generator=g0) / math.sqrt(Do)
+    bias = torch.randn(Dy, generator=g0) * 0.1
+    import faith_b200
+    o = O.OBounds(2.0, 0.5, *t).dense(W, bias)
+    g = faith_b200.BoundsLite(2.0, 0.5, *[v.to(DEV) for v in t]).dense(
+        types.SimpleNamespace(weight=W.to(DEV), bias=bias.to(DEV)))
+    # fp32 GEMMs with different summation order: error scales with sum_k |a_k w_k|, about
+    # sqrt(K) * |a| |w| ~ 0.3 here, so the absolute part of the bar is 1e-6 per unit of that sum
+    _cmp(g, o, "dense %s->%d" % (shape, Dy), rtol=1e-5, atol=2e-6)
+
+
+def test_matmul_identity_input_is_exact():
+    """First-layer case: lw = uw = one-hot rows; each output is a single product, so any
+    summation order gives the same bits as the reference."""
+    import faith_b200
+    D = 64
+    lw = torch.zeros(1, 4, D, D)
+    lw[0, 1] = torch.eye(D)
+    emb = torch.randn(1, 4, D, generator=torch.Generator().manual_seed(3))
+    W = torch.randn(128, D, generator=torch.Generator().manual_seed(4)) / 8
+    o = O.OBounds(2.0, 0.1, lw, emb, lw.clone(), emb.clone()).matmul(W)
+    g = faith_b200.BoundsLite(2.0, 0.1, lw.to(DEV), emb.to(DEV), lw.to(DEV), emb.to(DEV)).matmul(W.to(DEV))
+    assert torch.equal(g.lw.cpu(), o.lw) and torch.equal(g.uw.cpu(), o.uw)
+
+
+# ------------------------------------------------------------- dot product
+@pytest.mark.parametrize("B,Lx,Ly,Di,K", [(1, 2, 2, 64, 16), (4, 32, 32, 128, 32), (2, 8, 8, 64, 64),
+                                          (1, 5, 7, 24, 10), (2, 33, 9, 36, 130), (1, 16, 16, 256, 512)])
+@pytest.mark.parametrize("p", [2.0, float("inf")])
+def test_dot_product_shapes(B, Lx, Ly, Di, K, p):
+    import faith_b200
+    tx = cases.rand_bounds(301, B, Lx, Di, K, -0.5, 1.0)
+    ty = cases.rand_bounds(302, B, Ly, Di, K, -0.5, 1.0)
+    o = O.OBounds(p, 0.5, *tx).dot_product(O.OBounds(p, 0.5, *ty))
+    g = faith_b200.BoundsLite(p, 0.5, *[v.to(DEV) for v in tx]).dot_product(
+        faith_b200.BoundsLite(p, 0.5, *[v.to(DEV) for v in ty]))
+    # sums of K products of O(1) terms: absolute part scaled like the matmul test
+    _cmp(g, o, "dot", rtol=1e-5, atol=1e-6 * max(1.0, K / 8))
+
+
+def test_context_matches_oracle():
+    import faith_b200
+    B, L, Di, d = 4, 32, 128, 32
+    tp = cases.rand_bounds(303, B, L, Di, L, 0.0, 0.2)
+    tv = cases.rand_bounds(304, B, L, Di, d, -0.5, 1.0)
+    o = O.OBounds(2.0, 0.1, *tp).context(O.OBounds(2.0, 0.1, *tv))
+    g = faith_b200.BoundsLite(2.0, 0.1, *[v.to(DEV) for v in tp]).context(
+        faith_b200.BoundsLite(2.0, 0.1, *[v.to(DEV) for v in tv]))
+    _cmp(g, o, "context", rtol=1e-5, atol=4e-6)
+
+
+def test_split_merge_heads_round_trip():
+    from faith_b200 import ops
+    B, L, Di, H, d = 2, 5, 12, 4, 8
+    t = [v.to(DEV) for v in cases.rand_bounds(305, B, L, Di, H * d)]
+    x = (t[0], t[2], t[1], t[3])
+    o = O.split_heads(O.OBounds(2.0, 0.1, *[v.cpu() for v in (t[0], t[1], t[2], t[3])]), H)
+    s = ops.split_heads(x, H)
+    assert torch.equal(s[0].cpu(), o.lw) and torch.equal(s[3].cpu(), o.ub)
+    st = ops.split_heads(x, H, transpose_ld=True)
+    assert torch.equal(st[0].cpu(), o.lw.transpose(1, 3).contiguous())
+    assert torch.equal(st[2].cpu(), o.lb.transpose(1, 2).contiguous())
+    m = ops.merge_heads(s, H)
+    for a, b in zip(m, x):
+        assert torch.equal(a, b)
+
+
+# ------------------------------------------------- reference pybind surface
+def test_c_bound_relu_tanh_transposed_layout():
+    from faith_b200 import c_bound
+    for fn, name in ((c_bound.c_relu_verification, "relu"), (c_bound.c_tanh_verification, "tanh")):
+        for (B, L, Di, Do) in [(1, 2, 64, 64), (1, 8, 128, 256), (2, 3, 20, 12)]:
+            t = cases.rand_bounds(401, B, L, Di, Do, -0.7, 0.2)
+            o = getattr(O.OBounds(2.0, 0.5, *t), name)()
+            lw, lb, uw, ub = [v.to(DEV) for v in t]
+            tl, tu = lw.transpose(2, 3).contiguous(), uw.transpose(2, 3).contiguous()
+            o_lw, o_uw = torch.zeros_like(tl), torch.zeros_like(tu)
+            o_lb, o_ub = torch.zeros_like(lb), torch.zeros_like(ub)
+            fn(lb, ub, tl, tu, o_lb, o_ub, o_lw, o_uw, L, Di, Do, 0.5)
+            helpers.assert_close(o_lw.transpose(2, 3), o.lw, name + " lw")
+            helpers.assert_close(o_uw.transpose(2, 3), o.uw, name + " uw")
+            helpers.assert_close(o_lb, o.lb, name + " lb")
+            helpers.assert_close(o_ub, o.ub, name + " ub")
+
+
+@pytest.mark.parametrize("B,L,Di,K", [(1, 2, 64, 16), (2, 8, 64, 64), (4, 16, 128, 16), (1, 5, 24, 10)])
+def test_c_bound_dot_product_qk(B, L, Di, K):
+    from faith_b200 import c_bound
+    tx = cases.rand_bounds(402, B, L, Di, K, -0.5, 1.0)
+    ty = cases.rand_bounds(403, B, L, Di, K, -0.5, 1.0)
+    ox, oy = O.OBounds(2.0, 0.5, *tx), O.OBounds(2.0, 0.5, *ty)
+    o = ox.dot_product(oy)
+    x = [v.to(DEV) for v in tx]
+    y = [v.to(DEV) for v in ty]
+    z_lw = torch.zeros(B, L, L, Di, device=DEV)
+    z_uw = torch.zeros_like(z_lw)
+    z_lb = torch.zeros(B, L, L, device=DEV)
+    z_ub = torch.zeros_like(z_lb)
+    x_l, x_u, y_l, y_u = (torch.zeros(B, L, K, device=DEV) for _ in range(4))
+    c_bound.c_dot_product_verification_QK(
+        x_l, y_l, x_u, y_u, x[1], x[3], y[1], y[3],
+        x[0].transpose(2, 3).contiguous(), x[2].transpose(2, 3).contiguous(),
+        y[0].transpose(2, 3).contiguous(), y[2].transpose(2, 3).contiguous(),
+        z_lb, z_ub, z_lw, z_uw, B, L, K, Di, 0.5)
+    tol = dict(rtol=1e-5, atol=1e-6 * max(1.0, K / 8))
+    helpers.assert_close(z_lw.transpose(2, 3), o.lw, "qk lw", **tol)
+    helpers.assert_close(z_uw.transpose(2, 3), o.uw, "qk uw", **tol)
+    helpers.assert_close(z_lb, o.lb, "qk lb", **tol)
+    helpers.assert_close(z_ub, o.ub, "qk ub", **tol)
+    # the caller-visible scratch receives the concretised operand ranges
+    lx, ux = ox.concretize()
+    ly, uy = oy.concretize()
+    helpers.assert_close(x_l, lx, "x_l"); helpers.assert_close(x_u, ux, "x_u")
+    helpers.assert_close(y_l, ly, "y_l"); helpers.assert_close(y_u, uy, "y_u")
+
+
+@pytest.mark.parametrize("B,L,Di,Dout", [(1, 2, 64, 10), (2, 8, 64, 20), (4, 16, 128, 64)])
+def test_c_bound_dot_product_v(B, L, Di, Dout):
+    from faith_b200 import c_bound
+    tp = cases.rand_bounds(404, B, L, Di, L, 0.0, 0.2)          # probabilities [B, L, Di, L]
+    tv = cases.rand_bounds(405, B, Dout, Di, L, -0.5, 1.0)      # value.t()     [B, Dout, Di, L]
+    o = O.OBounds(2.0, 0.5, *tp).dot_product(O.OBounds(2.0, 0.5, *tv))
+    x = [v.to(DEV) for v in tp]
+    y = [v.to(DEV) for v in tv]
+    z_lw = torch.zeros(B, L, Dout, Di, device=DEV)
+    z_uw = torch.zeros_like(z_lw)
+    z_lb = torch.zeros(B, L, Dout, device=DEV)
+    z_ub = torch.zeros_like(z_lb)
+    x_l, x_u = torch.zeros(B, L, L, device=DEV), torch.zeros(B, L, L, device=DEV)
+    y_l, y_u = torch.zeros(B, Dout, L, device=DEV), torch.zeros(B, Dout, L, device=DEV)
+    c_bound.c_dot_product_verification_V(
+        x_l, y_l, x_u, y_u, x[1], x[3], y[1], y[3],
+        x[0].transpose(2, 3).contiguous(), x[2].transpose(2, 3).contiguous(),
+        y[0].transpose(2, 3).contiguous(), y[2].transpose(2, 3).contiguous(),
+        z_lb, z_ub, z_lw, z_uw, B, L, Dout, Di, 0.5)
+    tol = dict(rtol=1e-5, atol=4e-6)
+    helpers.assert_close(z_lw.transpose(2, 3), o.lw, "v lw", **tol)
+    helpers.assert_close(z_uw.transpose(2, 3), o.uw, "v uw", **tol)
+    helpers.assert_close(z_lb, o.lb, "v lb", **tol)
+    helpers.assert_close(z_ub, o.ub, "v ub", **tol)
+
+
+def test_c_bound_matmul():
+    from faith_b200 import c_bound
+    B, L, Di, Do, Dy = 1, 4, 64, 64, 64
+    t = cases.rand_bounds(406, B, L, Di, Do)
+    W = (torch.rand(Dy, Do, generator=torch.Generator().manual_seed(0)) - 0.5) / 4
+    o = O.OBounds(2.0, 0.5, *t).matmul(W)
+    lw, lb, uw, ub = [v.to(DEV) for v in t]
+    y_lw = torch.zeros(B, L, Di, Dy, device=DEV); y_uw = torch.zeros_like(y_lw)
+    y_lb = torch.zeros(B, L, Dy, device=DEV); y_ub = torch.zeros_like(y_lb)
+    c_bound.c_matmul_verification(lb, ub, lw, uw, W.to(DEV), y_lb, y_ub, y_lw, y_uw, B, L, Di, Do, Dy)
+    helpers.assert_close(y_lw, o.lw, "lw", atol=2e-6); helpers.assert_close(y_ub, o.ub, "ub", atol=2e-6)
+
+
+# ------------------------------------------------------------------- conv
+@pytest.mark.parametrize("cfg", [dict(B=1, Di=12, C=3, H=32, W=32, Co=16, k=3, s=1, p=1),
+                                 dict(B=2, Di=5, C=16, H=32, W=32, Co=32, k=3, s=2, p=1),
+                                 dict(B=1, Di=3, C=5, H=9, W=11, Co=7, k=3, s=1, p=0),
+                                 dict(B=1, Di=4, C=2, H=8, W=8, Co=20, k=5, s=2, p=2)])
+def test_conv_bounds(cfg):
+    from faith_b200 import ops
+    g = torch.Generator().manual_seed(501)
+    B, Di, C, H, W = cfg["B"], cfg["Di"], cfg["C"], cfg["H"], cfg["W"]
+    lw = torch.rand(B, Di, C, H, W, generator=g) - 0.5
+    uw = torch.rand(B, Di, C, H, W, generator=g) - 0.5
+    lb = torch.rand(B, C, H, W, generator=g)
+    ub = lb + torch.rand(B, C, H, W, generator=g)
+    wt = torch.randn(cfg["Co"], C, cfg["k"], cfg["k"], generator=g) * math.sqrt(2.0 / (C * cfg["k"] ** 2))
+    bias = torch.randn(cfg["Co"], generator=g) * 0.1
+    o = O.conv_bounds(O.OBounds(float("inf"), 0.01, lw, lb, uw, ub), wt, bias, cfg["s"], cfg["p"])
+    r = ops.conv2d((lw.to(DEV), uw.to(DEV), lb.to(DEV), ub.to(DEV)), wt.to(DEV), bias.to(DEV), cfg["s"], cfg["p"])
+    tol = dict(rtol=1e-5, atol=2e-6)
+    helpers.assert_close(r[0], o.lw, "conv lw", **tol)
+    helpers.assert_close(r[1], o.uw, "conv uw", **tol)
+    helpers.assert_close(r[2], o.lb, "conv lb", **tol)
+    helpers.assert_close(r[3], o.ub, "conv ub", **tol)

@@ -61,3 +61,25 @@ def test_bounds_contain_concrete_forward():
     y = O.concrete_forward(model, x)
     assert float(y.min()) >= float(l[0]) - 1e-5 and float(y.max()) <= float(u[0]) + 1e-5
     assert float(u[0] - l[0]) < 2.0  # and the bound is finite and of sane width at this eps
+
+
+def test_conv_oracle_agrees_with_im2col_matmul():
+    """Ties the (otherwise unpinned) conv restatement to the pinned matmul: unfold + matmul."""
+    import torch.nn.functional as F
+    g = torch.Generator().manual_seed(502)
+    B, Di, C, H, W, Co = 1, 6, 3, 8, 8, 5
+    lw = torch.rand(B, Di, C, H, W, generator=g) - 0.5
+    uw = torch.rand(B, Di, C, H, W, generator=g) - 0.5
+    lb = torch.rand(B, C, H, W, generator=g)
+    ub = lb + torch.rand(B, C, H, W, generator=g)
+    wt = torch.randn(Co, C, 3, 3, generator=g) * 0.3
+    o = O.conv_bounds(O.OBounds(2.0, 0.1, lw, lb, uw, ub), wt, None, 1, 1)
+
+    def cols(t):  # [N, C, H, W] -> [N, H*W, C*9]
+        return F.unfold(t, 3, padding=1).transpose(1, 2)
+
+    xw = O.OBounds(2.0, 0.1, cols(lw[0]).transpose(0, 1).unsqueeze(0), cols(lb), cols(uw[0]).transpose(0, 1).unsqueeze(0),
+                   cols(ub))
+    m = xw.matmul(wt.reshape(Co, -1))  # lw [1, H*W, Di, Co]
+    helpers.assert_close(m.lw[0].permute(1, 2, 0).reshape(Di, Co, H, W), o.lw[0], "lw", atol=2e-6)
+    helpers.assert_close(m.ub[0].transpose(0, 1).reshape(Co, H, W), o.ub[0], "ub", atol=2e-6)
