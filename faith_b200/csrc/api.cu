@@ -1,5 +1,7 @@
 // Status strings, error bookkeeping and the per-device property cache of libfaith_b200.
+#include <atomic>
 #include <mutex>
+#include <vector>
 
 #include "common.cuh"
 
@@ -28,7 +30,96 @@ const DeviceInfo& device_info() {
   return g_info[dev];
 }
 
+// ------------------------------------------------------------------ profiler
+namespace {
+struct ProfRec {
+  cudaEvent_t a, b;
+  int kind;
+  double flops, bytes;
+};
+std::mutex g_prof_mu;
+std::vector<ProfRec> g_prof;
+std::atomic<int> g_prof_on{0};
+std::atomic<long long> g_launches{0};
+thread_local int t_depth = 0;
+}  // namespace
+
+void count_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+ProfileScope::ProfileScope(int kind, double flops, double bytes, void* stream) : slot_(-1), stream_(stream) {
+  if (++t_depth != 1 || !g_prof_on.load(std::memory_order_relaxed)) return;
+  ProfRec r;
+  r.kind = kind;
+  r.flops = flops;
+  r.bytes = bytes;
+  if (cudaEventCreate(&r.a) != cudaSuccess) return;
+  if (cudaEventCreate(&r.b) != cudaSuccess) { cudaEventDestroy(r.a); return; }
+  cudaEventRecord(r.a, (cudaStream_t)stream);
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  g_prof.push_back(r);
+  slot_ = (int)g_prof.size() - 1;
+}
+
+ProfileScope::~ProfileScope() {
+  --t_depth;
+  if (slot_ < 0) return;
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  if (slot_ < (int)g_prof.size()) cudaEventRecord(g_prof[slot_].b, (cudaStream_t)stream_);
+}
+
 }  // namespace fb
+
+extern "C" int fb_profile_enable(int on) {
+  std::lock_guard<std::mutex> lk(fb::g_prof_mu);
+  for (auto& r : fb::g_prof) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
+  fb::g_prof.clear();
+  fb::g_prof_on.store(on ? 1 : 0);
+  return FB_OK;
+}
+
+extern "C" int fb_profile_read(int kind, double* ms, int64_t* calls, double* flops, double* bytes) {
+  if (kind < 0 || kind >= fb::PK_COUNT || !ms || !calls || !flops || !bytes) return FB_ERR_ARG;
+  std::lock_guard<std::mutex> lk(fb::g_prof_mu);
+  *ms = 0; *calls = 0; *flops = 0; *bytes = 0;
+  for (auto& r : fb::g_prof) {
+    if (r.kind != kind) continue;
+    FB_CUDA_OK(cudaEventSynchronize(r.b));
+    float t = 0.f;
+    FB_CUDA_OK(cudaEventElapsedTime(&t, r.a, r.b));
+    *ms += t; *calls += 1; *flops += r.flops; *bytes += r.bytes;
+  }
+  return FB_OK;
+}
+
+namespace fb {
+namespace {
+// 16 independent FMA chains per thread: the CUDA-core fp32 multiply-add rate of the device.
+__global__ void __launch_bounds__(256) ffma_peak_kernel(float* out, int iters, float a, float b) {
+  float v[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = (float)(threadIdx.x + i);
+  for (int it = 0; it < iters; ++it) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = fmaf(v[i], a, b);
+  }
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) s += v[i];
+  if (s == 12345.678f) out[0] = s;  // keeps the chains alive without a store in the common case
+}
+}  // namespace
+}  // namespace fb
+
+extern "C" int fb_bench_ffma(float* scratch, int iters, double* flops, void* stream) {
+  if (!scratch || iters <= 0 || !flops) return FB_ERR_ARG;
+  const int blocks = fb::device_info().sms * 8;
+  fb::ffma_peak_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(scratch, iters, 0.999f, 0.001f);
+  FB_LAUNCH_OK();
+  *flops = 2.0 * 16.0 * (double)iters * 256.0 * blocks;
+  return FB_OK;
+}
+
+extern "C" int64_t fb_launch_count(void) { return (int64_t)fb::g_launches.load(); }
 
 extern "C" const char* fb_status_string(int status) {
   switch (status) {

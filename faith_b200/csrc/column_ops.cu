@@ -450,10 +450,13 @@ using namespace fb;
 extern "C" int fb_concretize_f32(const float* lw, const float* uw, const float* lb, const float* ub, float* l,
                                  float* u, int64_t rows, int Di, int Do, int words, int p, float eps, int layout,
                                  void* stream) {
+  if (rows == 0 || Do == 0) return FB_OK;
   if (!lw || !uw || !lb || !ub || !l || !u) return FB_ERR_ARG;
   if (rows < 0 || Di <= 0 || Do < 0 || words <= 0 || !valid_norm(p)) return FB_ERR_ARG;
   if (layout != FB_NATIVE && layout != FB_TRANSPOSED) return FB_ERR_ARG;
   if (Di % words != 0) return FB_ERR_SHAPE;
+  const double mw = (double)rows * Di * Do, mb = (double)rows * Do;
+  ProfileScope prof(PK_RELAX, 4.0 * mw, 4.0 * (2 * mw + 4 * mb), stream);
   return launch_relax(OP_CONCRETIZE, lw, uw, lb, ub, nullptr, nullptr, l, u, rows, Di, Do, words, p, eps, layout,
                       nullptr, (cudaStream_t)stream);
 }
@@ -461,12 +464,15 @@ extern "C" int fb_concretize_f32(const float* lw, const float* uw, const float* 
 extern "C" int fb_relax_f32(int op, const float* lw, const float* uw, const float* lb, const float* ub,
                             float* out_lw, float* out_uw, float* out_lb, float* out_ub, int64_t rows, int Di, int Do,
                             int words, int p, float eps, int layout, int* violation, void* stream) {
+  if (rows == 0 || Do == 0) return (op < FB_RELU || op > FB_RECIPROCAL) ? FB_ERR_ARG : FB_OK;
   if (!lw || !uw || !lb || !ub || !out_lw || !out_uw || !out_lb || !out_ub) return FB_ERR_ARG;
   if (op < FB_RELU || op > FB_RECIPROCAL) return FB_ERR_ARG;
   if (rows < 0 || Di <= 0 || Do < 0 || words <= 0 || !valid_norm(p)) return FB_ERR_ARG;
   if (layout != FB_NATIVE && layout != FB_TRANSPOSED) return FB_ERR_ARG;
   if (Di % words != 0) return FB_ERR_SHAPE;
   if (out_lw == lw || out_lw == uw || out_uw == lw || out_uw == uw) return FB_ERR_ARG;
+  const double mw = (double)rows * Di * Do, mb = (double)rows * Do;
+  ProfileScope prof(PK_RELAX, 6.0 * mw, 4.0 * (4 * mw + 4 * mb), stream);
   return launch_relax(op, lw, uw, lb, ub, out_lw, out_uw, out_lb, out_ub, rows, Di, Do, words, p, eps, layout,
                       violation, (cudaStream_t)stream);
 }
@@ -481,6 +487,8 @@ extern "C" int fb_mul_bounds_f32(const float* x_lw, const float* x_uw, const flo
   if (Di % words != 0) return FB_ERR_SHAPE;
   if (rows == 0 || Do == 0) return FB_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  const double mw = (double)rows * Di * Do, mb = (double)rows * Do;
+  ProfileScope prof(PK_MUL, 12.0 * mw, 4.0 * (6 * mw + 6 * mb), stream);
   const int ntiles = (int)ceil_div(Do, kCW);
   const int64_t blocks = rows * ntiles;
   if (blocks > 0x7fffffff) return FB_ERR_SHAPE;

@@ -27,8 +27,28 @@ const DeviceInfo& device_info();
     }                                                      \
   } while (0)
 
-// Launch errors are read without clearing the sticky state of unrelated earlier failures.
-#define FB_LAUNCH_OK() FB_CUDA_OK(cudaGetLastError())
+// Checks the launches just enqueued (n of them, for the launch counter of fb_profile_*).
+#define FB_LAUNCH_OK_N(n)                \
+  do {                                   \
+    fb::count_launches(n);               \
+    FB_CUDA_OK(cudaGetLastError());      \
+  } while (0)
+#define FB_LAUNCH_OK() FB_LAUNCH_OK_N(1)
+
+void count_launches(int n);
+
+// Optional per-operator timing (fb_profile_enable): the outermost C-ABI operator call on a thread
+// brackets its launches with a pair of CUDA events on the caller's stream and records the
+// algorithmic work of the call.  Disabled (the default), a scope costs one branch.
+enum ProfileKind { PK_MATMUL = 0, PK_RELAX = 1, PK_DOT = 2, PK_MUL = 3, PK_ELEMENTWISE = 4, PK_CONV = 5, PK_COUNT = 6 };
+class ProfileScope {
+ public:
+  ProfileScope(int kind, double flops, double bytes, void* stream);
+  ~ProfileScope();
+ private:
+  int slot_;
+  void* stream_;
+};
 
 __host__ __device__ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline bool valid_norm(int p) { return p == FB_P1 || p == FB_P2 || p == FB_PINF; }

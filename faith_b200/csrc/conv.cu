@@ -129,6 +129,9 @@ extern "C" int fb_conv2d_f32(const float* x_lw, const float* x_uw, const float* 
   const int Ho = (H + 2 * pad - Kh) / stride + 1, Wo = (W + 2 * pad - Kw) / stride + 1;
   if (Ho <= 0 || Wo <= 0) return FB_ERR_SHAPE;
   cudaStream_t st = (cudaStream_t)stream;
+  const double n1 = (double)B * (Di + 1);
+  fb::ProfileScope prof(fb::PK_CONV, 8.0 * n1 * Cout * Ho * Wo * Cin * Kh * Kw,
+                        4.0 * (2 * n1 * Cin * H * W + 2 * n1 * Cout * Ho * Wo + (double)Cout * Cin * Kh * Kw), stream);
   int rc = fb::launch_conv(x_lw, x_uw, Wt, nullptr, y_lw, y_uw, (int64_t)B * Di, Cin, H, W, Cout, Kh, Kw, stride, pad,
                            Ho, Wo, st);
   if (rc != FB_OK) return rc;

@@ -312,6 +312,9 @@ extern "C" int fb_dot_product_f32(const float* x_lw, const float* x_uw, const fl
   if (Di == 1) return FB_ERR_SHAPE;
   if (B == 0) return FB_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  const double d1 = (double)Di + 1;
+  ProfileScope prof(PK_DOT, 16.0 * B * Lx * Ly * d1 * K,
+                    4.0 * (2.0 * B * Lx * d1 * K + 2.0 * B * Ly * d1 * K + 2.0 * B * Lx * Ly * d1), stream);
   int rc = fb_concretize_f32(x_lw, x_uw, x_lb, x_ub, x_l, x_u, (int64_t)B * Lx, Di, K, words, p, eps, layout, stream);
   if (rc != FB_OK) return rc;
   rc = fb_concretize_f32(y_lw, y_uw, y_lb, y_ub, y_l, y_u, (int64_t)B * Ly, Di, K, words, p, eps, layout, stream);

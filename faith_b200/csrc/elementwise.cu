@@ -210,12 +210,13 @@ extern "C" int fb_add_f32(const float* x_lw, const float* x_uw, const float* x_l
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t nw = rows * Di * Do, nb = rows * Do;
   if (nw == 0) return FB_OK;
+  ProfileScope prof(PK_ELEMENTWISE, 2.0 * (nw + nb), 4.0 * 6 * (nw + nb), stream);
   const bool vw = nw % 4 == 0 && aligned16(x_lw) && aligned16(x_uw) && aligned16(y_lw) && aligned16(y_uw) &&
                   aligned16(z_lw) && aligned16(z_uw);
   if (vw) add_kernel<4><<<stream_blocks(nw / 4), kThreads, 0, st>>>(x_lw, y_lw, z_lw, x_uw, y_uw, z_uw, nw);
   else add_kernel<1><<<stream_blocks(nw), kThreads, 0, st>>>(x_lw, y_lw, z_lw, x_uw, y_uw, z_uw, nw);
   add_kernel<1><<<stream_blocks(nb), kThreads, 0, st>>>(x_lb, y_lb, z_lb, x_ub, y_ub, z_ub, nb);
-  FB_LAUNCH_OK();
+  FB_LAUNCH_OK_N(2);
   return FB_OK;
 }
 
@@ -229,6 +230,7 @@ extern "C" int fb_scale_f32(const float* x_lw, const float* x_uw, const float* x
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t nw = rows * Di * Do, nb = rows * Do;
   if (nw == 0) return FB_OK;
+  ProfileScope prof(PK_ELEMENTWISE, 2.0 * (nw + nb), 4.0 * 4 * (nw + nb), stream);
   // a positive scalar keeps the sides, any other swaps them (Bounds.py:596-607)
   const float* s_lw = c > 0.f ? x_lw : x_uw;
   const float* s_uw = c > 0.f ? x_uw : x_lw;
@@ -238,7 +240,7 @@ extern "C" int fb_scale_f32(const float* x_lw, const float* x_uw, const float* x
   if (vw) scale_kernel<4><<<stream_blocks(nw / 4), kThreads, 0, st>>>(s_lw, z_lw, s_uw, z_uw, c, nw);
   else scale_kernel<1><<<stream_blocks(nw), kThreads, 0, st>>>(s_lw, z_lw, s_uw, z_uw, c, nw);
   scale_kernel<1><<<stream_blocks(nb), kThreads, 0, st>>>(s_lb, z_lb, s_ub, z_ub, c, nb);
-  FB_LAUNCH_OK();
+  FB_LAUNCH_OK_N(2);
   return FB_OK;
 }
 
@@ -249,6 +251,7 @@ extern "C" int fb_rowsum_f32(const float* x_lw, const float* x_uw, const float* 
   FB_REQUIRE(rows >= 0 && Di > 0 && Do >= 0, FB_ERR_ARG);
   if (rows == 0 || Do == 0) return FB_OK;
   const int64_t n_w = rows * Di, n_b = rows;
+  ProfileScope prof(PK_ELEMENTWISE, 2.0 * (n_w + n_b) * Do, 4.0 * 4 * (n_w + n_b) * Do, stream);
   rowsum_kernel<<<stream_blocks((n_w + n_b) * 32), kThreads, 0, (cudaStream_t)stream>>>(
       x_lw, x_uw, x_lb, x_ub, z_lw, z_uw, z_lb, z_ub, n_w, n_b, Do);
   FB_LAUNCH_OK();
@@ -267,6 +270,7 @@ extern "C" int fb_layernorm_novar_f32(const float* x_lw, const float* x_uw, cons
   FB_REQUIRE(z_lw != x_uw && z_uw != x_lw && z_lb != x_ub && z_ub != x_lb, FB_ERR_ARG);
   if (rows == 0 || Do == 0) return FB_OK;
   const int64_t n_w = rows * Di, n_b = rows;
+  ProfileScope prof(PK_ELEMENTWISE, 8.0 * (n_w + n_b) * Do, 4.0 * (r_lw ? 6 : 4) * (n_w + n_b) * Do, stream);
   layernorm_novar_kernel<<<stream_blocks((n_w + n_b) * 32), kThreads, 0, (cudaStream_t)stream>>>(
       x_lw, x_uw, x_lb, x_ub, r_lw, r_uw, r_lb, r_ub, gamma, beta, z_lw, z_uw, z_lb, z_ub, n_w, n_b, Do);
   FB_LAUNCH_OK();
@@ -279,6 +283,7 @@ extern "C" int fb_split_heads_f32(const float* x_w, const float* x_b, float* z_w
   FB_REQUIRE(B >= 0 && L > 0 && Di > 0 && H > 0 && d > 0, FB_ERR_ARG);
   if (B == 0) return FB_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  ProfileScope prof(PK_ELEMENTWISE, 0.0, 4.0 * 2 * ((double)B * L * (Di + 1) * H * d), stream);
   if (transpose_ld) {
     const int64_t bw = (int64_t)B * H * Di, bb = (int64_t)B * H;
     FB_REQUIRE(bw <= 0x7fffffff, FB_ERR_SHAPE);
@@ -291,7 +296,7 @@ extern "C" int fb_split_heads_f32(const float* x_w, const float* x_b, float* z_w
     else heads_permute_kernel<1, true><<<stream_blocks(nw), kThreads, 0, st>>>(x_w, z_w, B, L, Di, H, d);
     heads_permute_kernel<1, true><<<stream_blocks(nb), kThreads, 0, st>>>(x_b, z_b, B, L, 1, H, d);
   }
-  FB_LAUNCH_OK();
+  FB_LAUNCH_OK_N(2);
   return FB_OK;
 }
 
@@ -301,11 +306,12 @@ extern "C" int fb_merge_heads_f32(const float* x_w, const float* x_b, float* z_w
   FB_REQUIRE(B >= 0 && L > 0 && Di > 0 && H > 0 && d > 0, FB_ERR_ARG);
   if (B == 0) return FB_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  ProfileScope prof(PK_ELEMENTWISE, 0.0, 4.0 * 2 * ((double)B * L * (Di + 1) * H * d), stream);
   const bool vec = d % 4 == 0 && aligned16(x_w) && aligned16(z_w);
   const int64_t nw = (int64_t)B * L * Di * H * d, nb = (int64_t)B * L * H * d;
   if (vec) heads_permute_kernel<4, false><<<stream_blocks(nw / 4), kThreads, 0, st>>>(x_w, z_w, B, L, Di, H, d);
   else heads_permute_kernel<1, false><<<stream_blocks(nw), kThreads, 0, st>>>(x_w, z_w, B, L, Di, H, d);
   heads_permute_kernel<1, false><<<stream_blocks(nb), kThreads, 0, st>>>(x_b, z_b, B, L, 1, H, d);
-  FB_LAUNCH_OK();
+  FB_LAUNCH_OK_N(2);
   return FB_OK;
 }

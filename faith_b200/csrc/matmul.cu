@@ -12,6 +12,8 @@ extern "C" int fb_matmul_f32(const float* x_lw, const float* x_uw, const float* 
   if (!x_lw || !x_uw || !x_lb || !x_ub || !W || !y_lw || !y_uw || !y_lb || !y_ub) return FB_ERR_ARG;
   if (rows < 0 || Di <= 0 || Do <= 0 || Dy <= 0) return FB_ERR_ARG;
   cudaStream_t st = (cudaStream_t)stream;
+  const double M = (double)rows * (Di + 1);
+  fb::ProfileScope prof(fb::PK_MATMUL, 8.0 * M * Do * Dy, 4.0 * (2 * M * Do + 2 * M * Dy + (double)Do * Dy + Dy), stream);
   // weight rows: [rows * Di, Do] -> [rows * Di, Dy]; no bias on the symbolic part
   int rc = fb::launch_split_sign_ffma(x_lw, x_uw, W, nullptr, y_lw, y_uw, rows * (int64_t)Di, Dy, Do, st);
   if (rc != FB_OK) return rc;

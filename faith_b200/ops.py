@@ -69,7 +69,9 @@ def relax(op, lw, uw, lb, ub, p, eps, words=1, layout=FB_NATIVE, out=None, viola
     if out is None:
         out = (torch.empty_like(lw), torch.empty_like(uw), torch.empty_like(lb), torch.empty_like(ub))
     o_lw, o_uw, o_lb, o_ub = out
-    _chk(o_lw, o_uw, o_lb, o_ub, violation)
+    _chk(o_lw, o_uw, o_lb, o_ub)
+    if violation is not None and (violation.dtype != torch.int32 or not violation.is_cuda):
+        raise _lib.FaithError("violation flag must be an int32 CUDA tensor")
     with torch.cuda.device(dev):
         check(load().fb_relax_f32(op, _p(lw), _p(uw), _p(lb), _p(ub), _p(o_lw), _p(o_uw), _p(o_lb), _p(o_ub),
                                   rows, Di, Do, words, norm_code(p), eps, layout, _p(violation), _stream()),

@@ -185,6 +185,21 @@ int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, int S, int L
                            float* out_l, float* out_u, int* violation,
                            void* workspace, int64_t workspace_bytes, void* stream);
 
+/* ---- measurement hooks (no counterpart in the reference) --------------------------------
+ * fb_profile_enable(1) clears the records and makes every outermost operator call bracket its
+ * launches with a pair of CUDA events on the caller's stream; fb_profile_read() waits for the
+ * recorded events and returns, per operator kind (0 matmul, 1 relax/concretize, 2 dot product,
+ * 3 bound x bound multiply, 4 exact elementwise ops, 5 conv), the summed device time in ms, the
+ * number of calls and their algorithmic flops and bytes.  fb_launch_count() is the number of
+ * kernels this library has launched in the process so far. */
+int fb_profile_enable(int on);
+int fb_profile_read(int kind, double* ms, int64_t* calls, double* flops, double* bytes);
+int64_t fb_launch_count(void);
+/* Launches a register-only chain of fp32 multiply-adds on every SM (scratch: one device float)
+ * and returns in *flops the floating-point operations it performs; timed by the caller with
+ * CUDA events it gives the CUDA-core fp32 peak used as the roof of the FFMA kernels. */
+int fb_bench_ffma(float* scratch, int iters, double* flops, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

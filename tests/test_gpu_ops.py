@@ -181,8 +181,17 @@ def test_dot_product_shapes(B, Lx, Ly, Di, K, p):
     o = O.OBounds(p, 0.5, *tx).dot_product(O.OBounds(p, 0.5, *ty))
     g = faith_b200.BoundsLite(p, 0.5, *[v.to(DEV) for v in tx]).dot_product(
         faith_b200.BoundsLite(p, 0.5, *[v.to(DEV) for v in ty]))
-    # sums of K products of O(1) terms: absolute part scaled like the matmul test
-    _cmp(g, o, "dot", rtol=1e-5, atol=1e-6 * max(1.0, K / 8))
+    if p == 2.0:
+        # sums of K products of O(1) terms: absolute part scaled like the matmul test
+        _cmp(g, o, "dot", rtol=1e-5, atol=1e-6 * max(1.0, K / 8))
+    else:
+        # With the sum-abs dual norm the operand ranges are ~Di/4, the K-term sums reach 1e3..1e4
+        # and cancel: the fp32 summation-order noise of the reference itself exceeds the per-op
+        # bar, so the result is judged against the fp64 run of the same algorithm.
+        d = torch.float64
+        o64 = O.OBounds(p, 0.5, *[v.to(d) for v in tx]).dot_product(O.OBounds(p, 0.5, *[v.to(d) for v in ty]))
+        for k in ("lw", "uw", "lb", "ub"):
+            helpers.assert_within_noise(getattr(g, k), getattr(o, k), getattr(o64, k), "dot %s" % k)
 
 
 def test_context_matches_oracle():
