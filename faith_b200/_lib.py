@@ -36,6 +36,8 @@ SIGNATURES = {
     "fb_relax_f32": [_I] + [_P] * 8 + [_L, _I, _I, _I, _I, _F, _I, _P, _P],
     "fb_matmul_f32": [_P] * 10 + [_L, _I, _I, _I, _P],
     "fb_dot_product_f32": [_P] * 16 + [_I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P],
+    "fb_dot_product_noalloc_f32": [_P] * 12 + [_I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P],
+    "fb_dot_product_noalloc_max_floats": [],
     "fb_mul_bounds_f32": [_P] * 12 + [_L, _I, _I, _I, _I, _F, _P],
     "fb_add_f32": [_P] * 12 + [_L, _I, _I, _P],
     "fb_scale_f32": [_P] * 8 + [_L, _I, _I, _F, _P],
@@ -55,7 +57,8 @@ SIGNATURES = {
     "fb_last_cuda_error": [],
     "fb_version": [],
 }
-_OTHER_RESTYPE = {"fb_status_string": ctypes.c_char_p, "fb_encoder_workspace_bytes": _L, "fb_launch_count": _L}
+_OTHER_RESTYPE = {"fb_status_string": ctypes.c_char_p, "fb_encoder_workspace_bytes": _L, "fb_launch_count": _L,
+                   "fb_dot_product_noalloc_max_floats": _L}
 
 _lib = None
 

@@ -13,6 +13,8 @@
 //
 // Three launches: concretise x, concretise y (column kernels), then one kernel for the bias
 // part and one for the weight part.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace fb {
@@ -353,4 +355,54 @@ extern "C" int fb_dot_product_f32(const float* x_lw, const float* x_uw, const fl
   }
   FB_LAUNCH_OK();
   return FB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Variant for callers that must not allocate: the concretised operand ranges go to a fixed
+// array that lives in the library image instead of caller-provided scratch.
+namespace fb {
+namespace {
+constexpr int64_t kStaticScratchFloats = 4ll * 1024 * 1024;  // 16 MiB, held by every GPU that loads the library
+static __device__ __align__(256) float g_dot_static_scratch[kStaticScratchFloats];
+
+constexpr int kMaxStaticDevices = 64;
+float* g_static_ptr[kMaxStaticDevices] = {nullptr};
+std::mutex g_static_mu;
+
+// Device address of the array on the current device.  The symbol name is only a host-side
+// handle, so the address is asked from the runtime once per device and remembered.
+int static_scratch_address(float** out) {
+  int dev = 0;
+  FB_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxStaticDevices) return FB_ERR_ARG;
+  std::lock_guard<std::mutex> lk(g_static_mu);
+  if (g_static_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    FB_CUDA_OK(cudaGetSymbolAddress(&p, g_dot_static_scratch));
+    if (p == nullptr) return FB_ERR_CUDA;
+    g_static_ptr[dev] = static_cast<float*>(p);
+  }
+  *out = g_static_ptr[dev];
+  return FB_OK;
+}
+}  // namespace
+}  // namespace fb
+
+extern "C" int64_t fb_dot_product_noalloc_max_floats(void) { return fb::kStaticScratchFloats; }
+
+extern "C" int fb_dot_product_noalloc_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+                                          const float* y_lw, const float* y_uw, const float* y_lb, const float* y_ub,
+                                          float* z_lw, float* z_uw, float* z_lb, float* z_ub,
+                                          int B, int Lx, int Ly, int Di, int K, int words, int p, float eps,
+                                          float out_scale, int layout, void* stream) {
+  if (B < 0 || Lx <= 0 || Ly <= 0 || K <= 0) return FB_ERR_ARG;
+  // ranges of x: 2 * B * Lx * K floats, ranges of y: 2 * B * Ly * K floats (each part padded to 64 floats)
+  const int64_t nx = ((int64_t)B * Lx * K + 63) / 64 * 64, ny = ((int64_t)B * Ly * K + 63) / 64 * 64;
+  if (2 * nx + 2 * ny > fb::kStaticScratchFloats) return FB_ERR_WORKSPACE;
+  float* base = nullptr;
+  const int rc = fb::static_scratch_address(&base);
+  if (rc != FB_OK) return rc;
+  return fb_dot_product_f32(x_lw, x_uw, x_lb, x_ub, y_lw, y_uw, y_lb, y_ub, z_lw, z_uw, z_lb, z_ub,
+                            base, base + nx, base + 2 * nx, base + 2 * nx + ny,
+                            B, Lx, Ly, Di, K, words, p, eps, out_scale, layout, stream);
 }

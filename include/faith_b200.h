@@ -100,6 +100,35 @@ int fb_dot_product_f32(const float* x_lw, const float* x_uw, const float* x_lb, 
                        int B, int Lx, int Ly, int Di, int K, int words, int p, float eps,
                        float out_scale, int layout, void* stream);
 
+/* The same operator for callers that cannot allocate device memory.  (No counterpart in the
+ * reference, whose callers always allocate the scratch tensors themselves.)
+ *
+ * Some hosts of this library are not in a position to call cudaMalloc or to hand over scratch
+ * buffers: code that runs inside someone else's memory plan (a serving process with a fixed
+ * arena, a plugin that only receives its input and output pointers), or a region where an
+ * allocation would synchronise the device.  For them the four operand-range tensors
+ * (x_l, x_u, y_l, y_u) live in a 16 MiB array that is part of the library image on every GPU
+ * that loads it, from load until process exit.  The caller passes inputs and outputs only.
+ *
+ *  - Limit: 2*B*Lx*K + 2*B*Ly*K floats (each operand's share rounded up to 64 floats) must fit
+ *    in fb_dot_product_noalloc_max_floats() = 4 Mi floats; larger problems return
+ *    FB_ERR_WORKSPACE and launch nothing.  256 sentences x 4 heads at L = K = 32 fit exactly.
+ *  - The first call on each device looks up the array's device address (cudaGetSymbolAddress,
+ *    with that device current); make that first call outside any stream capture.
+ *  - The call itself performs no cudaMalloc / cudaFree and calls no allocating library routine.
+ *  - Every call on a device shares the one array.  The ranges are fully rewritten by each call
+ *    before they are read, so nothing needs clearing and stale contents are harmless, but two
+ *    calls that overlap on the GPU (different streams, or different host threads) race on it:
+ *    serialise them.
+ *  - The concretised ranges are not returned; use fb_dot_product_f32 when they are needed.
+ * All other arguments, results and error codes are those of fb_dot_product_f32. */
+int fb_dot_product_noalloc_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+                               const float* y_lw, const float* y_uw, const float* y_lb, const float* y_ub,
+                               float* z_lw, float* z_uw, float* z_lb, float* z_ub,
+                               int B, int Lx, int Ly, int Di, int K, int words, int p, float eps,
+                               float out_scale, int layout, void* stream);
+int64_t fb_dot_product_noalloc_max_floats(void);
+
 /* Elementwise product of two bounded quantities (McCormick planes), fused with the
  * concretisation of both operands.  Replaces Bounds.multiply(Bounds) (Bounds.py:608-651). */
 int fb_mul_bounds_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
