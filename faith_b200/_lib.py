@@ -35,6 +35,7 @@ SIGNATURES = {
     "fb_concretize_f32": [_P] * 6 + [_L, _I, _I, _I, _I, _F, _I, _P],
     "fb_relax_f32": [_I] + [_P] * 8 + [_L, _I, _I, _I, _I, _F, _I, _P, _P],
     "fb_matmul_f32": [_P] * 10 + [_L, _I, _I, _I, _P],
+    "fb_tc_error_flag": [ctypes.POINTER(_I)],
     "fb_dot_product_f32": [_P] * 16 + [_I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P],
     "fb_dot_product_noalloc_f32": [_P] * 12 + [_I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P],
     "fb_dot_product_noalloc_max_floats": [],

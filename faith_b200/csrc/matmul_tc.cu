@@ -1,0 +1,521 @@
+// Split-sign product of bounds with a constant weight on the 5th-generation tensor cores
+// (tcgen05 / TMEM), fp32-accurate through a 3xTF32 split.
+//
+//   y_c = c W^T,  y_r = r |W|^T,  y_lw = y_c - y_r,  y_uw = y_c + y_r,
+//   c = (x_lw + x_uw)/2,  r = (x_uw - x_lw)/2          (centre/radius form of Bounds.py:403-412)
+//
+// Every fp32 operand v is split into hi = tf32(v) and lo = tf32(v - hi); a product a*b is
+// evaluated as a_hi*b_hi + a_hi*b_lo + a_lo*b_hi with fp32 accumulation in tensor memory, which
+// keeps ~21 mantissa bits per product (the dropped lo*lo term is below 2^-22 relative).
+//
+// The tensor cores add into their fp32 accumulator with truncation, a bias that grows with the
+// number of accumulating instructions; the two small cross terms therefore go to accumulators of
+// their own (their truncation is negligible at 2^-11 of the magnitude) and the leading hi*hi term
+// is the only one that touches the main accumulators.  The four partial results are summed with
+// round-to-nearest in registers in the epilogue.
+//
+// One CTA computes a 128 x 64 tile of both outputs.  K is walked in blocks of 32:
+//   warp 0     TMA producer: raw fp32 tiles of x_lw, x_uw (128 rows x 32) and of W (64 rows x 32)
+//              into a two-stage shared-memory ring (128-byte swizzle).
+//   warps 2-9  converters: read the raw tiles, form c, r, split hi/lo, and
+//                - store the four A planes (c_hi, c_lo, r_hi, r_lo) of the block into TENSOR MEMORY
+//                  (tcgen05.st; the A operand of the MMAs comes from TMEM, lane = tile row),
+//                - store the four B planes (W_hi, W_lo, |W|_hi, |W|_lo) into shared memory in the
+//                  K-major 128B-swizzled layout the MMA descriptor expects.
+//   warp 1     MMA issuer (one thread): per 8-wide k step six tcgen05.mma.kind::tf32 instructions
+//              into four fp32 accumulators (centre / radius x main / correction), 64 columns each.
+//   warps 2-9  epilogue: tcgen05.ld the accumulators, y_c -/+ y_r (+ bias), store.
+// TMEM columns: [0,64) centre main, [64,128) radius main, [128,192) centre correction,
+// [192,256) radius correction, [256,512) two buffers of the four A planes.  No cluster launch
+// and no multicast is used.
+//
+// The kernel is persistent: a CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...  with one
+// running k-block counter, so the producer and the converters run ahead into the next tile while
+// the MMAs of the current one finish; the epilogue of tile t is slotted in after two k-blocks of
+// tile t+1 have been converted, which leaves the tensor cores idle only while the accumulators
+// are read out of tensor memory.
+//
+// Every wait on an mbarrier is bounded; on expiry the kernel raises a device-side flag
+// (fb_tc_error_flag), drains, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace fb {
+namespace {
+
+constexpr int BM = 128, BN = 64, BK = 32;
+constexpr int kConvWarps = 8;
+constexpr int kThreads = 32 * (2 + kConvWarps);
+constexpr uint32_t kTileBytes = BM * BK * 4;             // one 128 x 32 fp32 tile of x = 16 KB
+constexpr uint32_t kWTileBytes = BN * BK * 4;            // one 64 x 32 fp32 tile of W = 8 KB
+constexpr uint32_t kRawStageBytes = 2 * kTileBytes + kWTileBytes;  // x_lw, x_uw, W
+constexpr uint32_t kPlaneStageBytes = 4 * kWTileBytes;   // W_hi, W_lo, |W|_hi, |W|_lo
+constexpr uint32_t kSmemBytes = 2 * kRawStageBytes + 2 * kPlaneStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kAccC = 0, kAccR = 64, kCorC = 128, kCorR = 192, kABase = 256;  // TMEM column map
+constexpr unsigned long long kSpinLimit = 1ull << 22;
+
+static __device__ int g_tc_error = 0;
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false (and raises the error flags) when the limit is hit or another
+// role of this CTA has already given up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* cta_abort) {
+  for (unsigned long long i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*cta_abort) return false;
+    if (i > 4096) __nanosleep(64);
+  }
+  *cta_abort = 1;
+  atomicExch(&g_tc_error, 1);
+  return false;
+}
+
+// Same, for a whole warp: every lane waits, and the outcome is made uniform so that the
+// .sync.aligned tensor-memory instructions that follow are executed convergently.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* cta_abort) {
+  const bool ok = mbar_wait(bar, parity, cta_abort);
+  return __all_sync(0xffffffffu, ok);
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// D[tmem] (+)= A[tmem] * B[smem descriptor]^T, tf32 inputs, fp32 accumulate, M = 128.
+__device__ __forceinline__ void mma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+// fp32 -> tf32, round to nearest (ties away from zero), done on the integer pipe: add half a
+// tf32 ulp to the magnitude and clear the 13 low mantissa bits.
+__device__ __forceinline__ uint32_t tf32_rn_bits(float v) { return (__float_as_uint(v) + 0x1000u) & 0xffffe000u; }
+__device__ __forceinline__ void split_tf32(float v, uint32_t& hi, uint32_t& lo) {
+  hi = tf32_rn_bits(v);
+  lo = tf32_rn_bits(fsub(v, __uint_as_float(hi)));   // v - hi is exact in fp32
+}
+
+// Byte offset of (row, 16-byte chunk) inside a 128-row x 128-byte tile with the 128-byte swizzle
+// (chunk index XOR row mod 8); tiles are 1024-byte aligned.
+__device__ __forceinline__ uint32_t swz(int row, int chunk) { return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4)); }
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);        // start address, bits [0,14)
+  d |= (uint64_t)1 << 16;                         // leading byte offset (unused with swizzle), bits [16,30)
+  d |= (uint64_t)(1024 >> 4) << 32;               // stride byte offset, bits [32,46)
+  d |= (uint64_t)1 << 46;                         // descriptor version (Blackwell), bits [46,48)
+  d |= (uint64_t)2 << 61;                         // layout type SWIZZLE_128B, bits [61,64)
+  return d;
+}
+
+// Instruction descriptor: D fp32, A and B tf32, both K-major, M = 128, N = 128.
+constexpr uint32_t kInstrDesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+struct SharedLayout {
+  // offsets from the 1024-byte aligned base
+  __host__ __device__ static constexpr uint32_t raw(int s) { return (uint32_t)s * kRawStageBytes; }
+  __host__ __device__ static constexpr uint32_t planes(int s) { return 2 * kRawStageBytes + (uint32_t)s * kPlaneStageBytes; }
+  __host__ __device__ static constexpr uint32_t bars() { return 2 * kRawStageBytes + 2 * kPlaneStageBytes; }
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_constant__ CUtensorMap tm_up,
+                   const __grid_constant__ CUtensorMap tm_w, const float* __restrict__ bias,
+                   float* __restrict__ c_lo, float* __restrict__ c_up, int64_t M, int N, int K, int n_tiles_n,
+                   int64_t total_tiles) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  // barriers: full[2], raw_empty[2], ops_ready[2], mma_done[2], acc_ready, acc_free; then the TMEM base slot and the abort flag
+  const uint32_t bar0 = base + SharedLayout::bars();
+  const uint32_t bar_full[2] = {bar0 + 0, bar0 + 8};
+  const uint32_t bar_raw_empty[2] = {bar0 + 16, bar0 + 24};
+  const uint32_t bar_ops_ready[2] = {bar0 + 32, bar0 + 40};
+  const uint32_t bar_mma_done[2] = {bar0 + 48, bar0 + 56};
+  const uint32_t bar_acc_ready = bar0 + 64;
+  const uint32_t bar_acc_free = bar0 + 72;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + SharedLayout::bars() + 80);
+  volatile int* cta_abort = reinterpret_cast<volatile int*>(base_ptr + SharedLayout::bars() + 96);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nkb = (K + BK - 1) / BK;
+  // tiles of this CTA: blockIdx.x + i * gridDim.x, i = 0 .. my_tiles-1; n is the fast tile index
+  const int64_t my_tiles = (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
+  const int64_t total_it = my_tiles * nkb;   // k-blocks this CTA walks, across all its tiles
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_full[s], 1);
+      mbar_init(bar_raw_empty[s], kConvWarps);
+      mbar_init(bar_ops_ready[s], kConvWarps);
+      mbar_init(bar_mma_done[s], 1);
+    }
+    mbar_init(bar_acc_ready, 1);
+    mbar_init(bar_acc_free, kConvWarps);
+    *cta_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {  // one warp allocates all of tensor memory for this CTA
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      int64_t it = 0;
+      bool ok = true;
+      for (int64_t ti = 0; ti < my_tiles && ok; ++ti) {
+        const int64_t tile = blockIdx.x + ti * gridDim.x;
+        const int m0 = (int)(tile / n_tiles_n) * BM, n0 = (int)(tile % n_tiles_n) * BN;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = (int)(it & 1);
+          if (it >= 2 && !mbar_wait(bar_raw_empty[s], (uint32_t)(((it >> 1) - 1) & 1), cta_abort)) { ok = false; break; }
+          mbar_arrive_expect_tx(bar_full[s], kRawStageBytes);
+          const uint32_t dst = base + SharedLayout::raw(s);
+          tma_load_2d(dst, &tm_lo, kb * BK, m0, bar_full[s]);
+          tma_load_2d(dst + kTileBytes, &tm_up, kb * BK, m0, bar_full[s]);
+          tma_load_2d(dst + 2 * kTileBytes, &tm_w, kb * BK, n0, bar_full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      bool ok = true;
+      int64_t it = 0;
+      for (int64_t ti = 0; ti < my_tiles && ok; ++ti) {
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = (int)(it & 1);
+          ok = mbar_wait(bar_ops_ready[s], (uint32_t)((it >> 1) & 1), cta_abort);
+          // the first MMA of a tile overwrites the accumulators: the previous tile must have been read out
+          if (ok && kb == 0 && ti > 0) ok = mbar_wait(bar_acc_free, (uint32_t)((ti - 1) & 1), cta_abort);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t pl = base + SharedLayout::planes(s);
+          const uint32_t a_cols = tmem_base + kABase + (uint32_t)s * 128u;
+#pragma unroll
+          for (int j = 0; j < BK / 8; ++j) {
+            const uint32_t acc = (kb > 0 || j > 0) ? 1u : 0u;
+            const uint64_t b_whi = smem_desc_sw128(pl + 0 * kWTileBytes + j * 32);
+            const uint64_t b_wlo = smem_desc_sw128(pl + 1 * kWTileBytes + j * 32);
+            const uint64_t b_ahi = smem_desc_sw128(pl + 2 * kWTileBytes + j * 32);
+            const uint64_t b_alo = smem_desc_sw128(pl + 3 * kWTileBytes + j * 32);
+            const uint32_t a_chi = a_cols + 0 + j * 8, a_clo = a_cols + 32 + j * 8;
+            const uint32_t a_rhi = a_cols + 64 + j * 8, a_rlo = a_cols + 96 + j * 8;
+            mma_tf32_ts(tmem_base + kCorC, a_clo, b_whi, kInstrDesc, acc);
+            mma_tf32_ts(tmem_base + kCorC, a_chi, b_wlo, kInstrDesc, 1u);
+            mma_tf32_ts(tmem_base + kAccC, a_chi, b_whi, kInstrDesc, acc);
+            mma_tf32_ts(tmem_base + kCorR, a_rlo, b_ahi, kInstrDesc, acc);
+            mma_tf32_ts(tmem_base + kCorR, a_rhi, b_alo, kInstrDesc, 1u);
+            mma_tf32_ts(tmem_base + kAccR, a_rhi, b_ahi, kInstrDesc, acc);
+          }
+          tc_commit(bar_mma_done[s]);
+          if (kb == nkb - 1) tc_commit(bar_acc_ready);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------- converters, then epilogue
+    const int cw = warp - 2;           // 0..7
+    const int ct = threadIdx.x - 64;   // converter thread index 0..255
+    const int quarter = warp & 3;      // TMEM lane quarter this warp may access
+    const int half = cw >> 2;          // which 16 of the 32 k values of a block
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    bool ok = true;
+    // The epilogue of tile e runs after this many k-blocks (counted over all tiles) have been
+    // converted: two blocks into tile e+1, or at the very end for the last tile.
+    const int lead = nkb >= 2 ? 2 : 1;
+    int64_t epi_tile = 0;
+    for (int64_t it = 0; it < total_it && ok; ++it) {
+      const int s = (int)(it & 1);
+      ok = mbar_wait_warp(bar_full[s], (uint32_t)((it >> 1) & 1), cta_abort);
+      if (!ok) break;
+      const uint8_t* raw = base_ptr + SharedLayout::raw(s);
+      float4 vl[4], vu[4], vw[2];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const uint32_t off = swz(row, half * 4 + c);
+        vl[c] = *reinterpret_cast<const float4*>(raw + off);
+        vu[c] = *reinterpret_cast<const float4*>(raw + kTileBytes + off);
+      }
+      // W tile: 64 rows x 8 chunks; this thread converts two adjacent chunks of one row
+      const int wrow = ct >> 2, wchunk = (ct & 3) * 2;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) vw[c] = *reinterpret_cast<const float4*>(raw + 2 * kTileBytes + swz(wrow, wchunk + c));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_raw_empty[s]);
+      if (it >= 2) {
+        ok = mbar_wait_warp(bar_mma_done[s], (uint32_t)(((it >> 1) - 1) & 1), cta_abort);
+        if (!ok) break;
+        tc_fence_after();
+      }
+      {
+        uint32_t chi[16], clo[16], rhi[16], rlo[16];
+        uint8_t* pl = base_ptr + SharedLayout::planes(s);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const float l4[4] = {vl[c].x, vl[c].y, vl[c].z, vl[c].w};
+          const float u4[4] = {vu[c].x, vu[c].y, vu[c].z, vu[c].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            split_tf32(fmul(fadd(l4[e], u4[e]), 0.5f), chi[c * 4 + e], clo[c * 4 + e]);
+            split_tf32(fmul(fsub(u4[e], l4[e]), 0.5f), rhi[c * 4 + e], rlo[c * 4 + e]);
+          }
+        }
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const float w4[4] = {vw[c].x, vw[c].y, vw[c].z, vw[c].w};
+          uint32_t whi[4], wlo[4], ahi[4], alo[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            split_tf32(w4[e], whi[e], wlo[e]);
+            // |w| = sgn(w) * (hi + lo): flip the sign of both parts where w is negative
+            const uint32_t flip = __float_as_uint(w4[e]) & 0x80000000u;
+            ahi[e] = whi[e] ^ flip;
+            alo[e] = wlo[e] ^ flip;
+          }
+          const uint32_t off = swz(wrow, wchunk + c);
+          *reinterpret_cast<uint4*>(pl + 0 * kWTileBytes + off) = make_uint4(whi[0], whi[1], whi[2], whi[3]);
+          *reinterpret_cast<uint4*>(pl + 1 * kWTileBytes + off) = make_uint4(wlo[0], wlo[1], wlo[2], wlo[3]);
+          *reinterpret_cast<uint4*>(pl + 2 * kWTileBytes + off) = make_uint4(ahi[0], ahi[1], ahi[2], ahi[3]);
+          *reinterpret_cast<uint4*>(pl + 3 * kWTileBytes + off) = make_uint4(alo[0], alo[1], alo[2], alo[3]);
+        }
+        const uint32_t a_cols = tmem_base + lane_addr + kABase + (uint32_t)s * 128u + (uint32_t)half * 16u;
+        tmem_st16(a_cols + 0, chi);
+        tmem_st16(a_cols + 32, clo);
+        tmem_st16(a_cols + 64, rhi);
+        tmem_st16(a_cols + 96, rlo);
+      }
+      tmem_wait_st();
+      fence_async_smem();   // B planes were written through the generic proxy; the MMA reads them through the async proxy
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_ops_ready[s]);
+
+      // ---- epilogue of tile epi_tile, once the conversion is `lead` blocks into the next tile
+      const bool last_it = (it + 1 == total_it);
+      if (it + 1 == (epi_tile + 1) * nkb + lead || last_it) {
+        // at the very end, up to two tiles can be outstanding (nkb == 1): drain them all
+        while (ok && epi_tile < my_tiles && ((epi_tile + 1) * nkb + lead <= it + 1 || last_it)) {
+          ok = mbar_wait_warp(bar_acc_ready, (uint32_t)(epi_tile & 1), cta_abort);
+          if (!ok) break;
+          tc_fence_after();
+          const int64_t etile = blockIdx.x + epi_tile * gridDim.x;
+          const int64_t m = (etile / n_tiles_n) * BM + row;
+          const int ncol = half * 32;
+          const int nb = (int)(etile % n_tiles_n) * BN + ncol;
+          uint32_t t0[32], t1[32];
+          float yc[32], yr[32];
+          tmem_ld32(tmem_base + lane_addr + kAccC + ncol, t0);
+          tmem_ld32(tmem_base + lane_addr + kCorC + ncol, t1);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) yc[i] = fadd(__uint_as_float(t0[i]), __uint_as_float(t1[i]));
+          tmem_ld32(tmem_base + lane_addr + kAccR + ncol, t0);
+          tmem_ld32(tmem_base + lane_addr + kCorR + ncol, t1);
+          tmem_wait_ld();
+          // the accumulators are in registers now: hand tensor memory back to the MMA issuer
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_acc_free);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) yr[i] = fadd(__uint_as_float(t0[i]), __uint_as_float(t1[i]));
+          if (m < M) {
+            const bool vec_out = (N % 4 == 0) && aligned16(c_lo) && aligned16(c_up);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const int n = nb + q * 4;
+              float lo[4], up[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                lo[e] = fsub(yc[q * 4 + e], yr[q * 4 + e]);
+                up[e] = fadd(yc[q * 4 + e], yr[q * 4 + e]);
+                if (bias != nullptr && n + e < N) { lo[e] = fadd(lo[e], bias[n + e]); up[e] = fadd(up[e], bias[n + e]); }
+              }
+              if (vec_out && n + 3 < N) {
+                *reinterpret_cast<float4*>(c_lo + m * N + n) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+                *reinterpret_cast<float4*>(c_up + m * N + n) = make_float4(up[0], up[1], up[2], up[3]);
+              } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                  if (n + e < N) { c_lo[m * N + n + e] = lo[e]; c_up[m * N + n + e] = up[e]; }
+              }
+            }
+          }
+          ++epi_tile;
+        }
+      }
+    }
+  }
+  // Tear-down.  On the error path, give outstanding bulk copies time to land before the shared
+  // memory is released (bounded), then free the tensor memory.
+  if (*cta_abort) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, []() {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// 2-D fp32 row-major [rows, cols] tensor, box `box_rows` rows x 32 columns, 128-byte swizzle, zero fill.
+bool make_map(CUtensorMap* map, const float* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * sizeof(float)};
+  const cuuint32_t box[2] = {BK, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(ptr), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+bool tc_gemm_supported(const float* a_lo, const float* a_up, const float* W, int64_t M, int N, int K) {
+  return M >= 256 && M < (1ll << 31) && N >= 32 && K >= 8 && K % 4 == 0 && aligned16(a_lo) && aligned16(a_up) &&
+         aligned16(W) && encode_fn() != nullptr;
+}
+
+int launch_split_sign_tc(const float* a_lo, const float* a_up, const float* W, const float* bias, float* c_lo,
+                         float* c_up, int64_t M, int N, int K, cudaStream_t st) {
+  CUtensorMap tm_lo, tm_up, tm_w;
+  if (!make_map(&tm_lo, a_lo, (uint64_t)M, (uint64_t)K, BM) || !make_map(&tm_up, a_up, (uint64_t)M, (uint64_t)K, BM) ||
+      !make_map(&tm_w, W, (uint64_t)N, (uint64_t)K, BN))
+    return FB_ERR_CUDA;
+  const int64_t gm = ceil_div(M, BM);
+  const int gn = (int)ceil_div(N, BN);
+  const int64_t total_tiles = gm * gn;
+  static std::once_flag attr_once[64];
+  int dev = 0;
+  FB_CUDA_OK(cudaGetDevice(&dev));
+  cudaError_t attr_err = cudaSuccess;
+  std::call_once(attr_once[dev & 63], [&]() {
+    attr_err = cudaFuncSetAttribute(split_sign_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+  });
+  FB_CUDA_OK(attr_err);
+  // persistent: one CTA per SM (tensor memory and shared memory allow exactly one)
+  const int64_t sms = device_info().sms;
+  const unsigned grid = (unsigned)(total_tiles < sms ? total_tiles : sms);
+  split_sign_gemm_tc<<<grid, kThreads, kSmemBytes, st>>>(tm_lo, tm_up, tm_w, bias, c_lo, c_up, M, N, K, gn, total_tiles);
+  FB_LAUNCH_OK();
+  return FB_OK;
+}
+
+}  // namespace fb
+
+// Reads (and clears) the device-side flag that the tensor-core GEMM raises when one of its bounded
+// waits expires.  Synchronises the device.
+extern "C" int fb_tc_error_flag(int* flag) {
+  if (!flag) return FB_ERR_ARG;
+  int v = 0;
+  FB_CUDA_OK(cudaDeviceSynchronize());
+  FB_CUDA_OK(cudaMemcpyFromSymbol(&v, fb::g_tc_error, sizeof(int)));
+  if (v != 0) {
+    const int zero = 0;
+    FB_CUDA_OK(cudaMemcpyToSymbol(fb::g_tc_error, &zero, sizeof(int)));
+  }
+  *flag = v;
+  return FB_OK;
+}

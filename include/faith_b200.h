@@ -83,6 +83,11 @@ int fb_matmul_f32(const float* x_lw, const float* x_uw, const float* x_lb, const
                   float* y_lw, float* y_uw, float* y_lb, float* y_ub,
                   int64_t rows, int Di, int Do, int Dy, void* stream);
 
+/* The tensor-core GEMM behind fb_matmul_f32 bounds every wait inside the kernel; if a wait ever
+ * expires, the kernel raises a device-side flag, frees its tensor memory and returns.  This call
+ * synchronises the device, returns the flag in *flag (0 = never raised) and clears it. */
+int fb_tc_error_flag(int* flag);
+
 /* Bound x bound dot product  z[b,i,j] = sum_k x[b,i,k] * y[b,j,k]  (attention scores and,
  * with y = transposed values, the attention context).  Replaces Bounds.ori_dot_product
  * (Bounds.py:710-823) and c_dot_product_verification_QK / _V (kernel.cpp:133-241).

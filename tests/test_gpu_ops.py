@@ -156,9 +156,10 @@ def test_matmul_shapes(shape, Dy):
     _cmp(g, o, "dense %s->%d" % (shape, Dy), rtol=1e-5, atol=2e-6)
 
 
-def test_matmul_identity_input_is_exact():
-    """First-layer case: lw = uw = one-hot rows; each output is a single product, so any
-    summation order gives the same bits as the reference."""
+def test_matmul_identity_input():
+    """First-layer case: lw = uw = one-hot rows, so every output is a single product 1 * w.  The
+    CUDA-core kernel reproduces the reference bit for bit; the tensor-core kernel carries the
+    weight as two TF32 parts (22 mantissa bits), i.e. within 2^-21 relative."""
     import faith_b200
     D = 64
     lw = torch.zeros(1, 4, D, D)
@@ -167,7 +168,18 @@ def test_matmul_identity_input_is_exact():
     W = torch.randn(128, D, generator=torch.Generator().manual_seed(4)) / 8
     o = O.OBounds(2.0, 0.1, lw, emb, lw.clone(), emb.clone()).matmul(W)
     g = faith_b200.BoundsLite(2.0, 0.1, lw.to(DEV), emb.to(DEV), lw.to(DEV), emb.to(DEV)).matmul(W.to(DEV))
-    assert torch.equal(g.lw.cpu(), o.lw) and torch.equal(g.uw.cpu(), o.uw)
+    helpers.assert_close(g.lw, o.lw, "lw", rtol=2.0 ** -21, atol=0.0)
+    helpers.assert_close(g.uw, o.uw, "uw", rtol=2.0 ** -21, atol=0.0)
+    assert torch.equal(g.lw, g.uw)          # radius is exactly zero when lw == uw
+    helpers.assert_close(g.lb, o.lb, "lb")  # the 4-row bias GEMM runs on the CUDA cores
+
+
+def test_tensor_core_gemm_never_raised_its_error_flag():
+    import ctypes
+    import faith_b200
+    flag = ctypes.c_int(-1)
+    assert faith_b200.load().fb_tc_error_flag(ctypes.byref(flag)) == 0
+    assert flag.value == 0
 
 
 # ------------------------------------------------------------- dot product
