@@ -5,7 +5,8 @@
 #include <cstring>
 
 namespace fb {
-bool tc_gemm_supported(const float* a_lo, const float* a_up, const float* W, int64_t M, int N, int K);
+bool tc_gemm_supported(const float* a_lo, const float* a_up, const float* W, const float* c_lo, const float* c_up,
+                       int64_t M, int N, int K);
 int launch_split_sign_tc(const float* a_lo, const float* a_up, const float* W, const float* bias, float* c_lo,
                          float* c_up, int64_t M, int N, int K, cudaStream_t st);
 int launch_split_sign_ffma(const float* a_lo, const float* a_up, const float* W, const float* bias, float* c_lo,
@@ -23,7 +24,7 @@ static bool use_tensor_cores() {
 
 static int split_sign_gemm(const float* a_lo, const float* a_up, const float* W, const float* bias, float* c_lo,
                            float* c_up, int64_t M, int N, int K, cudaStream_t st) {
-  if (use_tensor_cores() && tc_gemm_supported(a_lo, a_up, W, M, N, K))
+  if (use_tensor_cores() && tc_gemm_supported(a_lo, a_up, W, c_lo, c_up, M, N, K))
     return launch_split_sign_tc(a_lo, a_up, W, bias, c_lo, c_up, M, N, K, st);
   return launch_split_sign_ffma(a_lo, a_up, W, bias, c_lo, c_up, M, N, K, st);
 }

@@ -24,7 +24,8 @@
 //                  K-major 128B-swizzled layout the MMA descriptor expects.
 //   warp 1     MMA issuer (one thread): per 8-wide k step six tcgen05.mma.kind::tf32 instructions
 //              into four fp32 accumulators (centre / radius x main / correction), 64 columns each.
-//   warps 2-9  epilogue: tcgen05.ld the accumulators, y_c -/+ y_r (+ bias), store.
+//   warps 2-9  epilogue: tcgen05.ld the accumulators, y_c -/+ y_r (+ bias), stage the two output tiles in
+//              shared memory (swizzled) and write them with TMA stores (full 128-byte lines).
 // TMEM columns: [0,64) centre main, [64,128) radius main, [128,192) centre correction,
 // [192,256) radius correction, [256,512) two buffers of the four A planes.  No cluster launch
 // and no multicast is used.
@@ -53,12 +54,17 @@ constexpr uint32_t kTileBytes = BM * BK * 4;             // one 128 x 32 fp32 ti
 constexpr uint32_t kWTileBytes = BN * BK * 4;            // one 64 x 32 fp32 tile of W = 8 KB
 constexpr uint32_t kRawStageBytes = 2 * kTileBytes + kWTileBytes;  // x_lw, x_uw, W
 constexpr uint32_t kPlaneStageBytes = 4 * kWTileBytes;   // W_hi, W_lo, |W|_hi, |W|_lo
-constexpr uint32_t kSmemBytes = 2 * kRawStageBytes + 2 * kPlaneStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int kRawStages = 2;                            // TMA runs two k-blocks ahead
+constexpr uint32_t kOutBoxBytes = BM * 32 * 4;            // one 128-row x 32-column fp32 box of an output tile = 16 KB
+constexpr uint32_t kOutStageBytes = 4 * kOutBoxBytes;    // lower and upper output tile, two boxes each
+constexpr uint32_t kSmemBytes = kRawStages * kRawStageBytes + 2 * kPlaneStageBytes + kOutStageBytes + 1024 /*align*/ + 256 /*barriers*/;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kAccC = 0, kAccR = 64, kCorC = 128, kCorR = 192, kABase = 256;  // TMEM column map
-constexpr unsigned long long kSpinLimit = 1ull << 22;
+constexpr uint32_t kTryNs = 20000;       // suspend-time hint of one mbarrier try (ns)
+constexpr uint32_t kMaxTries = 100000;  // x 20 us = 2 s upper bound for any single wait
 
 static __device__ int g_tc_error = 0;
+
 
 // ------------------------------------------------------------------ PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -72,24 +78,26 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+// One try: the hardware suspends the thread until the phase completes or ~`ns` nanoseconds pass, so a
+// waiting warp does not compete for issue slots with the MMA issuer and the converters.
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uint32_t ns) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(ns)
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns false (and raises the error flags) when the limit is hit or another
-// role of this CTA has already given up.
+// Bounded wait: at most kMaxTries suspended tries of ~kTryNs each (a couple of seconds in total).
+// Returns false (and raises the error flags) when the limit is hit or another role of this CTA has
+// already given up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* cta_abort) {
-  for (unsigned long long i = 0; i < kSpinLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
+  for (uint32_t i = 0; i < kMaxTries; ++i) {
+    if (mbar_try_wait(bar, parity, kTryNs)) return true;
     if (*cta_abort) return false;
-    if (i > 4096) __nanosleep(64);
   }
   *cta_abort = 1;
   atomicExch(&g_tc_error, 1);
@@ -110,6 +118,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+               ::"l"(map), "r"(x), "r"(y), "r"(src) : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// waits until the bulk stores committed so far have finished READING shared memory
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
 }
@@ -126,15 +143,55 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-// D[tmem] (+)= A[tmem] * B[smem descriptor]^T, tf32 inputs, fp32 accumulate, M = 128.
-__device__ __forceinline__ void mma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                            uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
-      : "memory");
+// D[tmem] (+)= A[tmem] * B[smem descriptor]^T, tf32 inputs, fp32 accumulate, M = 128; the
+// descriptor is given as two 32-bit halves and the accumulate flag is a compile-time constant, so
+// that the issuing thread spends one instruction per MMA (operands are loop-invariant registers).
+template <bool kAccumulate>
+__device__ __forceinline__ void mma_tf32_ts_lean(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
+                                                 uint32_t idesc) {
+  if (kAccumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 bd;\n\t"
+        "setp.eq.b32 p, 0, 0;\n\t"
+        "mov.b64 bd, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], bd, %4, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(0u)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 bd;\n\t"
+        "setp.ne.b32 p, 0, 0;\n\t"
+        "mov.b64 bd, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], bd, %4, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(0u)
+        : "memory");
+  }
+}
+
+// The 24 MMAs of one k-block (4 k steps x 6).  kFirst: this k-block starts a tile, so the first
+// MMA into each accumulator overwrites instead of accumulating.
+template <bool kFirst>
+__device__ __forceinline__ void issue_kblock(const uint32_t (&blo)[4][4], const uint32_t (&acol)[4][4], uint32_t b_hi,
+                                             uint32_t d_ac, uint32_t d_ar, uint32_t d_cc, uint32_t d_cr, uint32_t idesc) {
+  // planes of B: 0 W_hi, 1 W_lo, 2 |W|_hi, 3 |W|_lo;  planes of A: 0 c_hi, 1 c_lo, 2 r_hi, 3 r_lo
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (j == 0 && kFirst) {
+      mma_tf32_ts_lean<false>(d_cc, acol[1][j], blo[0][j], b_hi, idesc);
+      mma_tf32_ts_lean<true>(d_cc, acol[0][j], blo[1][j], b_hi, idesc);
+      mma_tf32_ts_lean<false>(d_ac, acol[0][j], blo[0][j], b_hi, idesc);
+      mma_tf32_ts_lean<false>(d_cr, acol[3][j], blo[2][j], b_hi, idesc);
+      mma_tf32_ts_lean<true>(d_cr, acol[2][j], blo[3][j], b_hi, idesc);
+      mma_tf32_ts_lean<false>(d_ar, acol[2][j], blo[2][j], b_hi, idesc);
+    } else {
+      mma_tf32_ts_lean<true>(d_cc, acol[1][j], blo[0][j], b_hi, idesc);
+      mma_tf32_ts_lean<true>(d_cc, acol[0][j], blo[1][j], b_hi, idesc);
+      mma_tf32_ts_lean<true>(d_ac, acol[0][j], blo[0][j], b_hi, idesc);
+      mma_tf32_ts_lean<true>(d_cr, acol[3][j], blo[2][j], b_hi, idesc);
+      mma_tf32_ts_lean<true>(d_cr, acol[2][j], blo[3][j], b_hi, idesc);
+      mma_tf32_ts_lean<true>(d_ar, acol[2][j], blo[2][j], b_hi, idesc);
+    }
+  }
 }
 
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* v) {
@@ -188,28 +245,30 @@ constexpr uint32_t kInstrDesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)
 struct SharedLayout {
   // offsets from the 1024-byte aligned base
   __host__ __device__ static constexpr uint32_t raw(int s) { return (uint32_t)s * kRawStageBytes; }
-  __host__ __device__ static constexpr uint32_t planes(int s) { return 2 * kRawStageBytes + (uint32_t)s * kPlaneStageBytes; }
-  __host__ __device__ static constexpr uint32_t bars() { return 2 * kRawStageBytes + 2 * kPlaneStageBytes; }
+  __host__ __device__ static constexpr uint32_t planes(int s) { return kRawStages * kRawStageBytes + (uint32_t)s * kPlaneStageBytes; }
+  __host__ __device__ static constexpr uint32_t out() { return kRawStages * kRawStageBytes + 2 * kPlaneStageBytes; }
+  __host__ __device__ static constexpr uint32_t bars() { return out() + kOutStageBytes; }
 };
 
 __global__ void __launch_bounds__(kThreads, 1)
 split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_constant__ CUtensorMap tm_up,
-                   const __grid_constant__ CUtensorMap tm_w, const float* __restrict__ bias,
-                   float* __restrict__ c_lo, float* __restrict__ c_up, int64_t M, int N, int K, int n_tiles_n,
-                   int64_t total_tiles) {
+                   const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_out_lo,
+                   const __grid_constant__ CUtensorMap tm_out_up, const float* __restrict__ bias, int64_t M, int N, int K,
+                   int n_tiles_n, int64_t total_tiles) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
   // barriers: full[2], raw_empty[2], ops_ready[2], mma_done[2], acc_ready, acc_free; then the TMEM base slot and the abort flag
   const uint32_t bar0 = base + SharedLayout::bars();
-  const uint32_t bar_full[2] = {bar0 + 0, bar0 + 8};
-  const uint32_t bar_raw_empty[2] = {bar0 + 16, bar0 + 24};
-  const uint32_t bar_ops_ready[2] = {bar0 + 32, bar0 + 40};
-  const uint32_t bar_mma_done[2] = {bar0 + 48, bar0 + 56};
-  const uint32_t bar_acc_ready = bar0 + 64;
-  const uint32_t bar_acc_free = bar0 + 72;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + SharedLayout::bars() + 80);
-  volatile int* cta_abort = reinterpret_cast<volatile int*>(base_ptr + SharedLayout::bars() + 96);
+  const uint32_t bar_full = bar0 + 0;            // [kRawStages]
+  const uint32_t bar_raw_empty = bar0 + 32;      // [kRawStages]
+  const uint32_t bar_ops_ready = bar0 + 64;      // [2]   (addresses are computed, never indexed from
+  const uint32_t bar_mma_done = bar0 + 80;       // [2]    an array: that would live in local memory)
+  const uint32_t bar_acc_ready = bar0 + 96;
+  const uint32_t bar_acc_free = bar0 + 104;
+  const uint32_t bar_conv = bar0 + 128;          // rendezvous of the converter warps in the epilogue (bounded, unlike bar.sync)
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + SharedLayout::bars() + 112);
+  volatile int* cta_abort = reinterpret_cast<volatile int*>(base_ptr + SharedLayout::bars() + 120);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nkb = (K + BK - 1) / BK;
@@ -218,14 +277,17 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
   const int64_t total_it = my_tiles * nkb;   // k-blocks this CTA walks, across all its tiles
 
   if (threadIdx.x == 0) {
+    for (int s = 0; s < kRawStages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_raw_empty + 8 * s, kConvWarps);
+    }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(bar_full[s], 1);
-      mbar_init(bar_raw_empty[s], kConvWarps);
-      mbar_init(bar_ops_ready[s], kConvWarps);
-      mbar_init(bar_mma_done[s], 1);
+      mbar_init(bar_ops_ready + 8 * s, kConvWarps);
+      mbar_init(bar_mma_done + 8 * s, 1);
     }
     mbar_init(bar_acc_ready, 1);
     mbar_init(bar_acc_free, kConvWarps);
+    mbar_init(bar_conv, kConvWarps);
     *cta_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -240,57 +302,69 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
-    if (lane == 0) {
-      int64_t it = 0;
-      bool ok = true;
-      for (int64_t ti = 0; ti < my_tiles && ok; ++ti) {
-        const int64_t tile = blockIdx.x + ti * gridDim.x;
-        const int m0 = (int)(tile / n_tiles_n) * BM, n0 = (int)(tile % n_tiles_n) * BN;
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
-          const int s = (int)(it & 1);
-          if (it >= 2 && !mbar_wait(bar_raw_empty[s], (uint32_t)(((it >> 1) - 1) & 1), cta_abort)) { ok = false; break; }
-          mbar_arrive_expect_tx(bar_full[s], kRawStageBytes);
-          const uint32_t dst = base + SharedLayout::raw(s);
-          tma_load_2d(dst, &tm_lo, kb * BK, m0, bar_full[s]);
-          tma_load_2d(dst + kTileBytes, &tm_up, kb * BK, m0, bar_full[s]);
-          tma_load_2d(dst + 2 * kTileBytes, &tm_w, kb * BK, n0, bar_full[s]);
+    // the whole warp walks the loop convergently (a lone thread looping while its 31 siblings sit at
+    // the final barrier runs much slower); only the copy instructions are issued by lane 0
+    int64_t it = 0;
+    bool ok = true;
+    for (int64_t ti = 0; ti < my_tiles && ok; ++ti) {
+      const int64_t tile = blockIdx.x + ti * gridDim.x;
+      const int m0 = (int)(tile / n_tiles_n) * BM, n0 = (int)(tile % n_tiles_n) * BN;
+      for (int kb = 0; kb < nkb; ++kb, ++it) {
+        const int rs = (int)(it % kRawStages);
+        const uint32_t full = bar_full + 8 * rs;
+        if (it >= kRawStages &&
+            !mbar_wait_warp(bar_raw_empty + 8 * rs, (uint32_t)((it / kRawStages - 1) & 1), cta_abort)) { ok = false; break; }
+        if (lane == 0) {
+          mbar_arrive_expect_tx(full, kRawStageBytes);
+          const uint32_t dst = base + SharedLayout::raw(rs);
+          tma_load_2d(dst, &tm_lo, kb * BK, m0, full);
+          tma_load_2d(dst + kTileBytes, &tm_up, kb * BK, m0, full);
+          tma_load_2d(dst + 2 * kTileBytes, &tm_w, kb * BK, n0, full);
         }
+        __syncwarp();
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      bool ok = true;
-      int64_t it = 0;
-      for (int64_t ti = 0; ti < my_tiles && ok; ++ti) {
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
-          const int s = (int)(it & 1);
-          ok = mbar_wait(bar_ops_ready[s], (uint32_t)((it >> 1) & 1), cta_abort);
-          // the first MMA of a tile overwrites the accumulators: the previous tile must have been read out
-          if (ok && kb == 0 && ti > 0) ok = mbar_wait(bar_acc_free, (uint32_t)((ti - 1) & 1), cta_abort);
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t pl = base + SharedLayout::planes(s);
-          const uint32_t a_cols = tmem_base + kABase + (uint32_t)s * 128u;
+    bool ok = true;
+    int64_t it = 0;
+    // The warp walks the loop convergently; lane 0 issues.  Descriptors are built once and only
+    // advanced by compile-time constants inside the loop.
+    const uint64_t bdesc0 = smem_desc_sw128(base + SharedLayout::planes(0));
+    const uint32_t d_cc = tmem_base + kCorC, d_ac = tmem_base + kAccC, d_cr = tmem_base + kCorR, d_ar = tmem_base + kAccR;
+    // every operand of the 2 x 24 MMAs (two operand stages) lives in a loop-invariant register
+    const uint32_t b_hi = (uint32_t)(bdesc0 >> 32);
+    uint32_t blo[2][4][4], acol[2][4][4];
 #pragma unroll
-          for (int j = 0; j < BK / 8; ++j) {
-            const uint32_t acc = (kb > 0 || j > 0) ? 1u : 0u;
-            const uint64_t b_whi = smem_desc_sw128(pl + 0 * kWTileBytes + j * 32);
-            const uint64_t b_wlo = smem_desc_sw128(pl + 1 * kWTileBytes + j * 32);
-            const uint64_t b_ahi = smem_desc_sw128(pl + 2 * kWTileBytes + j * 32);
-            const uint64_t b_alo = smem_desc_sw128(pl + 3 * kWTileBytes + j * 32);
-            const uint32_t a_chi = a_cols + 0 + j * 8, a_clo = a_cols + 32 + j * 8;
-            const uint32_t a_rhi = a_cols + 64 + j * 8, a_rlo = a_cols + 96 + j * 8;
-            mma_tf32_ts(tmem_base + kCorC, a_clo, b_whi, kInstrDesc, acc);
-            mma_tf32_ts(tmem_base + kCorC, a_chi, b_wlo, kInstrDesc, 1u);
-            mma_tf32_ts(tmem_base + kAccC, a_chi, b_whi, kInstrDesc, acc);
-            mma_tf32_ts(tmem_base + kCorR, a_rlo, b_ahi, kInstrDesc, acc);
-            mma_tf32_ts(tmem_base + kCorR, a_rhi, b_alo, kInstrDesc, 1u);
-            mma_tf32_ts(tmem_base + kAccR, a_rhi, b_ahi, kInstrDesc, acc);
+    for (int st = 0; st < 2; ++st)
+#pragma unroll
+      for (int pl = 0; pl < 4; ++pl)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          // descriptor address field is in 16-byte units: stage, plane, k step -> byte offset / 16
+          blo[st][pl][j] = (uint32_t)bdesc0 + ((st * kPlaneStageBytes + pl * kWTileBytes + j * 32) >> 4);
+          acol[st][pl][j] = tmem_base + kABase + st * 128 + pl * 32 + j * 8;
+        }
+    for (int64_t ti = 0; ti < my_tiles && ok; ++ti) {
+      for (int kb = 0; kb < nkb; ++kb, ++it) {
+        const int s = (int)(it & 1);
+        ok = mbar_wait_warp(bar_ops_ready + 8 * s, (uint32_t)((it >> 1) & 1), cta_abort);
+        // the first MMA of a tile overwrites the accumulators: the previous tile must have been read out
+        if (ok && kb == 0 && ti > 0) ok = mbar_wait_warp(bar_acc_free, (uint32_t)((ti - 1) & 1), cta_abort);
+        if (!ok) break;
+        tc_fence_after();
+        if (lane == 0) {
+          if (s == 0) {
+            if (kb == 0) issue_kblock<true>(blo[0], acol[0], b_hi, d_ac, d_ar, d_cc, d_cr, kInstrDesc);
+            else issue_kblock<false>(blo[0], acol[0], b_hi, d_ac, d_ar, d_cc, d_cr, kInstrDesc);
+          } else {
+            if (kb == 0) issue_kblock<true>(blo[1], acol[1], b_hi, d_ac, d_ar, d_cc, d_cr, kInstrDesc);
+            else issue_kblock<false>(blo[1], acol[1], b_hi, d_ac, d_ar, d_cc, d_cr, kInstrDesc);
           }
-          tc_commit(bar_mma_done[s]);
+          tc_commit(bar_mma_done + 8 * s);
           if (kb == nkb - 1) tc_commit(bar_acc_ready);
         }
+        __syncwarp();
       }
     }
   } else {
@@ -306,11 +380,21 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
     // converted: two blocks into tile e+1, or at the very end for the last tile.
     const int lead = nkb >= 2 ? 2 : 1;
     int64_t epi_tile = 0;
+    uint32_t conv_phase = 0;
+    // rendezvous of the eight converter warps through an mbarrier, so that the wait is bounded
+    auto conv_sync = [&]() -> bool {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_conv);
+      const bool r = mbar_wait_warp(bar_conv, conv_phase & 1u, cta_abort);
+      ++conv_phase;
+      return r;
+    };
     for (int64_t it = 0; it < total_it && ok; ++it) {
       const int s = (int)(it & 1);
-      ok = mbar_wait_warp(bar_full[s], (uint32_t)((it >> 1) & 1), cta_abort);
+      const int rs = (int)(it % kRawStages);
+      ok = mbar_wait_warp(bar_full + 8 * rs, (uint32_t)((it / kRawStages) & 1), cta_abort);
       if (!ok) break;
-      const uint8_t* raw = base_ptr + SharedLayout::raw(s);
+      const uint8_t* raw = base_ptr + SharedLayout::raw(rs);
       float4 vl[4], vu[4], vw[2];
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
@@ -323,42 +407,47 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
 #pragma unroll
       for (int c = 0; c < 2; ++c) vw[c] = *reinterpret_cast<const float4*>(raw + 2 * kTileBytes + swz(wrow, wchunk + c));
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_raw_empty[s]);
+      if (lane == 0) mbar_arrive(bar_raw_empty + 8 * rs);
+      // all arithmetic happens before the wait for the operand buffers, so that the stretch between
+      // "MMAs of k-block it-2 done" and "operands of k-block it ready" is only stores
+      uint32_t chi[16], clo[16], rhi[16], rlo[16];
+      uint32_t whi[8], wlo[8], ahi[8], alo[8];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float l4[4] = {vl[c].x, vl[c].y, vl[c].z, vl[c].w};
+        const float u4[4] = {vu[c].x, vu[c].y, vu[c].z, vu[c].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          split_tf32(fmul(fadd(l4[e], u4[e]), 0.5f), chi[c * 4 + e], clo[c * 4 + e]);
+          split_tf32(fmul(fsub(u4[e], l4[e]), 0.5f), rhi[c * 4 + e], rlo[c * 4 + e]);
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const float w4[4] = {vw[c].x, vw[c].y, vw[c].z, vw[c].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          split_tf32(w4[e], whi[c * 4 + e], wlo[c * 4 + e]);
+          // |w| = sgn(w) * (hi + lo): flip the sign of both parts where w is negative
+          const uint32_t flip = __float_as_uint(w4[e]) & 0x80000000u;
+          ahi[c * 4 + e] = whi[c * 4 + e] ^ flip;
+          alo[c * 4 + e] = wlo[c * 4 + e] ^ flip;
+        }
+      }
       if (it >= 2) {
-        ok = mbar_wait_warp(bar_mma_done[s], (uint32_t)(((it >> 1) - 1) & 1), cta_abort);
+        ok = mbar_wait_warp(bar_mma_done + 8 * s, (uint32_t)(((it >> 1) - 1) & 1), cta_abort);
         if (!ok) break;
         tc_fence_after();
       }
       {
-        uint32_t chi[16], clo[16], rhi[16], rlo[16];
         uint8_t* pl = base_ptr + SharedLayout::planes(s);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const float l4[4] = {vl[c].x, vl[c].y, vl[c].z, vl[c].w};
-          const float u4[4] = {vu[c].x, vu[c].y, vu[c].z, vu[c].w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            split_tf32(fmul(fadd(l4[e], u4[e]), 0.5f), chi[c * 4 + e], clo[c * 4 + e]);
-            split_tf32(fmul(fsub(u4[e], l4[e]), 0.5f), rhi[c * 4 + e], rlo[c * 4 + e]);
-          }
-        }
-#pragma unroll
         for (int c = 0; c < 2; ++c) {
-          const float w4[4] = {vw[c].x, vw[c].y, vw[c].z, vw[c].w};
-          uint32_t whi[4], wlo[4], ahi[4], alo[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            split_tf32(w4[e], whi[e], wlo[e]);
-            // |w| = sgn(w) * (hi + lo): flip the sign of both parts where w is negative
-            const uint32_t flip = __float_as_uint(w4[e]) & 0x80000000u;
-            ahi[e] = whi[e] ^ flip;
-            alo[e] = wlo[e] ^ flip;
-          }
           const uint32_t off = swz(wrow, wchunk + c);
-          *reinterpret_cast<uint4*>(pl + 0 * kWTileBytes + off) = make_uint4(whi[0], whi[1], whi[2], whi[3]);
-          *reinterpret_cast<uint4*>(pl + 1 * kWTileBytes + off) = make_uint4(wlo[0], wlo[1], wlo[2], wlo[3]);
-          *reinterpret_cast<uint4*>(pl + 2 * kWTileBytes + off) = make_uint4(ahi[0], ahi[1], ahi[2], ahi[3]);
-          *reinterpret_cast<uint4*>(pl + 3 * kWTileBytes + off) = make_uint4(alo[0], alo[1], alo[2], alo[3]);
+          *reinterpret_cast<uint4*>(pl + 0 * kWTileBytes + off) = make_uint4(whi[c * 4], whi[c * 4 + 1], whi[c * 4 + 2], whi[c * 4 + 3]);
+          *reinterpret_cast<uint4*>(pl + 1 * kWTileBytes + off) = make_uint4(wlo[c * 4], wlo[c * 4 + 1], wlo[c * 4 + 2], wlo[c * 4 + 3]);
+          *reinterpret_cast<uint4*>(pl + 2 * kWTileBytes + off) = make_uint4(ahi[c * 4], ahi[c * 4 + 1], ahi[c * 4 + 2], ahi[c * 4 + 3]);
+          *reinterpret_cast<uint4*>(pl + 3 * kWTileBytes + off) = make_uint4(alo[c * 4], alo[c * 4 + 1], alo[c * 4 + 2], alo[c * 4 + 3]);
         }
         const uint32_t a_cols = tmem_base + lane_addr + kABase + (uint32_t)s * 128u + (uint32_t)half * 16u;
         tmem_st16(a_cols + 0, chi);
@@ -370,7 +459,7 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
       fence_async_smem();   // B planes were written through the generic proxy; the MMA reads them through the async proxy
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_ops_ready[s]);
+      if (lane == 0) mbar_arrive(bar_ops_ready + 8 * s);
 
       // ---- epilogue of tile epi_tile, once the conversion is `lead` blocks into the next tile
       const bool last_it = (it + 1 == total_it);
@@ -381,7 +470,6 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
           if (!ok) break;
           tc_fence_after();
           const int64_t etile = blockIdx.x + epi_tile * gridDim.x;
-          const int64_t m = (etile / n_tiles_n) * BM + row;
           const int ncol = half * 32;
           const int nb = (int)(etile % n_tiles_n) * BN + ncol;
           uint32_t t0[32], t1[32];
@@ -400,33 +488,51 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
           if (lane == 0) mbar_arrive(bar_acc_free);
 #pragma unroll
           for (int i = 0; i < 32; ++i) yr[i] = fadd(__uint_as_float(t0[i]), __uint_as_float(t1[i]));
-          if (m < M) {
-            const bool vec_out = (N % 4 == 0) && aligned16(c_lo) && aligned16(c_up);
+          // Output: both tiles are staged in shared memory in the 128-byte-swizzled box layout and
+          // written by TMA, so that global memory sees whole 128-byte lines.  Rows and columns
+          // beyond M and N are clipped by the tensor map.
+          if (ct == 0) tma_store_wait_read();      // the previous tile's stores have read the staging buffer
+          ok = conv_sync();
+          if (!ok) break;
+          {
+            uint8_t* so = base_ptr + SharedLayout::out() + (uint32_t)half * kOutBoxBytes;
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
-              const int n = nb + q * 4;
               float lo[4], up[4];
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
                 lo[e] = fsub(yc[q * 4 + e], yr[q * 4 + e]);
                 up[e] = fadd(yc[q * 4 + e], yr[q * 4 + e]);
-                if (bias != nullptr && n + e < N) { lo[e] = fadd(lo[e], bias[n + e]); up[e] = fadd(up[e], bias[n + e]); }
+                if (bias != nullptr) {
+                  const int n = nb + q * 4 + e;
+                  const float bv = n < N ? bias[n] : 0.f;
+                  lo[e] = fadd(lo[e], bv);
+                  up[e] = fadd(up[e], bv);
+                }
               }
-              if (vec_out && n + 3 < N) {
-                *reinterpret_cast<float4*>(c_lo + m * N + n) = make_float4(lo[0], lo[1], lo[2], lo[3]);
-                *reinterpret_cast<float4*>(c_up + m * N + n) = make_float4(up[0], up[1], up[2], up[3]);
-              } else {
-#pragma unroll
-                for (int e = 0; e < 4; ++e)
-                  if (n + e < N) { c_lo[m * N + n + e] = lo[e]; c_up[m * N + n + e] = up[e]; }
-              }
+              const uint32_t off = swz(row, q);
+              *reinterpret_cast<float4*>(so + off) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+              *reinterpret_cast<float4*>(so + 2 * kOutBoxBytes + off) = make_float4(up[0], up[1], up[2], up[3]);
             }
+          }
+          fence_async_smem();
+          ok = conv_sync();
+          if (!ok) break;
+          if (ct == 0) {
+            const int my = (int)(etile / n_tiles_n) * BM, nx = (int)(etile % n_tiles_n) * BN;
+            const uint32_t so = base + SharedLayout::out();
+            tma_store_2d(&tm_out_lo, nx, my, so);
+            tma_store_2d(&tm_out_lo, nx + 32, my, so + kOutBoxBytes);
+            tma_store_2d(&tm_out_up, nx, my, so + 2 * kOutBoxBytes);
+            tma_store_2d(&tm_out_up, nx + 32, my, so + 3 * kOutBoxBytes);
+            tma_store_commit();
           }
           ++epi_tile;
         }
       }
     }
   }
+  if (threadIdx.x == 64) tma_store_wait_all();   // this thread issued the bulk stores of the epilogues
   // Tear-down.  On the error path, give outstanding bulk copies time to land before the shared
   // memory is released (bounded), then free the tensor memory.
   if (*cta_abort) {
@@ -473,16 +579,18 @@ bool make_map(CUtensorMap* map, const float* ptr, uint64_t rows, uint64_t cols, 
 
 }  // namespace
 
-bool tc_gemm_supported(const float* a_lo, const float* a_up, const float* W, int64_t M, int N, int K) {
-  return M >= 256 && M < (1ll << 31) && N >= 32 && K >= 8 && K % 4 == 0 && aligned16(a_lo) && aligned16(a_up) &&
-         aligned16(W) && encode_fn() != nullptr;
+bool tc_gemm_supported(const float* a_lo, const float* a_up, const float* W, const float* c_lo, const float* c_up,
+                       int64_t M, int N, int K) {
+  return M >= 256 && M < (1ll << 31) && N >= 32 && N % 4 == 0 && K >= 8 && K % 4 == 0 && aligned16(a_lo) &&
+         aligned16(a_up) && aligned16(W) && aligned16(c_lo) && aligned16(c_up) && encode_fn() != nullptr;
 }
 
 int launch_split_sign_tc(const float* a_lo, const float* a_up, const float* W, const float* bias, float* c_lo,
                          float* c_up, int64_t M, int N, int K, cudaStream_t st) {
-  CUtensorMap tm_lo, tm_up, tm_w;
+  CUtensorMap tm_lo, tm_up, tm_w, tm_out_lo, tm_out_up;
   if (!make_map(&tm_lo, a_lo, (uint64_t)M, (uint64_t)K, BM) || !make_map(&tm_up, a_up, (uint64_t)M, (uint64_t)K, BM) ||
-      !make_map(&tm_w, W, (uint64_t)N, (uint64_t)K, BN))
+      !make_map(&tm_w, W, (uint64_t)N, (uint64_t)K, BN) || !make_map(&tm_out_lo, c_lo, (uint64_t)M, (uint64_t)N, BM) ||
+      !make_map(&tm_out_up, c_up, (uint64_t)M, (uint64_t)N, BM))
     return FB_ERR_CUDA;
   const int64_t gm = ceil_div(M, BM);
   const int gn = (int)ceil_div(N, BN);
@@ -498,12 +606,13 @@ int launch_split_sign_tc(const float* a_lo, const float* a_up, const float* W, c
   // persistent: one CTA per SM (tensor memory and shared memory allow exactly one)
   const int64_t sms = device_info().sms;
   const unsigned grid = (unsigned)(total_tiles < sms ? total_tiles : sms);
-  split_sign_gemm_tc<<<grid, kThreads, kSmemBytes, st>>>(tm_lo, tm_up, tm_w, bias, c_lo, c_up, M, N, K, gn, total_tiles);
+  split_sign_gemm_tc<<<grid, kThreads, kSmemBytes, st>>>(tm_lo, tm_up, tm_w, tm_out_lo, tm_out_up, bias, M, N, K, gn, total_tiles);
   FB_LAUNCH_OK();
   return FB_OK;
 }
 
 }  // namespace fb
+
 
 // Reads (and clears) the device-side flag that the tensor-core GEMM raises when one of its bounded
 // waits expires.  Synchronises the device.
