@@ -209,6 +209,8 @@ dot_weight_native(const float* __restrict__ x_lw, const float* __restrict__ x_uw
   }
 }
 
+#include "dot_product_pipelined.cuh"
+
 // --------------------------------------------- weight part, transposed layout
 // x [B, Lx, K, Di], y [B, Ly, K, Di] -> z [B, Lx, Ly, Di]   (Di contiguous).
 // One thread per symbolic coordinate m (coalesced along Di), 4 x 4 (i, j) outputs per thread;
@@ -337,9 +339,14 @@ extern "C" int fb_dot_product_f32(const float* x_lw, const float* x_uw, const fl
     const bool vec = K % 4 == 0 && aligned16(x_lw) && aligned16(x_uw) && aligned16(y_lw) && aligned16(y_uw) &&
                      aligned16(x_l) && aligned16(y_l) && aligned16(y_u);
     if (vec) {
-      FB_CUDA_OK(cudaFuncSetAttribute(dot_weight_native<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      dot_weight_native<true><<<(unsigned)blocks, kThreads, smem, st>>>(x_lw, x_uw, y_lw, y_uw, x_l, y_l, y_u, z_lw,
-                                                                        z_uw, Lx, Ly, Di, K, n_it, n_jt, n_mt, out_scale);
+      // persistent, cp.async-pipelined kernel: one block per SM walks the (tile, k-chunk) items
+      const int n_kc = (int)ceil_div(K, TK);
+      const int64_t n_items = blocks * n_kc;
+      const size_t psmem = sizeof(float) * kDotPipeSmemFloats;
+      FB_CUDA_OK(cudaFuncSetAttribute(dot_weight_native_pipelined, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)psmem));
+      const int64_t sms = device_info().sms;
+      dot_weight_native_pipelined<<<(unsigned)(blocks < sms ? blocks : sms), kThreads, psmem, st>>>(
+          x_lw, x_uw, y_lw, y_uw, x_l, y_l, y_u, z_lw, z_uw, Lx, Ly, Di, K, n_it, n_jt, n_mt, n_kc, n_items, out_scale);
     } else {
       FB_CUDA_OK(cudaFuncSetAttribute(dot_weight_native<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
       dot_weight_native<false><<<(unsigned)blocks, kThreads, smem, st>>>(x_lw, x_uw, y_lw, y_uw, x_l, y_l, y_u, z_lw,

@@ -193,17 +193,17 @@ def test_dot_product_shapes(B, Lx, Ly, Di, K, p):
     o = O.OBounds(p, 0.5, *tx).dot_product(O.OBounds(p, 0.5, *ty))
     g = faith_b200.BoundsLite(p, 0.5, *[v.to(DEV) for v in tx]).dot_product(
         faith_b200.BoundsLite(p, 0.5, *[v.to(DEV) for v in ty]))
+    # The K-term sums reach 1e2..1e4 (operand ranges of a few units times K terms) and cancel, so two
+    # fp32 evaluation orders (the reference's four separate GEMMs, the kernel's fused centre/radius
+    # accumulation) differ by more than the per-operator bar near zeros of the result.  The result is
+    # therefore judged against the fp64 run of the same algorithm: within 4x the fp32 noise of the
+    # reference itself, plus an elementwise bar scaled to the size of the summed terms.
+    d = torch.float64
+    o64 = O.OBounds(p, 0.5, *[v.to(d) for v in tx]).dot_product(O.OBounds(p, 0.5, *[v.to(d) for v in ty]))
+    for k in ("lw", "uw", "lb", "ub"):
+        helpers.assert_within_noise(getattr(g, k), getattr(o, k), getattr(o64, k), "dot %s" % k)
     if p == 2.0:
-        # sums of K products of O(1) terms: absolute part scaled like the matmul test
-        _cmp(g, o, "dot", rtol=1e-5, atol=1e-6 * max(1.0, K / 8))
-    else:
-        # With the sum-abs dual norm the operand ranges are ~Di/4, the K-term sums reach 1e3..1e4
-        # and cancel: the fp32 summation-order noise of the reference itself exceeds the per-op
-        # bar, so the result is judged against the fp64 run of the same algorithm.
-        d = torch.float64
-        o64 = O.OBounds(p, 0.5, *[v.to(d) for v in tx]).dot_product(O.OBounds(p, 0.5, *[v.to(d) for v in ty]))
-        for k in ("lw", "uw", "lb", "ub"):
-            helpers.assert_within_noise(getattr(g, k), getattr(o, k), getattr(o64, k), "dot %s" % k)
+        _cmp(g, o, "dot", rtol=1e-5, atol=2e-6 * max(1.0, K / 8))
 
 
 def test_context_matches_oracle():
