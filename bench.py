@@ -252,11 +252,22 @@ def main():
         roofline = {"kernel": dom["op"], "bound": "tensor", "achieved": dom["tflops"], "peak": pk["bf16_sustained"],
                     "unit": "TFLOP/s", "frac": dom["tflops"] / pk["bf16_sustained"], "traffic": None,
                     "peak_source": pk["source"] + " (dense bf16, sustained)",
-                    "pipe": "fp32 FFMA (CUDA cores)", "pipe_peak": ffma_tflops,
-                    "frac_of_pipe": dom["tflops"] / 2.0 / ffma_tflops,
-                    "note": "achieved counts the algorithmic 8*M*K*N flops; the kernel executes half of them "
-                            "(centre/radius form), hence frac_of_pipe = achieved / 2 / pipe_peak",
                     "avg_ms_per_call": dom["ms"] / dom["calls"], "share_of_step": dom["share"]}
+        if dom["op"] == "matmul" and os.environ.get("FB_MATMUL_IMPL", "") != "ffma":
+            # tcgen05 kind::tf32 runs at half the bf16 rate; the 3xTF32 centre/radius kernel executes
+            # 12*M*K*N tensor flops for the 8*M*K*N algorithmic ones
+            tf32_peak = pk["bf16_tflops"] / 2.0
+            roofline.update({"pipe": "tcgen05 kind::tf32 (3xTF32, centre/radius)", "pipe_peak": tf32_peak,
+                             "frac_of_pipe": dom["tflops"] * 1.5 / tf32_peak,
+                             "note": "achieved counts the algorithmic 8*M*K*N flops; pipe_peak = measured bf16 burst / 2; "
+                                     "frac_of_pipe = achieved * 1.5 / pipe_peak (three TF32 products per fp32 product, "
+                                     "two GEMMs instead of four)",
+                             "hbm_frac": dom["gbs"] / pk["hbm_gbs"]})
+        else:
+            roofline.update({"pipe": "fp32 FFMA (CUDA cores)", "pipe_peak": ffma_tflops,
+                             "frac_of_pipe": dom["tflops"] * (0.5 if dom["op"] != "dot_product" else 0.75) / ffma_tflops,
+                             "note": "achieved counts algorithmic flops; the centre/radius kernels execute 1/2 (matmul, "
+                                     "conv) or 3/4 (dot product) of them"})
     else:
         roofline = {"kernel": dom["op"], "bound": "hbm", "achieved": dom["gbs"], "peak": pk["hbm_gbs"], "unit": "GB/s",
                     "frac": dom["gbs"] / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
