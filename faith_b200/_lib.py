@@ -34,6 +34,8 @@ class Encoder(ctypes.Structure):
 SIGNATURES = {
     "fb_concretize_f32": [_P] * 6 + [_L, _I, _I, _I, _I, _F, _I, _P],
     "fb_relax_f32": [_I] + [_P] * 8 + [_L, _I, _I, _I, _I, _F, _I, _P, _P],
+    "fb_norm_partials_f32": [_P] * 4 + [_L, _I, _I, _I, _P],
+    "fb_relax_with_norms_f32": [_I] + [_P] * 10 + [_L, _I, _I, _I, _F, _P, _P],
     "fb_matmul_f32": [_P] * 10 + [_L, _I, _I, _I, _P],
     "fb_tc_error_flag": [ctypes.POINTER(_I)],
     "fb_dot_product_f32": [_P] * 16 + [_I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P],

@@ -26,7 +26,8 @@ __device__ __forceinline__ void tile_concretize(const float* __restrict__ gl, co
                                                 int Di, int Do, int c0, int words, int p, float eps,
                                                 float* s_l, float* s_u,      // staged tile [Di][kCW] each
                                                 float* s_red,                // [2][8][kCW]
-                                                float lbv, float ubv, float& l_out, float& u_out) {
+                                                float lbv, float ubv, float& l_out, float& u_out,
+                                                bool raw = false) {
   constexpr int CVL = kCW / VEC;
   constexpr int RG = kThreads / CVL;
   const int tid = threadIdx.x;
@@ -104,8 +105,13 @@ __device__ __forceinline__ void tile_concretize(const float* __restrict__ gl, co
         sl = norm_combine(p, sl, s_red[k * kCW + tid]);
         su = norm_combine(p, su, s_red[8 * kCW + k * kCW + tid]);
       }
-      l_run = fadd(l_run, fmul(-eps, norm_finish(p, sl)));
-      u_run = fadd(u_run, fmul(eps, norm_finish(p, su)));
+      if (raw) {  // unfinished accumulation (sum |w|, sum w^2 or max |w|) for a cross-device reduction
+        l_run = sl;
+        u_run = su;
+      } else {
+        l_run = fadd(l_run, fmul(-eps, norm_finish(p, sl)));
+        u_run = fadd(u_run, fmul(eps, norm_finish(p, su)));
+      }
     }
     __syncthreads();
   }
@@ -313,6 +319,63 @@ col_mul_bounds_native(const float* __restrict__ x_lw, const float* __restrict__ 
   }
 }
 
+// ------------------------------------------------- dim_in-sharded relaxation
+// When the dim_in axis is split over several GPUs, the dual norm of a column needs the rows of
+// every shard.  Pass 1 (this kernel) writes the unfinished accumulation of the local rows, the
+// caller reduces it across devices (sum for p = inf and p = 2, max for p = 1), pass 2 applies the
+// relaxation to the local rows from the reduced values.  One perturbed word.
+template <int VEC>
+__global__ void __launch_bounds__(kThreads)
+col_norm_partials_native(const float* __restrict__ lw, const float* __restrict__ uw, float* __restrict__ part_l,
+                         float* __restrict__ part_u, int Di, int Do, int ntiles, int p) {
+  extern __shared__ __align__(16) float smem[];
+  const int64_t row = blockIdx.x / ntiles;
+  const int c0 = (int)(blockIdx.x % ntiles) * kCW;
+  const int tid = threadIdx.x;
+  float l, u;
+  tile_concretize<VEC, false>(lw + (size_t)row * Di * Do, uw + (size_t)row * Di * Do, Di, Do, c0, 1, p, 0.f, nullptr,
+                              nullptr, smem, 0.f, 0.f, l, u, true);
+  if (tid < kCW && c0 + tid < Do) {
+    part_l[(size_t)row * Do + c0 + tid] = l;
+    part_u[(size_t)row * Do + c0 + tid] = u;
+  }
+}
+
+template <int VEC>
+__global__ void __launch_bounds__(kThreads)
+col_relax_apply_native(int op, const float* __restrict__ lw, const float* __restrict__ uw,
+                       const float* __restrict__ lb, const float* __restrict__ ub,
+                       const float* __restrict__ norm_l, const float* __restrict__ norm_u,
+                       float* __restrict__ o_lw, float* __restrict__ o_uw, float* __restrict__ o_lb,
+                       float* __restrict__ o_ub, int Di, int Do, int ntiles, int p, float eps,
+                       int* __restrict__ violation) {
+  __shared__ float s_coef[4 * kCW];
+  const int64_t row = blockIdx.x / ntiles;
+  const int c0 = (int)(blockIdx.x % ntiles) * kCW;
+  const int tid = threadIdx.x;
+  if (tid < kCW) {
+    ColCoef c = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (c0 + tid < Do) {
+      const size_t o = (size_t)row * Do + c0 + tid;
+      const float lbv = lb[o], ubv = ub[o];
+      const float l = fadd(lbv, fmul(-eps, norm_finish(p, norm_l[o])));
+      const float u = fadd(ubv, fmul(eps, norm_finish(p, norm_u[o])));
+      bool bad = false;
+      c = relax_column(op, l, u, lbv, ubv, bad);
+      if (bad && violation != nullptr) *violation = 1;
+      o_lb[o] = c.nlb;
+      o_ub[o] = c.nub;
+    }
+    s_coef[0 * kCW + tid] = c.c_ll;
+    s_coef[1 * kCW + tid] = c.c_lu;
+    s_coef[2 * kCW + tid] = c.c_ul;
+    s_coef[3 * kCW + tid] = c.c_uu;
+  }
+  __syncthreads();
+  const size_t wb = (size_t)row * Di * Do;
+  tile_rescale<VEC, false>(lw + wb, uw + wb, o_lw + wb, o_uw + wb, Di, Do, c0, nullptr, nullptr, s_coef);
+}
+
 // ------------------------------------------------------------ transposed layout
 // [rows, Do, Di]: the Di values of a column are contiguous; one warp per column, two passes
 // (the second is served by L1/L2, a column is at most a few KB).
@@ -510,6 +573,46 @@ extern "C" int fb_mul_bounds_f32(const float* x_lw, const float* x_uw, const flo
   else if (staged) FB_MUL_LAUNCH(1, true);
   else FB_MUL_LAUNCH(1, false);
 #undef FB_MUL_LAUNCH
+  FB_LAUNCH_OK();
+  return FB_OK;
+}
+
+extern "C" int fb_norm_partials_f32(const float* lw, const float* uw, float* part_l, float* part_u, int64_t rows,
+                                    int Di_local, int Do, int p, void* stream) {
+  if (rows == 0 || Do == 0) return FB_OK;
+  if (!lw || !uw || !part_l || !part_u) return FB_ERR_ARG;
+  if (rows < 0 || Di_local <= 0 || Do < 0 || !valid_norm(p)) return FB_ERR_ARG;
+  const int ntiles = (int)ceil_div(Do, kCW);
+  const int64_t blocks = rows * ntiles;
+  if (blocks > 0x7fffffff) return FB_ERR_SHAPE;
+  const double mw = (double)rows * Di_local * Do;
+  ProfileScope prof(PK_RELAX, 4.0 * mw, 4.0 * (2 * mw + 2.0 * rows * Do), stream);
+  const size_t smem = sizeof(float) * 2 * 8 * kCW;
+  const bool vec = Do % 4 == 0 && aligned16(lw) && aligned16(uw);
+  if (vec) col_norm_partials_native<4><<<(unsigned)blocks, kThreads, smem, (cudaStream_t)stream>>>(lw, uw, part_l, part_u, Di_local, Do, ntiles, p);
+  else col_norm_partials_native<1><<<(unsigned)blocks, kThreads, smem, (cudaStream_t)stream>>>(lw, uw, part_l, part_u, Di_local, Do, ntiles, p);
+  FB_LAUNCH_OK();
+  return FB_OK;
+}
+
+extern "C" int fb_relax_with_norms_f32(int op, const float* lw, const float* uw, const float* lb, const float* ub,
+                                       const float* norm_l, const float* norm_u, float* out_lw, float* out_uw,
+                                       float* out_lb, float* out_ub, int64_t rows, int Di_local, int Do, int p,
+                                       float eps, int* violation, void* stream) {
+  if (op < FB_RELU || op > FB_RECIPROCAL) return FB_ERR_ARG;
+  if (rows == 0 || Do == 0) return FB_OK;
+  if (!lw || !uw || !lb || !ub || !norm_l || !norm_u || !out_lw || !out_uw || !out_lb || !out_ub) return FB_ERR_ARG;
+  if (rows < 0 || Di_local <= 0 || Do < 0 || !valid_norm(p)) return FB_ERR_ARG;
+  if (out_lw == lw || out_lw == uw || out_uw == lw || out_uw == uw) return FB_ERR_ARG;
+  const int ntiles = (int)ceil_div(Do, kCW);
+  const int64_t blocks = rows * ntiles;
+  if (blocks > 0x7fffffff) return FB_ERR_SHAPE;
+  const double mw = (double)rows * Di_local * Do;
+  ProfileScope prof(PK_RELAX, 2.0 * mw, 4.0 * (4 * mw + 6.0 * rows * Do), stream);
+  const bool vec = Do % 4 == 0 && aligned16(lw) && aligned16(uw) && aligned16(out_lw) && aligned16(out_uw);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (vec) col_relax_apply_native<4><<<(unsigned)blocks, kThreads, 0, st>>>(op, lw, uw, lb, ub, norm_l, norm_u, out_lw, out_uw, out_lb, out_ub, Di_local, Do, ntiles, p, eps, violation);
+  else col_relax_apply_native<1><<<(unsigned)blocks, kThreads, 0, st>>>(op, lw, uw, lb, ub, norm_l, norm_u, out_lw, out_uw, out_lb, out_ub, Di_local, Do, ntiles, p, eps, violation);
   FB_LAUNCH_OK();
   return FB_OK;
 }

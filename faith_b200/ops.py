@@ -230,3 +230,28 @@ def conv2d(x, weight, bias, stride, padding):
         check(load().fb_conv2d_f32(*[_p(t) for t in x], _p(weight), _p(bias), *[_p(t) for t in out],
                                    B, Di, C, H, W, Co, Kh, Kw, stride, padding, _stream()), "fb_conv2d_f32")
     return out
+
+
+def norm_partials(lw, uw, p):
+    """Unfinished dual-norm accumulation of the local dim_in rows: (part_l, part_u), each [.., Do]."""
+    dev = _chk(lw, uw)
+    Di, Do = lw.shape[-2], lw.shape[-1]
+    rows = lw.numel() // (Di * Do)
+    shape = lw.shape[:-2] + (Do,)
+    part_l, part_u = torch.empty(shape, device=dev), torch.empty(shape, device=dev)
+    with torch.cuda.device(dev):
+        check(load().fb_norm_partials_f32(_p(lw), _p(uw), _p(part_l), _p(part_u), rows, Di, Do, norm_code(p),
+                                          _stream()), "fb_norm_partials_f32")
+    return part_l, part_u
+
+
+def relax_with_norms(op, lw, uw, lb, ub, norm_l, norm_u, p, eps, violation=None):
+    dev = _chk(lw, uw, lb, ub, norm_l, norm_u)
+    Di, Do = lw.shape[-2], lw.shape[-1]
+    rows = lw.numel() // (Di * Do)
+    out = (torch.empty_like(lw), torch.empty_like(uw), torch.empty_like(lb), torch.empty_like(ub))
+    with torch.cuda.device(dev):
+        check(load().fb_relax_with_norms_f32(op, _p(lw), _p(uw), _p(lb), _p(ub), _p(norm_l), _p(norm_u),
+                                             *[_p(t) for t in out], rows, Di, Do, norm_code(p), eps,
+                                             _p(violation), _stream()), "fb_relax_with_norms_f32")
+    return out

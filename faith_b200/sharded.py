@@ -1,0 +1,92 @@
+"""Bound propagation with the dim_in axis sharded over the ranks of a process group.
+
+Every rank holds a contiguous slice of the dim_in rows of lw/uw; lb/ub and all per-column scalars
+are replicated and computed redundantly.  Linear operators (conv, matmul) need no communication:
+dim_in rows are independent GEMM / conv rows.  Each nonlinearity needs the dual norm of a column
+over the *whole* dim_in axis: the local unfinished accumulation is all-reduced (SUM for p = inf and
+p = 2, MAX for p = 1) before the relaxation is applied to the local rows.  The sum order of the
+norm changes with the number of ranks, so results agree with the single-rank run within the
+per-operator tolerance, not bit for bit.
+"""
+import torch
+
+from . import ops
+from ._lib import FB_RELU
+
+
+def shard_bounds(lw, uw, rank, world, dim=-2):
+    """Contiguous dim_in slice of rank `rank` (the remainder goes to the last ranks one row each)."""
+    n = lw.shape[dim]
+    base, rem = divmod(n, world)
+    start = rank * base + max(0, rank - (world - rem))
+    size = base + (1 if rank >= world - rem else 0)
+    return lw.narrow(dim, start, size).contiguous(), uw.narrow(dim, start, size).contiguous()
+
+
+def reduce_partials(part_l, part_u, p, group=None):
+    """All-reduce of the unfinished norms over the dim_in shards (one message for both sides)."""
+    import torch.distributed as dist
+    if group is None and not (dist.is_available() and dist.is_initialized()):
+        return part_l, part_u
+    if dist.get_world_size(group) == 1:
+        return part_l, part_u
+    buf = torch.stack((part_l, part_u))
+    dist.all_reduce(buf, op=dist.ReduceOp.MAX if p == 1 else dist.ReduceOp.SUM, group=group)
+    return buf[0], buf[1]
+
+
+def relax_sharded(op, lw, uw, lb, ub, p, eps, group=None):
+    """Fused concretise + relax + rescale of the local dim_in rows: partial norms, all-reduce, apply."""
+    part_l, part_u = ops.norm_partials(lw, uw, p)
+    norm_l, norm_u = reduce_partials(part_l, part_u, p, group)
+    return ops.relax_with_norms(op, lw, uw, lb, ub, norm_l.contiguous(), norm_u.contiguous(), p, eps)
+
+
+class CnnVerifier:
+    """Forward bound pass of conv -> relu -> conv -> relu -> linear on one image with every pixel
+    perturbed (dim_in = C*H*W), the dim_in axis sharded over the ranks of `group`.
+
+    layers: list of ("conv", weight [Co,Ci,k,k], bias, stride, pad) / ("relu",) / ("linear", W, b).
+    Returns the concretised output bounds (l, u), identical on every rank.
+    """
+
+    def __init__(self, layers, device, group=None):
+        self.device = torch.device(device)
+        self.group = group
+        self.layers = []
+        for ly in layers:
+            if ly[0] in ("conv", "linear"):
+                self.layers.append((ly[0],) + tuple(t.to(self.device, torch.float32).contiguous()
+                                                    if isinstance(t, torch.Tensor) else t for t in ly[1:]))
+            else:
+                self.layers.append(ly)
+
+    def forward(self, image, p, eps, rank=0, world=1):
+        C, H, W = image.shape
+        di = C * H * W
+        base, rem = divmod(di, world)
+        start = rank * base + max(0, rank - (world - rem))
+        size = base + (1 if rank >= world - rem else 0)
+        # identity dependence on every pixel: the local rows of eye(di)
+        lw = torch.zeros(size, di, device=self.device)
+        lw[torch.arange(size, device=self.device), start + torch.arange(size, device=self.device)] = 1.0
+        lw = lw.view(1, size, C, H, W)
+        uw = lw.clone()
+        lb = image.to(self.device, torch.float32).view(1, C, H, W).contiguous()
+        ub = lb.clone()
+        for ly in self.layers:
+            if ly[0] == "conv":
+                lw, uw, lb, ub = ops.conv2d((lw, uw, lb, ub), ly[1], ly[2], ly[3], ly[4])
+            elif ly[0] == "relu":
+                shp_w, shp_b = lw.shape, lb.shape
+                o = relax_sharded(FB_RELU, lw.reshape(1, size, -1), uw.reshape(1, size, -1), lb.reshape(1, -1),
+                                  ub.reshape(1, -1), p, eps, self.group)
+                lw, uw, lb, ub = o[0].view(shp_w), o[1].view(shp_w), o[2].view(shp_b), o[3].view(shp_b)
+            elif ly[0] == "linear":
+                lw, uw, lb, ub = ops.matmul(lw.reshape(1, 1, size, -1), uw.reshape(1, 1, size, -1),
+                                            lb.reshape(1, 1, -1), ub.reshape(1, 1, -1), ly[1], ly[2])
+        part_l, part_u = ops.norm_partials(lw.reshape(1, size, -1), uw.reshape(1, size, -1), p)
+        norm_l, norm_u = reduce_partials(part_l, part_u, p, self.group)
+        if p == 2:
+            norm_l, norm_u = norm_l.sqrt(), norm_u.sqrt()
+        return lb.reshape(-1) - eps * norm_l.reshape(-1), ub.reshape(-1) + eps * norm_u.reshape(-1)

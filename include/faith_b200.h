@@ -73,6 +73,22 @@ int fb_relax_f32(int op,
                  int64_t rows, int Di, int Do, int words, int p, float eps, int layout,
                  int* violation, void* stream);
 
+/* The same relaxation when the dim_in axis is sharded over several GPUs (each device holds
+ * Di_local rows of lw/uw of every column; lb/ub are replicated).  The reference is single-GPU;
+ * the split follows from Bounds.concretize (Bounds.py:311-326): the dual norm of a column is a
+ * sum (p = inf: sum |w|, p = 2: sum w^2 before the root) or a maximum (p = 1) over dim_in.
+ *   1. fb_norm_partials_f32 writes the unfinished accumulation of the local rows, [rows, Do] each;
+ *   2. the caller reduces part_l / part_u over the devices (all-reduce SUM, or MAX for FB_P1);
+ *   3. fb_relax_with_norms_f32 finishes the norm, concretises, relaxes and rescales the local rows.
+ * One perturbed word (words = 1).  Native layout. */
+int fb_norm_partials_f32(const float* lw, const float* uw, float* part_l, float* part_u,
+                         int64_t rows, int Di_local, int Do, int p, void* stream);
+int fb_relax_with_norms_f32(int op, const float* lw, const float* uw, const float* lb, const float* ub,
+                            const float* norm_l, const float* norm_u,
+                            float* out_lw, float* out_uw, float* out_lb, float* out_ub,
+                            int64_t rows, int Di_local, int Do, int p, float eps,
+                            int* violation, void* stream);
+
 /* Product with a constant weight W [Dy, Do] (nn.Linear layout) and optional bias [Dy]
  * (NULL = none): y_lw = x_lw W+ + x_uw W-, y_uw = x_lw W- + x_uw W+, same for lb/ub, then
  * + bias.  Replaces Bounds.ori_matmul / dense (Bounds.py:397-413, 1016-1025) and the

@@ -545,3 +545,49 @@ def model_to(model, dtype):
             return {k: cv(e) for k, e in v.items()}
         return v
     return cv(model)
+
+
+# ------------------------------------------------------------------ small CNN
+def cnn_forward(layers, image, p, eps):
+    """Forward bound pass of a CNN on one image with every pixel perturbed (dim_in = C*H*W):
+    layers is a list of ("conv", weight, bias, stride, pad) / ("relu",) / ("linear", W, b).
+    Conv bounds follow `conv_bounds`; relu and linear are the pinned `Bounds` operators on the
+    flattened [1, 1, Di, C*H*W] view.  Returns the concretised (l, u) of the outputs."""
+    C, H, W = image.shape
+    di = C * H * W
+    lw = torch.eye(di, dtype=image.dtype).view(1, di, C, H, W)
+    x = OBounds(p, eps, lw, image.view(1, C, H, W).clone(), lw.clone(), image.view(1, C, H, W).clone())
+    for ly in layers:
+        if ly[0] == "conv":
+            x = conv_bounds(x, ly[1], ly[2], ly[3], ly[4])
+        elif ly[0] == "relu":
+            if x.lw.dim() == 5:
+                c, h, w = x.lw.shape[2:]
+                x = tokens_as_conv(conv_as_tokens(x).relu(), c, h, w)
+            else:
+                x = x.relu()
+        elif ly[0] == "linear":
+            if x.lw.dim() == 5:
+                x = conv_as_tokens(x)
+            x = x.dense(ly[1], ly[2])
+    if x.lw.dim() == 5:
+        x = conv_as_tokens(x)
+    l, u = x.concretize()
+    return l.reshape(-1), u.reshape(-1)
+
+
+def make_cnn(seed, c_in=3, hw=32, dtype=torch.float32):
+    """conv 3->16 (3x3, s1, p1), relu, conv 16->32 (3x3, s2, p1), relu, linear -> 10; Kaiming-normal
+    weights, zero biases."""
+    g = torch.Generator().manual_seed(seed)
+
+    def kaiming(*shape):
+        fan_in = 1
+        for d in shape[1:]:
+            fan_in *= d
+        return (torch.randn(*shape, generator=g) * math.sqrt(2.0 / fan_in)).to(dtype)
+
+    ho = (hw + 2 - 3) // 2 + 1
+    return [("conv", kaiming(16, c_in, 3, 3), torch.zeros(16, dtype=dtype), 1, 1), ("relu",),
+            ("conv", kaiming(32, 16, 3, 3), torch.zeros(32, dtype=dtype), 2, 1), ("relu",),
+            ("linear", kaiming(10, 32 * ho * ho), torch.zeros(10, dtype=dtype))]
