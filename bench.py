@@ -122,6 +122,63 @@ def run_reference(args):
     }))
 
 
+def run_cnn(args):
+    """Secondary workload: conv 3->16, relu, conv 16->32 (stride 2), relu, linear 8192->10 on one 3x32x32
+    image with every pixel perturbed (dim_in = 3072, Linf eps = 2/255).  The dim_in axis is sharded over the
+    ranks; each relu all-reduces the partial norms over NCCL.  A step is one bound pass of the image."""
+    import torch.distributed as dist
+    import faith_b200
+    from faith_b200.sharded import CnnVerifier
+    from oracle import bounds_oracle as O
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = faith_b200.load()
+    layers = O.make_cnn(5)
+    img = torch.rand(3, 32, 32, generator=torch.Generator().manual_seed(5))
+    ver = CnnVerifier(layers, dev)
+    eps = 2.0 / 255
+
+    def step():
+        return ver.forward(img, float("inf"), eps, rank, world)
+
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
+        step()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    n0 = lib.fb_launch_count()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.steps):
+        l, u = step()
+    b.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = torch.tensor([a.elapsed_time(b)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        ms_step = float(ms.item()) / args.steps
+        print(json.dumps({"metric": "images/sec for CNN bound pass (dim_in sharded)", "value": 1e3 / ms_step,
+                          "unit": "images/s", "n_gpus": world, "steps": args.steps, "warmup": warmup,
+                          "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                          "dtype": "f32", "data": "synthetic",
+                          "config": {"workload": "CNN 3x32x32, conv3-16 s1, relu, conv16-32 s2, relu, linear 8192-10; "
+                                                 "dim_in 3072 sharded over ranks, Linf eps 2/255",
+                                     "collective": "NCCL all-reduce of [2, 16384] and [2, 8192] fp32 partial norms"},
+                          "gpu_launches": int(lib.fb_launch_count() - n0),
+                          "bounds": {"l0": float(l[0]), "u0": float(u[0])}}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -130,9 +187,14 @@ def main():
     ap.add_argument("--impl", default="faith_b200", choices=["faith_b200", "reference"])
     ap.add_argument("--sentences", type=int, default=CFG["sentences"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="encoder", choices=["encoder", "cnn"],
+                    help="encoder = the headline metric; cnn = secondary line for the dim_in-sharded CNN pass")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+        return
+    if args.workload == "cnn":
+        run_cnn(args)
         return
 
     import torch.distributed as dist
