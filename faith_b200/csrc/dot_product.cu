@@ -28,7 +28,7 @@ __global__ void __launch_bounds__(kThreads)
 dot_bias_kernel(const float* __restrict__ x_lb, const float* __restrict__ x_ub, const float* __restrict__ y_lb,
                 const float* __restrict__ y_ub, const float* __restrict__ x_l, const float* __restrict__ y_l,
                 const float* __restrict__ y_u, float* __restrict__ z_lb, float* __restrict__ z_ub,
-                int64_t total, int Lx, int Ly, int K, float out_scale) {
+                int64_t total, int Lx, int Ly, int K, float out_scale, int heads) {
   const int lane = threadIdx.x & 31;
   const int64_t warps = (int64_t)gridDim.x * (kThreads / 32);
   for (int64_t o = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5); o < total; o += warps) {
@@ -66,8 +66,10 @@ dot_bias_kernel(const float* __restrict__ x_lb, const float* __restrict__ x_ub, 
       l4 += __shfl_xor_sync(0xffffffffu, l4, s); u4 += __shfl_xor_sync(0xffffffffu, u4, s);
     }
     if (lane == 0) {
-      z_lb[o] = fmul(fadd(fadd(fadd(fadd(gl, l1), l2), l3), l4), out_scale);
-      z_ub[o] = fmul(fadd(fadd(fadd(fadd(gu, u1), u2), u3), u4), out_scale);
+      // heads > 1: head-merged output [S, Lx, heads * Ly]
+      const int64_t i_ = bi % Lx, od = (((b / heads) * Lx + i_) * heads + b % heads) * Ly + j;
+      z_lb[od] = fmul(fadd(fadd(fadd(fadd(gl, l1), l2), l3), l4), out_scale);
+      z_ub[od] = fmul(fadd(fadd(fadd(fadd(gu, u1), u2), u3), u4), out_scale);
     }
   }
 }
@@ -298,12 +300,13 @@ dot_weight_transposed(const float* __restrict__ x_lw, const float* __restrict__ 
 
 using namespace fb;
 
-extern "C" int fb_dot_product_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+extern "C" int fb_dot_product_heads_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
                                   const float* y_lw, const float* y_uw, const float* y_lb, const float* y_ub,
                                   float* z_lw, float* z_uw, float* z_lb, float* z_ub,
                                   float* x_l, float* x_u, float* y_l, float* y_u,
                                   int B, int Lx, int Ly, int Di, int K, int words, int p, float eps,
-                                  float out_scale, int layout, void* stream) {
+                                  float out_scale, int layout, int merge_heads, void* stream) {
+  if (merge_heads < 1 || (merge_heads > 1 && (layout != FB_NATIVE || B % merge_heads != 0 || K % 4 != 0))) return FB_ERR_ARG;
   if (!x_lw || !x_uw || !x_lb || !x_ub || !y_lw || !y_uw || !y_lb || !y_ub || !z_lw || !z_uw || !z_lb || !z_ub ||
       !x_l || !x_u || !y_l || !y_u)
     return FB_ERR_ARG;
@@ -328,7 +331,7 @@ extern "C" int fb_dot_product_f32(const float* x_lw, const float* x_uw, const fl
     const int64_t want = ceil_div(total, kThreads / 32);
     const int64_t cap = (int64_t)device_info().sms * 32;
     dot_bias_kernel<<<(unsigned)(want < cap ? want : cap), kThreads, 0, st>>>(x_lb, x_ub, y_lb, y_ub, x_l, y_l, y_u,
-                                                                               z_lb, z_ub, total, Lx, Ly, K, out_scale);
+                                                                               z_lb, z_ub, total, Lx, Ly, K, out_scale, merge_heads);
     FB_LAUNCH_OK();
   }
   if (layout == FB_NATIVE) {
@@ -338,6 +341,7 @@ extern "C" int fb_dot_product_f32(const float* x_lw, const float* x_uw, const fl
     const size_t smem = sizeof(float) * kDotSmemFloats;
     const bool vec = K % 4 == 0 && aligned16(x_lw) && aligned16(x_uw) && aligned16(y_lw) && aligned16(y_uw) &&
                      aligned16(x_l) && aligned16(y_l) && aligned16(y_u);
+    if (!vec && merge_heads > 1) return FB_ERR_ALIGN;
     if (vec) {
       // persistent, cp.async-pipelined kernel: one block per SM walks the (tile, k-chunk) items
       const int n_kc = (int)ceil_div(K, TK);
@@ -346,7 +350,7 @@ extern "C" int fb_dot_product_f32(const float* x_lw, const float* x_uw, const fl
       FB_CUDA_OK(cudaFuncSetAttribute(dot_weight_native_pipelined, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)psmem));
       const int64_t sms = device_info().sms;
       dot_weight_native_pipelined<<<(unsigned)(blocks < sms ? blocks : sms), kThreads, psmem, st>>>(
-          x_lw, x_uw, y_lw, y_uw, x_l, y_l, y_u, z_lw, z_uw, Lx, Ly, Di, K, n_it, n_jt, n_mt, n_kc, n_items, out_scale);
+          x_lw, x_uw, y_lw, y_uw, x_l, y_l, y_u, z_lw, z_uw, Lx, Ly, Di, K, n_it, n_jt, n_mt, n_kc, n_items, out_scale, merge_heads);
     } else {
       FB_CUDA_OK(cudaFuncSetAttribute(dot_weight_native<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
       dot_weight_native<false><<<(unsigned)blocks, kThreads, smem, st>>>(x_lw, x_uw, y_lw, y_uw, x_l, y_l, y_u, z_lw,
@@ -362,6 +366,16 @@ extern "C" int fb_dot_product_f32(const float* x_lw, const float* x_uw, const fl
   }
   FB_LAUNCH_OK();
   return FB_OK;
+}
+
+extern "C" int fb_dot_product_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+                                  const float* y_lw, const float* y_uw, const float* y_lb, const float* y_ub,
+                                  float* z_lw, float* z_uw, float* z_lb, float* z_ub,
+                                  float* x_l, float* x_u, float* y_l, float* y_u,
+                                  int B, int Lx, int Ly, int Di, int K, int words, int p, float eps,
+                                  float out_scale, int layout, void* stream) {
+  return fb_dot_product_heads_f32(x_lw, x_uw, x_lb, x_ub, y_lw, y_uw, y_lb, y_ub, z_lw, z_uw, z_lb, z_ub, x_l, x_u, y_l,
+                                  y_u, B, Lx, Ly, Di, K, words, p, eps, out_scale, layout, 1, stream);
 }
 
 // ---------------------------------------------------------------------------

@@ -65,7 +65,7 @@ dot_weight_native_pipelined(const float* __restrict__ x_lw, const float* __restr
                             const float* __restrict__ x_l, const float* __restrict__ y_l,
                             const float* __restrict__ y_u, float* __restrict__ z_lw, float* __restrict__ z_uw,
                             int Lx, int Ly, int Di, int K, int n_it, int n_jt, int n_mt, int n_kc, int64_t n_items,
-                            float out_scale) {
+                            float out_scale, int heads) {
   extern __shared__ __align__(16) float smem[];
   const int tid = threadIdx.x;
   const int tj = tid & 7, ti = (tid >> 3) & 7, tm = tid >> 6;
@@ -161,7 +161,9 @@ dot_weight_native_pipelined(const float* __restrict__ x_lw, const float* __restr
         for (int a = 0; a < 4; ++a) {
           const int i = t.i0 + ti + 8 * a;
           if (i >= Lx) continue;
-          const int64_t row = ((t.b * Lx + i) * (int64_t)Di + m) * Ly;
+          // heads > 1: b = s * heads + h and the output is written head-merged, [S, Lx, Di, heads * Ly]
+          const int64_t sb = t.b / heads, hb = t.b % heads;
+          const int64_t row = (((sb * Lx + i) * (int64_t)Di + m) * heads + hb) * Ly;
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             const int j = t.j0 + tj + 8 * c;

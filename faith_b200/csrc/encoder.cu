@@ -172,12 +172,10 @@ extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, i
     const fb_encoder_layer& ly = enc->layer[li];
     const BoundSet &X = slot[A], &T1 = slot[B], &T2 = slot[C], &T3 = slot[Dd];
     // queries and keys, split into heads: [S*H, L, Di, d]
-    FB_TRY(dense(X, ly.q_w, ly.q_b, T1, rows, Di, D, D, stream));
-    FB_TRY(fb_split_heads_f32(T1.lw, T1.lb, T2.lw, T2.lb, S, L, Di, H, d, 0, stream));
-    FB_TRY(fb_split_heads_f32(T1.uw, T1.ub, T2.uw, T2.ub, S, L, Di, H, d, 0, stream));
-    FB_TRY(dense(X, ly.k_w, ly.k_b, T1, rows, Di, D, D, stream));
-    FB_TRY(fb_split_heads_f32(T1.lw, T1.lb, T3.lw, T3.lb, S, L, Di, H, d, 0, stream));
-    FB_TRY(fb_split_heads_f32(T1.uw, T1.ub, T3.uw, T3.ub, S, L, Di, H, d, 0, stream));
+    FB_TRY(fb_matmul_heads_f32(X.lw, X.uw, X.lb, X.ub, ly.q_w, ly.q_b, T2.lw, T2.uw, T2.lb, T2.ub, rows, Di, D, D, L, H,
+                               stream));
+    FB_TRY(fb_matmul_heads_f32(X.lw, X.uw, X.lb, X.ub, ly.k_w, ly.k_b, T3.lw, T3.uw, T3.lb, T3.ub, rows, Di, D, D, L, H,
+                               stream));
     // scores [S*H, L, Di, L], scaled by 1/sqrt(d) -> T1
     FB_TRY(fb_dot_product_f32(T2.lw, T2.uw, T2.lb, T2.ub, T3.lw, T3.uw, T3.lb, T3.ub, T1.lw, T1.uw, T1.lb, T1.ub,
                               range[0], range[1], range[2], range[3], S * H, L, L, Di, d, words, p, eps, inv_sqrt_d,
@@ -193,15 +191,21 @@ extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, i
     FB_TRY(dense(X, ly.v_w, ly.v_b, T2, rows, Di, D, D, stream));
     FB_TRY(fb_split_heads_f32(T2.lw, T2.lb, T3.lw, T3.lb, S, L, Di, H, d, 1, stream));
     FB_TRY(fb_split_heads_f32(T2.uw, T2.ub, T3.uw, T3.ub, S, L, Di, H, d, 1, stream));
-    // context [S*H, L, Di, d] -> T2, merged [S, L, Di, D] -> T1
-    FB_TRY(fb_dot_product_f32(T1.lw, T1.uw, T1.lb, T1.ub, T3.lw, T3.uw, T3.lb, T3.ub, T2.lw, T2.uw, T2.lb, T2.ub,
-                              range[0], range[1], range[2], range[3], S * H, L, d, Di, L, words, p, eps, 1.0f,
-                              FB_NATIVE, stream));
-    FB_TRY(fb_merge_heads_f32(T2.lw, T2.lb, T1.lw, T1.lb, S, L, Di, H, d, stream));
-    FB_TRY(fb_merge_heads_f32(T2.uw, T2.ub, T1.uw, T1.ub, S, L, Di, H, d, stream));
+    // context, written head-merged as [S, L, Di, D] -> T2
+    FB_TRY(fb_dot_product_heads_f32(T1.lw, T1.uw, T1.lb, T1.ub, T3.lw, T3.uw, T3.lb, T3.ub, T2.lw, T2.uw, T2.lb, T2.ub,
+                                    range[0], range[1], range[2], range[3], S * H, L, d, Di, L, words, p, eps, 1.0f,
+                                    FB_NATIVE, (L % 4 == 0) ? H : 1, stream));
+    if (L % 4 != 0) {  // unvectorised path: merge with the permute kernel
+      FB_TRY(fb_merge_heads_f32(T2.lw, T2.lb, T1.lw, T1.lb, S, L, Di, H, d, stream));
+      FB_TRY(fb_merge_heads_f32(T2.uw, T2.ub, T1.uw, T1.ub, S, L, Di, H, d, stream));
+      FB_CUDA_OK(cudaMemcpyAsync(T2.lw, T1.lw, (size_t)rows * Di * D * 4, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+      FB_CUDA_OK(cudaMemcpyAsync(T2.uw, T1.uw, (size_t)rows * Di * D * 4, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+      FB_CUDA_OK(cudaMemcpyAsync(T2.lb, T1.lb, (size_t)rows * D * 4, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+      FB_CUDA_OK(cudaMemcpyAsync(T2.ub, T1.ub, (size_t)rows * D * 4, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+    }
     // attention output: dense, + residual, layer norm -> T3
-    FB_TRY(dense(T1, ly.ao_w, ly.ao_b, T2, rows, Di, D, D, stream));
-    FB_TRY(norm_residual(enc, T2, &X, ly.ln1_g, ly.ln1_b, T3, rows, Di, D, stream));
+    FB_TRY(dense(T2, ly.ao_w, ly.ao_b, T1, rows, Di, D, D, stream));
+    FB_TRY(norm_residual(enc, T1, &X, ly.ln1_g, ly.ln1_b, T3, rows, Di, D, stream));
     // feed-forward: dense, relu, dense, + residual, layer norm -> T1
     FB_TRY(dense(T3, ly.f1_w, ly.f1_b, T1, rows, Di, D, F, stream));
     FB_TRY(relax(FB_RELU, T1, T2, rows, Di, F, words, p, eps, nullptr, stream));

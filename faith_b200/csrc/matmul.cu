@@ -7,10 +7,11 @@
 namespace fb {
 bool tc_gemm_supported(const float* a_lo, const float* a_up, const float* W, const float* c_lo, const float* c_up,
                        int64_t M, int N, int K);
+bool tc_split_supported(int64_t M, int N, int split_rows, int split_d);
 int launch_split_sign_tc(const float* a_lo, const float* a_up, const float* W, const float* bias, float* c_lo,
-                         float* c_up, int64_t M, int N, int K, cudaStream_t st);
+                         float* c_up, int64_t M, int N, int K, cudaStream_t st, int split_rows, int split_d);
 int launch_split_sign_ffma(const float* a_lo, const float* a_up, const float* W, const float* bias, float* c_lo,
-                           float* c_up, int64_t M, int N, int K, cudaStream_t st);
+                           float* c_up, int64_t M, int N, int K, cudaStream_t st, int split_rows, int split_d);
 
 // FB_MATMUL_IMPL=ffma forces the CUDA-core kernel (exact fp32 products); default: tensor cores
 // (3xTF32) for the large weight GEMM when the shape allows it.
@@ -22,25 +23,43 @@ static bool use_tensor_cores() {
   return v;
 }
 
+// split_rows > 0: head-split store of the result, [group * H + head][row in group][feature in head]
+// with groups of split_rows consecutive rows and heads of split_d consecutive columns.
 static int split_sign_gemm(const float* a_lo, const float* a_up, const float* W, const float* bias, float* c_lo,
-                           float* c_up, int64_t M, int N, int K, cudaStream_t st) {
-  if (use_tensor_cores() && tc_gemm_supported(a_lo, a_up, W, c_lo, c_up, M, N, K))
-    return launch_split_sign_tc(a_lo, a_up, W, bias, c_lo, c_up, M, N, K, st);
-  return launch_split_sign_ffma(a_lo, a_up, W, bias, c_lo, c_up, M, N, K, st);
+                           float* c_up, int64_t M, int N, int K, cudaStream_t st, int split_rows = 0, int split_d = 0) {
+  if (use_tensor_cores() && tc_gemm_supported(a_lo, a_up, W, c_lo, c_up, M, N, K) &&
+      (split_rows == 0 || tc_split_supported(M, N, split_rows, split_d)))
+    return launch_split_sign_tc(a_lo, a_up, W, bias, c_lo, c_up, M, N, K, st, split_rows, split_d);
+  return launch_split_sign_ffma(a_lo, a_up, W, bias, c_lo, c_up, M, N, K, st, split_rows, split_d);
 }
 }  // namespace fb
+
+static int matmul_impl(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub, const float* W,
+                       const float* bias, float* y_lw, float* y_uw, float* y_lb, float* y_ub, int64_t rows, int Di,
+                       int Do, int Dy, int L, int heads, void* stream) {
+  if (!x_lw || !x_uw || !x_lb || !x_ub || !W || !y_lw || !y_uw || !y_lb || !y_ub) return FB_ERR_ARG;
+  if (rows < 0 || Di <= 0 || Do <= 0 || Dy <= 0) return FB_ERR_ARG;
+  if (heads > 1 && (L <= 0 || rows % L != 0 || Dy % heads != 0)) return FB_ERR_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  const double M = (double)rows * (Di + 1);
+  fb::ProfileScope prof(fb::PK_MATMUL, 8.0 * M * Do * Dy, 4.0 * (2 * M * Do + 2 * M * Dy + (double)Do * Dy + Dy), stream);
+  const int d = heads > 1 ? Dy / heads : 0;
+  // weight rows: [rows * Di, Do] -> [rows * Di, Dy]; no bias on the symbolic part
+  int rc = fb::split_sign_gemm(x_lw, x_uw, W, nullptr, y_lw, y_uw, rows * (int64_t)Di, Dy, Do, st,
+                               heads > 1 ? L * Di : 0, d);
+  if (rc != FB_OK) return rc;
+  // bias rows: [rows, Do] -> [rows, Dy], + bias
+  return fb::split_sign_gemm(x_lb, x_ub, W, bias, y_lb, y_ub, rows, Dy, Do, st, heads > 1 ? L : 0, d);
+}
 
 extern "C" int fb_matmul_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
                              const float* W, const float* bias, float* y_lw, float* y_uw, float* y_lb, float* y_ub,
                              int64_t rows, int Di, int Do, int Dy, void* stream) {
-  if (!x_lw || !x_uw || !x_lb || !x_ub || !W || !y_lw || !y_uw || !y_lb || !y_ub) return FB_ERR_ARG;
-  if (rows < 0 || Di <= 0 || Do <= 0 || Dy <= 0) return FB_ERR_ARG;
-  cudaStream_t st = (cudaStream_t)stream;
-  const double M = (double)rows * (Di + 1);
-  fb::ProfileScope prof(fb::PK_MATMUL, 8.0 * M * Do * Dy, 4.0 * (2 * M * Do + 2 * M * Dy + (double)Do * Dy + Dy), stream);
-  // weight rows: [rows * Di, Do] -> [rows * Di, Dy]; no bias on the symbolic part
-  int rc = fb::split_sign_gemm(x_lw, x_uw, W, nullptr, y_lw, y_uw, rows * (int64_t)Di, Dy, Do, st);
-  if (rc != FB_OK) return rc;
-  // bias rows: [rows, Do] -> [rows, Dy], + bias
-  return fb::split_sign_gemm(x_lb, x_ub, W, bias, y_lb, y_ub, rows, Dy, Do, st);
+  return matmul_impl(x_lw, x_uw, x_lb, x_ub, W, bias, y_lw, y_uw, y_lb, y_ub, rows, Di, Do, Dy, 0, 1, stream);
+}
+
+extern "C" int fb_matmul_heads_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+                                   const float* W, const float* bias, float* y_lw, float* y_uw, float* y_lb,
+                                   float* y_ub, int64_t rows, int Di, int Do, int Dy, int L, int heads, void* stream) {
+  return matmul_impl(x_lw, x_uw, x_lb, x_ub, W, bias, y_lw, y_uw, y_lb, y_ub, rows, Di, Do, Dy, L, heads, stream);
 }

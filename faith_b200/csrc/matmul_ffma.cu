@@ -26,7 +26,8 @@ template <bool VEC>
 __global__ void __launch_bounds__(kThreads)
 split_sign_gemm_ffma(const float* __restrict__ a_lo, const float* __restrict__ a_up,
                      const float* __restrict__ W, const float* __restrict__ bias,
-                     float* __restrict__ c_lo, float* __restrict__ c_up, int64_t M, int N, int K) {
+                     float* __restrict__ c_lo, float* __restrict__ c_up, int64_t M, int N, int K, int split_rows,
+                     int split_d) {
   extern __shared__ __align__(16) float smem[];
   const int tid = threadIdx.x;
   const int tx = tid & 15, ty = tid >> 4;
@@ -127,7 +128,9 @@ split_sign_gemm_ffma(const float* __restrict__ a_lo, const float* __restrict__ a
   }
 
   // epilogue: y_lo = centre - radius, y_up = centre + radius (+ bias)
-  const bool vec_out = (N % 4 == 0) && aligned16(c_lo) && aligned16(c_up);
+  // split_rows > 0: head-split store, element (m, n) goes to [(g * H + h), r, f] with g = m / split_rows,
+  // r = m % split_rows, h = n / split_d, f = n % split_d (H = N / split_d)
+  const bool vec_out = split_rows == 0 && (N % 4 == 0) && aligned16(c_lo) && aligned16(c_up);
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int64_t m = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
@@ -149,7 +152,16 @@ split_sign_gemm_ffma(const float* __restrict__ a_lo, const float* __restrict__ a
       } else {
 #pragma unroll
         for (int e = 0; e < 4; ++e)
-          if (n + e < N) { c_lo[m * N + n + e] = lo[e]; c_up[m * N + n + e] = up[e]; }
+          if (n + e < N) {
+            int64_t o = m * N + n + e;
+            if (split_rows > 0) {
+              const int64_t g = m / split_rows, r = m % split_rows;
+              const int hh = (n + e) / split_d, f = (n + e) % split_d;
+              o = ((g * (N / split_d) + hh) * split_rows + r) * split_d + f;
+            }
+            c_lo[o] = lo[e];
+            c_up[o] = up[e];
+          }
       }
     }
   }
@@ -206,9 +218,9 @@ split_sign_gemv_rows(const float* __restrict__ a_lo, const float* __restrict__ a
 
 // One split-sign GEMM: (a_lo, a_up) [M, K] x W[N, K]^T (+ bias) -> (c_lo, c_up) [M, N].
 int launch_split_sign_ffma(const float* a_lo, const float* a_up, const float* W, const float* bias, float* c_lo,
-                           float* c_up, int64_t M, int N, int K, cudaStream_t st) {
+                           float* c_up, int64_t M, int N, int K, cudaStream_t st, int split_rows, int split_d) {
   if (M == 0 || N == 0) return FB_OK;
-  if (N <= 16) {
+  if (N <= 16 && split_rows == 0) {
     const int64_t want = ceil_div(M, kThreads / 32);
     const int64_t cap = (int64_t)device_info().sms * 16;
     const unsigned blocks = (unsigned)(want < cap ? want : cap);
@@ -223,10 +235,10 @@ int launch_split_sign_ffma(const float* a_lo, const float* a_up, const float* W,
   const bool vec = K % 4 == 0 && aligned16(a_lo) && aligned16(a_up) && aligned16(W);
   if (vec) {
     FB_CUDA_OK(cudaFuncSetAttribute(split_sign_gemm_ffma<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    split_sign_gemm_ffma<true><<<dim3((unsigned)gm, gn), kThreads, smem, st>>>(a_lo, a_up, W, bias, c_lo, c_up, M, N, K);
+    split_sign_gemm_ffma<true><<<dim3((unsigned)gm, gn), kThreads, smem, st>>>(a_lo, a_up, W, bias, c_lo, c_up, M, N, K, split_rows, split_d);
   } else {
     FB_CUDA_OK(cudaFuncSetAttribute(split_sign_gemm_ffma<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    split_sign_gemm_ffma<false><<<dim3((unsigned)gm, gn), kThreads, smem, st>>>(a_lo, a_up, W, bias, c_lo, c_up, M, N, K);
+    split_sign_gemm_ffma<false><<<dim3((unsigned)gm, gn), kThreads, smem, st>>>(a_lo, a_up, W, bias, c_lo, c_up, M, N, K, split_rows, split_d);
   }
   FB_LAUNCH_OK();
   return FB_OK;

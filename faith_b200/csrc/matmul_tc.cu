@@ -118,9 +118,9 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
-               ::"l"(map), "r"(x), "r"(y), "r"(src) : "memory");
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, int x, int y, int z, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
+               ::"l"(map), "r"(x), "r"(y), "r"(z), "r"(src) : "memory");
 }
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // waits until the bulk stores committed so far have finished READING shared memory
@@ -254,7 +254,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_constant__ CUtensorMap tm_up,
                    const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_out_lo,
                    const __grid_constant__ CUtensorMap tm_out_up, const float* __restrict__ bias, int64_t M, int N, int K,
-                   int n_tiles_n, int64_t total_tiles) {
+                   int n_tiles_n, int64_t total_tiles, int split_rows, int split_d) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -519,12 +519,23 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
           ok = conv_sync();
           if (!ok) break;
           if (ct == 0) {
+            // The output tensor map is 3-D.  Plain store: (column, row, 0).  Head-split store
+            // (split_rows > 0): the output is [group * heads + head][row in group][feature in head], a
+            // 32-column box lies inside one head and its 128 rows inside one group.
             const int my = (int)(etile / n_tiles_n) * BM, nx = (int)(etile % n_tiles_n) * BN;
             const uint32_t so = base + SharedLayout::out();
-            tma_store_2d(&tm_out_lo, nx, my, so);
-            tma_store_2d(&tm_out_lo, nx + 32, my, so + kOutBoxBytes);
-            tma_store_2d(&tm_out_up, nx, my, so + 2 * kOutBoxBytes);
-            tma_store_2d(&tm_out_up, nx + 32, my, so + 3 * kOutBoxBytes);
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+              int cx = nx + 32 * q, cy = my, cz = 0;
+              if (split_rows > 0) {
+                const int heads = N / split_d;
+                cz = (my / split_rows) * heads + cx / split_d;
+                cy = my % split_rows;
+                cx = cx % split_d;
+              }
+              tma_store_3d(&tm_out_lo, cx, cy, cz, so + q * kOutBoxBytes);
+              tma_store_3d(&tm_out_up, cx, cy, cz, so + (2 + q) * kOutBoxBytes);
+            }
             tma_store_commit();
           }
           ++epi_tile;
@@ -577,7 +588,33 @@ bool make_map(CUtensorMap* map, const float* ptr, uint64_t rows, uint64_t cols, 
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Output map, always 3-D: plain [1][rows][cols], or head-split [groups * heads][split_rows][split_d].
+bool make_out_map(CUtensorMap* map, const float* ptr, uint64_t M, uint64_t N, int split_rows, int split_d) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {N, M, 1};
+  cuuint64_t strides[2] = {N * sizeof(float), M * N * sizeof(float)};
+  if (split_rows > 0) {
+    dims[0] = (cuuint64_t)split_d;
+    dims[1] = (cuuint64_t)split_rows;
+    dims[2] = (M / split_rows) * (N / split_d);
+    strides[0] = (cuuint64_t)split_d * sizeof(float);
+    strides[1] = (cuuint64_t)split_rows * split_d * sizeof(float);
+  }
+  const cuuint32_t box[3] = {32, BM, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(ptr), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace
+
+// Head-split store is possible when a 128-row tile stays inside one group and a 32-column box inside one head.
+bool tc_split_supported(int64_t M, int N, int split_rows, int split_d) {
+  return split_rows > 0 && split_d > 0 && split_rows % BM == 0 && M % split_rows == 0 && split_d % 32 == 0 &&
+         N % split_d == 0;
+}
 
 bool tc_gemm_supported(const float* a_lo, const float* a_up, const float* W, const float* c_lo, const float* c_up,
                        int64_t M, int N, int K) {
@@ -586,11 +623,12 @@ bool tc_gemm_supported(const float* a_lo, const float* a_up, const float* W, con
 }
 
 int launch_split_sign_tc(const float* a_lo, const float* a_up, const float* W, const float* bias, float* c_lo,
-                         float* c_up, int64_t M, int N, int K, cudaStream_t st) {
+                         float* c_up, int64_t M, int N, int K, cudaStream_t st, int split_rows, int split_d) {
   CUtensorMap tm_lo, tm_up, tm_w, tm_out_lo, tm_out_up;
   if (!make_map(&tm_lo, a_lo, (uint64_t)M, (uint64_t)K, BM) || !make_map(&tm_up, a_up, (uint64_t)M, (uint64_t)K, BM) ||
-      !make_map(&tm_w, W, (uint64_t)N, (uint64_t)K, BN) || !make_map(&tm_out_lo, c_lo, (uint64_t)M, (uint64_t)N, BM) ||
-      !make_map(&tm_out_up, c_up, (uint64_t)M, (uint64_t)N, BM))
+      !make_map(&tm_w, W, (uint64_t)N, (uint64_t)K, BN) ||
+      !make_out_map(&tm_out_lo, c_lo, (uint64_t)M, (uint64_t)N, split_rows, split_d) ||
+      !make_out_map(&tm_out_up, c_up, (uint64_t)M, (uint64_t)N, split_rows, split_d))
     return FB_ERR_CUDA;
   const int64_t gm = ceil_div(M, BM);
   const int gn = (int)ceil_div(N, BN);
@@ -606,7 +644,7 @@ int launch_split_sign_tc(const float* a_lo, const float* a_up, const float* W, c
   // persistent: one CTA per SM (tensor memory and shared memory allow exactly one)
   const int64_t sms = device_info().sms;
   const unsigned grid = (unsigned)(total_tiles < sms ? total_tiles : sms);
-  split_sign_gemm_tc<<<grid, kThreads, kSmemBytes, st>>>(tm_lo, tm_up, tm_w, tm_out_lo, tm_out_up, bias, M, N, K, gn, total_tiles);
+  split_sign_gemm_tc<<<grid, kThreads, kSmemBytes, st>>>(tm_lo, tm_up, tm_w, tm_out_lo, tm_out_up, bias, M, N, K, gn, total_tiles, split_rows, split_d);
   FB_LAUNCH_OK();
   return FB_OK;
 }

@@ -99,6 +99,14 @@ int fb_matmul_f32(const float* x_lw, const float* x_uw, const float* x_lb, const
                   float* y_lw, float* y_uw, float* y_lb, float* y_ub,
                   int64_t rows, int Di, int Do, int Dy, void* stream);
 
+/* fb_matmul_f32 with the head split of the attention projections folded into the store
+ * (VerifierForward.py:208-229): rows = S * L; with heads = H > 1 and d = Dy / H the outputs are written as
+ * y_lw, y_uw [S * H, L, Di, d] and y_lb, y_ub [S * H, L, d]. */
+int fb_matmul_heads_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+                        const float* W, const float* bias,
+                        float* y_lw, float* y_uw, float* y_lb, float* y_ub,
+                        int64_t rows, int Di, int Do, int Dy, int L, int heads, void* stream);
+
 /* The tensor-core GEMM behind fb_matmul_f32 bounds every wait inside the kernel; if a wait ever
  * expires, the kernel raises a device-side flag, frees its tensor memory and returns.  This call
  * synchronises the device, returns the flag in *flag (0 = never raised) and clears it. */
@@ -120,6 +128,16 @@ int fb_dot_product_f32(const float* x_lw, const float* x_uw, const float* x_lb, 
                        float* x_l, float* x_u, float* y_l, float* y_u,
                        int B, int Lx, int Ly, int Di, int K, int words, int p, float eps,
                        float out_scale, int layout, void* stream);
+
+/* fb_dot_product_f32 with the head merge of the attention context folded into the store
+ * (VerifierForward.py:253-265): with merge_heads = H > 1 (native layout, B = S * H), z is written as
+ * [S, Lx, Di, H * Ly] / [S, Lx, H * Ly] instead of [B, Lx, Di, Ly] / [B, Lx, Ly]. */
+int fb_dot_product_heads_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+                             const float* y_lw, const float* y_uw, const float* y_lb, const float* y_ub,
+                             float* z_lw, float* z_uw, float* z_lb, float* z_ub,
+                             float* x_l, float* x_u, float* y_l, float* y_u,
+                             int B, int Lx, int Ly, int Di, int K, int words, int p, float eps,
+                             float out_scale, int layout, int merge_heads, void* stream);
 
 /* The same operator for callers that cannot allocate device memory.  (No counterpart in the
  * reference, whose callers always allocate the scratch tensors themselves.)

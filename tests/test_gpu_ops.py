@@ -343,3 +343,45 @@ def test_conv_bounds(cfg):
     helpers.assert_close(r[1], o.uw, "conv uw", **tol)
     helpers.assert_close(r[2], o.lb, "conv lb", **tol)
     helpers.assert_close(r[3], o.ub, "conv ub", **tol)
+
+
+def test_dot_product_with_merged_head_store():
+    """fb_dot_product_heads_f32 writes the context head-merged; same values as dot product + merge."""
+    from faith_b200 import _lib, ops
+    lib = _lib.load()
+    S, H, L, Di, d = 2, 4, 8, 16, 12
+    tp = [v.to(DEV) for v in cases.rand_bounds(601, S * H, L, Di, L, 0.0, 0.2)]
+    tv = [v.to(DEV) for v in cases.rand_bounds(602, S * H, d, Di, L, -0.5, 1.0)]
+    x = (tp[0], tp[2], tp[1], tp[3])
+    y = (tv[0], tv[2], tv[1], tv[3])
+    ref = ops.merge_heads(ops.dot_product(x, y, 2.0, 0.1), H)
+    z = [torch.full((S, L, Di, H * d), float("nan"), device=DEV), torch.full((S, L, Di, H * d), float("nan"), device=DEV),
+         torch.full((S, L, H * d), float("nan"), device=DEV), torch.full((S, L, H * d), float("nan"), device=DEV)]
+    scr = [torch.empty(S * H, L, L, device=DEV), torch.empty(S * H, L, L, device=DEV),
+           torch.empty(S * H, d, L, device=DEV), torch.empty(S * H, d, L, device=DEV)]
+    ptrs = [t.data_ptr() for t in x + y] + [t.data_ptr() for t in z] + [t.data_ptr() for t in scr]
+    _lib.check(lib.fb_dot_product_heads_f32(*ptrs, S * H, L, d, Di, L, 1, _lib.FB_P2, 0.1, 1.0, _lib.FB_NATIVE, H,
+                                            torch.cuda.current_stream().cuda_stream), "fb_dot_product_heads_f32")
+    for a, b in zip(z, ref):
+        assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("S,L,Di,H,d", [(2, 8, 32, 2, 32), (3, 4, 64, 4, 64), (2, 5, 12, 4, 8)])
+def test_matmul_with_head_split_store(S, L, Di, H, d):
+    """fb_matmul_heads_f32 (tensor-core TMA store or CUDA-core path) equals dense followed by the split."""
+    from faith_b200 import _lib, ops
+    lib = _lib.load()
+    D = H * d
+    t = [v.to(DEV) for v in cases.rand_bounds(603, S, L, Di, D)]
+    g = torch.Generator().manual_seed(9)
+    W = (torch.randn(D, D, generator=g) / math.sqrt(D)).to(DEV)
+    bias = (torch.randn(D, generator=g) * 0.1).to(DEV)
+    y = ops.matmul(t[0], t[2], t[1], t[3], W, bias)
+    ref = ops.split_heads(y, H)
+    z = [torch.full((S * H, L, Di, d), float("nan"), device=DEV), torch.full((S * H, L, Di, d), float("nan"), device=DEV),
+         torch.full((S * H, L, d), float("nan"), device=DEV), torch.full((S * H, L, d), float("nan"), device=DEV)]
+    _lib.check(lib.fb_matmul_heads_f32(t[0].data_ptr(), t[2].data_ptr(), t[1].data_ptr(), t[3].data_ptr(), W.data_ptr(),
+                                       bias.data_ptr(), *[v.data_ptr() for v in z], S * L, Di, D, D, L, H,
+                                       torch.cuda.current_stream().cuda_stream), "fb_matmul_heads_f32")
+    for a, b in zip(z, ref):
+        assert torch.equal(a, b)
