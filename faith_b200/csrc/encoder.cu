@@ -9,6 +9,8 @@
 // first token -> dense -> tanh -> classifier folded to logit0 - logit1 -> concretise.
 #include <math.h>
 
+#include <utility>
+
 #include "common.cuh"
 
 namespace fb {
@@ -170,7 +172,8 @@ extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, i
   const float inv_sqrt_d = (float)(1.0 / sqrt((double)d));
   for (int li = 0; li < enc->layers; ++li) {
     const fb_encoder_layer& ly = enc->layer[li];
-    const BoundSet &X = slot[A], &T1 = slot[B], &T2 = slot[C], &T3 = slot[Dd];
+    const BoundSet X = slot[A], T3 = slot[Dd];
+    BoundSet T1 = slot[B], T2 = slot[C];
     // queries and keys, split into heads: [S*H, L, Di, d]
     FB_TRY(fb_matmul_heads_f32(X.lw, X.uw, X.lb, X.ub, ly.q_w, ly.q_b, T2.lw, T2.uw, T2.lb, T2.ub, rows, Di, D, D, L, H,
                                stream));
@@ -181,12 +184,22 @@ extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, i
                               range[0], range[1], range[2], range[3], S * H, L, L, Di, d, words, p, eps, inv_sqrt_d,
                               FB_NATIVE, stream));
     const int64_t hrows = (int64_t)S * H * L;
-    // softmax = exp / row sum
-    FB_TRY(relax(FB_EXP, T1, T2, hrows, Di, L, words, p, eps, nullptr, stream));                     // E  -> T2
-    FB_TRY(fb_rowsum_f32(T2.lw, T2.uw, T2.lb, T2.ub, T1.lw, T1.uw, T1.lb, T1.ub, hrows, Di, L, stream));  // sum -> T1
-    FB_TRY(relax(FB_RECIPROCAL, T1, T3, hrows, Di, L, words, p, eps, violation, stream));             // 1/sum -> T3
-    FB_TRY(fb_mul_bounds_f32(T2.lw, T2.uw, T2.lb, T2.ub, T3.lw, T3.uw, T3.lb, T3.ub, T1.lw, T1.uw, T1.lb, T1.ub, hrows,
-                             Di, L, words, p, eps, stream));                                          // probs -> T1
+    // softmax: fused kernel when the score row fits one tile, else exp / row sum / reciprocal / product
+    int src = fb_softmax_f32(T1.lw, T1.uw, T1.lb, T1.ub, T2.lw, T2.uw, T2.lb, T2.ub, hrows, Di, L, words, p, eps,
+                             violation, stream);
+    if (src == FB_OK) {
+      // probabilities are in T2; the stages below expect them in T1
+      std::swap(T1, T2);
+      std::swap(B, C);
+    } else if (src == FB_ERR_SHAPE || src == FB_ERR_ALIGN) {
+      FB_TRY(relax(FB_EXP, T1, T2, hrows, Di, L, words, p, eps, nullptr, stream));                     // E  -> T2
+      FB_TRY(fb_rowsum_f32(T2.lw, T2.uw, T2.lb, T2.ub, T1.lw, T1.uw, T1.lb, T1.ub, hrows, Di, L, stream));  // sum -> T1
+      FB_TRY(relax(FB_RECIPROCAL, T1, T3, hrows, Di, L, words, p, eps, violation, stream));             // 1/sum -> T3
+      FB_TRY(fb_mul_bounds_f32(T2.lw, T2.uw, T2.lb, T2.ub, T3.lw, T3.uw, T3.lb, T3.ub, T1.lw, T1.uw, T1.lb, T1.ub,
+                               hrows, Di, L, words, p, eps, stream));                                   // probs -> T1
+    } else {
+      return src;
+    }
     // values, split into heads with position/feature swapped: [S*H, d, Di, L]
     FB_TRY(dense(X, ly.v_w, ly.v_b, T2, rows, Di, D, D, stream));
     FB_TRY(fb_split_heads_f32(T2.lw, T2.lb, T3.lw, T3.lb, S, L, Di, H, d, 1, stream));

@@ -255,3 +255,19 @@ def relax_with_norms(op, lw, uw, lb, ub, norm_l, norm_u, p, eps, violation=None)
                                              *[_p(t) for t in out], rows, Di, Do, norm_code(p), eps,
                                              _p(violation), _stream()), "fb_relax_with_norms_f32")
     return out
+
+
+def softmax_fused(x, p, eps, words=1, violation=None):
+    """Fused softmax bound; returns None when the shape needs the unfused chain."""
+    dev = _chk(*x)
+    lw, uw, lb, ub = x
+    Di, Do = lw.shape[-2], lw.shape[-1]
+    rows = lb.numel() // Do
+    out = (torch.empty_like(lw), torch.empty_like(uw), torch.empty_like(lb), torch.empty_like(ub))
+    with torch.cuda.device(dev):
+        rc = load().fb_softmax_f32(*[_p(t) for t in x], *[_p(t) for t in out], rows, Di, Do, words, norm_code(p), eps,
+                                   _p(violation), _stream())
+    if rc in (2, 3):   # FB_ERR_SHAPE / FB_ERR_ALIGN: not a fused shape
+        return None
+    check(rc, "fb_softmax_f32")
+    return out

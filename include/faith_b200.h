@@ -194,6 +194,15 @@ int fb_rowsum_f32(const float* x_lw, const float* x_uw, const float* x_lb, const
                   float* z_lw, float* z_uw, float* z_lb, float* z_ub,
                   int64_t rows, int Di, int Do, void* stream);
 
+/* Fused softmax bound: exp, feature-axis sum, reciprocal and McCormick product in one kernel
+ * (Bounds.softmax, Bounds.py:1005-1014).  Needs the feature axis in one tile: Do <= 32, Do % 4 == 0
+ * and the two [Di, 32] tiles in shared memory; other shapes return FB_ERR_SHAPE (callers then run the
+ * chain fb_relax_f32(FB_EXP) / fb_rowsum_f32 / fb_relax_f32(FB_RECIPROCAL) / fb_mul_bounds_f32).
+ * `violation` as in fb_relax_f32(FB_RECIPROCAL). */
+int fb_softmax_f32(const float* lw, const float* uw, const float* lb, const float* ub,
+                   float* out_lw, float* out_uw, float* out_lb, float* out_ub,
+                   int64_t rows, int Di, int Do, int words, int p, float eps, int* violation, void* stream);
+
 /* Layer normalisation without the variance ("no_var", Bounds.py:1111-1131), optionally fused
  * with a preceding residual add: t = x (+ r); t -= mean over features of the opposite side;
  * out = t * gamma (split by sign of gamma) + beta on lb/ub.  r_* may all be NULL. */

@@ -385,3 +385,23 @@ def test_matmul_with_head_split_store(S, L, Di, H, d):
                                        torch.cuda.current_stream().cuda_stream), "fb_matmul_heads_f32")
     for a, b in zip(z, ref):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("shape", [(4, 32, 128, 32), (2, 3, 64, 8), (1, 5, 40, 20)])
+@pytest.mark.parametrize("p,words", [(2.0, 1), (float("inf"), 1), (1.0, 2)])
+def test_fused_softmax_matches_oracle_and_chain(shape, p, words):
+    """The fused softmax kernel against the oracle and against the four-kernel chain it replaces."""
+    import faith_b200
+    from faith_b200 import ops
+    B, L, Di, Do = shape
+    t = cases.rand_bounds(604, B, L, Di, Do, -0.5, 0.2)
+    o = O.OBounds(p, 0.1, *t, words=words).softmax()
+    g = faith_b200.BoundsLite(p, 0.1, *[v.to(DEV) for v in t], perturbed_words=words)
+    fused = ops.softmax_fused(g._t4(), p, 0.1, words)
+    assert fused is not None
+    e = g.exp()
+    s = ops.rowsum(e._t4())
+    chain = e.divide(g._new(s[0], s[1], s[2], s[3]))
+    for k, i in (("lw", 0), ("uw", 1), ("lb", 2), ("ub", 3)):
+        helpers.assert_close(fused[i], getattr(o, k), "fused softmax %s vs oracle" % k)
+        helpers.assert_close(fused[i], getattr(chain, k), "fused softmax %s vs chain" % k)
