@@ -48,8 +48,12 @@ namespace fb {
 namespace {
 
 constexpr int BM = 128, BN = 64, BK = 32;
-constexpr int kConvWarps = 8;
-constexpr int kThreads = 32 * (2 + kConvWarps);
+constexpr int kGroupWarps = 8;                           // converter warps per group: 4 row quarters x 2 k halves of a k-block
+constexpr int kConvGroups = 2;                           // group g converts the k-blocks it = g (mod 2)
+constexpr int kConvWarps = kConvGroups * kGroupWarps;
+constexpr int kIssuers = 3;                              // MMA-issuing warps, each owning accumulators of its own
+constexpr int kCtrlWarps = 1 + kIssuers;                 // TMA producer + issuers
+constexpr int kThreads = 32 * (kCtrlWarps + kConvWarps);
 constexpr uint32_t kTileBytes = BM * BK * 4;             // one 128 x 32 fp32 tile of x = 16 KB
 constexpr uint32_t kWTileBytes = BN * BK * 4;            // one 64 x 32 fp32 tile of W = 8 KB
 constexpr uint32_t kRawStageBytes = 2 * kTileBytes + kWTileBytes;  // x_lw, x_uw, W
@@ -64,6 +68,12 @@ constexpr uint32_t kTryNs = 20000;       // suspend-time hint of one mbarrier tr
 constexpr uint32_t kMaxTries = 100000;  // x 20 us = 2 s upper bound for any single wait
 
 static __device__ int g_tc_error = 0;
+#ifdef FBX_TRACE
+static __device__ long long g_trace[64 * 16];
+#define FBX_T(it, slot) do { if (blockIdx.x == 0 && lane == 0 && (it) >= 32 && (it) < 96) g_trace[((it) - 32) * 16 + (slot)] = clock64(); } while (0)
+#else
+#define FBX_T(it, slot) do { } while (0)
+#endif
 
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -94,7 +104,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uin
 // Bounded wait: at most kMaxTries suspended tries of ~kTryNs each (a couple of seconds in total).
 // Returns false (and raises the error flags) when the limit is hit or another role of this CTA has
 // already given up.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* cta_abort) {
+  // fast path: in a well-fed pipeline the phase is usually complete already, and the non-blocking
+  // test answers much sooner than a suspending try
+#ifndef FBX_NO_TEST
+  for (int i = 0; i < 4; ++i)
+    if (mbar_test_wait(bar, parity)) return true;
+#endif
   for (uint32_t i = 0; i < kMaxTries; ++i) {
     if (mbar_try_wait(bar, parity, kTryNs)) return true;
     if (*cta_abort) return false;
@@ -168,30 +195,41 @@ __device__ __forceinline__ void mma_tf32_ts_lean(uint32_t d_tmem, uint32_t a_tme
   }
 }
 
-// The 24 MMAs of one k-block (4 k steps x 6).  kFirst: this k-block starts a tile, so the first
-// MMA into each accumulator overwrites instead of accumulating.
-template <bool kFirst>
+// The MMAs of one k-block (4 k steps x 6), split over three issuing warps by accumulator, so that
+// no accumulator is shared between issuers and no ordering between them is needed:
+//   role 0: the two main accumulators,   acc_c += c_hi W_hi,  acc_r += r_hi |W|_hi
+//   role 1: centre correction,           cor_c += c_lo W_hi + c_hi W_lo
+//   role 2: radius correction,           cor_r += r_lo |W|_hi + r_hi |W|_lo
+// One issuing thread sustains one MMA per ~50-90 cycles whatever the MMA's size; a 128 x 64 x 8 MMA
+// keeps the tensor core busy for 32, so a single issuer leaves it idle most of the time.
+// kFirst: this k-block starts a tile, so the first MMA into each accumulator overwrites.
+// planes of B: 0 W_hi, 1 W_lo, 2 |W|_hi, 3 |W|_lo;  planes of A: 0 c_hi, 1 c_lo, 2 r_hi, 3 r_lo
+template <int kRole, bool kFirst>
 __device__ __forceinline__ void issue_kblock(const uint32_t (&blo)[4][4], const uint32_t (&acol)[4][4], uint32_t b_hi,
-                                             uint32_t d_ac, uint32_t d_ar, uint32_t d_cc, uint32_t d_cr, uint32_t idesc) {
-  // planes of B: 0 W_hi, 1 W_lo, 2 |W|_hi, 3 |W|_lo;  planes of A: 0 c_hi, 1 c_lo, 2 r_hi, 3 r_lo
+                                             uint32_t d0, uint32_t d1, uint32_t idesc) {
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    if (j == 0 && kFirst) {
-      mma_tf32_ts_lean<false>(d_cc, acol[1][j], blo[0][j], b_hi, idesc);
-      mma_tf32_ts_lean<true>(d_cc, acol[0][j], blo[1][j], b_hi, idesc);
-      mma_tf32_ts_lean<false>(d_ac, acol[0][j], blo[0][j], b_hi, idesc);
-      mma_tf32_ts_lean<false>(d_cr, acol[3][j], blo[2][j], b_hi, idesc);
-      mma_tf32_ts_lean<true>(d_cr, acol[2][j], blo[3][j], b_hi, idesc);
-      mma_tf32_ts_lean<false>(d_ar, acol[2][j], blo[2][j], b_hi, idesc);
+    if (kRole == 0) {
+      if (j == 0 && kFirst) {
+        mma_tf32_ts_lean<false>(d0, acol[0][j], blo[0][j], b_hi, idesc);
+        mma_tf32_ts_lean<false>(d1, acol[2][j], blo[2][j], b_hi, idesc);
+      } else {
+        mma_tf32_ts_lean<true>(d0, acol[0][j], blo[0][j], b_hi, idesc);
+        mma_tf32_ts_lean<true>(d1, acol[2][j], blo[2][j], b_hi, idesc);
+      }
     } else {
-      mma_tf32_ts_lean<true>(d_cc, acol[1][j], blo[0][j], b_hi, idesc);
-      mma_tf32_ts_lean<true>(d_cc, acol[0][j], blo[1][j], b_hi, idesc);
-      mma_tf32_ts_lean<true>(d_ac, acol[0][j], blo[0][j], b_hi, idesc);
-      mma_tf32_ts_lean<true>(d_cr, acol[3][j], blo[2][j], b_hi, idesc);
-      mma_tf32_ts_lean<true>(d_cr, acol[2][j], blo[3][j], b_hi, idesc);
-      mma_tf32_ts_lean<true>(d_ar, acol[2][j], blo[2][j], b_hi, idesc);
+      constexpr int lo = kRole == 1 ? 1 : 3, hi = kRole == 1 ? 0 : 2;   // A planes; B planes are hi, lo the other way round
+      if (j == 0 && kFirst) mma_tf32_ts_lean<false>(d0, acol[lo][j], blo[hi][j], b_hi, idesc);
+      else mma_tf32_ts_lean<true>(d0, acol[lo][j], blo[hi][j], b_hi, idesc);
+      mma_tf32_ts_lean<true>(d0, acol[hi][j], blo[lo][j], b_hi, idesc);
     }
   }
+}
+template <int kRole>
+__device__ __forceinline__ void issue_kblock_role(bool first, const uint32_t (&blo)[4][4], const uint32_t (&acol)[4][4],
+                                                  uint32_t b_hi, uint32_t d0, uint32_t d1, uint32_t idesc) {
+  if (first) issue_kblock<kRole, true>(blo, acol, b_hi, d0, d1, idesc);
+  else issue_kblock<kRole, false>(blo, acol, b_hi, d0, d1, idesc);
 }
 
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* v) {
@@ -200,6 +238,11 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* v) {
       ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
         "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
       : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+               : "memory");
 }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
@@ -216,12 +259,25 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* v) {
       : "memory");
 }
 
-// fp32 -> tf32, round to nearest (ties away from zero), done on the integer pipe: add half a
-// tf32 ulp to the magnitude and clear the 13 low mantissa bits.
-__device__ __forceinline__ uint32_t tf32_rn_bits(float v) { return (__float_as_uint(v) + 0x1000u) & 0xffffe000u; }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
+
+// Split of an fp32 value for the 3xTF32 product: hi = v with the 13 low mantissa bits cleared (the
+// value the tensor core reads from an fp32 word anyway), lo = v - hi, exact in fp32 and below
+// 2^-10 |v|.  lo is handed over as it is; the tensor core reads its leading 11 significant bits.
+// What is lost per operand is below 2^-20 |v| (2^-22 |v| on average), against 2^-24 |v| for a
+// rounded fp32 operation.  One logic and one floating-point instruction per value: the integer
+// pipe is half as wide as the fp32 pipe on this architecture and an integer round-to-nearest of
+// both parts (four integer instructions) made the conversion the bottleneck of the whole kernel.
 __device__ __forceinline__ void split_tf32(float v, uint32_t& hi, uint32_t& lo) {
-  hi = tf32_rn_bits(v);
-  lo = tf32_rn_bits(fsub(v, __uint_as_float(hi)));   // v - hi is exact in fp32
+  hi = __float_as_uint(v) & 0xffffe000u;
+  lo = __float_as_uint(fsub(v, __uint_as_float(hi)));
 }
 
 // Byte offset of (row, 16-byte chunk) inside a 128-row x 128-byte tile with the 128-byte swizzle
@@ -273,19 +329,21 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nkb = (K + BK - 1) / BK;
   // tiles of this CTA: blockIdx.x + i * gridDim.x, i = 0 .. my_tiles-1; n is the fast tile index
-  const int64_t my_tiles = (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
-  const int64_t total_it = my_tiles * nkb;   // k-blocks this CTA walks, across all its tiles
+  // (the host side guarantees that tile and k-block counts fit 32 bits: 64-bit loop counters and a
+  // 64-bit division per k-block cost more instructions than the conversion itself)
+  const int my_tiles = (int)((total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x);
+  const int total_it = my_tiles * nkb;   // k-blocks this CTA walks, across all its tiles
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kRawStages; ++s) {
       mbar_init(bar_full + 8 * s, 1);
-      mbar_init(bar_raw_empty + 8 * s, kConvWarps);
+      mbar_init(bar_raw_empty + 8 * s, kGroupWarps);
     }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(bar_ops_ready + 8 * s, kConvWarps);
-      mbar_init(bar_mma_done + 8 * s, 1);
+      mbar_init(bar_ops_ready + 8 * s, kGroupWarps);
+      mbar_init(bar_mma_done + 8 * s, kIssuers);
     }
-    mbar_init(bar_acc_ready, 1);
+    mbar_init(bar_acc_ready, kIssuers);
     mbar_init(bar_acc_free, kConvWarps);
     mbar_init(bar_conv, kConvWarps);
     *cta_abort = 0;
@@ -304,10 +362,10 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
     // ---------------------------------------------------------------- TMA producer
     // the whole warp walks the loop convergently (a lone thread looping while its 31 siblings sit at
     // the final barrier runs much slower); only the copy instructions are issued by lane 0
-    int64_t it = 0;
+    int it = 0;
     bool ok = true;
-    for (int64_t ti = 0; ti < my_tiles && ok; ++ti) {
-      const int64_t tile = blockIdx.x + ti * gridDim.x;
+    for (int ti = 0; ti < my_tiles && ok; ++ti) {
+      const int tile = blockIdx.x + ti * gridDim.x;
       const int m0 = (int)(tile / n_tiles_n) * BM, n0 = (int)(tile % n_tiles_n) * BN;
       for (int kb = 0; kb < nkb; ++kb, ++it) {
         const int rs = (int)(it % kRawStages);
@@ -315,25 +373,30 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
         if (it >= kRawStages &&
             !mbar_wait_warp(bar_raw_empty + 8 * rs, (uint32_t)((it / kRawStages - 1) & 1), cta_abort)) { ok = false; break; }
         if (lane == 0) {
+#ifdef FBX_NO_TMA
+          mbar_arrive(full);
+#else
           mbar_arrive_expect_tx(full, kRawStageBytes);
           const uint32_t dst = base + SharedLayout::raw(rs);
           tma_load_2d(dst, &tm_lo, kb * BK, m0, full);
           tma_load_2d(dst + kTileBytes, &tm_up, kb * BK, m0, full);
           tma_load_2d(dst + 2 * kTileBytes, &tm_w, kb * BK, n0, full);
+#endif
         }
         __syncwarp();
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp < kCtrlWarps) {
+    // ------------------------------------------------------------------ MMA issuers (warps 1-3)
+    // Each warp walks the loop convergently; lane 0 issues.  Descriptors are built once and only
+    // advanced by compile-time constants inside the loop: every operand of a warp's 2 x 8 MMAs
+    // (two operand stages) lives in a loop-invariant register.
+    const int role = warp - 1;
     bool ok = true;
-    int64_t it = 0;
-    // The warp walks the loop convergently; lane 0 issues.  Descriptors are built once and only
-    // advanced by compile-time constants inside the loop.
+    int it = 0;
     const uint64_t bdesc0 = smem_desc_sw128(base + SharedLayout::planes(0));
-    const uint32_t d_cc = tmem_base + kCorC, d_ac = tmem_base + kAccC, d_cr = tmem_base + kCorR, d_ar = tmem_base + kAccR;
-    // every operand of the 2 x 24 MMAs (two operand stages) lives in a loop-invariant register
     const uint32_t b_hi = (uint32_t)(bdesc0 >> 32);
+    const uint32_t d0 = tmem_base + (role == 0 ? kAccC : role == 1 ? kCorC : kCorR), d1 = tmem_base + kAccR;
     uint32_t blo[2][4][4], acol[2][4][4];
 #pragma unroll
     for (int st = 0; st < 2; ++st)
@@ -345,43 +408,56 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
           blo[st][pl][j] = (uint32_t)bdesc0 + ((st * kPlaneStageBytes + pl * kWTileBytes + j * 32) >> 4);
           acol[st][pl][j] = tmem_base + kABase + st * 128 + pl * 32 + j * 8;
         }
-    for (int64_t ti = 0; ti < my_tiles && ok; ++ti) {
+    for (int ti = 0; ti < my_tiles && ok; ++ti) {
       for (int kb = 0; kb < nkb; ++kb, ++it) {
         const int s = (int)(it & 1);
         ok = mbar_wait_warp(bar_ops_ready + 8 * s, (uint32_t)((it >> 1) & 1), cta_abort);
         // the first MMA of a tile overwrites the accumulators: the previous tile must have been read out
         if (ok && kb == 0 && ti > 0) ok = mbar_wait_warp(bar_acc_free, (uint32_t)((ti - 1) & 1), cta_abort);
         if (!ok) break;
+        if (role == 0) FBX_T(it, 8);
         tc_fence_after();
         if (lane == 0) {
+#ifndef FBX_NO_MMA
           if (s == 0) {
-            if (kb == 0) issue_kblock<true>(blo[0], acol[0], b_hi, d_ac, d_ar, d_cc, d_cr, kInstrDesc);
-            else issue_kblock<false>(blo[0], acol[0], b_hi, d_ac, d_ar, d_cc, d_cr, kInstrDesc);
+            if (role == 0) issue_kblock_role<0>(kb == 0, blo[0], acol[0], b_hi, d0, d1, kInstrDesc);
+            else if (role == 1) issue_kblock_role<1>(kb == 0, blo[0], acol[0], b_hi, d0, d1, kInstrDesc);
+            else issue_kblock_role<2>(kb == 0, blo[0], acol[0], b_hi, d0, d1, kInstrDesc);
           } else {
-            if (kb == 0) issue_kblock<true>(blo[1], acol[1], b_hi, d_ac, d_ar, d_cc, d_cr, kInstrDesc);
-            else issue_kblock<false>(blo[1], acol[1], b_hi, d_ac, d_ar, d_cc, d_cr, kInstrDesc);
+            if (role == 0) issue_kblock_role<0>(kb == 0, blo[1], acol[1], b_hi, d0, d1, kInstrDesc);
+            else if (role == 1) issue_kblock_role<1>(kb == 0, blo[1], acol[1], b_hi, d0, d1, kInstrDesc);
+            else issue_kblock_role<2>(kb == 0, blo[1], acol[1], b_hi, d0, d1, kInstrDesc);
           }
+#endif
+          if (role == 0) FBX_T(it, 9);
           tc_commit(bar_mma_done + 8 * s);
           if (kb == nkb - 1) tc_commit(bar_acc_ready);
+          if (role == 0) FBX_T(it, 10);
         }
         __syncwarp();
       }
     }
   } else {
     // ------------------------------------------------- converters, then epilogue
-    const int cw = warp - 2;           // 0..7
-    const int ct = threadIdx.x - 64;   // converter thread index 0..255
+    // Two groups of eight warps; group g converts the k-blocks it = g (mod 2) into operand stage g
+    // (raw stage g, plane stage g, A buffer g).  The conversion of a k-block is a chain of
+    // latencies (shared-memory loads, arithmetic, tensor-memory stores, barrier hand-overs) about
+    // twice as long as the MMAs of a k-block.  A group loads and converts its next block in
+    // registers while the MMAs still read its operand stage and only the stores wait for them, so
+    // the two chains, half a period apart, overlap each other and the MMAs.
+    const int cw = warp - kCtrlWarps;  // 0..15
+    const int g = cw >> 3;             // converter group
+    const int ct = threadIdx.x - 32 * kCtrlWarps;   // converter thread index 0..511
+    const int gt = ct & 255;           // index inside the group
     const int quarter = warp & 3;      // TMEM lane quarter this warp may access
-    const int half = cw >> 2;          // which 16 of the 32 k values of a block
+    const int half = (cw >> 2) & 1;    // which 16 of the 32 k values of a block
+    const int cq = cw >> 2;            // epilogue: which 16 of the 64 tile columns
     const int row = quarter * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     bool ok = true;
-    // The epilogue of tile e runs after this many k-blocks (counted over all tiles) have been
-    // converted: two blocks into tile e+1, or at the very end for the last tile.
-    const int lead = nkb >= 2 ? 2 : 1;
-    int64_t epi_tile = 0;
+    int epi_tile = 0;
     uint32_t conv_phase = 0;
-    // rendezvous of the eight converter warps through an mbarrier, so that the wait is bounded
+    // rendezvous of the converter warps through an mbarrier, so that the wait is bounded
     auto conv_sync = [&]() -> bool {
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_conv);
@@ -389,161 +465,198 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
       ++conv_phase;
       return r;
     };
-    for (int64_t it = 0; it < total_it && ok; ++it) {
-      const int s = (int)(it & 1);
-      const int rs = (int)(it % kRawStages);
-      ok = mbar_wait_warp(bar_full + 8 * rs, (uint32_t)((it / kRawStages) & 1), cta_abort);
-      if (!ok) break;
-      const uint8_t* raw = base_ptr + SharedLayout::raw(rs);
-      float4 vl[4], vu[4], vw[2];
+    // Epilogue of one tile: warp (quarter, cq) reads rows quarter*32.. and
+    // columns cq*16.. of the four accumulators.
+    auto epilogue = [&](int e) -> bool {
+      if (!mbar_wait_warp(bar_acc_ready, (uint32_t)(e & 1), cta_abort)) return false;
+      tc_fence_after();
+      const int etile = blockIdx.x + e * gridDim.x;
+      const int ncol = cq * 16;
+      const int nb = (int)(etile % n_tiles_n) * BN + ncol;
+      uint32_t t0[16], t1[16];
+      float yc[16], yr[16];
+      tmem_ld16(tmem_base + lane_addr + kAccC + ncol, t0);
+      tmem_ld16(tmem_base + lane_addr + kCorC + ncol, t1);
+      tmem_wait_ld();
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const uint32_t off = swz(row, half * 4 + c);
-        vl[c] = *reinterpret_cast<const float4*>(raw + off);
-        vu[c] = *reinterpret_cast<const float4*>(raw + kTileBytes + off);
-      }
-      // W tile: 64 rows x 8 chunks; this thread converts two adjacent chunks of one row
-      const int wrow = ct >> 2, wchunk = (ct & 3) * 2;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) vw[c] = *reinterpret_cast<const float4*>(raw + 2 * kTileBytes + swz(wrow, wchunk + c));
+      for (int i = 0; i < 16; ++i) yc[i] = fadd(__uint_as_float(t0[i]), __uint_as_float(t1[i]));
+      tmem_ld16(tmem_base + lane_addr + kAccR + ncol, t0);
+      tmem_ld16(tmem_base + lane_addr + kCorR + ncol, t1);
+      tmem_wait_ld();
+      // the accumulators are in registers now: hand tensor memory back to the MMA issuer
+      tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_raw_empty + 8 * rs);
-      // all arithmetic happens before the wait for the operand buffers, so that the stretch between
-      // "MMAs of k-block it-2 done" and "operands of k-block it ready" is only stores
+      if (lane == 0) mbar_arrive(bar_acc_free);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) yr[i] = fadd(__uint_as_float(t0[i]), __uint_as_float(t1[i]));
+      // Output: both tiles are staged in shared memory in the 128-byte-swizzled box layout and
+      // written by TMA, so that global memory sees whole 128-byte lines.  Rows and columns
+      // beyond M and N are clipped by the tensor map.
+      if (ct == 0) tma_store_wait_read();      // the previous tile's stores have read the staging buffer
+      if (!conv_sync()) return false;
+      {
+        uint8_t* so = base_ptr + SharedLayout::out() + (uint32_t)(cq >> 1) * kOutBoxBytes;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          float lo[4], up[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            lo[i] = fsub(yc[q * 4 + i], yr[q * 4 + i]);
+            up[i] = fadd(yc[q * 4 + i], yr[q * 4 + i]);
+            if (bias != nullptr) {
+              const int n = nb + q * 4 + i;
+              const float bv = n < N ? bias[n] : 0.f;
+              lo[i] = fadd(lo[i], bv);
+              up[i] = fadd(up[i], bv);
+            }
+          }
+          const uint32_t off = swz(row, (cq & 1) * 4 + q);
+          *reinterpret_cast<float4*>(so + off) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+          *reinterpret_cast<float4*>(so + 2 * kOutBoxBytes + off) = make_float4(up[0], up[1], up[2], up[3]);
+        }
+      }
+      fence_async_smem();
+      if (!conv_sync()) return false;
+      if (ct == 0) {
+        // The output tensor map is 3-D.  Plain store: (column, row, 0).  Head-split store
+        // (split_rows > 0): the output is [group * heads + head][row in group][feature in head], a
+        // 32-column box lies inside one head and its 128 rows inside one group.
+        const int my = (int)(etile / n_tiles_n) * BM, nx = (int)(etile % n_tiles_n) * BN;
+        const uint32_t so = base + SharedLayout::out();
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          int cx = nx + 32 * q, cy = my, cz = 0;
+          if (split_rows > 0) {
+            const int heads = N / split_d;
+            cz = (my / split_rows) * heads + cx / split_d;
+            cy = my % split_rows;
+            cx = cx % split_d;
+          }
+#ifndef FBX_NO_STORE
+          tma_store_3d(&tm_out_lo, cx, cy, cz, so + q * kOutBoxBytes);
+          tma_store_3d(&tm_out_up, cx, cy, cz, so + (2 + q) * kOutBoxBytes);
+#endif
+        }
+        tma_store_commit();
+      }
+      return true;
+    };
+    // need = tile of k-block it-2, kept incrementally (it advances by two per iteration)
+    int need = 0, need_kb = g - 2;
+    for (int it = g; it < total_it && ok; it += 2, need_kb += 2) {
+      // The stores of k-block it wait for the MMAs of k-block it-2.  Those wait for the accumulators
+      // of the tile before theirs to be read out, so the epilogues of all earlier tiles come first.
+      // Both groups run every epilogue, in the same order.
+      while (need_kb >= nkb) { need_kb -= nkb; ++need; }
+      while (ok && epi_tile < need) { ok = epilogue(epi_tile); ++epi_tile; }
+      if (!ok) break;
+      ok = mbar_wait_warp(bar_full + 8 * g, (uint32_t)((it >> 1) & 1), cta_abort);
+      if (!ok) break;
+      const uint8_t* raw = base_ptr + SharedLayout::raw(g);
       uint32_t chi[16], clo[16], rhi[16], rlo[16];
+      // W tile: 64 rows x 8 chunks; this thread converts two adjacent chunks of one row
+      const int wrow = gt >> 2, wchunk = (gt & 3) * 2;
+      float4 vw[2];
+      {
+        float4 vl[4], vu[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint32_t off = swz(row, half * 4 + q);
+#ifdef FBX_NO_LDS
+          vl[q] = make_float4((float)off, 1.f, (float)it, 2.f);
+          vu[q] = make_float4((float)row, 3.f, (float)it, 4.f);
+#else
+          vl[q] = *reinterpret_cast<const float4*>(raw + off);
+          vu[q] = *reinterpret_cast<const float4*>(raw + kTileBytes + off);
+#endif
+        }
+#pragma unroll
+        for (int q = 0; q < 2; ++q)
+#ifdef FBX_NO_LDS
+          vw[q] = make_float4((float)wrow, 1.5f, (float)it, -2.f);
+#else
+          vw[q] = *reinterpret_cast<const float4*>(raw + 2 * kTileBytes + swz(wrow, wchunk + q));
+#endif
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_raw_empty + 8 * g);
+        // all arithmetic happens before the wait for the operand stage
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float l4[4] = {vl[q].x, vl[q].y, vl[q].z, vl[q].w};
+          const float u4[4] = {vu[q].x, vu[q].y, vu[q].z, vu[q].w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+#ifdef FBX_NO_ALU
+            chi[q * 4 + i] = clo[q * 4 + i] = __float_as_uint(l4[i]); rhi[q * 4 + i] = rlo[q * 4 + i] = __float_as_uint(u4[i]);
+#else
+            // centre (l + u) / 2 and radius (u - l) / 2, each rounded once
+            const float hu = fmul(u4[i], 0.5f);
+            split_tf32(__fmaf_rn(l4[i], 0.5f, hu), chi[q * 4 + i], clo[q * 4 + i]);
+            split_tf32(__fmaf_rn(l4[i], -0.5f, hu), rhi[q * 4 + i], rlo[q * 4 + i]);
+#endif
+          }
+        }
+      }
       uint32_t whi[8], wlo[8], ahi[8], alo[8];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const float l4[4] = {vl[c].x, vl[c].y, vl[c].z, vl[c].w};
-        const float u4[4] = {vu[c].x, vu[c].y, vu[c].z, vu[c].w};
+      for (int q = 0; q < 2; ++q) {
+        const float w4[4] = {vw[q].x, vw[q].y, vw[q].z, vw[q].w};
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          split_tf32(fmul(fadd(l4[e], u4[e]), 0.5f), chi[c * 4 + e], clo[c * 4 + e]);
-          split_tf32(fmul(fsub(u4[e], l4[e]), 0.5f), rhi[c * 4 + e], rlo[c * 4 + e]);
+        for (int i = 0; i < 4; ++i) {
+#ifdef FBX_NO_ALU
+          whi[q * 4 + i] = wlo[q * 4 + i] = ahi[q * 4 + i] = alo[q * 4 + i] = __float_as_uint(w4[i]);
+#else
+          split_tf32(w4[i], whi[q * 4 + i], wlo[q * 4 + i]);
+          // |w| = sgn(w) * (hi + lo); hi and lo both carry the sign of w (lo may be zero)
+          ahi[q * 4 + i] = whi[q * 4 + i] & 0x7fffffffu;
+          alo[q * 4 + i] = wlo[q * 4 + i] & 0x7fffffffu;
+#endif
         }
       }
+      // pin the converted values in registers here: the compiler would otherwise sink the arithmetic below the wait
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const float w4[4] = {vw[c].x, vw[c].y, vw[c].z, vw[c].w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          split_tf32(w4[e], whi[c * 4 + e], wlo[c * 4 + e]);
-          // |w| = sgn(w) * (hi + lo): flip the sign of both parts where w is negative
-          const uint32_t flip = __float_as_uint(w4[e]) & 0x80000000u;
-          ahi[c * 4 + e] = whi[c * 4 + e] ^ flip;
-          alo[c * 4 + e] = wlo[c * 4 + e] ^ flip;
-        }
-      }
+      for (int i = 0; i < 16; ++i) asm volatile("" : "+r"(chi[i]), "+r"(clo[i]), "+r"(rhi[i]), "+r"(rlo[i]));
       if (it >= 2) {
-        ok = mbar_wait_warp(bar_mma_done + 8 * s, (uint32_t)(((it >> 1) - 1) & 1), cta_abort);
+        ok = mbar_wait_warp(bar_mma_done + 8 * g, (uint32_t)(((it >> 1) - 1) & 1), cta_abort);
         if (!ok) break;
         tc_fence_after();
       }
+      if ((cw & 7) == 0) FBX_T(it, 11);
+      if ((cw & 7) == 5) FBX_T(it, 12);
       {
-        uint8_t* pl = base_ptr + SharedLayout::planes(s);
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          const uint32_t off = swz(wrow, wchunk + c);
-          *reinterpret_cast<uint4*>(pl + 0 * kWTileBytes + off) = make_uint4(whi[c * 4], whi[c * 4 + 1], whi[c * 4 + 2], whi[c * 4 + 3]);
-          *reinterpret_cast<uint4*>(pl + 1 * kWTileBytes + off) = make_uint4(wlo[c * 4], wlo[c * 4 + 1], wlo[c * 4 + 2], wlo[c * 4 + 3]);
-          *reinterpret_cast<uint4*>(pl + 2 * kWTileBytes + off) = make_uint4(ahi[c * 4], ahi[c * 4 + 1], ahi[c * 4 + 2], ahi[c * 4 + 3]);
-          *reinterpret_cast<uint4*>(pl + 3 * kWTileBytes + off) = make_uint4(alo[c * 4], alo[c * 4 + 1], alo[c * 4 + 2], alo[c * 4 + 3]);
-        }
-        const uint32_t a_cols = tmem_base + lane_addr + kABase + (uint32_t)s * 128u + (uint32_t)half * 16u;
+        const uint32_t a_cols = tmem_base + lane_addr + kABase + (uint32_t)g * 128u + (uint32_t)half * 16u;
+#ifndef FBX_NO_TMEM_ST
         tmem_st16(a_cols + 0, chi);
         tmem_st16(a_cols + 32, clo);
         tmem_st16(a_cols + 64, rhi);
         tmem_st16(a_cols + 96, rlo);
-      }
-      tmem_wait_st();
-      fence_async_smem();   // B planes were written through the generic proxy; the MMA reads them through the async proxy
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_ops_ready + 8 * s);
-
-      // ---- epilogue of tile epi_tile, once the conversion is `lead` blocks into the next tile
-      const bool last_it = (it + 1 == total_it);
-      if (it + 1 == (epi_tile + 1) * nkb + lead || last_it) {
-        // at the very end, up to two tiles can be outstanding (nkb == 1): drain them all
-        while (ok && epi_tile < my_tiles && ((epi_tile + 1) * nkb + lead <= it + 1 || last_it)) {
-          ok = mbar_wait_warp(bar_acc_ready, (uint32_t)(epi_tile & 1), cta_abort);
-          if (!ok) break;
-          tc_fence_after();
-          const int64_t etile = blockIdx.x + epi_tile * gridDim.x;
-          const int ncol = half * 32;
-          const int nb = (int)(etile % n_tiles_n) * BN + ncol;
-          uint32_t t0[32], t1[32];
-          float yc[32], yr[32];
-          tmem_ld32(tmem_base + lane_addr + kAccC + ncol, t0);
-          tmem_ld32(tmem_base + lane_addr + kCorC + ncol, t1);
-          tmem_wait_ld();
+#else
+        if (chi[3] == 0x12345u && rlo[5] == 0x777u) *cta_abort = 0;
+#endif
+        uint8_t* pl = base_ptr + SharedLayout::planes(g);
+#ifdef FBX_NO_STS
+        if (whi[0] == 0x12345u && alo[7] == 0x777u && wlo[1] == 0x999u && ahi[2] == 0x9u)
+#endif
 #pragma unroll
-          for (int i = 0; i < 32; ++i) yc[i] = fadd(__uint_as_float(t0[i]), __uint_as_float(t1[i]));
-          tmem_ld32(tmem_base + lane_addr + kAccR + ncol, t0);
-          tmem_ld32(tmem_base + lane_addr + kCorR + ncol, t1);
-          tmem_wait_ld();
-          // the accumulators are in registers now: hand tensor memory back to the MMA issuer
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar_acc_free);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) yr[i] = fadd(__uint_as_float(t0[i]), __uint_as_float(t1[i]));
-          // Output: both tiles are staged in shared memory in the 128-byte-swizzled box layout and
-          // written by TMA, so that global memory sees whole 128-byte lines.  Rows and columns
-          // beyond M and N are clipped by the tensor map.
-          if (ct == 0) tma_store_wait_read();      // the previous tile's stores have read the staging buffer
-          ok = conv_sync();
-          if (!ok) break;
-          {
-            uint8_t* so = base_ptr + SharedLayout::out() + (uint32_t)half * kOutBoxBytes;
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              float lo[4], up[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                lo[e] = fsub(yc[q * 4 + e], yr[q * 4 + e]);
-                up[e] = fadd(yc[q * 4 + e], yr[q * 4 + e]);
-                if (bias != nullptr) {
-                  const int n = nb + q * 4 + e;
-                  const float bv = n < N ? bias[n] : 0.f;
-                  lo[e] = fadd(lo[e], bv);
-                  up[e] = fadd(up[e], bv);
-                }
-              }
-              const uint32_t off = swz(row, q);
-              *reinterpret_cast<float4*>(so + off) = make_float4(lo[0], lo[1], lo[2], lo[3]);
-              *reinterpret_cast<float4*>(so + 2 * kOutBoxBytes + off) = make_float4(up[0], up[1], up[2], up[3]);
-            }
-          }
-          fence_async_smem();
-          ok = conv_sync();
-          if (!ok) break;
-          if (ct == 0) {
-            // The output tensor map is 3-D.  Plain store: (column, row, 0).  Head-split store
-            // (split_rows > 0): the output is [group * heads + head][row in group][feature in head], a
-            // 32-column box lies inside one head and its 128 rows inside one group.
-            const int my = (int)(etile / n_tiles_n) * BM, nx = (int)(etile % n_tiles_n) * BN;
-            const uint32_t so = base + SharedLayout::out();
-#pragma unroll
-            for (int q = 0; q < 2; ++q) {
-              int cx = nx + 32 * q, cy = my, cz = 0;
-              if (split_rows > 0) {
-                const int heads = N / split_d;
-                cz = (my / split_rows) * heads + cx / split_d;
-                cy = my % split_rows;
-                cx = cx % split_d;
-              }
-              tma_store_3d(&tm_out_lo, cx, cy, cz, so + q * kOutBoxBytes);
-              tma_store_3d(&tm_out_up, cx, cy, cz, so + (2 + q) * kOutBoxBytes);
-            }
-            tma_store_commit();
-          }
-          ++epi_tile;
+        for (int q = 0; q < 2; ++q) {
+          const uint32_t off = swz(wrow, wchunk + q);
+          *reinterpret_cast<uint4*>(pl + 0 * kWTileBytes + off) = make_uint4(whi[q * 4], whi[q * 4 + 1], whi[q * 4 + 2], whi[q * 4 + 3]);
+          *reinterpret_cast<uint4*>(pl + 1 * kWTileBytes + off) = make_uint4(wlo[q * 4], wlo[q * 4 + 1], wlo[q * 4 + 2], wlo[q * 4 + 3]);
+          *reinterpret_cast<uint4*>(pl + 2 * kWTileBytes + off) = make_uint4(ahi[q * 4], ahi[q * 4 + 1], ahi[q * 4 + 2], ahi[q * 4 + 3]);
+          *reinterpret_cast<uint4*>(pl + 3 * kWTileBytes + off) = make_uint4(alo[q * 4], alo[q * 4 + 1], alo[q * 4 + 2], alo[q * 4 + 3]);
         }
       }
+      fence_async_smem();   // B planes were written through the generic proxy; the MMA reads them through the async proxy
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_ops_ready + 8 * g);
+      FBX_T(it, cw & 7);
     }
+    // the tiles whose epilogue has not been triggered by a later conversion
+    while (ok && epi_tile < my_tiles) { ok = epilogue(epi_tile); ++epi_tile; }
   }
-  if (threadIdx.x == 64) tma_store_wait_all();   // this thread issued the bulk stores of the epilogues
+  if (threadIdx.x == 32 * kCtrlWarps) tma_store_wait_all();   // this thread issued the bulk stores of the epilogues
   // Tear-down.  On the error path, give outstanding bulk copies time to land before the shared
   // memory is released (bounded), then free the tensor memory.
   if (*cta_abort) {
@@ -618,7 +731,9 @@ bool tc_split_supported(int64_t M, int N, int split_rows, int split_d) {
 
 bool tc_gemm_supported(const float* a_lo, const float* a_up, const float* W, const float* c_lo, const float* c_up,
                        int64_t M, int N, int K) {
-  return M >= 256 && M < (1ll << 31) && N >= 32 && N % 4 == 0 && K >= 8 && K % 4 == 0 && aligned16(a_lo) &&
+  // the kernel counts tiles and k-blocks in 32 bits
+  const int64_t k_blocks = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * ((K + BK - 1) / BK);
+  return M >= 256 && M < (1ll << 31) && k_blocks < (1ll << 31) && N >= 32 && N % 4 == 0 && K >= 8 && K % 4 == 0 && aligned16(a_lo) &&
          aligned16(a_up) && aligned16(W) && aligned16(c_lo) && aligned16(c_up) && encode_fn() != nullptr;
 }
 
@@ -654,6 +769,9 @@ int launch_split_sign_tc(const float* a_lo, const float* a_up, const float* W, c
 
 // Reads (and clears) the device-side flag that the tensor-core GEMM raises when one of its bounded
 // waits expires.  Synchronises the device.
+#ifdef FBX_TRACE
+extern "C" void fb_tc_trace(long long* out) { cudaMemcpyFromSymbol(out, fb::g_trace, sizeof(long long) * 64 * 16); }
+#endif
 extern "C" int fb_tc_error_flag(int* flag) {
   if (!flag) return FB_ERR_ARG;
   int v = 0;
