@@ -4,37 +4,44 @@
 //   y_c = c W^T,  y_r = r |W|^T,  y_lw = y_c - y_r,  y_uw = y_c + y_r,
 //   c = (x_lw + x_uw)/2,  r = (x_uw - x_lw)/2          (centre/radius form of Bounds.py:403-412)
 //
-// Every fp32 operand v is split into hi = tf32(v) and lo = tf32(v - hi); a product a*b is
-// evaluated as a_hi*b_hi + a_hi*b_lo + a_lo*b_hi with fp32 accumulation in tensor memory, which
-// keeps ~21 mantissa bits per product (the dropped lo*lo term is below 2^-22 relative).
+// Every fp32 operand v is split into hi = v with the 13 low mantissa bits cleared and lo = v - hi
+// (exact); a product a*b is evaluated as a_hi*b_hi + a_hi*b_lo + a_lo*b_hi with fp32 accumulation in
+// tensor memory.  The tensor core reads the leading 11 significant bits of lo; what is dropped per
+// operand is below 2^-20 |v| (2^-22 |v| on average) and the dropped lo*lo term is below 2^-20.
 //
 // The tensor cores add into their fp32 accumulator with truncation, a bias that grows with the
 // number of accumulating instructions; the two small cross terms therefore go to accumulators of
-// their own (their truncation is negligible at 2^-11 of the magnitude) and the leading hi*hi term
+// their own (their truncation is negligible at 2^-10 of the magnitude) and the leading hi*hi term
 // is the only one that touches the main accumulators.  The four partial results are summed with
 // round-to-nearest in registers in the epilogue.
 //
-// One CTA computes a 128 x 64 tile of both outputs.  K is walked in blocks of 32:
-//   warp 0     TMA producer: raw fp32 tiles of x_lw, x_uw (128 rows x 32) and of W (64 rows x 32)
-//              into a two-stage shared-memory ring (128-byte swizzle).
-//   warps 2-9  converters: read the raw tiles, form c, r, split hi/lo, and
+// One CTA computes a 128 x 64 tile of both outputs (four accumulators of 64 columns and two
+// operand buffers of 128 columns fill the 512 columns of tensor memory, which is what limits the
+// tile to 64 columns).  K is walked in blocks of 32.  Warp roles (24 warps):
+//   warp 0       TMA producer: raw fp32 tiles of x_lw, x_uw (128 rows x 32) and of W (64 rows x 32)
+//                into a two-stage shared-memory ring (128-byte swizzle).
+//   warps 1-3    MMA issuers, one per accumulator set (main centre + main radius / centre
+//                correction / radius correction), 8 tcgen05.mma.kind::tf32 per k-block each.  One
+//                thread sustains one MMA per 50-110 cycles whatever its size (measured), a
+//                128 x 64 x 8 MMA occupies the tensor core for 32: three issuers keep it fed, and
+//                as no accumulator is shared between them they need no order among themselves.
+//   warps 4-7    epilogue, one warp per tensor-memory lane quarter: tcgen05.ld the accumulators,
+//                y_c -/+ y_r (+ bias), stage the two output tiles in shared memory (swizzled) and
+//                write them with TMA stores (full 128-byte lines).
+//   warps 8-23   converters, two groups of eight; group g handles the k-blocks it = g (mod 2):
+//                read the raw tiles, form c, r, split hi/lo, and
 //                - store the four A planes (c_hi, c_lo, r_hi, r_lo) of the block into TENSOR MEMORY
 //                  (tcgen05.st; the A operand of the MMAs comes from TMEM, lane = tile row),
 //                - store the four B planes (W_hi, W_lo, |W|_hi, |W|_lo) into shared memory in the
 //                  K-major 128B-swizzled layout the MMA descriptor expects.
-//   warp 1     MMA issuer (one thread): per 8-wide k step six tcgen05.mma.kind::tf32 instructions
-//              into four fp32 accumulators (centre / radius x main / correction), 64 columns each.
-//   warps 2-9  epilogue: tcgen05.ld the accumulators, y_c -/+ y_r (+ bias), stage the two output tiles in
-//              shared memory (swizzled) and write them with TMA stores (full 128-byte lines).
 // TMEM columns: [0,64) centre main, [64,128) radius main, [128,192) centre correction,
 // [192,256) radius correction, [256,512) two buffers of the four A planes.  No cluster launch
 // and no multicast is used.
 //
 // The kernel is persistent: a CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...  with one
 // running k-block counter, so the producer and the converters run ahead into the next tile while
-// the MMAs of the current one finish; the epilogue of tile t is slotted in after two k-blocks of
-// tile t+1 have been converted, which leaves the tensor cores idle only while the accumulators
-// are read out of tensor memory.
+// the MMAs of the current one finish and the epilogue warps write it out; the tensor cores idle
+// only while the accumulators are read out of tensor memory.
 //
 // Every wait on an mbarrier is bounded; on expiry the kernel raises a device-side flag
 // (fb_tc_error_flag), drains, frees its tensor memory and returns.
@@ -52,8 +59,11 @@ constexpr int kGroupWarps = 8;                           // converter warps per 
 constexpr int kConvGroups = 2;                           // group g converts the k-blocks it = g (mod 2)
 constexpr int kConvWarps = kConvGroups * kGroupWarps;
 constexpr int kIssuers = 3;                              // MMA-issuing warps, each owning accumulators of its own
+constexpr int kEpiWarps = 4;                             // epilogue warps, one per tensor-memory lane quarter
 constexpr int kCtrlWarps = 1 + kIssuers;                 // TMA producer + issuers
-constexpr int kThreads = 32 * (kCtrlWarps + kConvWarps);
+constexpr int kFirstConvWarp = kCtrlWarps + kEpiWarps;
+constexpr int kThreads = 32 * (kFirstConvWarp + kConvWarps);
+static_assert(kCtrlWarps % 4 == 0, "epilogue warp e must be the warp of lane quarter e");
 constexpr uint32_t kTileBytes = BM * BK * 4;             // one 128 x 32 fp32 tile of x = 16 KB
 constexpr uint32_t kWTileBytes = BN * BK * 4;            // one 64 x 32 fp32 tile of W = 8 KB
 constexpr uint32_t kRawStageBytes = 2 * kTileBytes + kWTileBytes;  // x_lw, x_uw, W
@@ -68,12 +78,6 @@ constexpr uint32_t kTryNs = 20000;       // suspend-time hint of one mbarrier tr
 constexpr uint32_t kMaxTries = 100000;  // x 20 us = 2 s upper bound for any single wait
 
 static __device__ int g_tc_error = 0;
-#ifdef FBX_TRACE
-static __device__ long long g_trace[64 * 16];
-#define FBX_T(it, slot) do { if (blockIdx.x == 0 && lane == 0 && (it) >= 32 && (it) < 96) g_trace[((it) - 32) * 16 + (slot)] = clock64(); } while (0)
-#else
-#define FBX_T(it, slot) do { } while (0)
-#endif
 
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -118,10 +122,8 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* cta_abort) {
   // fast path: in a well-fed pipeline the phase is usually complete already, and the non-blocking
   // test answers much sooner than a suspending try
-#ifndef FBX_NO_TEST
   for (int i = 0; i < 4; ++i)
     if (mbar_test_wait(bar, parity)) return true;
-#endif
   for (uint32_t i = 0; i < kMaxTries; ++i) {
     if (mbar_try_wait(bar, parity, kTryNs)) return true;
     if (*cta_abort) return false;
@@ -268,6 +270,13 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* v) {
       : "memory");
 }
 
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t* v) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+               : "r"(taddr)
+               : "memory");
+}
+
 // Split of an fp32 value for the 3xTF32 product: hi = v with the 13 low mantissa bits cleared (the
 // value the tensor core reads from an fp32 word anyway), lo = v - hi, exact in fp32 and below
 // 2^-10 |v|.  lo is handed over as it is; the tensor core reads its leading 11 significant bits.
@@ -344,8 +353,8 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
       mbar_init(bar_mma_done + 8 * s, kIssuers);
     }
     mbar_init(bar_acc_ready, kIssuers);
-    mbar_init(bar_acc_free, kConvWarps);
-    mbar_init(bar_conv, kConvWarps);
+    mbar_init(bar_acc_free, kEpiWarps);
+    mbar_init(bar_conv, kEpiWarps);
     *cta_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -373,15 +382,11 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
         if (it >= kRawStages &&
             !mbar_wait_warp(bar_raw_empty + 8 * rs, (uint32_t)((it / kRawStages - 1) & 1), cta_abort)) { ok = false; break; }
         if (lane == 0) {
-#ifdef FBX_NO_TMA
-          mbar_arrive(full);
-#else
           mbar_arrive_expect_tx(full, kRawStageBytes);
           const uint32_t dst = base + SharedLayout::raw(rs);
           tma_load_2d(dst, &tm_lo, kb * BK, m0, full);
           tma_load_2d(dst + kTileBytes, &tm_up, kb * BK, m0, full);
           tma_load_2d(dst + 2 * kTileBytes, &tm_w, kb * BK, n0, full);
-#endif
         }
         __syncwarp();
       }
@@ -415,10 +420,8 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
         // the first MMA of a tile overwrites the accumulators: the previous tile must have been read out
         if (ok && kb == 0 && ti > 0) ok = mbar_wait_warp(bar_acc_free, (uint32_t)((ti - 1) & 1), cta_abort);
         if (!ok) break;
-        if (role == 0) FBX_T(it, 8);
         tc_fence_after();
         if (lane == 0) {
-#ifndef FBX_NO_MMA
           if (s == 0) {
             if (role == 0) issue_kblock_role<0>(kb == 0, blo[0], acol[0], b_hi, d0, d1, kInstrDesc);
             else if (role == 1) issue_kblock_role<1>(kb == 0, blo[0], acol[0], b_hi, d0, d1, kInstrDesc);
@@ -428,100 +431,87 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
             else if (role == 1) issue_kblock_role<1>(kb == 0, blo[1], acol[1], b_hi, d0, d1, kInstrDesc);
             else issue_kblock_role<2>(kb == 0, blo[1], acol[1], b_hi, d0, d1, kInstrDesc);
           }
-#endif
-          if (role == 0) FBX_T(it, 9);
           tc_commit(bar_mma_done + 8 * s);
           if (kb == nkb - 1) tc_commit(bar_acc_ready);
-          if (role == 0) FBX_T(it, 10);
         }
         __syncwarp();
       }
     }
-  } else {
-    // ------------------------------------------------- converters, then epilogue
-    // Two groups of eight warps; group g converts the k-blocks it = g (mod 2) into operand stage g
-    // (raw stage g, plane stage g, A buffer g).  The conversion of a k-block is a chain of
-    // latencies (shared-memory loads, arithmetic, tensor-memory stores, barrier hand-overs) about
-    // twice as long as the MMAs of a k-block.  A group loads and converts its next block in
-    // registers while the MMAs still read its operand stage and only the stores wait for them, so
-    // the two chains, half a period apart, overlap each other and the MMAs.
-    const int cw = warp - kCtrlWarps;  // 0..15
-    const int g = cw >> 3;             // converter group
-    const int ct = threadIdx.x - 32 * kCtrlWarps;   // converter thread index 0..511
-    const int gt = ct & 255;           // index inside the group
-    const int quarter = warp & 3;      // TMEM lane quarter this warp may access
-    const int half = (cw >> 2) & 1;    // which 16 of the 32 k values of a block
-    const int cq = cw >> 2;            // epilogue: which 16 of the 64 tile columns
+  } else if (warp < kFirstConvWarp) {
+    // ------------------------------------------------------------------ epilogue (warps 4-7)
+    // Warp q reads rows q*32.. of the four accumulators, 8 columns at a time, combines them
+    // (y_c -/+ y_r, + bias), stages the two output tiles in shared memory in the 128-byte-swizzled
+    // box layout and has them written by TMA, so that global memory sees whole 128-byte lines.
+    // Rows and columns beyond M and N are clipped by the tensor map.  The accumulators are handed
+    // back to the MMA issuers as soon as the last column is in registers; the converters never
+    // stop for an epilogue.
+    const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const bool leader = threadIdx.x == 32 * kCtrlWarps;
     bool ok = true;
-    int epi_tile = 0;
-    uint32_t conv_phase = 0;
-    // rendezvous of the converter warps through an mbarrier, so that the wait is bounded
-    auto conv_sync = [&]() -> bool {
+    uint32_t epi_phase = 0;
+    // rendezvous of the epilogue warps through an mbarrier, so that the wait is bounded
+    auto epi_sync = [&]() -> bool {
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_conv);
-      const bool r = mbar_wait_warp(bar_conv, conv_phase & 1u, cta_abort);
-      ++conv_phase;
+      const bool r = mbar_wait_warp(bar_conv, epi_phase & 1u, cta_abort);
+      ++epi_phase;
       return r;
     };
-    // Epilogue of one tile: warp (quarter, cq) reads rows quarter*32.. and
-    // columns cq*16.. of the four accumulators.
-    auto epilogue = [&](int e) -> bool {
-      if (!mbar_wait_warp(bar_acc_ready, (uint32_t)(e & 1), cta_abort)) return false;
+    for (int e = 0; e < my_tiles && ok; ++e) {
+      ok = mbar_wait_warp(bar_acc_ready, (uint32_t)(e & 1), cta_abort);
+      if (!ok) break;
       tc_fence_after();
       const int etile = blockIdx.x + e * gridDim.x;
-      const int ncol = cq * 16;
-      const int nb = (int)(etile % n_tiles_n) * BN + ncol;
-      uint32_t t0[16], t1[16];
-      float yc[16], yr[16];
-      tmem_ld16(tmem_base + lane_addr + kAccC + ncol, t0);
-      tmem_ld16(tmem_base + lane_addr + kCorC + ncol, t1);
-      tmem_wait_ld();
+      const int my = (etile / n_tiles_n) * BM, nx = (etile % n_tiles_n) * BN;
+      if (leader) tma_store_wait_read();      // the previous tile's stores have read the staging buffer
+      ok = epi_sync();
+      if (!ok) break;
 #pragma unroll
-      for (int i = 0; i < 16; ++i) yc[i] = fadd(__uint_as_float(t0[i]), __uint_as_float(t1[i]));
-      tmem_ld16(tmem_base + lane_addr + kAccR + ncol, t0);
-      tmem_ld16(tmem_base + lane_addr + kCorR + ncol, t1);
-      tmem_wait_ld();
-      // the accumulators are in registers now: hand tensor memory back to the MMA issuer
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_acc_free);
+      for (int cq = 0; cq < 8; ++cq) {
+        const int ncol = cq * 8;
+        uint32_t t0[8], t1[8], t2[8], t3[8];
+        tmem_ld8(tmem_base + lane_addr + kAccC + ncol, t0);
+        tmem_ld8(tmem_base + lane_addr + kCorC + ncol, t1);
+        tmem_ld8(tmem_base + lane_addr + kAccR + ncol, t2);
+        tmem_ld8(tmem_base + lane_addr + kCorR + ncol, t3);
+        tmem_wait_ld();
+        if (cq == 7) {
+          // the accumulators are in registers now: hand tensor memory back to the MMA issuers
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_acc_free);
+        }
+        uint8_t* so = base_ptr + SharedLayout::out() + (uint32_t)(cq >> 2) * kOutBoxBytes;
 #pragma unroll
-      for (int i = 0; i < 16; ++i) yr[i] = fadd(__uint_as_float(t0[i]), __uint_as_float(t1[i]));
-      // Output: both tiles are staged in shared memory in the 128-byte-swizzled box layout and
-      // written by TMA, so that global memory sees whole 128-byte lines.  Rows and columns
-      // beyond M and N are clipped by the tensor map.
-      if (ct == 0) tma_store_wait_read();      // the previous tile's stores have read the staging buffer
-      if (!conv_sync()) return false;
-      {
-        uint8_t* so = base_ptr + SharedLayout::out() + (uint32_t)(cq >> 1) * kOutBoxBytes;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
+        for (int q = 0; q < 2; ++q) {
           float lo[4], up[4];
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            lo[i] = fsub(yc[q * 4 + i], yr[q * 4 + i]);
-            up[i] = fadd(yc[q * 4 + i], yr[q * 4 + i]);
+            const float yc = fadd(__uint_as_float(t0[q * 4 + i]), __uint_as_float(t1[q * 4 + i]));
+            const float yr = fadd(__uint_as_float(t2[q * 4 + i]), __uint_as_float(t3[q * 4 + i]));
+            lo[i] = fsub(yc, yr);
+            up[i] = fadd(yc, yr);
             if (bias != nullptr) {
-              const int n = nb + q * 4 + i;
+              const int n = nx + ncol + q * 4 + i;
               const float bv = n < N ? bias[n] : 0.f;
               lo[i] = fadd(lo[i], bv);
               up[i] = fadd(up[i], bv);
             }
           }
-          const uint32_t off = swz(row, (cq & 1) * 4 + q);
+          const uint32_t off = swz(row, (cq & 3) * 2 + q);
           *reinterpret_cast<float4*>(so + off) = make_float4(lo[0], lo[1], lo[2], lo[3]);
           *reinterpret_cast<float4*>(so + 2 * kOutBoxBytes + off) = make_float4(up[0], up[1], up[2], up[3]);
         }
       }
       fence_async_smem();
-      if (!conv_sync()) return false;
-      if (ct == 0) {
+      ok = epi_sync();
+      if (!ok) break;
+      if (leader) {
         // The output tensor map is 3-D.  Plain store: (column, row, 0).  Head-split store
         // (split_rows > 0): the output is [group * heads + head][row in group][feature in head], a
         // 32-column box lies inside one head and its 128 rows inside one group.
-        const int my = (int)(etile / n_tiles_n) * BM, nx = (int)(etile % n_tiles_n) * BN;
         const uint32_t so = base + SharedLayout::out();
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
@@ -532,118 +522,100 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
             cy = my % split_rows;
             cx = cx % split_d;
           }
-#ifndef FBX_NO_STORE
           tma_store_3d(&tm_out_lo, cx, cy, cz, so + q * kOutBoxBytes);
           tma_store_3d(&tm_out_up, cx, cy, cz, so + (2 + q) * kOutBoxBytes);
-#endif
         }
         tma_store_commit();
       }
-      return true;
-    };
-    // need = tile of k-block it-2, kept incrementally (it advances by two per iteration)
-    int need = 0, need_kb = g - 2;
-    for (int it = g; it < total_it && ok; it += 2, need_kb += 2) {
-      // The stores of k-block it wait for the MMAs of k-block it-2.  Those wait for the accumulators
-      // of the tile before theirs to be read out, so the epilogues of all earlier tiles come first.
-      // Both groups run every epilogue, in the same order.
-      while (need_kb >= nkb) { need_kb -= nkb; ++need; }
-      while (ok && epi_tile < need) { ok = epilogue(epi_tile); ++epi_tile; }
-      if (!ok) break;
+    }
+  } else {
+    // ------------------------------------------------- converters
+    // Two groups of eight warps; group g converts the k-blocks it = g (mod 2) into operand stage g
+    // (raw stage g, plane stage g, A buffer g).  The conversion of a k-block is a chain of
+    // latencies (shared-memory loads, arithmetic, tensor-memory stores, barrier hand-overs) longer
+    // than the MMAs of a k-block; with two groups half a period apart the chains overlap.
+    const int cw = warp - kFirstConvWarp;  // 0..15
+    const int g = cw >> 3;             // converter group
+    const int gt = (threadIdx.x - 32 * kFirstConvWarp) & 255;   // thread index inside the group
+    const int quarter = warp & 3;      // TMEM lane quarter this warp may access
+    const int half = (cw >> 2) & 1;    // which 16 of the 32 k values of a block
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    bool ok = true;
+    for (int it = g; it < total_it && ok; it += 2) {
       ok = mbar_wait_warp(bar_full + 8 * g, (uint32_t)((it >> 1) & 1), cta_abort);
       if (!ok) break;
       const uint8_t* raw = base_ptr + SharedLayout::raw(g);
-      uint32_t chi[16], clo[16], rhi[16], rlo[16];
       // W tile: 64 rows x 8 chunks; this thread converts two adjacent chunks of one row
       const int wrow = gt >> 2, wchunk = (gt & 3) * 2;
-      float4 vw[2];
+      float c[16], r[16];
+      uint32_t whi[8], wlo[8];
       {
-        float4 vl[4], vu[4];
+        float4 vl[4], vu[4], vw[2];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const uint32_t off = swz(row, half * 4 + q);
-#ifdef FBX_NO_LDS
-          vl[q] = make_float4((float)off, 1.f, (float)it, 2.f);
-          vu[q] = make_float4((float)row, 3.f, (float)it, 4.f);
-#else
           vl[q] = *reinterpret_cast<const float4*>(raw + off);
           vu[q] = *reinterpret_cast<const float4*>(raw + kTileBytes + off);
-#endif
         }
 #pragma unroll
-        for (int q = 0; q < 2; ++q)
-#ifdef FBX_NO_LDS
-          vw[q] = make_float4((float)wrow, 1.5f, (float)it, -2.f);
-#else
-          vw[q] = *reinterpret_cast<const float4*>(raw + 2 * kTileBytes + swz(wrow, wchunk + q));
-#endif
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_raw_empty + 8 * g);
-        // all arithmetic happens before the wait for the operand stage
+        for (int q = 0; q < 2; ++q) vw[q] = *reinterpret_cast<const float4*>(raw + 2 * kTileBytes + swz(wrow, wchunk + q));
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const float l4[4] = {vl[q].x, vl[q].y, vl[q].z, vl[q].w};
           const float u4[4] = {vu[q].x, vu[q].y, vu[q].z, vu[q].w};
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-#ifdef FBX_NO_ALU
-            chi[q * 4 + i] = clo[q * 4 + i] = __float_as_uint(l4[i]); rhi[q * 4 + i] = rlo[q * 4 + i] = __float_as_uint(u4[i]);
-#else
             // centre (l + u) / 2 and radius (u - l) / 2, each rounded once
             const float hu = fmul(u4[i], 0.5f);
-            split_tf32(__fmaf_rn(l4[i], 0.5f, hu), chi[q * 4 + i], clo[q * 4 + i]);
-            split_tf32(__fmaf_rn(l4[i], -0.5f, hu), rhi[q * 4 + i], rlo[q * 4 + i]);
-#endif
+            c[q * 4 + i] = __fmaf_rn(l4[i], 0.5f, hu);
+            r[q * 4 + i] = __fmaf_rn(l4[i], -0.5f, hu);
           }
         }
-      }
-      uint32_t whi[8], wlo[8], ahi[8], alo[8];
 #pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        const float w4[4] = {vw[q].x, vw[q].y, vw[q].z, vw[q].w};
+        for (int q = 0; q < 2; ++q) {
+          const float w4[4] = {vw[q].x, vw[q].y, vw[q].z, vw[q].w};
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-#ifdef FBX_NO_ALU
-          whi[q * 4 + i] = wlo[q * 4 + i] = ahi[q * 4 + i] = alo[q * 4 + i] = __float_as_uint(w4[i]);
-#else
-          split_tf32(w4[i], whi[q * 4 + i], wlo[q * 4 + i]);
-          // |w| = sgn(w) * (hi + lo); hi and lo both carry the sign of w (lo may be zero)
-          ahi[q * 4 + i] = whi[q * 4 + i] & 0x7fffffffu;
-          alo[q * 4 + i] = wlo[q * 4 + i] & 0x7fffffffu;
-#endif
+          for (int i = 0; i < 4; ++i) split_tf32(w4[i], whi[q * 4 + i], wlo[q * 4 + i]);
         }
       }
-      // pin the converted values in registers here: the compiler would otherwise sink the arithmetic below the wait
+      // The raw stage goes back to the TMA producer only when every value loaded from it has been
+      // used: a shared-memory load completes asynchronously and the hardware only waits for it at
+      // the first instruction that reads its result.  (With the arrive placed directly behind the
+      // loads, k-block it+2 was seen overwriting rows of k-block it that were still being read.)
+      // The empty asm statements keep the arithmetic above from being moved below the arrive.
 #pragma unroll
-      for (int i = 0; i < 16; ++i) asm volatile("" : "+r"(chi[i]), "+r"(clo[i]), "+r"(rhi[i]), "+r"(rlo[i]));
+      for (int i = 0; i < 16; ++i) asm volatile("" : "+f"(c[i]), "+f"(r[i]));
+#pragma unroll
+      for (int i = 0; i < 8; ++i) asm volatile("" : "+r"(whi[i]), "+r"(wlo[i]));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_raw_empty + 8 * g);
       if (it >= 2) {
         ok = mbar_wait_warp(bar_mma_done + 8 * g, (uint32_t)(((it >> 1) - 1) & 1), cta_abort);
         if (!ok) break;
         tc_fence_after();
       }
-      if ((cw & 7) == 0) FBX_T(it, 11);
-      if ((cw & 7) == 5) FBX_T(it, 12);
       {
         const uint32_t a_cols = tmem_base + lane_addr + kABase + (uint32_t)g * 128u + (uint32_t)half * 16u;
-#ifndef FBX_NO_TMEM_ST
-        tmem_st16(a_cols + 0, chi);
-        tmem_st16(a_cols + 32, clo);
-        tmem_st16(a_cols + 64, rhi);
-        tmem_st16(a_cols + 96, rlo);
-#else
-        if (chi[3] == 0x12345u && rlo[5] == 0x777u) *cta_abort = 0;
-#endif
+        uint32_t hi[16], lo[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) split_tf32(c[i], hi[i], lo[i]);
+        tmem_st16(a_cols + 0, hi);
+        tmem_st16(a_cols + 32, lo);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) split_tf32(r[i], hi[i], lo[i]);
+        tmem_st16(a_cols + 64, hi);
+        tmem_st16(a_cols + 96, lo);
         uint8_t* pl = base_ptr + SharedLayout::planes(g);
-#ifdef FBX_NO_STS
-        if (whi[0] == 0x12345u && alo[7] == 0x777u && wlo[1] == 0x999u && ahi[2] == 0x9u)
-#endif
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
           const uint32_t off = swz(wrow, wchunk + q);
+          // |w| = sgn(w) * (hi + lo); hi and lo both carry the sign of w (lo may be zero)
+          const uint32_t m = 0x7fffffffu;
           *reinterpret_cast<uint4*>(pl + 0 * kWTileBytes + off) = make_uint4(whi[q * 4], whi[q * 4 + 1], whi[q * 4 + 2], whi[q * 4 + 3]);
           *reinterpret_cast<uint4*>(pl + 1 * kWTileBytes + off) = make_uint4(wlo[q * 4], wlo[q * 4 + 1], wlo[q * 4 + 2], wlo[q * 4 + 3]);
-          *reinterpret_cast<uint4*>(pl + 2 * kWTileBytes + off) = make_uint4(ahi[q * 4], ahi[q * 4 + 1], ahi[q * 4 + 2], ahi[q * 4 + 3]);
-          *reinterpret_cast<uint4*>(pl + 3 * kWTileBytes + off) = make_uint4(alo[q * 4], alo[q * 4 + 1], alo[q * 4 + 2], alo[q * 4 + 3]);
+          *reinterpret_cast<uint4*>(pl + 2 * kWTileBytes + off) = make_uint4(whi[q * 4] & m, whi[q * 4 + 1] & m, whi[q * 4 + 2] & m, whi[q * 4 + 3] & m);
+          *reinterpret_cast<uint4*>(pl + 3 * kWTileBytes + off) = make_uint4(wlo[q * 4] & m, wlo[q * 4 + 1] & m, wlo[q * 4 + 2] & m, wlo[q * 4 + 3] & m);
         }
       }
       fence_async_smem();   // B planes were written through the generic proxy; the MMA reads them through the async proxy
@@ -651,10 +623,7 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_ops_ready + 8 * g);
-      FBX_T(it, cw & 7);
     }
-    // the tiles whose epilogue has not been triggered by a later conversion
-    while (ok && epi_tile < my_tiles) { ok = epilogue(epi_tile); ++epi_tile; }
   }
   if (threadIdx.x == 32 * kCtrlWarps) tma_store_wait_all();   // this thread issued the bulk stores of the epilogues
   // Tear-down.  On the error path, give outstanding bulk copies time to land before the shared
@@ -769,9 +738,6 @@ int launch_split_sign_tc(const float* a_lo, const float* a_up, const float* W, c
 
 // Reads (and clears) the device-side flag that the tensor-core GEMM raises when one of its bounded
 // waits expires.  Synchronises the device.
-#ifdef FBX_TRACE
-extern "C" void fb_tc_trace(long long* out) { cudaMemcpyFromSymbol(out, fb::g_trace, sizeof(long long) * 64 * 16); }
-#endif
 extern "C" int fb_tc_error_flag(int* flag) {
   if (!flag) return FB_ERR_ARG;
   int v = 0;

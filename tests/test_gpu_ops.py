@@ -156,6 +156,32 @@ def test_matmul_shapes(shape, Dy):
     _cmp(g, o, "dense %s->%d" % (shape, Dy), rtol=1e-5, atol=2e-6)
 
 
+def test_matmul_tensor_core_stage_reuse_is_race_free():
+    """Every k-block contributes a distinct power of two, so the exact result tells which k-block's
+    data each product saw; repeated launches must agree bit for bit.  K = 512 walks each
+    shared-memory / tensor-memory stage eight times (a release of a raw stage ahead of the
+    completion of the loads from it showed up here as rows that carried the data of k-block it+2)."""
+    from faith_b200 import ops
+    rows, Di, Do, Dy = 16, 128, 512, 512
+    kb = torch.arange(Do, device=DEV) // 32
+    x = (2.0 ** kb.float()).expand(1, rows, Di, Do).contiguous()
+    zb = torch.zeros(1, rows, Do, device=DEV)
+    W = torch.ones(Dy, Do, device=DEV)
+    expect = 32.0 * (2 ** (Do // 32) - 1)
+    for _ in range(10):
+        y_lw, y_uw, y_lb, y_ub = ops.matmul(x, x, zb, zb, W, None)
+        assert bool((y_lw == expect).all()) and bool((y_uw == expect).all())
+    g0 = torch.Generator().manual_seed(11)
+    lw = torch.randn(1, rows, Di, Do, generator=g0).to(DEV)
+    uw = lw + torch.rand(1, rows, Di, Do, generator=g0).to(DEV)
+    Wr = (torch.randn(Dy, Do, generator=g0) / math.sqrt(Do)).to(DEV)
+    first = ops.matmul(lw, uw, zb, zb, Wr, None)
+    for _ in range(10):
+        again = ops.matmul(lw, uw, zb, zb, Wr, None)
+        for a, b in zip(first, again):
+            assert torch.equal(a, b)
+
+
 def test_matmul_identity_input():
     """First-layer case: lw = uw = one-hot rows, so every output is a single product 1 * w.  The
     CUDA-core kernel reproduces the reference bit for bit; the tensor-core kernel carries the
