@@ -15,6 +15,9 @@
 // part and one for the weight part.
 #include <mutex>
 
+#include <cstdlib>
+#include <cstring>
+
 #include "common.cuh"
 
 namespace fb {
@@ -298,6 +301,26 @@ dot_weight_transposed(const float* __restrict__ x_lw, const float* __restrict__ 
 }  // namespace
 }  // namespace fb
 
+namespace fb {
+// dot_product_tc.cu
+bool dot_tc_supported(const float* x_lw, const float* x_uw, const float* y_lw, const float* y_uw, const float* x_l,
+                      const float* y_l, const float* y_u, const float* z_lw, const float* z_uw, int B, int Lx, int Ly,
+                      int Di, int K, int heads);
+int launch_dot_weight_tc(const float* x_lw, const float* x_uw, const float* y_lw, const float* y_uw, const float* x_l,
+                         const float* y_l, const float* y_u, float* z_lw, float* z_uw, int B, int Lx, int Ly, int Di,
+                         float out_scale, int heads, cudaStream_t st);
+namespace {
+// FB_DOT_IMPL=ffma in the environment keeps the dot product on the CUDA-core kernels (exact fp32 products)
+bool dot_force_cuda_cores() {
+  static const bool v = [] {
+    const char* e = getenv("FB_DOT_IMPL");
+    return e != nullptr && strcmp(e, "ffma") == 0;
+  }();
+  return v;
+}
+}  // namespace
+}  // namespace fb
+
 using namespace fb;
 
 extern "C" int fb_dot_product_heads_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
@@ -333,6 +356,11 @@ extern "C" int fb_dot_product_heads_f32(const float* x_lw, const float* x_uw, co
     dot_bias_kernel<<<(unsigned)(want < cap ? want : cap), kThreads, 0, st>>>(x_lb, x_ub, y_lb, y_ub, x_l, y_l, y_u,
                                                                                z_lb, z_ub, total, Lx, Ly, K, out_scale, merge_heads);
     FB_LAUNCH_OK();
+  }
+  if (layout == FB_NATIVE && !dot_force_cuda_cores() &&
+      dot_tc_supported(x_lw, x_uw, y_lw, y_uw, x_l, y_l, y_u, z_lw, z_uw, B, Lx, Ly, Di, K, merge_heads)) {
+    // attention shapes: tensor-core kernel
+    return launch_dot_weight_tc(x_lw, x_uw, y_lw, y_uw, x_l, y_l, y_u, z_lw, z_uw, B, Lx, Ly, Di, out_scale, merge_heads, st);
   }
   if (layout == FB_NATIVE) {
     const int n_it = (int)ceil_div(Lx, TI), n_jt = (int)ceil_div(Ly, TJ), n_mt = (int)ceil_div(Di, TM);

@@ -135,6 +135,41 @@ def test_unwritten_outputs_are_detected():
         assert bool(torch.isfinite(v).all())
 
 
+def test_dot_product_tensor_core_shapes_match_fp64_and_repeat():
+    """Attention shapes (K = 32, Ly = 32, Lx a multiple of 32, Di a multiple of 4) take the tcgen05
+    kernel.  The weight part is checked against an fp64 evaluation of the centre/radius formula
+    (tolerance: the per-operator bar with the absolute part scaled to the size of the summed terms)
+    and repeated launches must agree bit for bit."""
+    from faith_b200 import ops
+    for B, Lx, Di in ((8, 32, 128), (4, 64, 64), (3, 32, 12)):
+        g0 = torch.Generator().manual_seed(17 + B)
+        def mk(L):
+            lw = torch.randn(B, L, Di, 32, generator=g0) * 0.3
+            uw = lw + torch.rand(B, L, Di, 32, generator=g0) * 0.1
+            lb = torch.randn(B, L, 32, generator=g0)
+            ub = lb + torch.rand(B, L, 32, generator=g0) * 0.1
+            return [t.to(DEV) for t in (lw, uw, lb, ub)]
+        x, y = mk(Lx), mk(32)
+        first = ops.dot_product(x, y, float("inf"), 0.01, 1, 0.25)
+        for _ in range(5):
+            again = ops.dot_product(x, y, float("inf"), 0.01, 1, 0.25)
+            for a, b in zip(first, again):
+                assert torch.equal(a, b)
+        X = [t.double() for t in x]
+        Y = [t.double() for t in y]
+        xl = X[2] - 0.01 * X[0].abs().sum(2)
+        yl = Y[2] - 0.01 * Y[0].abs().sum(2)
+        yu = Y[3] + 0.01 * Y[1].abs().sum(2)
+        xc, xr, yc, yr = (X[0] + X[1]) / 2, (X[1] - X[0]) / 2, (Y[0] + Y[1]) / 2, (Y[1] - Y[0]) / 2
+        P = torch.einsum("bjmk,bik->bimj", yc, xl)
+        Q = torch.einsum("bjmk,bik->bimj", yr, xl.abs())
+        zl = torch.einsum("bimk,bjk->bimj", xc, yl) - torch.einsum("bimk,bjk->bimj", xr, yl.abs()) + P - Q
+        zu = torch.einsum("bimk,bjk->bimj", xc, yu) + torch.einsum("bimk,bjk->bimj", xr, yu.abs()) + P + Q
+        for got, ref in ((first[0], zl * 0.25), (first[1], zu * 0.25)):
+            err = (got.double() - ref).abs()
+            assert bool((err <= 4e-6 + 1e-5 * ref.abs()).all()), float(err.max())
+
+
 # ------------------------------------------------------------------ matmul
 @pytest.mark.parametrize("shape,Dy", [((1, 2, 64, 64), 64), ((1, 16, 64, 64), 128), ((2, 8, 128, 256), 512),
                                       ((1, 3, 24, 20), 7), ((1, 5, 33, 130), 129), ((1, 4, 64, 128), 2),
