@@ -77,6 +77,71 @@ dot_bias_kernel(const float* __restrict__ x_lb, const float* __restrict__ x_ub, 
   }
 }
 
+// Tiled version of the bias part: one block per (b, 32 i, 32 j) tile; the seven row tiles are staged
+// in shared memory (row stride 33 floats: conflict-free both for the row-wise fill and for the
+// column-wise reads), K in chunks of 32; thread (i, jq) owns the outputs (i, jq + 8 c), c = 0..3.
+// Same partial sums and the same final order of additions as dot_bias_kernel.
+__global__ void __launch_bounds__(kThreads)
+dot_bias_tiled(const float* __restrict__ x_lb, const float* __restrict__ x_ub, const float* __restrict__ y_lb,
+               const float* __restrict__ y_ub, const float* __restrict__ x_l, const float* __restrict__ y_l,
+               const float* __restrict__ y_u, float* __restrict__ z_lb, float* __restrict__ z_ub,
+               int Lx, int Ly, int K, int n_it, int n_jt, float out_scale, int heads) {
+  __shared__ float sm[7][32][33];   // x_lb, x_ub, x_l, y_lb, y_ub, y_l, y_u
+  int w = blockIdx.x;
+  const int jt = w % n_jt; w /= n_jt;
+  const int it = w % n_it;
+  const int64_t b = w / n_it;
+  const int i0 = it * 32, j0 = jt * 32;
+  const int tid = threadIdx.x, ti = tid >> 3, tj = tid & 7;
+  float gl[4], gu[4], l1[4], l2[4], l3[4], l4[4], u1[4], u2[4], u3[4], u4[4];
+#pragma unroll
+  for (int c = 0; c < 4; ++c) gl[c] = gu[c] = l1[c] = l2[c] = l3[c] = l4[c] = u1[c] = u2[c] = u3[c] = u4[c] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += 32) {
+    const float* src[7] = {x_lb, x_ub, x_l, y_lb, y_ub, y_l, y_u};
+#pragma unroll
+    for (int a = 0; a < 7; ++a) {
+      const bool isx = a < 3;
+      const int L = isx ? Lx : Ly, r0 = isx ? i0 : j0;
+      for (int f = tid; f < 32 * 32; f += kThreads) {
+        const int r = f >> 5, k = f & 31;
+        const bool ok = r0 + r < L && k0 + k < K;
+        sm[a][r][k] = ok ? src[a][((int64_t)b * L + r0 + r) * K + k0 + k] : 0.f;
+      }
+    }
+    __syncthreads();
+#pragma unroll 4
+    for (int k = 0; k < 32; ++k) {
+      const float xl = sm[0][ti][k], xu = sm[1][ti][k], lx = sm[2][ti][k];
+      const float lxp = lx > 0.f ? lx : 0.f, lxn = lx < 0.f ? lx : 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int j = tj + 8 * c;
+        const float yl = sm[3][j][k], yu = sm[4][j][k], ly = sm[5][j][k], uy = sm[6][j][k];
+        const float lyp = ly > 0.f ? ly : 0.f, lyn = ly < 0.f ? ly : 0.f;
+        const float uyp = uy > 0.f ? uy : 0.f, uyn = uy < 0.f ? uy : 0.f;
+        gl[c] = fadd(gl[c], fmul(-ly, lx));
+        gu[c] = fadd(gu[c], fmul(-uy, lx));
+        l1[c] = fmaf(xl, lyp, l1[c]); l2[c] = fmaf(xu, lyn, l2[c]); l3[c] = fmaf(yl, lxp, l3[c]); l4[c] = fmaf(yu, lxn, l4[c]);
+        u1[c] = fmaf(xu, uyp, u1[c]); u2[c] = fmaf(xl, uyn, u2[c]); u3[c] = fmaf(yu, lxp, u3[c]); u4[c] = fmaf(yl, lxn, u4[c]);
+      }
+    }
+    __syncthreads();
+  }
+  const int i = i0 + ti;
+  if (i < Lx) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int j = j0 + tj + 8 * c;
+      if (j < Ly) {
+        // heads > 1: head-merged output [S, Lx, heads * Ly]
+        const int64_t od = (((b / heads) * Lx + i) * heads + b % heads) * Ly + j;
+        z_lb[od] = fmul(fadd(fadd(fadd(fadd(gl[c], l1[c]), l2[c]), l3[c]), l4[c]), out_scale);
+        z_ub[od] = fmul(fadd(fadd(fadd(fadd(gu[c], u1[c]), u2[c]), u3[c]), u4[c]), out_scale);
+      }
+    }
+  }
+}
+
 // ------------------------------------------------- weight part, native layout
 // x [B, Lx, Di, K], y [B, Ly, Di, K] -> z [B, Lx, Di, Ly].
 // Block tile: TI = 32 rows of x, TJ = 32 rows of y, TM = 4 symbolic coordinates, K in chunks of
@@ -350,11 +415,18 @@ extern "C" int fb_dot_product_heads_f32(const float* x_lw, const float* x_uw, co
   rc = fb_concretize_f32(y_lw, y_uw, y_lb, y_ub, y_l, y_u, (int64_t)B * Ly, Di, K, words, p, eps, layout, stream);
   if (rc != FB_OK) return rc;
   {
-    const int64_t total = (int64_t)B * Lx * Ly;
-    const int64_t want = ceil_div(total, kThreads / 32);
-    const int64_t cap = (int64_t)device_info().sms * 32;
-    dot_bias_kernel<<<(unsigned)(want < cap ? want : cap), kThreads, 0, st>>>(x_lb, x_ub, y_lb, y_ub, x_l, y_l, y_u,
-                                                                               z_lb, z_ub, total, Lx, Ly, K, out_scale, merge_heads);
+    const int n_it = (int)ceil_div(Lx, 32), n_jt = (int)ceil_div(Ly, 32);
+    const int64_t blocks = (int64_t)B * n_it * n_jt;
+    if (blocks <= 0x7fffffff) {
+      dot_bias_tiled<<<(unsigned)blocks, kThreads, 0, st>>>(x_lb, x_ub, y_lb, y_ub, x_l, y_l, y_u, z_lb, z_ub, Lx, Ly, K,
+                                                           n_it, n_jt, out_scale, merge_heads);
+    } else {
+      const int64_t total = (int64_t)B * Lx * Ly;
+      const int64_t want = ceil_div(total, kThreads / 32);
+      const int64_t cap = (int64_t)device_info().sms * 32;
+      dot_bias_kernel<<<(unsigned)(want < cap ? want : cap), kThreads, 0, st>>>(x_lb, x_ub, y_lb, y_ub, x_l, y_l, y_u,
+                                                                                 z_lb, z_ub, total, Lx, Ly, K, out_scale, merge_heads);
+    }
     FB_LAUNCH_OK();
   }
   if (layout == FB_NATIVE && !dot_force_cuda_cores() &&
