@@ -3,19 +3,19 @@
 // evaluated in centre/radius form like the FFMA GEMM:
 //   c = (x_lw + x_uw)/2, r = (x_uw - x_lw)/2, y_c = conv(c, W), y_r = conv(r, |W|),
 //   y_lw = y_c - y_r, y_uw = y_c + y_r.
-// Direct convolution on CUDA cores: a block owns one image, an 8 x 32 tile of output pixels and
-// 16 output channels; input channels are staged through shared memory four at a time (centre
-// and radius planes with halo), the weights of the chunk are broadcast from shared memory.
+// Direct convolution on CUDA cores: a block owns one image, a TH x TW tile of output pixels
+// (8 x 32, or 16 x 16 for narrow outputs such as the 16 x 16 map of a stride-2 layer) and CO
+// output channels (16 or 32); input channels are staged through shared memory four at a time
+// (centre and radius planes with halo), the weights of the chunk are broadcast from shared memory.
 #include "common.cuh"
 
 namespace fb {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int TH = 8, TW = 32;   // output tile
-constexpr int CO = 16;           // output channels per block
 constexpr int CC = 4;            // input channels per shared-memory stage
 
+template <int TH, int TW, int CO>
 __global__ void __launch_bounds__(kThreads)
 conv_bounds_kernel(const float* __restrict__ x_lo, const float* __restrict__ x_up, const float* __restrict__ Wt,
                    const float* __restrict__ bias, float* __restrict__ y_lo, float* __restrict__ y_up,
@@ -34,7 +34,7 @@ conv_bounds_kernel(const float* __restrict__ x_lo, const float* __restrict__ x_u
   const int cq = (int)(bid % co_chunks); bid /= co_chunks;
   const int64_t n = bid;  // image index
   const int tid = threadIdx.x;
-  const int tw = tid & 31, th = tid >> 5;
+  const int tw = tid % TW, th = tid / TW;
   const int oh = th_i * TH + th, ow = tw_i * TW + tw;
   const int ih0 = th_i * TH * stride - pad, iw0 = tw_i * TW * stride - pad;
   const int co0 = cq * CO;
@@ -98,10 +98,11 @@ conv_bounds_kernel(const float* __restrict__ x_lo, const float* __restrict__ x_u
   }
 }
 
-int launch_conv(const float* x_lo, const float* x_up, const float* Wt, const float* bias, float* y_lo, float* y_up,
-                int64_t N, int Cin, int H, int W, int Cout, int Kh, int Kw, int stride, int pad, int Ho, int Wo,
-                cudaStream_t st) {
-  if (N == 0) return FB_OK;
+template <int TH, int TW, int CO>
+int launch_conv_t(const float* x_lo, const float* x_up, const float* Wt, const float* bias, float* y_lo, float* y_up,
+                  int64_t N, int Cin, int H, int W, int Cout, int Kh, int Kw, int stride, int pad, int Ho, int Wo,
+                  cudaStream_t st) {
+  static_assert(TH * TW == kThreads, "one thread per output pixel of the tile");
   const int in_h = (TH - 1) * stride + Kh, in_w = (TW - 1) * stride + Kw;
   const size_t smem = sizeof(float) * ((size_t)2 * CC * in_h * in_w + (size_t)CC * Kh * Kw * CO);
   if (smem > (size_t)device_info().smem_optin) return FB_ERR_SHAPE;
@@ -109,11 +110,23 @@ int launch_conv(const float* x_lo, const float* x_up, const float* Wt, const flo
   const int64_t blocks = N * co_chunks * tiles_h * tiles_w;
   if (blocks > 0x7fffffff) return FB_ERR_SHAPE;
   if (smem > 48 * 1024)
-    FB_CUDA_OK(cudaFuncSetAttribute(conv_bounds_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  conv_bounds_kernel<<<(unsigned)blocks, kThreads, smem, st>>>(x_lo, x_up, Wt, bias, y_lo, y_up, Cin, H, W, Cout, Kh,
-                                                               Kw, stride, pad, Ho, Wo, tiles_h, tiles_w, co_chunks);
+    FB_CUDA_OK(cudaFuncSetAttribute(conv_bounds_kernel<TH, TW, CO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  conv_bounds_kernel<TH, TW, CO><<<(unsigned)blocks, kThreads, smem, st>>>(x_lo, x_up, Wt, bias, y_lo, y_up, Cin, H, W, Cout,
+                                                                         Kh, Kw, stride, pad, Ho, Wo, tiles_h, tiles_w,
+                                                                         co_chunks);
   FB_LAUNCH_OK();
   return FB_OK;
+}
+
+int launch_conv(const float* x_lo, const float* x_up, const float* Wt, const float* bias, float* y_lo, float* y_up,
+                int64_t N, int Cin, int H, int W, int Cout, int Kh, int Kw, int stride, int pad, int Ho, int Wo,
+                cudaStream_t st) {
+  if (N == 0) return FB_OK;
+  const bool narrow = Wo <= 16, wide_co = Cout > 16;
+#define FB_CONV_ARGS x_lo, x_up, Wt, bias, y_lo, y_up, N, Cin, H, W, Cout, Kh, Kw, stride, pad, Ho, Wo, st
+  if (narrow) return wide_co ? launch_conv_t<16, 16, 32>(FB_CONV_ARGS) : launch_conv_t<16, 16, 16>(FB_CONV_ARGS);
+  return wide_co ? launch_conv_t<8, 32, 32>(FB_CONV_ARGS) : launch_conv_t<8, 32, 16>(FB_CONV_ARGS);
+#undef FB_CONV_ARGS
 }
 
 }  // namespace

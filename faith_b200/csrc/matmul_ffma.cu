@@ -214,12 +214,84 @@ split_sign_gemv_rows(const float* __restrict__ a_lo, const float* __restrict__ a
   }
 }
 
+// Narrow outputs with a long contraction (e.g. the 8192 -> 10 head of the CNN): a block owns eight
+// rows of A (one per warp) and walks K in chunks of 512; the chunk of W is staged in shared memory
+// once per block and read by all eight warps, the rows of A are read with 128-bit loads.
+constexpr int kGemvChunk = 512;
+template <int NMAX>
+__global__ void __launch_bounds__(kThreads)
+split_sign_gemv_tiled(const float* __restrict__ a_lo, const float* __restrict__ a_up,
+                      const float* __restrict__ W, const float* __restrict__ bias,
+                      float* __restrict__ c_lo, float* __restrict__ c_up, int64_t M, int N, int K) {
+  __shared__ __align__(16) float sw[NMAX][kGemvChunk];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t m = (int64_t)blockIdx.x * (kThreads / 32) + warp;
+  float sc[NMAX], sr[NMAX];
+#pragma unroll
+  for (int n = 0; n < NMAX; ++n) { sc[n] = 0.f; sr[n] = 0.f; }
+  for (int k0 = 0; k0 < K; k0 += kGemvChunk) {
+    const int kc = min(kGemvChunk, K - k0);   // multiple of 4
+    for (int f = threadIdx.x; f < NMAX * (kGemvChunk / 4); f += kThreads) {
+      const int n = f / (kGemvChunk / 4), k4 = (f % (kGemvChunk / 4)) * 4;
+      float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (n < N && k4 < kc) w = *reinterpret_cast<const float4*>(W + (int64_t)n * K + k0 + k4);
+      *reinterpret_cast<float4*>(&sw[n][k4]) = w;
+    }
+    __syncthreads();
+    if (m < M) {
+      for (int k4 = lane * 4; k4 < kc; k4 += 128) {
+        const float4 lo = *reinterpret_cast<const float4*>(a_lo + m * K + k0 + k4);
+        const float4 up = *reinterpret_cast<const float4*>(a_up + m * K + k0 + k4);
+        const float c[4] = {fmul(fadd(lo.x, up.x), 0.5f), fmul(fadd(lo.y, up.y), 0.5f), fmul(fadd(lo.z, up.z), 0.5f), fmul(fadd(lo.w, up.w), 0.5f)};
+        const float r[4] = {fmul(fsub(up.x, lo.x), 0.5f), fmul(fsub(up.y, lo.y), 0.5f), fmul(fsub(up.z, lo.z), 0.5f), fmul(fsub(up.w, lo.w), 0.5f)};
+#pragma unroll
+        for (int n = 0; n < NMAX; ++n) {
+          if (n < N) {
+            const float4 w = *reinterpret_cast<const float4*>(&sw[n][k4]);
+            sc[n] = fmaf(c[0], w.x, sc[n]); sr[n] = fmaf(r[0], fabsf(w.x), sr[n]);
+            sc[n] = fmaf(c[1], w.y, sc[n]); sr[n] = fmaf(r[1], fabsf(w.y), sr[n]);
+            sc[n] = fmaf(c[2], w.z, sc[n]); sr[n] = fmaf(r[2], fabsf(w.z), sr[n]);
+            sc[n] = fmaf(c[3], w.w, sc[n]); sr[n] = fmaf(r[3], fabsf(w.w), sr[n]);
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  if (m >= M) return;
+#pragma unroll
+  for (int n = 0; n < NMAX; ++n) {
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) {
+      sc[n] += __shfl_xor_sync(0xffffffffu, sc[n], s);
+      sr[n] += __shfl_xor_sync(0xffffffffu, sr[n], s);
+    }
+  }
+  if (lane == 0) {
+#pragma unroll
+    for (int n = 0; n < NMAX; ++n) {
+      if (n < N) {
+        float lo = fsub(sc[n], sr[n]), up = fadd(sc[n], sr[n]);
+        if (bias != nullptr) { lo = fadd(lo, bias[n]); up = fadd(up, bias[n]); }
+        c_lo[m * N + n] = lo;
+        c_up[m * N + n] = up;
+      }
+    }
+  }
+}
+
 }  // namespace
 
 // One split-sign GEMM: (a_lo, a_up) [M, K] x W[N, K]^T (+ bias) -> (c_lo, c_up) [M, N].
 int launch_split_sign_ffma(const float* a_lo, const float* a_up, const float* W, const float* bias, float* c_lo,
                            float* c_up, int64_t M, int N, int K, cudaStream_t st, int split_rows, int split_d) {
   if (M == 0 || N == 0) return FB_OK;
+  if (N <= 16 && split_rows == 0 && K >= 1024 && K % 4 == 0 && aligned16(a_lo) && aligned16(a_up) && aligned16(W) &&
+      ceil_div(M, kThreads / 32) <= 0x7fffffff) {
+    split_sign_gemv_tiled<16><<<(unsigned)ceil_div(M, kThreads / 32), kThreads, 0, st>>>(a_lo, a_up, W, bias, c_lo, c_up, M, N, K);
+    FB_LAUNCH_OK();
+    return FB_OK;
+  }
   if (N <= 16 && split_rows == 0) {
     const int64_t want = ceil_div(M, kThreads / 32);
     const int64_t cap = (int64_t)device_info().sms * 16;
