@@ -17,7 +17,7 @@
 //
 // One CTA computes a 128 x 64 tile of both outputs (four accumulators of 64 columns and two
 // operand buffers of 128 columns fill the 512 columns of tensor memory, which is what limits the
-// tile to 64 columns).  K is walked in blocks of 32.  Warp roles (24 warps):
+// tile to 64 columns).  K is walked in blocks of 32.  Warp roles (28 warps):
 //   warp 0       TMA producer: raw fp32 tiles of x_lw, x_uw (128 rows x 32) and of W (64 rows x 32)
 //                into a two-stage shared-memory ring (128-byte swizzle).
 //   warps 1-3    MMA issuers, one per accumulator set (main centre + main radius / centre
@@ -25,10 +25,10 @@
 //                thread sustains one MMA per 50-110 cycles whatever its size (measured), a
 //                128 x 64 x 8 MMA occupies the tensor core for 32: three issuers keep it fed, and
 //                as no accumulator is shared between them they need no order among themselves.
-//   warps 4-7    epilogue, one warp per tensor-memory lane quarter: tcgen05.ld the accumulators,
+//   warps 4-11   epilogue, two warps per tensor-memory lane quarter (32 columns each): tcgen05.ld the accumulators,
 //                y_c -/+ y_r (+ bias), stage the two output tiles in shared memory (swizzled) and
 //                write them with TMA stores (full 128-byte lines).
-//   warps 8-23   converters, two groups of eight; group g handles the k-blocks it = g (mod 2):
+//   warps 12-27  converters, two groups of eight; group g handles the k-blocks it = g (mod 2):
 //                read the raw tiles, form c, r, split hi/lo, and
 //                - store the four A planes (c_hi, c_lo, r_hi, r_lo) of the block into TENSOR MEMORY
 //                  (tcgen05.st; the A operand of the MMAs comes from TMEM, lane = tile row),
@@ -59,7 +59,7 @@ constexpr int kGroupWarps = 8;                           // converter warps per 
 constexpr int kConvGroups = 2;                           // group g converts the k-blocks it = g (mod 2)
 constexpr int kConvWarps = kConvGroups * kGroupWarps;
 constexpr int kIssuers = 3;                              // MMA-issuing warps, each owning accumulators of its own
-constexpr int kEpiWarps = 4;                             // epilogue warps, one per tensor-memory lane quarter
+constexpr int kEpiWarps = 8;                             // epilogue warps: 4 tensor-memory lane quarters x 2 column halves
 constexpr int kCtrlWarps = 1 + kIssuers;                 // TMA producer + issuers
 constexpr int kFirstConvWarp = kCtrlWarps + kEpiWarps;
 constexpr int kThreads = 32 * (kFirstConvWarp + kConvWarps);
@@ -250,8 +250,8 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
       }
     }
   } else if (warp < kFirstConvWarp) {
-    // ------------------------------------------------------------------ epilogue (warps 4-7)
-    // Warp q reads rows q*32.. of the four accumulators, 8 columns at a time, combines them
+    // ------------------------------------------------------------------ epilogue (warps 4-11)
+    // Warp (q, h) reads rows q*32.. and columns h*32.. of the four accumulators, 8 columns at a time, combines them
     // (y_c -/+ y_r, + bias), stages the two output tiles in shared memory in the 128-byte-swizzled
     // box layout and has them written by TMA, so that global memory sees whole 128-byte lines.
     // Rows and columns beyond M and N are clipped by the tensor map.  The accumulators are handed
@@ -271,17 +271,20 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
       ++epi_phase;
       return r;
     };
+    const int chalf = (warp - kCtrlWarps) >> 2;   // which 32 of the 64 tile columns (= which output box)
     for (int e = 0; e < my_tiles && ok; ++e) {
+      // the staging buffer is free once the previous tile's stores have read it: settle that before
+      // the accumulators become ready, so that nothing stands between "ready" and the read-out
+      if (leader) tma_store_wait_read();
+      ok = epi_sync();
+      if (!ok) break;
       ok = mbar_wait_warp(bar_acc_ready, (uint32_t)(e & 1), cta_abort);
       if (!ok) break;
       tc_fence_after();
       const int etile = blockIdx.x + e * gridDim.x;
       const int my = (etile / n_tiles_n) * BM, nx = (etile % n_tiles_n) * BN;
-      if (leader) tma_store_wait_read();      // the previous tile's stores have read the staging buffer
-      ok = epi_sync();
-      if (!ok) break;
 #pragma unroll
-      for (int cq = 0; cq < 8; ++cq) {
+      for (int cq = 4 * chalf; cq < 4 * chalf + 4; ++cq) {
         const int ncol = cq * 8;
         uint32_t t0[8], t1[8], t2[8], t3[8];
         tmem_ld8(tmem_base + lane_addr + kAccC + ncol, t0);
@@ -289,7 +292,7 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
         tmem_ld8(tmem_base + lane_addr + kAccR + ncol, t2);
         tmem_ld8(tmem_base + lane_addr + kCorR + ncol, t3);
         tmem_wait_ld();
-        if (cq == 7) {
+        if (cq == 4 * chalf + 3) {
           // the accumulators are in registers now: hand tensor memory back to the MMA issuers
           tc_fence_before();
           __syncwarp();
