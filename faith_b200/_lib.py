@@ -41,6 +41,7 @@ SIGNATURES = {
     "fb_dot_product_f32": [_P] * 16 + [_I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P],
     "fb_matmul_heads_f32": [_P] * 10 + [_L, _I, _I, _I, _I, _I, _P],
     "fb_dot_product_heads_f32": [_P] * 16 + [_I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _P],
+    "fb_context_heads_f32": [_P] * 16 + [_I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P],
     "fb_dot_product_noalloc_f32": [_P] * 12 + [_I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P],
     "fb_dot_product_noalloc_max_floats": [],
     "fb_mul_bounds_f32": [_P] * 12 + [_L, _I, _I, _I, _I, _F, _P],

@@ -85,7 +85,7 @@ __global__ void __launch_bounds__(kThreads)
 dot_bias_tiled(const float* __restrict__ x_lb, const float* __restrict__ x_ub, const float* __restrict__ y_lb,
                const float* __restrict__ y_ub, const float* __restrict__ x_l, const float* __restrict__ y_l,
                const float* __restrict__ y_u, float* __restrict__ z_lb, float* __restrict__ z_ub,
-               int Lx, int Ly, int K, int n_it, int n_jt, float out_scale, int heads) {
+               int Lx, int Ly, int K, int n_it, int n_jt, float out_scale, int heads, int y_kmajor) {
   __shared__ float sm[7][32][33];   // x_lb, x_ub, x_l, y_lb, y_ub, y_l, y_u
   int w = blockIdx.x;
   const int jt = w % n_jt; w /= n_jt;
@@ -105,7 +105,10 @@ dot_bias_tiled(const float* __restrict__ x_lb, const float* __restrict__ x_ub, c
       for (int f = tid; f < 32 * 32; f += kThreads) {
         const int r = f >> 5, k = f & 31;
         const bool ok = r0 + r < L && k0 + k < K;
-        sm[a][r][k] = ok ? src[a][((int64_t)b * L + r0 + r) * K + k0 + k] : 0.f;
+        // y_kmajor: y_lb / y_ub (a = 3, 4) are stored [b, k, j] instead of [b, j, k]
+        const bool km = y_kmajor && (a == 3 || a == 4);
+        const int64_t idx = km ? ((int64_t)b * K + k0 + k) * L + r0 + r : ((int64_t)b * L + r0 + r) * K + k0 + k;
+        sm[a][r][k] = ok ? src[a][idx] : 0.f;
       }
     }
     __syncthreads();
@@ -373,7 +376,7 @@ bool dot_tc_supported(const float* x_lw, const float* x_uw, const float* y_lw, c
                       int Di, int K, int heads);
 int launch_dot_weight_tc(const float* x_lw, const float* x_uw, const float* y_lw, const float* y_uw, const float* x_l,
                          const float* y_l, const float* y_u, float* z_lw, float* z_uw, int B, int Lx, int Ly, int Di,
-                         float out_scale, int heads, cudaStream_t st);
+                         float out_scale, int heads, int y_kmajor, cudaStream_t st);
 namespace {
 // FB_DOT_IMPL=ffma in the environment keeps the dot product on the CUDA-core kernels (exact fp32 products)
 bool dot_force_cuda_cores() {
@@ -419,7 +422,7 @@ extern "C" int fb_dot_product_heads_f32(const float* x_lw, const float* x_uw, co
     const int64_t blocks = (int64_t)B * n_it * n_jt;
     if (blocks <= 0x7fffffff) {
       dot_bias_tiled<<<(unsigned)blocks, kThreads, 0, st>>>(x_lb, x_ub, y_lb, y_ub, x_l, y_l, y_u, z_lb, z_ub, Lx, Ly, K,
-                                                           n_it, n_jt, out_scale, merge_heads);
+                                                           n_it, n_jt, out_scale, merge_heads, 0);
     } else {
       const int64_t total = (int64_t)B * Lx * Ly;
       const int64_t want = ceil_div(total, kThreads / 32);
@@ -432,7 +435,7 @@ extern "C" int fb_dot_product_heads_f32(const float* x_lw, const float* x_uw, co
   if (layout == FB_NATIVE && !dot_force_cuda_cores() &&
       dot_tc_supported(x_lw, x_uw, y_lw, y_uw, x_l, y_l, y_u, z_lw, z_uw, B, Lx, Ly, Di, K, merge_heads)) {
     // attention shapes: tensor-core kernel
-    return launch_dot_weight_tc(x_lw, x_uw, y_lw, y_uw, x_l, y_l, y_u, z_lw, z_uw, B, Lx, Ly, Di, out_scale, merge_heads, st);
+    return launch_dot_weight_tc(x_lw, x_uw, y_lw, y_uw, x_l, y_l, y_u, z_lw, z_uw, B, Lx, Ly, Di, out_scale, merge_heads, 0, st);
   }
   if (layout == FB_NATIVE) {
     const int n_it = (int)ceil_div(Lx, TI), n_jt = (int)ceil_div(Ly, TJ), n_mt = (int)ceil_div(Di, TM);
@@ -476,6 +479,66 @@ extern "C" int fb_dot_product_f32(const float* x_lw, const float* x_uw, const fl
                                   float out_scale, int layout, void* stream) {
   return fb_dot_product_heads_f32(x_lw, x_uw, x_lb, x_ub, y_lw, y_uw, y_lb, y_ub, z_lw, z_uw, z_lb, z_ub, x_l, x_u, y_l,
                                   y_u, B, Lx, Ly, Di, K, words, p, eps, out_scale, layout, 1, stream);
+}
+
+namespace fb {
+namespace {
+// In-place transposition of [B][R][C] -> [B][C][R] for small matrices (R * C <= 4096): one block per b.
+__global__ void __launch_bounds__(256) transpose_small_inplace(float* a, float* b2, int R, int C) {
+  __shared__ float t[2][4096];
+  float* pa = a + (int64_t)blockIdx.x * R * C;
+  float* pb = b2 + (int64_t)blockIdx.x * R * C;
+  for (int f = threadIdx.x; f < R * C; f += 256) { t[0][f] = pa[f]; t[1][f] = pb[f]; }
+  __syncthreads();
+  for (int f = threadIdx.x; f < R * C; f += 256) {
+    const int c = f / R, r = f % R;      // output element (c, r)
+    pa[f] = t[0][r * C + c];
+    pb[f] = t[1][r * C + c];
+  }
+}
+}  // namespace
+}  // namespace fb
+
+// Context product of the attention block (Bounds.context, Bounds.py:843-850: dot_product with V.t()) that
+// takes the values as the projection writes them, v_lw / v_uw [B, K, Di, Ly], v_lb / v_ub [B, K, Ly] (K = key
+// positions, Ly = head features), instead of the transposed copy [B, Ly, Di, K]; z as in
+// fb_dot_product_heads_f32.  Only the shapes of the tensor-core kernel (K = Ly = 32, Lx % 32 == 0,
+// Di % 4 == 0, 16-byte aligned pointers); otherwise FB_ERR_SHAPE and nothing is launched.
+// y_l / y_u receive the concretised value ranges as [B, Ly, K].
+extern "C" int fb_context_heads_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+                                    const float* v_lw, const float* v_uw, const float* v_lb, const float* v_ub,
+                                    float* z_lw, float* z_uw, float* z_lb, float* z_ub,
+                                    float* x_l, float* x_u, float* y_l, float* y_u,
+                                    int B, int Lx, int Ly, int Di, int K, int words, int p, float eps,
+                                    float out_scale, int merge_heads, void* stream) {
+  if (!x_lw || !x_uw || !x_lb || !x_ub || !v_lw || !v_uw || !v_lb || !v_ub || !z_lw || !z_uw || !z_lb || !z_ub ||
+      !x_l || !x_u || !y_l || !y_u)
+    return FB_ERR_ARG;
+  if (B < 0 || Lx <= 0 || Ly <= 0 || Di <= 0 || K <= 0 || words <= 0 || !valid_norm(p) || merge_heads < 1) return FB_ERR_ARG;
+  if (!(out_scale > 0.f)) return FB_ERR_ARG;
+  if (Di % words != 0 || Di == 1) return FB_ERR_SHAPE;
+  if (B == 0) return FB_OK;
+  if (dot_force_cuda_cores() ||
+      !dot_tc_supported(x_lw, x_uw, v_lw, v_uw, x_l, y_l, y_u, z_lw, z_uw, B, Lx, Ly, Di, K, merge_heads))
+    return FB_ERR_SHAPE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const double d1 = (double)Di + 1;
+  ProfileScope prof(PK_DOT, 16.0 * B * Lx * Ly * d1 * K,
+                    4.0 * (2.0 * B * Lx * d1 * K + 2.0 * B * Ly * d1 * K + 2.0 * B * Lx * Ly * d1), stream);
+  int rc = fb_concretize_f32(x_lw, x_uw, x_lb, x_ub, x_l, x_u, (int64_t)B * Lx, Di, K, words, p, eps, FB_NATIVE, stream);
+  if (rc != FB_OK) return rc;
+  // ranges of the values in their own layout [B, K, Ly], then transposed in place to [B, Ly, K]
+  rc = fb_concretize_f32(v_lw, v_uw, v_lb, v_ub, y_l, y_u, (int64_t)B * K, Di, Ly, words, p, eps, FB_NATIVE, stream);
+  if (rc != FB_OK) return rc;
+  transpose_small_inplace<<<(unsigned)B, 256, 0, st>>>(y_l, y_u, K, Ly);
+  FB_LAUNCH_OK();
+  {
+    const int n_it = (int)ceil_div(Lx, 32), n_jt = (int)ceil_div(Ly, 32);
+    dot_bias_tiled<<<(unsigned)((int64_t)B * n_it * n_jt), kThreads, 0, st>>>(x_lb, x_ub, v_lb, v_ub, x_l, y_l, y_u, z_lb, z_ub,
+                                                                            Lx, Ly, K, n_it, n_jt, out_scale, merge_heads, 1);
+    FB_LAUNCH_OK();
+  }
+  return launch_dot_weight_tc(x_lw, x_uw, v_lw, v_uw, x_l, y_l, y_u, z_lw, z_uw, B, Lx, Ly, Di, out_scale, merge_heads, 1, st);
 }
 
 // ---------------------------------------------------------------------------

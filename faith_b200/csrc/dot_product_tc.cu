@@ -6,6 +6,8 @@
 //   z_uw[b,i,m,j] = sum_k  x_c uy + x_r |uy| + y_c lx + y_r |lx|           centre/radius form)
 //   x_c = (x_lw + x_uw)/2, x_r = (x_uw - x_lw)/2 at [b,i,m,k];  y_c, y_r at [b,j,m,k];
 //   lx = x_l[b,i,k];  ly = y_l[b,j,k], uy = y_u[b,j,k]  (concretised operand ranges)
+// With y_kmajor the weights of y are given as [b,k,m,j] (contraction axis first), which is how the
+// value projection writes them: the context product then needs no transposed copy of V.
 //
 // One tile = one b, 32 values of i, 4 values of m, all 32 values of j.  It is made of four GEMMs with
 // M = 128, K = 32:
@@ -85,7 +87,7 @@ dot_weight_tc(const __grid_constant__ CUtensorMap tm_xl, const __grid_constant__
               const __grid_constant__ CUtensorMap tm_lx, const __grid_constant__ CUtensorMap tm_ly,
               const __grid_constant__ CUtensorMap tm_uy, const __grid_constant__ CUtensorMap tm_zl,
               const __grid_constant__ CUtensorMap tm_zu, int Lx, int Ly, int n_ib, int n_mb, int total_tiles,
-              float out_scale, int heads) {
+              float out_scale, int heads, int y_kmajor) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -311,17 +313,32 @@ dot_weight_tc(const __grid_constant__ CUtensorMap tm_xl, const __grid_constant__
       const uint8_t* tl = raw + (grp == 0 ? kDtRawXl : kDtRawYl);
       const uint8_t* tu = raw + (grp == 0 ? kDtRawXu : kDtRawYu);
       float c[16], r[16];
+      if (grp == 1 && y_kmajor) {
+        // y given as [b, k, m, j] (the value tensor as the projection writes it): the tile is
+        // [k][m][j]; this thread's row (j, m) is gathered element by element
+        const int j = row >> 2, m = row & 3;
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const uint32_t off = swz(row, half * 4 + q);
-        const float4 vl = *reinterpret_cast<const float4*>(tl + off);
-        const float4 vu = *reinterpret_cast<const float4*>(tu + off);
-        const float l4[4] = {vl.x, vl.y, vl.z, vl.w}, u4[4] = {vu.x, vu.y, vu.z, vu.w};
+        for (int kk = 0; kk < 16; ++kk) {
+          const int k = half * 16 + kk;
+          const uint32_t off = swz(k * 4 + m, j >> 2) + (uint32_t)(j & 3) * 4u;
+          const float lo = *reinterpret_cast<const float*>(tl + off), up = *reinterpret_cast<const float*>(tu + off);
+          const float hu = fmul(up, 0.5f);
+          c[kk] = __fmaf_rn(lo, 0.5f, hu);
+          r[kk] = __fmaf_rn(lo, -0.5f, hu);
+        }
+      } else {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float hu = fmul(u4[i], 0.5f);
-          c[q * 4 + i] = __fmaf_rn(l4[i], 0.5f, hu);
-          r[q * 4 + i] = __fmaf_rn(l4[i], -0.5f, hu);
+        for (int q = 0; q < 4; ++q) {
+          const uint32_t off = swz(row, half * 4 + q);
+          const float4 vl = *reinterpret_cast<const float4*>(tl + off);
+          const float4 vu = *reinterpret_cast<const float4*>(tu + off);
+          const float l4[4] = {vl.x, vl.y, vl.z, vl.w}, u4[4] = {vu.x, vu.y, vu.z, vu.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float hu = fmul(u4[i], 0.5f);
+            c[q * 4 + i] = __fmaf_rn(l4[i], 0.5f, hu);
+            r[q * 4 + i] = __fmaf_rn(l4[i], -0.5f, hu);
+          }
         }
       }
       // range tiles: group 0 converts [ly; uy] (64 rows x 8 chunks, two chunks per thread), group 1 lx
@@ -451,7 +468,7 @@ bool dot_tc_supported(const float* x_lw, const float* x_uw, const float* y_lw, c
 
 int launch_dot_weight_tc(const float* x_lw, const float* x_uw, const float* y_lw, const float* y_uw, const float* x_l,
                          const float* y_l, const float* y_u, float* z_lw, float* z_uw, int B, int Lx, int Ly, int Di,
-                         float out_scale, int heads, cudaStream_t st) {
+                         float out_scale, int heads, int y_kmajor, cudaStream_t st) {
   CUtensorMap tm_xl, tm_xu, tm_yl, tm_yu, tm_lx, tm_ly, tm_uy, tm_zl, tm_zu;
   const uint64_t S = (uint64_t)(B / heads);
   if (!make_map3(&tm_xl, x_lw, 32, (uint64_t)Di, (uint64_t)B * Lx) || !make_map3(&tm_xu, x_uw, 32, (uint64_t)Di, (uint64_t)B * Lx) ||
@@ -466,7 +483,7 @@ int launch_dot_weight_tc(const float* x_lw, const float* x_uw, const float* y_lw
   FB_CUDA_OK(cudaFuncSetAttribute(dot_weight_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDtSmemBytes));
   const int sms = device_info().sms;
   dot_weight_tc<<<(unsigned)(total < sms ? total : sms), kDtThreads, kDtSmemBytes, st>>>(
-      tm_xl, tm_xu, tm_yl, tm_yu, tm_lx, tm_ly, tm_uy, tm_zl, tm_zu, Lx, Ly, n_ib, n_mb, total, out_scale, heads);
+      tm_xl, tm_xu, tm_yl, tm_yu, tm_lx, tm_ly, tm_uy, tm_zl, tm_zu, Lx, Ly, n_ib, n_mb, total, out_scale, heads, y_kmajor);
   FB_LAUNCH_OK();
   return FB_OK;
 }

@@ -200,14 +200,25 @@ extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, i
     } else {
       return src;
     }
-    // values, split into heads with position/feature swapped: [S*H, d, Di, L]
-    FB_TRY(dense(X, ly.v_w, ly.v_b, T2, rows, Di, D, D, stream));
-    FB_TRY(fb_split_heads_f32(T2.lw, T2.lb, T3.lw, T3.lb, S, L, Di, H, d, 1, stream));
-    FB_TRY(fb_split_heads_f32(T2.uw, T2.ub, T3.uw, T3.ub, S, L, Di, H, d, 1, stream));
-    // context, written head-merged as [S, L, Di, D] -> T2
-    FB_TRY(fb_dot_product_heads_f32(T1.lw, T1.uw, T1.lb, T1.ub, T3.lw, T3.uw, T3.lb, T3.ub, T2.lw, T2.uw, T2.lb, T2.ub,
-                                    range[0], range[1], range[2], range[3], S * H, L, d, Di, L, words, p, eps, 1.0f,
-                                    FB_NATIVE, (L % 4 == 0) ? H : 1, stream));
+    // values, split into heads [S*H, L, Di, d]; the tensor-core context product reads them in this layout
+    int crc = FB_ERR_SHAPE;
+    if (L % 4 == 0) {
+      FB_TRY(fb_matmul_heads_f32(X.lw, X.uw, X.lb, X.ub, ly.v_w, ly.v_b, T3.lw, T3.uw, T3.lb, T3.ub, rows, Di, D, D, L, H,
+                                 stream));
+      // context, written head-merged as [S, L, Di, D] -> T2
+      crc = fb_context_heads_f32(T1.lw, T1.uw, T1.lb, T1.ub, T3.lw, T3.uw, T3.lb, T3.ub, T2.lw, T2.uw, T2.lb, T2.ub,
+                                 range[0], range[1], range[2], range[3], S * H, L, d, Di, L, words, p, eps, 1.0f, H, stream);
+      if (crc != FB_OK && crc != FB_ERR_SHAPE) return crc;
+    }
+    if (crc == FB_ERR_SHAPE) {
+      // other shapes: values with position/feature swapped, [S*H, d, Di, L], and the general dot product
+      FB_TRY(dense(X, ly.v_w, ly.v_b, T2, rows, Di, D, D, stream));
+      FB_TRY(fb_split_heads_f32(T2.lw, T2.lb, T3.lw, T3.lb, S, L, Di, H, d, 1, stream));
+      FB_TRY(fb_split_heads_f32(T2.uw, T2.ub, T3.uw, T3.ub, S, L, Di, H, d, 1, stream));
+      FB_TRY(fb_dot_product_heads_f32(T1.lw, T1.uw, T1.lb, T1.ub, T3.lw, T3.uw, T3.lb, T3.ub, T2.lw, T2.uw, T2.lb, T2.ub,
+                                      range[0], range[1], range[2], range[3], S * H, L, d, Di, L, words, p, eps, 1.0f,
+                                      FB_NATIVE, (L % 4 == 0) ? H : 1, stream));
+    }
     if (L % 4 != 0) {  // unvectorised path: merge with the permute kernel
       FB_TRY(fb_merge_heads_f32(T2.lw, T2.lb, T1.lw, T1.lb, S, L, Di, H, d, stream));
       FB_TRY(fb_merge_heads_f32(T2.uw, T2.ub, T1.uw, T1.ub, S, L, Di, H, d, stream));

@@ -121,6 +121,28 @@ def dot_product(x, y, p, eps, words=1, out_scale=1.0, layout=FB_NATIVE, scratch=
     return out
 
 
+def context_kmajor(x, v, p, eps, words=1, out_scale=1.0, merge_heads=1):
+    """Context product with the values in the projection's own layout: x (lw, uw [B, Lx, Di, K], lb, ub
+    [B, Lx, K]), v (lw, uw [B, K, Di, Ly], lb, ub [B, K, Ly]).  Returns z as fb_dot_product_heads_f32 does.
+    Raises FaithError (FB_ERR_SHAPE) outside the tensor-core shapes."""
+    x_lw, x_uw, x_lb, x_ub = x
+    v_lw, v_uw, v_lb, v_ub = v
+    dev = _chk(*x, *v)
+    B, Lx, K = x_lb.shape
+    Ly = v_lb.shape[2]
+    Di = x_lw.shape[2]
+    S = B // merge_heads
+    zw = (S, Lx, Di, merge_heads * Ly) if merge_heads > 1 else (B, Lx, Di, Ly)
+    zb = (S, Lx, merge_heads * Ly) if merge_heads > 1 else (B, Lx, Ly)
+    out = (torch.empty(zw, device=dev), torch.empty(zw, device=dev), torch.empty(zb, device=dev), torch.empty(zb, device=dev))
+    scratch = (torch.empty_like(x_lb), torch.empty_like(x_lb), torch.empty((B, Ly, K), device=dev), torch.empty((B, Ly, K), device=dev))
+    with torch.cuda.device(dev):
+        check(load().fb_context_heads_f32(_p(x_lw), _p(x_uw), _p(x_lb), _p(x_ub), _p(v_lw), _p(v_uw), _p(v_lb), _p(v_ub),
+                                          *[_p(t) for t in out], *[_p(t) for t in scratch], B, Lx, Ly, Di, K, words,
+                                          norm_code(p), eps, out_scale, merge_heads, _stream()), "fb_context_heads_f32")
+    return out
+
+
 def mul_bounds(x, y, p, eps, words=1):
     dev = _chk(*x, *y)
     x_lw, x_uw, x_lb, x_ub = x

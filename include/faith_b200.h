@@ -139,6 +139,22 @@ int fb_dot_product_heads_f32(const float* x_lw, const float* x_uw, const float* 
                              int B, int Lx, int Ly, int Di, int K, int words, int p, float eps,
                              float out_scale, int layout, int merge_heads, void* stream);
 
+/* Context product of the attention block, Bounds.context (Bounds.py:843-850: dot_product with V.t()),
+ * taking the values in the layout the projection writes, v_lw / v_uw [B, K, Di, Ly] and v_lb / v_ub
+ * [B, K, Ly] (K = key positions, Ly = head features), so that no transposed copy of V is needed
+ * (the reference's transpose_for_scores + .t() are permute copies, VerifierForward.py:208-229).
+ * x = attention probabilities [B, Lx, Di, K]; z, merge_heads and the scratch tensors as in
+ * fb_dot_product_heads_f32 (y_l, y_u receive the value ranges as [B, Ly, K]).
+ * Tensor-core shapes only: K = Ly = 32, Lx a multiple of 32, Di a multiple of 4, 16-byte aligned
+ * pointers; otherwise FB_ERR_SHAPE and nothing is launched (transpose V and call
+ * fb_dot_product_heads_f32). */
+int fb_context_heads_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+                         const float* v_lw, const float* v_uw, const float* v_lb, const float* v_ub,
+                         float* z_lw, float* z_uw, float* z_lb, float* z_ub,
+                         float* x_l, float* x_u, float* y_l, float* y_u,
+                         int B, int Lx, int Ly, int Di, int K, int words, int p, float eps,
+                         float out_scale, int merge_heads, void* stream);
+
 /* The same operator for callers that cannot allocate device memory.  (No counterpart in the
  * reference, whose callers always allocate the scratch tensors themselves.)
  *

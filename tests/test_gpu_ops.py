@@ -170,6 +170,35 @@ def test_dot_product_tensor_core_shapes_match_fp64_and_repeat():
             assert bool((err <= 4e-6 + 1e-5 * ref.abs()).all()), float(err.max())
 
 
+def test_context_with_values_in_projection_layout_matches_transposed_path():
+    """fb_context_heads_f32 (values as [B, K, Di, Ly]) against fb_dot_product with the transposed copy
+    of the same values, with and without the head merge; shapes outside the kernel are refused."""
+    from faith_b200 import ops, _lib
+    B, L, Di, d, H = 8, 32, 64, 32, 4
+    g0 = torch.Generator().manual_seed(23)
+    def mk(shape_w, shape_b, s):
+        lw = torch.randn(*shape_w, generator=g0) * s
+        uw = lw + torch.rand(*shape_w, generator=g0) * 0.05
+        lb = torch.rand(*shape_b, generator=g0)
+        ub = lb + torch.rand(*shape_b, generator=g0) * 0.05
+        return [t.to(DEV) for t in (lw, uw, lb, ub)]
+    x = mk((B, L, Di, L), (B, L, L), 0.05)          # probabilities [B, Lx, Di, K]
+    v = mk((B, L, Di, d), (B, L, d), 0.3)           # values [B, K, Di, Ly]
+    vt = [v[0].permute(0, 3, 2, 1).contiguous(), v[1].permute(0, 3, 2, 1).contiguous(),
+          v[2].permute(0, 2, 1).contiguous(), v[3].permute(0, 2, 1).contiguous()]
+    ref = ops.dot_product(x, vt, 2.0, 0.02, 2, 1.0)
+    got = ops.context_kmajor(x, v, 2.0, 0.02, 2, 1.0, 1)
+    for a, b, name in zip(got, ref, ("lw", "uw", "lb", "ub")):
+        helpers.assert_close(a, b.cpu(), "context " + name, rtol=1e-6, atol=1e-7)
+    merged = ops.context_kmajor(x, v, 2.0, 0.02, 2, 1.0, H)
+    m_ref = ops.merge_heads(ref, H)
+    for a, b, name in zip(merged, m_ref, ("lw", "uw", "lb", "ub")):
+        helpers.assert_close(a, b.cpu(), "merged context " + name, rtol=1e-6, atol=1e-7)
+    x48 = mk((B, 48, Di, L), (B, 48, L), 0.05)
+    with pytest.raises(_lib.FaithError):
+        ops.context_kmajor(x48, v, 2.0, 0.02, 2, 1.0, 1)
+
+
 # ------------------------------------------------------------------ matmul
 @pytest.mark.parametrize("shape,Dy", [((1, 2, 64, 64), 64), ((1, 16, 64, 64), 128), ((2, 8, 128, 256), 512),
                                       ((1, 3, 24, 20), 7), ((1, 5, 33, 130), 129), ((1, 4, 64, 128), 2),
