@@ -1,0 +1,114 @@
+"""Parity at the benchmark's own operator configurations (shapes, seeds, norms and radii of the
+benchmark description; synthetic inputs stand in for the reference's SST / Yelp data and trained
+checkpoints, which are not available):
+
+  C1  Linear + ReLU   lw [1,16,64,64] -> [1,16,64,128], identity lw at word 0, L-inf, eps 0.01
+  C2  Q K^T           two perturbed words (dim_in 128), p = 2, eps 0.05, 4 heads of 32 features
+  C3  Tanh + Linear   [8,64,256,256], four perturbed words, p = 1 (q = inf), eps 0.1
+
+Each is compared with the oracle (pinned to the reference in tests/test_oracle_*.py) on identical
+seeded inputs within the per-operator bar; C3 is compared on two of its eight batch rows (the
+oracle needs seconds per row) and checked for finiteness and ordering at full size.
+"""
+import math
+import types
+
+import pytest
+import torch
+
+import helpers
+from oracle import bounds_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _input_bounds(x0, positions):
+    """Identity weights at the perturbed positions (VerifierForward.py:127-156)."""
+    B, L, D = x0.shape
+    Di = D * len(positions)
+    lw = torch.zeros(B, L, Di, D)
+    for w, pos in enumerate(positions):
+        lw[:, pos, w * D:(w + 1) * D] = torch.eye(D)
+    return lw, x0.clone(), lw.clone(), x0.clone()    # lw, lb, uw, ub
+
+
+def _gpu(p, eps, t, words):
+    import faith_b200
+    return faith_b200.BoundsLite(p, eps, *[v.to(DEV) for v in t], perturbed_words=words)
+
+
+def _cmp(g, o, what, rtol=1e-5, atol=1e-6):
+    for k in ("lw", "uw", "lb", "ub"):
+        helpers.assert_close(getattr(g, k), getattr(o, k), "%s %s" % (what, k), rtol=rtol, atol=atol)
+
+
+def test_config1_linear_relu():
+    g0 = torch.Generator().manual_seed(1)
+    x0 = torch.randn(1, 16, 64, generator=g0)
+    W = torch.randn(128, 64, generator=g0) / 8
+    bias = 0.1 * torch.randn(128, generator=g0)
+    t = _input_bounds(x0, [0])
+    p, eps = float("inf"), 0.01
+    o = O.OBounds(p, eps, *t).dense(W, bias).relu()
+    g = _gpu(p, eps, t, 1).dense(types.SimpleNamespace(weight=W.to(DEV), bias=bias.to(DEV))).relu()
+    _cmp(g, o, "C1 linear+relu", atol=2e-6)
+    gl, gu = g.concretize()
+    ol, ou = o.concretize()
+    helpers.assert_close(gl, ol, "C1 l", atol=2e-6)
+    helpers.assert_close(gu, ou, "C1 u", atol=2e-6)
+
+
+def test_config2_query_key_product():
+    from faith_b200 import ops
+    g0 = torch.Generator().manual_seed(2)
+    x0 = torch.randn(1, 32, 64, generator=g0)
+    Wq = torch.randn(128, 64, generator=g0) / math.sqrt(128)
+    Wk = torch.randn(128, 64, generator=g0) / math.sqrt(128)
+    zero = torch.zeros(128)
+    t = _input_bounds(x0, [1, 2])
+    p, eps, heads = 2.0, 0.05, 4
+    ox = O.OBounds(p, eps, *t, words=2)
+    oq, ok = O.split_heads(ox.dense(Wq, zero), heads), O.split_heads(ox.dense(Wk, zero), heads)
+    oz = oq.dot_product(ok)
+    gx = _gpu(p, eps, t, 2)
+
+    def proj(W):
+        y = gx.dense(types.SimpleNamespace(weight=W.to(DEV), bias=zero.to(DEV)))
+        s = ops.split_heads(y._t4(), heads, False)
+        return y._new(s[0], s[1], s[2], s[3])
+
+    gq, gk = proj(Wq), proj(Wk)
+    assert tuple(gq.lw.shape) == (4, 32, 128, 32)
+    gz = gq.dot_product(gk)
+    assert tuple(gz.lw.shape) == (4, 32, 128, 32) and tuple(gz.lb.shape) == (4, 32, 32)
+    # GEMM-shaped: two fp32 summation orders differ by ~1e-6 of the summed magnitude (K = 32 x 128 terms)
+    _cmp(gz, oz, "C2 q k^T", atol=4e-6)
+
+
+def test_config3_tanh_linear():
+    g0 = torch.Generator().manual_seed(3)
+    x0 = torch.randn(8, 64, 64, generator=g0)
+    W1 = torch.randn(256, 64, generator=g0) / 16
+    W2 = torch.randn(256, 256, generator=g0) / 16
+    positions = [1, 2, 3, 4]
+    t = _input_bounds(x0, positions)
+    p, eps = 1.0, 0.1
+    gh = _gpu(p, eps, t, 4).matmul(W1.to(DEV))
+    assert tuple(gh.lw.shape) == (8, 64, 256, 256)
+    gt = gh.tanh()
+    gy = gt.matmul(W2.to(DEV))
+    for b in (gt, gy):
+        for k in ("lw", "uw", "lb", "ub"):
+            assert bool(torch.isfinite(getattr(b, k)).all())
+        l, u = b.concretize()
+        assert bool((l <= u + 1e-5).all())
+    # oracle on two batch rows
+    t2 = [v[:2] for v in t]
+    oh = O.OBounds(p, eps, *t2, words=4).matmul(W1)
+    ot = oh.tanh()
+    oy = ot.matmul(W2)
+    sub = lambda b: types.SimpleNamespace(lw=b.lw[:2], uw=b.uw[:2], lb=b.lb[:2], ub=b.ub[:2])
+    _cmp(sub(gt), ot, "C3 tanh", atol=2e-6)
+    # K = 256 contraction of values up to ~1: absolute part scaled to the summed magnitude
+    _cmp(sub(gy), oy, "C3 tanh+linear", atol=8e-6)
