@@ -317,10 +317,10 @@ def main():
                     "avg_ms_per_call": dom["ms"] / dom["calls"], "share_of_step": dom["share"]}
         if dom["op"] == "matmul" and os.environ.get("FB_MATMUL_IMPL", "") != "ffma":
             # DRAM traffic per launch from the ncu capture of the 32-sentence case
-            # (profiles/split_sign_gemm_tc_32_sentences.md): 134.4 MB read + 83.4 MB written against 268.6 MB
+            # (profiles/split_sign_gemm_tc_32_sentences.md): 134.4 MB read + 86.9 MB written against 268.6 MB
             # algorithmic (reads match; a third of the writes was still in L2 when the kernel ended), scaled to
             # this run's average launch by the bytes it processes
-            roofline["traffic"] = dom["bytes_per_call"] * (134.37 + 83.44) / 268.6
+            roofline["traffic"] = dom["bytes_per_call"] * (134.41 + 86.90) / 268.6
             roofline["traffic_note"] = "bytes; ncu dram read+write of a 32-sentence launch scaled by algorithmic bytes"
 
             # tcgen05 kind::tf32 runs at half the bf16 rate; the 3xTF32 centre/radius kernel executes
