@@ -7,8 +7,8 @@ checkpoints, which are not available):
   C3  Tanh + Linear   [8,64,256,256], four perturbed words, p = 1 (q = inf), eps 0.1
 
 Each is compared with the oracle (pinned to the reference in tests/test_oracle_*.py) on identical
-seeded inputs within the per-operator bar; C3 is compared on two of its eight batch rows (the
-oracle needs seconds per row) and checked for finiteness and ordering at full size.
+seeded inputs within the per-operator bar; C3 is compared operator by operator on two of its eight
+batch rows and checked for finiteness and ordering at full size.
 """
 import math
 import types
@@ -103,12 +103,15 @@ def test_config3_tanh_linear():
             assert bool(torch.isfinite(getattr(b, k)).all())
         l, u = b.concretize()
         assert bool((l <= u + 1e-5).all())
-    # oracle on two batch rows
+    # Oracle on two batch rows, operator by operator on identical inputs: each oracle operator is fed
+    # the GPU result of the previous one.  (Chained end to end, the 10-step bisection of the tanh
+    # relaxation turns a last-bit difference of its input range into a different tangent point for a few
+    # per cent of the columns, i.e. 1e-5-sized jumps that say nothing about either implementation.)
     t2 = [v[:2] for v in t]
     oh = O.OBounds(p, eps, *t2, words=4).matmul(W1)
-    ot = oh.tanh()
-    oy = ot.matmul(W2)
     sub = lambda b: types.SimpleNamespace(lw=b.lw[:2], uw=b.uw[:2], lb=b.lb[:2], ub=b.ub[:2])
-    _cmp(sub(gt), ot, "C3 tanh", atol=2e-6)
+    _cmp(sub(gh), oh, "C3 first linear", atol=2e-6)
+    cpu = lambda b: O.OBounds(p, eps, b.lw[:2].cpu(), b.lb[:2].cpu(), b.uw[:2].cpu(), b.ub[:2].cpu(), words=4)
+    _cmp(sub(gt), cpu(gh).tanh(), "C3 tanh", atol=2e-6)
     # K = 256 contraction of values up to ~1: absolute part scaled to the summed magnitude
-    _cmp(sub(gy), oy, "C3 tanh+linear", atol=8e-6)
+    _cmp(sub(gy), cpu(gt).matmul(W2), "C3 linear after tanh", atol=8e-6)
