@@ -115,3 +115,38 @@ def test_config3_tanh_linear():
     _cmp(sub(gt), cpu(gh).tanh(), "C3 tanh", atol=2e-6)
     # K = 256 contraction of values up to ~1: absolute part scaled to the summed magnitude
     _cmp(sub(gy), cpu(gt).matmul(W2), "C3 linear after tanh", atol=8e-6)
+
+
+def test_config5_cnn_full_size_properties():
+    """C5: 3x32x32 image, every pixel perturbed (dim_in = 3072), L-inf eps 2/255; conv 3->16, relu, conv 16->32
+    stride 2, relu, linear 8192->10.  At full size: finite, ordered, and 512 sampled images of the ball
+    (half of them on vertices) plus the unperturbed image land inside the interval.  (Parity of the same pass
+    with the oracle is checked on a smaller image in test_gpu_sharded.py, parity of the conv operator at the
+    first layer's full shape in test_gpu_ops.py::test_conv_bounds.)"""
+    import torch.nn.functional as F
+    from faith_b200.sharded import CnnVerifier
+    layers = O.make_cnn(5)
+    img = torch.rand(3, 32, 32, generator=torch.Generator().manual_seed(5))
+    eps = 2.0 / 255
+    l, u = CnnVerifier(layers, DEV).forward(img, float("inf"), eps)
+    l, u = l.cpu(), u.cpu()
+    assert tuple(l.shape) == (10,) or l.numel() == 10
+    assert bool(torch.isfinite(l).all()) and bool(torch.isfinite(u).all())
+    assert bool((l <= u).all())
+
+    def net(x):
+        for ly in layers:
+            if ly[0] == "conv":
+                x = F.conv2d(x, ly[1], ly[2], ly[3], ly[4])
+            elif ly[0] == "relu":
+                x = torch.relu(x)
+            else:
+                x = F.linear(x.flatten(1), ly[1], ly[2])
+        return x
+    g = torch.Generator().manual_seed(6)
+    n = 512
+    delta = (torch.randint(0, 2, (n, 3, 32, 32), generator=g).float() * 2 - 1) * eps
+    delta[: n // 2] *= torch.rand(n // 2, 1, 1, 1, generator=g)
+    x = torch.cat([img.unsqueeze(0), img.unsqueeze(0) + delta])
+    y = net(x)
+    assert bool((y >= l.reshape(1, -1) - 1e-4).all()) and bool((y <= u.reshape(1, -1) + 1e-4).all())
