@@ -16,6 +16,7 @@ constexpr int kThreads = 256;
 constexpr int kCW = 32;  // columns per block tile
 
 constexpr int OP_CONCRETIZE = -1;
+constexpr int OP_COEF_ONLY = 16;   // added to a relaxation op: write the column coefficients instead of rescaling
 
 // ---------------------------------------------------------------------------
 // Norm pass over one operand pair (lw, uw) of a tile.  Returns, for threads tid < kCW, the
@@ -203,6 +204,21 @@ col_relax_native(int op, const float* __restrict__ lw, const float* __restrict__
     if (mine) {
       o_lb[(size_t)row * Do + c0 + tid] = l;
       o_ub[(size_t)row * Do + c0 + tid] = u;
+    }
+    return;
+  }
+  if (op >= OP_COEF_ONLY) {
+    // coefficients only: o_lw / o_uw are [rows, Do] arrays that receive the own-side slopes; a column
+    // with a cross term (possible only for an inverted range l > u) raises bit 1 of the flag
+    if (mine) {
+      bool bad = false;
+      const ColCoef c = relax_column(op - OP_COEF_ONLY, l, u, lbv, ubv, bad);
+      if (violation != nullptr && (bad || c.c_lu != 0.f || c.c_ul != 0.f)) atomicOr(violation, bad ? 1 : 2);
+      const size_t o = (size_t)row * Do + c0 + tid;
+      o_lw[o] = c.c_ll;
+      o_uw[o] = c.c_uu;
+      o_lb[o] = c.nlb;
+      o_ub[o] = c.nub;
     }
     return;
   }
@@ -482,11 +498,11 @@ int launch_relax(int op, const float* lw, const float* uw, const float* lb, cons
   const int64_t blocks = rows * ntiles;
   if (blocks > 0x7fffffff) return FB_ERR_SHAPE;
   const bool vec = Do % 4 == 0 && aligned16(lw) && aligned16(uw) &&
-                   (op == OP_CONCRETIZE || (aligned16(o_lw) && aligned16(o_uw)));
-  // Keep the tile in shared memory when a few blocks per SM still fit; concretise alone
-  // has no second pass and never stages.
+                   (op == OP_CONCRETIZE || op >= OP_COEF_ONLY || (aligned16(o_lw) && aligned16(o_uw)));
+  // Keep the tile in shared memory when a few blocks per SM still fit; concretise alone and the
+  // coefficient-only mode have no second pass and never stage.
   const size_t staged_bytes = relax_smem_bytes(Di, true, 2);
-  const bool staged = op != OP_CONCRETIZE && staged_bytes <= 72 * 1024;
+  const bool staged = op != OP_CONCRETIZE && op < OP_COEF_ONLY && staged_bytes <= 72 * 1024;
   const size_t smem = staged ? staged_bytes : relax_smem_bytes(Di, false, 2);
 #define FB_RELAX_LAUNCH(V, S)                                                                              \
   do {                                                                                                     \
@@ -615,4 +631,24 @@ extern "C" int fb_relax_with_norms_f32(int op, const float* lw, const float* uw,
   else col_relax_apply_native<1><<<(unsigned)blocks, kThreads, 0, st>>>(op, lw, uw, lb, ub, norm_l, norm_u, out_lw, out_uw, out_lb, out_ub, Di_local, Do, ntiles, p, eps, violation);
   FB_LAUNCH_OK();
   return FB_OK;
+}
+
+// Relaxation without the rescale pass: the dual norms, the relaxed bias terms and, instead of the
+// rescaled weights, the own-side slopes of every column, c_l and c_u [rows, Do] (out_lw = c_l * lw,
+// out_uw = c_u * uw).  For relu, tanh and exp (positive slopes, Bounds.py:921-1103) these are the only
+// non-zero coefficients of a well-formed column; a column that would need a cross term (inverted range)
+// sets bit 1 of *violation.  The consumer applies the slopes while it reads the weights
+// (fb_matmul_coef_f32), which saves one write and one read of lw / uw.  Native layout only.
+extern "C" int fb_relax_coef_f32(int op, const float* lw, const float* uw, const float* lb, const float* ub,
+                                 float* c_l, float* c_u, float* out_lb, float* out_ub, int64_t rows, int Di, int Do,
+                                 int words, int p, float eps, int* violation, void* stream) {
+  if (op != FB_RELU && op != FB_TANH && op != FB_EXP) return FB_ERR_ARG;
+  if (rows == 0 || Do == 0) return FB_OK;
+  if (!lw || !uw || !lb || !ub || !c_l || !c_u || !out_lb || !out_ub) return FB_ERR_ARG;
+  if (rows < 0 || Di <= 0 || Do < 0 || words <= 0 || !valid_norm(p)) return FB_ERR_ARG;
+  if (Di % words != 0) return FB_ERR_SHAPE;
+  const double mw = (double)rows * Di * Do, mb = (double)rows * Do;
+  ProfileScope prof(PK_RELAX, 4.0 * mw, 4.0 * (2 * mw + 6 * mb), stream);
+  return launch_relax(op + OP_COEF_ONLY, lw, uw, lb, ub, c_l, c_u, out_lb, out_ub, rows, Di, Do, words, p, eps,
+                      FB_NATIVE, violation, (cudaStream_t)stream);
 }

@@ -230,8 +230,25 @@ extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, i
     // attention output: dense, + residual, layer norm -> T3
     FB_TRY(dense(T2, ly.ao_w, ly.ao_b, T1, rows, Di, D, D, stream));
     FB_TRY(norm_residual(enc, T1, &X, ly.ln1_g, ly.ln1_b, T3, rows, Di, D, stream));
-    // feed-forward: dense, relu, dense, + residual, layer norm -> T1
+    // feed-forward: dense, relu, dense, + residual, layer norm
     FB_TRY(dense(T3, ly.f1_w, ly.f1_b, T1, rows, Di, D, F, stream));
+    // Where the shapes allow it the relu is not materialised: its column slopes go to the (now unused)
+    // slot of the layer input and the second product applies them while it reads the hidden bounds.
+    int frc = fb_relax_coef_f32(FB_RELU, T1.lw, T1.uw, T1.lb, T1.ub, X.lw, X.uw, T2.lb, T2.ub, rows, Di, F, words, p, eps,
+                                nullptr, stream);
+    if (frc == FB_OK)
+      frc = fb_matmul_coef_f32(T1.lw, T1.uw, T2.lb, T2.ub, X.lw, X.uw, ly.f2_w, ly.f2_b, T2.lw, T2.uw, X.lb, X.ub, rows, Di,
+                               F, D, stream);
+    if (frc == FB_OK) {
+      const BoundSet Y = {T2.lw, T2.uw, X.lb, X.ub};
+      FB_TRY(norm_residual(enc, Y, &T3, ly.ln2_g, ly.ln2_b, T1, rows, Di, D, stream));
+      // the layer output (slot B) becomes the next layer's input
+      const int newA = B;
+      B = A;
+      A = newA;
+      continue;
+    }
+    if (frc != FB_ERR_SHAPE) return frc;
     FB_TRY(relax(FB_RELU, T1, T2, rows, Di, F, words, p, eps, nullptr, stream));
     FB_TRY(dense(T2, ly.f2_w, ly.f2_b, T1, rows, Di, F, D, stream));
     FB_TRY(norm_residual(enc, T1, &T3, ly.ln2_g, ly.ln2_b, T2, rows, Di, D, stream));

@@ -9,7 +9,8 @@ bool tc_gemm_supported(const float* a_lo, const float* a_up, const float* W, con
                        int64_t M, int N, int K);
 bool tc_split_supported(int64_t M, int N, int split_rows, int split_d);
 int launch_split_sign_tc(const float* a_lo, const float* a_up, const float* W, const float* bias, float* c_lo,
-                         float* c_up, int64_t M, int N, int K, cudaStream_t st, int split_rows, int split_d);
+                         float* c_up, int64_t M, int N, int K, cudaStream_t st, int split_rows, int split_d,
+                         const float* coef_l = nullptr, const float* coef_u = nullptr, int coef_di = 1);
 int launch_split_sign_ffma(const float* a_lo, const float* a_up, const float* W, const float* bias, float* c_lo,
                            float* c_up, int64_t M, int N, int K, cudaStream_t st, int split_rows, int split_d);
 
@@ -62,4 +63,29 @@ extern "C" int fb_matmul_heads_f32(const float* x_lw, const float* x_uw, const f
                                    const float* W, const float* bias, float* y_lw, float* y_uw, float* y_lb,
                                    float* y_ub, int64_t rows, int Di, int Do, int Dy, int L, int heads, void* stream) {
   return matmul_impl(x_lw, x_uw, x_lb, x_ub, W, bias, y_lw, y_uw, y_lb, y_ub, rows, Di, Do, Dy, L, heads, stream);
+}
+
+// Product of a relaxed bound with a constant weight, the relaxation given by its column slopes
+// (fb_relax_coef_f32): y = matmul((c_l * x_lw, c_u * x_uw, x_lb, x_ub), W) + bias, where c_l, c_u are
+// [rows, Do] and x_lb, x_ub are the relaxed bias terms.  The slopes are applied by the GEMM while it
+// reads the weights, so dense(relu(x)) needs no pass that writes relu(x) (Bounds.py:921-963 followed by
+// :397-413).  Tensor-core shapes with Di a multiple of 128 and Do a multiple of 32 only; otherwise
+// FB_ERR_SHAPE and nothing is launched (run fb_relax_f32 and fb_matmul_f32).
+extern "C" int fb_matmul_coef_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+                                  const float* c_l, const float* c_u, const float* W, const float* bias,
+                                  float* y_lw, float* y_uw, float* y_lb, float* y_ub,
+                                  int64_t rows, int Di, int Do, int Dy, void* stream) {
+  if (!x_lw || !x_uw || !x_lb || !x_ub || !c_l || !c_u || !W || !y_lw || !y_uw || !y_lb || !y_ub) return FB_ERR_ARG;
+  if (rows < 0 || Di <= 0 || Do <= 0 || Dy <= 0) return FB_ERR_ARG;
+  const int64_t M = rows * (int64_t)Di;
+  if (!fb::use_tensor_cores() || Di % 128 != 0 || Do % 32 != 0 || !fb::aligned16(c_l) || !fb::aligned16(c_u) ||
+      !fb::tc_gemm_supported(x_lw, x_uw, W, y_lw, y_uw, M, Dy, Do))
+    return FB_ERR_SHAPE;
+  if (rows == 0) return FB_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const double Mt = (double)rows * (Di + 1);
+  fb::ProfileScope prof(fb::PK_MATMUL, 8.0 * Mt * Do * Dy, 4.0 * (2 * Mt * Do + 2 * Mt * Dy + (double)Do * Dy + Dy), stream);
+  int rc = fb::launch_split_sign_tc(x_lw, x_uw, W, nullptr, y_lw, y_uw, M, Dy, Do, st, 0, 0, c_l, c_u, Di);
+  if (rc != FB_OK) return rc;
+  return fb::split_sign_gemm(x_lb, x_ub, W, bias, y_lb, y_ub, rows, Dy, Do, st);
 }

@@ -127,11 +127,15 @@ struct SharedLayout {
   __host__ __device__ static constexpr uint32_t bars() { return out() + kOutStageBytes; }
 };
 
+// kCoef: column slopes of a relaxation are applied to the operands on the fly (a separate instantiation, so
+// that the plain kernel keeps its register allocation).
+template <bool kCoef>
 __global__ void __launch_bounds__(kThreads, 1)
 split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_constant__ CUtensorMap tm_up,
                    const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_out_lo,
                    const __grid_constant__ CUtensorMap tm_out_up, const float* __restrict__ bias, int64_t M, int N, int K,
-                   int n_tiles_n, int64_t total_tiles, int split_rows, int split_d) {
+                   int n_tiles_n, int64_t total_tiles, int split_rows, int split_d,
+                   const float* __restrict__ coef_l, const float* __restrict__ coef_u, int coef_di) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -357,7 +361,26 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
     const int row = quarter * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     bool ok = true;
-    for (int it = g; it < total_it && ok; it += 2) {
+    int c_ti = 0, c_kb = g;   // tile and k-block of `it`, kept incrementally (used by the coefficient loads)
+    for (int it = g; it < total_it && ok; it += 2, c_kb += 2) {
+      // Column coefficients of a relaxation applied on the fly (coef_l != nullptr): x_lw is read as
+      // coef_l[row block, k] * x_lw and x_uw as coef_u[row block, k] * x_uw, the row block being the
+      // (b, l) row of the bound (tile row / coef_di; a tile never straddles two row blocks).  The 16
+      // values per side are the same for every thread of the CTA; they are fetched first so that their
+      // latency hides behind the wait and the shared-memory loads.
+      float4 kl[4], ku[4];
+      if (kCoef) {
+        while (c_kb >= nkb) { c_kb -= nkb; ++c_ti; }
+        const int tile = blockIdx.x + c_ti * gridDim.x;
+        const int64_t rb = ((int64_t)(tile / n_tiles_n) * BM) / coef_di;
+        const float* pl = coef_l + rb * K + c_kb * BK + half * 16;
+        const float* pu = coef_u + rb * K + c_kb * BK + half * 16;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          kl[q] = __ldg(reinterpret_cast<const float4*>(pl) + q);
+          ku[q] = __ldg(reinterpret_cast<const float4*>(pu) + q);
+        }
+      }
       ok = mbar_wait_warp(bar_full + 8 * g, (uint32_t)((it >> 1) & 1), cta_abort);
       if (!ok) break;
       const uint8_t* raw = base_ptr + SharedLayout::raw(g);
@@ -377,8 +400,12 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
         for (int q = 0; q < 2; ++q) vw[q] = *reinterpret_cast<const float4*>(raw + 2 * kTileBytes + swz(wrow, wchunk + q));
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          const float l4[4] = {vl[q].x, vl[q].y, vl[q].z, vl[q].w};
-          const float u4[4] = {vu[q].x, vu[q].y, vu[q].z, vu[q].w};
+          float l4[4] = {vl[q].x, vl[q].y, vl[q].z, vl[q].w};
+          float u4[4] = {vu[q].x, vu[q].y, vu[q].z, vu[q].w};
+          if (kCoef) {   // one rounded product per side, as the rescale pass of the relaxation kernels
+            l4[0] = fmul(kl[q].x, l4[0]); l4[1] = fmul(kl[q].y, l4[1]); l4[2] = fmul(kl[q].z, l4[2]); l4[3] = fmul(kl[q].w, l4[3]);
+            u4[0] = fmul(ku[q].x, u4[0]); u4[1] = fmul(ku[q].y, u4[1]); u4[2] = fmul(ku[q].z, u4[2]); u4[3] = fmul(ku[q].w, u4[3]);
+          }
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             // centre (l + u) / 2 and radius (u - l) / 2, each rounded once
@@ -505,7 +532,8 @@ bool tc_gemm_supported(const float* a_lo, const float* a_up, const float* W, con
 }
 
 int launch_split_sign_tc(const float* a_lo, const float* a_up, const float* W, const float* bias, float* c_lo,
-                         float* c_up, int64_t M, int N, int K, cudaStream_t st, int split_rows, int split_d) {
+                         float* c_up, int64_t M, int N, int K, cudaStream_t st, int split_rows, int split_d,
+                         const float* coef_l, const float* coef_u, int coef_di) {
   CUtensorMap tm_lo, tm_up, tm_w, tm_out_lo, tm_out_up;
   if (!make_map(&tm_lo, a_lo, (uint64_t)M, (uint64_t)K, BM) || !make_map(&tm_up, a_up, (uint64_t)M, (uint64_t)K, BM) ||
       !make_map(&tm_w, W, (uint64_t)N, (uint64_t)K, BN) ||
@@ -520,13 +548,18 @@ int launch_split_sign_tc(const float* a_lo, const float* a_up, const float* W, c
   FB_CUDA_OK(cudaGetDevice(&dev));
   cudaError_t attr_err = cudaSuccess;
   std::call_once(attr_once[dev & 63], [&]() {
-    attr_err = cudaFuncSetAttribute(split_sign_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    if (attr_err == cudaSuccess)
+      attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
   });
   FB_CUDA_OK(attr_err);
   // persistent: one CTA per SM (tensor memory and shared memory allow exactly one)
   const int64_t sms = device_info().sms;
   const unsigned grid = (unsigned)(total_tiles < sms ? total_tiles : sms);
-  split_sign_gemm_tc<<<grid, kThreads, kSmemBytes, st>>>(tm_lo, tm_up, tm_w, tm_out_lo, tm_out_up, bias, M, N, K, gn, total_tiles, split_rows, split_d);
+  if (coef_l != nullptr)
+    split_sign_gemm_tc<true><<<grid, kThreads, kSmemBytes, st>>>(tm_lo, tm_up, tm_w, tm_out_lo, tm_out_up, bias, M, N, K, gn, total_tiles, split_rows, split_d, coef_l, coef_u, coef_di);
+  else
+    split_sign_gemm_tc<false><<<grid, kThreads, kSmemBytes, st>>>(tm_lo, tm_up, tm_w, tm_out_lo, tm_out_up, bias, M, N, K, gn, total_tiles, split_rows, split_d, nullptr, nullptr, 1);
   FB_LAUNCH_OK();
   return FB_OK;
 }

@@ -96,6 +96,34 @@ def matmul(lw, uw, lb, ub, W, bias=None):
     return y_lw, y_uw, y_lb, y_ub
 
 
+def relax_coef(op, lw, uw, lb, ub, p, eps, words=1, violation=None):
+    """Relaxation without the rescale pass: returns (c_l, c_u, out_lb, out_ub), all [rows..., Do]."""
+    dev = _chk(lw, uw, lb, ub)
+    rows = lb.numel() // lb.shape[-1]
+    Di, Do = lw.shape[-2], lw.shape[-1]
+    out = tuple(torch.empty_like(lb) for _ in range(4))
+    with torch.cuda.device(dev):
+        check(load().fb_relax_coef_f32(int(op), _p(lw), _p(uw), _p(lb), _p(ub), *[_p(t) for t in out], rows, Di, Do,
+                                       int(words), norm_code(p), float(eps), _p(violation), _stream()), "fb_relax_coef_f32")
+    return out
+
+
+def matmul_coef(lw, uw, lb, ub, c_l, c_u, W, bias=None):
+    """matmul of (c_l * lw, c_u * uw, lb, ub) with W (+ bias): the consumer side of relax_coef."""
+    dev = _chk(lw, uw, lb, ub, c_l, c_u, W, bias)
+    rows = lb.numel() // lb.shape[-1]
+    Di, Do = lw.shape[-2], lw.shape[-1]
+    Dy = W.shape[0]
+    y_lw = torch.empty(lw.shape[:-1] + (Dy,), device=dev, dtype=torch.float32)
+    y_uw = torch.empty_like(y_lw)
+    y_lb = torch.empty(lb.shape[:-1] + (Dy,), device=dev, dtype=torch.float32)
+    y_ub = torch.empty_like(y_lb)
+    with torch.cuda.device(dev):
+        check(load().fb_matmul_coef_f32(_p(lw), _p(uw), _p(lb), _p(ub), _p(c_l), _p(c_u), _p(W), _p(bias), _p(y_lw), _p(y_uw),
+                                        _p(y_lb), _p(y_ub), rows, Di, Do, Dy, _stream()), "fb_matmul_coef_f32")
+    return y_lw, y_uw, y_lb, y_ub
+
+
 def dot_product(x, y, p, eps, words=1, out_scale=1.0, layout=FB_NATIVE, scratch=None, out=None):
     """x, y: (lw, uw, lb, ub).  Returns (z_lw, z_uw, z_lb, z_ub)."""
     x_lw, x_uw, x_lb, x_ub = x

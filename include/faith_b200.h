@@ -107,6 +107,24 @@ int fb_matmul_heads_f32(const float* x_lw, const float* x_uw, const float* x_lb,
                         float* y_lw, float* y_uw, float* y_lb, float* y_ub,
                         int64_t rows, int Di, int Do, int Dy, int L, int heads, void* stream);
 
+/* A relaxation without its rescale pass, and the product that applies it while reading (dense after relu
+ * of the feed-forward block, Bounds.py:921-963 + :397-413; also tanh and exp, whose slopes are positive).
+ * fb_relax_coef_f32 writes, instead of rescaled weights, the own-side slopes c_l, c_u [rows, Do]
+ * (out_lw = c_l * lw, out_uw = c_u * uw) and the relaxed bias terms out_lb, out_ub; a column that would
+ * need a cross term (inverted range l > u) sets bit 1 of *violation, FB_RECIPROCAL is not accepted.
+ * fb_matmul_coef_f32 computes matmul((c_l * x_lw, c_u * x_uw, x_lb, x_ub), W) + bias with x_lb, x_ub the
+ * relaxed bias terms; results equal fb_relax_f32 followed by fb_matmul_f32 bit for bit.  Tensor-core
+ * shapes with Di a multiple of 128 and Do a multiple of 32 only, otherwise FB_ERR_SHAPE and nothing is
+ * launched.  No counterpart in the reference's extension module. */
+int fb_relax_coef_f32(int op, const float* lw, const float* uw, const float* lb, const float* ub,
+                      float* c_l, float* c_u, float* out_lb, float* out_ub,
+                      int64_t rows, int Di, int Do, int words, int p, float eps,
+                      int* violation, void* stream);
+int fb_matmul_coef_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+                       const float* c_l, const float* c_u, const float* W, const float* bias,
+                       float* y_lw, float* y_uw, float* y_lb, float* y_ub,
+                       int64_t rows, int Di, int Do, int Dy, void* stream);
+
 /* The tensor-core GEMM behind fb_matmul_f32 bounds every wait inside the kernel; if a wait ever
  * expires, the kernel raises a device-side flag, frees its tensor memory and returns.  This call
  * synchronises the device, returns the flag in *flag (0 = never raised) and clears it. */

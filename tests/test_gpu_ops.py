@@ -246,6 +246,31 @@ def test_matmul_tensor_core_stage_reuse_is_race_free():
             assert torch.equal(a, b)
 
 
+@pytest.mark.parametrize("op_name", ["relu", "tanh"])
+@pytest.mark.parametrize("p,words,Di", [(float("inf"), 1, 128), (2.0, 2, 256)])
+def test_relaxation_applied_by_the_following_product(op_name, p, words, Di):
+    """fb_relax_coef_f32 + fb_matmul_coef_f32 (slopes applied while the product reads its operands) must
+    reproduce fb_relax_f32 followed by fb_matmul_f32 bit for bit; shapes outside the kernel are refused."""
+    from faith_b200 import ops, _lib
+    op = {"relu": _lib.FB_RELU, "tanh": _lib.FB_TANH}[op_name]
+    B, L, Do, Dy = 2, 5, 96, 72
+    t = cases.rand_bounds(91, B, L, Di, Do, -0.4, 0.6)
+    g0 = torch.Generator().manual_seed(6)
+    W = (torch.randn(Dy, Do, generator=g0) / math.sqrt(Do)).to(DEV)
+    bias = (torch.randn(Dy, generator=g0) * 0.1).to(DEV)
+    lw, lb, uw, ub = [v.to(DEV) for v in t]
+    eps = 0.05
+    r = ops.relax(op, lw, uw, lb, ub, p, eps, words)
+    ref = ops.matmul(r[0], r[1], r[2], r[3], W, bias)
+    c_l, c_u, nlb, nub = ops.relax_coef(op, lw, uw, lb, ub, p, eps, words)
+    assert torch.equal(nlb, r[2]) and torch.equal(nub, r[3])
+    got = ops.matmul_coef(lw, uw, nlb, nub, c_l, c_u, W, bias)
+    for a, b, name in zip(got, ref, ("lw", "uw", "lb", "ub")):
+        assert torch.equal(a, b), name
+    with pytest.raises(_lib.FaithError):   # dim_in not a multiple of 128
+        ops.matmul_coef(lw[:, :, :64].contiguous(), uw[:, :, :64].contiguous(), nlb, nub, c_l, c_u, W, bias)
+
+
 def test_matmul_identity_input():
     """First-layer case: lw = uw = one-hot rows, so every output is a single product 1 * w.  The
     CUDA-core kernel reproduces the reference bit for bit; the tensor-core kernel carries the
