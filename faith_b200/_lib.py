@@ -40,10 +40,14 @@ SIGNATURES = {
     "fb_tc_error_flag": [ctypes.POINTER(_I)],
     "fb_dot_product_f32": [_P] * 16 + [_I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P],
     "fb_matmul_heads_f32": [_P] * 10 + [_L, _I, _I, _I, _I, _I, _P],
+    "fb_matmul_heads_ranges_f32": [_P] * 13 + [_L, _I, _I, _I, _I, _I, _I, _I, _F, _P],
     "fb_relax_coef_f32": [_I] + [_P] * 8 + [_L, _I, _I, _I, _I, _F, _P, _P],
+    "fb_relax_coef_given_f32": [_I] + [_P] * 8 + [_L, _I, _P, _P],
     "fb_matmul_coef_f32": [_P] * 12 + [_L, _I, _I, _I, _P],
     "fb_dot_product_heads_f32": [_P] * 16 + [_I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _P],
+    "fb_dot_product_given_f32": [_P] * 16 + [_I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _P],
     "fb_context_heads_f32": [_P] * 16 + [_I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P],
+    "fb_context_given_f32": [_P] * 16 + [_I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _P],
     "fb_dot_product_noalloc_f32": [_P] * 12 + [_I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P],
     "fb_dot_product_noalloc_max_floats": [],
     "fb_mul_bounds_f32": [_P] * 12 + [_L, _I, _I, _I, _I, _F, _P],

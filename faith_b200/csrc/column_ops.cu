@@ -521,6 +521,24 @@ int launch_relax(int op, const float* lw, const float* uw, const float* lb, cons
   return FB_OK;
 }
 
+
+// Slopes and relaxed bias terms of a relaxation whose concretised ranges are already known (written by
+// the kernel that produced the bound): one thread per (row, column), no access to lw / uw.
+__global__ void __launch_bounds__(256)
+relax_coef_given_kernel(int op, const float* __restrict__ lb, const float* __restrict__ ub, const float* __restrict__ l,
+                        const float* __restrict__ u, float* __restrict__ c_l, float* __restrict__ c_u,
+                        float* __restrict__ o_lb, float* __restrict__ o_ub, int64_t n, int* __restrict__ violation) {
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < n; t += (int64_t)gridDim.x * blockDim.x) {
+    bool bad = false;
+    const ColCoef c = relax_column(op, l[t], u[t], lb[t], ub[t], bad);
+    if (violation != nullptr && (bad || c.c_lu != 0.f || c.c_ul != 0.f)) atomicOr(violation, bad ? 1 : 2);
+    c_l[t] = c.c_ll;
+    c_u[t] = c.c_uu;
+    o_lb[t] = c.nlb;
+    o_ub[t] = c.nub;
+  }
+}
+
 }  // namespace
 }  // namespace fb
 
@@ -651,4 +669,22 @@ extern "C" int fb_relax_coef_f32(int op, const float* lw, const float* uw, const
   ProfileScope prof(PK_RELAX, 4.0 * mw, 4.0 * (2 * mw + 6 * mb), stream);
   return launch_relax(op + OP_COEF_ONLY, lw, uw, lb, ub, c_l, c_u, out_lb, out_ub, rows, Di, Do, words, p, eps,
                       FB_NATIVE, violation, (cudaStream_t)stream);
+}
+
+// fb_relax_coef_f32 for a bound whose concretised range l, u [rows, Do] the caller already holds (e.g. from
+// fb_matmul_heads_ranges_f32): no pass over lw / uw at all.  out_lb / out_ub may alias lb / ub.
+extern "C" int fb_relax_coef_given_f32(int op, const float* lb, const float* ub, const float* l, const float* u,
+                                       float* c_l, float* c_u, float* out_lb, float* out_ub, int64_t rows, int Do,
+                                       int* violation, void* stream) {
+  if (op != FB_RELU && op != FB_TANH && op != FB_EXP) return FB_ERR_ARG;
+  if (rows == 0 || Do == 0) return FB_OK;
+  if (!lb || !ub || !l || !u || !c_l || !c_u || !out_lb || !out_ub) return FB_ERR_ARG;
+  if (rows < 0 || Do < 0) return FB_ERR_ARG;
+  const int64_t n = rows * Do;
+  ProfileScope prof(PK_RELAX, 8.0 * n, 4.0 * 8 * n, stream);
+  const int64_t want = ceil_div(n, 256), cap = (int64_t)device_info().sms * 16;
+  relax_coef_given_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, (cudaStream_t)stream>>>(op, lb, ub, l, u, c_l, c_u,
+                                                                                                out_lb, out_ub, n, violation);
+  FB_LAUNCH_OK();
+  return FB_OK;
 }

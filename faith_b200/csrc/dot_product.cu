@@ -391,12 +391,15 @@ bool dot_force_cuda_cores() {
 
 using namespace fb;
 
-extern "C" int fb_dot_product_heads_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
-                                  const float* y_lw, const float* y_uw, const float* y_lb, const float* y_ub,
-                                  float* z_lw, float* z_uw, float* z_lb, float* z_ub,
-                                  float* x_l, float* x_u, float* y_l, float* y_u,
-                                  int B, int Lx, int Ly, int Di, int K, int words, int p, float eps,
-                                  float out_scale, int layout, int merge_heads, void* stream) {
+// given: bit 0 = x_l / x_u already hold the concretised range of x, bit 1 = y_l / y_u that of y
+// (e.g. from fb_matmul_heads_ranges_f32); the corresponding concretisation pass is skipped.
+static int dot_heads_impl(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+                          const float* y_lw, const float* y_uw, const float* y_lb, const float* y_ub,
+                          float* z_lw, float* z_uw, float* z_lb, float* z_ub,
+                          float* x_l, float* x_u, float* y_l, float* y_u,
+                          int B, int Lx, int Ly, int Di, int K, int words, int p, float eps,
+                          float out_scale, int layout, int merge_heads, int given, void* stream) {
+  if (given < 0 || given > 3) return FB_ERR_ARG;
   if (merge_heads < 1 || (merge_heads > 1 && (layout != FB_NATIVE || B % merge_heads != 0 || K % 4 != 0))) return FB_ERR_ARG;
   if (!x_lw || !x_uw || !x_lb || !x_ub || !y_lw || !y_uw || !y_lb || !y_ub || !z_lw || !z_uw || !z_lb || !z_ub ||
       !x_l || !x_u || !y_l || !y_u)
@@ -413,9 +416,10 @@ extern "C" int fb_dot_product_heads_f32(const float* x_lw, const float* x_uw, co
   const double d1 = (double)Di + 1;
   ProfileScope prof(PK_DOT, 16.0 * B * Lx * Ly * d1 * K,
                     4.0 * (2.0 * B * Lx * d1 * K + 2.0 * B * Ly * d1 * K + 2.0 * B * Lx * Ly * d1), stream);
-  int rc = fb_concretize_f32(x_lw, x_uw, x_lb, x_ub, x_l, x_u, (int64_t)B * Lx, Di, K, words, p, eps, layout, stream);
+  int rc = FB_OK;
+  if (!(given & 1)) rc = fb_concretize_f32(x_lw, x_uw, x_lb, x_ub, x_l, x_u, (int64_t)B * Lx, Di, K, words, p, eps, layout, stream);
   if (rc != FB_OK) return rc;
-  rc = fb_concretize_f32(y_lw, y_uw, y_lb, y_ub, y_l, y_u, (int64_t)B * Ly, Di, K, words, p, eps, layout, stream);
+  if (!(given & 2)) rc = fb_concretize_f32(y_lw, y_uw, y_lb, y_ub, y_l, y_u, (int64_t)B * Ly, Di, K, words, p, eps, layout, stream);
   if (rc != FB_OK) return rc;
   {
     const int n_it = (int)ceil_div(Lx, 32), n_jt = (int)ceil_div(Ly, 32);
@@ -471,6 +475,28 @@ extern "C" int fb_dot_product_heads_f32(const float* x_lw, const float* x_uw, co
   return FB_OK;
 }
 
+extern "C" int fb_dot_product_heads_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+                                  const float* y_lw, const float* y_uw, const float* y_lb, const float* y_ub,
+                                  float* z_lw, float* z_uw, float* z_lb, float* z_ub,
+                                  float* x_l, float* x_u, float* y_l, float* y_u,
+                                  int B, int Lx, int Ly, int Di, int K, int words, int p, float eps,
+                                  float out_scale, int layout, int merge_heads, void* stream) {
+  return dot_heads_impl(x_lw, x_uw, x_lb, x_ub, y_lw, y_uw, y_lb, y_ub, z_lw, z_uw, z_lb, z_ub, x_l, x_u, y_l, y_u, B, Lx,
+                        Ly, Di, K, words, p, eps, out_scale, layout, merge_heads, 0, stream);
+}
+
+// fb_dot_product_heads_f32 for operands whose concretised ranges the caller already has (written by the
+// kernel that produced the operand): `given` bit 0 = x_l / x_u are inputs, bit 1 = y_l / y_u are inputs.
+extern "C" int fb_dot_product_given_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+                                  const float* y_lw, const float* y_uw, const float* y_lb, const float* y_ub,
+                                  float* z_lw, float* z_uw, float* z_lb, float* z_ub,
+                                  float* x_l, float* x_u, float* y_l, float* y_u,
+                                  int B, int Lx, int Ly, int Di, int K, int words, int p, float eps,
+                                  float out_scale, int layout, int merge_heads, int given, void* stream) {
+  return dot_heads_impl(x_lw, x_uw, x_lb, x_ub, y_lw, y_uw, y_lb, y_ub, z_lw, z_uw, z_lb, z_ub, x_l, x_u, y_l, y_u, B, Lx,
+                        Ly, Di, K, words, p, eps, out_scale, layout, merge_heads, given, stream);
+}
+
 extern "C" int fb_dot_product_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
                                   const float* y_lw, const float* y_uw, const float* y_lb, const float* y_ub,
                                   float* z_lw, float* z_uw, float* z_lb, float* z_ub,
@@ -505,12 +531,15 @@ __global__ void __launch_bounds__(256) transpose_small_inplace(float* a, float* 
 // fb_dot_product_heads_f32.  Only the shapes of the tensor-core kernel (K = Ly = 32, Lx % 32 == 0,
 // Di % 4 == 0, 16-byte aligned pointers); otherwise FB_ERR_SHAPE and nothing is launched.
 // y_l / y_u receive the concretised value ranges as [B, Ly, K].
-extern "C" int fb_context_heads_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+// `given` as in fb_dot_product_given_f32; given ranges of the values are expected as [B, K, Ly] (the layout
+// of v_lb / v_ub) and are transposed in place like computed ones.
+extern "C" int fb_context_given_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
                                     const float* v_lw, const float* v_uw, const float* v_lb, const float* v_ub,
                                     float* z_lw, float* z_uw, float* z_lb, float* z_ub,
                                     float* x_l, float* x_u, float* y_l, float* y_u,
                                     int B, int Lx, int Ly, int Di, int K, int words, int p, float eps,
-                                    float out_scale, int merge_heads, void* stream) {
+                                    float out_scale, int merge_heads, int given, void* stream) {
+  if (given < 0 || given > 3) return FB_ERR_ARG;
   if (!x_lw || !x_uw || !x_lb || !x_ub || !v_lw || !v_uw || !v_lb || !v_ub || !z_lw || !z_uw || !z_lb || !z_ub ||
       !x_l || !x_u || !y_l || !y_u)
     return FB_ERR_ARG;
@@ -525,10 +554,11 @@ extern "C" int fb_context_heads_f32(const float* x_lw, const float* x_uw, const 
   const double d1 = (double)Di + 1;
   ProfileScope prof(PK_DOT, 16.0 * B * Lx * Ly * d1 * K,
                     4.0 * (2.0 * B * Lx * d1 * K + 2.0 * B * Ly * d1 * K + 2.0 * B * Lx * Ly * d1), stream);
-  int rc = fb_concretize_f32(x_lw, x_uw, x_lb, x_ub, x_l, x_u, (int64_t)B * Lx, Di, K, words, p, eps, FB_NATIVE, stream);
+  int rc = FB_OK;
+  if (!(given & 1)) rc = fb_concretize_f32(x_lw, x_uw, x_lb, x_ub, x_l, x_u, (int64_t)B * Lx, Di, K, words, p, eps, FB_NATIVE, stream);
   if (rc != FB_OK) return rc;
   // ranges of the values in their own layout [B, K, Ly], then transposed in place to [B, Ly, K]
-  rc = fb_concretize_f32(v_lw, v_uw, v_lb, v_ub, y_l, y_u, (int64_t)B * K, Di, Ly, words, p, eps, FB_NATIVE, stream);
+  if (!(given & 2)) rc = fb_concretize_f32(v_lw, v_uw, v_lb, v_ub, y_l, y_u, (int64_t)B * K, Di, Ly, words, p, eps, FB_NATIVE, stream);
   if (rc != FB_OK) return rc;
   transpose_small_inplace<<<(unsigned)B, 256, 0, st>>>(y_l, y_u, K, Ly);
   FB_LAUNCH_OK();
@@ -539,6 +569,16 @@ extern "C" int fb_context_heads_f32(const float* x_lw, const float* x_uw, const 
     FB_LAUNCH_OK();
   }
   return launch_dot_weight_tc(x_lw, x_uw, v_lw, v_uw, x_l, y_l, y_u, z_lw, z_uw, B, Lx, Ly, Di, out_scale, merge_heads, 1, st);
+}
+
+extern "C" int fb_context_heads_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+                                    const float* v_lw, const float* v_uw, const float* v_lb, const float* v_ub,
+                                    float* z_lw, float* z_uw, float* z_lb, float* z_ub,
+                                    float* x_l, float* x_u, float* y_l, float* y_u,
+                                    int B, int Lx, int Ly, int Di, int K, int words, int p, float eps,
+                                    float out_scale, int merge_heads, void* stream) {
+  return fb_context_given_f32(x_lw, x_uw, x_lb, x_ub, v_lw, v_uw, v_lb, v_ub, z_lw, z_uw, z_lb, z_ub, x_l, x_u, y_l, y_u, B,
+                              Lx, Ly, Di, K, words, p, eps, out_scale, merge_heads, 0, stream);
 }
 
 // ---------------------------------------------------------------------------

@@ -27,6 +27,7 @@ struct Plan {
   int64_t slot_bytes;        // one slot: lw, uw, lb, ub
   int64_t range_floats;      // one operand-range scratch tensor of the dot product
   int64_t small_bytes;       // folded classifier weight + bias
+  int64_t norm_floats;       // column norms that the projection GEMMs hand to the range kernel (lower + upper)
   int64_t total;
 };
 
@@ -41,7 +42,8 @@ Plan make_plan(const fb_encoder* e, int S, int L, int words) {
   const int64_t d = D / H;
   p.range_floats = (int64_t)S * H * (L > d ? L : d) * (L > d ? L : d);
   p.small_bytes = align_up((D + 1) * 4, 256);
-  p.total = 4 * p.slot_bytes + 4 * align_up(p.range_floats * 4, 256) + p.small_bytes;
+  p.norm_floats = 2 * (int64_t)S * L * words * (D > F ? D : F);
+  p.total = 4 * p.slot_bytes + 4 * align_up(p.range_floats * 4, 256) + p.small_bytes + align_up(p.norm_floats * 4, 256);
   return p;
 }
 
@@ -154,6 +156,8 @@ extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, i
     range[i] = reinterpret_cast<float*>(base + 4 * plan.slot_bytes + i * align_up(plan.range_floats * 4, 256));
   float* fold_w = reinterpret_cast<float*>(base + 4 * plan.slot_bytes + 4 * align_up(plan.range_floats * 4, 256));
   float* fold_b = fold_w + D;
+  float* norm_ws = reinterpret_cast<float*>(base + 4 * plan.slot_bytes + 4 * align_up(plan.range_floats * 4, 256) +
+                                            plan.small_bytes);
 
   FB_CUDA_OK(cudaMemsetAsync(violation, 0, sizeof(int), st));
 
@@ -174,15 +178,34 @@ extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, i
     const fb_encoder_layer& ly = enc->layer[li];
     const BoundSet X = slot[A], T3 = slot[Dd];
     BoundSet T1 = slot[B], T2 = slot[C];
-    // queries and keys, split into heads: [S*H, L, Di, d]
-    FB_TRY(fb_matmul_heads_f32(X.lw, X.uw, X.lb, X.ub, ly.q_w, ly.q_b, T2.lw, T2.uw, T2.lb, T2.ub, rows, Di, D, D, L, H,
-                               stream));
-    FB_TRY(fb_matmul_heads_f32(X.lw, X.uw, X.lb, X.ub, ly.k_w, ly.k_b, T3.lw, T3.uw, T3.lb, T3.ub, rows, Di, D, D, L, H,
-                               stream));
+    // queries and keys, split into heads: [S*H, L, Di, d].  Where the shapes allow it the projection also
+    // returns the concretised range of its result (column norms taken in the GEMM epilogue), which the
+    // product below would otherwise compute in a pass of its own over the operand.
+    int given = 0;
+    int qrc = fb_matmul_heads_ranges_f32(X.lw, X.uw, X.lb, X.ub, ly.q_w, ly.q_b, T2.lw, T2.uw, T2.lb, T2.ub, range[0],
+                                         range[1], norm_ws, rows, Di, D, D, L, H, words, p, eps, stream);
+    if (qrc == FB_OK) {
+      given |= 1;
+    } else if (qrc == FB_ERR_SHAPE) {
+      FB_TRY(fb_matmul_heads_f32(X.lw, X.uw, X.lb, X.ub, ly.q_w, ly.q_b, T2.lw, T2.uw, T2.lb, T2.ub, rows, Di, D, D, L, H,
+                                 stream));
+    } else {
+      return qrc;
+    }
+    qrc = fb_matmul_heads_ranges_f32(X.lw, X.uw, X.lb, X.ub, ly.k_w, ly.k_b, T3.lw, T3.uw, T3.lb, T3.ub, range[2], range[3],
+                                     norm_ws, rows, Di, D, D, L, H, words, p, eps, stream);
+    if (qrc == FB_OK) {
+      given |= 2;
+    } else if (qrc == FB_ERR_SHAPE) {
+      FB_TRY(fb_matmul_heads_f32(X.lw, X.uw, X.lb, X.ub, ly.k_w, ly.k_b, T3.lw, T3.uw, T3.lb, T3.ub, rows, Di, D, D, L, H,
+                                 stream));
+    } else {
+      return qrc;
+    }
     // scores [S*H, L, Di, L], scaled by 1/sqrt(d) -> T1
-    FB_TRY(fb_dot_product_f32(T2.lw, T2.uw, T2.lb, T2.ub, T3.lw, T3.uw, T3.lb, T3.ub, T1.lw, T1.uw, T1.lb, T1.ub,
-                              range[0], range[1], range[2], range[3], S * H, L, L, Di, d, words, p, eps, inv_sqrt_d,
-                              FB_NATIVE, stream));
+    FB_TRY(fb_dot_product_given_f32(T2.lw, T2.uw, T2.lb, T2.ub, T3.lw, T3.uw, T3.lb, T3.ub, T1.lw, T1.uw, T1.lb, T1.ub,
+                                    range[0], range[1], range[2], range[3], S * H, L, L, Di, d, words, p, eps, inv_sqrt_d,
+                                    FB_NATIVE, 1, given, stream));
     const int64_t hrows = (int64_t)S * H * L;
     // softmax: fused kernel when the score row fits one tile, else exp / row sum / reciprocal / product
     int src = fb_softmax_f32(T1.lw, T1.uw, T1.lb, T1.ub, T2.lw, T2.uw, T2.lb, T2.ub, hrows, Di, L, words, p, eps,
@@ -203,11 +226,21 @@ extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, i
     // values, split into heads [S*H, L, Di, d]; the tensor-core context product reads them in this layout
     int crc = FB_ERR_SHAPE;
     if (L % 4 == 0) {
-      FB_TRY(fb_matmul_heads_f32(X.lw, X.uw, X.lb, X.ub, ly.v_w, ly.v_b, T3.lw, T3.uw, T3.lb, T3.ub, rows, Di, D, D, L, H,
-                                 stream));
+      int vgiven = 0;
+      const int vrc = fb_matmul_heads_ranges_f32(X.lw, X.uw, X.lb, X.ub, ly.v_w, ly.v_b, T3.lw, T3.uw, T3.lb, T3.ub, range[2],
+                                                 range[3], norm_ws, rows, Di, D, D, L, H, words, p, eps, stream);
+      if (vrc == FB_OK) {
+        vgiven = 2;
+      } else if (vrc == FB_ERR_SHAPE) {
+        FB_TRY(fb_matmul_heads_f32(X.lw, X.uw, X.lb, X.ub, ly.v_w, ly.v_b, T3.lw, T3.uw, T3.lb, T3.ub, rows, Di, D, D, L, H,
+                                   stream));
+      } else {
+        return vrc;
+      }
       // context, written head-merged as [S, L, Di, D] -> T2
-      crc = fb_context_heads_f32(T1.lw, T1.uw, T1.lb, T1.ub, T3.lw, T3.uw, T3.lb, T3.ub, T2.lw, T2.uw, T2.lb, T2.ub,
-                                 range[0], range[1], range[2], range[3], S * H, L, d, Di, L, words, p, eps, 1.0f, H, stream);
+      crc = fb_context_given_f32(T1.lw, T1.uw, T1.lb, T1.ub, T3.lw, T3.uw, T3.lb, T3.ub, T2.lw, T2.uw, T2.lb, T2.ub,
+                                 range[0], range[1], range[2], range[3], S * H, L, d, Di, L, words, p, eps, 1.0f, H, vgiven,
+                                 stream);
       if (crc != FB_OK && crc != FB_ERR_SHAPE) return crc;
     }
     if (crc == FB_ERR_SHAPE) {
@@ -231,11 +264,19 @@ extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, i
     FB_TRY(dense(T2, ly.ao_w, ly.ao_b, T1, rows, Di, D, D, stream));
     FB_TRY(norm_residual(enc, T1, &X, ly.ln1_g, ly.ln1_b, T3, rows, Di, D, stream));
     // feed-forward: dense, relu, dense, + residual, layer norm
-    FB_TRY(dense(T3, ly.f1_w, ly.f1_b, T1, rows, Di, D, F, stream));
     // Where the shapes allow it the relu is not materialised: its column slopes go to the (now unused)
-    // slot of the layer input and the second product applies them while it reads the hidden bounds.
-    int frc = fb_relax_coef_f32(FB_RELU, T1.lw, T1.uw, T1.lb, T1.ub, X.lw, X.uw, T2.lb, T2.ub, rows, Di, F, words, p, eps,
-                                nullptr, stream);
+    // slot of the layer input and the second product applies them while it reads the hidden bounds.  The
+    // first product hands over the concretised range of the hidden bounds (into the unused lb / ub of
+    // that slot), so the slopes need no pass over the hidden weights either.
+    int frc = fb_matmul_heads_ranges_f32(T3.lw, T3.uw, T3.lb, T3.ub, ly.f1_w, ly.f1_b, T1.lw, T1.uw, T1.lb, T1.ub, X.lb, X.ub,
+                                         norm_ws, rows, Di, D, F, L, 1, words, p, eps, stream);
+    if (frc == FB_OK) {
+      frc = fb_relax_coef_given_f32(FB_RELU, T1.lb, T1.ub, X.lb, X.ub, X.lw, X.uw, T2.lb, T2.ub, rows, F, nullptr, stream);
+    } else if (frc == FB_ERR_SHAPE) {
+      FB_TRY(dense(T3, ly.f1_w, ly.f1_b, T1, rows, Di, D, F, stream));
+      frc = fb_relax_coef_f32(FB_RELU, T1.lw, T1.uw, T1.lb, T1.ub, X.lw, X.uw, T2.lb, T2.ub, rows, Di, F, words, p, eps,
+                              nullptr, stream);
+    }
     if (frc == FB_OK)
       frc = fb_matmul_coef_f32(T1.lw, T1.uw, T2.lb, T2.ub, X.lw, X.uw, ly.f2_w, ly.f2_b, T2.lw, T2.uw, X.lb, X.ub, rows, Di,
                                F, D, stream);

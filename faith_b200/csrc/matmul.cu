@@ -10,7 +10,8 @@ bool tc_gemm_supported(const float* a_lo, const float* a_up, const float* W, con
 bool tc_split_supported(int64_t M, int N, int split_rows, int split_d);
 int launch_split_sign_tc(const float* a_lo, const float* a_up, const float* W, const float* bias, float* c_lo,
                          float* c_up, int64_t M, int N, int K, cudaStream_t st, int split_rows, int split_d,
-                         const float* coef_l = nullptr, const float* coef_u = nullptr, int coef_di = 1);
+                         const float* coef_l = nullptr, const float* coef_u = nullptr, int coef_di = 1,
+                         float* norm_lo = nullptr, float* norm_up = nullptr, int norm_p = 0);
 int launch_split_sign_ffma(const float* a_lo, const float* a_up, const float* W, const float* bias, float* c_lo,
                            float* c_up, int64_t M, int N, int K, cudaStream_t st, int split_rows, int split_d);
 
@@ -32,6 +33,31 @@ static int split_sign_gemm(const float* a_lo, const float* a_up, const float* W,
       (split_rows == 0 || tc_split_supported(M, N, split_rows, split_d)))
     return launch_split_sign_tc(a_lo, a_up, W, bias, c_lo, c_up, M, N, K, st, split_rows, split_d);
   return launch_split_sign_ffma(a_lo, a_up, W, bias, c_lo, c_up, M, N, K, st, split_rows, split_d);
+}
+
+// Ranges of a (head-split) product from the per-word-block column norms that the GEMM epilogue wrote:
+//   l[g, l, j] = lb[g, l, j] - eps * sum_w norm_lo[(row * words + w), h * d + j],   g = s * heads + h, row = s * L + l
+// and the mirror for u (Bounds.py:311-326).
+__global__ void __launch_bounds__(256)
+ranges_from_norms_kernel(const float* __restrict__ lb, const float* __restrict__ ub, const float* __restrict__ norm_lo,
+                         const float* __restrict__ norm_up, float* __restrict__ out_l, float* __restrict__ out_u,
+                         int64_t total, int L, int heads, int d, int words, float eps) {
+  const int Dy = heads * d;
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+    const int j = (int)(t % d);
+    const int l = (int)((t / d) % L);
+    const int64_t g = t / ((int64_t)d * L);
+    const int h = (int)(g % heads);
+    const int64_t row = (g / heads) * L + l;
+    float lo = lb[t], up = ub[t];
+    for (int w = 0; w < words; ++w) {
+      const int64_t o = (row * words + w) * Dy + h * d + j;
+      lo = fadd(lo, fmul(-eps, norm_lo[o]));
+      up = fadd(up, fmul(eps, norm_up[o]));
+    }
+    out_l[t] = lo;
+    out_u[t] = up;
+  }
 }
 }  // namespace fb
 
@@ -88,4 +114,42 @@ extern "C" int fb_matmul_coef_f32(const float* x_lw, const float* x_uw, const fl
   int rc = fb::launch_split_sign_tc(x_lw, x_uw, W, nullptr, y_lw, y_uw, M, Dy, Do, st, 0, 0, c_l, c_u, Di);
   if (rc != FB_OK) return rc;
   return fb::split_sign_gemm(x_lb, x_ub, W, bias, y_lb, y_ub, rows, Dy, Do, st);
+}
+
+// fb_matmul_heads_f32 that also returns the concretised range of its result, y_l / y_u in the layout of
+// y_lb / y_ub: the column norms over dim_in are taken by the GEMM epilogue from the tile it is about to
+// store (one word block of dim_in per 128-row tile), so the dot product that consumes y needs no pass of
+// its own over y_lw / y_uw (Bounds.py:311-326 fused into :397-413).  norm_ws: 2 * rows * words * Dy floats
+// of scratch.  Tensor-core shapes with Di == 128 * words only; otherwise FB_ERR_SHAPE and nothing is
+// launched (run fb_matmul_heads_f32 and fb_concretize_f32).
+extern "C" int fb_matmul_heads_ranges_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+                                          const float* W, const float* bias, float* y_lw, float* y_uw, float* y_lb,
+                                          float* y_ub, float* y_l, float* y_u, float* norm_ws, int64_t rows, int Di,
+                                          int Do, int Dy, int L, int heads, int words, int p, float eps, void* stream) {
+  if (!x_lw || !x_uw || !x_lb || !x_ub || !W || !y_lw || !y_uw || !y_lb || !y_ub || !y_l || !y_u || !norm_ws)
+    return FB_ERR_ARG;
+  if (rows < 0 || Di <= 0 || Do <= 0 || Dy <= 0 || words <= 0 || heads < 1 || !fb::valid_norm(p)) return FB_ERR_ARG;
+  if (L <= 0 || rows % L != 0 || Dy % heads != 0) return FB_ERR_ARG;
+  const int64_t M = rows * (int64_t)Di;
+  const int d = Dy / heads;
+  if (!fb::use_tensor_cores() || Di != 128 * words || !fb::tc_gemm_supported(x_lw, x_uw, W, y_lw, y_uw, M, Dy, Do) ||
+      (heads > 1 && !fb::tc_split_supported(M, Dy, L * Di, d)))
+    return FB_ERR_SHAPE;
+  if (rows == 0) return FB_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const double Mt = (double)rows * (Di + 1);
+  fb::ProfileScope prof(fb::PK_MATMUL, 8.0 * Mt * Do * Dy, 4.0 * (2 * Mt * Do + 2 * Mt * Dy + (double)Do * Dy + Dy), stream);
+  float* norm_lo = norm_ws;
+  float* norm_up = norm_ws + rows * words * Dy;
+  int rc = fb::launch_split_sign_tc(x_lw, x_uw, W, nullptr, y_lw, y_uw, M, Dy, Do, st, heads > 1 ? L * Di : 0,
+                                    heads > 1 ? d : 0, nullptr, nullptr, 1, norm_lo, norm_up, p);
+  if (rc != FB_OK) return rc;
+  rc = fb::split_sign_gemm(x_lb, x_ub, W, bias, y_lb, y_ub, rows, Dy, Do, st, heads > 1 ? L : 0, heads > 1 ? d : 0);
+  if (rc != FB_OK) return rc;
+  const int64_t total = rows * Dy;
+  const int64_t want = fb::ceil_div(total, 256), cap = (int64_t)fb::device_info().sms * 8;
+  fb::ranges_from_norms_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, st>>>(y_lb, y_ub, norm_lo, norm_up, y_l, y_u,
+                                                                                   total, L, heads, d, words, eps);
+  FB_LAUNCH_OK();
+  return FB_OK;
 }

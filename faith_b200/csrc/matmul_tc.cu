@@ -129,13 +129,18 @@ struct SharedLayout {
 
 // kCoef: column slopes of a relaxation are applied to the operands on the fly (a separate instantiation, so
 // that the plain kernel keeps its register allocation).
-template <bool kCoef>
+// kNorm: the epilogue also writes the dual norm over the 128 rows of every output column of the tile,
+// norm_lo / norm_up [M / 128][N] (norm_p as in the concretisation: sum |x|, sqrt(sum x^2) or max |x|).  With one
+// word block of dim_in per tile that is the concretisation term of the result, so the product that
+// consumes it needs no pass of its own over y_lw / y_uw.
+template <bool kCoef, bool kNorm>
 __global__ void __launch_bounds__(kThreads, 1)
 split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_constant__ CUtensorMap tm_up,
                    const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_out_lo,
                    const __grid_constant__ CUtensorMap tm_out_up, const float* __restrict__ bias, int64_t M, int N, int K,
                    int n_tiles_n, int64_t total_tiles, int split_rows, int split_d,
-                   const float* __restrict__ coef_l, const float* __restrict__ coef_u, int coef_di) {
+                   const float* __restrict__ coef_l, const float* __restrict__ coef_u, int coef_di,
+                   float* __restrict__ norm_lo, float* __restrict__ norm_up, int norm_p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -346,6 +351,29 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
         }
         tma_store_commit();
       }
+      if (kNorm) {
+        // Column norms of the staged tile.  Warp w reads 16 columns of box w / 2 (lower q0, lower q1, upper q0,
+        // upper q1): lanes 0-15 the rows with bit 2 clear, lanes 16-31 those with bit 2 set, which the
+        // swizzle puts into the other half of the banks.  The next tile overwrites the staging buffer
+        // only behind the rendezvous at the top of the loop.
+        const int ew = warp - kCtrlWarps;
+        const int box = ew >> 1;
+        const int c = (ew & 1) * 16 + (lane & 15);
+        const int rsel = (lane >> 4) * 4;
+        const uint8_t* sb = base_ptr + SharedLayout::out() + (uint32_t)box * kOutBoxBytes + (c & 3) * 4;
+        float acc = 0.f;
+        for (int i8 = 0; i8 < 16; ++i8) {
+          // rows 8 * i8 + rsel + {0, 1, 2, 3}: the four loads first, then the four accumulations
+          float v[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) v[k] = *reinterpret_cast<const float*>(sb + swz(8 * i8 + rsel + k, c >> 2));
+#pragma unroll
+          for (int k = 0; k < 4; ++k) acc = norm_accum(norm_p, acc, v[k]);
+        }
+        acc = norm_finish(norm_p, norm_combine(norm_p, acc, __shfl_xor_sync(0xffffffffu, acc, 16)));
+        const int n = nx + (box & 1) * 32 + c;
+        if (lane < 16 && n < N) (box < 2 ? norm_lo : norm_up)[(int64_t)(my / BM) * N + n] = acc;
+      }
     }
   } else {
     // ------------------------------------------------- converters
@@ -533,7 +561,9 @@ bool tc_gemm_supported(const float* a_lo, const float* a_up, const float* W, con
 
 int launch_split_sign_tc(const float* a_lo, const float* a_up, const float* W, const float* bias, float* c_lo,
                          float* c_up, int64_t M, int N, int K, cudaStream_t st, int split_rows, int split_d,
-                         const float* coef_l, const float* coef_u, int coef_di) {
+                         const float* coef_l, const float* coef_u, int coef_di, float* norm_lo, float* norm_up,
+                         int norm_p) {
+  if (norm_lo != nullptr && (coef_l != nullptr || norm_up == nullptr || M % BM != 0)) return FB_ERR_ARG;
   CUtensorMap tm_lo, tm_up, tm_w, tm_out_lo, tm_out_up;
   if (!make_map(&tm_lo, a_lo, (uint64_t)M, (uint64_t)K, BM) || !make_map(&tm_up, a_up, (uint64_t)M, (uint64_t)K, BM) ||
       !make_map(&tm_w, W, (uint64_t)N, (uint64_t)K, BN) ||
@@ -548,18 +578,22 @@ int launch_split_sign_tc(const float* a_lo, const float* a_up, const float* W, c
   FB_CUDA_OK(cudaGetDevice(&dev));
   cudaError_t attr_err = cudaSuccess;
   std::call_once(attr_once[dev & 63], [&]() {
-    attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
     if (attr_err == cudaSuccess)
-      attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+      attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    if (attr_err == cudaSuccess)
+      attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
   });
   FB_CUDA_OK(attr_err);
   // persistent: one CTA per SM (tensor memory and shared memory allow exactly one)
   const int64_t sms = device_info().sms;
   const unsigned grid = (unsigned)(total_tiles < sms ? total_tiles : sms);
   if (coef_l != nullptr)
-    split_sign_gemm_tc<true><<<grid, kThreads, kSmemBytes, st>>>(tm_lo, tm_up, tm_w, tm_out_lo, tm_out_up, bias, M, N, K, gn, total_tiles, split_rows, split_d, coef_l, coef_u, coef_di);
+    split_sign_gemm_tc<true, false><<<grid, kThreads, kSmemBytes, st>>>(tm_lo, tm_up, tm_w, tm_out_lo, tm_out_up, bias, M, N, K, gn, total_tiles, split_rows, split_d, coef_l, coef_u, coef_di, nullptr, nullptr, 0);
+  else if (norm_lo != nullptr)
+    split_sign_gemm_tc<false, true><<<grid, kThreads, kSmemBytes, st>>>(tm_lo, tm_up, tm_w, tm_out_lo, tm_out_up, bias, M, N, K, gn, total_tiles, split_rows, split_d, nullptr, nullptr, 1, norm_lo, norm_up, norm_p);
   else
-    split_sign_gemm_tc<false><<<grid, kThreads, kSmemBytes, st>>>(tm_lo, tm_up, tm_w, tm_out_lo, tm_out_up, bias, M, N, K, gn, total_tiles, split_rows, split_d, nullptr, nullptr, 1);
+    split_sign_gemm_tc<false, false><<<grid, kThreads, kSmemBytes, st>>>(tm_lo, tm_up, tm_w, tm_out_lo, tm_out_up, bias, M, N, K, gn, total_tiles, split_rows, split_d, nullptr, nullptr, 1, nullptr, nullptr, 0);
   FB_LAUNCH_OK();
   return FB_OK;
 }

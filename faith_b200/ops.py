@@ -108,6 +108,17 @@ def relax_coef(op, lw, uw, lb, ub, p, eps, words=1, violation=None):
     return out
 
 
+def relax_coef_given(op, lb, ub, l, u, violation=None):
+    """relax_coef for a bound whose concretised range (l, u) is already known: no pass over lw / uw."""
+    dev = _chk(lb, ub, l, u)
+    rows = lb.numel() // lb.shape[-1]
+    out = tuple(torch.empty_like(lb) for _ in range(4))
+    with torch.cuda.device(dev):
+        check(load().fb_relax_coef_given_f32(int(op), _p(lb), _p(ub), _p(l), _p(u), *[_p(t) for t in out], rows,
+                                             lb.shape[-1], _p(violation), _stream()), "fb_relax_coef_given_f32")
+    return out
+
+
 def matmul_coef(lw, uw, lb, ub, c_l, c_u, W, bias=None):
     """matmul of (c_l * lw, c_u * uw, lb, ub) with W (+ bias): the consumer side of relax_coef."""
     dev = _chk(lw, uw, lb, ub, c_l, c_u, W, bias)
@@ -122,6 +133,25 @@ def matmul_coef(lw, uw, lb, ub, c_l, c_u, W, bias=None):
         check(load().fb_matmul_coef_f32(_p(lw), _p(uw), _p(lb), _p(ub), _p(c_l), _p(c_u), _p(W), _p(bias), _p(y_lw), _p(y_uw),
                                         _p(y_lb), _p(y_ub), rows, Di, Do, Dy, _stream()), "fb_matmul_coef_f32")
     return y_lw, y_uw, y_lb, y_ub
+
+
+def matmul_heads_ranges(lw, uw, lb, ub, W, bias, heads, p, eps, words=1):
+    """Projection with head-split store that also returns the concretised range of its result: lw, uw
+    [S, L, Di, Do], lb, ub [S, L, Do] -> (y_lw, y_uw [S*heads, L, Di, d], y_lb, y_ub, y_l, y_u [S*heads, L, d]).
+    Raises FaithError (FB_ERR_SHAPE) outside the tensor-core shapes with Di == 128 * words."""
+    dev = _chk(lw, uw, lb, ub, W, bias)
+    S, L, Di, Do = lw.shape
+    Dy = W.shape[0]
+    d = Dy // heads
+    y_lw = torch.empty((S * heads, L, Di, d), device=dev, dtype=torch.float32)
+    y_uw = torch.empty_like(y_lw)
+    y_lb, y_ub, y_l, y_u = (torch.empty((S * heads, L, d), device=dev, dtype=torch.float32) for _ in range(4))
+    ws = torch.empty(2 * S * L * words * Dy, device=dev, dtype=torch.float32)
+    with torch.cuda.device(dev):
+        check(load().fb_matmul_heads_ranges_f32(_p(lw), _p(uw), _p(lb), _p(ub), _p(W), _p(bias), _p(y_lw), _p(y_uw), _p(y_lb),
+                                                _p(y_ub), _p(y_l), _p(y_u), _p(ws), S * L, Di, Do, Dy, L, heads, int(words),
+                                                norm_code(p), float(eps), _stream()), "fb_matmul_heads_ranges_f32")
+    return y_lw, y_uw, y_lb, y_ub, y_l, y_u
 
 
 def dot_product(x, y, p, eps, words=1, out_scale=1.0, layout=FB_NATIVE, scratch=None, out=None):

@@ -107,6 +107,19 @@ int fb_matmul_heads_f32(const float* x_lw, const float* x_uw, const float* x_lb,
                         float* y_lw, float* y_uw, float* y_lb, float* y_ub,
                         int64_t rows, int Di, int Do, int Dy, int L, int heads, void* stream);
 
+/* fb_matmul_heads_f32 that also returns the concretised range of its result (Bounds.py:311-326 on the
+ * output of :397-413): y_l, y_u in the layout of y_lb, y_ub.  The dual norms over dim_in are taken by the
+ * GEMM epilogue from the tile it is about to store, so the dot product that consumes y
+ * (fb_dot_product_given_f32, fb_context_given_f32) needs no pass of its own over y_lw / y_uw.
+ * norm_ws: 2 * rows * words * Dy floats of scratch.  Tensor-core shapes with Di == 128 * words only,
+ * otherwise FB_ERR_SHAPE and nothing is launched.  No counterpart in the reference's extension module. */
+int fb_matmul_heads_ranges_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+                               const float* W, const float* bias,
+                               float* y_lw, float* y_uw, float* y_lb, float* y_ub,
+                               float* y_l, float* y_u, float* norm_ws,
+                               int64_t rows, int Di, int Do, int Dy, int L, int heads,
+                               int words, int p, float eps, void* stream);
+
 /* A relaxation without its rescale pass, and the product that applies it while reading (dense after relu
  * of the feed-forward block, Bounds.py:921-963 + :397-413; also tanh and exp, whose slopes are positive).
  * fb_relax_coef_f32 writes, instead of rescaled weights, the own-side slopes c_l, c_u [rows, Do]
@@ -120,6 +133,11 @@ int fb_relax_coef_f32(int op, const float* lw, const float* uw, const float* lb,
                       float* c_l, float* c_u, float* out_lb, float* out_ub,
                       int64_t rows, int Di, int Do, int words, int p, float eps,
                       int* violation, void* stream);
+/* fb_relax_coef_f32 for a bound whose concretised range l, u [rows, Do] the caller already holds (e.g. from
+ * fb_matmul_heads_ranges_f32 with heads = 1): no pass over lw / uw. */
+int fb_relax_coef_given_f32(int op, const float* lb, const float* ub, const float* l, const float* u,
+                            float* c_l, float* c_u, float* out_lb, float* out_ub,
+                            int64_t rows, int Do, int* violation, void* stream);
 int fb_matmul_coef_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
                        const float* c_l, const float* c_u, const float* W, const float* bias,
                        float* y_lw, float* y_uw, float* y_lb, float* y_ub,
@@ -157,6 +175,16 @@ int fb_dot_product_heads_f32(const float* x_lw, const float* x_uw, const float* 
                              int B, int Lx, int Ly, int Di, int K, int words, int p, float eps,
                              float out_scale, int layout, int merge_heads, void* stream);
 
+/* fb_dot_product_heads_f32 for operands whose concretised ranges the caller already holds (written by
+ * the kernel that produced the operand, e.g. fb_matmul_heads_ranges_f32): bit 0 of `given` makes
+ * x_l / x_u inputs, bit 1 y_l / y_u; the corresponding concretisation pass is skipped. */
+int fb_dot_product_given_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+                             const float* y_lw, const float* y_uw, const float* y_lb, const float* y_ub,
+                             float* z_lw, float* z_uw, float* z_lb, float* z_ub,
+                             float* x_l, float* x_u, float* y_l, float* y_u,
+                             int B, int Lx, int Ly, int Di, int K, int words, int p, float eps,
+                             float out_scale, int layout, int merge_heads, int given, void* stream);
+
 /* Context product of the attention block, Bounds.context (Bounds.py:843-850: dot_product with V.t()),
  * taking the values in the layout the projection writes, v_lw / v_uw [B, K, Di, Ly] and v_lb / v_ub
  * [B, K, Ly] (K = key positions, Ly = head features), so that no transposed copy of V is needed
@@ -172,6 +200,15 @@ int fb_context_heads_f32(const float* x_lw, const float* x_uw, const float* x_lb
                          float* x_l, float* x_u, float* y_l, float* y_u,
                          int B, int Lx, int Ly, int Di, int K, int words, int p, float eps,
                          float out_scale, int merge_heads, void* stream);
+
+/* fb_context_heads_f32 with `given` as in fb_dot_product_given_f32; given value ranges are expected as
+ * [B, K, Ly] (the layout of v_lb / v_ub) and are transposed in place to [B, Ly, K] like computed ones. */
+int fb_context_given_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+                         const float* v_lw, const float* v_uw, const float* v_lb, const float* v_ub,
+                         float* z_lw, float* z_uw, float* z_lb, float* z_ub,
+                         float* x_l, float* x_u, float* y_l, float* y_u,
+                         int B, int Lx, int Ly, int Di, int K, int words, int p, float eps,
+                         float out_scale, int merge_heads, int given, void* stream);
 
 /* The same operator for callers that cannot allocate device memory.  (No counterpart in the
  * reference, whose callers always allocate the scratch tensors themselves.)

@@ -520,3 +520,107 @@ def test_fused_softmax_matches_oracle_and_chain(shape, p, words):
     for k, i in (("lw", 0), ("uw", 1), ("lb", 2), ("ub", 3)):
         helpers.assert_close(fused[i], getattr(o, k), "fused softmax %s vs oracle" % k)
         helpers.assert_close(fused[i], getattr(chain, k), "fused softmax %s vs chain" % k)
+
+
+@pytest.mark.parametrize("p,words", [(float("inf"), 1), (2.0, 1), (1.0, 1), (2.0, 2), (float("inf"), 2)])
+def test_projection_returns_ranges_for_the_dot_product(p, words):
+    """fb_matmul_heads_ranges_f32: same bounds as fb_matmul_heads_f32 bit for bit, ranges equal to a
+    concretisation pass over them, and the dot product / context product fed with those ranges
+    (fb_dot_product_given_f32, fb_context_given_f32) equal to the ones that concretise themselves."""
+    from faith_b200 import _lib, ops
+    lib = _lib.load()
+    S, L, H, d = 2, 32, 4, 32
+    D, Di, eps = H * d, 128 * words, 0.05
+    st = torch.cuda.current_stream().cuda_stream
+    g = torch.Generator().manual_seed(11)
+
+    def project(seed):
+        t = [v.to(DEV) for v in cases.rand_bounds(seed, S, L, Di, D)]
+        W = (torch.randn(D, D, generator=g) / math.sqrt(D)).to(DEV)
+        bias = (torch.randn(D, generator=g) * 0.1).to(DEV)
+        y = ops.matmul_heads_ranges(t[0], t[2], t[1], t[3], W, bias, H, p, eps, words)
+        z = [torch.empty_like(y[0]), torch.empty_like(y[0]), torch.empty_like(y[2]), torch.empty_like(y[2])]
+        _lib.check(lib.fb_matmul_heads_f32(t[0].data_ptr(), t[2].data_ptr(), t[1].data_ptr(), t[3].data_ptr(), W.data_ptr(),
+                                           bias.data_ptr(), *[v.data_ptr() for v in z], S * L, Di, D, D, L, H, st),
+                   "fb_matmul_heads_f32")
+        for a, b in zip(y[:4], z):
+            assert torch.equal(a, b)
+        l, u = ops.concretize(y[0], y[1], y[2], y[3], p, eps, words)
+        helpers.assert_close(y[4], l, "range l from the GEMM epilogue")
+        helpers.assert_close(y[5], u, "range u from the GEMM epilogue")
+        return y
+
+    q, k = project(701), project(702)
+    B = S * H
+
+    def run(fn, name, x, y, zshape, zbshape, ranges, extra):
+        z = [torch.full(zshape, float("nan"), device=DEV), torch.full(zshape, float("nan"), device=DEV),
+             torch.full(zbshape, float("nan"), device=DEV), torch.full(zbshape, float("nan"), device=DEV)]
+        ptrs = [t.data_ptr() for t in x[:4]] + [t.data_ptr() for t in y[:4]] + [t.data_ptr() for t in z] + \
+               [t.data_ptr() for t in ranges]
+        _lib.check(fn(*ptrs, *extra, st), name)
+        return z
+
+    # The products fed with ranges (here: the ones a concretisation pass computes, so that the comparison
+    # is exact) equal the products that concretise themselves, and the given ranges stay untouched.
+    def conc(b):
+        return [v.contiguous() for v in ops.concretize(b[0], b[1], b[2], b[3], p, eps, words)]
+
+    ql, qu = conc(q)
+    kl, ku = conc(k)
+    rg = [ql.clone(), qu.clone(), kl.clone(), ku.clone()]
+    rs = [torch.empty_like(v) for v in rg]
+    common = (B, L, L, Di, d, words, ops.norm_code(p), eps, 0.25)
+    zg = run(lib.fb_dot_product_given_f32, "fb_dot_product_given_f32", q, k, (B, L, Di, L), (B, L, L), rg,
+             common + (_lib.FB_NATIVE, 1, 3))
+    zs = run(lib.fb_dot_product_given_f32, "fb_dot_product_given_f32", q, k, (B, L, Di, L), (B, L, L), rs,
+             common + (_lib.FB_NATIVE, 1, 0))
+    for a, b in zip(rg, (ql, qu, kl, ku)):
+        assert torch.equal(a, b)
+    for a, b in zip(rs, (ql, qu, kl, ku)):
+        assert torch.equal(a, b)
+    for a, b in zip(zg, zs):
+        assert torch.equal(a, b)
+    # with the epilogue's own ranges (last-bit differences in the norms): close
+    re_ = [q[4].clone(), q[5].clone(), k[4].clone(), k[5].clone()]
+    ze = run(lib.fb_dot_product_given_f32, "fb_dot_product_given_f32", q, k, (B, L, Di, L), (B, L, L), re_,
+             common + (_lib.FB_NATIVE, 1, 3))
+    for a, b, name in zip(ze, zs, ("lw", "uw", "lb", "ub")):
+        helpers.assert_close(a, b, "scores %s with the epilogue's ranges" % name, atol=4e-6)
+    # context: x = the scores scaled down, values = k in the projection's layout [B, K, Di, Ly], value ranges given
+    x = [v * 0.05 for v in zs]
+    vr = [torch.empty(B, L, L, device=DEV), torch.empty(B, L, L, device=DEV), kl.clone(), ku.clone()]
+    vs = [torch.empty(B, L, L, device=DEV), torch.empty(B, L, L, device=DEV), torch.empty(B, d, L, device=DEV),
+          torch.empty(B, d, L, device=DEV)]
+    ccommon = (B, L, d, Di, L, words, ops.norm_code(p), eps, 1.0, H)
+    cg = run(lib.fb_context_given_f32, "fb_context_given_f32", x, k, (S, L, Di, D), (S, L, D), vr, ccommon + (2,))
+    cs = run(lib.fb_context_given_f32, "fb_context_given_f32", x, k, (S, L, Di, D), (S, L, D), vs, ccommon + (0,))
+    for a, b in zip(vr, vs):
+        assert torch.equal(a, b)          # both hold the transposed value ranges now
+    for a, b in zip(cg, cs):
+        assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("op_name", ["relu", "tanh"])
+@pytest.mark.parametrize("p,words", [(float("inf"), 1), (2.0, 2), (1.0, 1)])
+def test_relaxation_slopes_from_given_ranges(op_name, p, words):
+    """fb_relax_coef_given_f32 (ranges handed over by the producer) equals fb_relax_coef_f32 (ranges from a
+    pass over lw / uw) bit for bit when it is given the ranges of a concretisation pass; and a hidden layer
+    produced by fb_matmul_heads_ranges_f32 (heads = 1) yields slopes within the per-operator bar."""
+    from faith_b200 import ops, _lib
+    op = {"relu": _lib.FB_RELU, "tanh": _lib.FB_TANH}[op_name]
+    S, L, D, F, eps = 2, 4, 64, 96, 0.05
+    Di = 128 * words
+    t = [v.to(DEV) for v in cases.rand_bounds(95, S, L, Di, D, -0.4, 0.6)]
+    g0 = torch.Generator().manual_seed(8)
+    W = (torch.randn(F, D, generator=g0) / math.sqrt(D)).to(DEV)
+    bias = (torch.randn(F, generator=g0) * 0.1).to(DEV)
+    y = ops.matmul_heads_ranges(t[0], t[2], t[1], t[3], W, bias, 1, p, eps, words)   # hidden bounds [S, L, Di, F] + ranges
+    ref = ops.relax_coef(op, y[0], y[1], y[2], y[3], p, eps, words)
+    l, u = ops.concretize(y[0], y[1], y[2], y[3], p, eps, words)
+    same = ops.relax_coef_given(op, y[2], y[3], l.contiguous(), u.contiguous())
+    for a, b, name in zip(same, ref, ("c_l", "c_u", "lb", "ub")):
+        assert torch.equal(a, b), name
+    got = ops.relax_coef_given(op, y[2], y[3], y[4], y[5])
+    for a, b, name in zip(got, ref, ("c_l", "c_u", "lb", "ub")):
+        helpers.assert_close(a, b, "%s %s from the epilogue's ranges" % (op_name, name), atol=2e-6)
