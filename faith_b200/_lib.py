@@ -55,6 +55,7 @@ SIGNATURES = {
     "fb_scale_f32": [_P] * 8 + [_L, _I, _I, _F, _P],
     "fb_rowsum_f32": [_P] * 8 + [_L, _I, _I, _P],
     "fb_softmax_f32": [_P] * 8 + [_L, _I, _I, _I, _I, _F, _P, _P],
+    "fb_softmax_ranges_f32": [_P] * 10 + [_L, _I, _I, _I, _I, _F, _P, _P],
     "fb_layernorm_novar_f32": [_P] * 14 + [_L, _I, _I, _P],
     "fb_split_heads_f32": [_P] * 4 + [_I] * 6 + [_P],
     "fb_merge_heads_f32": [_P] * 4 + [_I] * 5 + [_P],

@@ -208,9 +208,12 @@ extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, i
                                     FB_NATIVE, 1, given, stream));
     const int64_t hrows = (int64_t)S * H * L;
     // softmax: fused kernel when the score row fits one tile, else exp / row sum / reciprocal / product
-    int src = fb_softmax_f32(T1.lw, T1.uw, T1.lb, T1.ub, T2.lw, T2.uw, T2.lb, T2.ub, hrows, Di, L, words, p, eps,
-                             violation, stream);
+    // (the fused kernel also returns the concretised range of the probabilities for the context product)
+    int pgiven = 0;
+    int src = fb_softmax_ranges_f32(T1.lw, T1.uw, T1.lb, T1.ub, T2.lw, T2.uw, T2.lb, T2.ub, range[0], range[1], hrows, Di,
+                                    L, words, p, eps, violation, stream);
     if (src == FB_OK) {
+      pgiven = 1;
       // probabilities are in T2; the stages below expect them in T1
       std::swap(T1, T2);
       std::swap(B, C);
@@ -226,11 +229,11 @@ extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, i
     // values, split into heads [S*H, L, Di, d]; the tensor-core context product reads them in this layout
     int crc = FB_ERR_SHAPE;
     if (L % 4 == 0) {
-      int vgiven = 0;
+      int vgiven = pgiven;
       const int vrc = fb_matmul_heads_ranges_f32(X.lw, X.uw, X.lb, X.ub, ly.v_w, ly.v_b, T3.lw, T3.uw, T3.lb, T3.ub, range[2],
                                                  range[3], norm_ws, rows, Di, D, D, L, H, words, p, eps, stream);
       if (vrc == FB_OK) {
-        vgiven = 2;
+        vgiven |= 2;
       } else if (vrc == FB_ERR_SHAPE) {
         FB_TRY(fb_matmul_heads_f32(X.lw, X.uw, X.lb, X.ub, ly.v_w, ly.v_b, T3.lw, T3.uw, T3.lb, T3.ub, rows, Di, D, D, L, H,
                                    stream));

@@ -31,7 +31,8 @@ __device__ __forceinline__ float block_reduce(float v, int p, float* s_tmp) {
 __global__ void __launch_bounds__(kThreads)
 softmax_bounds_kernel(const float* __restrict__ lw, const float* __restrict__ uw, const float* __restrict__ lb,
                       const float* __restrict__ ub, float* __restrict__ o_lw, float* __restrict__ o_uw,
-                      float* __restrict__ o_lb, float* __restrict__ o_ub, int Di, int Do, int words, int p, float eps,
+                      float* __restrict__ o_lb, float* __restrict__ o_ub, float* __restrict__ o_l,
+                      float* __restrict__ o_u, int Di, int Do, int words, int p, float eps,
                       int* __restrict__ violation) {
   extern __shared__ __align__(16) float smem[];
   float* s_l = smem;                       // [Di][32] scores lw
@@ -179,34 +180,81 @@ softmax_bounds_kernel(const float* __restrict__ lw, const float* __restrict__ uw
   // lower plane: alpha = l(1/sum) on exp, beta = l(exp) on 1/sum; upper plane: alpha = u(1/sum), beta = l(exp)
   const float al_ = lr, au_ = ur;
   __syncthreads();
+  float res_lb = 0.f, res_ub = 0.f;   // bias terms of the result, column tid
   if (mine) {
     const float be = c_la[tid];
     const float gl_ = fmul(-al_, be), gu_ = fmul(-au_, be);
     const float tl = fadd(fmul(al_ > 0.f ? c_elb[tid] : c_eub[tid], al_), gl_);
     const float tu = fadd(fmul(au_ > 0.f ? c_eub[tid] : c_elb[tid], au_), gu_);
-    o_lb[row * Do + tid] = fadd(tl, fmul(be > 0.f ? rc.nlb : rc.nub, be));
-    o_ub[row * Do + tid] = fadd(tu, fmul(be > 0.f ? rc.nub : rc.nlb, be));
+    res_lb = fadd(tl, fmul(be > 0.f ? rc.nlb : rc.nub, be));
+    res_ub = fadd(tu, fmul(be > 0.f ? rc.nub : rc.nlb, be));
+    o_lb[row * Do + tid] = res_lb;
+    o_ub[row * Do + tid] = res_ub;
   }
-  if (!col_ok) return;
-  float kl[4], ku[4], be[4];
+  const bool want_ranges = o_l != nullptr;   // uniform
+  if (!col_ok && !want_ranges) return;
+  float kl[4] = {0.f, 0.f, 0.f, 0.f}, ku[4] = {0.f, 0.f, 0.f, 0.f}, be[4] = {0.f, 0.f, 0.f, 0.f};
+  if (col_ok) {
 #pragma unroll
-  for (int e = 0; e < 4; ++e) { kl[e] = c_kl[col + e]; ku[e] = c_ku[col + e]; be[e] = c_la[col + e]; }
+    for (int e = 0; e < 4; ++e) { kl[e] = c_kl[col + e]; ku[e] = c_ku[col + e]; be[e] = c_la[col + e]; }
+  }
   float* ol = o_lw + (size_t)row * Di * Do;
   float* ou = o_uw + (size_t)row * Di * Do;
-  for (int r = rg; r < Di; r += 32) {
-    const float4 a4 = *reinterpret_cast<const float4*>(s_l + r * kCW + col);
-    const float4 b4 = *reinterpret_cast<const float4*>(s_u + r * kCW + col);
-    const float a[4] = {a4.x, a4.y, a4.z, a4.w}, b[4] = {b4.x, b4.y, b4.z, b4.w};
-    const float r_l = fmul(s_su[r], kl_r), r_u = fmul(s_sl[r], ku_r);
-    float yl[4], yu[4];
+  // The rows are walked word block by word block, so that the dual norms of the result (its concretised
+  // range, for the product that consumes the probabilities) can be accumulated on the way out.
+  for (int w = 0; w < words; ++w) {
+    float nl[4] = {0.f, 0.f, 0.f, 0.f}, nu[4] = {0.f, 0.f, 0.f, 0.f};
+    if (col_ok) {
+      for (int r = w * blk + rg; r < (w + 1) * blk; r += 32) {
+        const float4 a4 = *reinterpret_cast<const float4*>(s_l + r * kCW + col);
+        const float4 b4 = *reinterpret_cast<const float4*>(s_u + r * kCW + col);
+        const float a[4] = {a4.x, a4.y, a4.z, a4.w}, b[4] = {b4.x, b4.y, b4.z, b4.w};
+        const float r_l = fmul(s_su[r], kl_r), r_u = fmul(s_sl[r], ku_r);
+        float yl[4], yu[4];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const float e_l = fmul(a[e], kl[e]), e_u = fmul(b[e], ku[e]);
-      yl[e] = fadd(fmul(al_ > 0.f ? e_l : e_u, al_), fmul(be[e] > 0.f ? r_l : r_u, be[e]));
-      yu[e] = fadd(fmul(au_ > 0.f ? e_u : e_l, au_), fmul(be[e] > 0.f ? r_u : r_l, be[e]));
+        for (int e = 0; e < 4; ++e) {
+          const float e_l = fmul(a[e], kl[e]), e_u = fmul(b[e], ku[e]);
+          yl[e] = fadd(fmul(al_ > 0.f ? e_l : e_u, al_), fmul(be[e] > 0.f ? r_l : r_u, be[e]));
+          yu[e] = fadd(fmul(au_ > 0.f ? e_u : e_l, au_), fmul(be[e] > 0.f ? r_u : r_l, be[e]));
+          nl[e] = norm_accum(p, nl[e], yl[e]);
+          nu[e] = norm_accum(p, nu[e], yu[e]);
+        }
+        *reinterpret_cast<float4*>(ol + (size_t)r * Do + col) = make_float4(yl[0], yl[1], yl[2], yl[3]);
+        *reinterpret_cast<float4*>(ou + (size_t)r * Do + col) = make_float4(yu[0], yu[1], yu[2], yu[3]);
+      }
     }
-    *reinterpret_cast<float4*>(ol + (size_t)r * Do + col) = make_float4(yl[0], yl[1], yl[2], yl[3]);
-    *reinterpret_cast<float4*>(ou + (size_t)r * Do + col) = make_float4(yu[0], yu[1], yu[2], yu[3]);
+    if (want_ranges) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+#pragma unroll
+        for (int s = 8; s < 32; s <<= 1) {
+          nl[e] = norm_combine(p, nl[e], __shfl_xor_sync(0xffffffffu, nl[e], s));
+          nu[e] = norm_combine(p, nu[e], __shfl_xor_sync(0xffffffffu, nu[e], s));
+        }
+      __syncthreads();
+      if (lane < 8) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          s_red[warp * kCW + lane * 4 + e] = nl[e];
+          s_red[8 * kCW + warp * kCW + lane * 4 + e] = nu[e];
+        }
+      }
+      __syncthreads();
+      if (tid < kCW) {
+        float sl = s_red[tid], su = s_red[8 * kCW + tid];
+#pragma unroll
+        for (int k = 1; k < 8; ++k) {
+          sl = norm_combine(p, sl, s_red[k * kCW + tid]);
+          su = norm_combine(p, su, s_red[8 * kCW + k * kCW + tid]);
+        }
+        res_lb = fadd(res_lb, fmul(-eps, norm_finish(p, sl)));
+        res_ub = fadd(res_ub, fmul(eps, norm_finish(p, su)));
+      }
+    }
+  }
+  if (want_ranges && mine) {
+    o_l[row * Do + tid] = res_lb;
+    o_u[row * Do + tid] = res_ub;
   }
 }
 
@@ -215,9 +263,13 @@ softmax_bounds_kernel(const float* __restrict__ lw, const float* __restrict__ uw
 
 using namespace fb;
 
-extern "C" int fb_softmax_f32(const float* lw, const float* uw, const float* lb, const float* ub, float* out_lw,
-                              float* out_uw, float* out_lb, float* out_ub, int64_t rows, int Di, int Do, int words,
-                              int p, float eps, int* violation, void* stream) {
+// out_l / out_u (both or neither): concretised range of the result, [rows, Do], as fb_concretize_f32 would return
+// it for the written bounds; the kernel accumulates the dual norms while it writes the result.
+extern "C" int fb_softmax_ranges_f32(const float* lw, const float* uw, const float* lb, const float* ub, float* out_lw,
+                                     float* out_uw, float* out_lb, float* out_ub, float* out_l, float* out_u,
+                                     int64_t rows, int Di, int Do, int words, int p, float eps, int* violation,
+                                     void* stream) {
+  if ((out_l == nullptr) != (out_u == nullptr)) return FB_ERR_ARG;
   if (rows == 0) return FB_OK;
   if (!lw || !uw || !lb || !ub || !out_lw || !out_uw || !out_lb || !out_ub) return FB_ERR_ARG;
   if (rows < 0 || Di <= 0 || Do <= 0 || words <= 0 || !valid_norm(p)) return FB_ERR_ARG;
@@ -231,7 +283,15 @@ extern "C" int fb_softmax_f32(const float* lw, const float* uw, const float* lb,
   if (smem > 48 * 1024)
     FB_CUDA_OK(cudaFuncSetAttribute(softmax_bounds_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   softmax_bounds_kernel<<<(unsigned)rows, kThreads, smem, (cudaStream_t)stream>>>(lw, uw, lb, ub, out_lw, out_uw, out_lb,
-                                                                                  out_ub, Di, Do, words, p, eps, violation);
+                                                                                  out_ub, out_l, out_u, Di, Do, words, p,
+                                                                                  eps, violation);
   FB_LAUNCH_OK();
   return FB_OK;
+}
+
+extern "C" int fb_softmax_f32(const float* lw, const float* uw, const float* lb, const float* ub, float* out_lw,
+                              float* out_uw, float* out_lb, float* out_ub, int64_t rows, int Di, int Do, int words,
+                              int p, float eps, int* violation, void* stream) {
+  return fb_softmax_ranges_f32(lw, uw, lb, ub, out_lw, out_uw, out_lb, out_ub, nullptr, nullptr, rows, Di, Do, words, p,
+                               eps, violation, stream);
 }

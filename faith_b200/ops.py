@@ -337,17 +337,20 @@ def relax_with_norms(op, lw, uw, lb, ub, norm_l, norm_u, p, eps, violation=None)
     return out
 
 
-def softmax_fused(x, p, eps, words=1, violation=None):
-    """Fused softmax bound; returns None when the shape needs the unfused chain."""
+def softmax_fused(x, p, eps, words=1, violation=None, ranges=False):
+    """Fused softmax bound; returns None when the shape needs the unfused chain.  ranges=True appends the
+    concretised range (l, u) of the result to the returned tuple."""
     dev = _chk(*x)
     lw, uw, lb, ub = x
     Di, Do = lw.shape[-2], lw.shape[-1]
     rows = lb.numel() // Do
     out = (torch.empty_like(lw), torch.empty_like(uw), torch.empty_like(lb), torch.empty_like(ub))
+    if ranges:
+        out = out + (torch.empty_like(lb), torch.empty_like(ub))
     with torch.cuda.device(dev):
-        rc = load().fb_softmax_f32(*[_p(t) for t in x], *[_p(t) for t in out], rows, Di, Do, words, norm_code(p), eps,
-                                   _p(violation), _stream())
+        rc = load().fb_softmax_ranges_f32(*[_p(t) for t in x], *[_p(t) for t in out], *([] if ranges else [None, None]),
+                                          rows, Di, Do, words, norm_code(p), eps, _p(violation), _stream())
     if rc in (2, 3):   # FB_ERR_SHAPE / FB_ERR_ALIGN: not a fused shape
         return None
-    check(rc, "fb_softmax_f32")
+    check(rc, "fb_softmax_ranges_f32")
     return out

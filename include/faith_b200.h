@@ -274,6 +274,14 @@ int fb_softmax_f32(const float* lw, const float* uw, const float* lb, const floa
                    float* out_lw, float* out_uw, float* out_lb, float* out_ub,
                    int64_t rows, int Di, int Do, int words, int p, float eps, int* violation, void* stream);
 
+/* fb_softmax_f32 that also returns the concretised range of its result, out_l / out_u [rows, Do] (what
+ * fb_concretize_f32 returns for the written bounds): the dual norms are accumulated while the result is
+ * written, so the context product that consumes the probabilities (fb_context_given_f32) needs no pass
+ * of its own over them.  out_l and out_u may both be NULL (= fb_softmax_f32). */
+int fb_softmax_ranges_f32(const float* lw, const float* uw, const float* lb, const float* ub,
+                          float* out_lw, float* out_uw, float* out_lb, float* out_ub, float* out_l, float* out_u,
+                          int64_t rows, int Di, int Do, int words, int p, float eps, int* violation, void* stream);
+
 /* Layer normalisation without the variance ("no_var", Bounds.py:1111-1131), optionally fused
  * with a preceding residual add: t = x (+ r); t -= mean over features of the opposite side;
  * out = t * gamma (split by sign of gamma) + beta on lb/ub.  r_* may all be NULL. */

@@ -624,3 +624,23 @@ def test_relaxation_slopes_from_given_ranges(op_name, p, words):
     got = ops.relax_coef_given(op, y[2], y[3], y[4], y[5])
     for a, b, name in zip(got, ref, ("c_l", "c_u", "lb", "ub")):
         helpers.assert_close(a, b, "%s %s from the epilogue's ranges" % (op_name, name), atol=2e-6)
+
+
+@pytest.mark.parametrize("shape", [(4, 32, 128, 32), (2, 3, 64, 8), (1, 5, 40, 20)])
+@pytest.mark.parametrize("p,words", [(2.0, 1), (float("inf"), 1), (1.0, 2), (2.0, 2)])
+def test_fused_softmax_returns_the_range_of_its_result(shape, p, words):
+    """fb_softmax_ranges_f32: the bounds are those of fb_softmax_f32 bit for bit, and the range it
+    accumulates while writing equals a concretisation pass over the written bounds."""
+    import faith_b200
+    from faith_b200 import ops
+    B, L, Di, Do = shape
+    t = cases.rand_bounds(604, B, L, Di, Do, -0.5, 0.2)
+    g = faith_b200.BoundsLite(p, 0.1, *[v.to(DEV) for v in t], perturbed_words=words)
+    plain = ops.softmax_fused(g._t4(), p, 0.1, words)
+    withr = ops.softmax_fused(g._t4(), p, 0.1, words, ranges=True)
+    assert plain is not None and withr is not None and len(withr) == 6
+    for a, b in zip(plain, withr[:4]):
+        assert torch.equal(a, b)
+    l, u = ops.concretize(plain[0], plain[1], plain[2], plain[3], p, 0.1, words)
+    helpers.assert_close(withr[4], l, "softmax range l")
+    helpers.assert_close(withr[5], u, "softmax range u")
