@@ -14,6 +14,7 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int CC = 4;            // input channels per shared-memory stage
+constexpr int kStageBatch = 6;   // input elements per thread whose global loads are in flight together
 
 template <int TH, int TW, int CO>
 __global__ void __launch_bounds__(kThreads)
@@ -46,17 +47,32 @@ conv_bounds_kernel(const float* __restrict__ x_lo, const float* __restrict__ x_u
   const float* img_lo = x_lo + n * (int64_t)Cin * H * W;
   const float* img_up = x_up + n * (int64_t)Cin * H * W;
   for (int c0 = 0; c0 < Cin; c0 += CC) {
-    for (int f = tid; f < CC * plane; f += kThreads) {
-      const int c = f / plane, rem = f % plane;
-      const int ih = ih0 + rem / in_w, iw = iw0 + rem % in_w;
-      float lo = 0.f, up = 0.f;
-      if (c0 + c < Cin && ih >= 0 && ih < H && iw >= 0 && iw < W) {
-        const int64_t o = ((int64_t)(c0 + c) * H + ih) * W + iw;
-        lo = __ldg(img_lo + o);
-        up = __ldg(img_up + o);
+    // staged in batches of kStageBatch elements per thread: all global loads of a batch are issued before
+    // the first of them is used, so their latencies overlap instead of adding up
+    for (int f0 = tid; f0 < CC * plane; f0 += kThreads * kStageBatch) {
+      float lo[kStageBatch], up[kStageBatch];
+#pragma unroll
+      for (int b = 0; b < kStageBatch; ++b) {
+        const int f = f0 + b * kThreads;
+        const int c = f / plane, rem = f - c * plane;
+        const int rh = rem / in_w;
+        const int ih = ih0 + rh, iw = iw0 + rem - rh * in_w;
+        lo[b] = 0.f;
+        up[b] = 0.f;
+        if (f < CC * plane && c0 + c < Cin && ih >= 0 && ih < H && iw >= 0 && iw < W) {
+          const int64_t o = ((int64_t)(c0 + c) * H + ih) * W + iw;
+          lo[b] = __ldg(img_lo + o);
+          up[b] = __ldg(img_up + o);
+        }
       }
-      s_c[f] = fmul(fadd(lo, up), 0.5f);
-      s_r[f] = fmul(fsub(up, lo), 0.5f);
+#pragma unroll
+      for (int b = 0; b < kStageBatch; ++b) {
+        const int f = f0 + b * kThreads;
+        if (f < CC * plane) {
+          s_c[f] = fmul(fadd(lo[b], up[b]), 0.5f);
+          s_r[f] = fmul(fsub(up[b], lo[b]), 0.5f);
+        }
+      }
     }
     for (int f = tid; f < CC * Kh * Kw * CO; f += kThreads) {
       const int o = f % CO, t = f / CO;
