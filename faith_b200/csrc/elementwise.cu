@@ -142,6 +142,64 @@ layernorm_novar_kernel(const float* __restrict__ x_lw, const float* __restrict__
   }
 }
 
+// The same operator for Do == 128 (the model width of the headline encoder): a warp owns a row, every lane
+// four consecutive features, so each tensor is touched by one 128-bit access per lane and the row stays in
+// registers between the mean and the rescale (the general kernel reads it twice with 32-bit accesses).
+template <bool kResidual>
+__global__ void __launch_bounds__(kThreads)
+layernorm_novar_row128_kernel(const float* __restrict__ x_lw, const float* __restrict__ x_uw,
+                              const float* __restrict__ x_lb, const float* __restrict__ x_ub,
+                              const float* __restrict__ r_lw, const float* __restrict__ r_uw,
+                              const float* __restrict__ r_lb, const float* __restrict__ r_ub,
+                              const float* __restrict__ gamma, const float* __restrict__ beta,
+                              float* __restrict__ z_lw, float* __restrict__ z_uw, float* __restrict__ z_lb,
+                              float* __restrict__ z_ub, int64_t n_w, int64_t n_b) {
+  constexpr int Do = 128;
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * (kThreads / 32);
+  const float inv_n = 1.0f / (float)Do;
+  const float4 g4 = __ldg(reinterpret_cast<const float4*>(gamma) + lane);
+  const float4 b4 = __ldg(reinterpret_cast<const float4*>(beta) + lane);
+  const float g[4] = {g4.x, g4.y, g4.z, g4.w}, be[4] = {b4.x, b4.y, b4.z, b4.w};
+  float gp[4], gn[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) { gp[e] = (g[e] > 0.f) ? g[e] : 0.f; gn[e] = fsub(g[e], gp[e]); }
+  for (int64_t row = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5); row < n_w + n_b; row += warps) {
+    bool is_bias;
+    const RowPtrs q = pick_rows(row, n_w, Do, x_lw, x_uw, x_lb, x_ub, r_lw, r_uw, r_lb, r_ub,
+                                z_lw, z_uw, z_lb, z_ub, is_bias);
+    const float4 a4 = reinterpret_cast<const float4*>(q.x_l)[lane];
+    const float4 c4 = reinterpret_cast<const float4*>(q.x_u)[lane];
+    float a[4] = {a4.x, a4.y, a4.z, a4.w}, b[4] = {c4.x, c4.y, c4.z, c4.w};
+    if (kResidual) {
+      const float4 ra = reinterpret_cast<const float4*>(q.r_l)[lane];
+      const float4 rb = reinterpret_cast<const float4*>(q.r_u)[lane];
+      a[0] = fadd(a[0], ra.x); a[1] = fadd(a[1], ra.y); a[2] = fadd(a[2], ra.z); a[3] = fadd(a[3], ra.w);
+      b[0] = fadd(b[0], rb.x); b[1] = fadd(b[1], rb.y); b[2] = fadd(b[2], rb.z); b[3] = fadd(b[3], rb.w);
+    }
+    // mean of each side: sum_k t_k * (1/n), as the reference's product with a constant 1/n matrix
+    float ml = 0.f, mu = 0.f;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { ml = fmaf(a[e], inv_n, ml); mu = fmaf(b[e], inv_n, mu); }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) {
+      ml += __shfl_xor_sync(0xffffffffu, ml, s);
+      mu += __shfl_xor_sync(0xffffffffu, mu, s);
+    }
+    float ol[4], ou[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float cl = fsub(a[e], mu);  // lower line minus the mean of the upper line
+      const float cu = fsub(b[e], ml);
+      ol[e] = fadd(fmul(cl, gp[e]), fmul(cu, gn[e]));
+      ou[e] = fadd(fmul(cl, gn[e]), fmul(cu, gp[e]));
+      if (is_bias) { ol[e] = fadd(ol[e], be[e]); ou[e] = fadd(ou[e], be[e]); }
+    }
+    reinterpret_cast<float4*>(q.z_l)[lane] = make_float4(ol[0], ol[1], ol[2], ol[3]);
+    reinterpret_cast<float4*>(q.z_u)[lane] = make_float4(ou[0], ou[1], ou[2], ou[3]);
+  }
+}
+
 // Head split / merge: pure index permutations with the head dimension d contiguous on both
 // sides.  One thread per group of VEC consecutive features.
 //   split: src [B, L, M, H, d] -> dst [B, H, L, M, d]      (M = Di for weights, 1 for biases)
@@ -271,8 +329,21 @@ extern "C" int fb_layernorm_novar_f32(const float* x_lw, const float* x_uw, cons
   if (rows == 0 || Do == 0) return FB_OK;
   const int64_t n_w = rows * Di, n_b = rows;
   ProfileScope prof(PK_ELEMENTWISE, 8.0 * (n_w + n_b) * Do, 4.0 * (r_lw ? 6 : 4) * (n_w + n_b) * Do, stream);
-  layernorm_novar_kernel<<<stream_blocks((n_w + n_b) * 32), kThreads, 0, (cudaStream_t)stream>>>(
-      x_lw, x_uw, x_lb, x_ub, r_lw, r_uw, r_lb, r_ub, gamma, beta, z_lw, z_uw, z_lb, z_ub, n_w, n_b, Do);
+  const bool row128 = Do == 128 && aligned16(x_lw) && aligned16(x_uw) && aligned16(x_lb) && aligned16(x_ub) &&
+                      aligned16(z_lw) && aligned16(z_uw) && aligned16(z_lb) && aligned16(z_ub) && aligned16(gamma) &&
+                      aligned16(beta) &&
+                      (!r_lw || (aligned16(r_lw) && aligned16(r_uw) && aligned16(r_lb) && aligned16(r_ub)));
+  const unsigned blocks = stream_blocks((n_w + n_b) * 32);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (row128 && r_lw)
+    layernorm_novar_row128_kernel<true><<<blocks, kThreads, 0, st>>>(x_lw, x_uw, x_lb, x_ub, r_lw, r_uw, r_lb, r_ub, gamma,
+                                                                      beta, z_lw, z_uw, z_lb, z_ub, n_w, n_b);
+  else if (row128)
+    layernorm_novar_row128_kernel<false><<<blocks, kThreads, 0, st>>>(x_lw, x_uw, x_lb, x_ub, r_lw, r_uw, r_lb, r_ub, gamma,
+                                                                       beta, z_lw, z_uw, z_lb, z_ub, n_w, n_b);
+  else
+    layernorm_novar_kernel<<<blocks, kThreads, 0, st>>>(x_lw, x_uw, x_lb, x_ub, r_lw, r_uw, r_lb, r_ub, gamma, beta, z_lw,
+                                                        z_uw, z_lb, z_ub, n_w, n_b, Do);
   FB_LAUNCH_OK();
   return FB_OK;
 }

@@ -644,3 +644,25 @@ def test_fused_softmax_returns_the_range_of_its_result(shape, p, words):
     l, u = ops.concretize(plain[0], plain[1], plain[2], plain[3], p, 0.1, words)
     helpers.assert_close(withr[4], l, "softmax range l")
     helpers.assert_close(withr[5], u, "softmax range u")
+
+
+@pytest.mark.parametrize("residual", [False, True])
+def test_layer_norm_of_128_features_matches_oracle(residual):
+    """Do == 128 takes the single-pass kernel with 128-bit accesses (a row per warp, kept in registers);
+    compared with the oracle's layer_norm (after add for the residual form)."""
+    from faith_b200 import ops
+    B, L, Di, Do = 2, 5, 24, 128
+    t = cases.rand_bounds(801, B, L, Di, Do)
+    r = cases.rand_bounds(802, B, L, Di, Do)
+    g0 = torch.Generator().manual_seed(12)
+    gamma = torch.randn(Do, generator=g0)
+    beta = 0.1 * torch.randn(Do, generator=g0)
+    o = O.OBounds(2.0, 0.1, *t)
+    if residual:
+        o = o.add(O.OBounds(2.0, 0.1, *r))
+    o = o.layer_norm(gamma, beta, "no_var")
+    x = tuple(v.to(DEV) for v in (t[0], t[2], t[1], t[3]))      # lw, uw, lb, ub
+    res = tuple(v.to(DEV) for v in (r[0], r[2], r[1], r[3])) if residual else None
+    got = ops.layernorm_novar(x, gamma.to(DEV), beta.to(DEV), res)
+    for a, k in zip(got, ("lw", "uw", "lb", "ub")):
+        helpers.assert_close(a, getattr(o, k), "layer norm %s" % k)
