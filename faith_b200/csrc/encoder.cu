@@ -82,6 +82,59 @@ input_bounds_kernel(const float* __restrict__ emb, float* __restrict__ lw, float
   }
 }
 
+// Input bounds and the embedding layer norm in one pass for d_model == 128 (a warp per row, four features per
+// lane): the rows of lw = uw are generated in registers (one-hot at the perturbed positions, zero elsewhere)
+// instead of being written by input_bounds_kernel and read back by the layer norm; same arithmetic as
+// fb_layernorm_novar_f32 (Bounds.py:1111-1131 on the bounds of VerifierForward.py:127-152).
+__global__ void __launch_bounds__(256)
+input_bounds_norm128_kernel(const float* __restrict__ emb, const float* __restrict__ gamma, const float* __restrict__ beta,
+                            float* __restrict__ lw, float* __restrict__ uw, float* __restrict__ lb, float* __restrict__ ub,
+                            int64_t n_w_rows, int64_t n_b_rows, int L, int words, Positions pos) {
+  constexpr int D = 128;
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * 8;
+  const float inv_n = 1.0f / (float)D;
+  const float4 g4 = __ldg(reinterpret_cast<const float4*>(gamma) + lane);
+  const float4 b4 = __ldg(reinterpret_cast<const float4*>(beta) + lane);
+  const float g[4] = {g4.x, g4.y, g4.z, g4.w}, be[4] = {b4.x, b4.y, b4.z, b4.w};
+  float gp[4], gn[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) { gp[e] = (g[e] > 0.f) ? g[e] : 0.f; gn[e] = fsub(g[e], gp[e]); }
+  const int Di = words * D;
+  for (int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); row < n_w_rows + n_b_rows; row += warps) {
+    const bool is_bias = row >= n_w_rows;
+    float a[4];
+    if (is_bias) {
+      const float4 v = __ldg(reinterpret_cast<const float4*>(emb + (row - n_w_rows) * D) + lane);
+      a[0] = v.x; a[1] = v.y; a[2] = v.z; a[3] = v.w;
+    } else {
+      const int m = (int)(row % Di);
+      const int l = (int)((row / Di) % L);
+      const int w = m / D;
+      const int hot = (l == pos.v[w]) ? m - w * D : -1;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) a[e] = (4 * lane + e == hot) ? 1.f : 0.f;
+    }
+    float mean = 0.f;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) mean = fmaf(a[e], inv_n, mean);
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) mean += __shfl_xor_sync(0xffffffffu, mean, s);
+    float ol[4], ou[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float c = fsub(a[e], mean);     // lower and upper line coincide
+      ol[e] = fadd(fmul(c, gp[e]), fmul(c, gn[e]));
+      ou[e] = fadd(fmul(c, gn[e]), fmul(c, gp[e]));
+      if (is_bias) { ol[e] = fadd(ol[e], be[e]); ou[e] = fadd(ou[e], be[e]); }
+    }
+    float* zl = is_bias ? lb + (row - n_w_rows) * D : lw + row * D;
+    float* zu = is_bias ? ub + (row - n_w_rows) * D : uw + row * D;
+    reinterpret_cast<float4*>(zl)[lane] = make_float4(ol[0], ol[1], ol[2], ol[3]);
+    reinterpret_cast<float4*>(zu)[lane] = make_float4(ou[0], ou[1], ou[2], ou[3]);
+  }
+}
+
 // classifier folded to one row: w = cls_w[0] - cls_w[1], b = cls_b[0] - cls_b[1]
 // (VerifierForward.py:289-292)
 __global__ void fold_classifier_kernel(const float* __restrict__ cls_w, const float* __restrict__ cls_b,
@@ -166,12 +219,20 @@ extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, i
   {
     Positions pos = {{0, 0, 0, 0}};
     for (int w = 0; w < words; ++w) pos.v[w] = positions[w];
-    const int64_t n_w = rows * Di * D, n_b = rows * D;
-    const int64_t want = ceil_div(n_w, 256), cap = (int64_t)device_info().sms * 16;
-    input_bounds_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, st>>>(emb, slot[B].lw, slot[B].uw, slot[B].lb,
-                                                                             slot[B].ub, n_w, n_b, L, D, words, pos);
-    FB_LAUNCH_OK();
-    FB_TRY(norm_residual(enc, slot[B], nullptr, enc->emb_ln_g, enc->emb_ln_b, slot[A], rows, Di, D, stream));
+    if (enc->layer_norm == 1 && D == 128 && aligned16(emb) && aligned16(enc->emb_ln_g) && aligned16(enc->emb_ln_b)) {
+      const int64_t n_w_rows = rows * Di, n_b_rows = rows;
+      const int64_t want = ceil_div(n_w_rows + n_b_rows, 8), cap = (int64_t)device_info().sms * 16;
+      input_bounds_norm128_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, st>>>(
+          emb, enc->emb_ln_g, enc->emb_ln_b, slot[A].lw, slot[A].uw, slot[A].lb, slot[A].ub, n_w_rows, n_b_rows, L, words, pos);
+      FB_LAUNCH_OK();
+    } else {
+      const int64_t n_w = rows * Di * D, n_b = rows * D;
+      const int64_t want = ceil_div(n_w, 256), cap = (int64_t)device_info().sms * 16;
+      input_bounds_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, st>>>(emb, slot[B].lw, slot[B].uw, slot[B].lb,
+                                                                               slot[B].ub, n_w, n_b, L, D, words, pos);
+      FB_LAUNCH_OK();
+      FB_TRY(norm_residual(enc, slot[B], nullptr, enc->emb_ln_g, enc->emb_ln_b, slot[A], rows, Di, D, stream));
+    }
   }
   const float inv_sqrt_d = (float)(1.0 / sqrt((double)d));
   for (int li = 0; li < enc->layers; ++li) {

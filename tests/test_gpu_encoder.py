@@ -135,3 +135,21 @@ def test_encoder_full_size_config_properties():
     l64, u64 = O.encoder_forward(O.model_to(model, torch.float64), emb[:2].double(), [1], float("inf"), 1e-3)
     helpers.assert_within_noise(l[:2], l32, l64, "l")
     helpers.assert_within_noise(u[:2], u32, u64, "u")
+
+
+def test_encoder_full_width_two_perturbed_words():
+    """d_model 128 with two perturbed words (dim_in 256, L2): the paths that exist only for 128-wide
+    models (input bounds fused with the embedding layer norm, ranges handed over by the GEMM epilogue
+    with one word block per tile) with more than one word block."""
+    import faith_b200
+    model = O.make_encoder(4)
+    emb = torch.randn(2, 32, 128, generator=torch.Generator().manual_seed(5))
+    ver = faith_b200.EncoderVerifier(model, DEV)
+    l, u, viol = ver.forward(emb.to(DEV), [1, 5], 2.0, 1e-3)
+    assert int(viol.item()) == 0
+    l32, u32 = O.encoder_forward(model, emb, [1, 5], 2.0, 1e-3)
+    l64, u64 = O.encoder_forward(O.model_to(model, torch.float64), emb.double(), [1, 5], 2.0, 1e-3)
+    helpers.assert_within_noise(l, l32, l64, "l")
+    helpers.assert_within_noise(u, u32, u64, "u")
+    y = O.concrete_forward(model, emb)
+    assert bool((l.cpu() <= y + 1e-5).all()) and bool((y <= u.cpu() + 1e-5).all())
