@@ -42,7 +42,7 @@ Plan make_plan(const fb_encoder* e, int S, int L, int words) {
   const int64_t d = D / H;
   p.range_floats = (int64_t)S * H * (L > d ? L : d) * (L > d ? L : d);
   p.small_bytes = align_up((D + 1) * 4, 256);
-  p.norm_floats = 2 * (int64_t)S * L * words * (D > F ? D : F);
+  p.norm_floats = 2 * (int64_t)S * L * (words + 1) * (D > F ? D : F);
   p.total = 4 * p.slot_bytes + 4 * align_up(p.range_floats * 4, 256) + p.small_bytes + align_up(p.norm_floats * 4, 256);
   return p;
 }

@@ -37,9 +37,12 @@ static int split_sign_gemm(const float* a_lo, const float* a_up, const float* W,
 
 // Ranges of a (head-split) product from the per-word-block column norms that the GEMM epilogue wrote:
 //   l[g, l, j] = lb[g, l, j] - eps * sum_w norm_lo[(row * words + w), h * d + j],   g = s * heads + h, row = s * L + l
-// and the mirror for u (Bounds.py:311-326).
+// and the mirror for u (Bounds.py:311-326).  With plain_lb / plain_ub != nullptr the bias terms come from
+// there in the unsplit layout [rows, heads * d] and are written to lb / ub in the head-split layout on the way
+// (the head split of the bias rows, VerifierForward.py:208-229, folded into this kernel).
 __global__ void __launch_bounds__(256)
-ranges_from_norms_kernel(const float* __restrict__ lb, const float* __restrict__ ub, const float* __restrict__ norm_lo,
+ranges_from_norms_kernel(float* __restrict__ lb, float* __restrict__ ub, const float* __restrict__ plain_lb,
+                         const float* __restrict__ plain_ub, const float* __restrict__ norm_lo,
                          const float* __restrict__ norm_up, float* __restrict__ out_l, float* __restrict__ out_u,
                          int64_t total, int L, int heads, int d, int words, float eps) {
   const int Dy = heads * d;
@@ -49,7 +52,16 @@ ranges_from_norms_kernel(const float* __restrict__ lb, const float* __restrict__
     const int64_t g = t / ((int64_t)d * L);
     const int h = (int)(g % heads);
     const int64_t row = (g / heads) * L + l;
-    float lo = lb[t], up = ub[t];
+    float lo, up;
+    if (plain_lb != nullptr) {
+      lo = plain_lb[row * Dy + h * d + j];
+      up = plain_ub[row * Dy + h * d + j];
+      lb[t] = lo;
+      ub[t] = up;
+    } else {
+      lo = lb[t];
+      up = ub[t];
+    }
     for (int w = 0; w < words; ++w) {
       const int64_t o = (row * words + w) * Dy + h * d + j;
       lo = fadd(lo, fmul(-eps, norm_lo[o]));
@@ -119,8 +131,8 @@ extern "C" int fb_matmul_coef_f32(const float* x_lw, const float* x_uw, const fl
 // fb_matmul_heads_f32 that also returns the concretised range of its result, y_l / y_u in the layout of
 // y_lb / y_ub: the column norms over dim_in are taken by the GEMM epilogue from the tile it is about to
 // store (one word block of dim_in per 128-row tile), so the dot product that consumes y needs no pass of
-// its own over y_lw / y_uw (Bounds.py:311-326 fused into :397-413).  norm_ws: 2 * rows * words * Dy floats
-// of scratch.  Tensor-core shapes with Di == 128 * words only; otherwise FB_ERR_SHAPE and nothing is
+// its own over y_lw / y_uw (Bounds.py:311-326 fused into :397-413).  norm_ws: 2 * rows * (words + 1) * Dy
+// floats of scratch.  Tensor-core shapes with Di == 128 * words only; otherwise FB_ERR_SHAPE and nothing is
 // launched (run fb_matmul_heads_f32 and fb_concretize_f32).
 extern "C" int fb_matmul_heads_ranges_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
                                           const float* W, const float* bias, float* y_lw, float* y_uw, float* y_lb,
@@ -144,12 +156,24 @@ extern "C" int fb_matmul_heads_ranges_f32(const float* x_lw, const float* x_uw, 
   int rc = fb::launch_split_sign_tc(x_lw, x_uw, W, nullptr, y_lw, y_uw, M, Dy, Do, st, heads > 1 ? L * Di : 0,
                                     heads > 1 ? d : 0, nullptr, nullptr, 1, norm_lo, norm_up, p);
   if (rc != FB_OK) return rc;
-  rc = fb::split_sign_gemm(x_lb, x_ub, W, bias, y_lb, y_ub, rows, Dy, Do, st, heads > 1 ? L : 0, heads > 1 ? d : 0);
+  // Bias rows.  A head-split store of [rows, Dy] does not fit the tensor-core kernel's output boxes (L rows per
+  // group), and the CUDA-core kernel has too few tiles to fill the machine at this size: with heads > 1 the
+  // tensor-core kernel writes them unsplit into the scratch and the range kernel splits them on the way.
+  float* plain_lb = nullptr;
+  float* plain_ub = nullptr;
+  if (heads > 1 && fb::tc_gemm_supported(x_lb, x_ub, W, norm_ws, norm_ws, rows, Dy, Do)) {
+    plain_lb = norm_ws + 2 * rows * words * Dy;
+    plain_ub = plain_lb + rows * Dy;
+    rc = fb::launch_split_sign_tc(x_lb, x_ub, W, bias, plain_lb, plain_ub, rows, Dy, Do, st, 0, 0);
+  } else {
+    rc = fb::split_sign_gemm(x_lb, x_ub, W, bias, y_lb, y_ub, rows, Dy, Do, st, heads > 1 ? L : 0, heads > 1 ? d : 0);
+  }
   if (rc != FB_OK) return rc;
   const int64_t total = rows * Dy;
   const int64_t want = fb::ceil_div(total, 256), cap = (int64_t)fb::device_info().sms * 8;
-  fb::ranges_from_norms_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, st>>>(y_lb, y_ub, norm_lo, norm_up, y_l, y_u,
-                                                                                   total, L, heads, d, words, eps);
+  fb::ranges_from_norms_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, st>>>(y_lb, y_ub, plain_lb, plain_ub, norm_lo,
+                                                                                   norm_up, y_l, y_u, total, L, heads, d,
+                                                                                   words, eps);
   FB_LAUNCH_OK();
   return FB_OK;
 }

@@ -146,7 +146,7 @@ def matmul_heads_ranges(lw, uw, lb, ub, W, bias, heads, p, eps, words=1):
     y_lw = torch.empty((S * heads, L, Di, d), device=dev, dtype=torch.float32)
     y_uw = torch.empty_like(y_lw)
     y_lb, y_ub, y_l, y_u = (torch.empty((S * heads, L, d), device=dev, dtype=torch.float32) for _ in range(4))
-    ws = torch.empty(2 * S * L * words * Dy, device=dev, dtype=torch.float32)
+    ws = torch.empty(2 * S * L * (words + 1) * Dy, device=dev, dtype=torch.float32)
     with torch.cuda.device(dev):
         check(load().fb_matmul_heads_ranges_f32(_p(lw), _p(uw), _p(lb), _p(ub), _p(W), _p(bias), _p(y_lw), _p(y_uw), _p(y_lb),
                                                 _p(y_ub), _p(y_l), _p(y_u), _p(ws), S * L, Di, Do, Dy, L, heads, int(words),
