@@ -325,8 +325,17 @@ extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, i
       FB_CUDA_OK(cudaMemcpyAsync(T2.ub, T1.ub, (size_t)rows * D * 4, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
     }
     // attention output: dense, + residual, layer norm -> T3
-    FB_TRY(dense(T2, ly.ao_w, ly.ao_b, T1, rows, Di, D, D, stream));
-    FB_TRY(norm_residual(enc, T1, &X, ly.ln1_g, ly.ln1_b, T3, rows, Di, D, stream));
+    // (the residual is added by the GEMM epilogue where the shapes allow it: the layer norm then reads one bound)
+    const int arc = fb_matmul_residual_f32(T2.lw, T2.uw, T2.lb, T2.ub, nullptr, nullptr, ly.ao_w, ly.ao_b, X.lw, X.uw, X.lb,
+                                           X.ub, T1.lw, T1.uw, T1.lb, T1.ub, rows, Di, D, D, stream);
+    if (arc == FB_OK) {
+      FB_TRY(norm_residual(enc, T1, nullptr, ly.ln1_g, ly.ln1_b, T3, rows, Di, D, stream));
+    } else if (arc == FB_ERR_SHAPE) {
+      FB_TRY(dense(T2, ly.ao_w, ly.ao_b, T1, rows, Di, D, D, stream));
+      FB_TRY(norm_residual(enc, T1, &X, ly.ln1_g, ly.ln1_b, T3, rows, Di, D, stream));
+    } else {
+      return arc;
+    }
     // feed-forward: dense, relu, dense, + residual, layer norm
     // Where the shapes allow it the relu is not materialised: its column slopes go to the (now unused)
     // slot of the layer input and the second product applies them while it reads the hidden bounds.  The
@@ -341,12 +350,19 @@ extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, i
       frc = fb_relax_coef_f32(FB_RELU, T1.lw, T1.uw, T1.lb, T1.ub, X.lw, X.uw, T2.lb, T2.ub, rows, Di, F, words, p, eps,
                               nullptr, stream);
     }
-    if (frc == FB_OK)
-      frc = fb_matmul_coef_f32(T1.lw, T1.uw, T2.lb, T2.ub, X.lw, X.uw, ly.f2_w, ly.f2_b, T2.lw, T2.uw, X.lb, X.ub, rows, Di,
-                               F, D, stream);
+    bool residual_added = false;
+    if (frc == FB_OK) {
+      frc = fb_matmul_residual_f32(T1.lw, T1.uw, T2.lb, T2.ub, X.lw, X.uw, ly.f2_w, ly.f2_b, T3.lw, T3.uw, T3.lb, T3.ub, T2.lw,
+                                   T2.uw, X.lb, X.ub, rows, Di, F, D, stream);
+      if (frc == FB_OK)
+        residual_added = true;
+      else if (frc == FB_ERR_SHAPE)
+        frc = fb_matmul_coef_f32(T1.lw, T1.uw, T2.lb, T2.ub, X.lw, X.uw, ly.f2_w, ly.f2_b, T2.lw, T2.uw, X.lb, X.ub, rows, Di,
+                                 F, D, stream);
+    }
     if (frc == FB_OK) {
       const BoundSet Y = {T2.lw, T2.uw, X.lb, X.ub};
-      FB_TRY(norm_residual(enc, Y, &T3, ly.ln2_g, ly.ln2_b, T1, rows, Di, D, stream));
+      FB_TRY(norm_residual(enc, Y, residual_added ? nullptr : &T3, ly.ln2_g, ly.ln2_b, T1, rows, Di, D, stream));
       // the layer output (slot B) becomes the next layer's input
       const int newA = B;
       B = A;

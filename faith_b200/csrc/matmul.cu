@@ -11,7 +11,8 @@ bool tc_split_supported(int64_t M, int N, int split_rows, int split_d);
 int launch_split_sign_tc(const float* a_lo, const float* a_up, const float* W, const float* bias, float* c_lo,
                          float* c_up, int64_t M, int N, int K, cudaStream_t st, int split_rows, int split_d,
                          const float* coef_l = nullptr, const float* coef_u = nullptr, int coef_di = 1,
-                         float* norm_lo = nullptr, float* norm_up = nullptr, int norm_p = 0);
+                         float* norm_lo = nullptr, float* norm_up = nullptr, int norm_p = 0,
+                         const float* res_lo = nullptr, const float* res_up = nullptr);
 int launch_split_sign_ffma(const float* a_lo, const float* a_up, const float* W, const float* bias, float* c_lo,
                            float* c_up, int64_t M, int N, int K, cudaStream_t st, int split_rows, int split_d);
 
@@ -176,4 +177,39 @@ extern "C" int fb_matmul_heads_ranges_f32(const float* x_lw, const float* x_uw, 
                                                                                    words, eps);
   FB_LAUNCH_OK();
   return FB_OK;
+}
+
+// dense (optionally of a relaxed bound given by its slopes, as fb_matmul_coef_f32) followed by the residual add
+// of the encoder blocks (Bounds.add, Bounds.py:383-395, after :397-413): y = matmul(x, W) + bias + r.  The
+// residual tile is fetched into the epilogue's staging buffer while the tile is computed and added before the
+// store, bit-identical to fb_matmul_f32 followed by fb_add_f32; the layer norm that follows then reads one
+// bound instead of two.  c_l / c_u may be NULL (plain dense).  Tensor-core shapes for both the weight rows and
+// the bias rows (rows >= 256) only, otherwise FB_ERR_SHAPE and nothing is launched.
+extern "C" int fb_matmul_residual_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+                                      const float* c_l, const float* c_u, const float* W, const float* bias,
+                                      const float* r_lw, const float* r_uw, const float* r_lb, const float* r_ub,
+                                      float* y_lw, float* y_uw, float* y_lb, float* y_ub,
+                                      int64_t rows, int Di, int Do, int Dy, void* stream) {
+  if (!x_lw || !x_uw || !x_lb || !x_ub || !W || !r_lw || !r_uw || !r_lb || !r_ub || !y_lw || !y_uw || !y_lb || !y_ub)
+    return FB_ERR_ARG;
+  if ((c_l == nullptr) != (c_u == nullptr)) return FB_ERR_ARG;
+  if (rows < 0 || Di <= 0 || Do <= 0 || Dy <= 0) return FB_ERR_ARG;
+  if (y_lw == r_lw || y_lw == r_uw || y_uw == r_lw || y_uw == r_uw || y_lb == r_lb || y_lb == r_ub || y_ub == r_lb ||
+      y_ub == r_ub)
+    return FB_ERR_ARG;
+  const int64_t M = rows * (int64_t)Di;
+  if (!fb::use_tensor_cores() || !fb::tc_gemm_supported(x_lw, x_uw, W, y_lw, y_uw, M, Dy, Do) ||
+      !fb::tc_gemm_supported(x_lb, x_ub, W, y_lb, y_ub, rows, Dy, Do) || !fb::aligned16(r_lw) || !fb::aligned16(r_uw) ||
+      !fb::aligned16(r_lb) || !fb::aligned16(r_ub))
+    return FB_ERR_SHAPE;
+  if (c_l != nullptr && (Di % 128 != 0 || Do % 32 != 0 || !fb::aligned16(c_l) || !fb::aligned16(c_u))) return FB_ERR_SHAPE;
+  if (rows == 0) return FB_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const double Mt = (double)rows * (Di + 1);
+  fb::ProfileScope prof(fb::PK_MATMUL, 8.0 * Mt * Do * Dy, 4.0 * (2 * Mt * Do + 4 * Mt * Dy + (double)Do * Dy + Dy), stream);
+  int rc = fb::launch_split_sign_tc(x_lw, x_uw, W, nullptr, y_lw, y_uw, M, Dy, Do, st, 0, 0, c_l, c_u, Di, nullptr, nullptr, 0,
+                                    r_lw, r_uw);
+  if (rc != FB_OK) return rc;
+  return fb::launch_split_sign_tc(x_lb, x_ub, W, bias, y_lb, y_ub, rows, Dy, Do, st, 0, 0, nullptr, nullptr, 1, nullptr,
+                                  nullptr, 0, r_lb, r_ub);
 }

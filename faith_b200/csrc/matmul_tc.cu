@@ -133,11 +133,15 @@ struct SharedLayout {
 // norm_lo / norm_up [M / 128][N] (norm_p as in the concretisation: sum |x|, sqrt(sum x^2) or max |x|).  With one
 // word block of dim_in per tile that is the concretisation term of the result, so the product that
 // consumes it needs no pass of its own over y_lw / y_uw.
-template <bool kCoef, bool kNorm>
+// kResid: a residual bound (same shape and layout as the result, plain store only) is added to the result in
+// the epilogue: its tile is fetched by TMA into the staging buffer while the k-blocks of the tile are still
+// running, so the layer norm that follows reads one tensor pair instead of two.
+template <bool kCoef, bool kNorm, bool kResid>
 __global__ void __launch_bounds__(kThreads, 1)
 split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_constant__ CUtensorMap tm_up,
                    const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_out_lo,
-                   const __grid_constant__ CUtensorMap tm_out_up, const float* __restrict__ bias, int64_t M, int N, int K,
+                   const __grid_constant__ CUtensorMap tm_out_up, const __grid_constant__ CUtensorMap tm_res_lo,
+                   const __grid_constant__ CUtensorMap tm_res_up, const float* __restrict__ bias, int64_t M, int N, int K,
                    int n_tiles_n, int64_t total_tiles, int split_rows, int split_d,
                    const float* __restrict__ coef_l, const float* __restrict__ coef_u, int coef_di,
                    float* __restrict__ norm_lo, float* __restrict__ norm_up, int norm_p) {
@@ -153,6 +157,7 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
   const uint32_t bar_acc_ready = bar0 + 96;
   const uint32_t bar_acc_free = bar0 + 104;
   const uint32_t bar_conv = bar0 + 128;          // rendezvous of the converter warps in the epilogue (bounded, unlike bar.sync)
+  const uint32_t bar_res = bar0 + 136;           // residual tile has landed in the staging buffer (kResid)
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + SharedLayout::bars() + 112);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(base_ptr + SharedLayout::bars() + 120);
 
@@ -176,6 +181,7 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
     mbar_init(bar_acc_ready, kIssuers);
     mbar_init(bar_acc_free, kEpiWarps);
     mbar_init(bar_conv, kEpiWarps);
+    mbar_init(bar_res, 1);
     *cta_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -287,11 +293,25 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
       if (leader) tma_store_wait_read();
       ok = epi_sync();
       if (!ok) break;
+      const int etile = blockIdx.x + e * gridDim.x;
+      const int my = (etile / n_tiles_n) * BM, nx = (etile % n_tiles_n) * BN;
+      if (kResid && leader) {
+        // the staging buffer is free now: fetch the residual tile into it (same boxes as the store below)
+        const uint32_t so = base + SharedLayout::out();
+        mbar_arrive_expect_tx(bar_res, kOutStageBytes);
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          tma_load_3d(so + q * kOutBoxBytes, &tm_res_lo, nx + 32 * q, my, 0, bar_res);
+          tma_load_3d(so + (2 + q) * kOutBoxBytes, &tm_res_up, nx + 32 * q, my, 0, bar_res);
+        }
+      }
       ok = mbar_wait_warp(bar_acc_ready, (uint32_t)(e & 1), cta_abort);
       if (!ok) break;
       tc_fence_after();
-      const int etile = blockIdx.x + e * gridDim.x;
-      const int my = (etile / n_tiles_n) * BM, nx = (etile % n_tiles_n) * BN;
+      if (kResid) {
+        ok = mbar_wait_warp(bar_res, (uint32_t)(e & 1), cta_abort);
+        if (!ok) break;
+      }
 #pragma unroll
       for (int cq = 4 * chalf; cq < 4 * chalf + 4; ++cq) {
         const int ncol = cq * 8;
@@ -325,6 +345,12 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
             }
           }
           const uint32_t off = swz(row, (cq & 3) * 2 + q);
+          if (kResid) {
+            const float4 rl = *reinterpret_cast<const float4*>(so + off);
+            const float4 ru = *reinterpret_cast<const float4*>(so + 2 * kOutBoxBytes + off);
+            lo[0] = fadd(lo[0], rl.x); lo[1] = fadd(lo[1], rl.y); lo[2] = fadd(lo[2], rl.z); lo[3] = fadd(lo[3], rl.w);
+            up[0] = fadd(up[0], ru.x); up[1] = fadd(up[1], ru.y); up[2] = fadd(up[2], ru.z); up[3] = fadd(up[3], ru.w);
+          }
           *reinterpret_cast<float4*>(so + off) = make_float4(lo[0], lo[1], lo[2], lo[3]);
           *reinterpret_cast<float4*>(so + 2 * kOutBoxBytes + off) = make_float4(up[0], up[1], up[2], up[3]);
         }
@@ -562,13 +588,21 @@ bool tc_gemm_supported(const float* a_lo, const float* a_up, const float* W, con
 int launch_split_sign_tc(const float* a_lo, const float* a_up, const float* W, const float* bias, float* c_lo,
                          float* c_up, int64_t M, int N, int K, cudaStream_t st, int split_rows, int split_d,
                          const float* coef_l, const float* coef_u, int coef_di, float* norm_lo, float* norm_up,
-                         int norm_p) {
+                         int norm_p, const float* res_lo, const float* res_up) {
   if (norm_lo != nullptr && (coef_l != nullptr || norm_up == nullptr || M % BM != 0)) return FB_ERR_ARG;
-  CUtensorMap tm_lo, tm_up, tm_w, tm_out_lo, tm_out_up;
+  if (res_lo != nullptr && (res_up == nullptr || norm_lo != nullptr || split_rows > 0 || !aligned16(res_lo) || !aligned16(res_up)))
+    return FB_ERR_ARG;
+  CUtensorMap tm_lo, tm_up, tm_w, tm_out_lo, tm_out_up, tm_res_lo, tm_res_up;
   if (!make_map(&tm_lo, a_lo, (uint64_t)M, (uint64_t)K, BM) || !make_map(&tm_up, a_up, (uint64_t)M, (uint64_t)K, BM) ||
       !make_map(&tm_w, W, (uint64_t)N, (uint64_t)K, BN) ||
       !make_out_map(&tm_out_lo, c_lo, (uint64_t)M, (uint64_t)N, split_rows, split_d) ||
       !make_out_map(&tm_out_up, c_up, (uint64_t)M, (uint64_t)N, split_rows, split_d))
+    return FB_ERR_CUDA;
+  // the residual maps are only read by the kResid instantiations; elsewhere they are copies of the output maps
+  tm_res_lo = tm_out_lo;
+  tm_res_up = tm_out_up;
+  if (res_lo != nullptr && (!make_out_map(&tm_res_lo, res_lo, (uint64_t)M, (uint64_t)N, 0, 0) ||
+                            !make_out_map(&tm_res_up, res_up, (uint64_t)M, (uint64_t)N, 0, 0)))
     return FB_ERR_CUDA;
   const int64_t gm = ceil_div(M, BM);
   const int gn = (int)ceil_div(N, BN);
@@ -578,22 +612,33 @@ int launch_split_sign_tc(const float* a_lo, const float* a_up, const float* W, c
   FB_CUDA_OK(cudaGetDevice(&dev));
   cudaError_t attr_err = cudaSuccess;
   std::call_once(attr_once[dev & 63], [&]() {
-    attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    const int bytes = (int)kSmemBytes;
+    attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     if (attr_err == cudaSuccess)
-      attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+      attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<true, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     if (attr_err == cudaSuccess)
-      attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+      attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<false, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (attr_err == cudaSuccess)
+      attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (attr_err == cudaSuccess)
+      attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
   });
   FB_CUDA_OK(attr_err);
   // persistent: one CTA per SM (tensor memory and shared memory allow exactly one)
   const int64_t sms = device_info().sms;
   const unsigned grid = (unsigned)(total_tiles < sms ? total_tiles : sms);
-  if (coef_l != nullptr)
-    split_sign_gemm_tc<true, false><<<grid, kThreads, kSmemBytes, st>>>(tm_lo, tm_up, tm_w, tm_out_lo, tm_out_up, bias, M, N, K, gn, total_tiles, split_rows, split_d, coef_l, coef_u, coef_di, nullptr, nullptr, 0);
+#define FB_TC_ARGS tm_lo, tm_up, tm_w, tm_out_lo, tm_out_up, tm_res_lo, tm_res_up, bias, M, N, K, gn, total_tiles, split_rows, split_d
+  if (coef_l != nullptr && res_lo != nullptr)
+    split_sign_gemm_tc<true, false, true><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, coef_l, coef_u, coef_di, nullptr, nullptr, 0);
+  else if (coef_l != nullptr)
+    split_sign_gemm_tc<true, false, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, coef_l, coef_u, coef_di, nullptr, nullptr, 0);
   else if (norm_lo != nullptr)
-    split_sign_gemm_tc<false, true><<<grid, kThreads, kSmemBytes, st>>>(tm_lo, tm_up, tm_w, tm_out_lo, tm_out_up, bias, M, N, K, gn, total_tiles, split_rows, split_d, nullptr, nullptr, 1, norm_lo, norm_up, norm_p);
+    split_sign_gemm_tc<false, true, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, norm_lo, norm_up, norm_p);
+  else if (res_lo != nullptr)
+    split_sign_gemm_tc<false, false, true><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, nullptr, nullptr, 0);
   else
-    split_sign_gemm_tc<false, false><<<grid, kThreads, kSmemBytes, st>>>(tm_lo, tm_up, tm_w, tm_out_lo, tm_out_up, bias, M, N, K, gn, total_tiles, split_rows, split_d, nullptr, nullptr, 1, nullptr, nullptr, 0);
+    split_sign_gemm_tc<false, false, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, nullptr, nullptr, 0);
+#undef FB_TC_ARGS
   FB_LAUNCH_OK();
   return FB_OK;
 }

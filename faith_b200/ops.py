@@ -108,6 +108,23 @@ def relax_coef(op, lw, uw, lb, ub, p, eps, words=1, violation=None):
     return out
 
 
+def matmul_residual(lw, uw, lb, ub, W, bias, residual, c_l=None, c_u=None):
+    """matmul of (lw, uw, lb, ub) (or of (c_l * lw, c_u * uw, lb, ub)) with W, + bias, + residual (lw, uw, lb, ub)."""
+    dev = _chk(lw, uw, lb, ub, W, bias, *residual)
+    rows = lb.numel() // lb.shape[-1]
+    Di, Do = lw.shape[-2], lw.shape[-1]
+    Dy = W.shape[0]
+    y_lw = torch.empty(lw.shape[:-1] + (Dy,), device=dev, dtype=torch.float32)
+    y_uw = torch.empty_like(y_lw)
+    y_lb = torch.empty(lb.shape[:-1] + (Dy,), device=dev, dtype=torch.float32)
+    y_ub = torch.empty_like(y_lb)
+    with torch.cuda.device(dev):
+        check(load().fb_matmul_residual_f32(_p(lw), _p(uw), _p(lb), _p(ub), _p(c_l), _p(c_u), _p(W), _p(bias),
+                                            *[_p(t) for t in residual], _p(y_lw), _p(y_uw), _p(y_lb), _p(y_ub), rows, Di, Do,
+                                            Dy, _stream()), "fb_matmul_residual_f32")
+    return y_lw, y_uw, y_lb, y_ub
+
+
 def relax_coef_given(op, lb, ub, l, u, violation=None):
     """relax_coef for a bound whose concretised range (l, u) is already known: no pass over lw / uw."""
     dev = _chk(lb, ub, l, u)

@@ -143,6 +143,18 @@ int fb_matmul_coef_f32(const float* x_lw, const float* x_uw, const float* x_lb, 
                        float* y_lw, float* y_uw, float* y_lb, float* y_ub,
                        int64_t rows, int Di, int Do, int Dy, void* stream);
 
+/* dense followed by the residual add of the encoder blocks: y = matmul(x, W) + bias + r (Bounds.py:397-413 and
+ * :383-395), optionally of a relaxed bound given by its slopes c_l, c_u as in fb_matmul_coef_f32 (both NULL:
+ * plain dense).  The GEMM epilogue fetches the residual tile while the tile is computed and adds it before the
+ * store; bit-identical to fb_matmul_f32 (fb_matmul_coef_f32) followed by fb_add_f32.  Tensor-core shapes for
+ * the weight rows and the bias rows (rows >= 256) only, otherwise FB_ERR_SHAPE and nothing is launched.  No
+ * counterpart in the reference's extension module. */
+int fb_matmul_residual_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+                           const float* c_l, const float* c_u, const float* W, const float* bias,
+                           const float* r_lw, const float* r_uw, const float* r_lb, const float* r_ub,
+                           float* y_lw, float* y_uw, float* y_lb, float* y_ub,
+                           int64_t rows, int Di, int Do, int Dy, void* stream);
+
 /* The tensor-core GEMM behind fb_matmul_f32 bounds every wait inside the kernel; if a wait ever
  * expires, the kernel raises a device-side flag, frees its tensor memory and returns.  This call
  * synchronises the device, returns the flag in *flag (0 = never raised) and clears it. */

@@ -671,3 +671,40 @@ def test_layer_norm_of_128_features_matches_oracle(residual):
     got = ops.layernorm_novar(x, gamma.to(DEV), beta.to(DEV), res)
     for a, k in zip(got, ("lw", "uw", "lb", "ub")):
         helpers.assert_close(a, getattr(o, k), "layer norm %s" % k)
+
+
+@pytest.mark.parametrize("with_slopes", [False, True])
+@pytest.mark.parametrize("Do,Dy", [(128, 128), (512, 96)])
+def test_dense_with_residual_added_in_the_epilogue(with_slopes, Do, Dy):
+    """fb_matmul_residual_f32 equals fb_matmul_f32 (or fb_relax_coef_f32 + fb_matmul_coef_f32) followed by
+    fb_add_f32 bit for bit; ten launches give identical results; shapes without 256 bias rows are refused."""
+    from faith_b200 import ops, _lib
+    S, L, Di, eps, p = 8, 32, 128, 0.05, float("inf")
+    t = cases.rand_bounds(901, S, L, Di, Do, -0.4, 0.6)
+    r = cases.rand_bounds(902, S, L, Di, Dy)
+    g0 = torch.Generator().manual_seed(13)
+    W = (torch.randn(Dy, Do, generator=g0) / math.sqrt(Do)).to(DEV)
+    bias = (torch.randn(Dy, generator=g0) * 0.1).to(DEV)
+    lw, lb, uw, ub = [v.to(DEV) for v in t]
+    res = tuple(v.to(DEV) for v in (r[0], r[2], r[1], r[3]))
+    if with_slopes:
+        c_l, c_u, nlb, nub = ops.relax_coef(_lib.FB_RELU, lw, uw, lb, ub, p, eps, 1)
+        y = ops.matmul_coef(lw, uw, nlb, nub, c_l, c_u, W, bias)
+        args = (lw, uw, nlb, nub, W, bias, res, c_l, c_u)
+    else:
+        y = ops.matmul(lw, uw, lb, ub, W, bias)
+        args = (lw, uw, lb, ub, W, bias, res)
+    ref = ops.add(y, res)
+    first = ops.matmul_residual(*args)
+    for a, b, name in zip(first, ref, ("lw", "uw", "lb", "ub")):
+        assert torch.equal(a, b), name
+    for _ in range(9):
+        again = ops.matmul_residual(*args)
+        for a, b in zip(again, first):
+            assert torch.equal(a, b)
+    flag = __import__("ctypes").c_int(0)
+    _lib.check(_lib.load().fb_tc_error_flag(__import__("ctypes").byref(flag)), "fb_tc_error_flag")
+    assert flag.value == 0
+    with pytest.raises(_lib.FaithError):   # 64 bias rows: below the tensor-core kernel's minimum
+        ops.matmul_residual(lw[:2].contiguous(), uw[:2].contiguous(), lb[:2].contiguous(), ub[:2].contiguous(), W, bias,
+                            tuple(v[:2].contiguous() for v in res))
