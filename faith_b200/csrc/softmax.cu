@@ -28,12 +28,16 @@ __device__ __forceinline__ float block_reduce(float v, int p, float* s_tmp) {
   return r;
 }
 
+// kP: the norm of the perturbation (FB_P1, FB_P2, FB_PINF) as a template parameter, so that the per-element
+// accumulation of the dual norms compiles to one or two instructions instead of a chain of tests.
+template <int kP>
 __global__ void __launch_bounds__(kThreads)
 softmax_bounds_kernel(const float* __restrict__ lw, const float* __restrict__ uw, const float* __restrict__ lb,
                       const float* __restrict__ ub, float* __restrict__ o_lw, float* __restrict__ o_uw,
                       float* __restrict__ o_lb, float* __restrict__ o_ub, float* __restrict__ o_l,
-                      float* __restrict__ o_u, int Di, int Do, int words, int p, float eps,
+                      float* __restrict__ o_u, int Di, int Do, int words, float eps,
                       int* __restrict__ violation) {
+  constexpr int p = kP;
   extern __shared__ __align__(16) float smem[];
   float* s_l = smem;                       // [Di][32] scores lw
   float* s_u = s_l + (size_t)Di * kCW;     // [Di][32] scores uw
@@ -280,11 +284,17 @@ extern "C" int fb_softmax_ranges_f32(const float* lw, const float* uw, const flo
   if (!aligned16(lw) || !aligned16(uw) || !aligned16(out_lw) || !aligned16(out_uw)) return FB_ERR_ALIGN;
   const double mw = (double)rows * Di * Do, mb = (double)rows * Do;
   ProfileScope prof(PK_RELAX, 30.0 * mw, 4.0 * (4 * mw + 4 * mb), stream);
-  if (smem > 48 * 1024)
-    FB_CUDA_OK(cudaFuncSetAttribute(softmax_bounds_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  softmax_bounds_kernel<<<(unsigned)rows, kThreads, smem, (cudaStream_t)stream>>>(lw, uw, lb, ub, out_lw, out_uw, out_lb,
-                                                                                  out_ub, out_l, out_u, Di, Do, words, p,
-                                                                                  eps, violation);
+#define FB_SOFTMAX_LAUNCH(P)                                                                                          \
+  do {                                                                                                                \
+    if (smem > 48 * 1024)                                                                                             \
+      FB_CUDA_OK(cudaFuncSetAttribute(softmax_bounds_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    softmax_bounds_kernel<P><<<(unsigned)rows, kThreads, smem, (cudaStream_t)stream>>>(                                \
+        lw, uw, lb, ub, out_lw, out_uw, out_lb, out_ub, out_l, out_u, Di, Do, words, eps, violation);                  \
+  } while (0)
+  if (p == FB_PINF) FB_SOFTMAX_LAUNCH(FB_PINF);
+  else if (p == FB_P2) FB_SOFTMAX_LAUNCH(FB_P2);
+  else FB_SOFTMAX_LAUNCH(FB_P1);
+#undef FB_SOFTMAX_LAUNCH
   FB_LAUNCH_OK();
   return FB_OK;
 }
