@@ -127,21 +127,6 @@ struct SharedLayout {
   __host__ __device__ static constexpr uint32_t bars() { return out() + kOutStageBytes; }
 };
 
-// Partial dual norm of one column of a staged 128-row box (128-byte swizzle) over the 64 rows with
-// (row & 4) == rsel: rows 8 * i + rsel + {0, 1, 2, 3}, the four loads first, then the four accumulations.
-template <int kP>
-__device__ __forceinline__ float column_partial(const uint8_t* sb, int rsel, int chunk) {
-  float acc = 0.f;
-  for (int i8 = 0; i8 < 16; ++i8) {
-    float v[4];
-#pragma unroll
-    for (int k = 0; k < 4; ++k) v[k] = *reinterpret_cast<const float*>(sb + swz(8 * i8 + rsel + k, chunk));
-#pragma unroll
-    for (int k = 0; k < 4; ++k) acc = norm_accum(kP, acc, v[k]);
-  }
-  return acc;
-}
-
 // kCoef: column slopes of a relaxation are applied to the operands on the fly (a separate instantiation, so
 // that the plain kernel keeps its register allocation).
 // kNorm: the epilogue also writes the dual norm over the 128 rows of every output column of the tile,
@@ -402,10 +387,15 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
         const int c = (ew & 1) * 16 + (lane & 15);
         const int rsel = (lane >> 4) * 4;
         const uint8_t* sb = base_ptr + SharedLayout::out() + (uint32_t)box * kOutBoxBytes + (c & 3) * 4;
-        // (the kind of norm is decided once, outside the loops: a test per element costs more than the sum)
-        float acc = norm_p == FB_PINF ? column_partial<FB_PINF>(sb, rsel, c >> 2)
-                  : norm_p == FB_P2   ? column_partial<FB_P2>(sb, rsel, c >> 2)
-                                      : column_partial<FB_P1>(sb, rsel, c >> 2);
+        float acc = 0.f;
+        for (int i8 = 0; i8 < 16; ++i8) {
+          // rows 8 * i8 + rsel + {0, 1, 2, 3}: the four loads first, then the four accumulations
+          float v[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) v[k] = *reinterpret_cast<const float*>(sb + swz(8 * i8 + rsel + k, c >> 2));
+#pragma unroll
+          for (int k = 0; k < 4; ++k) acc = norm_accum(norm_p, acc, v[k]);
+        }
         acc = norm_finish(norm_p, norm_combine(norm_p, acc, __shfl_xor_sync(0xffffffffu, acc, 16)));
         const int n = nx + (box & 1) * 32 + c;
         if (lane < 16 && n < N) (box < 2 ? norm_lo : norm_up)[(int64_t)(my / BM) * N + n] = acc;

@@ -58,7 +58,9 @@ softmax_bounds_kernel(const float* __restrict__ lw, const float* __restrict__ uw
   // column-wise dual norm of (a[r][c] * ka[c], b[r][c] * kb[c]) over the rows of every word block,
   // added word by word onto the start values in nl / nu (the bias terms), as the reference's
   // concretize does; result for threads tid < 32 (column tid)
-  auto column_norms = [&](bool from_global, const float* ka, const float* kb, float& nl, float& nu) {
+  // With row_sums (second pass only) the same scaled values also give the sums over the features of every
+  // row, s_sl / s_su: the denominator of the softmax.
+  auto column_norms = [&](bool from_global, bool row_sums, const float* ka, const float* kb, float& nl, float& nu) {
     float tl = nl, tu = nu;
     for (int w = 0; w < words; ++w) {
       float al[4] = {0.f, 0.f, 0.f, 0.f}, au[4] = {0.f, 0.f, 0.f, 0.f};
@@ -76,6 +78,18 @@ softmax_bounds_kernel(const float* __restrict__ lw, const float* __restrict__ uw
           b = *reinterpret_cast<const float4*>(s_u + r * kCW + col);
           a.x = fmul(a.x, ka[col + 0]); a.y = fmul(a.y, ka[col + 1]); a.z = fmul(a.z, ka[col + 2]); a.w = fmul(a.w, ka[col + 3]);
           b.x = fmul(b.x, kb[col + 0]); b.y = fmul(b.y, kb[col + 1]); b.z = fmul(b.z, kb[col + 2]); b.w = fmul(b.w, kb[col + 3]);
+          if (row_sums) {
+            // the eight lanes that share a row (cvl = 0..7) add their four columns each
+            const unsigned group = 0xffu << (lane & 24);
+            float sa = fadd(fadd(a.x, a.y), fadd(a.z, a.w));
+            float sb = fadd(fadd(b.x, b.y), fadd(b.z, b.w));
+#pragma unroll
+            for (int s = 1; s < 8; s <<= 1) {
+              sa += __shfl_xor_sync(group, sa, s);
+              sb += __shfl_xor_sync(group, sb, s);
+            }
+            if (cvl == 0) { s_sl[r] = sa; s_su[r] = sb; }
+          }
         }
         al[0] = norm_accum(p, al[0], a.x); al[1] = norm_accum(p, al[1], a.y); al[2] = norm_accum(p, al[2], a.z); al[3] = norm_accum(p, al[3], a.w);
         au[0] = norm_accum(p, au[0], b.x); au[1] = norm_accum(p, au[1], b.y); au[2] = norm_accum(p, au[2], b.z); au[3] = norm_accum(p, au[3], b.w);
@@ -116,7 +130,7 @@ softmax_bounds_kernel(const float* __restrict__ lw, const float* __restrict__ uw
   float lbv = 0.f, ubv = 0.f;
   if (mine) { lbv = lb[row * Do + tid]; ubv = ub[row * Do + tid]; }
   float l = lbv, u = ubv;
-  column_norms(true, nullptr, nullptr, l, u);
+  column_norms(true, false, nullptr, nullptr, l, u);
   float* c_kl = s_col + 0 * kCW;   // exp slope on lw
   float* c_ku = s_col + 1 * kCW;   // exp slope on uw
   float* c_elb = s_col + 2 * kCW;  // exp.lb
@@ -129,21 +143,10 @@ softmax_bounds_kernel(const float* __restrict__ lw, const float* __restrict__ uw
     c_kl[tid] = c.c_ll; c_ku[tid] = c.c_uu; c_elb[tid] = c.nlb; c_eub[tid] = c.nub;
   }
   __syncthreads();
-  // ---- stage 2: row sums of exp.lw / exp.uw over the features, and the lower range of exp
-  for (int r = rg; r < Di; r += 32) {
-    const float4 a = *reinterpret_cast<const float4*>(s_l + r * kCW + col);
-    const float4 b = *reinterpret_cast<const float4*>(s_u + r * kCW + col);
-    float sa = fadd(fadd(fmul(a.x, c_kl[col]), fmul(a.y, c_kl[col + 1])), fadd(fmul(a.z, c_kl[col + 2]), fmul(a.w, c_kl[col + 3])));
-    float sb = fadd(fadd(fmul(b.x, c_ku[col]), fmul(b.y, c_ku[col + 1])), fadd(fmul(b.z, c_ku[col + 2]), fmul(b.w, c_ku[col + 3])));
-#pragma unroll
-    for (int s = 1; s < 8; s <<= 1) {
-      sa += __shfl_xor_sync(0xffffffffu, sa, s);
-      sb += __shfl_xor_sync(0xffffffffu, sb, s);
-    }
-    if (cvl == 0) { s_sl[r] = sa; s_su[r] = sb; }
-  }
+  // ---- stage 2: row sums of exp.lw / exp.uw over the features, and the lower range of exp (one pass over
+  // the tiles: the scaled values feed both)
   float la = mine ? c_elb[tid] : 0.f, ua_unused = mine ? c_eub[tid] : 0.f;
-  column_norms(false, c_kl, c_ku, la, ua_unused);
+  column_norms(false, true, c_kl, c_ku, la, ua_unused);
   if (tid < kCW) c_la[tid] = la;
   // ---- stage 3: bounds of the sum, reciprocal relaxation (Bounds.py:1136-1161), range of 1/sum
   float s_lb = 0.f, s_ub = 0.f;
