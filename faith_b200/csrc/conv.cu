@@ -16,12 +16,15 @@ constexpr int kThreads = 256;
 constexpr int CC = 4;            // input channels per shared-memory stage
 constexpr int kStageBatch = 6;   // input elements per thread whose global loads are in flight together
 
-template <int TH, int TW, int CO>
-__global__ void __launch_bounds__(kThreads)
+// KS: filter size when it is the same in both directions and known at compile time (3), 0 = taken from the
+// arguments; with KS the tap loops are unrolled and their index arithmetic disappears.
+template <int TH, int TW, int CO, int KS>
+__global__ void __launch_bounds__(kThreads, 2)
 conv_bounds_kernel(const float* __restrict__ x_lo, const float* __restrict__ x_up, const float* __restrict__ Wt,
                    const float* __restrict__ bias, float* __restrict__ y_lo, float* __restrict__ y_up,
-                   int Cin, int H, int W, int Cout, int Kh, int Kw, int stride, int pad, int Ho, int Wo,
+                   int Cin, int H, int W, int Cout, int Kh_arg, int Kw_arg, int stride, int pad, int Ho, int Wo,
                    int tiles_h, int tiles_w, int co_chunks) {
+  const int Kh = KS ? KS : Kh_arg, Kw = KS ? KS : Kw_arg;
   extern __shared__ __align__(16) float smem[];
   const int in_h = (TH - 1) * stride + Kh, in_w = (TW - 1) * stride + Kw;
   const int plane = in_h * in_w;
@@ -82,10 +85,14 @@ conv_bounds_kernel(const float* __restrict__ x_lo, const float* __restrict__ x_u
       s_w[f] = w;
     }
     __syncthreads();
+    const int s0 = th * stride * in_w + tw * stride;   // this thread's window in a staged plane
+#pragma unroll(KS ? CC : 1)
     for (int c = 0; c < CC; ++c) {
-      for (int kh = 0; kh < Kh; ++kh) {
-        for (int kw = 0; kw < Kw; ++kw) {
-          const int si = c * plane + (th * stride + kh) * in_w + tw * stride + kw;
+#pragma unroll
+      for (int kh = 0; kh < (KS ? KS : Kh); ++kh) {
+#pragma unroll
+        for (int kw = 0; kw < (KS ? KS : Kw); ++kw) {
+          const int si = s0 + c * plane + kh * in_w + kw;
           const float vc = s_c[si], vr = s_r[si];
           const float* wp = s_w + ((c * Kh + kh) * Kw + kw) * CO;
 #pragma unroll
@@ -114,7 +121,7 @@ conv_bounds_kernel(const float* __restrict__ x_lo, const float* __restrict__ x_u
   }
 }
 
-template <int TH, int TW, int CO>
+template <int TH, int TW, int CO, int KS>
 int launch_conv_t(const float* x_lo, const float* x_up, const float* Wt, const float* bias, float* y_lo, float* y_up,
                   int64_t N, int Cin, int H, int W, int Cout, int Kh, int Kw, int stride, int pad, int Ho, int Wo,
                   cudaStream_t st) {
@@ -126,8 +133,8 @@ int launch_conv_t(const float* x_lo, const float* x_up, const float* Wt, const f
   const int64_t blocks = N * co_chunks * tiles_h * tiles_w;
   if (blocks > 0x7fffffff) return FB_ERR_SHAPE;
   if (smem > 48 * 1024)
-    FB_CUDA_OK(cudaFuncSetAttribute(conv_bounds_kernel<TH, TW, CO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  conv_bounds_kernel<TH, TW, CO><<<(unsigned)blocks, kThreads, smem, st>>>(x_lo, x_up, Wt, bias, y_lo, y_up, Cin, H, W, Cout,
+    FB_CUDA_OK(cudaFuncSetAttribute(conv_bounds_kernel<TH, TW, CO, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  conv_bounds_kernel<TH, TW, CO, KS><<<(unsigned)blocks, kThreads, smem, st>>>(x_lo, x_up, Wt, bias, y_lo, y_up, Cin, H, W, Cout,
                                                                          Kh, Kw, stride, pad, Ho, Wo, tiles_h, tiles_w,
                                                                          co_chunks);
   FB_LAUNCH_OK();
@@ -140,8 +147,12 @@ int launch_conv(const float* x_lo, const float* x_up, const float* Wt, const flo
   if (N == 0) return FB_OK;
   const bool narrow = Wo <= 16, wide_co = Cout > 16;
 #define FB_CONV_ARGS x_lo, x_up, Wt, bias, y_lo, y_up, N, Cin, H, W, Cout, Kh, Kw, stride, pad, Ho, Wo, st
-  if (narrow) return wide_co ? launch_conv_t<16, 16, 32>(FB_CONV_ARGS) : launch_conv_t<16, 16, 16>(FB_CONV_ARGS);
-  return wide_co ? launch_conv_t<8, 32, 32>(FB_CONV_ARGS) : launch_conv_t<8, 32, 16>(FB_CONV_ARGS);
+  if (Kh == 3 && Kw == 3) {
+    if (narrow) return wide_co ? launch_conv_t<16, 16, 32, 3>(FB_CONV_ARGS) : launch_conv_t<16, 16, 16, 3>(FB_CONV_ARGS);
+    return wide_co ? launch_conv_t<8, 32, 32, 3>(FB_CONV_ARGS) : launch_conv_t<8, 32, 16, 3>(FB_CONV_ARGS);
+  }
+  if (narrow) return wide_co ? launch_conv_t<16, 16, 32, 0>(FB_CONV_ARGS) : launch_conv_t<16, 16, 16, 0>(FB_CONV_ARGS);
+  return wide_co ? launch_conv_t<8, 32, 32, 0>(FB_CONV_ARGS) : launch_conv_t<8, 32, 16, 0>(FB_CONV_ARGS);
 #undef FB_CONV_ARGS
 }
 
