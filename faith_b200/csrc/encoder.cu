@@ -239,11 +239,17 @@ extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, i
     const fb_encoder_layer& ly = enc->layer[li];
     const BoundSet X = slot[A], T3 = slot[Dd];
     BoundSet T1 = slot[B], T2 = slot[C];
+    // Xin: the layer input as the products read it.  Before the first relaxation the two lines of the bound
+    // coincide (lw == uw, VerifierForward.py:127-152 through an exact layer norm); handing the GEMM one
+    // tensor as both lines selects its zero-radius instantiation.  (X itself keeps both buffers: they serve
+    // as scratch later in the layer.)
+    BoundSet Xin = X;
+    if (li == 0) Xin.uw = Xin.lw;
     // queries and keys, split into heads: [S*H, L, Di, d].  Where the shapes allow it the projection also
     // returns the concretised range of its result (column norms taken in the GEMM epilogue), which the
     // product below would otherwise compute in a pass of its own over the operand.
     int given = 0;
-    int qrc = fb_matmul_heads_ranges_f32(X.lw, X.uw, X.lb, X.ub, ly.q_w, ly.q_b, T2.lw, T2.uw, T2.lb, T2.ub, range[0],
+    int qrc = fb_matmul_heads_ranges_f32(Xin.lw, Xin.uw, X.lb, X.ub, ly.q_w, ly.q_b, T2.lw, T2.uw, T2.lb, T2.ub, range[0],
                                          range[1], norm_ws, rows, Di, D, D, L, H, words, p, eps, stream);
     if (qrc == FB_OK) {
       given |= 1;
@@ -253,7 +259,7 @@ extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, i
     } else {
       return qrc;
     }
-    qrc = fb_matmul_heads_ranges_f32(X.lw, X.uw, X.lb, X.ub, ly.k_w, ly.k_b, T3.lw, T3.uw, T3.lb, T3.ub, range[2], range[3],
+    qrc = fb_matmul_heads_ranges_f32(Xin.lw, Xin.uw, X.lb, X.ub, ly.k_w, ly.k_b, T3.lw, T3.uw, T3.lb, T3.ub, range[2], range[3],
                                      norm_ws, rows, Di, D, D, L, H, words, p, eps, stream);
     if (qrc == FB_OK) {
       given |= 2;
@@ -291,7 +297,7 @@ extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, i
     int crc = FB_ERR_SHAPE;
     if (L % 4 == 0) {
       int vgiven = pgiven;
-      const int vrc = fb_matmul_heads_ranges_f32(X.lw, X.uw, X.lb, X.ub, ly.v_w, ly.v_b, T3.lw, T3.uw, T3.lb, T3.ub, range[2],
+      const int vrc = fb_matmul_heads_ranges_f32(Xin.lw, Xin.uw, X.lb, X.ub, ly.v_w, ly.v_b, T3.lw, T3.uw, T3.lb, T3.ub, range[2],
                                                  range[3], norm_ws, rows, Di, D, D, L, H, words, p, eps, stream);
       if (vrc == FB_OK) {
         vgiven |= 2;

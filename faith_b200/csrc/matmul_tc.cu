@@ -88,18 +88,19 @@ constexpr uint32_t kAccC = 0, kAccR = 64, kCorC = 128, kCorR = 192, kABase = 256
 // keeps the tensor core busy for 32, so a single issuer leaves it idle most of the time.
 // kFirst: this k-block starts a tile, so the first MMA into each accumulator overwrites.
 // planes of B: 0 W_hi, 1 W_lo, 2 |W|_hi, 3 |W|_lo;  planes of A: 0 c_hi, 1 c_lo, 2 r_hi, 3 r_lo
-template <int kRole, bool kFirst>
+template <int kRole, bool kFirst, bool kPoint>
 __device__ __forceinline__ void issue_kblock(const uint32_t (&blo)[4][4], const uint32_t (&acol)[4][4], uint32_t b_hi,
                                              uint32_t d0, uint32_t d1, uint32_t idesc) {
+  constexpr int kSteps = (kPoint && kRole == 2) ? 0 : 4;   // zero radius: no radius products at all
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
+  for (int j = 0; j < kSteps; ++j) {
     if (kRole == 0) {
       if (j == 0 && kFirst) {
         mma_tf32_ts_lean<false>(d0, acol[0][j], blo[0][j], b_hi, idesc);
-        mma_tf32_ts_lean<false>(d1, acol[2][j], blo[2][j], b_hi, idesc);
+        if (!kPoint) mma_tf32_ts_lean<false>(d1, acol[2][j], blo[2][j], b_hi, idesc);
       } else {
         mma_tf32_ts_lean<true>(d0, acol[0][j], blo[0][j], b_hi, idesc);
-        mma_tf32_ts_lean<true>(d1, acol[2][j], blo[2][j], b_hi, idesc);
+        if (!kPoint) mma_tf32_ts_lean<true>(d1, acol[2][j], blo[2][j], b_hi, idesc);
       }
     } else {
       constexpr int lo = kRole == 1 ? 1 : 3, hi = kRole == 1 ? 0 : 2;   // A planes; B planes are hi, lo the other way round
@@ -109,11 +110,11 @@ __device__ __forceinline__ void issue_kblock(const uint32_t (&blo)[4][4], const 
     }
   }
 }
-template <int kRole>
+template <int kRole, bool kPoint>
 __device__ __forceinline__ void issue_kblock_role(bool first, const uint32_t (&blo)[4][4], const uint32_t (&acol)[4][4],
                                                   uint32_t b_hi, uint32_t d0, uint32_t d1, uint32_t idesc) {
-  if (first) issue_kblock<kRole, true>(blo, acol, b_hi, d0, d1, idesc);
-  else issue_kblock<kRole, false>(blo, acol, b_hi, d0, d1, idesc);
+  if (first) issue_kblock<kRole, true, kPoint>(blo, acol, b_hi, d0, d1, idesc);
+  else issue_kblock<kRole, false, kPoint>(blo, acol, b_hi, d0, d1, idesc);
 }
 
 // Instruction descriptor: D fp32, A and B tf32, both K-major, M = 128, N = 128.
@@ -136,7 +137,10 @@ struct SharedLayout {
 // kResid: a residual bound (same shape and layout as the result, plain store only) is added to the result in
 // the epilogue: its tile is fetched by TMA into the staging buffer while the k-blocks of the tile are still
 // running, so the layer norm that follows reads one tensor pair instead of two.
-template <bool kCoef, bool kNorm, bool kResid>
+// kPoint: x_lw and x_uw are the same tensor (every stage before the first relaxation): the radius is zero, so
+// x_uw is not loaded, no radius planes are written, the radius products are not issued and the epilogue reads
+// two accumulators; the results equal those of the general kernel bit for bit.
+template <bool kCoef, bool kNorm, bool kResid, bool kPoint>
 __global__ void __launch_bounds__(kThreads, 1)
 split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_constant__ CUtensorMap tm_up,
                    const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_out_lo,
@@ -209,10 +213,10 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
         if (it >= kRawStages &&
             !mbar_wait_warp(bar_raw_empty + 8 * rs, (uint32_t)((it / kRawStages - 1) & 1), cta_abort)) { ok = false; break; }
         if (lane == 0) {
-          mbar_arrive_expect_tx(full, kRawStageBytes);
+          mbar_arrive_expect_tx(full, kPoint ? kRawStageBytes - kTileBytes : kRawStageBytes);
           const uint32_t dst = base + SharedLayout::raw(rs);
           tma_load_2d(dst, &tm_lo, kb * BK, m0, full);
-          tma_load_2d(dst + kTileBytes, &tm_up, kb * BK, m0, full);
+          if (!kPoint) tma_load_2d(dst + kTileBytes, &tm_up, kb * BK, m0, full);
           tma_load_2d(dst + 2 * kTileBytes, &tm_w, kb * BK, n0, full);
         }
         __syncwarp();
@@ -250,13 +254,13 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
         tc_fence_after();
         if (lane == 0) {
           if (s == 0) {
-            if (role == 0) issue_kblock_role<0>(kb == 0, blo[0], acol[0], b_hi, d0, d1, kInstrDesc);
-            else if (role == 1) issue_kblock_role<1>(kb == 0, blo[0], acol[0], b_hi, d0, d1, kInstrDesc);
-            else issue_kblock_role<2>(kb == 0, blo[0], acol[0], b_hi, d0, d1, kInstrDesc);
+            if (role == 0) issue_kblock_role<0, kPoint>(kb == 0, blo[0], acol[0], b_hi, d0, d1, kInstrDesc);
+            else if (role == 1) issue_kblock_role<1, kPoint>(kb == 0, blo[0], acol[0], b_hi, d0, d1, kInstrDesc);
+            else issue_kblock_role<2, kPoint>(kb == 0, blo[0], acol[0], b_hi, d0, d1, kInstrDesc);
           } else {
-            if (role == 0) issue_kblock_role<0>(kb == 0, blo[1], acol[1], b_hi, d0, d1, kInstrDesc);
-            else if (role == 1) issue_kblock_role<1>(kb == 0, blo[1], acol[1], b_hi, d0, d1, kInstrDesc);
-            else issue_kblock_role<2>(kb == 0, blo[1], acol[1], b_hi, d0, d1, kInstrDesc);
+            if (role == 0) issue_kblock_role<0, kPoint>(kb == 0, blo[1], acol[1], b_hi, d0, d1, kInstrDesc);
+            else if (role == 1) issue_kblock_role<1, kPoint>(kb == 0, blo[1], acol[1], b_hi, d0, d1, kInstrDesc);
+            else issue_kblock_role<2, kPoint>(kb == 0, blo[1], acol[1], b_hi, d0, d1, kInstrDesc);
           }
           tc_commit(bar_mma_done + 8 * s);
           if (kb == nkb - 1) tc_commit(bar_acc_ready);
@@ -318,8 +322,10 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
         uint32_t t0[8], t1[8], t2[8], t3[8];
         tmem_ld8(tmem_base + lane_addr + kAccC + ncol, t0);
         tmem_ld8(tmem_base + lane_addr + kCorC + ncol, t1);
-        tmem_ld8(tmem_base + lane_addr + kAccR + ncol, t2);
-        tmem_ld8(tmem_base + lane_addr + kCorR + ncol, t3);
+        if (!kPoint) {
+          tmem_ld8(tmem_base + lane_addr + kAccR + ncol, t2);
+          tmem_ld8(tmem_base + lane_addr + kCorR + ncol, t3);
+        }
         tmem_wait_ld();
         if (cq == 4 * chalf + 3) {
           // the accumulators are in registers now: hand tensor memory back to the MMA issuers
@@ -334,9 +340,14 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const float yc = fadd(__uint_as_float(t0[q * 4 + i]), __uint_as_float(t1[q * 4 + i]));
-            const float yr = fadd(__uint_as_float(t2[q * 4 + i]), __uint_as_float(t3[q * 4 + i]));
-            lo[i] = fsub(yc, yr);
-            up[i] = fadd(yc, yr);
+            if (kPoint) {
+              lo[i] = yc;
+              up[i] = yc;
+            } else {
+              const float yr = fadd(__uint_as_float(t2[q * 4 + i]), __uint_as_float(t3[q * 4 + i]));
+              lo[i] = fsub(yc, yr);
+              up[i] = fadd(yc, yr);
+            }
             if (bias != nullptr) {
               const int n = nx + ncol + q * 4 + i;
               const float bv = n < N ? bias[n] : 0.f;
@@ -448,7 +459,7 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
         for (int q = 0; q < 4; ++q) {
           const uint32_t off = swz(row, half * 4 + q);
           vl[q] = *reinterpret_cast<const float4*>(raw + off);
-          vu[q] = *reinterpret_cast<const float4*>(raw + kTileBytes + off);
+          vu[q] = kPoint ? vl[q] : *reinterpret_cast<const float4*>(raw + kTileBytes + off);
         }
 #pragma unroll
         for (int q = 0; q < 2; ++q) vw[q] = *reinterpret_cast<const float4*>(raw + 2 * kTileBytes + swz(wrow, wchunk + q));
@@ -481,7 +492,10 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
       // loads, k-block it+2 was seen overwriting rows of k-block it that were still being read.)
       // The empty asm statements keep the arithmetic above from being moved below the arrive.
 #pragma unroll
-      for (int i = 0; i < 16; ++i) asm volatile("" : "+f"(c[i]), "+f"(r[i]));
+      for (int i = 0; i < 16; ++i) {
+        if (kPoint) asm volatile("" : "+f"(c[i]));
+        else asm volatile("" : "+f"(c[i]), "+f"(r[i]));
+      }
 #pragma unroll
       for (int i = 0; i < 8; ++i) asm volatile("" : "+r"(whi[i]), "+r"(wlo[i]));
       __syncwarp();
@@ -498,10 +512,12 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
         for (int i = 0; i < 16; ++i) split_tf32(c[i], hi[i], lo[i]);
         tmem_st16(a_cols + 0, hi);
         tmem_st16(a_cols + 32, lo);
+        if (!kPoint) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) split_tf32(r[i], hi[i], lo[i]);
-        tmem_st16(a_cols + 64, hi);
-        tmem_st16(a_cols + 96, lo);
+          for (int i = 0; i < 16; ++i) split_tf32(r[i], hi[i], lo[i]);
+          tmem_st16(a_cols + 64, hi);
+          tmem_st16(a_cols + 96, lo);
+        }
         uint8_t* pl = base_ptr + SharedLayout::planes(g);
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
@@ -510,8 +526,10 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
           const uint32_t m = 0x7fffffffu;
           *reinterpret_cast<uint4*>(pl + 0 * kWTileBytes + off) = make_uint4(whi[q * 4], whi[q * 4 + 1], whi[q * 4 + 2], whi[q * 4 + 3]);
           *reinterpret_cast<uint4*>(pl + 1 * kWTileBytes + off) = make_uint4(wlo[q * 4], wlo[q * 4 + 1], wlo[q * 4 + 2], wlo[q * 4 + 3]);
-          *reinterpret_cast<uint4*>(pl + 2 * kWTileBytes + off) = make_uint4(whi[q * 4] & m, whi[q * 4 + 1] & m, whi[q * 4 + 2] & m, whi[q * 4 + 3] & m);
-          *reinterpret_cast<uint4*>(pl + 3 * kWTileBytes + off) = make_uint4(wlo[q * 4] & m, wlo[q * 4 + 1] & m, wlo[q * 4 + 2] & m, wlo[q * 4 + 3] & m);
+          if (!kPoint) {
+            *reinterpret_cast<uint4*>(pl + 2 * kWTileBytes + off) = make_uint4(whi[q * 4] & m, whi[q * 4 + 1] & m, whi[q * 4 + 2] & m, whi[q * 4 + 3] & m);
+            *reinterpret_cast<uint4*>(pl + 3 * kWTileBytes + off) = make_uint4(wlo[q * 4] & m, wlo[q * 4 + 1] & m, wlo[q * 4 + 2] & m, wlo[q * 4 + 3] & m);
+          }
         }
       }
       fence_async_smem();   // B planes were written through the generic proxy; the MMA reads them through the async proxy
@@ -613,15 +631,17 @@ int launch_split_sign_tc(const float* a_lo, const float* a_up, const float* W, c
   cudaError_t attr_err = cudaSuccess;
   std::call_once(attr_once[dev & 63], [&]() {
     const int bytes = (int)kSmemBytes;
-    attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<false, false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     if (attr_err == cudaSuccess)
-      attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<true, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+      attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<true, false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     if (attr_err == cudaSuccess)
-      attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<false, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+      attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<false, true, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     if (attr_err == cudaSuccess)
-      attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+      attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<false, false, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     if (attr_err == cudaSuccess)
-      attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+      attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<true, false, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (attr_err == cudaSuccess)
+      attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<false, true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
   });
   FB_CUDA_OK(attr_err);
   // persistent: one CTA per SM (tensor memory and shared memory allow exactly one)
@@ -629,15 +649,17 @@ int launch_split_sign_tc(const float* a_lo, const float* a_up, const float* W, c
   const unsigned grid = (unsigned)(total_tiles < sms ? total_tiles : sms);
 #define FB_TC_ARGS tm_lo, tm_up, tm_w, tm_out_lo, tm_out_up, tm_res_lo, tm_res_up, bias, M, N, K, gn, total_tiles, split_rows, split_d
   if (coef_l != nullptr && res_lo != nullptr)
-    split_sign_gemm_tc<true, false, true><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, coef_l, coef_u, coef_di, nullptr, nullptr, 0);
+    split_sign_gemm_tc<true, false, true, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, coef_l, coef_u, coef_di, nullptr, nullptr, 0);
   else if (coef_l != nullptr)
-    split_sign_gemm_tc<true, false, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, coef_l, coef_u, coef_di, nullptr, nullptr, 0);
+    split_sign_gemm_tc<true, false, false, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, coef_l, coef_u, coef_di, nullptr, nullptr, 0);
+  else if (norm_lo != nullptr && a_lo == a_up)   // one tensor as both lines: zero radius
+    split_sign_gemm_tc<false, true, false, true><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, norm_lo, norm_up, norm_p);
   else if (norm_lo != nullptr)
-    split_sign_gemm_tc<false, true, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, norm_lo, norm_up, norm_p);
+    split_sign_gemm_tc<false, true, false, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, norm_lo, norm_up, norm_p);
   else if (res_lo != nullptr)
-    split_sign_gemm_tc<false, false, true><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, nullptr, nullptr, 0);
+    split_sign_gemm_tc<false, false, true, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, nullptr, nullptr, 0);
   else
-    split_sign_gemm_tc<false, false, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, nullptr, nullptr, 0);
+    split_sign_gemm_tc<false, false, false, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, nullptr, nullptr, 0);
 #undef FB_TC_ARGS
   FB_LAUNCH_OK();
   return FB_OK;

@@ -708,3 +708,27 @@ def test_dense_with_residual_added_in_the_epilogue(with_slopes, Do, Dy):
     with pytest.raises(_lib.FaithError):   # 64 bias rows: below the tensor-core kernel's minimum
         ops.matmul_residual(lw[:2].contiguous(), uw[:2].contiguous(), lb[:2].contiguous(), ub[:2].contiguous(), W, bias,
                             tuple(v[:2].contiguous() for v in res))
+
+
+@pytest.mark.parametrize("p,words", [(float("inf"), 1), (2.0, 2)])
+def test_projection_of_a_point_bound_takes_the_zero_radius_kernel(p, words):
+    """One tensor passed as both lw and uw (every stage before the first relaxation) selects the GEMM
+    instantiation that skips the radius half; its results equal those of the general kernel, fed a separate
+    copy of the tensor, bit for bit; lower and upper outputs coincide."""
+    from faith_b200 import ops
+    S, L, H, d = 2, 32, 4, 32
+    D, Di, eps = H * d, 128 * words, 0.05
+    t = [v.to(DEV) for v in cases.rand_bounds(903, S, L, Di, D)]
+    g = torch.Generator().manual_seed(14)
+    W = (torch.randn(D, D, generator=g) / math.sqrt(D)).to(DEV)
+    bias = (torch.randn(D, generator=g) * 0.1).to(DEV)
+    lw, lb = t[0], t[1]
+    general = ops.matmul_heads_ranges(lw, lw.clone(), lb, lb.clone(), W, bias, H, p, eps, words)
+    point = ops.matmul_heads_ranges(lw, lw, lb, lb, W, bias, H, p, eps, words)
+    for a, b, name in zip(point, general, ("lw", "uw", "lb", "ub", "l", "u")):
+        assert torch.equal(a, b), name
+    assert torch.equal(point[0], point[1])
+    for _ in range(5):
+        again = ops.matmul_heads_ranges(lw, lw, lb, lb, W, bias, H, p, eps, words)
+        for a, b in zip(again, point):
+            assert torch.equal(a, b)
