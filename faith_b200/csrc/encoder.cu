@@ -332,7 +332,7 @@ extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, i
     }
     // attention output: dense, + residual, layer norm -> T3
     // (the residual is added by the GEMM epilogue where the shapes allow it: the layer norm then reads one bound)
-    const int arc = fb_matmul_residual_f32(T2.lw, T2.uw, T2.lb, T2.ub, nullptr, nullptr, ly.ao_w, ly.ao_b, X.lw, X.uw, X.lb,
+    const int arc = fb_matmul_residual_f32(T2.lw, T2.uw, T2.lb, T2.ub, nullptr, nullptr, ly.ao_w, ly.ao_b, Xin.lw, Xin.uw, X.lb,
                                            X.ub, T1.lw, T1.uw, T1.lb, T1.ub, rows, Di, D, D, stream);
     if (arc == FB_OK) {
       FB_TRY(norm_residual(enc, T1, nullptr, ly.ln1_g, ly.ln1_b, T3, rows, Di, D, stream));
