@@ -245,32 +245,39 @@ extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, i
     // as scratch later in the layer.)
     BoundSet Xin = X;
     if (li == 0) Xin.uw = Xin.lw;
+    // The projections of such an input have coinciding lines as well: in the first layer Q, K and V are kept
+    // once (both line pointers name the lw buffer; the zero-radius GEMM stores the same tile through both),
+    // so the products that read them fetch every tile from HBM once.
+    BoundSet Qh = T2, Kh = T3;
+    if (li == 0) { Qh.uw = Qh.lw; Kh.uw = Kh.lw; }
     // queries and keys, split into heads: [S*H, L, Di, d].  Where the shapes allow it the projection also
     // returns the concretised range of its result (column norms taken in the GEMM epilogue), which the
     // product below would otherwise compute in a pass of its own over the operand.
     int given = 0;
-    int qrc = fb_matmul_heads_ranges_f32(Xin.lw, Xin.uw, X.lb, X.ub, ly.q_w, ly.q_b, T2.lw, T2.uw, T2.lb, T2.ub, range[0],
+    int qrc = fb_matmul_heads_ranges_f32(Xin.lw, Xin.uw, X.lb, X.ub, ly.q_w, ly.q_b, Qh.lw, Qh.uw, T2.lb, T2.ub, range[0],
                                          range[1], norm_ws, rows, Di, D, D, L, H, words, p, eps, stream);
     if (qrc == FB_OK) {
       given |= 1;
     } else if (qrc == FB_ERR_SHAPE) {
+      Qh = T2;
       FB_TRY(fb_matmul_heads_f32(X.lw, X.uw, X.lb, X.ub, ly.q_w, ly.q_b, T2.lw, T2.uw, T2.lb, T2.ub, rows, Di, D, D, L, H,
                                  stream));
     } else {
       return qrc;
     }
-    qrc = fb_matmul_heads_ranges_f32(Xin.lw, Xin.uw, X.lb, X.ub, ly.k_w, ly.k_b, T3.lw, T3.uw, T3.lb, T3.ub, range[2], range[3],
+    qrc = fb_matmul_heads_ranges_f32(Xin.lw, Xin.uw, X.lb, X.ub, ly.k_w, ly.k_b, Kh.lw, Kh.uw, T3.lb, T3.ub, range[2], range[3],
                                      norm_ws, rows, Di, D, D, L, H, words, p, eps, stream);
     if (qrc == FB_OK) {
       given |= 2;
     } else if (qrc == FB_ERR_SHAPE) {
+      Kh = T3;
       FB_TRY(fb_matmul_heads_f32(X.lw, X.uw, X.lb, X.ub, ly.k_w, ly.k_b, T3.lw, T3.uw, T3.lb, T3.ub, rows, Di, D, D, L, H,
                                  stream));
     } else {
       return qrc;
     }
     // scores [S*H, L, Di, L], scaled by 1/sqrt(d) -> T1
-    FB_TRY(fb_dot_product_given_f32(T2.lw, T2.uw, T2.lb, T2.ub, T3.lw, T3.uw, T3.lb, T3.ub, T1.lw, T1.uw, T1.lb, T1.ub,
+    FB_TRY(fb_dot_product_given_f32(Qh.lw, Qh.uw, T2.lb, T2.ub, Kh.lw, Kh.uw, T3.lb, T3.ub, T1.lw, T1.uw, T1.lb, T1.ub,
                                     range[0], range[1], range[2], range[3], S * H, L, L, Di, d, words, p, eps, inv_sqrt_d,
                                     FB_NATIVE, 1, given, stream));
     const int64_t hrows = (int64_t)S * H * L;
@@ -297,18 +304,21 @@ extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, i
     int crc = FB_ERR_SHAPE;
     if (L % 4 == 0) {
       int vgiven = pgiven;
-      const int vrc = fb_matmul_heads_ranges_f32(Xin.lw, Xin.uw, X.lb, X.ub, ly.v_w, ly.v_b, T3.lw, T3.uw, T3.lb, T3.ub, range[2],
+      BoundSet Vh = T3;
+      if (li == 0) Vh.uw = Vh.lw;
+      const int vrc = fb_matmul_heads_ranges_f32(Xin.lw, Xin.uw, X.lb, X.ub, ly.v_w, ly.v_b, Vh.lw, Vh.uw, T3.lb, T3.ub, range[2],
                                                  range[3], norm_ws, rows, Di, D, D, L, H, words, p, eps, stream);
       if (vrc == FB_OK) {
         vgiven |= 2;
       } else if (vrc == FB_ERR_SHAPE) {
+        Vh = T3;
         FB_TRY(fb_matmul_heads_f32(X.lw, X.uw, X.lb, X.ub, ly.v_w, ly.v_b, T3.lw, T3.uw, T3.lb, T3.ub, rows, Di, D, D, L, H,
                                    stream));
       } else {
         return vrc;
       }
       // context, written head-merged as [S, L, Di, D] -> T2
-      crc = fb_context_given_f32(T1.lw, T1.uw, T1.lb, T1.ub, T3.lw, T3.uw, T3.lb, T3.ub, T2.lw, T2.uw, T2.lb, T2.ub,
+      crc = fb_context_given_f32(T1.lw, T1.uw, T1.lb, T1.ub, Vh.lw, Vh.uw, T3.lb, T3.ub, T2.lw, T2.uw, T2.lb, T2.ub,
                                  range[0], range[1], range[2], range[3], S * H, L, d, Di, L, words, p, eps, 1.0f, H, vgiven,
                                  stream);
       if (crc != FB_OK && crc != FB_ERR_SHAPE) return crc;
