@@ -219,11 +219,13 @@ extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, i
   {
     Positions pos = {{0, 0, 0, 0}};
     for (int w = 0; w < words; ++w) pos.v[w] = positions[w];
+    // (lw == uw at the input: the first layer reads the lw buffer as both lines, so the fused kernel is given
+    // that buffer twice and the uw buffer of the slot stays unwritten)
     if (enc->layer_norm == 1 && D == 128 && aligned16(emb) && aligned16(enc->emb_ln_g) && aligned16(enc->emb_ln_b)) {
       const int64_t n_w_rows = rows * Di, n_b_rows = rows;
       const int64_t want = ceil_div(n_w_rows + n_b_rows, 8), cap = (int64_t)device_info().sms * 16;
       input_bounds_norm128_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, st>>>(
-          emb, enc->emb_ln_g, enc->emb_ln_b, slot[A].lw, slot[A].uw, slot[A].lb, slot[A].ub, n_w_rows, n_b_rows, L, words, pos);
+          emb, enc->emb_ln_g, enc->emb_ln_b, slot[A].lw, slot[A].lw, slot[A].lb, slot[A].ub, n_w_rows, n_b_rows, L, words, pos);
       FB_LAUNCH_OK();
     } else {
       const int64_t n_w = rows * Di * D, n_b = rows * D;
@@ -260,7 +262,7 @@ extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, i
       given |= 1;
     } else if (qrc == FB_ERR_SHAPE) {
       Qh = T2;
-      FB_TRY(fb_matmul_heads_f32(X.lw, X.uw, X.lb, X.ub, ly.q_w, ly.q_b, T2.lw, T2.uw, T2.lb, T2.ub, rows, Di, D, D, L, H,
+      FB_TRY(fb_matmul_heads_f32(Xin.lw, Xin.uw, X.lb, X.ub, ly.q_w, ly.q_b, T2.lw, T2.uw, T2.lb, T2.ub, rows, Di, D, D, L, H,
                                  stream));
     } else {
       return qrc;
@@ -271,7 +273,7 @@ extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, i
       given |= 2;
     } else if (qrc == FB_ERR_SHAPE) {
       Kh = T3;
-      FB_TRY(fb_matmul_heads_f32(X.lw, X.uw, X.lb, X.ub, ly.k_w, ly.k_b, T3.lw, T3.uw, T3.lb, T3.ub, rows, Di, D, D, L, H,
+      FB_TRY(fb_matmul_heads_f32(Xin.lw, Xin.uw, X.lb, X.ub, ly.k_w, ly.k_b, T3.lw, T3.uw, T3.lb, T3.ub, rows, Di, D, D, L, H,
                                  stream));
     } else {
       return qrc;
@@ -312,7 +314,7 @@ extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, i
         vgiven |= 2;
       } else if (vrc == FB_ERR_SHAPE) {
         Vh = T3;
-        FB_TRY(fb_matmul_heads_f32(X.lw, X.uw, X.lb, X.ub, ly.v_w, ly.v_b, T3.lw, T3.uw, T3.lb, T3.ub, rows, Di, D, D, L, H,
+        FB_TRY(fb_matmul_heads_f32(Xin.lw, Xin.uw, X.lb, X.ub, ly.v_w, ly.v_b, T3.lw, T3.uw, T3.lb, T3.ub, rows, Di, D, D, L, H,
                                    stream));
       } else {
         return vrc;
@@ -325,7 +327,7 @@ extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, i
     }
     if (crc == FB_ERR_SHAPE) {
       // other shapes: values with position/feature swapped, [S*H, d, Di, L], and the general dot product
-      FB_TRY(dense(X, ly.v_w, ly.v_b, T2, rows, Di, D, D, stream));
+      FB_TRY(dense(Xin, ly.v_w, ly.v_b, T2, rows, Di, D, D, stream));
       FB_TRY(fb_split_heads_f32(T2.lw, T2.lb, T3.lw, T3.lb, S, L, Di, H, d, 1, stream));
       FB_TRY(fb_split_heads_f32(T2.uw, T2.ub, T3.uw, T3.ub, S, L, Di, H, d, 1, stream));
       FB_TRY(fb_dot_product_heads_f32(T1.lw, T1.uw, T1.lb, T1.ub, T3.lw, T3.uw, T3.lb, T3.ub, T2.lw, T2.uw, T2.lb, T2.ub,
@@ -348,7 +350,7 @@ extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, i
       FB_TRY(norm_residual(enc, T1, nullptr, ly.ln1_g, ly.ln1_b, T3, rows, Di, D, stream));
     } else if (arc == FB_ERR_SHAPE) {
       FB_TRY(dense(T2, ly.ao_w, ly.ao_b, T1, rows, Di, D, D, stream));
-      FB_TRY(norm_residual(enc, T1, &X, ly.ln1_g, ly.ln1_b, T3, rows, Di, D, stream));
+      FB_TRY(norm_residual(enc, T1, &Xin, ly.ln1_g, ly.ln1_b, T3, rows, Di, D, stream));
     } else {
       return arc;
     }
