@@ -111,6 +111,9 @@ int fb_matmul_heads_f32(const float* x_lw, const float* x_uw, const float* x_lb,
  * output of :397-413): y_l, y_u in the layout of y_lb, y_ub.  The dual norms over dim_in are taken by the
  * GEMM epilogue from the tile it is about to store, so the dot product that consumes y
  * (fb_dot_product_given_f32, fb_context_given_f32) needs no pass of its own over y_lw / y_uw.
+ * x_uw may be the same pointer as x_lw (a bound whose two lines coincide, as everywhere before the first
+ * relaxation): the kernel then skips the radius half of the work, and y_uw may be the same pointer as y_lw
+ * (both lines of the result are equal; the tile is stored through both).
  * norm_ws: 2 * rows * (words + 1) * Dy floats of scratch.  Tensor-core shapes with Di == 128 * words only,
  * otherwise FB_ERR_SHAPE and nothing is launched.  No counterpart in the reference's extension module. */
 int fb_matmul_heads_ranges_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
