@@ -41,35 +41,65 @@ static int split_sign_gemm(const float* a_lo, const float* a_up, const float* W,
 // and the mirror for u (Bounds.py:311-326).  With plain_lb / plain_ub != nullptr the bias terms come from
 // there in the unsplit layout [rows, heads * d] and are written to lb / ub in the head-split layout on the way
 // (the head split of the bias rows, VerifierForward.py:208-229, folded into this kernel).
+// VEC = 4: a thread handles four consecutive features (d % 4 == 0, 16-byte aligned pointers), 128-bit accesses.
+template <int VEC>
 __global__ void __launch_bounds__(256)
 ranges_from_norms_kernel(float* __restrict__ lb, float* __restrict__ ub, const float* __restrict__ plain_lb,
                          const float* __restrict__ plain_ub, const float* __restrict__ norm_lo,
                          const float* __restrict__ norm_up, float* __restrict__ out_l, float* __restrict__ out_u,
                          int64_t total, int L, int heads, int d, int words, float eps) {
   const int Dy = heads * d;
-  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
-    const int j = (int)(t % d);
-    const int l = (int)((t / d) % L);
-    const int64_t g = t / ((int64_t)d * L);
+  const int dv = d / VEC;
+  for (int64_t tv = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; tv < total / VEC; tv += (int64_t)gridDim.x * blockDim.x) {
+    const int j = (int)(tv % dv) * VEC;
+    const int l = (int)((tv / dv) % L);
+    const int64_t g = tv / ((int64_t)dv * L);
     const int h = (int)(g % heads);
     const int64_t row = (g / heads) * L + l;
-    float lo, up;
-    if (plain_lb != nullptr) {
-      lo = plain_lb[row * Dy + h * d + j];
-      up = plain_ub[row * Dy + h * d + j];
-      lb[t] = lo;
-      ub[t] = up;
+    const int64_t t = tv * VEC;
+    const int64_t src = row * Dy + h * d + j;
+    float lo[VEC], up[VEC];
+    if (VEC == 4) {
+      const float4 a = *reinterpret_cast<const float4*>((plain_lb != nullptr ? plain_lb + src : lb + t));
+      const float4 b = *reinterpret_cast<const float4*>((plain_ub != nullptr ? plain_ub + src : ub + t));
+      lo[0] = a.x; lo[VEC > 1 ? 1 : 0] = a.y; lo[VEC > 2 ? 2 : 0] = a.z; lo[VEC > 3 ? 3 : 0] = a.w;
+      up[0] = b.x; up[VEC > 1 ? 1 : 0] = b.y; up[VEC > 2 ? 2 : 0] = b.z; up[VEC > 3 ? 3 : 0] = b.w;
     } else {
-      lo = lb[t];
-      up = ub[t];
+      lo[0] = plain_lb != nullptr ? plain_lb[src] : lb[t];
+      up[0] = plain_ub != nullptr ? plain_ub[src] : ub[t];
+    }
+    if (plain_lb != nullptr) {
+      if (VEC == 4) {
+        *reinterpret_cast<float4*>(lb + t) = make_float4(lo[0], lo[VEC > 1 ? 1 : 0], lo[VEC > 2 ? 2 : 0], lo[VEC > 3 ? 3 : 0]);
+        *reinterpret_cast<float4*>(ub + t) = make_float4(up[0], up[VEC > 1 ? 1 : 0], up[VEC > 2 ? 2 : 0], up[VEC > 3 ? 3 : 0]);
+      } else {
+        lb[t] = lo[0];
+        ub[t] = up[0];
+      }
     }
     for (int w = 0; w < words; ++w) {
       const int64_t o = (row * words + w) * Dy + h * d + j;
-      lo = fadd(lo, fmul(-eps, norm_lo[o]));
-      up = fadd(up, fmul(eps, norm_up[o]));
+      if (VEC == 4) {
+        const float4 nl = *reinterpret_cast<const float4*>(norm_lo + o);
+        const float4 nu = *reinterpret_cast<const float4*>(norm_up + o);
+        const float n_l[4] = {nl.x, nl.y, nl.z, nl.w}, n_u[4] = {nu.x, nu.y, nu.z, nu.w};
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          lo[e] = fadd(lo[e], fmul(-eps, n_l[e]));
+          up[e] = fadd(up[e], fmul(eps, n_u[e]));
+        }
+      } else {
+        lo[0] = fadd(lo[0], fmul(-eps, norm_lo[o]));
+        up[0] = fadd(up[0], fmul(eps, norm_up[o]));
+      }
     }
-    out_l[t] = lo;
-    out_u[t] = up;
+    if (VEC == 4) {
+      *reinterpret_cast<float4*>(out_l + t) = make_float4(lo[0], lo[VEC > 1 ? 1 : 0], lo[VEC > 2 ? 2 : 0], lo[VEC > 3 ? 3 : 0]);
+      *reinterpret_cast<float4*>(out_u + t) = make_float4(up[0], up[VEC > 1 ? 1 : 0], up[VEC > 2 ? 2 : 0], up[VEC > 3 ? 3 : 0]);
+    } else {
+      out_l[t] = lo[0];
+      out_u[t] = up[0];
+    }
   }
 }
 }  // namespace fb
@@ -171,10 +201,16 @@ extern "C" int fb_matmul_heads_ranges_f32(const float* x_lw, const float* x_uw, 
   }
   if (rc != FB_OK) return rc;
   const int64_t total = rows * Dy;
-  const int64_t want = fb::ceil_div(total, 256), cap = (int64_t)fb::device_info().sms * 8;
-  fb::ranges_from_norms_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, st>>>(y_lb, y_ub, plain_lb, plain_ub, norm_lo,
-                                                                                   norm_up, y_l, y_u, total, L, heads, d,
-                                                                                   words, eps);
+  const bool vec = d % 4 == 0 && fb::aligned16(y_lb) && fb::aligned16(y_ub) && fb::aligned16(y_l) && fb::aligned16(y_u) &&
+                   fb::aligned16(norm_ws) && (rows * words * Dy) % 4 == 0;
+  const int64_t want = fb::ceil_div(vec ? total / 4 : total, 256), cap = (int64_t)fb::device_info().sms * 8;
+  const unsigned blocks = (unsigned)(want < cap ? want : cap);
+  if (vec)
+    fb::ranges_from_norms_kernel<4><<<blocks, 256, 0, st>>>(y_lb, y_ub, plain_lb, plain_ub, norm_lo, norm_up, y_l, y_u, total, L,
+                                                            heads, d, words, eps);
+  else
+    fb::ranges_from_norms_kernel<1><<<blocks, 256, 0, st>>>(y_lb, y_ub, plain_lb, plain_ub, norm_lo, norm_up, y_l, y_u, total, L,
+                                                            heads, d, words, eps);
   FB_LAUNCH_OK();
   return FB_OK;
 }
