@@ -5,8 +5,9 @@
 
 One process per GPU (torchrun for N > 1); the 256 sentences are split evenly over the ranks and no
 collective is on the data path (sentences are independent).  A step is one bound pass over all
-sentences.  Rank 0 prints one JSON line.  `--impl reference` times the CPU implementation of the
-same pass (the oracle port of the reference's PyTorch `Bounds`) on the host cores instead.
+sentences.  Rank 0 prints one JSON line.  `--impl reference` times the reference's own CPU implementation of
+the same pass on the host cores instead (its unchanged VerifierForward and Bounds when staged under oracle/_ref,
+else the oracle port).
 """
 import argparse
 import ctypes
@@ -86,14 +87,44 @@ class ClockSampler:
                 "samples": len(mhz)}
 
 
+_REF = {}
+
+
+def reference_kind():
+    """"reference" when the reference's own modules are staged under oracle/_ref (oracle/stage_reference.py),
+    else "port" (the restatement in oracle/bounds_oracle.py)."""
+    if "kind" not in _REF:
+        sys.path.insert(0, os.path.join(ROOT, "oracle"))
+        import stage_reference
+        _REF["kind"] = "reference" if stage_reference.staged_root() else "port"
+    return _REF["kind"]
+
+
 def cpu_reference_pass(model, emb, n_sentences, threads):
-    """The reference's CPU path: one sentence per call (VerifierForward.py:13), PyTorch fp32."""
-    from oracle import bounds_oracle as O
+    """The reference's CPU path, one sentence per call (VerifierForward.py:13), PyTorch fp32: the unchanged
+    VerifierForward._bound_input ... _bound_classifier (VerifierForward.py:93-125, 289-305) when its modules are
+    staged, else the oracle port."""
     torch.set_num_threads(threads)
+    if reference_kind() == "reference":
+        import reference_loader
+        if "ver" not in _REF:
+            _REF["ver"] = reference_loader.build_reference_verifier(model, float("inf"))
+        t0 = time.perf_counter()
+        for s in range(n_sentences):
+            reference_loader.reference_encoder_pass(_REF["ver"], emb[s:s + 1], CFG["index"], CFG["eps"])
+        return time.perf_counter() - t0
+    from oracle import bounds_oracle as O
     t0 = time.perf_counter()
     for s in range(n_sentences):
         O.encoder_forward(model, emb[s:s + 1], [CFG["index"]], float("inf"), CFG["eps"])
     return time.perf_counter() - t0
+
+
+def baseline_sample_text(n):
+    if reference_kind() == "reference":
+        return ("%d of the 256 sentences, one sentence per call through the reference's unchanged VerifierForward "
+                "and Bounds (fp32 PyTorch on CPU)" % n)
+    return "%d of the 256 sentences, one sentence per call, fp32 PyTorch on CPU (oracle port of the reference Bounds)" % n
 
 
 def run_reference(args):
@@ -111,13 +142,13 @@ def run_reference(args):
     times = [cpu_reference_pass(model, emb[i * sample:], sample, threads) for i in range(args.steps)]
     per_step = sum(times) / len(times)
     value = sample / per_step
-    sample_txt = "%d of the 256 sentences per step, one sentence per call, fp32 PyTorch on CPU" % sample
+    sample_txt = baseline_sample_text(sample) + ", per step"
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD, "sample": sample_txt},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample_txt},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": reference_kind(), "sample": sample_txt},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -362,9 +393,8 @@ def main():
         cpu_reference_pass(model, emb_host, 1, threads)
         n = 8
         secs = cpu_reference_pass(model, emb_host, n, threads)
-        line["cpu_baseline"] = {"value": n / secs, "unit": UNIT, "cores": threads, "kind": "port",
-                                "sample": "%d of the 256 sentences, one sentence per call, fp32 PyTorch on CPU "
-                                          "(oracle port of the reference Bounds)" % n}
+        line["cpu_baseline"] = {"value": n / secs, "unit": UNIT, "cores": threads, "kind": reference_kind(),
+                                "sample": baseline_sample_text(n)}
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
