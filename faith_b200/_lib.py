@@ -38,6 +38,8 @@ SIGNATURES = {
     "fb_relax_with_norms_f32": [_I] + [_P] * 10 + [_L, _I, _I, _I, _F, _P, _P],
     "fb_matmul_f32": [_P] * 10 + [_L, _I, _I, _I, _P],
     "fb_tc_error_flag": [ctypes.POINTER(_I)],
+    "fb_tc_check": [],
+    "fb_tc_selftest_timeout": [_P] * 5 + [_L, _I, _I, _I, _I, _P, _P],
     "fb_dot_product_f32": [_P] * 16 + [_I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P],
     "fb_matmul_heads_f32": [_P] * 10 + [_L, _I, _I, _I, _I, _I, _P],
     "fb_matmul_residual_f32": [_P] * 16 + [_L, _I, _I, _I, _P],

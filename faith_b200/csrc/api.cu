@@ -129,6 +129,8 @@ extern "C" const char* fb_status_string(int status) {
     case FB_ERR_ALIGN: return "pointer not 16-byte aligned";
     case FB_ERR_CUDA: return "CUDA runtime error (see fb_last_cuda_error)";
     case FB_ERR_WORKSPACE: return "workspace too small";
+    case FB_ERR_TIMEOUT: return "a bounded wait inside a kernel expired; results are not valid";
+    case FB_ERR_NCCL: return "collective communication failed";
     default: return "unknown status";
   }
 }

@@ -619,10 +619,18 @@ extern "C" int fb_dot_product_noalloc_f32(const float* x_lw, const float* x_uw, 
                                           float* z_lw, float* z_uw, float* z_lb, float* z_ub,
                                           int B, int Lx, int Ly, int Di, int K, int words, int p, float eps,
                                           float out_scale, int layout, void* stream) {
-  if (B < 0 || Lx <= 0 || Ly <= 0 || K <= 0) return FB_ERR_ARG;
+  if (B < 0 || Lx <= 0 || Ly <= 0 || K <= 0 || Di <= 0 || words <= 0 || Di % words != 0 || !fb::valid_norm(p) ||
+      (layout != FB_NATIVE && layout != FB_TRANSPOSED))
+    return FB_ERR_ARG;
+  // Each factor is bounded by the capacity before the products are formed, so that three large sizes cannot wrap
+  // around 64 bits and slip under the limit: this check is all that stands between a caller and a write past the array.
+  const int64_t cap = fb::kStaticScratchFloats;
+  if (B > cap || Lx > cap || Ly > cap || K > cap) return FB_ERR_WORKSPACE;
+  if ((int64_t)B * Lx > cap || (int64_t)B * Ly > cap) return FB_ERR_WORKSPACE;       // each product below 2^44
+  if ((int64_t)B * Lx * K > cap || (int64_t)B * Ly * K > cap) return FB_ERR_WORKSPACE;  // (B * L <= 2^22) * (K <= 2^22) < 2^63
   // ranges of x: 2 * B * Lx * K floats, ranges of y: 2 * B * Ly * K floats (each part padded to 64 floats)
   const int64_t nx = ((int64_t)B * Lx * K + 63) / 64 * 64, ny = ((int64_t)B * Ly * K + 63) / 64 * 64;
-  if (2 * nx + 2 * ny > fb::kStaticScratchFloats) return FB_ERR_WORKSPACE;
+  if (2 * nx + 2 * ny > cap) return FB_ERR_WORKSPACE;
   float* base = nullptr;
   const int rc = fb::static_scratch_address(&base);
   if (rc != FB_OK) return rc;

@@ -37,6 +37,7 @@
 #include <cuda.h>
 
 #include <mutex>
+#include <unordered_map>
 
 #include "common.cuh"
 
@@ -87,7 +88,7 @@ dot_weight_tc(const __grid_constant__ CUtensorMap tm_xl, const __grid_constant__
               const __grid_constant__ CUtensorMap tm_lx, const __grid_constant__ CUtensorMap tm_ly,
               const __grid_constant__ CUtensorMap tm_uy, const __grid_constant__ CUtensorMap tm_zl,
               const __grid_constant__ CUtensorMap tm_zu, int Lx, int Ly, int n_ib, int n_mb, int total_tiles,
-              float out_scale, int heads, int y_kmajor) {
+              float out_scale, int heads, int y_kmajor, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -417,6 +418,7 @@ dot_weight_tc(const __grid_constant__ CUtensorMap tm_xl, const __grid_constant__
   // memory is released (bounded), then free the tensor memory.
   if (*cta_abort) {
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    if (threadIdx.x == 0 && status != nullptr) atomicOr(status, 4);   // bit 2 of the caller's status word
   }
   tc_fence_before();
   __syncthreads();
@@ -430,27 +432,11 @@ dot_weight_tc(const __grid_constant__ CUtensorMap tm_xl, const __grid_constant__
 
 // 3-D fp32 tensor [d2][d1][d0] (d0 contiguous), box 32 x 4 x 32 (d0 x d1 x d2), 128-byte swizzle, zero fill.
 bool make_map3(CUtensorMap* map, const float* ptr, uint64_t d0, uint64_t d1, uint64_t d2) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return false;
-  const cuuint64_t dims[3] = {d0, d1, d2};
-  const cuuint64_t strides[2] = {d0 * sizeof(float), d0 * d1 * sizeof(float)};
-  const cuuint32_t box[3] = {32, 4, 32};
-  const cuuint32_t estr[3] = {1, 1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(ptr), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return get_map(map, ptr, 3, d0, d1, d2, d0 * sizeof(float), d0 * d1 * sizeof(float), 32, 4, 32);
 }
 // 2-D fp32 row-major [rows, 32], box 32 rows x 32 columns, 128-byte swizzle.
 bool make_map2(CUtensorMap* map, const float* ptr, uint64_t rows) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return false;
-  const cuuint64_t dims[2] = {32, rows};
-  const cuuint64_t strides[1] = {32 * sizeof(float)};
-  const cuuint32_t box[2] = {32, 32};
-  const cuuint32_t estr[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(ptr), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return get_map(map, ptr, 2, 32, rows, 1, 32 * sizeof(float), 0, 32, 32);
 }
 
 }  // namespace
@@ -466,6 +452,8 @@ bool dot_tc_supported(const float* x_lw, const float* x_uw, const float* y_lw, c
          aligned16(y_u) && aligned16(z_lw) && aligned16(z_uw) && encode_fn() != nullptr;
 }
 
+int* tc_status_sink();
+
 int launch_dot_weight_tc(const float* x_lw, const float* x_uw, const float* y_lw, const float* y_uw, const float* x_l,
                          const float* y_l, const float* y_u, float* z_lw, float* z_uw, int B, int Lx, int Ly, int Di,
                          float out_scale, int heads, int y_kmajor, cudaStream_t st) {
@@ -480,10 +468,17 @@ int launch_dot_weight_tc(const float* x_lw, const float* x_uw, const float* y_lw
     return FB_ERR_CUDA;
   const int n_ib = Lx / 32, n_mb = Di / 4;
   const int total = B * n_ib * n_mb;
-  FB_CUDA_OK(cudaFuncSetAttribute(dot_weight_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDtSmemBytes));
+  static std::once_flag attr_once[64];
+  int dev = 0;
+  FB_CUDA_OK(cudaGetDevice(&dev));
+  cudaError_t attr_err = cudaSuccess;
+  std::call_once(attr_once[dev & 63], [&]() {
+    attr_err = cudaFuncSetAttribute(dot_weight_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDtSmemBytes);
+  });
+  FB_CUDA_OK(attr_err);
   const int sms = device_info().sms;
   dot_weight_tc<<<(unsigned)(total < sms ? total : sms), kDtThreads, kDtSmemBytes, st>>>(
-      tm_xl, tm_xu, tm_yl, tm_yu, tm_lx, tm_ly, tm_uy, tm_zl, tm_zu, Lx, Ly, n_ib, n_mb, total, out_scale, heads, y_kmajor);
+      tm_xl, tm_xu, tm_yl, tm_yu, tm_lx, tm_ly, tm_uy, tm_zl, tm_zu, Lx, Ly, n_ib, n_mb, total, out_scale, heads, y_kmajor, tc_status_sink());
   FB_LAUNCH_OK();
   return FB_OK;
 }

@@ -14,7 +14,16 @@
 #include "common.cuh"
 
 namespace fb {
+void tc_set_status_sink(int* status);
+
 namespace {
+
+// While a pass is being enqueued, the tensor-core kernels of this thread report an expired wait into the pass's
+// status word (bit 2 of `violation`).
+struct StatusSinkScope {
+  explicit StatusSinkScope(int* status) { tc_set_status_sink(status); }
+  ~StatusSinkScope() { tc_set_status_sink(nullptr); }
+};
 
 struct BoundSet {
   float *lw, *uw, *lb, *ub;
@@ -213,6 +222,7 @@ extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, i
                                             plan.small_bytes);
 
   FB_CUDA_OK(cudaMemsetAsync(violation, 0, sizeof(int), st));
+  const StatusSinkScope sink(violation);
 
   // slot roles rotate; names follow the walk-through in the file header
   int A = 0, B = 1, C = 2, Dd = 3;
@@ -224,8 +234,10 @@ extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, i
     if (enc->layer_norm == 1 && D == 128 && aligned16(emb) && aligned16(enc->emb_ln_g) && aligned16(enc->emb_ln_b)) {
       const int64_t n_w_rows = rows * Di, n_b_rows = rows;
       const int64_t want = ceil_div(n_w_rows + n_b_rows, 8), cap = (int64_t)device_info().sms * 16;
+      // (without encoder layers the pooler reads both buffers, so both are written)
       input_bounds_norm128_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, st>>>(
-          emb, enc->emb_ln_g, enc->emb_ln_b, slot[A].lw, slot[A].lw, slot[A].lb, slot[A].ub, n_w_rows, n_b_rows, L, words, pos);
+          emb, enc->emb_ln_g, enc->emb_ln_b, slot[A].lw, enc->layers == 0 ? slot[A].uw : slot[A].lw, slot[A].lb, slot[A].ub,
+          n_w_rows, n_b_rows, L, words, pos);
       FB_LAUNCH_OK();
     } else {
       const int64_t n_w = rows * Di * D, n_b = rows * D;
@@ -362,11 +374,11 @@ extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, i
     int frc = fb_matmul_heads_ranges_f32(T3.lw, T3.uw, T3.lb, T3.ub, ly.f1_w, ly.f1_b, T1.lw, T1.uw, T1.lb, T1.ub, X.lb, X.ub,
                                          norm_ws, rows, Di, D, F, L, 1, words, p, eps, stream);
     if (frc == FB_OK) {
-      frc = fb_relax_coef_given_f32(FB_RELU, T1.lb, T1.ub, X.lb, X.ub, X.lw, X.uw, T2.lb, T2.ub, rows, F, nullptr, stream);
+      frc = fb_relax_coef_given_f32(FB_RELU, T1.lb, T1.ub, X.lb, X.ub, X.lw, X.uw, T2.lb, T2.ub, rows, F, violation, stream);
     } else if (frc == FB_ERR_SHAPE) {
       FB_TRY(dense(T3, ly.f1_w, ly.f1_b, T1, rows, Di, D, F, stream));
       frc = fb_relax_coef_f32(FB_RELU, T1.lw, T1.uw, T1.lb, T1.ub, X.lw, X.uw, T2.lb, T2.ub, rows, Di, F, words, p, eps,
-                              nullptr, stream);
+                              violation, stream);
     }
     bool residual_added = false;
     if (frc == FB_OK) {

@@ -44,10 +44,12 @@
 // only while the accumulators are read out of tensor memory.
 //
 // Every wait on an mbarrier is bounded; on expiry the kernel raises a device-side flag
-// (fb_tc_error_flag), drains, frees its tensor memory and returns.
+// (fb_tc_error_flag, and bit 2 of the caller's status word where one is registered), drains, frees its
+// tensor memory and returns.
 #include <cuda.h>
 
 #include <mutex>
+#include <unordered_map>
 
 #include "common.cuh"
 
@@ -117,7 +119,7 @@ __device__ __forceinline__ void issue_kblock_role(bool first, const uint32_t (&b
   else issue_kblock<kRole, false, kPoint>(blo, acol, b_hi, d0, d1, idesc);
 }
 
-// Instruction descriptor: D fp32, A and B tf32, both K-major, M = 128, N = 128.
+// Instruction descriptor: D fp32, A and B tf32, both K-major, M = 128, N = 64.
 constexpr uint32_t kInstrDesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 
 struct SharedLayout {
@@ -140,6 +142,10 @@ struct SharedLayout {
 // kPoint: x_lw and x_uw are the same tensor (every stage before the first relaxation): the radius is zero, so
 // x_uw is not loaded, no radius planes are written, the radius products are not issued and the epilogue reads
 // two accumulators; the results equal those of the general kernel bit for bit.
+//
+// status: device word of the caller (may be null); bit 2 is set when a bounded wait of this launch expired.
+// wait_tries: bound of every mbarrier wait in tries of ~20 us.  skip_it >= 0 makes the producer of CTA 0 leave
+// out the loads of that k-block: the self-test of the give-up path (fb_tc_selftest_timeout), never set otherwise.
 template <bool kCoef, bool kNorm, bool kResid, bool kPoint>
 __global__ void __launch_bounds__(kThreads, 1)
 split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_constant__ CUtensorMap tm_up,
@@ -148,7 +154,8 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
                    const __grid_constant__ CUtensorMap tm_res_up, const float* __restrict__ bias, int64_t M, int N, int K,
                    int n_tiles_n, int64_t total_tiles, int split_rows, int split_d,
                    const float* __restrict__ coef_l, const float* __restrict__ coef_u, int coef_di,
-                   float* __restrict__ norm_lo, float* __restrict__ norm_up, int norm_p) {
+                   float* __restrict__ norm_lo, float* __restrict__ norm_up, int norm_p,
+                   int* __restrict__ status, uint32_t wait_tries, int skip_it) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -197,6 +204,7 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const WaitCtx wc = {cta_abort, wait_tries};
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -211,8 +219,8 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
         const int rs = (int)(it % kRawStages);
         const uint32_t full = bar_full + 8 * rs;
         if (it >= kRawStages &&
-            !mbar_wait_warp(bar_raw_empty + 8 * rs, (uint32_t)((it / kRawStages - 1) & 1), cta_abort)) { ok = false; break; }
-        if (lane == 0) {
+            !mbar_wait_warp(bar_raw_empty + 8 * rs, (uint32_t)((it / kRawStages - 1) & 1), wc)) { ok = false; break; }
+        if (lane == 0 && !(blockIdx.x == 0 && it == skip_it)) {
           mbar_arrive_expect_tx(full, kPoint ? kRawStageBytes - kTileBytes : kRawStageBytes);
           const uint32_t dst = base + SharedLayout::raw(rs);
           tma_load_2d(dst, &tm_lo, kb * BK, m0, full);
@@ -247,9 +255,9 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
     for (int ti = 0; ti < my_tiles && ok; ++ti) {
       for (int kb = 0; kb < nkb; ++kb, ++it) {
         const int s = (int)(it & 1);
-        ok = mbar_wait_warp(bar_ops_ready + 8 * s, (uint32_t)((it >> 1) & 1), cta_abort);
+        ok = mbar_wait_warp(bar_ops_ready + 8 * s, (uint32_t)((it >> 1) & 1), wc);
         // the first MMA of a tile overwrites the accumulators: the previous tile must have been read out
-        if (ok && kb == 0 && ti > 0) ok = mbar_wait_warp(bar_acc_free, (uint32_t)((ti - 1) & 1), cta_abort);
+        if (ok && kb == 0 && ti > 0) ok = mbar_wait_warp(bar_acc_free, (uint32_t)((ti - 1) & 1), wc);
         if (!ok) break;
         tc_fence_after();
         if (lane == 0) {
@@ -286,7 +294,7 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
     auto epi_sync = [&]() -> bool {
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_conv);
-      const bool r = mbar_wait_warp(bar_conv, epi_phase & 1u, cta_abort);
+      const bool r = mbar_wait_warp(bar_conv, epi_phase & 1u, wc);
       ++epi_phase;
       return r;
     };
@@ -309,11 +317,11 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
           tma_load_3d(so + (2 + q) * kOutBoxBytes, &tm_res_up, nx + 32 * q, my, 0, bar_res);
         }
       }
-      ok = mbar_wait_warp(bar_acc_ready, (uint32_t)(e & 1), cta_abort);
+      ok = mbar_wait_warp(bar_acc_ready, (uint32_t)(e & 1), wc);
       if (!ok) break;
       tc_fence_after();
       if (kResid) {
-        ok = mbar_wait_warp(bar_res, (uint32_t)(e & 1), cta_abort);
+        ok = mbar_wait_warp(bar_res, (uint32_t)(e & 1), wc);
         if (!ok) break;
       }
 #pragma unroll
@@ -446,7 +454,7 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
           ku[q] = __ldg(reinterpret_cast<const float4*>(pu) + q);
         }
       }
-      ok = mbar_wait_warp(bar_full + 8 * g, (uint32_t)((it >> 1) & 1), cta_abort);
+      ok = mbar_wait_warp(bar_full + 8 * g, (uint32_t)((it >> 1) & 1), wc);
       if (!ok) break;
       const uint8_t* raw = base_ptr + SharedLayout::raw(g);
       // W tile: 64 rows x 8 chunks; this thread converts two adjacent chunks of one row
@@ -501,7 +509,7 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_raw_empty + 8 * g);
       if (it >= 2) {
-        ok = mbar_wait_warp(bar_mma_done + 8 * g, (uint32_t)(((it >> 1) - 1) & 1), cta_abort);
+        ok = mbar_wait_warp(bar_mma_done + 8 * g, (uint32_t)(((it >> 1) - 1) & 1), wc);
         if (!ok) break;
         tc_fence_after();
       }
@@ -544,6 +552,7 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
   // memory is released (bounded), then free the tensor memory.
   if (*cta_abort) {
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    if (threadIdx.x == 0 && status != nullptr) atomicOr(status, 4);
   }
   tc_fence_before();
   __syncthreads();
@@ -554,40 +563,29 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
 }
 
 // ------------------------------------------------------------------------ host side
-// 2-D fp32 row-major [rows, cols] tensor, box `box_rows` rows x 32 columns, 128-byte swizzle, zero fill.
+// 2-D fp32 row-major [rows, cols] tensor, box `box_rows` rows x 32 columns.
 bool make_map(CUtensorMap* map, const float* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return false;
-  const cuuint64_t dims[2] = {cols, rows};
-  const cuuint64_t strides[1] = {cols * sizeof(float)};
-  const cuuint32_t box[2] = {BK, box_rows};
-  const cuuint32_t estr[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(ptr), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return get_map(map, ptr, 2, cols, rows, 1, cols * sizeof(float), 0, BK, box_rows);
 }
 
 // Output map, always 3-D: plain [1][rows][cols], or head-split [groups * heads][split_rows][split_d].
 bool make_out_map(CUtensorMap* map, const float* ptr, uint64_t M, uint64_t N, int split_rows, int split_d) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return false;
-  cuuint64_t dims[3] = {N, M, 1};
-  cuuint64_t strides[2] = {N * sizeof(float), M * N * sizeof(float)};
-  if (split_rows > 0) {
-    dims[0] = (cuuint64_t)split_d;
-    dims[1] = (cuuint64_t)split_rows;
-    dims[2] = (M / split_rows) * (N / split_d);
-    strides[0] = (cuuint64_t)split_d * sizeof(float);
-    strides[1] = (cuuint64_t)split_rows * split_d * sizeof(float);
-  }
-  const cuuint32_t box[3] = {32, BM, 1};
-  const cuuint32_t estr[3] = {1, 1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(ptr), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  if (split_rows > 0)
+    return get_map(map, ptr, 3, (uint64_t)split_d, (uint64_t)split_rows, (M / split_rows) * (N / split_d),
+                   (uint64_t)split_d * sizeof(float), (uint64_t)split_rows * split_d * sizeof(float), 32, BM);
+  return get_map(map, ptr, 3, N, M, 1, N * sizeof(float), M * N * sizeof(float), 32, BM);
 }
 
+thread_local int* t_status_sink = nullptr;
+uint32_t g_wait_tries = kMaxTries;
+int g_skip_it = -1;
+
 }  // namespace
+
+// The encoder driver registers its status word here around a pass: a tensor-core kernel whose bounded wait
+// expires sets bit 2 of it (besides the flag behind fb_tc_error_flag).
+void tc_set_status_sink(int* status) { t_status_sink = status; }
+int* tc_status_sink() { return t_status_sink; }
 
 // Head-split store is possible when a 128-row tile stays inside one group and a 32-column box inside one head.
 bool tc_split_supported(int64_t M, int N, int split_rows, int split_d) {
@@ -647,19 +645,22 @@ int launch_split_sign_tc(const float* a_lo, const float* a_up, const float* W, c
   // persistent: one CTA per SM (tensor memory and shared memory allow exactly one)
   const int64_t sms = device_info().sms;
   const unsigned grid = (unsigned)(total_tiles < sms ? total_tiles : sms);
+  int* status = t_status_sink;
+  const uint32_t tries = g_wait_tries;
+  const int skip = g_skip_it;
 #define FB_TC_ARGS tm_lo, tm_up, tm_w, tm_out_lo, tm_out_up, tm_res_lo, tm_res_up, bias, M, N, K, gn, total_tiles, split_rows, split_d
   if (coef_l != nullptr && res_lo != nullptr)
-    split_sign_gemm_tc<true, false, true, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, coef_l, coef_u, coef_di, nullptr, nullptr, 0);
+    split_sign_gemm_tc<true, false, true, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, coef_l, coef_u, coef_di, nullptr, nullptr, 0, status, tries, skip);
   else if (coef_l != nullptr)
-    split_sign_gemm_tc<true, false, false, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, coef_l, coef_u, coef_di, nullptr, nullptr, 0);
+    split_sign_gemm_tc<true, false, false, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, coef_l, coef_u, coef_di, nullptr, nullptr, 0, status, tries, skip);
   else if (norm_lo != nullptr && a_lo == a_up)   // one tensor as both lines: zero radius
-    split_sign_gemm_tc<false, true, false, true><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, norm_lo, norm_up, norm_p);
+    split_sign_gemm_tc<false, true, false, true><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, norm_lo, norm_up, norm_p, status, tries, skip);
   else if (norm_lo != nullptr)
-    split_sign_gemm_tc<false, true, false, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, norm_lo, norm_up, norm_p);
+    split_sign_gemm_tc<false, true, false, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, norm_lo, norm_up, norm_p, status, tries, skip);
   else if (res_lo != nullptr)
-    split_sign_gemm_tc<false, false, true, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, nullptr, nullptr, 0);
+    split_sign_gemm_tc<false, false, true, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, nullptr, nullptr, 0, status, tries, skip);
   else
-    split_sign_gemm_tc<false, false, false, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, nullptr, nullptr, 0);
+    split_sign_gemm_tc<false, false, false, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, nullptr, nullptr, 0, status, tries, skip);
 #undef FB_TC_ARGS
   FB_LAUNCH_OK();
   return FB_OK;
@@ -668,7 +669,7 @@ int launch_split_sign_tc(const float* a_lo, const float* a_up, const float* W, c
 }  // namespace fb
 
 
-// Reads (and clears) the device-side flag that the tensor-core GEMM raises when one of its bounded
+// Reads (and clears) the device-side flag that the tensor-core kernels raise when one of their bounded
 // waits expires.  Synchronises the device.
 namespace fb { int dot_tc_error_flag(int* flag); }
 
@@ -686,4 +687,35 @@ extern "C" int fb_tc_error_flag(int* flag) {
   if (rc != FB_OK) return rc;
   *flag = (v != 0 || v2 != 0) ? 1 : 0;
   return FB_OK;
+}
+
+extern "C" int fb_tc_check(void) {
+  int flag = 0;
+  const int rc = fb_tc_error_flag(&flag);
+  if (rc != FB_OK) return rc;
+  return flag ? FB_ERR_TIMEOUT : FB_OK;
+}
+
+// Self-test of the give-up path: runs the product once with the loads of one k-block of CTA 0 left out and every
+// wait limited to `tries` tries of ~20 us.  The CTA's converters run out of patience, the CTA drains, frees its tensor
+// memory and returns; the call then reports FB_ERR_TIMEOUT (anything else means the path is broken).  Results of this
+// call are garbage by construction.  Not thread-safe against concurrent products (process-wide switches).
+extern "C" int fb_tc_selftest_timeout(const float* x_lw, const float* x_uw, const float* W, float* y_lw, float* y_uw,
+                                      int64_t M, int N, int K, int skip_kblock, int tries, int* status, void* stream) {
+  if (!x_lw || !x_uw || !W || !y_lw || !y_uw || skip_kblock < 0 || tries <= 0) return FB_ERR_ARG;
+  if (!fb::tc_gemm_supported(x_lw, x_uw, W, y_lw, y_uw, M, N, K)) return FB_ERR_SHAPE;
+  int flag = 0;
+  int rc = fb_tc_error_flag(&flag);   // start from a clean flag
+  if (rc != FB_OK) return rc;
+  fb::g_wait_tries = (uint32_t)tries;
+  fb::g_skip_it = skip_kblock;
+  int* const saved_sink = fb::t_status_sink;
+  fb::t_status_sink = status;
+  rc = fb::launch_split_sign_tc(x_lw, x_uw, W, nullptr, y_lw, y_uw, M, N, K, (cudaStream_t)stream, 0, 0, nullptr, nullptr, 1,
+                                nullptr, nullptr, 0, nullptr, nullptr);
+  fb::t_status_sink = saved_sink;
+  fb::g_wait_tries = fb::kMaxTries;
+  fb::g_skip_it = -1;
+  if (rc != FB_OK) return rc;
+  return fb_tc_check();
 }

@@ -1,6 +1,7 @@
 // Inline-PTX wrappers shared by the tcgen05 kernels (mbarrier, TMA, tensor memory, tcgen05.mma) and the
 // host helper that resolves cuTensorMapEncodeTiled.  Included inside namespace fb, anonymous namespace,
-// after <cuda.h>, <mutex> and common.cuh; every including file gets its own copy of the error flag.
+// after <cuda.h>, <mutex>, <unordered_map> and common.cuh; every including file gets its own copy of the error
+// flag and of the tensor-map cache.
 
 constexpr uint32_t kTryNs = 20000;       // suspend-time hint of one mbarrier try (ns)
 constexpr uint32_t kMaxTries = 100000;  // x 20 us = 2 s upper bound for any single wait
@@ -44,27 +45,55 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: at most kMaxTries suspended tries of ~kTryNs each (a couple of seconds in total).
+// Bounded wait: at most `tries` suspended tries of ~kTryNs each (kMaxTries: a couple of seconds in total).
 // Returns false (and raises the error flags) when the limit is hit or another role of this CTA has
 // already given up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* cta_abort) {
+struct WaitCtx {
+  volatile int* cta_abort;
+  uint32_t tries;
+};
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& wc) {
   // fast path: in a well-fed pipeline the phase is usually complete already, and the non-blocking
   // test answers much sooner than a suspending try
   for (int i = 0; i < 4; ++i)
     if (mbar_test_wait(bar, parity)) return true;
-  for (uint32_t i = 0; i < kMaxTries; ++i) {
+  for (uint32_t i = 0; i < wc.tries; ++i) {
     if (mbar_try_wait(bar, parity, kTryNs)) return true;
-    if (*cta_abort) return false;
+    if (*wc.cta_abort) return false;
   }
-  *cta_abort = 1;
+  *wc.cta_abort = 1;
   atomicExch(&g_tc_error, 1);
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* cta_abort) {
+  const WaitCtx wc = {cta_abort, kMaxTries};
+  return mbar_wait(bar, parity, wc);
 }
 
 // Same, for a whole warp: every lane waits, and the outcome is made uniform so that the
 // .sync.aligned tensor-memory instructions that follow are executed convergently.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, const WaitCtx& wc) {
+  const bool ok = mbar_wait(bar, parity, wc);
+  return __all_sync(0xffffffffu, ok);
+}
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* cta_abort) {
   const bool ok = mbar_wait(bar, parity, cta_abort);
+  return __all_sync(0xffffffffu, ok);
+}
+
+// Bounded wait by polling (no suspension): for the few warps whose wake-up latency is on the critical path.
+// About 40 cycles per round; 512 rounds per try of the suspending wait keep the two bounds comparable.
+__device__ __forceinline__ bool mbar_poll_warp(uint32_t bar, uint32_t parity, const WaitCtx& wc) {
+  bool ok = false;
+  const uint32_t rounds = wc.tries > (0xffffffffu >> 9) ? 0xffffffffu : wc.tries << 9;
+  for (uint32_t i = 0; i < rounds; ++i) {
+    if (mbar_test_wait(bar, parity)) { ok = true; break; }
+    if ((i & 255u) == 255u && *wc.cta_abort) break;
+  }
+  if (!ok && !*wc.cta_abort) {
+    *wc.cta_abort = 1;
+    atomicExch(&g_tc_error, 1);
+  }
   return __all_sync(0xffffffffu, ok);
 }
 
@@ -139,6 +168,11 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* v) {
         "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
       : "memory");
 }
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+               : "memory");
+}
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
@@ -202,5 +236,52 @@ EncodeTiledFn encode_fn() {
       fn = reinterpret_cast<EncodeTiledFn>(p);
   });
   return fn;
+}
+
+// Encoded tensor maps are kept per (pointer, shape, box): a bound pass calls the same products on the same
+// arena addresses over and over, and an encode costs a driver call each.
+struct MapKey {
+  const void* ptr;
+  uint64_t d0, d1, d2, s0, s1;
+  uint32_t b0, b1, b2, rank;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && d2 == o.d2 && s0 == o.s0 && s1 == o.s1 && b0 == o.b0 && b1 == o.b1 &&
+           b2 == o.b2 && rank == o.rank;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    uint64_t h = reinterpret_cast<uintptr_t>(k.ptr) * 0x9E3779B97F4A7C15ull;
+    h ^= (k.d0 + 0x632BE59BD9B4E019ull) * 0xFF51AFD7ED558CCDull + (k.d1 << 17) + (k.d2 << 40) + k.s0 * 31 + k.s1 * 131 + k.b1 * 7 + k.b2 * 3 + k.rank;
+    return (size_t)(h ^ (h >> 29));
+  }
+};
+std::mutex g_map_mu;
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+
+// fp32 tensor of up to three dimensions (innermost first; s0, s1: byte strides of dimensions 1 and 2), box
+// {b0, b1, b2}, 128-byte swizzle, zero fill.
+bool get_map(CUtensorMap* out, const float* ptr, uint32_t rank, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s0, uint64_t s1,
+             uint32_t b0, uint32_t b1, uint32_t b2 = 1) {
+  const MapKey key = {ptr, d0, d1, d2, s0, s1, b0, b1, b2, rank};
+  {
+    std::lock_guard<std::mutex> lk(g_map_mu);
+    auto it = g_maps.find(key);
+    if (it != g_maps.end()) { *out = it->second; return true; }
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[3] = {d0, d1, d2};
+  const cuuint64_t strides[2] = {s0, s1};
+  const cuuint32_t box[3] = {b0, b1, b2};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  if (fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, rank, const_cast<float*>(ptr), dims, strides, box, estr,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  std::lock_guard<std::mutex> lk(g_map_mu);
+  if (g_maps.size() > 4096) g_maps.clear();   // callers with ever-changing addresses: start over
+  g_maps.emplace(key, *out);
+  return true;
 }
 

@@ -48,9 +48,22 @@ class EncoderVerifier:
             raise _lib.FaithError("invalid encoder configuration")
         return n
 
+    @staticmethod
+    def check_status(violation):
+        """Reads the status word of a pass (synchronises) and raises if the bounds must not be used: bit 2 = a
+        bounded wait inside a tensor-core kernel expired, so l / u are partly written.  Returns the word;
+        bits 0 and 1 (softmax denominator not provably positive, inverted hidden range) are left to the caller
+        as in the reference, which asserts on the first (Bounds.py:1147)."""
+        v = int(violation.item())
+        if v & 4:
+            raise _lib.FaithError("a bounded wait inside a tensor-core kernel expired during the bound pass; "
+                                  "the returned bounds are not valid (status word %d)" % v)
+        return v
+
     def forward(self, emb, positions, p, eps, out=None):
         """emb [S, L, D] on the device; positions: perturbed token indices.  Returns (l, u, violation):
-        concretised bounds of logit0 - logit1 per sentence and the device flag of the positivity check."""
+        concretised bounds of logit0 - logit1 per sentence and the device status word of the pass (see
+        check_status; any non-zero value means the bounds are no proof)."""
         ops._chk(emb)
         S, L, D = emb.shape
         words = len(positions)

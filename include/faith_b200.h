@@ -36,7 +36,9 @@ enum fb_status {
   FB_ERR_SHAPE = 2,   /* sizes the kernels do not support (documented per function) */
   FB_ERR_ALIGN = 3,   /* pointer not aligned to 16 bytes where the vector path needs it */
   FB_ERR_CUDA = 4,    /* a CUDA runtime call or launch failed; see fb_last_cuda_error() */
-  FB_ERR_WORKSPACE = 5 /* caller-provided scratch too small */
+  FB_ERR_WORKSPACE = 5, /* caller-provided scratch too small */
+  FB_ERR_TIMEOUT = 6,   /* a bounded wait inside a kernel (or on a peer) expired; results are not valid */
+  FB_ERR_NCCL = 7       /* a collective failed; see fb_comm_last_error() */
 };
 
 enum fb_norm { FB_P1 = 1, FB_P2 = 2, FB_PINF = 3 };
@@ -158,10 +160,23 @@ int fb_matmul_residual_f32(const float* x_lw, const float* x_uw, const float* x_
                            float* y_lw, float* y_uw, float* y_lb, float* y_ub,
                            int64_t rows, int Di, int Do, int Dy, void* stream);
 
-/* The tensor-core GEMM behind fb_matmul_f32 bounds every wait inside the kernel; if a wait ever
- * expires, the kernel raises a device-side flag, frees its tensor memory and returns.  This call
- * synchronises the device, returns the flag in *flag (0 = never raised) and clears it. */
+/* The tensor-core kernels behind fb_matmul_f32 and fb_dot_product_f32 bound every wait inside the kernel; if a
+ * wait ever expires, the kernel raises a device-side flag, frees its tensor memory and returns, leaving its
+ * outputs partly written.  fb_tc_error_flag synchronises the device, returns the flag in *flag (0 = never
+ * raised) and clears it; fb_tc_check does the same and returns FB_ERR_TIMEOUT when the flag was raised.
+ * fb_encoder_forward_f32 reports the same condition without a synchronisation of its own: bit 2 of its
+ * `violation` word.  No counterpart in the reference (its kernels have no waits). */
 int fb_tc_error_flag(int* flag);
+int fb_tc_check(void);
+
+/* Self-test of that give-up path (the reference has nothing comparable): the product of x [M, K] with W [N, K]
+ * is launched once with the operand loads of k-block `skip_kblock` of the first thread block left out and every
+ * wait limited to `tries` tries of about 20 microseconds.  The block runs out of patience, drains, frees its
+ * tensor memory and returns; the expected return value is FB_ERR_TIMEOUT, and the device stays usable.  y is
+ * scratch (garbage afterwards).  `status` (device int, may be NULL) receives bit 2 the way the `violation` word of
+ * fb_encoder_forward_f32 does.  Not to be run concurrently with other products of the same process. */
+int fb_tc_selftest_timeout(const float* x_lw, const float* x_uw, const float* W, float* y_lw, float* y_uw,
+                           int64_t M, int N, int K, int skip_kblock, int tries, int* status, void* stream);
 
 /* Bound x bound dot product  z[b,i,j] = sum_k x[b,i,k] * y[b,j,k]  (attention scores and,
  * with y = transposed values, the attention context).  Replaces Bounds.ori_dot_product
@@ -349,8 +364,12 @@ int64_t fb_encoder_workspace_bytes(const fb_encoder* enc, int S, int L, int word
 
 /* emb [S, L, d_model] (device); positions[words] (host) = perturbed token indices;
  * out_l, out_u [S] (device) = concretised bounds of logit0 - logit1;
- * violation [1] (device int, zeroed by the call): set when a softmax denominator was not
- * provably positive (the reference's assertion, Bounds.py:1147). */
+ * violation [1] (device int, zeroed by the call), a bit set the caller must read together with out_l / out_u:
+ *   bit 0  a softmax denominator was not provably positive (the reference's assertion, Bounds.py:1147);
+ *   bit 1  a hidden unit had an inverted range (l > u) where the feed-forward relu is applied through its slopes:
+ *          the result then differs from the reference's add_linear (Bounds.py:362-381) for that unit;
+ *   bit 2  a bounded wait inside a tensor-core kernel of this pass expired: out_l / out_u are NOT valid.
+ * Any non-zero value means the bounds must not be used as a proof. */
 int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, int S, int L,
                            const int* positions, int words, int p, float eps,
                            float* out_l, float* out_u, int* violation,

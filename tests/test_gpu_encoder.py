@@ -127,6 +127,7 @@ def test_encoder_full_size_config_properties():
     emb = torch.randn(8, 32, 128, generator=torch.Generator().manual_seed(4))
     ver = faith_b200.EncoderVerifier(model, DEV)
     l, u, viol = ver.forward(emb.to(DEV), [1], float("inf"), 1e-3)
+    assert ver.check_status(viol) == 0
     l, u = l.cpu(), u.cpu()
     assert bool(torch.isfinite(l).all()) and bool(torch.isfinite(u).all())
     y = O.concrete_forward(model, emb)
@@ -153,3 +154,18 @@ def test_encoder_full_width_two_perturbed_words():
     helpers.assert_within_noise(u, u32, u64, "u")
     y = O.concrete_forward(model, emb)
     assert bool((l.cpu() <= y + 1e-5).all()) and bool((y <= u.cpu() + 1e-5).all())
+
+
+def test_encoder_without_layers():
+    """An encoder with no layers (embedding layer norm, pooler, classifier): the driver's input stage must leave both
+    lines of the bound written for the pooler (d_model 128 takes the fused input kernel)."""
+    import faith_b200
+    model = O.make_encoder(7, layers=0)
+    emb = torch.randn(3, 8, 128, generator=torch.Generator().manual_seed(7))
+    ver = faith_b200.EncoderVerifier(model, DEV)
+    l, u, viol = ver.forward(emb.to(DEV), [2], float("inf"), 0.01)
+    assert ver.check_status(viol) == 0
+    l32, u32 = O.encoder_forward(model, emb, [2], float("inf"), 0.01)
+    l64, u64 = O.encoder_forward(O.model_to(model, torch.float64), emb.double(), [2], float("inf"), 0.01)
+    helpers.assert_within_noise(l, l32, l64, "l")
+    helpers.assert_within_noise(u, u32, u64, "u")

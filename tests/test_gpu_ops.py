@@ -732,3 +732,31 @@ def test_projection_of_a_point_bound_takes_the_zero_radius_kernel(p, words):
         again = ops.matmul_heads_ranges(lw, lw, lb, lb, W, bias, H, p, eps, words)
         for a, b in zip(again, point):
             assert torch.equal(a, b)
+
+
+def test_tensor_core_give_up_path_reports_a_timeout_and_leaves_the_gpu_usable():
+    """A wait that runs out must surface, not vanish: the product is launched with the operand loads of one k-block
+    of the first thread block left out and every wait limited to about half a millisecond.  The block has to drain,
+    free its tensor memory and return; the call reports FB_ERR_TIMEOUT, bit 2 of the status word is set, the flag is
+    clear afterwards, and the next product on the same device is correct."""
+    import ctypes
+    from faith_b200 import ops, _lib
+    lib = _lib.load()
+    g = torch.Generator().manual_seed(77)
+    rows, Di, Do, Dy = 4, 128, 128, 128
+    lw = torch.randn(rows, Di, Do, generator=g).to(DEV)
+    uw = (lw.cpu() + torch.rand(rows, Di, Do, generator=g)).to(DEV)
+    W = (torch.randn(Dy, Do, generator=g) / 8).to(DEV)
+    y = [torch.empty(rows, Di, Dy, device=DEV) for _ in range(2)]
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    st = torch.cuda.current_stream().cuda_stream
+    rc = lib.fb_tc_selftest_timeout(lw.data_ptr(), uw.data_ptr(), W.data_ptr(), y[0].data_ptr(), y[1].data_ptr(),
+                                    rows * Di, Dy, Do, 1, 25, status.data_ptr(), st)
+    assert rc == 6, lib.fb_status_string(rc)          # FB_ERR_TIMEOUT
+    assert int(status.item()) & 4
+    assert lib.fb_tc_check() == 0                     # the flag was cleared by the read
+    lb = torch.zeros(rows, Do, device=DEV)
+    got = ops.matmul(lw, uw, lb, lb, W, None)
+    assert lib.fb_tc_check() == 0
+    ref_l = lw.double() @ W.double().clamp(min=0).t() + uw.double() @ W.double().clamp(max=0).t()
+    assert float((got[0].double() - ref_l).abs().max()) < 1e-4

@@ -69,3 +69,8 @@ def test_noalloc_rejects_sizes_beyond_the_fixed_array():
     rc = lib.fb_dot_product_noalloc_f32(*ptrs, B, L, L, 128, K, 1, _lib.FB_P2, 0.5, 1.0, _lib.FB_NATIVE, None)
     assert rc == 5  # FB_ERR_WORKSPACE, nothing launched
     torch.cuda.synchronize()
+    # sizes whose product wraps around 64 bits must be refused too (2^31 - 1 cubed), not slip under the limit
+    big = 2 ** 31 - 1
+    rc = lib.fb_dot_product_noalloc_f32(*ptrs, big, big, big, 128, big, 1, _lib.FB_P2, 0.5, 1.0, _lib.FB_NATIVE, None)
+    assert rc == 5
+    torch.cuda.synchronize()
