@@ -64,19 +64,24 @@ def load_reference_bounds():
     return mod
 
 
-def load_reference_kernel_test():
+def load_reference_kernel_test(c_bound=None):
     """Returns the module object of HandTunedKernels/kernel_test/transformer_forward_test_bound.py
-    (its test-local `Bounds(p, eps, lw, lb, uw, ub)` class and the comparator)."""
-    if "ktest" in _cache:
-        return _cache["ktest"]
+    (its test-local `Bounds(p, eps, lw, lb, uw, ub)` class, the comparator and the *_test functions).
+    The module builds its extension with torch.utils.cpp_extension.load at import (:24-31); that call is
+    answered with `c_bound` (an object exposing the c_*_verification functions), so that the module's
+    cuda_* methods run whatever the caller plugs in.  Without `c_bound` an empty stand-in is given."""
+    key = "ktest" if c_bound is None else ("ktest", id(c_bound))
+    if key in _cache:
+        return _cache[key]
     import torch.utils.cpp_extension as cpp_ext
     saved = cpp_ext.load
-    cpp_ext.load = lambda *a, **k: types.SimpleNamespace()
+    cpp_ext.load = lambda *a, **k: (c_bound if c_bound is not None else types.SimpleNamespace())
     saved_env = os.environ.get("CUDA_VISIBLE_DEVICES")
     try:
         path = os.path.join(REFERENCE_ROOT, "HandTunedKernels", "kernel_test",
                             "transformer_forward_test_bound.py")
-        spec = importlib.util.spec_from_file_location("faith_reference_kernel_test", path)
+        spec = importlib.util.spec_from_file_location(
+            "faith_reference_kernel_test" if c_bound is None else "faith_reference_kernel_test_plugged", path)
         mod = importlib.util.module_from_spec(spec)
         spec.loader.exec_module(mod)
     finally:
@@ -85,7 +90,7 @@ def load_reference_kernel_test():
             os.environ.pop("CUDA_VISIBLE_DEVICES", None)
         else:
             os.environ["CUDA_VISIBLE_DEVICES"] = saved_env
-    _cache["ktest"] = mod
+    _cache[key] = mod
     return mod
 
 
@@ -121,20 +126,21 @@ def load_reference_verifier():
     return vf_mod.VerifierForward
 
 
-def build_reference_verifier(model, p, perturbed_words=1):
+def build_reference_verifier(model, p, perturbed_words=1, device="cpu"):
     """A reference VerifierForward wired to a stand-in encoder built from an oracle model
     dict (see oracle.bounds_oracle.make_encoder).  Only the attributes the forward bound
-    pass reads are provided (Verifier.py:11-34, VerifierForward.py:15-20,199-204)."""
+    pass reads are provided (Verifier.py:11-34, VerifierForward.py:15-20,199-204).
+    `device`: where the weights live and where `_bound_input` creates its tensors."""
     import torch.nn as nn
     VF = load_reference_verifier()
 
     def lin(w, b):
         m = nn.Linear(w.shape[1], w.shape[0])
-        m.weight.data, m.bias.data = w.clone(), b.clone()
+        m.weight.data, m.bias.data = w.clone().to(device), b.clone().to(device)
         return m
 
     def ln(g, b):
-        return types.SimpleNamespace(weight=g.clone(), bias=b.clone())
+        return types.SimpleNamespace(weight=g.clone().to(device), bias=b.clone().to(device))
 
     heads = model["heads"]
     layers = []
@@ -150,7 +156,7 @@ def build_reference_verifier(model, p, perturbed_words=1):
             output=types.SimpleNamespace(dense=lin(ly["f2_w"], ly["f2_b"]), LayerNorm=ln(ly["ln2_g"], ly["ln2_b"]))))
     v = VF.__new__(VF)
     v.args = make_args(p=p, perturbed_words=perturbed_words)
-    v.device = "cpu"
+    v.device = device
     v.p = p
     v.ibp = False
     v.debug = False
@@ -168,11 +174,27 @@ def build_reference_verifier(model, p, perturbed_words=1):
     return v
 
 
-def reference_encoder_pass(verifier, emb_one, index, eps):
+def reference_encoder_pass(verifier, emb_one, index, eps, bounds_cls=None):
     """Runs the reference bound pass for one sentence (emb_one [1, L, D]) and returns the
     concretised (l, u) of logit0 - logit1 plus the stage bounds, following
     VerifierForward.verify_safety (VerifierForward.py:93-119) and _bound_classifier
-    (:289-305) without the `check` calls (they need a concrete forward of the real model)."""
+    (:289-305) without the `check` calls (they need a concrete forward of the real model).
+    `bounds_cls`: the class the verifier's module-level name `Bounds` is bound to for the duration of the
+    pass (VerifierForward.py:7 imports it by name; _bound_input :153 and _bound_pooling :270 construct through
+    it), i.e. the one place where another implementation of the operator API plugs in.  None = the reference's."""
+    import copy
+    import torch
+    vf_mod = sys.modules["Verifiers.VerifierForward"]
+    saved_cls = vf_mod.Bounds
+    if bounds_cls is not None:
+        vf_mod.Bounds = bounds_cls
+    try:
+        return _reference_encoder_pass(verifier, emb_one, index, eps)
+    finally:
+        vf_mod.Bounds = saved_cls
+
+
+def _reference_encoder_pass(verifier, emb_one, index, eps):
     import copy
     import torch
     stages = []
