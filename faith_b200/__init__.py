@@ -4,8 +4,10 @@ Host-side mirror of the reference's operator interface over libfaith_b200.so:
   - `faith_b200.c_bound`  -- the pybind module surface of HandTunedKernels/kernel.cpp
   - `faith_b200.Bounds`   -- the `Bounds` class of Verifiers/Bounds.py with every operator on the GPU
   - `faith_b200.EncoderVerifier` -- the whole forward bound pass in one C++ driver call
+  - `faith_b200.EpsilonSearch`   -- the reference's search for the certified radius (Verifier.py:106-147), batched
 """
 from . import c_bound, ops  # noqa: F401
 from .bounds import Bounds, BoundsLite  # noqa: F401
 from .encoder import EncoderVerifier  # noqa: F401
+from .search import EpsilonSearch  # noqa: F401
 from ._lib import FaithError, load  # noqa: F401

@@ -65,6 +65,7 @@ SIGNATURES = {
     "fb_conv2d_f32": [_P] * 10 + [_I] * 10 + [_P],
     "fb_encoder_workspace_bytes": [ctypes.POINTER(Encoder), _I, _I, _I],
     "fb_encoder_forward_f32": [ctypes.POINTER(Encoder), _P, _I, _I, ctypes.POINTER(_I), _I, _I, _F, _P, _P, _P, _P, _L, _P],
+    "fb_encoder_forward_instances_f32": [ctypes.POINTER(Encoder), _P, _I, _I, _P, _P, _I, _I, _P, _P, _P, _P, _L, _P],
     "fb_profile_enable": [_I],
     "fb_profile_read": [_I, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(_L), ctypes.POINTER(ctypes.c_double),
                         ctypes.POINTER(ctypes.c_double)],

@@ -69,10 +69,14 @@ BoundSet carve_slot(char* base, const Plan& p) {
 // (VerifierForward.py:127-152).  positions are packed into `pos` (up to 4 words).
 struct Positions { int v[4]; };
 
+// With inst_pos / inst_eps != nullptr every sentence is a verification instance of its own: its perturbed positions
+// are inst_pos[s * words + w] and its identity block carries inst_eps[s] instead of 1 (the perturbation radius
+// folded into the weights: the dual norm is homogeneous, eps * ||lw|| = ||eps * lw||, so the pass then runs with
+// radius 1 for every instance).
 __global__ void __launch_bounds__(256)
 input_bounds_kernel(const float* __restrict__ emb, float* __restrict__ lw, float* __restrict__ uw,
                     float* __restrict__ lb, float* __restrict__ ub, int64_t n_w, int64_t n_b, int L, int D, int words,
-                    Positions pos) {
+                    Positions pos, const int* __restrict__ inst_pos, const float* __restrict__ inst_eps) {
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   const int Di = words * D;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_w; i += stride) {
@@ -80,7 +84,10 @@ input_bounds_kernel(const float* __restrict__ emb, float* __restrict__ lw, float
     const int m = (int)((i / D) % Di);
     const int l = (int)((i / ((int64_t)D * Di)) % L);
     const int w = m / D;
-    const float v = (l == pos.v[w] && (m - w * D) == j) ? 1.f : 0.f;
+    const int64_t sidx = i / ((int64_t)D * Di * L);
+    const int pw = inst_pos != nullptr ? inst_pos[sidx * words + w] : pos.v[w];
+    const float one = inst_eps != nullptr ? inst_eps[sidx] : 1.f;
+    const float v = (l == pw && (m - w * D) == j) ? one : 0.f;
     lw[i] = v;
     uw[i] = v;
   }
@@ -98,7 +105,8 @@ input_bounds_kernel(const float* __restrict__ emb, float* __restrict__ lw, float
 __global__ void __launch_bounds__(256)
 input_bounds_norm128_kernel(const float* __restrict__ emb, const float* __restrict__ gamma, const float* __restrict__ beta,
                             float* __restrict__ lw, float* __restrict__ uw, float* __restrict__ lb, float* __restrict__ ub,
-                            int64_t n_w_rows, int64_t n_b_rows, int L, int words, Positions pos) {
+                            int64_t n_w_rows, int64_t n_b_rows, int L, int words, Positions pos,
+                            const int* __restrict__ inst_pos, const float* __restrict__ inst_eps) {
   constexpr int D = 128;
   const int lane = threadIdx.x & 31;
   const int64_t warps = (int64_t)gridDim.x * 8;
@@ -120,9 +128,12 @@ input_bounds_norm128_kernel(const float* __restrict__ emb, const float* __restri
       const int m = (int)(row % Di);
       const int l = (int)((row / Di) % L);
       const int w = m / D;
-      const int hot = (l == pos.v[w]) ? m - w * D : -1;
+      const int64_t sidx = row / ((int64_t)Di * L);
+      const int pw = inst_pos != nullptr ? inst_pos[sidx * words + w] : pos.v[w];
+      const float one = inst_eps != nullptr ? inst_eps[sidx] : 1.f;
+      const int hot = (l == pw) ? m - w * D : -1;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) a[e] = (4 * lane + e == hot) ? 1.f : 0.f;
+      for (int e = 0; e < 4; ++e) a[e] = (4 * lane + e == hot) ? one : 0.f;
     }
     float mean = 0.f;
 #pragma unroll
@@ -193,15 +204,17 @@ extern "C" int64_t fb_encoder_workspace_bytes(const fb_encoder* enc, int S, int 
   return make_plan(enc, S, L, words).total;
 }
 
-extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, int S, int L, const int* positions,
-                                      int words, int p, float eps, float* out_l, float* out_u, int* violation,
-                                      void* workspace, int64_t workspace_bytes, void* stream) {
-  if (!enc || !emb || !positions || !out_l || !out_u || !violation || !workspace) return FB_ERR_ARG;
+// positions (host, one set for all sentences) or inst_pos / inst_eps (device, one set and one radius per sentence)
+static int encoder_forward_impl(const fb_encoder* enc, const float* emb, int S, int L, const int* positions,
+                                const int* inst_pos, const float* inst_eps, int words, int p, float eps, float* out_l,
+                                float* out_u, int* violation, void* workspace, int64_t workspace_bytes, void* stream) {
+  if (!enc || !emb || !out_l || !out_u || !violation || !workspace) return FB_ERR_ARG;
+  if ((positions == nullptr) == (inst_pos == nullptr) || (inst_pos == nullptr) != (inst_eps == nullptr)) return FB_ERR_ARG;
   if (S <= 0 || L <= 0 || words <= 0 || words > 4 || !valid_norm(p)) return FB_ERR_ARG;
   if (enc->layers < 0 || enc->heads <= 0 || enc->d_model <= 0 || enc->d_model % enc->heads != 0 || enc->ffn <= 0)
     return FB_ERR_ARG;
   if (enc->layer_norm != 0 && enc->layer_norm != 1) return FB_ERR_ARG;
-  for (int w = 0; w < words; ++w)
+  for (int w = 0; positions != nullptr && w < words; ++w)
     if (positions[w] < 0 || positions[w] >= L) return FB_ERR_ARG;
   if (!aligned16(workspace)) return FB_ERR_ALIGN;
   const Plan plan = make_plan(enc, S, L, words);
@@ -228,7 +241,7 @@ extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, i
   int A = 0, B = 1, C = 2, Dd = 3;
   {
     Positions pos = {{0, 0, 0, 0}};
-    for (int w = 0; w < words; ++w) pos.v[w] = positions[w];
+    for (int w = 0; positions != nullptr && w < words; ++w) pos.v[w] = positions[w];
     // (lw == uw at the input: the first layer reads the lw buffer as both lines, so the fused kernel is given
     // that buffer twice and the uw buffer of the slot stays unwritten)
     if (enc->layer_norm == 1 && D == 128 && aligned16(emb) && aligned16(enc->emb_ln_g) && aligned16(enc->emb_ln_b)) {
@@ -237,13 +250,13 @@ extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, i
       // (without encoder layers the pooler reads both buffers, so both are written)
       input_bounds_norm128_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, st>>>(
           emb, enc->emb_ln_g, enc->emb_ln_b, slot[A].lw, enc->layers == 0 ? slot[A].uw : slot[A].lw, slot[A].lb, slot[A].ub,
-          n_w_rows, n_b_rows, L, words, pos);
+          n_w_rows, n_b_rows, L, words, pos, inst_pos, inst_eps);
       FB_LAUNCH_OK();
     } else {
       const int64_t n_w = rows * Di * D, n_b = rows * D;
       const int64_t want = ceil_div(n_w, 256), cap = (int64_t)device_info().sms * 16;
       input_bounds_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, st>>>(emb, slot[B].lw, slot[B].uw, slot[B].lb,
-                                                                               slot[B].ub, n_w, n_b, L, D, words, pos);
+                                                                               slot[B].ub, n_w, n_b, L, D, words, pos, inst_pos, inst_eps);
       FB_LAUNCH_OK();
       FB_TRY(norm_residual(enc, slot[B], nullptr, enc->emb_ln_g, enc->emb_ln_b, slot[A], rows, Di, D, stream));
     }
@@ -427,4 +440,22 @@ extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, i
     FB_TRY(fb_concretize_f32(T2.lw, T2.uw, T2.lb, T2.ub, out_l, out_u, S, Di, 1, words, p, eps, FB_NATIVE, stream));
   }
   return FB_OK;
+}
+
+extern "C" int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, int S, int L, const int* positions,
+                                      int words, int p, float eps, float* out_l, float* out_u, int* violation,
+                                      void* workspace, int64_t workspace_bytes, void* stream) {
+  if (!positions) return FB_ERR_ARG;
+  return encoder_forward_impl(enc, emb, S, L, positions, nullptr, nullptr, words, p, eps, out_l, out_u, violation, workspace,
+                              workspace_bytes, stream);
+}
+
+extern "C" int fb_encoder_forward_instances_f32(const fb_encoder* enc, const float* emb, int S, int L,
+                                                const int* positions, const float* eps, int words, int p,
+                                                float* out_l, float* out_u, int* violation, void* workspace,
+                                                int64_t workspace_bytes, void* stream) {
+  if (!positions || !eps) return FB_ERR_ARG;
+  // the radius of every instance sits in its identity block: the pass itself runs with radius 1
+  return encoder_forward_impl(enc, emb, S, L, nullptr, positions, eps, words, p, 1.0f, out_l, out_u, violation, workspace,
+                              workspace_bytes, stream);
 }

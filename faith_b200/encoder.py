@@ -82,3 +82,28 @@ class EncoderVerifier:
                                                 viol.data_ptr(), self._ws.data_ptr(), need,
                                                 torch.cuda.current_stream().cuda_stream), "fb_encoder_forward_f32")
         return l, u, viol
+
+    def forward_instances(self, emb, positions, p, eps, out=None):
+        """The pass for S independent verification instances: emb [S, L, D], positions [S, words] (int32) and
+        eps [S] (float32), all on the device.  Returns (l, u, violation) like forward()."""
+        ops._chk(emb, eps)
+        S, L, D = emb.shape
+        if positions.dtype != torch.int32 or not positions.is_cuda or not positions.is_contiguous() or positions.dim() != 2 \
+                or positions.shape[0] != S or eps.shape != (S,):
+            raise ValueError("positions must be a contiguous int32 CUDA tensor [S, words] and eps a float32 tensor [S]")
+        words = positions.shape[1]
+        need = self.workspace_bytes(S, L, words)
+        if self._ws is None or self._ws.numel() < need:
+            self._ws = None
+            self._ws = torch.empty(need, dtype=torch.uint8, device=self.device)
+        if out is None:
+            out = (torch.empty(S, device=self.device), torch.empty(S, device=self.device),
+                   torch.empty(1, dtype=torch.int32, device=self.device))
+        l, u, viol = out
+        with torch.cuda.device(self.device):
+            check(load().fb_encoder_forward_instances_f32(ctypes.byref(self._enc), emb.data_ptr(), S, L, positions.data_ptr(),
+                                                          eps.data_ptr(), words, ops.norm_code(p), l.data_ptr(), u.data_ptr(),
+                                                          viol.data_ptr(), self._ws.data_ptr(), need,
+                                                          torch.cuda.current_stream().cuda_stream),
+                  "fb_encoder_forward_instances_f32")
+        return l, u, viol

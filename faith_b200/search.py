@@ -1,0 +1,83 @@
+"""The reference's search for the largest certified perturbation radius, with the probes batched.
+
+Reference: Verifier.verify (Transformer_Verification_Code/Verifiers/Verifier.py:106-147, one perturbed word): for every
+perturbable position i of a sentence, one probe at max_eps (whose answer the reference does not use, :116) and then
+num_verify_iters bisection steps on [0, max_eps], each step a full bound pass (verify_safety) at m = (l + r) / 2 that
+moves l up when the sentence is certified (logit0 - logit1 > 0 for label 0, < 0 for label 1,
+VerifierForward.py:306-312) and r down otherwise; the answer is l.  Sentences, positions and probes of different words are
+independent given the radius, so here every round is ONE call of the whole-model driver over all (sentence, position)
+pairs, each instance with its own radius (fb_encoder_forward_instances_f32).
+"""
+import torch
+
+
+def perturbable_positions(length, tokens=None):
+    """Positions the reference perturbs: 1 .. length-2 ([CLS] and [SEP] stay, Verifier.py:107), minus word pieces
+    (a token starting with '#' at i or i+1, :109-110) when the tokens are known."""
+    out = []
+    for i in range(1, length - 1):
+        if tokens is not None and (tokens[i][0] == "#" or tokens[i + 1][0] == "#"):
+            continue
+        out.append(i)
+    return out
+
+
+class EpsilonSearch:
+    """verifier: a faith_b200.EncoderVerifier.  max_instances bounds the instances of one driver call (the driver's
+    arena grows with it: about 68 MB per instance for the 128-wide, 32-token model)."""
+
+    def __init__(self, verifier, p, max_eps, num_verify_iters=10, max_instances=256, probe_max_eps=True):
+        self.ver = verifier
+        self.p = p
+        self.max_eps = float(max_eps)
+        self.iters = int(num_verify_iters)
+        self.max_instances = int(max_instances)
+        self.probe_max_eps = probe_max_eps
+        self.passes = 0          # driver calls made
+        self.instances = 0       # instances propagated (the reference would have made this many verify_safety calls)
+
+    def _safe(self, emb, sent, pos, labels, eps):
+        """One round: certified[j] for instance j = (sentence sent[j], position pos[j]) at radius eps[j]."""
+        dev = self.ver.device
+        n = sent.numel()
+        safe = torch.empty(n, dtype=torch.bool, device=dev)
+        for a in range(0, n, self.max_instances):
+            b = min(n, a + self.max_instances)
+            e = emb.index_select(0, sent[a:b])
+            l, u, viol = self.ver.forward_instances(e, pos[a:b].reshape(-1, 1).contiguous(), self.p, eps[a:b].contiguous())
+            status = self.ver.check_status(viol)
+            # bit 0 (a softmax denominator not provably positive) is the reference's failed assertion, which
+            # verify_safety turns into "not certified" (VerifierForward.py:120-125); the flag is per call, so the
+            # whole chunk is treated that way
+            ok = torch.where(labels.index_select(0, sent[a:b]) == 0, l > 0, u < 0)
+            safe[a:b] = ok if status == 0 else torch.zeros_like(ok)
+            self.passes += 1
+            self.instances += b - a
+        return safe
+
+    def run(self, emb, labels, positions=None):
+        """emb [N, L, D] and labels [N] on the device; positions: per sentence the list of positions to search (default:
+        all perturbable ones).  Returns a list of dicts {position: eps} per sentence, eps being the reference's `l`
+        after the last bisection step."""
+        dev = self.ver.device
+        N, L, _ = emb.shape
+        if positions is None:
+            positions = [perturbable_positions(L)] * N
+        sent = torch.tensor([s for s in range(N) for _ in positions[s]], dtype=torch.int64, device=dev)
+        pos = torch.tensor([i for s in range(N) for i in positions[s]], dtype=torch.int32, device=dev)
+        labels = labels.to(dev)
+        lo = torch.zeros(sent.numel(), dtype=torch.float64, device=dev)
+        hi = torch.full_like(lo, self.max_eps)
+        if self.probe_max_eps:
+            self._safe(emb, sent, pos, labels, hi.float())   # the reference's first probe; its answer is not used
+        for _ in range(self.iters):
+            mid = (lo + hi) / 2          # the reference bisects in Python floats (double precision)
+            safe = self._safe(emb, sent, pos, labels, mid.float())
+            lo = torch.where(safe, mid, lo)
+            hi = torch.where(safe, hi, mid)
+        lo = lo.cpu().tolist()
+        out, k = [], 0
+        for s in range(N):
+            out.append({int(i): lo[k + j] for j, i in enumerate(positions[s])})
+            k += len(positions[s])
+        return out

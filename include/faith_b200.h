@@ -375,6 +375,18 @@ int fb_encoder_forward_f32(const fb_encoder* enc, const float* emb, int S, int L
                            float* out_l, float* out_u, int* violation,
                            void* workspace, int64_t workspace_bytes, void* stream);
 
+/* The same pass for S independent verification instances: instance s has its own perturbed positions
+ * positions[s * words + w] and its own radius eps[s] (both DEVICE arrays; positions must lie in [0, L), which
+ * the caller guarantees).  This is how the reference's search over the radius (Verifier.py:106-147: per word a
+ * probe at max_eps and num_verify_iters bisection steps, each a call of verify_safety) is batched: the probes of
+ * all words and sentences of a round are instances of one call.  The radius is folded into the identity block of the
+ * input bound (the dual norm is homogeneous), so results agree with fb_encoder_forward_f32 up to rounding, not bit for
+ * bit.  emb [S, L, d_model]: the embeddings of instance s (instances of one sentence repeat its rows). */
+int fb_encoder_forward_instances_f32(const fb_encoder* enc, const float* emb, int S, int L,
+                                     const int* positions, const float* eps, int words, int p,
+                                     float* out_l, float* out_u, int* violation,
+                                     void* workspace, int64_t workspace_bytes, void* stream);
+
 /* ---- measurement hooks (no counterpart in the reference) --------------------------------
  * fb_profile_enable(1) clears the records and makes every outermost operator call bracket its
  * launches with a pair of CUDA events on the caller's stream; fb_profile_read() waits for the

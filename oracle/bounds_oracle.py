@@ -591,3 +591,26 @@ def make_cnn(seed, c_in=3, hw=32, dtype=torch.float32):
     return [("conv", kaiming(16, c_in, 3, 3), torch.zeros(16, dtype=dtype), 1, 1), ("relu",),
             ("conv", kaiming(32, 16, 3, 3), torch.zeros(32, dtype=dtype), 2, 1), ("relu",),
             ("linear", kaiming(10, 32 * ho * ho), torch.zeros(10, dtype=dtype))]
+
+
+def epsilon_search(model, emb_one, label, p, max_eps, iters, positions=None):
+    """Largest certified radius per perturbed position of one sentence (emb_one [1, L, D]): the reference's loop,
+    Verifier.verify (Verifiers/Verifier.py:106-147, one perturbed word): a probe at max_eps whose answer is not
+    used, then `iters` bisection steps on [0, max_eps] in Python floats; a probe certifies when the concretised
+    logit0 - logit1 keeps the sign of the label (VerifierForward.py:306-312).  Returns {position: eps}."""
+    L = emb_one.shape[1]
+    out = {}
+    for i in (positions if positions is not None else range(1, L - 1)):
+        def safe(eps):
+            l, u = encoder_forward(model, emb_one, [i], p, eps)
+            return bool(l[0] > 0) if label == 0 else bool(u[0] < 0)
+        lo, hi = 0.0, float(max_eps)
+        safe(hi)
+        for _ in range(iters):
+            m = (lo + hi) / 2
+            if safe(m):
+                lo = m
+            else:
+                hi = m
+        out[int(i)] = lo
+    return out

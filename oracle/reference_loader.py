@@ -214,3 +214,37 @@ def _reference_encoder_pass(verifier, emb_one, index, eps):
         b = b.dense(cls, verifier.tvm_model_lut, FLAG=0)
         l, u = b.concretize()
     return l[0][0][0], u[0][0][0], stages
+
+
+def reference_epsilon_search(verifier, emb_one, label, max_eps, num_iters):
+    """Runs the reference's own search loop, Verifier.verify (Verifier.py:62-208, one perturbed word), unchanged
+    for one sentence (emb_one [1, L, D]) and returns {position: eps}.  The loop asks its `target` for the
+    embeddings, the tokens and the concrete activations (`std`) that `check` compares the bounds with; check
+    never asserts (utils.py:30 is commented out), so the stand-in target hands out zeros of the right shapes."""
+    import contextlib
+    import io
+    import torch
+    L, D = emb_one.shape[1], emb_one.shape[2]
+    n_layers = len(verifier.encoding_layers)
+    heads = verifier.encoding_layers[0].attention.self.num_attention_heads if n_layers else 1
+    dev = emb_one.device
+    std = {
+        "embedding_output": torch.zeros(1, L, D, device=dev),
+        "attention_scores": [torch.zeros(1, heads, L, L, device=dev) for _ in range(n_layers)],
+        "attention_probs": [torch.zeros(1, heads, L, L, device=dev) for _ in range(n_layers)],
+        "encoded_layers": [torch.zeros(1, L, D, device=dev) for _ in range(n_layers)],
+        "pooled_output": torch.zeros(1, D, device=dev),
+    }
+    tokens = ["[CLS]"] + ["w%d" % i for i in range(1, L - 1)] + ["[SEP]"]
+    verifier.target = types.SimpleNamespace(get_embeddings=lambda examples: (emb_one.clone(), [tokens]),
+                                            step=lambda examples: [std])
+    verifier.logger = types.SimpleNamespace(write=lambda *a, **k: None)
+    verifier.max_eps = max_eps
+    verifier.num_verify_iters = num_iters
+    verifier.eps = max_eps
+    verifier.debug_pos = 1
+    verifier.method = "forward"
+    verifier.res = os.devnull
+    with contextlib.redirect_stdout(io.StringIO()):
+        result, _avg, _min = verifier.verify({"label": label})
+    return {int(b["position"]): float(b["eps"]) for b in result["bounds"]}

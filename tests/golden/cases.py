@@ -54,6 +54,13 @@ OP_CASES["add_bounds"] = dict(op="add", p=2.0, words=1, eps=0.5, seed=63, B=1, L
 # small encoder for the end-to-end golden (eps small enough that bounds stay tight)
 ENCODER_CASE = dict(seed=71, layers=2, d_model=32, heads=2, ffn=64, L=8, B=2, eps=1e-3, p=INF, index=1, std=0.1)
 
+# search for the largest certified radius (Verifier.py:106-147): per word a probe at max_eps and `iters` bisection
+# steps.  A small encoder with BERT-like initialisation (std 0.02): its fp32 rounding noise (1e-7 on the logit bounds) is
+# four orders of magnitude below what one bisection step changes, so every implementation must take the same
+# decisions; max_eps sits above the radius where certification stops and below the one where a softmax denominator
+# is no longer provably positive.
+SEARCH_CASE = dict(seed=72, layers=2, d_model=32, heads=2, ffn=64, L=8, B=2, std=0.02, p=INF, max_eps=1.0, iters=8)
+
 
 def case_inputs(c):
     """Materialises the input tensors of an operator case: (x_bounds_tuple, extras)."""

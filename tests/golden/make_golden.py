@@ -8,7 +8,8 @@ For every case of cases.OP_CASES the reference `Bounds` operator
 (Transformer_Verification_Code/Verifiers/Bounds.py) is run on the seeded inputs and its four
 output tensors are stored; for the encoder case the reference `VerifierForward` pass
 (Verifiers/VerifierForward.py:93-119) is run sentence by sentence and the concretised logit
-bounds plus a few stage tensors are stored.
+bounds plus a few stage tensors are stored; for the search case the reference's `Verifier.verify`
+(Verifiers/Verifier.py:62-147) is run and the radius it finds per position is stored.
 """
 import os
 import sys
@@ -102,7 +103,20 @@ def main():
     enc["l"] = np.array(ls, dtype=np.float32)
     enc["u"] = np.array(us, dtype=np.float32)
     np.savez_compressed(os.path.join(HERE, "encoder.npz"), **enc)
-    print("wrote ops.npz (%d arrays) and encoder.npz (%d arrays)" % (len(out), len(enc)))
+
+    # the reference's own search loop (Verifier.verify, unchanged) on the same sentences
+    sc = cases.SEARCH_CASE
+    model = O.make_encoder(sc["seed"], sc["layers"], sc["d_model"], sc["heads"], sc["ffn"], sc["std"])
+    emb = cases.encoder_inputs(sc)
+    ver = ref_loader.build_reference_verifier(model, sc["p"])
+    y = O.concrete_forward(model, emb)
+    srch = {"labels": np.array([0 if float(y[s]) > 0 else 1 for s in range(sc["B"])], dtype=np.int64)}
+    for s in range(sc["B"]):
+        r = ref_loader.reference_epsilon_search(ver, emb[s:s + 1], int(srch["labels"][s]), sc["max_eps"], sc["iters"])
+        srch["s%d/positions" % s] = np.array(sorted(r), dtype=np.int64)
+        srch["s%d/eps" % s] = np.array([r[i] for i in sorted(r)], dtype=np.float64)
+    np.savez_compressed(os.path.join(HERE, "search.npz"), **srch)
+    print("wrote ops.npz (%d arrays), encoder.npz (%d arrays) and search.npz (%d arrays)" % (len(out), len(enc), len(srch)))
 
 
 if __name__ == "__main__":

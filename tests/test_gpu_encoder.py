@@ -1,5 +1,6 @@
 """The C++ whole-model driver against the CPU oracle: per-stage noise budget, golden vectors and
 sampled containment of concrete forward passes."""
+import numpy as np
 import pytest
 import torch
 
@@ -169,3 +170,54 @@ def test_encoder_without_layers():
     l64, u64 = O.encoder_forward(O.model_to(model, torch.float64), emb.double(), [2], float("inf"), 0.01)
     helpers.assert_within_noise(l, l32, l64, "l")
     helpers.assert_within_noise(u, u32, u64, "u")
+
+
+def test_instances_entry_point_matches_one_call_per_radius():
+    """fb_encoder_forward_instances_f32 (own positions and radius per instance, the radius folded into the input
+    weights) against fb_encoder_forward_f32 called once per (position, radius): same bounds up to rounding."""
+    import faith_b200
+    c, model, emb = _small()
+    ver = faith_b200.EncoderVerifier(model, DEV)
+    combos = [(0, 1, 2e-4), (0, 5, 6e-4), (1, 3, 1e-4), (1, 6, 3e-4), (0, 2, 4e-4)]
+    e = torch.stack([emb[s] for s, _, _ in combos]).to(DEV)
+    pos = torch.tensor([[i] for _, i, _ in combos], dtype=torch.int32, device=DEV)
+    eps = torch.tensor([r for _, _, r in combos], dtype=torch.float32, device=DEV)
+    l, u, viol = ver.forward_instances(e, pos, c["p"], eps)
+    assert ver.check_status(viol) == 0
+    for k, (s, i, r) in enumerate(combos):
+        l1, u1, v1 = ver.forward(emb[s:s + 1].to(DEV), [i], c["p"], r)
+        l64, u64 = O.encoder_forward(O.model_to(model, torch.float64), emb[s:s + 1].double(), [i], c["p"], r)
+        l32, u32 = O.encoder_forward(model, emb[s:s + 1], [i], c["p"], r)
+        helpers.assert_within_noise(l[k:k + 1], l32, l64, "instance %d l" % k)
+        helpers.assert_within_noise(u[k:k + 1], u32, u64, "instance %d u" % k)
+        helpers.assert_within_noise(l[k:k + 1], l1, l64, "instance %d l vs single call" % k)
+        helpers.assert_within_noise(u[k:k + 1], u1, u64, "instance %d u vs single call" % k)
+
+
+def test_batched_search_reproduces_the_reference_radii():
+    """The reference's search (Verifier.verify, run unchanged on CPU when the golden file was made) against the
+    batched search: all (sentence, position) pairs of a bisection round are instances of one driver call.  A
+    bisection step whose bound lands within rounding noise of zero may go the other way, which moves the answer by
+    at most the width of the last steps (max_eps / 2^iters); most positions agree to the last bit."""
+    import faith_b200
+    from faith_b200.search import EpsilonSearch
+    c = sc = cases.SEARCH_CASE
+    model = O.make_encoder(c["seed"], c["layers"], c["d_model"], c["heads"], c["ffn"], c["std"])
+    emb = cases.encoder_inputs(c)
+    g = helpers.load_golden("search.npz")
+    ver = faith_b200.EncoderVerifier(model, DEV)
+    labels = torch.as_tensor(g["labels"])
+    srch = EpsilonSearch(ver, c["p"], sc["max_eps"], sc["iters"], max_instances=8)
+    got = srch.run(emb.to(DEV), labels)
+    step = sc["max_eps"] / 2 ** sc["iters"]
+    n, same = 0, 0
+    for s in range(c["B"]):
+        pos = [int(i) for i in g["s%d/positions" % s]]
+        assert sorted(got[s]) == pos
+        for i, e in zip(pos, g["s%d/eps" % s]):
+            n += 1
+            same += np.float32(got[s][i]) == np.float32(e)   # the reference keeps its answer in a float32 tensor
+            assert abs(got[s][i] - float(e)) <= 2.001 * step, (s, i, got[s][i], float(e))
+    assert same >= n - 1, "%d of %d radii differ from the reference" % (n - same, n)
+    # 12 words x (1 + 8) probes = 108 verify_safety calls of the reference, here 9 rounds of 2 calls (8 instances each)
+    assert srch.instances == n * (sc["iters"] + 1) and srch.passes == (sc["iters"] + 1) * 2

@@ -1,6 +1,7 @@
 """The CPU oracle against the committed golden vectors (outputs of the reference's own
 Python `Bounds`, see tests/golden/make_golden.py)."""
 import pytest
+import numpy as np
 import torch
 
 import cases
@@ -83,3 +84,24 @@ def test_conv_oracle_agrees_with_im2col_matmul():
     m = xw.matmul(wt.reshape(Co, -1))  # lw [1, H*W, Di, Co]
     helpers.assert_close(m.lw[0].permute(1, 2, 0).reshape(Di, Co, H, W), o.lw[0], "lw", atol=2e-6)
     helpers.assert_close(m.ub[0].transpose(0, 1).reshape(Co, H, W), o.ub[0], "ub", atol=2e-6)
+
+
+def test_oracle_search_loop_matches_the_reference_verifier():
+    """The restated search loop against the radii the reference's own Verifier.verify found (tests/golden/search.npz).
+    A bisection probe whose bound lands within fp32 rounding noise of zero could be answered the other way by another
+    summation order, which would move the answer by at most the width of the last steps; with this model's noise that
+    is rare, so at most one position may differ."""
+    c = sc = cases.SEARCH_CASE
+    model = O.make_encoder(c["seed"], c["layers"], c["d_model"], c["heads"], c["ffn"], c["std"])
+    emb = cases.encoder_inputs(c)
+    g = helpers.load_golden("search.npz")
+    n, same = 0, 0
+    for s in range(c["B"]):
+        got = O.epsilon_search(model, emb[s:s + 1], int(g["labels"][s]), c["p"], sc["max_eps"], sc["iters"])
+        assert sorted(got) == [int(i) for i in g["s%d/positions" % s]]
+        for i, e in zip(g["s%d/positions" % s], g["s%d/eps" % s]):
+            # the reference keeps its answer in a float32 tensor (Verifier.py:92, :137)
+            n += 1
+            same += np.float32(got[int(i)]) == np.float32(e)
+            assert abs(got[int(i)] - float(e)) <= 2.001 * sc["max_eps"] / 2 ** sc["iters"], (s, int(i), got[int(i)], float(e))
+    assert same >= n - 1, "%d of %d radii differ from the reference" % (n - same, n)
