@@ -11,7 +11,8 @@ LIB_PATH = os.path.join(_HERE, "libfaith_b200.so")
 
 FB_P1, FB_P2, FB_PINF = 1, 2, 3
 FB_NATIVE, FB_TRANSPOSED = 0, 1
-FB_RELU, FB_TANH, FB_EXP, FB_RECIPROCAL = 0, 1, 2, 3
+FB_RELU, FB_TANH, FB_EXP, FB_RECIPROCAL, FB_SQR, FB_SQRT = 0, 1, 2, 3, 4, 5
+FB_INTERVAL = 8
 
 _P = ctypes.c_void_p
 _I = ctypes.c_int
@@ -57,6 +58,9 @@ SIGNATURES = {
     "fb_add_f32": [_P] * 12 + [_L, _I, _I, _P],
     "fb_scale_f32": [_P] * 8 + [_L, _I, _I, _F, _P],
     "fb_rowsum_f32": [_P] * 8 + [_L, _I, _I, _P],
+    "fb_mul_features_f32": [_P] * 9 + [_L, _I, _I, _P],
+    "fb_interval_mul_f32": [_P] * 6 + [_L, _P],
+    "fb_interval_dot_f32": [_P] * 6 + [_I, _I, _I, _I, _P],
     "fb_softmax_f32": [_P] * 8 + [_L, _I, _I, _I, _I, _F, _P, _P],
     "fb_softmax_ranges_f32": [_P] * 10 + [_L, _I, _I, _I, _I, _F, _P, _P],
     "fb_layernorm_novar_f32": [_P] * 14 + [_L, _I, _I, _P],

@@ -561,9 +561,10 @@ extern "C" int fb_concretize_f32(const float* lw, const float* uw, const float* 
 extern "C" int fb_relax_f32(int op, const float* lw, const float* uw, const float* lb, const float* ub,
                             float* out_lw, float* out_uw, float* out_lb, float* out_ub, int64_t rows, int Di, int Do,
                             int words, int p, float eps, int layout, int* violation, void* stream) {
-  if (rows == 0 || Do == 0) return (op < FB_RELU || op > FB_RECIPROCAL) ? FB_ERR_ARG : FB_OK;
+  const bool known_op = (op >= FB_RELU && op <= FB_SQRT) || (op >= FB_INTERVAL + FB_RELU && op <= FB_INTERVAL + FB_SQRT);
+  if (rows == 0 || Do == 0) return known_op ? FB_OK : FB_ERR_ARG;
   if (!lw || !uw || !lb || !ub || !out_lw || !out_uw || !out_lb || !out_ub) return FB_ERR_ARG;
-  if (op < FB_RELU || op > FB_RECIPROCAL) return FB_ERR_ARG;
+  if (!known_op) return FB_ERR_ARG;
   if (rows < 0 || Di <= 0 || Do < 0 || words <= 0 || !valid_norm(p)) return FB_ERR_ARG;
   if (layout != FB_NATIVE && layout != FB_TRANSPOSED) return FB_ERR_ARG;
   if (Di % words != 0) return FB_ERR_SHAPE;

@@ -126,6 +126,50 @@ __device__ __forceinline__ float exp_capped(float x) {
 // the column coefficients.  `bad` is set when FB_RECIPROCAL sees l < 1e-12.
 __device__ inline ColCoef relax_column(int op, float l, float u, float lb, float ub, bool& bad) {
   ColCoef c = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (op >= FB_INTERVAL) {
+    // interval form (the reference's `ibp` branches): constant bounds, no dependence on the weights
+    switch (op - FB_INTERVAL) {
+      case FB_RELU: c.nlb = fmaxf(l, 0.f); c.nub = fmaxf(u, 0.f); break;       // Bounds.py:924-926
+      case FB_TANH: c.nlb = tanhf(l); c.nub = tanhf(u); break;                  // :1030-1032
+      case FB_EXP: c.nlb = expf(l); c.nub = expf(u); break;                     // :973-975
+      case FB_RECIPROCAL: c.nlb = fdiv(1.f, u); c.nub = fdiv(1.f, l); break;    // :1139-1143
+      case FB_SQR: {                                                            // :863-866
+        const float a = fmul(l, l), b = fmul(u, u);
+        const float both = 1.f - ((l > 0.f) ? 1.f : 0.f) - ((u < 0.f) ? 1.f : 0.f);
+        const float lo = fminf(a, b);
+        c.nlb = fsub(lo, fmul(both, lo));   // zero when the range crosses zero
+        c.nub = fmaxf(a, b);
+        break;
+      }
+      default:                                                                  // FB_SQRT, :894-898
+        if (!(l > 0.f)) bad = true;
+        c.nlb = sqrtf(l);
+        c.nub = sqrtf(u);
+        break;
+    }
+    return c;
+  }
+  if (op == FB_SQR) {  // Bounds.py:867-885: chord above; tangent below, placed so that it never goes negative
+    add_line(c, 1.f, false, fadd(u, l), l, fmul(l, l), lb, ub);
+    if (u < 0.f) {
+      const float m = fmaxf(fmul(fadd(l, u), 0.5f), fmul(2.f, u));
+      add_line(c, 1.f, true, fmul(2.f, m), m, fmul(m, m), lb, ub);
+    }
+    if (l > 0.f) {
+      const float m = fminf(fmul(fadd(l, u), 0.5f), fmul(2.f, l));
+      add_line(c, 1.f, true, fmul(2.f, m), m, fmul(m, m), lb, ub);
+    }
+    return c;
+  }
+  if (op == FB_SQRT) {  // Bounds.py:892-913: chord below, tangent at the midpoint above
+    if (!(l > 0.f)) bad = true;
+    const float sl = sqrtf(l);
+    add_line(c, 1.f, true, fdiv(fsub(sqrtf(u), sl), fadd(fsub(u, l), kGuard)), l, sl, lb, ub);
+    const float m = fmul(fadd(l, u), 0.5f);
+    const float sm = sqrtf(m);
+    add_line(c, 1.f, false, fdiv(0.5f, sm), m, sm, lb, ub);
+    return c;
+  }
   if (op == FB_EXP) {  // Bounds.py:982-997; both slopes are applied to the own side
     const float m = fminf(fmul(fadd(l, u), 0.5f), fadd(l, 0.99f));
     const float kl = expf(fminf(m, 12.f));

@@ -252,6 +252,67 @@ heads_split_transpose_kernel(const float* __restrict__ src, float* __restrict__ 
   }
 }
 
+// z_l = x_l * w+ + x_u * w-,  z_u = x_l * w- + x_u * w+ with w a vector over the feature axis (Bounds.py:653-664);
+// n elements of rows of length Do.
+__global__ void __launch_bounds__(kThreads)
+mul_features_kernel(const float* xl, const float* xu, const float* __restrict__ w, float* zl, float* zu, int64_t n, int Do) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const float wv = w[i % Do];
+    const float wp = wv > 0.f ? wv : 0.f;
+    const float wn = fsub(wv, wp);
+    const float a = xl[i], b = xu[i];   // both read before either is written: z may alias x
+    zl[i] = fadd(fmul(a, wp), fmul(b, wn));
+    zu[i] = fadd(fmul(a, wn), fmul(b, wp));
+  }
+}
+
+// Interval product of two boxes, elementwise (Bounds.get_bounds_xy in `ibp` mode, Bounds.py:667-678).
+__global__ void __launch_bounds__(kThreads)
+interval_mul_kernel(const float* __restrict__ xl, const float* __restrict__ xu, const float* __restrict__ yl,
+                    const float* __restrict__ yu, float* __restrict__ zl, float* __restrict__ zu, int64_t n) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const float p1 = fmul(xl[i], yl[i]), p2 = fmul(xl[i], yu[i]), p3 = fmul(xu[i], yl[i]), p4 = fmul(xu[i], yu[i]);
+    zl[i] = fminf(p1, fminf(p2, fminf(p3, p4)));
+    zu[i] = fmaxf(p1, fmaxf(p2, fmaxf(p3, p4)));
+  }
+}
+
+// Interval dot product z[b, i, j] = sum_k [x[b, i, k]] * [y[b, j, k]] (Bounds.py:711-721): one warp per (b, i, j),
+// the lanes stride over k; the partial sums are added in a fixed tree, k ascending within a lane.
+__global__ void __launch_bounds__(kThreads)
+interval_dot_kernel(const float* __restrict__ xl, const float* __restrict__ xu, const float* __restrict__ yl,
+                    const float* __restrict__ yu, float* __restrict__ zl, float* __restrict__ zu, int64_t n_out, int Lx,
+                    int Ly, int K) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t o = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; o < n_out; o += warps) {
+    const int j = (int)(o % Ly);
+    const int64_t bi = o / Ly;          // b * Lx + i
+    const int64_t b = bi / Lx;
+    const float* pxl = xl + bi * K;
+    const float* pxu = xu + bi * K;
+    const float* pyl = yl + (b * Ly + j) * K;
+    const float* pyu = yu + (b * Ly + j) * K;
+    float lo = 0.f, hi = 0.f;
+    for (int k = lane; k < K; k += 32) {
+      const float p1 = fmul(pxl[k], pyl[k]), p2 = fmul(pxl[k], pyu[k]), p3 = fmul(pxu[k], pyl[k]), p4 = fmul(pxu[k], pyu[k]);
+      lo = fadd(lo, fminf(fminf(p1, p2), fminf(p3, p4)));
+      hi = fadd(hi, fmaxf(fmaxf(p1, p2), fmaxf(p3, p4)));
+    }
+#pragma unroll
+    for (int sft = 16; sft > 0; sft >>= 1) {
+      lo = fadd(lo, __shfl_xor_sync(0xffffffffu, lo, sft));
+      hi = fadd(hi, __shfl_xor_sync(0xffffffffu, hi, sft));
+    }
+    if (lane == 0) {
+      zl[o] = lo;
+      zu[o] = hi;
+    }
+  }
+}
+
 }  // namespace
 }  // namespace fb
 
@@ -384,5 +445,43 @@ extern "C" int fb_merge_heads_f32(const float* x_w, const float* x_b, float* z_w
   else heads_permute_kernel<1, false><<<stream_blocks(nw), kThreads, 0, st>>>(x_w, z_w, B, L, Di, H, d);
   heads_permute_kernel<1, false><<<stream_blocks(nb), kThreads, 0, st>>>(x_b, z_b, B, L, 1, H, d);
   FB_LAUNCH_OK_N(2);
+  return FB_OK;
+}
+
+extern "C" int fb_mul_features_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+                                   const float* w, float* z_lw, float* z_uw, float* z_lb, float* z_ub,
+                                   int64_t rows, int Di, int Do, void* stream) {
+  FB_REQUIRE(x_lw && x_uw && x_lb && x_ub && w && z_lw && z_uw && z_lb && z_ub, FB_ERR_ARG);
+  FB_REQUIRE(rows >= 0 && Di > 0 && Do >= 0, FB_ERR_ARG);
+  const int64_t nw = rows * Di * Do, nb = rows * Do;
+  if (nb == 0) return FB_OK;
+  ProfileScope prof(PK_ELEMENTWISE, 4.0 * (nw + nb), 4.0 * 4 * (nw + nb), stream);
+  cudaStream_t st = (cudaStream_t)stream;
+  mul_features_kernel<<<stream_blocks(nw), kThreads, 0, st>>>(x_lw, x_uw, w, z_lw, z_uw, nw, Do);
+  mul_features_kernel<<<stream_blocks(nb), kThreads, 0, st>>>(x_lb, x_ub, w, z_lb, z_ub, nb, Do);
+  FB_LAUNCH_OK_N(2);
+  return FB_OK;
+}
+
+extern "C" int fb_interval_mul_f32(const float* x_l, const float* x_u, const float* y_l, const float* y_u,
+                                   float* z_l, float* z_u, int64_t n, void* stream) {
+  FB_REQUIRE(x_l && x_u && y_l && y_u && z_l && z_u && n >= 0, FB_ERR_ARG);
+  if (n == 0) return FB_OK;
+  ProfileScope prof(PK_MUL, 4.0 * n, 4.0 * 6 * n, stream);
+  interval_mul_kernel<<<stream_blocks(n), kThreads, 0, (cudaStream_t)stream>>>(x_l, x_u, y_l, y_u, z_l, z_u, n);
+  FB_LAUNCH_OK();
+  return FB_OK;
+}
+
+extern "C" int fb_interval_dot_f32(const float* x_l, const float* x_u, const float* y_l, const float* y_u,
+                                   float* z_l, float* z_u, int B, int Lx, int Ly, int K, void* stream) {
+  FB_REQUIRE(x_l && x_u && y_l && y_u && z_l && z_u, FB_ERR_ARG);
+  FB_REQUIRE(B >= 0 && Lx > 0 && Ly > 0 && K > 0, FB_ERR_ARG);
+  const int64_t n_out = (int64_t)B * Lx * Ly;
+  if (n_out == 0) return FB_OK;
+  ProfileScope prof(PK_DOT, 8.0 * n_out * K, 4.0 * (2.0 * B * (Lx + Ly) * K + 2.0 * n_out), stream);
+  interval_dot_kernel<<<stream_blocks(n_out * 32), kThreads, 0, (cudaStream_t)stream>>>(x_l, x_u, y_l, y_u, z_l, z_u, n_out,
+                                                                                         Lx, Ly, K);
+  FB_LAUNCH_OK();
   return FB_OK;
 }

@@ -254,6 +254,45 @@ def scale(x, c):
     return out
 
 
+def mul_features(x, w):
+    """x * w with w a vector over the feature axis, split by sign (Bounds.py:653-664)."""
+    dev = _chk(*x, w)
+    lw, uw, lb, ub = x
+    rows, Di, Do = lb.numel() // lb.shape[-1], lw.shape[-2], lw.shape[-1]
+    if w.numel() != Do:
+        raise _lib.FaithError("feature vector of %d elements against %d features" % (w.numel(), Do))
+    z = tuple(torch.empty_like(t) for t in x)
+    with torch.cuda.device(dev):
+        check(load().fb_mul_features_f32(_p(lw), _p(uw), _p(lb), _p(ub), _p(w), _p(z[0]), _p(z[1]), _p(z[2]), _p(z[3]),
+                                         rows, Di, Do, _stream()), "fb_mul_features_f32")
+    return z
+
+
+def interval_mul(xl, xu, yl, yu):
+    """Elementwise product of two boxes (Bounds.py:667-678)."""
+    dev = _chk(xl, xu, yl, yu)
+    zl, zu = torch.empty_like(xl), torch.empty_like(xu)
+    with torch.cuda.device(dev):
+        check(load().fb_interval_mul_f32(_p(xl), _p(xu), _p(yl), _p(yu), _p(zl), _p(zu), xl.numel(), _stream()),
+              "fb_interval_mul_f32")
+    return zl, zu
+
+
+def interval_dot(xl, xu, yl, yu):
+    """z[b,i,j] = sum_k [x[b,i,k]] * [y[b,j,k]] for boxes x [B,Lx,K], y [B,Ly,K] (Bounds.py:711-721)."""
+    dev = _chk(xl, xu, yl, yu)
+    B, Lx, K = xl.shape
+    Ly = yl.shape[1]
+    if yl.shape[0] != B or yl.shape[2] != K:
+        raise _lib.FaithError("interval_dot: shapes %s and %s do not match" % (tuple(xl.shape), tuple(yl.shape)))
+    zl = torch.empty(B, Lx, Ly, device=dev, dtype=torch.float32)
+    zu = torch.empty_like(zl)
+    with torch.cuda.device(dev):
+        check(load().fb_interval_dot_f32(_p(xl), _p(xu), _p(yl), _p(yu), _p(zl), _p(zu), B, Lx, Ly, K, _stream()),
+              "fb_interval_dot_f32")
+    return zl, zu
+
+
 def rowsum(x):
     dev = _chk(*x)
     x_lw, x_uw, x_lb, x_ub = x

@@ -7,7 +7,13 @@ moves l up when the sentence is certified (logit0 - logit1 > 0 for label 0, < 0 
 VerifierForward.py:306-312) and r down otherwise; the answer is l.  Sentences, positions and probes of different words are
 independent given the radius, so here every round is ONE call of the whole-model driver over all (sentence, position)
 pairs, each instance with its own radius (fb_encoder_forward_instances_f32).
+
+With two perturbed words (Verifier.py:149-201) the reference first warms max_eps up on the pair (1, 2), then for every
+pair of positions doubles or halves the radius until the answer flips and bisects from there: the number of probes
+differs from pair to pair, so here every pair carries its own small state machine and a round evaluates the current
+probe of every pair that is not finished.
 """
+import numpy as np
 import torch
 
 
@@ -44,7 +50,7 @@ class EpsilonSearch:
         for a in range(0, n, self.max_instances):
             b = min(n, a + self.max_instances)
             e = emb.index_select(0, sent[a:b])
-            l, u, viol = self.ver.forward_instances(e, pos[a:b].reshape(-1, 1).contiguous(), self.p, eps[a:b].contiguous())
+            l, u, viol = self.ver.forward_instances(e, pos[a:b].reshape(b - a, -1).contiguous(), self.p, eps[a:b].contiguous())
             status = self.ver.check_status(viol)
             # bit 0 (a softmax denominator not provably positive) is the reference's failed assertion, which
             # verify_safety turns into "not certified" (VerifierForward.py:120-125); the flag is per call, so the
@@ -81,3 +87,76 @@ class EpsilonSearch:
             out.append({int(i): lo[k + j] for j, i in enumerate(positions[s])})
             k += len(positions[s])
         return out
+
+    def run_pairs(self, emb, labels, pairs=None, warm_up=True):
+        """Two perturbed words.  emb [N, L, D], labels [N]; pairs: per sentence the list of (i1, i2) to search (default:
+        all i1 < i2 among the perturbable positions).  Returns (list of dicts {(i1, i2): eps} per sentence, max_eps after
+        the warm-up).  The warm-up is the reference's (Verifier.py:150-157): on the first sentence and the pair (1, 2),
+        halve max_eps until it certifies, then double it until it does not."""
+        dev = self.ver.device
+        N, L, _ = emb.shape
+        labels = labels.to(dev)
+        if pairs is None:
+            pp = perturbable_positions(L)
+            pairs = [[(a, b) for k, a in enumerate(pp) for b in pp[k + 1:]]] * N
+        max_eps = self.max_eps
+        if warm_up:
+            s0 = torch.zeros(1, dtype=torch.int64, device=dev)
+            p0 = torch.tensor([[1, 2]], dtype=torch.int32, device=dev)
+
+            def probe(e):
+                return bool(self._safe(emb, s0, p0, labels, torch.tensor([e], dtype=torch.float32, device=dev))[0])
+            while not probe(max_eps):
+                max_eps /= 2
+            while probe(max_eps):
+                max_eps *= 2
+        sent = torch.tensor([s for s in range(N) for _ in pairs[s]], dtype=torch.int64, device=dev)
+        pos = torch.tensor([list(q) for s in range(N) for q in pairs[s]], dtype=torch.int32, device=dev).reshape(-1, 2)
+        n = sent.numel()
+        lo, hi = np.zeros(n), np.full(n, max_eps)     # the reference's l, r (Python floats)
+        phase = np.zeros(n, dtype=np.int64)           # 0 first probe, 1 doubling, 2 halving, 3 bisecting, 4 done
+        step = np.zeros(n, dtype=np.int64)
+        cur = hi.copy()
+        while (phase != 4).any():
+            act = np.nonzero(phase != 4)[0]
+            idx = torch.as_tensor(act, device=dev)
+            safe = self._safe(emb, sent[idx], pos[idx], labels,
+                              torch.as_tensor(cur[act], dtype=torch.float32, device=dev)).cpu().numpy()
+            for k, ok in zip(act, safe):
+                ph = phase[k]
+                if ph in (0, 1):
+                    if ok:                       # while safe: l = r; r *= 2
+                        lo[k] = hi[k]
+                        hi[k] *= 2
+                        cur[k] = hi[k]
+                        phase[k] = 1
+                        continue
+                    if ph == 0:                  # never certified: halve until it is
+                        hi[k] /= 2
+                        cur[k] = hi[k]
+                        phase[k] = 2
+                        continue
+                    phase[k] = 3                 # doubling ended: bisect [l, r]
+                elif ph == 2:
+                    if not ok:
+                        hi[k] /= 2
+                        cur[k] = hi[k]
+                        continue
+                    lo[k], hi[k] = hi[k], hi[k] * 2
+                    phase[k] = 3
+                else:                            # one bisection step
+                    if ok:
+                        lo[k] = cur[k]
+                    else:
+                        hi[k] = cur[k]
+                    step[k] += 1
+                if phase[k] == 3:
+                    if step[k] >= self.iters:
+                        phase[k] = 4
+                    else:
+                        cur[k] = (lo[k] + hi[k]) / 2
+        out, k = [], 0
+        for s in range(N):
+            out.append({tuple(q): float(lo[k + j]) for j, q in enumerate(pairs[s])})
+            k += len(pairs[s])
+        return out, max_eps

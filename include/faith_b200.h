@@ -44,8 +44,9 @@ enum fb_status {
 enum fb_norm { FB_P1 = 1, FB_P2 = 2, FB_PINF = 3 };
 enum fb_layout { FB_NATIVE = 0 /* [rows, Di, Do] */, FB_TRANSPOSED = 1 /* [rows, Do, Di] */ };
 
-/* Relaxation selector of fb_relax_f32. */
-enum fb_relax_op { FB_RELU = 0, FB_TANH = 1, FB_EXP = 2, FB_RECIPROCAL = 3 };
+/* Relaxation selector of fb_relax_f32.  FB_INTERVAL added to an operator selects its interval form (the
+ * reference's `ibp` branches: constant bounds, zero weights). */
+enum fb_relax_op { FB_RELU = 0, FB_TANH = 1, FB_EXP = 2, FB_RECIPROCAL = 3, FB_SQR = 4, FB_SQRT = 5, FB_INTERVAL = 8 };
 
 const char* fb_status_string(int status);
 /* cudaError_t (as int) of the most recent FB_ERR_CUDA on the calling thread. */
@@ -65,10 +66,15 @@ int fb_concretize_f32(const float* lw, const float* uw, const float* lb, const f
  *   op = FB_TANH        Bounds.ori_tanh  (Bounds.py:1027-1103); kernel.cpp:101-131 c_tanh_verification
  *   op = FB_EXP         Bounds.exp       (Bounds.py:970-1003)
  *   op = FB_RECIPROCAL  Bounds.reciprocal (Bounds.py:1136-1161)
+ *   op = FB_SQR         Bounds.sqr        (Bounds.py:860-890)
+ *   op = FB_SQRT        Bounds.sqrt       (Bounds.py:892-919)
+ *   op + FB_INTERVAL    the `ibp` branch of the same operator (Bounds.py:863-866, 896-898, 924-926, 973-975,
+ *                       1030-1032, 1139-1143): out_lb / out_ub are the images of the concretised range, out_lw and
+ *                       out_uw are zero
  * Outputs have the shape and layout of the inputs and must not alias them.
  * `violation` (device int, may be NULL) is set to 1 by FB_RECIPROCAL when some concretised
- * lower bound is below 1e-12, the condition the reference asserts on (Bounds.py:1147); the
- * caller zeroes it beforehand. */
+ * lower bound is below 1e-12, the condition the reference asserts on (Bounds.py:1147), and by FB_SQRT
+ * (both forms) when some lower bound is not positive (Bounds.py:894); the caller zeroes it beforehand. */
 int fb_relax_f32(int op,
                  const float* lw, const float* uw, const float* lb, const float* ub,
                  float* out_lw, float* out_uw, float* out_lb, float* out_ub,
@@ -288,6 +294,22 @@ int fb_add_f32(const float* x_lw, const float* x_uw, const float* x_lb, const fl
 int fb_scale_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
                  float* z_lw, float* z_uw, float* z_lb, float* z_ub,
                  int64_t rows, int Di, int Do, float c, void* stream);
+
+/* Multiplication by a constant vector over the feature axis, split by sign (Bounds.multiply with a tensor,
+ * Bounds.py:653-664; the gain of a layer norm): z_l = x_l w+ + x_u w-, z_u = x_l w- + x_u w+ on the weights and on
+ * the bias terms.  w [Do].  z may alias x. */
+int fb_mul_features_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+                        const float* w, float* z_lw, float* z_uw, float* z_lb, float* z_ub,
+                        int64_t rows, int Di, int Do, void* stream);
+
+/* Interval arithmetic of the reference's `ibp` mode, where a bound is a box [lb, ub] with zero weights:
+ * elementwise product of two boxes (Bounds.get_bounds_xy, Bounds.py:667-678, inside Bounds.multiply) over n
+ * elements, and the dot product z[b,i,j] = sum_k [x[b,i,k]] * [y[b,j,k]] of two boxes (the dim_in == 1 branch of
+ * Bounds.dot_product, Bounds.py:711-721): x [B, Lx, K], y [B, Ly, K], z [B, Lx, Ly]. */
+int fb_interval_mul_f32(const float* x_l, const float* x_u, const float* y_l, const float* y_u,
+                        float* z_l, float* z_u, int64_t n, void* stream);
+int fb_interval_dot_f32(const float* x_l, const float* x_u, const float* y_l, const float* y_u,
+                        float* z_l, float* z_u, int B, int Lx, int Ly, int K, void* stream);
 
 /* Sum over the feature axis, broadcast back to every feature: the denominator of the softmax
  * (Bounds.softmax, Bounds.py:1007-1013).  Shapes as the input. */

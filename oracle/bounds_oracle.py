@@ -39,16 +39,37 @@ def dual_exponent(p):
 
 
 class OBounds:
-    def __init__(self, p, eps, lw, lb, uw, ub, words=1):
+    def __init__(self, p, eps, lw, lb, uw, ub, words=1, ibp=False):
         self.p = float(p)
         self.q = dual_exponent(self.p)
         self.eps = eps
         self.words = words
+        # interval mode (`--method ibp`): every operator takes its interval branch and the weight tensors are
+        # cut down to `words` rows (Bounds.py:274, 285-288)
+        self.ibp = ibp
+        if ibp:
+            lw, uw = lw[:, :, :words, :], uw[:, :, :words, :]
         self.lw, self.lb, self.uw, self.ub = lw, lb, uw, ub
 
     # ------------------------------------------------------------------ helpers
     def like(self, lw, lb, uw, ub):
-        return OBounds(self.p, self.eps, lw, lb, uw, ub, self.words)
+        return OBounds(self.p, self.eps, lw, lb, uw, ub, self.words, self.ibp)
+
+    def _box(self, lb, ub):
+        """Result of an interval branch: constant bounds, zero weights."""
+        return self.like(torch.zeros_like(self.lw), lb, torch.zeros_like(self.uw), ub)
+
+    def _line(self, mask, k, x0, y0, lower):
+        """One call of add_linear (Bounds.py:362-381): mask * (line of slope k through (x0, y0) applied to this bound),
+        for the lower (lower=True) or upper output; a positive slope keeps the side, any other swaps it."""
+        dt = k.dtype
+        own_w, own_b, oth_w, oth_b = (self.lw, self.lb, self.uw, self.ub) if lower else (self.uw, self.ub, self.lw, self.lb)
+        kp = (k > 0).to(dt)
+        w = mask.unsqueeze(2) * kp.unsqueeze(2) * own_w * k.unsqueeze(2)
+        b = mask * kp * ((own_b - x0) * k + y0)
+        w = w + mask.unsqueeze(2) * (1 - kp).unsqueeze(2) * oth_w * k.unsqueeze(2)
+        b = b + mask * (1 - kp) * ((oth_b - x0) * k + y0)
+        return w, b
 
     @property
     def shape(self):
@@ -127,6 +148,8 @@ class OBounds:
         crossing columns get the chord through (l, 0) above and slope [|u| > |l|] below."""
         l, u = self.concretize()
         dt = l.dtype
+        if self.ibp:  # Bounds.py:924-926
+            return self._box(torch.clamp(l, min=0), torch.clamp(u, min=0))
         pos = (l > 0).to(dt)
         neg = (u < 0).to(dt)
         both = 1 - pos - neg
@@ -155,6 +178,8 @@ class OBounds:
         point whose tangent passes through the far end point."""
         l, u = self.concretize()
         dt = l.dtype
+        if self.ibp:  # Bounds.py:1030-1032
+            return self._box(torch.tanh(l), torch.tanh(u))
         pos = (l > 0).to(dt)
         neg = (u < 0).to(dt)
         both = 1 - pos - neg
@@ -213,6 +238,8 @@ class OBounds:
         positive); upper: chord.  Above 12 the exponential is continued linearly."""
         l, u = self.concretize()
         dt = l.dtype
+        if self.ibp:  # Bounds.py:973-975
+            return self._box(torch.exp(l), torch.exp(u))
         thres = torch.tensor(12.0, dtype=dt)
 
         def exp_capped(x):
@@ -229,6 +256,8 @@ class OBounds:
         """Bounds.py:1136-1161.  Input must be positive.  Lower: tangent at the midpoint;
         upper: chord.  Both slopes are negative, so each output line uses the opposite input."""
         l, u = self.concretize()
+        if self.ibp:  # Bounds.py:1139-1143 (no positivity check in this branch)
+            return self._box(1.0 / u, 1.0 / l)
         if not bool(torch.min(l) >= GUARD):
             raise AssertionError("reciprocal of a bound that is not strictly positive")
         m = (l + u) / 2
@@ -237,10 +266,48 @@ class OBounds:
         return self.like(self.uw * kl.unsqueeze(2), self.ub * kl + 2 / m,
                          self.lw * ku.unsqueeze(2), self.lb * ku - ku * l + 1 / l)
 
+    def sqr(self):
+        """Bounds.py:860-890.  Upper: the chord; lower: a tangent placed so that it never goes negative on the
+        range (one-sided columns), zero for columns whose range crosses zero."""
+        l, u = self.concretize()
+        dt = l.dtype
+        pos = (l > 0).to(dt)
+        neg = (u < 0).to(dt)
+        both = 1 - pos - neg
+        if self.ibp:
+            lo = torch.min(l * l, u * u)
+            return self._box(lo - both * lo, torch.max(l * l, u * u))
+        one = torch.ones_like(l)
+        uw, ub = self._line(one, u + l, l, l.pow(2), lower=False)
+        m = torch.max((l + u) / 2, 2 * u)
+        w1, b1 = self._line(neg, 2 * m, m, m.pow(2), lower=True)
+        m = torch.min((l + u) / 2, 2 * l)
+        w2, b2 = self._line(pos, 2 * m, m, m.pow(2), lower=True)
+        return self.like(w1 + w2, b1 + b2, uw, ub)
+
+    def sqrt(self):
+        """Bounds.py:892-919.  Input must be positive.  Lower: the chord; upper: the tangent at the midpoint."""
+        l, u = self.concretize()
+        if not bool(torch.min(l) > 0):
+            raise AssertionError("square root of a bound that is not strictly positive")
+        if self.ibp:
+            return self._box(torch.sqrt(l), torch.sqrt(u))
+        one = torch.ones_like(l)
+        k = (torch.sqrt(u) - torch.sqrt(l)) / (u - l + GUARD)
+        lw, lb = self._line(one, k, l, torch.sqrt(l), lower=True)
+        m = (l + u) / 2
+        uw, ub = self._line(one, 0.5 / torch.sqrt(m), m, torch.sqrt(m), lower=False)
+        return self.like(lw, lb, uw, ub)
+
     # --------------------------------------------------- two-input relaxations
     def mul_bounds(self, other):
         """Elementwise product of two bounded quantities, McCormick planes through
         (l_x, l_y) below and (l_x, u_y) above (Bounds.py:608-651, 680-688)."""
+        if self.ibp:  # get_bounds_xy in interval mode: the planes are the constants min / max of the corner products
+            la, ua = self.concretize()
+            lo, uo = other.concretize()
+            p1, p2, p3, p4 = la * lo, la * uo, ua * lo, ua * uo
+            return self._box(torch.min(p1, torch.min(p2, torch.min(p3, p4))), torch.max(p1, torch.max(p2, torch.max(p3, p4))))
         la, _ = self.concretize()
         lo, uo = other.concretize()
         dt = la.dtype
@@ -282,14 +349,17 @@ class OBounds:
         picks the operand line by its sign, and the constant -alpha*beta is summed over k."""
         B, Lx, Di, K = self.lw.shape
         Ly = other.lw.shape[1]
-        if Di == 1:  # interval product, no symbolic part (Bounds.py:711-721)
+        if Di == 1 or self.ibp:
+            # interval product, no symbolic part (Bounds.py:711-721).  In interval mode with two perturbed words the
+            # reference takes its general path, whose planes are then the same constants (alpha = beta = 0,
+            # gamma = min / max of the corner products, :667-678) and whose ranges equal lb, ub (zero weights).
             l1, u1 = self.lb.unsqueeze(-2), self.ub.unsqueeze(-2)
             l2, u2 = other.lb.unsqueeze(1), other.ub.unsqueeze(1)
             p1, p2, p3, p4 = l1 * l2, l1 * u2, u1 * l2, u1 * u2
             lo = torch.min(torch.min(p1, p2), torch.min(p3, p4)).sum(-1)
             hi = torch.max(torch.max(p1, p2), torch.max(p3, p4)).sum(-1)
-            w = lo.unsqueeze(-2) * 0
-            return self.like(w, lo, w, hi)
+            w = (lo.unsqueeze(-2) * 0).expand(B, Lx, Di, Ly).clone()
+            return self.like(w, lo, w.clone(), hi)
         lx, _ = self.concretize()
         ly, uy = other.concretize()
         dt = lx.dtype
@@ -340,15 +410,19 @@ class OBounds:
 
     # --------------------------------------------------------------- layer norm
     def layer_norm(self, gamma, beta, mode="no_var"):
-        """Bounds.py:1111-1131 for mode "no" and "no_var": subtract the feature mean (the mean
-        of the *other* line, because of the minus sign), scale by gamma, add beta."""
+        """Bounds.py:1111-1131: subtract the feature mean (the mean of the *other* line, because of the minus
+        sign); mode "standard" divides by the root of the variance (mean of the relaxed squares plus 1e-12);
+        scale by gamma, add beta."""
         if mode == "no":
             return self
-        if mode != "no_var":
-            raise NotImplementedError("only layer_norm in {'no', 'no_var'}")
+        if mode not in ("no_var", "standard"):
+            raise NotImplementedError("layer_norm mode %r" % (mode,))
         do = self.lw.shape[-1]
-        avg = torch.ones((do, do), dtype=self.lw.dtype) * (1.0 / do)
+        avg = torch.ones((do, do), dtype=self.lw.dtype, device=self.lw.device) * (1.0 / do)
         centred = self.add(self.matmul(avg).scale(-1.0))
+        if mode == "standard":
+            variance = centred.sqr().matmul(avg)
+            centred = centred.divide(variance.add(GUARD).sqrt())
         return centred.mul_tensor(gamma).add(beta)
 
 
@@ -424,18 +498,24 @@ def merge_heads(x, heads):
     return x.like(w(x.lw), b(x.lb), w(x.uw), b(x.ub))
 
 
-def input_bounds(emb, positions, p, eps):
-    """Bounds of the embedding output: identity dependence on the perturbed word(s)
-    (VerifierForward.py:127-152).  emb [B, L, D]; positions: list of token indices."""
+def input_bounds(emb, positions, p, eps, ibp=False):
+    """Bounds of the embedding output: identity dependence on the perturbed word(s), or in interval mode the box
+    of radius eps around the perturbed rows with zero weights (VerifierForward.py:127-152).
+    emb [B, L, D]; positions: list of token indices."""
     B, L, D = emb.shape
     words = len(positions)
     lw = torch.zeros(B, L, D * words, D, dtype=emb.dtype)
+    lb, ub = emb.clone(), emb.clone()
     for i, pos in enumerate(positions):
-        lw[:, pos, D * i:D * (i + 1), :] = torch.eye(D, dtype=emb.dtype)
-    return OBounds(p, eps, lw, emb.clone(), lw.clone(), emb.clone(), words)
+        if ibp:
+            lb[:, pos] -= eps
+            ub[:, pos] += eps
+        else:
+            lw[:, pos, D * i:D * (i + 1), :] = torch.eye(D, dtype=emb.dtype)
+    return OBounds(p, eps, lw, lb, lw.clone(), ub, words, ibp)
 
 
-def encoder_forward(model, emb, positions, p, eps, trace=None):
+def encoder_forward(model, emb, positions, p, eps, trace=None, ibp=False):
     """One forward bound pass of a BERT-style encoder (VerifierForward.py:93-119 without the
     `check` calls and the epsilon search).  `model` is a dict of tensors:
 
@@ -453,7 +533,7 @@ def encoder_forward(model, emb, positions, p, eps, trace=None):
             trace.append((name, b))
         return b
 
-    x = input_bounds(emb, positions, p, eps).layer_norm(model["emb_ln_g"], model["emb_ln_b"], ln)
+    x = input_bounds(emb, positions, p, eps, ibp).layer_norm(model["emb_ln_g"], model["emb_ln_b"], ln)
     rec("embedding", x)
     for i, ly in enumerate(model["layers"]):
         q = split_heads(x.dense(ly["q_w"], ly["q_b"]), heads)
@@ -485,7 +565,10 @@ def concrete_forward(model, emb):
     def norm(t, g, b):
         if ln == "no":
             return t
-        return (t - t.mean(-1, keepdim=True)) * g + b
+        c = t - t.mean(-1, keepdim=True)
+        if ln == "standard":
+            c = c / torch.sqrt((c * c).mean(-1, keepdim=True) + GUARD)
+        return c * g + b
 
     x = norm(emb, model["emb_ln_g"], model["emb_ln_b"])
     N, L, D = x.shape
@@ -614,3 +697,47 @@ def epsilon_search(model, emb_one, label, p, max_eps, iters, positions=None):
                 hi = m
         out[int(i)] = lo
     return out
+
+
+def epsilon_search_pairs(model, emb_one, label, p, max_eps, iters, pairs=None, warm_up=True):
+    """The same search with two perturbed words (Verifiers/Verifier.py:149-201): warm max_eps up on the pair (1, 2)
+    (halve until certified, double until not), then per pair of positions double the radius while certified, or halve it
+    until certified, and bisect `iters` times from there.  Returns ({(i1, i2): eps}, max_eps after the warm-up)."""
+    L = emb_one.shape[1]
+
+    def safe(pos, eps):
+        try:
+            l, u = encoder_forward(model, emb_one, list(pos), p, eps)
+        except AssertionError:   # a failed assertion inside the pass counts as "not certified" (VerifierForward.py:120-125)
+            return False
+        return bool(l[0] > 0) if label == 0 else bool(u[0] < 0)
+
+    max_eps = float(max_eps)
+    if warm_up:
+        while not safe((1, 2), max_eps):
+            max_eps /= 2
+        while safe((1, 2), max_eps):
+            max_eps *= 2
+    if pairs is None:
+        pairs = [(a, b) for a in range(1, L - 1) for b in range(a + 1, L - 1)]
+    out = {}
+    for pr in pairs:
+        lo, hi = 0.0, max_eps
+        ok = safe(pr, hi)
+        while ok:
+            lo = hi
+            hi *= 2
+            ok = safe(pr, hi)
+        if lo == 0:
+            while not ok:
+                hi /= 2
+                ok = safe(pr, hi)
+            lo, hi = hi, hi * 2
+        for _ in range(iters):
+            m = (lo + hi) / 2
+            if safe(pr, m):
+                lo = m
+            else:
+                hi = m
+        out[tuple(pr)] = lo
+    return out, max_eps

@@ -126,7 +126,7 @@ def load_reference_verifier():
     return vf_mod.VerifierForward
 
 
-def build_reference_verifier(model, p, perturbed_words=1, device="cpu"):
+def build_reference_verifier(model, p, perturbed_words=1, device="cpu", method="forward"):
     """A reference VerifierForward wired to a stand-in encoder built from an oracle model
     dict (see oracle.bounds_oracle.make_encoder).  Only the attributes the forward bound
     pass reads are provided (Verifier.py:11-34, VerifierForward.py:15-20,199-204).
@@ -155,10 +155,10 @@ def build_reference_verifier(model, p, perturbed_words=1, device="cpu"):
             intermediate=types.SimpleNamespace(dense=lin(ly["f1_w"], ly["f1_b"])),
             output=types.SimpleNamespace(dense=lin(ly["f2_w"], ly["f2_b"]), LayerNorm=ln(ly["ln2_g"], ly["ln2_b"]))))
     v = VF.__new__(VF)
-    v.args = make_args(p=p, perturbed_words=perturbed_words)
+    v.args = make_args(p=p, perturbed_words=perturbed_words, method=method)
     v.device = device
     v.p = p
-    v.ibp = False
+    v.ibp = method == "ibp"
     v.debug = False
     v.verbose = False
     v.perturbed_words = perturbed_words
@@ -217,8 +217,9 @@ def _reference_encoder_pass(verifier, emb_one, index, eps):
 
 
 def reference_epsilon_search(verifier, emb_one, label, max_eps, num_iters):
-    """Runs the reference's own search loop, Verifier.verify (Verifier.py:62-208, one perturbed word), unchanged
-    for one sentence (emb_one [1, L, D]) and returns {position: eps}.  The loop asks its `target` for the
+    """Runs the reference's own search loop, Verifier.verify (Verifier.py:62-208), unchanged for one sentence
+    (emb_one [1, L, D]) and returns {position: eps}, or {(i1, i2): eps} when the verifier perturbs two words (its
+    max_eps is then warmed up first, :150-157, and left in verifier.max_eps).  The loop asks its `target` for the
     embeddings, the tokens and the concrete activations (`std`) that `check` compares the bounds with; check
     never asserts (utils.py:30 is commented out), so the stand-in target hands out zeros of the right shapes."""
     import contextlib
@@ -240,6 +241,7 @@ def reference_epsilon_search(verifier, emb_one, label, max_eps, num_iters):
                                             step=lambda examples: [std])
     verifier.logger = types.SimpleNamespace(write=lambda *a, **k: None)
     verifier.max_eps = max_eps
+    verifier.warmed = False
     verifier.num_verify_iters = num_iters
     verifier.eps = max_eps
     verifier.debug_pos = 1
@@ -247,4 +249,6 @@ def reference_epsilon_search(verifier, emb_one, label, max_eps, num_iters):
     verifier.res = os.devnull
     with contextlib.redirect_stdout(io.StringIO()):
         result, _avg, _min = verifier.verify({"label": label})
-    return {int(b["position"]): float(b["eps"]) for b in result["bounds"]}
+    def key(pos):
+        return tuple(int(i) for i in pos) if isinstance(pos, (tuple, list)) else int(pos)
+    return {key(b["position"]): float(b["eps"]) for b in result["bounds"]}

@@ -27,7 +27,7 @@ import ref_loader  # noqa: E402
 
 def run_reference_op(c):
     mod = ref_loader.load_reference_bounds()
-    args = ref_loader.make_args(p=c["p"], perturbed_words=c["words"])
+    args = ref_loader.make_args(p=c["p"], perturbed_words=c["words"], method="ibp" if c.get("ibp") else "forward")
     (lw, lb, uw, ub), ex = cases.case_inputs(c)
 
     def mk(t):
@@ -65,6 +65,15 @@ def run_reference_op(c):
     elif op == "layer_norm":
         import types
         r = x.layer_norm(types.SimpleNamespace(weight=ex["W"], bias=ex["bias"]), "no_var")
+    elif op == "layer_norm_std":
+        import types
+        r = x.layer_norm(types.SimpleNamespace(weight=ex["W"], bias=ex["bias"]), "standard")
+    elif op == "mul_tensor":
+        r = x.multiply(ex["W"])
+    elif op == "sqr":
+        r = x.sqr()
+    elif op == "sqrt":
+        r = x.sqrt()
     elif op == "scale":
         r = x.multiply(c["c"])
     elif op == "add":
@@ -80,6 +89,8 @@ def main():
     torch.set_num_threads(1)  # one summation order, whatever machine generates the files
     out = {}
     for name, c in cases.OP_CASES.items():
+        if not c.get("golden", True):
+            continue
         for k, v in run_reference_op(c).items():
             out["%s/%s" % (name, k)] = v.detach().contiguous().numpy().astype(np.float32)
     np.savez_compressed(os.path.join(HERE, "ops.npz"), **out)
@@ -115,6 +126,14 @@ def main():
         r = ref_loader.reference_epsilon_search(ver, emb[s:s + 1], int(srch["labels"][s]), sc["max_eps"], sc["iters"])
         srch["s%d/positions" % s] = np.array(sorted(r), dtype=np.int64)
         srch["s%d/eps" % s] = np.array([r[i] for i in sorted(r)], dtype=np.float64)
+    # two perturbed words: warm-up of max_eps, doubling / halving, bisection (Verifier.py:149-201)
+    ver2 = ref_loader.build_reference_verifier(model, sc["p"], perturbed_words=2)
+    for s in range(sc["B"]):
+        r = ref_loader.reference_epsilon_search(ver2, emb[s:s + 1], int(srch["labels"][s]), sc["max_eps"], sc["iters2"])
+        keys = sorted(r)
+        srch["s%d/pairs" % s] = np.array(keys, dtype=np.int64)
+        srch["s%d/pair_eps" % s] = np.array([r[k] for k in keys], dtype=np.float64)
+        srch["s%d/warmed_max_eps" % s] = np.array(ver2.max_eps, dtype=np.float64)
     np.savez_compressed(os.path.join(HERE, "search.npz"), **srch)
     print("wrote ops.npz (%d arrays), encoder.npz (%d arrays) and search.npz (%d arrays)" % (len(out), len(enc), len(srch)))
 

@@ -20,7 +20,8 @@ def load_golden(name):
 
 
 def oracle_bounds(c, t, dtype=torch.float32):
-    return O.OBounds(c["p"], c["eps"], t[0].to(dtype), t[1].to(dtype), t[2].to(dtype), t[3].to(dtype), c["words"])
+    return O.OBounds(c["p"], c["eps"], t[0].to(dtype), t[1].to(dtype), t[2].to(dtype), t[3].to(dtype), c["words"],
+                     c.get("ibp", False))
 
 
 def run_oracle_op(c, dtype=torch.float32):
@@ -53,6 +54,14 @@ def run_oracle_op(c, dtype=torch.float32):
         r = x.softmax()
     elif op == "layer_norm":
         r = x.layer_norm(ex["W"].to(dtype), ex["bias"].to(dtype), "no_var")
+    elif op == "layer_norm_std":
+        r = x.layer_norm(ex["W"].to(dtype), ex["bias"].to(dtype), "standard")
+    elif op == "mul_tensor":
+        r = x.mul_tensor(ex["W"].to(dtype))
+    elif op == "sqr":
+        r = x.sqr()
+    elif op == "sqrt":
+        r = x.sqrt()
     elif op == "scale":
         r = x.scale(c["c"])
     elif op == "add":

@@ -221,3 +221,27 @@ def test_batched_search_reproduces_the_reference_radii():
     assert same >= n - 1, "%d of %d radii differ from the reference" % (n - same, n)
     # 12 words x (1 + 8) probes = 108 verify_safety calls of the reference, here 9 rounds of 2 calls (8 instances each)
     assert srch.instances == n * (sc["iters"] + 1) and srch.passes == (sc["iters"] + 1) * 2
+
+
+def test_batched_two_word_search_reproduces_the_reference_radii():
+    """Two perturbed words (Verifier.py:149-201): warm-up of max_eps, then per pair doubling / halving and bisection,
+    every pair with its own state machine and one driver call per round for all unfinished pairs."""
+    import faith_b200
+    from faith_b200.search import EpsilonSearch
+    c = cases.SEARCH_CASE
+    model = O.make_encoder(c["seed"], c["layers"], c["d_model"], c["heads"], c["ffn"], c["std"])
+    emb = cases.encoder_inputs(c)
+    g = helpers.load_golden("search.npz")
+    ver = faith_b200.EncoderVerifier(model, DEV)
+    step_floor = 2.0 ** -c["iters2"]
+    for s in range(c["B"]):   # the reference warms max_eps up per verifier; the golden file used a fresh one per sentence
+        srch = EpsilonSearch(ver, c["p"], c["max_eps"], c["iters2"], max_instances=16)
+        got, warmed = srch.run_pairs(emb[s:s + 1].to(DEV), torch.as_tensor(g["labels"][s:s + 1]))
+        assert warmed == float(g["s%d/warmed_max_eps" % s])
+        pairs = [tuple(int(v) for v in q) for q in g["s%d/pairs" % s]]
+        assert sorted(got[0]) == pairs
+        diff = 0
+        for q, e in zip(pairs, g["s%d/pair_eps" % s]):
+            diff += np.float32(got[0][q]) != np.float32(e)
+            assert abs(got[0][q] - float(e)) <= 2.001 * step_floor * max(float(e), warmed), (s, q, got[0][q], float(e))
+        assert diff <= 1, "%d of %d radii differ from the reference" % (diff, len(pairs))

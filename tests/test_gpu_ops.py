@@ -15,7 +15,8 @@ DEV = "cuda:0"
 
 def gpu_bounds(c, t):
     import faith_b200
-    return faith_b200.BoundsLite(c["p"], c["eps"], t[0].to(DEV), t[1].to(DEV), t[2].to(DEV), t[3].to(DEV), c["words"])
+    return faith_b200.BoundsLite(c["p"], c["eps"], t[0].to(DEV), t[1].to(DEV), t[2].to(DEV), t[3].to(DEV), c["words"],
+                                 ibp=c.get("ibp", False))
 
 
 def run_gpu_op(c):
@@ -26,7 +27,7 @@ def run_gpu_op(c):
     if op == "concretize":
         l, u = x.concretize()
         return {"l": l, "u": u}
-    if op in ("relu", "tanh", "exp", "reciprocal", "softmax"):
+    if op in ("relu", "tanh", "exp", "reciprocal", "softmax", "sqr", "sqrt"):
         r = getattr(x, op)()
     elif op == "matmul":
         r = x.matmul(ex["W"].to(DEV))
@@ -40,6 +41,10 @@ def run_gpu_op(c):
         r = x.multiply(gpu_bounds(c, ex["y"]))
     elif op == "layer_norm":
         r = x.layer_norm(types.SimpleNamespace(weight=ex["W"].to(DEV), bias=ex["bias"].to(DEV)), "no_var")
+    elif op == "layer_norm_std":
+        r = x.layer_norm(types.SimpleNamespace(weight=ex["W"].to(DEV), bias=ex["bias"].to(DEV)), "standard")
+    elif op == "mul_tensor":
+        r = x.multiply(ex["W"].to(DEV))
     elif op == "scale":
         r = x.multiply(c["c"])
     elif op == "add":
@@ -61,7 +66,8 @@ def test_op_matches_oracle_and_golden(name, golden_ops):
     ref = helpers.run_oracle_op(c)
     for k in ref:
         helpers.assert_close(got[k], ref[k], "%s/%s vs oracle" % (name, k))
-        helpers.assert_close(got[k], golden_ops["%s/%s" % (name, k)], "%s/%s vs golden" % (name, k))
+        if c.get("golden", True):
+            helpers.assert_close(got[k], golden_ops["%s/%s" % (name, k)], "%s/%s vs golden" % (name, k))
 
 
 def _pair(seed, B, L, Di, Do, p, eps, words, shift=-0.7, wscale=0.2):
@@ -760,3 +766,35 @@ def test_tensor_core_give_up_path_reports_a_timeout_and_leaves_the_gpu_usable():
     assert lib.fb_tc_check() == 0
     ref_l = lw.double() @ W.double().clamp(min=0).t() + uw.double() @ W.double().clamp(max=0).t()
     assert float((got[0].double() - ref_l).abs().max()) < 1e-4
+
+
+# ------------------------------------------------------------------------------------------------
+# Interval mode against the reference itself, live on the GPU: its interval relu and its interval products move
+# constants to the device with .cuda() (Bounds.py:925, :676), so those branches only run where there is a GPU.
+@pytest.mark.parametrize("name", sorted(n for n, c in cases.OP_CASES.items() if not c.get("golden", True)))
+def test_interval_mode_matches_the_reference_on_the_gpu(name):
+    import os
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), os.pardir, "oracle"))
+    import reference_loader
+    if not reference_loader.reference_available():
+        pytest.skip("reference modules not staged")
+    mod = reference_loader.load_reference_bounds()
+    c = cases.OP_CASES[name]
+    args = reference_loader.make_args(p=c["p"], perturbed_words=c["words"], method="ibp")
+    x_t, ex = cases.case_inputs(c)
+
+    def mk(t):
+        return mod.Bounds(args, c["p"], c["eps"], lw=t[0].to(DEV), lb=t[1].to(DEV), uw=t[2].to(DEV), ub=t[3].to(DEV))
+
+    x = mk(x_t)
+    op = c["op"]
+    if op == "dot":
+        ref = x.dot_product(mk(ex["y"]))
+    elif op == "mul_bounds":
+        ref = x.multiply(mk(ex["y"]))
+    else:
+        ref = getattr(x, op)()
+    got = run_gpu_op(c)
+    for k in ("lw", "uw", "lb", "ub"):
+        helpers.assert_close(got[k], getattr(ref, k), "%s/%s vs the reference on the GPU" % (name, k))

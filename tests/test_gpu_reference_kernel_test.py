@@ -123,10 +123,10 @@ def test_reference_dot_product_V_test(batch, length, dim_in, dim_out):
 # the GPU through the C ABI, while the control flow, the head split and merge (:208-229, :253-265) and the
 # classifier fold (:289-292) are the reference's own code.
 
-def _verifier_pass(model, emb, positions, p, eps):
+def _verifier_pass(model, emb, positions, p, eps, method="forward"):
     import faith_b200
     words = len(positions)
-    ver = reference_loader.build_reference_verifier(model, p, perturbed_words=words, device=DEV)
+    ver = reference_loader.build_reference_verifier(model, p, perturbed_words=words, device=DEV, method=method)
     index = positions[0] if words == 1 else positions
     out = []
     for s in range(emb.shape[0]):
@@ -196,3 +196,26 @@ def test_reference_verifier_on_the_headline_model():
     assert int(viol.item()) == 0
     _noise_ok(dl.reshape(1), l32.reshape(1), l64.reshape(1), "driver logit lower")
     _noise_ok(du.reshape(1), u32.reshape(1), u64.reshape(1), "driver logit upper")
+
+
+@pytest.mark.parametrize("method,layer_norm,positions", [("forward", "standard", [1]), ("ibp", "no_var", [1]),
+                                                         ("ibp", "standard", [1, 2])])
+def test_reference_verifier_other_modes_on_the_gpu_operators(method, layer_norm, positions):
+    """The other configurations of the reference verifier, unchanged on faith_b200.Bounds: layer_norm="standard"
+    (variance through sqr / sqrt / divide, Bounds.py:1122-1124) and interval mode (--method ibp, every operator's
+    interval branch), against the oracle and by containment of the unperturbed forward pass."""
+    sys.path.insert(0, os.path.join(HERE, "golden"))
+    import cases
+    c = dict(cases.ENCODER_CASE, std=0.02, eps=1e-3)
+    p = float("inf")
+    model = O.make_encoder(c["seed"], c["layers"], c["d_model"], c["heads"], c["ffn"], c["std"], layer_norm=layer_norm)
+    emb = cases.encoder_inputs(c)
+    res = _verifier_pass(model, emb, positions, p, c["eps"], method=method)
+    ibp = method == "ibp"
+    l32, u32 = O.encoder_forward(model, emb, positions, p, c["eps"], ibp=ibp)
+    l64, u64 = O.encoder_forward(O.model_to(model, torch.float64), emb.double(), positions, p, c["eps"], ibp=ibp)
+    y = O.concrete_forward(model, emb)
+    for s, (l, u, _) in enumerate(res):
+        _noise_ok(l.reshape(1), l32[s:s + 1], l64[s:s + 1], "logit lower", floor=1e-6)
+        _noise_ok(u.reshape(1), u32[s:s + 1], u64[s:s + 1], "logit upper", floor=1e-6)
+        assert float(l) - 1e-6 <= float(y[s]) <= float(u) + 1e-6

@@ -14,7 +14,7 @@ def golden_ops():
     return helpers.load_golden("ops.npz")
 
 
-@pytest.mark.parametrize("name", sorted(cases.OP_CASES))
+@pytest.mark.parametrize("name", sorted(n for n, c in cases.OP_CASES.items() if c.get("golden", True)))
 def test_op_matches_golden(name, golden_ops):
     torch.set_num_threads(1)
     out = helpers.run_oracle_op(cases.OP_CASES[name])
@@ -105,3 +105,18 @@ def test_oracle_search_loop_matches_the_reference_verifier():
             same += np.float32(got[int(i)]) == np.float32(e)
             assert abs(got[int(i)] - float(e)) <= 2.001 * sc["max_eps"] / 2 ** sc["iters"], (s, int(i), got[int(i)], float(e))
     assert same >= n - 1, "%d of %d radii differ from the reference" % (n - same, n)
+
+
+def test_oracle_two_word_search_matches_the_reference_verifier():
+    """Two perturbed words (Verifier.py:149-201): the warmed-up max_eps and the radius per pair of positions of the
+    first sentence, against what the reference's own loop found."""
+    c = cases.SEARCH_CASE
+    model = O.make_encoder(c["seed"], c["layers"], c["d_model"], c["heads"], c["ffn"], c["std"])
+    emb = cases.encoder_inputs(c)
+    g = helpers.load_golden("search.npz")
+    got, warmed = O.epsilon_search_pairs(model, emb[:1], int(g["labels"][0]), c["p"], c["max_eps"], c["iters2"])
+    assert warmed == float(g["s0/warmed_max_eps"])
+    pairs = [tuple(int(v) for v in q) for q in g["s0/pairs"]]
+    assert sorted(got) == pairs
+    diff = [q for q, e in zip(pairs, g["s0/pair_eps"]) if np.float32(got[q]) != np.float32(e)]
+    assert len(diff) <= 1, diff

@@ -6,11 +6,12 @@ import torch
 import cases
 import helpers
 import ref_loader
+from oracle import bounds_oracle as O
 
 pytestmark = pytest.mark.skipif(not ref_loader.reference_available(), reason="reference checkout not present")
 
 
-@pytest.mark.parametrize("name", sorted(cases.OP_CASES))
+@pytest.mark.parametrize("name", sorted(n for n, c in cases.OP_CASES.items() if c.get("golden", True)))
 def test_op_matches_reference(name):
     import make_golden
     torch.set_num_threads(1)
@@ -71,3 +72,20 @@ def test_encoder_pass_matches_reference():
         rl, ru, _ = ref_loader.reference_encoder_pass(ver, emb[s:s + 1], c["index"], c["eps"])
         helpers.assert_within_noise(l[s], rl, l64[s], "l")
         helpers.assert_within_noise(u[s], ru, u64[s], "u")
+
+
+def test_encoder_pass_with_standard_layer_norm_matches_reference():
+    """layer_norm="standard" (Bounds.py:1122-1124: variance through sqr, division through sqrt and reciprocal) over a
+    whole pass of the reference's VerifierForward, against the oracle."""
+    c = dict(cases.ENCODER_CASE, std=0.02, eps=1e-3)
+    model = O.make_encoder(c["seed"], c["layers"], c["d_model"], c["heads"], c["ffn"], c["std"], layer_norm="standard")
+    emb = cases.encoder_inputs(c)
+    ver = ref_loader.build_reference_verifier(model, c["p"])
+    l, u = O.encoder_forward(model, emb, [c["index"]], c["p"], c["eps"])
+    l64, u64 = O.encoder_forward(O.model_to(model, torch.float64), emb.double(), [c["index"]], c["p"], c["eps"])
+    y = O.concrete_forward(model, emb)
+    for s in range(c["B"]):
+        rl, ru, _ = ref_loader.reference_encoder_pass(ver, emb[s:s + 1], c["index"], c["eps"])
+        helpers.assert_within_noise(l[s:s + 1], rl.reshape(1), l64[s:s + 1], "logit lower")
+        helpers.assert_within_noise(u[s:s + 1], ru.reshape(1), u64[s:s + 1], "logit upper")
+        assert float(rl) <= float(y[s]) <= float(ru)
