@@ -70,6 +70,17 @@ SIGNATURES = {
     "fb_encoder_workspace_bytes": [ctypes.POINTER(Encoder), _I, _I, _I],
     "fb_encoder_forward_f32": [ctypes.POINTER(Encoder), _P, _I, _I, ctypes.POINTER(_I), _I, _I, _F, _P, _P, _P, _P, _L, _P],
     "fb_encoder_forward_instances_f32": [ctypes.POINTER(Encoder), _P, _I, _I, _P, _P, _I, _I, _P, _P, _P, _P, _L, _P],
+    "fb_comm_unique_id": [_P],
+    "fb_comm_create": [ctypes.POINTER(_P), _P, _I, _I, _L],
+    "fb_comm_destroy": [_P],
+    "fb_comm_abort": [_P],
+    "fb_comm_info": [_P, ctypes.POINTER(_I), ctypes.POINTER(_I), ctypes.POINTER(_L)],
+    "fb_comm_set_wait_ns": [_P, ctypes.c_uint64],
+    "fb_comm_check": [_P, _I],
+    "fb_comm_last_error": [],
+    "fb_allreduce_f32": [_P, _P, _L, _I, _I, _P],
+    "fb_relax_sharded_f32": [_P, _I, _I] + [_P] * 9 + [_L, _I, _I, _I, _I, _F, _P, _P],
+    "fb_concretize_sharded_f32": [_P, _I] + [_P] * 7 + [_L, _I, _I, _I, _I, _F, _P],
     "fb_profile_enable": [_I],
     "fb_profile_read": [_I, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(_L), ctypes.POINTER(ctypes.c_double),
                         ctypes.POINTER(ctypes.c_double)],
@@ -79,7 +90,7 @@ SIGNATURES = {
     "fb_last_cuda_error": [],
     "fb_version": [],
 }
-_OTHER_RESTYPE = {"fb_status_string": ctypes.c_char_p, "fb_encoder_workspace_bytes": _L, "fb_launch_count": _L,
+_OTHER_RESTYPE = {"fb_comm_last_error": ctypes.c_char_p, "fb_status_string": ctypes.c_char_p, "fb_encoder_workspace_bytes": _L, "fb_launch_count": _L,
                    "fb_dot_product_noalloc_max_floats": _L}
 
 _lib = None
@@ -113,4 +124,6 @@ def check(status, what):
         extra = ""
         if status == 4:
             extra = " (cudaError %d)" % lib.fb_last_cuda_error()
+        if status == 7:
+            extra = " (%s)" % lib.fb_comm_last_error().decode()
         raise FaithError("%s failed: %s%s" % (what, msg, extra))

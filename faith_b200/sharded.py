@@ -7,11 +7,17 @@ over the *whole* dim_in axis: the local unfinished accumulation is all-reduced (
 p = 2, MAX for p = 1) before the relaxation is applied to the local rows.  The sum order of the
 norm changes with the number of ranks, so results agree with the single-rank run within the
 per-operator tolerance, not bit for bit.
+
+With a `faith_b200.comm.Comm` the three steps of a sharded relaxation (partial norms, all-reduce, apply) are one C
+call that enqueues everything on the current stream (fb_relax_sharded_f32), the all-reduce being NCCL's or the
+library's one-shot exchange over NVLink.  Without one (CPU tests of the host logic over gloo, single rank) the
+partial norms are reduced through torch.distributed.  One perturbed word only: the whole dim_in axis is one norm
+block here (the CNN of the benchmark perturbs every pixel), and the C entry points reject anything else.
 """
 import torch
 
-from . import ops
-from ._lib import FB_RELU
+from . import _lib, ops
+from ._lib import FB_RELU, check, load
 
 
 def shard_bounds(lw, uw, rank, world, dim=-2):
@@ -35,11 +41,39 @@ def reduce_partials(part_l, part_u, p, group=None):
     return buf[0], buf[1]
 
 
-def relax_sharded(op, lw, uw, lb, ub, p, eps, group=None):
-    """Fused concretise + relax + rescale of the local dim_in rows: partial norms, all-reduce, apply."""
-    part_l, part_u = ops.norm_partials(lw, uw, p)
-    norm_l, norm_u = reduce_partials(part_l, part_u, p, group)
-    return ops.relax_with_norms(op, lw, uw, lb, ub, norm_l.contiguous(), norm_u.contiguous(), p, eps)
+def relax_sharded(op, lw, uw, lb, ub, p, eps, group=None, comm=None, algo=0, part_ws=None):
+    """Fused concretise + relax + rescale of the local dim_in rows: partial norms, all-reduce, apply.
+    comm: a faith_b200.comm.Comm -> one C call, nothing in between touches the host."""
+    if comm is None:
+        part_l, part_u = ops.norm_partials(lw, uw, p)
+        norm_l, norm_u = reduce_partials(part_l, part_u, p, group)
+        return ops.relax_with_norms(op, lw, uw, lb, ub, norm_l.contiguous(), norm_u.contiguous(), p, eps)
+    dev = ops._chk(lw, uw, lb, ub)
+    rows, Di, Do = lb.numel() // lb.shape[-1], lw.shape[-2], lw.shape[-1]
+    if part_ws is None or part_ws.numel() < 2 * rows * Do:
+        part_ws = torch.empty(2 * rows * Do, device=dev)
+    out = (torch.empty_like(lw), torch.empty_like(uw), torch.empty_like(lb), torch.empty_like(ub))
+    with torch.cuda.device(dev):
+        check(load().fb_relax_sharded_f32(comm._h, algo, op, lw.data_ptr(), uw.data_ptr(), lb.data_ptr(), ub.data_ptr(),
+                                          out[0].data_ptr(), out[1].data_ptr(), out[2].data_ptr(), out[3].data_ptr(),
+                                          part_ws.data_ptr(), rows, Di, Do, 1, ops.norm_code(p), float(eps), None,
+                                          ops._stream()), "fb_relax_sharded_f32")
+    return out
+
+
+def concretize_sharded(lw, uw, lb, ub, p, eps, comm, algo=0, part_ws=None):
+    """Concretisation of a dim_in shard through the communicator (fb_concretize_sharded_f32)."""
+    dev = ops._chk(lw, uw, lb, ub)
+    rows, Di, Do = lb.numel() // lb.shape[-1], lw.shape[-2], lw.shape[-1]
+    if part_ws is None or part_ws.numel() < 2 * rows * Do:
+        part_ws = torch.empty(2 * rows * Do, device=dev)
+    l, u = torch.empty_like(lb), torch.empty_like(ub)
+    with torch.cuda.device(dev):
+        check(load().fb_concretize_sharded_f32(comm._h if comm is not None else None, algo, lw.data_ptr(), uw.data_ptr(),
+                                               lb.data_ptr(), ub.data_ptr(), l.data_ptr(), u.data_ptr(), part_ws.data_ptr(),
+                                               rows, Di, Do, 1, ops.norm_code(p), float(eps), ops._stream()),
+              "fb_concretize_sharded_f32")
+    return l, u
 
 
 class CnnVerifier:
@@ -50,9 +84,12 @@ class CnnVerifier:
     Returns the concretised output bounds (l, u), identical on every rank.
     """
 
-    def __init__(self, layers, device, group=None):
+    def __init__(self, layers, device, group=None, comm=None, algo=0):
         self.device = torch.device(device)
         self.group = group
+        self.comm = comm        # faith_b200.comm.Comm: the all-reduces are enqueued by the library (NCCL or one-shot)
+        self.algo = algo
+        self._ws = None
         self.layers = []
         for ly in layers:
             if ly[0] in ("conv", "linear"):
@@ -79,12 +116,18 @@ class CnnVerifier:
                 lw, uw, lb, ub = ops.conv2d((lw, uw, lb, ub), ly[1], ly[2], ly[3], ly[4])
             elif ly[0] == "relu":
                 shp_w, shp_b = lw.shape, lb.shape
+                if self.comm is not None and (self._ws is None or self._ws.numel() < 2 * lb.numel()):
+                    self._ws = torch.empty(2 * lb.numel(), device=self.device)
                 o = relax_sharded(FB_RELU, lw.reshape(1, size, -1), uw.reshape(1, size, -1), lb.reshape(1, -1),
-                                  ub.reshape(1, -1), p, eps, self.group)
+                                  ub.reshape(1, -1), p, eps, self.group, self.comm, self.algo, self._ws)
                 lw, uw, lb, ub = o[0].view(shp_w), o[1].view(shp_w), o[2].view(shp_b), o[3].view(shp_b)
             elif ly[0] == "linear":
                 lw, uw, lb, ub = ops.matmul(lw.reshape(1, 1, size, -1), uw.reshape(1, 1, size, -1),
                                             lb.reshape(1, 1, -1), ub.reshape(1, 1, -1), ly[1], ly[2])
+        if self.comm is not None:
+            l, u = concretize_sharded(lw.reshape(1, size, -1), uw.reshape(1, size, -1), lb.reshape(1, -1), ub.reshape(1, -1),
+                                      p, eps, self.comm, self.algo)
+            return l.reshape(-1), u.reshape(-1)
         part_l, part_u = ops.norm_partials(lw.reshape(1, size, -1), uw.reshape(1, size, -1), p)
         norm_l, norm_u = reduce_partials(part_l, part_u, p, self.group)
         if p == 2:

@@ -409,6 +409,53 @@ int fb_encoder_forward_instances_f32(const fb_encoder* enc, const float* emb, in
                                      float* out_l, float* out_u, int* violation,
                                      void* workspace, int64_t workspace_bytes, void* stream);
 
+/* ---- dim_in sharded over several GPUs: communicator and fused steps (no counterpart in the reference, which is
+ * single-GPU; the split follows from Bounds.concretize, Bounds.py:311-326, see fb_norm_partials_f32) -------------
+ *
+ * fb_comm wraps an NCCL communicator (one process per GPU; NCCL is bound at run time by dlopen, the environment
+ * variable FB_NCCL_LIB overrides the library name).  Rank 0 obtains a 128-byte id with fb_comm_unique_id and
+ * hands it to the other ranks by any means; every rank then calls fb_comm_create with its device current.
+ * oneshot_floats > 0 additionally sets up the one-shot all-reduce over NVLink for vectors of up to that many
+ * floats: this is the one place where the library allocates device memory (2 * world * oneshot_floats floats plus
+ * flags per rank, freed by fb_comm_destroy) and maps it into the peers through CUDA IPC.  world <= 8.
+ *
+ * Errors: FB_ERR_NCCL when a NCCL call fails or ncclCommGetAsyncError reports an asynchronous error (polled
+ * after every collective and by fb_comm_check); fb_comm_last_error() gives the text.  The one-shot path never
+ * blocks for ever: a wait for a peer is bounded (2 s, fb_comm_set_wait_ns), on expiry the kernel sets a status
+ * word and returns, and fb_comm_check(c, 1) -- which synchronises the device -- reports FB_ERR_TIMEOUT. */
+typedef struct fb_comm fb_comm;
+int fb_comm_unique_id(void* id128);
+int fb_comm_create(fb_comm** out, const void* id128, int rank, int world, int64_t oneshot_floats);
+int fb_comm_destroy(fb_comm* c);
+int fb_comm_abort(fb_comm* c);
+int fb_comm_info(const fb_comm* c, int* rank, int* world, int64_t* oneshot_floats);
+int fb_comm_set_wait_ns(fb_comm* c, uint64_t ns);
+int fb_comm_check(fb_comm* c, int sync);
+const char* fb_comm_last_error(void);
+
+enum fb_reduce_op { FB_SUM = 0, FB_MAX = 1 };
+enum fb_allreduce_algo { FB_ALGO_NCCL = 0, FB_ALGO_ONESHOT = 1 };
+/* In-place all-reduce of n floats on `stream`.  FB_ALGO_ONESHOT: every rank stores its vector into all peers'
+ * receive slots with ordinary stores over NVLink, publishes a flag, waits (bounded) for the others and sums the
+ * slots in rank order (bit-identical on all ranks); n must not exceed oneshot_floats, else FB_ERR_WORKSPACE.
+ * Calls on one communicator must not overlap on the GPU. */
+int fb_allreduce_f32(fb_comm* c, float* buf, int64_t n, int op, int algo, void* stream);
+
+/* fb_relax_f32 and fb_concretize_f32 for a dim_in shard: partial norms of the local rows, all-reduce over the
+ * ranks (SUM, or MAX for FB_P1), relaxation of the local rows / concretisation, all enqueued on `stream` with no
+ * host round trip.  lb, ub are replicated; part_ws: 2 * rows * Do floats of scratch.  c may be NULL (single
+ * rank).  One perturbed word only: words != 1 returns FB_ERR_SHAPE (several word blocks would need one partial
+ * per block and shards aligned to the blocks). */
+int fb_relax_sharded_f32(fb_comm* c, int algo, int op,
+                         const float* lw, const float* uw, const float* lb, const float* ub,
+                         float* out_lw, float* out_uw, float* out_lb, float* out_ub, float* part_ws,
+                         int64_t rows, int Di_local, int Do, int words, int p, float eps,
+                         int* violation, void* stream);
+int fb_concretize_sharded_f32(fb_comm* c, int algo,
+                              const float* lw, const float* uw, const float* lb, const float* ub,
+                              float* l, float* u, float* part_ws,
+                              int64_t rows, int Di_local, int Do, int words, int p, float eps, void* stream);
+
 /* ---- measurement hooks (no counterpart in the reference) --------------------------------
  * fb_profile_enable(1) clears the records and makes every outermost operator call bracket its
  * launches with a pair of CUDA events on the caller's stream; fb_profile_read() waits for the
