@@ -5,13 +5,18 @@
 
 One process per GPU (torchrun for N > 1); the 256 sentences are split evenly over the ranks and no
 collective is on the data path (sentences are independent).  A step is one bound pass over all
-sentences.  Rank 0 prints one JSON line.  `--impl reference` times the reference's own CPU implementation of
+sentences.  Rank 0 prints one JSON line.  Besides the headline it carries: the roofline of the dominant
+kernel against the roofs measured in the same run (tensor pipe with TF32 operands, CUDA-core fp32, and the
+HBM copy bandwidth of MEASURED_PEAKS.json), the same pass at eps = 1e-3, one entry per benchmark configuration
+(`per_config`: C1 linear + relu, C2 attention dot product, C3 tanh + linear, C5 CNN), and the dim_in-sharded CNN
+pass over all ranks (`cnn`).  `--impl reference` times the reference's own CPU implementation of
 the same pass on the host cores instead (its unchanged VerifierForward and Bounds when staged under oracle/_ref,
 else the oracle port).
 """
 import argparse
 import ctypes
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -30,6 +35,8 @@ CFG = dict(layers=3, d_model=128, heads=4, ffn=512, L=32, sentences=256, eps=0.0
 WORKLOAD = ("forward bound pass, 3-layer encoder d128 h4 ffn512 relu, layer_norm no_var, token-0 pooler + tanh, "
             "2-class head; L=32, 1 perturbed word (dim_in=128), Linf eps=0.01, 256 sentences")
 KINDS = ["matmul", "relax", "dot_product", "mul_bounds", "elementwise", "conv"]
+MIN_TIMED_SECONDS = 0.5
+INF = float("inf")
 
 
 def peaks():
@@ -51,7 +58,7 @@ class ClockSampler:
         self.proc = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.FIELDS,
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -59,7 +66,7 @@ class ClockSampler:
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.1)
         self.proc.terminate()
         try:
             out, _ = self.proc.communicate(timeout=5)
@@ -108,7 +115,7 @@ def cpu_reference_pass(model, emb, n_sentences, threads):
     if reference_kind() == "reference":
         import reference_loader
         if "ver" not in _REF:
-            _REF["ver"] = reference_loader.build_reference_verifier(model, float("inf"))
+            _REF["ver"] = reference_loader.build_reference_verifier(model, INF)
         t0 = time.perf_counter()
         for s in range(n_sentences):
             reference_loader.reference_encoder_pass(_REF["ver"], emb[s:s + 1], CFG["index"], CFG["eps"])
@@ -116,7 +123,7 @@ def cpu_reference_pass(model, emb, n_sentences, threads):
     from oracle import bounds_oracle as O
     t0 = time.perf_counter()
     for s in range(n_sentences):
-        O.encoder_forward(model, emb[s:s + 1], [CFG["index"]], float("inf"), CFG["eps"])
+        O.encoder_forward(model, emb[s:s + 1], [CFG["index"]], INF, CFG["eps"])
     return time.perf_counter() - t0
 
 
@@ -153,63 +160,260 @@ def run_reference(args):
     }))
 
 
-def run_cnn(args):
-    """Secondary workload: conv 3->16, relu, conv 16->32 (stride 2), relu, linear 8192->10 on one 3x32x32
-    image with every pixel perturbed (dim_in = 3072, Linf eps = 2/255).  The dim_in axis is sharded over the
-    ranks; each relu all-reduces the partial norms over NCCL.  A step is one bound pass of the image."""
-    import torch.distributed as dist
-    import faith_b200
-    from faith_b200.sharded import CnnVerifier
+# ------------------------------------------------------------------------------------------------ helpers
+class Ctx:
+    """Device, ranks and timing helpers shared by the parts of the benchmark."""
+
+    def __init__(self):
+        import torch.distributed as dist
+        self.dist = dist
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback")
+        torch.cuda.set_device(self.local)
+        self.dev = torch.device("cuda", self.local)
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=self.dev)
+
+    def smi_index(self):
+        """Index nvidia-smi knows this rank's GPU by (CUDA_VISIBLE_DEVICES may renumber)."""
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ids = [v.strip() for v in vis.split(",") if v.strip()]
+            if self.local < len(ids) and ids[self.local].isdigit():
+                return int(ids[self.local])
+        return self.local
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(self, fn, steps):
+        """Device time of `steps` calls of fn in ms (CUDA events on the launching stream), max over the ranks."""
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        self.barrier()
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        self.barrier()
+        ms = torch.tensor([a.elapsed_time(b)], device=self.dev)
+        if self.world > 1:
+            self.dist.all_reduce(ms, op=self.dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    def local_ms(self, fn, reps, warm=3):
+        """Device time of one call in ms on this rank alone: (median, min) over `reps` single calls."""
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(reps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return statistics.median(ts), min(ts)
+
+    def loop_ms(self, fn, n, warm=3):
+        """Device time per call in ms when n calls are enqueued back to back (launch latency hidden)."""
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / n
+
+
+def measure_pipes(lib, ctx):
+    """CUDA-core fp32 and tensor-pipe TF32 rates of this device, measured now (TFLOP/s)."""
+    st = torch.cuda.current_stream().cuda_stream
+    scratch = torch.zeros(1, device=ctx.dev)
+    fl = ctypes.c_double()
+    out = {}
+    for name, call, small, big in (("ffma", lambda it: lib.fb_bench_ffma(scratch.data_ptr(), it, ctypes.byref(fl), st), 2000, 20000),
+                                   ("tf32", lambda it: lib.fb_bench_tf32(it, ctypes.byref(fl), st), 200, 4000)):
+        call(small)
+        torch.cuda.synchronize()
+        best = 0.0
+        for _ in range(3):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            rc = call(big)
+            b.record()
+            torch.cuda.synchronize()
+            if rc == 0:
+                best = max(best, fl.value / a.elapsed_time(b) / 1e9)
+        out[name] = best
+    return out
+
+
+def roof_entry(name, ms, flops, nbytes, pipe_tflops, pipe_name, hbm_gbs, extra=None):
+    """One measured operator against its binding roof: T_roof = max(flops / pipe, bytes / HBM)."""
+    t_pipe = flops / (pipe_tflops * 1e9) if pipe_tflops else 0.0      # ms
+    t_hbm = nbytes / (hbm_gbs * 1e6)
+    bound = "hbm" if t_hbm >= t_pipe else pipe_name
+    e = {"op": name, "ms": ms, "tflops": flops / ms / 1e9, "gbs": nbytes / ms / 1e6, "bound": bound,
+         "roof_ms": max(t_pipe, t_hbm), "frac": max(t_pipe, t_hbm) / ms}
+    if extra:
+        e.update(extra)
+    return e
+
+
+# ------------------------------------------------------------------------------------- per-configuration lines
+def per_config_lines(ctx, lib, pipes, pk):
+    """Benchmark configurations 1-3 and 5 on this GPU: device time of one launch sequence on its own (latency:
+    the microsecond-sized problems are below a kernel launch) and the steady state over many independent
+    instances in one call, each against its roof."""
+    from faith_b200 import ops
+    from faith_b200._lib import FB_RELU, FB_TANH
     from oracle import bounds_oracle as O
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    lib = faith_b200.load()
+    dev = ctx.dev
+    hbm = pk["hbm_gbs"]
+    tf32_alg = pipes["tf32"] * 8.0 / 12.0     # algorithmic flops per second of the 3xTF32 centre/radius kernels
+    ffma_alg = pipes["ffma"] * 2.0            # the CUDA-core GEMM executes half of the algorithmic flops
+    g = torch.Generator().manual_seed(1)
+    out = []
+
+    def bounds(B, L, Di, Do, seed):
+        gg = torch.Generator().manual_seed(seed)
+        lw = (torch.rand(B, L, Di, Do, generator=gg) - 0.5) * 0.2
+        uw = lw + torch.rand(B, L, Di, Do, generator=gg) * 0.02
+        lb = torch.rand(B, L, Do, generator=gg) - 0.5
+        ub = lb + torch.rand(B, L, Do, generator=gg) * 0.1
+        return [t.to(dev) for t in (lw, uw, lb, ub)]
+
+    # C1: Linear 64 -> 128 + bias, ReLU on [1, 16, 64, *] (eps 0.01, L-inf)
+    W = (torch.randn(128, 64, generator=g) / 8).to(dev)
+    bias = (0.1 * torch.randn(128, generator=g)).to(dev)
+
+    def c1(x):
+        y = ops.matmul(x[0], x[1], x[2], x[3], W, bias)
+        return ops.relax(FB_RELU, y[0], y[1], y[2], y[3], INF, 0.01)
+
+    def c1_work(B):
+        M = B * 16 * 65
+        return 8.0 * M * 64 * 128, 4.0 * (2 * M * 64 + 2 * M * 128) + 4.0 * (4 * M * 128)
+    x1 = bounds(1, 16, 64, 64, 1)
+    med, best = ctx.local_ms(lambda: c1(x1), 50)
+    fl, by = c1_work(1)
+    out.append(roof_entry("C1 linear 64->128 + relu, one instance [1,16,64,*]", best, fl, by, ffma_alg, "ffma", hbm,
+                          {"median_ms": med, "mode": "single launch sequence (2 GEMM launches + 1 relaxation): launch latency"}))
+    nb = 2048
+    xb = bounds(nb, 16, 64, 64, 2)
+    per = ctx.loop_ms(lambda: c1(xb), 10)
+    fl, by = c1_work(nb)
+    out.append(roof_entry("C1 steady state, %d independent instances per call" % nb, per, fl, by, tf32_alg, "tf32x3", hbm,
+                          {"instances_per_s": nb / per * 1e3, "us_per_instance": per / nb * 1e3}))
+    del xb
+
+    # C2: attention scores Q.K^T, [4, 32, 128, 32] per instance (2 perturbed words, L2, eps 0.05)
+    def c2(q, k):
+        return ops.dot_product((q[0], q[1], q[2], q[3]), (k[0], k[1], k[2], k[3]), 2.0, 0.05, 2)
+
+    def c2_work(B):
+        return 16.0 * B * 32 * 32 * 129 * 32, 4.0 * (4.0 * B * 32 * 129 * 32 + 2.0 * B * 32 * 32 * 129)
+    q, k = bounds(4, 32, 128, 32, 3), bounds(4, 32, 128, 32, 4)
+    med, best = ctx.local_ms(lambda: c2(q, k), 50)
+    fl, by = c2_work(4)
+    out.append(roof_entry("C2 dot product Q.K^T, one instance [4,32,128,32]", best, fl, by, tf32_alg, "tf32x3", hbm,
+                          {"median_ms": med, "mode": "single call (2 concretisations + bias + weight kernel): launch latency"}))
+    nb = 1024
+    qb, kb = bounds(4 * nb, 32, 128, 32, 5), bounds(4 * nb, 32, 128, 32, 6)
+    per = ctx.loop_ms(lambda: c2(qb, kb), 10)
+    fl, by = c2_work(4 * nb)
+    out.append(roof_entry("C2 steady state, %d independent instances per call" % nb, per, fl, by, tf32_alg, "tf32x3", hbm,
+                          {"instances_per_s": nb / per * 1e3, "us_per_instance": per / nb * 1e3}))
+    del qb, kb
+
+    # C3: tanh relaxation and Linear 256 -> 256 on [8, 64, 256, 256] (4 perturbed words, L1, eps 0.1)
+    x3 = bounds(8, 64, 256, 256, 7)
+    W3 = (torch.randn(256, 256, generator=g) / 16).to(dev)
+    M3 = 8 * 64 * 257
+    per = ctx.loop_ms(lambda: ops.relax(FB_TANH, x3[0], x3[1], x3[2], x3[3], 1.0, 0.1, 4), 20)
+    out.append(roof_entry("C3 tanh relaxation [8,64,256,256]", per, 6.0 * M3 * 256, 4.0 * 4 * M3 * 256, None, "-", hbm))
+    per = ctx.loop_ms(lambda: ops.matmul(x3[0], x3[1], x3[2], x3[3], W3, None), 20)
+    out.append(roof_entry("C3 linear 256->256 [8,64,256,256]", per, 8.0 * M3 * 256 * 256, 4.0 * (4.0 * M3 * 256 + 256 * 256),
+                          tf32_alg, "tf32x3", hbm))
+    del x3
+
+    # C5: CNN pass of one 3x32x32 image with every pixel perturbed (dim_in 3072), one GPU
+    from faith_b200.sharded import CnnVerifier
     layers = O.make_cnn(5)
     img = torch.rand(3, 32, 32, generator=torch.Generator().manual_seed(5))
     ver = CnnVerifier(layers, dev)
+    per = ctx.loop_ms(lambda: ver.forward(img, INF, 2.0 / 255), 10)
+    out.append(roof_entry("C5 CNN pass, one image (conv3-16, relu, conv16-32 s2, relu, linear 8192-10), 1 GPU", per, 41.9e9,
+                          2.3e9, ffma_alg, "ffma", hbm, {"images_per_s": 1e3 / per}))
+    return out
+
+
+def gemm_shape_lines(ctx, pipes, pk, S):
+    """The three GEMM shapes of the headline pass at this rank's share of the sentences, each against its binding
+    roof (tensor pipe with three TF32 products per fp32 product, or HBM)."""
+    from faith_b200 import ops
+    dev = ctx.dev
+    L, D, F = CFG["L"], CFG["d_model"], CFG["ffn"]
+    tf32_alg = pipes["tf32"] * 8.0 / 12.0
+    rows = S * L
+    out = []
+    for (K, N, calls, what) in ((D, D, 4 * CFG["layers"], "projections (Q, K, V, attention output)"),
+                                (D, F, CFG["layers"], "feed-forward 1"), (F, D, CFG["layers"], "feed-forward 2")):
+        lw = torch.randn(rows, D, K, device=dev)
+        uw = lw + 0.01
+        lb = torch.randn(rows, K, device=dev)
+        W = torch.randn(N, K, device=dev) * 0.02
+        per = ctx.loop_ms(lambda: ops.matmul(lw, uw, lb, lb, W, None), 6)
+        M = rows * (D + 1)
+        out.append(roof_entry("K=%d N=%d" % (K, N), per, 8.0 * M * K * N, 4.0 * (2.0 * M * K + 2.0 * M * N + K * N), tf32_alg,
+                              "tf32x3", pk["hbm_gbs"], {"calls_per_pass": calls, "what": what}))
+        del lw, uw, lb, W
+    return out
+
+
+def cnn_sharded(ctx, lib, steps):
+    """Benchmark configuration 5 with dim_in (3072 pixels) sharded over all ranks: the partial norms before each relu
+    and before the final concretisation are all-reduced, by NCCL and by the library's one-shot exchange."""
+    from faith_b200.comm import ALGO_NCCL, ALGO_ONESHOT, Comm
+    from faith_b200.sharded import CnnVerifier
+    from oracle import bounds_oracle as O
+    layers = O.make_cnn(5)
+    img = torch.rand(3, 32, 32, generator=torch.Generator().manual_seed(5))
     eps = 2.0 / 255
-
-    def step():
-        return ver.forward(img, float("inf"), eps, rank, world)
-
-    warmup = max(args.warmup, 3)
-    for _ in range(warmup):
-        step()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    n0 = lib.fb_launch_count()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(args.steps):
-        l, u = step()
-    b.record()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    ms = torch.tensor([a.elapsed_time(b)], device=dev)
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    if rank == 0:
-        ms_step = float(ms.item()) / args.steps
-        print(json.dumps({"metric": "images/sec for CNN bound pass (dim_in sharded)", "value": 1e3 / ms_step,
-                          "unit": "images/s", "n_gpus": world, "steps": args.steps, "warmup": warmup,
-                          "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-                          "dtype": "f32", "data": "synthetic",
-                          "config": {"workload": "CNN 3x32x32, conv3-16 s1, relu, conv16-32 s2, relu, linear 8192-10; "
-                                                 "dim_in 3072 sharded over ranks, Linf eps 2/255",
-                                     "collective": "NCCL all-reduce of [2, 16384] and [2, 8192] fp32 partial norms"},
-                          "gpu_launches": int(lib.fb_launch_count() - n0),
-                          "bounds": {"l0": float(l[0]), "u0": float(u[0])}}))
-    if world > 1:
-        dist.destroy_process_group()
+    res = {"workload": "CNN 3x32x32 (conv3-16 s1, relu, conv16-32 s2, relu, linear 8192-10), Linf eps 2/255, dim_in 3072 "
+                       "sharded over the ranks; all-reduce of [2,16384], [2,8192] and [2,10] fp32 partial norms per image",
+           "n_gpus": ctx.world, "unit": "images/s"}
+    comm = None
+    if ctx.world > 1:
+        comm = Comm.from_process_group(oneshot_floats=1 << 16)
+    algos = [("nccl", ALGO_NCCL), ("oneshot", ALGO_ONESHOT)] if comm is not None else [("single", ALGO_NCCL)]
+    for name, algo in algos:
+        ver = CnnVerifier(layers, ctx.dev, comm=comm, algo=algo)
+        for _ in range(3):
+            l, u = ver.forward(img, INF, eps, ctx.rank, ctx.world)
+        n0 = lib.fb_launch_count()
+        ms = ctx.timed(lambda: ver.forward(img, INF, eps, ctx.rank, ctx.world), steps)
+        res[name] = {"ms_per_image": ms / steps, "images_per_s": 1e3 * steps / ms,
+                     "launches_per_image": int(lib.fb_launch_count() - n0) // steps}
+        if comm is not None:
+            comm.check(sync=True)
+        l, u = ver.forward(img, INF, eps, ctx.rank, ctx.world)
+        res[name]["bounds_logit0"] = [float(l[0]), float(u[0])]
+    if comm is not None:
+        comm.destroy()
+    return res
 
 
+# ----------------------------------------------------------------------------------------------------- main
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -218,30 +422,20 @@ def main():
     ap.add_argument("--impl", default="faith_b200", choices=["faith_b200", "reference"])
     ap.add_argument("--sentences", type=int, default=CFG["sentences"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="encoder", choices=["encoder", "cnn"],
-                    help="encoder = the headline metric; cnn = secondary line for the dim_in-sharded CNN pass")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="headline only: skips the per-configuration lines, the eps = 1e-3 companion and the sharded CNN pass")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
         return
-    if args.workload == "cnn":
-        run_cnn(args)
-        return
 
-    import torch.distributed as dist
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")   # plain peer loads and stores for everything this benchmark sends
     import faith_b200
     from faith_b200 import _lib
     from oracle import bounds_oracle as O
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+    ctx = Ctx()
+    world, rank, dev, dist = ctx.world, ctx.rank, ctx.dev, ctx.dist
     lib = faith_b200.load()
     warmup = max(args.warmup, 3)
 
@@ -255,51 +449,53 @@ def main():
     emb_dev = emb_pinned.to(dev)
     ver = faith_b200.EncoderVerifier(model, dev)
     out = (torch.empty(S, device=dev), torch.empty(S, device=dev), torch.empty(1, dtype=torch.int32, device=dev))
-    res_host = torch.empty(2, S).pin_memory()
-    p_inf = float("inf")
+    lu_dev = torch.empty(S, 2, device=dev)
+    gathered = [torch.empty(per if r < world - 1 else total - (world - 1) * per, 2, device=dev) for r in range(world)] \
+        if rank == 0 else None
+    res_host = torch.empty(total, 2).pin_memory() if rank == 0 else None
+    eps_run = [CFG["eps"]]
 
     def step_resident():
-        ver.forward(emb_dev, [CFG["index"]], p_inf, CFG["eps"], out=out)
+        ver.forward(emb_dev, [CFG["index"]], INF, eps_run[0], out=out)
 
     def step_e2e():
+        # the call a user makes: host embeddings in, (l, u) of all 256 sentences back on the host of rank 0
         e = emb_pinned.to(dev, non_blocking=True)
-        ver.forward(e, [CFG["index"]], p_inf, CFG["eps"], out=out)
-        res_host[0].copy_(out[0], non_blocking=True)
-        res_host[1].copy_(out[1], non_blocking=True)
-
-    def barrier():
+        ver.forward(e, [CFG["index"]], INF, eps_run[0], out=out)
+        torch.stack((out[0], out[1]), dim=1, out=lu_dev)
         if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed(fn, steps):
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        a.record()
-        for _ in range(steps):
-            fn()
-        b.record()
-        barrier()
-        ms = torch.tensor([a.elapsed_time(b)], device=dev)
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item())
+            dist.gather(lu_dev, gathered, dst=0)
+            if rank == 0:
+                off = 0
+                for t in gathered:
+                    res_host[off:off + t.shape[0]].copy_(t, non_blocking=True)
+                    off += t.shape[0]
+        else:
+            res_host.copy_(lu_dev, non_blocking=True)
 
     for _ in range(warmup):
         step_resident()
-    barrier()
+    ctx.barrier()
+    # The timed region is `blocks` consecutive blocks of `steps` passes, sized from one probe block so that it lasts at
+    # least half a second on every rank count (at 8 GPUs a pass is a few milliseconds and a 10-pass region would see two
+    # clock samples).
+    probe_ms = ctx.timed(step_resident, args.steps)
+    blocks = max(1, int(math.ceil(MIN_TIMED_SECONDS * 1e3 / max(probe_ms, 1e-3))))
+    n_steps = args.steps * blocks
     launches0 = lib.fb_launch_count()
-    sampler = ClockSampler(local) if rank == 0 else None
-    ms_total = timed(step_resident, args.steps)
+    sampler = ClockSampler(ctx.smi_index()) if rank == 0 else None
+    ms_total = ctx.timed(step_resident, n_steps)
     clocks = sampler.stop() if sampler else None
     launches = lib.fb_launch_count() - launches0
+    tc_flag = lib.fb_tc_check()          # synchronising read of the tensor-core kernels' give-up flag
+    viol = int(out[2].item())
     for _ in range(2):
         step_e2e()
-    ms_e2e = timed(step_e2e, args.steps)
+    ms_e2e = ctx.timed(step_e2e, n_steps)
 
     # per-operator device times of the same step, from CUDA events around every operator call
     lib.fb_profile_enable(1)
-    barrier()
+    ctx.barrier()
     for _ in range(args.steps):
         step_resident()
     torch.cuda.synchronize()
@@ -314,60 +510,70 @@ def main():
                                bytes_per_call=by.value / calls.value))
     lib.fb_profile_enable(0)
 
-    # CUDA-core fp32 peak of this device, measured now (roof of the FFMA GEMM)
-    scratch = torch.zeros(1, device=dev)
-    fl = ctypes.c_double()
-    lib.fb_bench_ffma(scratch.data_ptr(), 2000, ctypes.byref(fl), torch.cuda.current_stream().cuda_stream)
-    torch.cuda.synchronize()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    lib.fb_bench_ffma(scratch.data_ptr(), 20000, ctypes.byref(fl), torch.cuda.current_stream().cuda_stream)
-    b.record()
-    torch.cuda.synchronize()
-    ffma_tflops = fl.value / a.elapsed_time(b) / 1e9
+    pipes = measure_pipes(lib, ctx)
+    pk = peaks()
 
-    viol = int(out[2].item())
+    extras = {}
+    if not args.no_extras:
+        # the same pass at eps = 1e-3, where the bounds of the third layer stay finite and tight
+        eps_run[0] = 1e-3
+        for _ in range(2):
+            step_resident()
+        ms_small = ctx.timed(step_resident, args.steps)
+        l_s, u_s = out[0].clone(), out[1].clone()
+        extras["eps_1e-3"] = {"ms_per_step": ms_small / args.steps, "value": total / (ms_small / args.steps / 1e3), "unit": UNIT,
+                              "violation_flag": int(out[2].item()),
+                              "finite": bool(torch.isfinite(l_s).all() and torch.isfinite(u_s).all()),
+                              "mean_width": float((u_s - l_s).mean())}
+        eps_run[0] = CFG["eps"]
+        ver._ws = None
+        torch.cuda.empty_cache()
+        extras["gemm_shapes"] = gemm_shape_lines(ctx, pipes, pk, S)
+        torch.cuda.empty_cache()
+        extras["cnn"] = cnn_sharded(ctx, lib, max(args.steps, 10))
+        if rank == 0:
+            extras["per_config"] = per_config_lines(ctx, lib, pipes, pk)
+        ctx.barrier()
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
 
-    pk = peaks()
-    ms_step = ms_total / args.steps
+    ms_step = ms_total / n_steps
     value = total / (ms_step / 1e3)
-    e2e_value = total / (ms_e2e / args.steps / 1e3)
+    e2e_value = total / (ms_e2e / n_steps / 1e3)
     total_op_ms = sum(o["ms"] for o in per_op) or 1.0
     for o in per_op:
         o["share"] = o["ms"] / total_op_ms
         o["hbm_frac"] = o["gbs"] / pk["hbm_gbs"]
     dom = max(per_op, key=lambda o: o["ms"])
-    if dom["op"] in ("matmul", "dot_product", "conv"):
-        roofline = {"kernel": dom["op"], "bound": "tensor", "achieved": dom["tflops"], "peak": pk["bf16_sustained"],
-                    "unit": "TFLOP/s", "frac": dom["tflops"] / pk["bf16_sustained"], "traffic": None,
-                    "peak_source": pk["source"] + " (dense bf16, sustained)",
+    tf32_alg = pipes["tf32"] * 8.0 / 12.0
+    if dom["op"] == "matmul" and os.environ.get("FB_MATMUL_IMPL", "") != "ffma":
+        roofline = {"kernel": "split_sign_gemm_tc (all products of the pass)", "bound": "tensor", "achieved": dom["tflops"],
+                    "peak": tf32_alg, "unit": "TFLOP/s", "frac": dom["tflops"] / tf32_alg,
+                    "peak_source": "measured in this run: tcgen05 kind::tf32 rate %.0f TFLOP/s x 8/12 (the kernel executes three "
+                                   "TF32 products per fp32 product on two GEMMs instead of four: 12 tensor flops per 8 "
+                                   "algorithmic ones)" % pipes["tf32"],
+                    "avg_ms_per_call": dom["ms"] / dom["calls"], "share_of_step": dom["share"],
+                    "hbm_frac": dom["gbs"] / pk["hbm_gbs"], "hbm_peak": pk["hbm_gbs"], "hbm_source": pk["source"],
+                    "frac_of_bf16_sustained": dom["tflops"] / pk["bf16_sustained"],
+                    # DRAM traffic per launch from the ncu capture of the 32-sentence case (profiles/): reads equal the
+                    # algorithmic bytes, a third of the writes was still in L2 at kernel end (ratio 0.82 for the plain
+                    # instantiation, 0.93 for the one that writes column norms)
+                    "traffic": dom["bytes_per_call"] * 0.87,
+                    "traffic_note": "bytes per launch; ncu dram read+write of 32-sentence launches scaled by algorithmic bytes"}
+        shapes = extras.get("gemm_shapes")
+        if shapes:
+            w = sum(s["ms"] * s["calls_per_pass"] for s in shapes)
+            roofline["frac_binding_roof_time_weighted"] = sum(s["roof_ms"] * s["calls_per_pass"] for s in shapes) / w
+            roofline["by_shape"] = shapes
+    elif dom["op"] in ("matmul", "dot_product", "conv"):
+        ffma_alg = pipes["ffma"] * (2.0 if dom["op"] != "dot_product" else 4.0 / 3.0)
+        roofline = {"kernel": dom["op"], "bound": "tensor", "achieved": dom["tflops"], "peak": ffma_alg, "unit": "TFLOP/s",
+                    "frac": dom["tflops"] / ffma_alg, "traffic": None,
+                    "peak_source": "measured in this run: CUDA-core fp32 FMA rate, scaled to algorithmic flops",
                     "avg_ms_per_call": dom["ms"] / dom["calls"], "share_of_step": dom["share"]}
-        if dom["op"] == "matmul" and os.environ.get("FB_MATMUL_IMPL", "") != "ffma":
-            # DRAM traffic per launch from the ncu capture of the 32-sentence case
-            # (profiles/split_sign_gemm_tc_32_sentences.md): 134.4 MB read + 86.9 MB written against 268.6 MB
-            # algorithmic (reads match; a third of the writes was still in L2 when the kernel ended), scaled to
-            # this run's average launch by the bytes it processes
-            roofline["traffic"] = dom["bytes_per_call"] * (134.41 + 86.90) / 268.6
-            roofline["traffic_note"] = "bytes; ncu dram read+write of a 32-sentence launch scaled by algorithmic bytes"
-
-            # tcgen05 kind::tf32 runs at half the bf16 rate; the 3xTF32 centre/radius kernel executes
-            # 12*M*K*N tensor flops for the 8*M*K*N algorithmic ones
-            tf32_peak = pk["bf16_tflops"] / 2.0
-            roofline.update({"pipe": "tcgen05 kind::tf32 (3xTF32, centre/radius)", "pipe_peak": tf32_peak,
-                             "frac_of_pipe": dom["tflops"] * 1.5 / tf32_peak,
-                             "note": "achieved counts the algorithmic 8*M*K*N flops; pipe_peak = measured bf16 burst / 2; "
-                                     "frac_of_pipe = achieved * 1.5 / pipe_peak (three TF32 products per fp32 product, "
-                                     "two GEMMs instead of four)",
-                             "hbm_frac": dom["gbs"] / pk["hbm_gbs"]})
-        else:
-            roofline.update({"pipe": "fp32 FFMA (CUDA cores)", "pipe_peak": ffma_tflops,
-                             "frac_of_pipe": dom["tflops"] * (0.5 if dom["op"] != "dot_product" else 0.75) / ffma_tflops,
-                             "note": "achieved counts algorithmic flops; the centre/radius kernels execute 1/2 (matmul, "
-                                     "conv) or 3/4 (dot product) of them"})
     else:
         roofline = {"kernel": dom["op"], "bound": "hbm", "achieved": dom["gbs"], "peak": pk["hbm_gbs"], "unit": "GB/s",
                     "frac": dom["gbs"] / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
@@ -379,15 +585,24 @@ def main():
         "data": "synthetic",
         "config": {"workload": WORKLOAD, "sentences": total, "sentences_per_gpu": per, "sharding": "sentences",
                    "l2": "per-step working set is several GB per GPU, far above the 126 MB L2; no flush needed",
-                   "violation_flag": viol},
+                   "timed_region": "%d blocks of %d steps = %d passes (>= %.1f s)" % (blocks, args.steps, n_steps, MIN_TIMED_SECONDS),
+                   "violation_flag": viol, "tc_error_flag": tc_flag},
+        "timed_steps": n_steps,
         "clocks": clocks,
-        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": emb_pinned.numel() * 4 * world,
-                "d2h_bytes_per_step": 2 * S * 4 * world},
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": emb_host.numel() * 4,
+                "d2h_bytes_per_step": total * 2 * 4,
+                "path": "pinned host embeddings -> device, pass, (l, u) gathered to rank 0 and copied to its host"},
         "gpu_launches": int(launches),
+        "launches_per_step": int(launches) // n_steps,
         "roofline": roofline,
         "per_op": per_op,
-        "ffma_peak_tflops": ffma_tflops,
+        "pipe_peaks_tflops": pipes,
     }
+    if clocks and clocks.get("sm_mhz") and clocks.get("sm_max_mhz"):
+        # the pass at the clock the run actually had, expressed at the maximum clock: makes a power-capped single GPU and
+        # uncapped GPUs of a larger run comparable
+        line["ms_per_step_at_max_clock"] = ms_step * clocks["sm_mhz"] / clocks["sm_max_mhz"]
+    line.update(extras)
     if world == 1 and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
         cpu_reference_pass(model, emb_host, 1, threads)

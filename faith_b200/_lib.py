@@ -86,6 +86,7 @@ SIGNATURES = {
                         ctypes.POINTER(ctypes.c_double)],
     "fb_launch_count": [],
     "fb_bench_ffma": [_P, _I, ctypes.POINTER(ctypes.c_double), _P],
+    "fb_bench_tf32": [_I, ctypes.POINTER(ctypes.c_double), _P],
     "fb_status_string": [_I],
     "fb_last_cuda_error": [],
     "fb_version": [],

@@ -689,6 +689,85 @@ extern "C" int fb_tc_error_flag(int* flag) {
   return FB_OK;
 }
 
+// ------------------------------------------------------------------------------------------------
+// Measurement aid: the rate of the tensor pipe for kind::tf32, the roof of the 3xTF32 kernels above.  Every SM runs
+// one CTA whose single issuing thread feeds 128 x 256 x 8 MMAs (operands in shared memory, two accumulators of 256
+// columns alternating so that consecutive instructions do not depend on each other) as fast as the pipe takes them.
+namespace fb {
+namespace {
+constexpr uint32_t kPeakSmem = 48 * 1024 + 1024 + 64;   // A 128 x 32, B 256 x 32 fp32 (128-byte rows, swizzled), barrier
+constexpr uint32_t kPeakIdesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+
+__device__ __forceinline__ void mma_tf32_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc), "r"(0u)
+      : "memory");
+}
+
+__global__ void __launch_bounds__(128, 1) tf32_peak_kernel(int iters, int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bar = base + 48 * 1024;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + 48 * 1024 + 16);
+  volatile int* cta_abort = reinterpret_cast<volatile int*>(base_ptr + 48 * 1024 + 24);
+  for (uint32_t i = threadIdx.x; i < 48 * 1024 / 4; i += blockDim.x) reinterpret_cast<float*>(base_ptr)[i] = 0.f;
+  if (threadIdx.x == 0) {
+    mbar_init(bar, 1);
+    *cta_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (threadIdx.x < 32) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
+    tmem_relinquish();
+  }
+  fence_async_smem();   // the zero fill went through the generic proxy; the MMAs read through the async proxy
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  if (threadIdx.x == 0) {
+    const uint64_t ad = smem_desc_sw128(base), bd = smem_desc_sw128(base + 16 * 1024);
+    for (int it = 0; it < iters; ++it) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {   // four k steps of a 32-wide tile, two accumulators
+        mma_tf32_ss(tmem, ad + 2 * j, bd + 2 * j, kPeakIdesc, 1u);
+        mma_tf32_ss(tmem + 256, ad + 2 * j, bd + 2 * j, kPeakIdesc, 1u);
+      }
+    }
+    tc_commit(bar);
+    const WaitCtx wc = {cta_abort, kMaxTries};
+    if (!mbar_wait(bar, 0, wc) && status != nullptr) atomicOr(status, 4);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+}  // namespace
+}  // namespace fb
+
+extern "C" int fb_bench_tf32(int iters, double* flops, void* stream) {
+  if (iters <= 0 || !flops) return FB_ERR_ARG;
+  static std::once_flag once[64];
+  int dev = 0;
+  FB_CUDA_OK(cudaGetDevice(&dev));
+  cudaError_t attr_err = cudaSuccess;
+  std::call_once(once[dev & 63], [&]() {
+    attr_err = cudaFuncSetAttribute(fb::tf32_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fb::kPeakSmem);
+  });
+  FB_CUDA_OK(attr_err);
+  const int blocks = fb::device_info().sms;
+  fb::tf32_peak_kernel<<<blocks, 128, fb::kPeakSmem, (cudaStream_t)stream>>>(iters, fb::t_status_sink);
+  FB_LAUNCH_OK();
+  *flops = 2.0 * 128.0 * 256.0 * 8.0 * 8.0 * (double)iters * blocks;
+  return FB_OK;
+}
+
 extern "C" int fb_tc_check(void) {
   int flag = 0;
   const int rc = fb_tc_error_flag(&flag);

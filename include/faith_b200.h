@@ -470,6 +470,10 @@ int64_t fb_launch_count(void);
  * and returns in *flops the floating-point operations it performs; timed by the caller with
  * CUDA events it gives the CUDA-core fp32 peak used as the roof of the FFMA kernels. */
 int fb_bench_ffma(float* scratch, int iters, double* flops, void* stream);
+/* The same for the tensor pipe with kind::tf32 operands: every SM issues 128 x 256 x 8 tcgen05.mma instructions back
+ * to back (8 * iters per SM); *flops receives the floating-point operations performed.  The rate is the roof of the
+ * 3xTF32 kernels (which execute three such products per fp32 product). */
+int fb_bench_tf32(int iters, double* flops, void* stream);
 
 #ifdef __cplusplus
 }
