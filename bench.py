@@ -175,7 +175,9 @@ class Ctx:
         torch.cuda.set_device(self.local)
         self.dev = torch.device("cuda", self.local)
         if self.world > 1:
-            dist.init_process_group("nccl", device_id=self.dev)
+            import datetime
+            # a collective that one rank never joins must end this run in minutes, not after the default ten
+            dist.init_process_group("nccl", device_id=self.dev, timeout=datetime.timedelta(seconds=90))
 
     def smi_index(self):
         """Index nvidia-smi knows this rank's GPU by (CUDA_VISIBLE_DEVICES may renumber)."""
@@ -430,6 +432,8 @@ def main():
         return
 
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")   # plain peer loads and stores for everything this benchmark sends
+    if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+        os.environ["NCCL_DEBUG"] = "WARN"            # NCCL's version banner goes to stdout, which carries the JSON line
     import faith_b200
     from faith_b200 import _lib
     from oracle import bounds_oracle as O

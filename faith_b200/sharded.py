@@ -41,12 +41,13 @@ def reduce_partials(part_l, part_u, p, group=None):
     return buf[0], buf[1]
 
 
-def relax_sharded(op, lw, uw, lb, ub, p, eps, group=None, comm=None, algo=0, part_ws=None):
+def relax_sharded(op, lw, uw, lb, ub, p, eps, group=None, comm=None, algo=0, part_ws=None, world=None):
     """Fused concretise + relax + rescale of the local dim_in rows: partial norms, all-reduce, apply.
-    comm: a faith_b200.comm.Comm -> one C call, nothing in between touches the host."""
+    comm: a faith_b200.comm.Comm -> one C call, nothing in between touches the host.
+    world == 1 says that the rows are not sharded at all (no reduction, whatever process group may exist)."""
     if comm is None:
         part_l, part_u = ops.norm_partials(lw, uw, p)
-        norm_l, norm_u = reduce_partials(part_l, part_u, p, group)
+        norm_l, norm_u = (part_l, part_u) if world == 1 else reduce_partials(part_l, part_u, p, group)
         return ops.relax_with_norms(op, lw, uw, lb, ub, norm_l.contiguous(), norm_u.contiguous(), p, eps)
     dev = ops._chk(lw, uw, lb, ub)
     rows, Di, Do = lb.numel() // lb.shape[-1], lw.shape[-2], lw.shape[-1]
@@ -116,20 +117,21 @@ class CnnVerifier:
                 lw, uw, lb, ub = ops.conv2d((lw, uw, lb, ub), ly[1], ly[2], ly[3], ly[4])
             elif ly[0] == "relu":
                 shp_w, shp_b = lw.shape, lb.shape
-                if self.comm is not None and (self._ws is None or self._ws.numel() < 2 * lb.numel()):
+                comm = self.comm if world > 1 else None
+                if comm is not None and (self._ws is None or self._ws.numel() < 2 * lb.numel()):
                     self._ws = torch.empty(2 * lb.numel(), device=self.device)
                 o = relax_sharded(FB_RELU, lw.reshape(1, size, -1), uw.reshape(1, size, -1), lb.reshape(1, -1),
-                                  ub.reshape(1, -1), p, eps, self.group, self.comm, self.algo, self._ws)
+                                  ub.reshape(1, -1), p, eps, self.group, comm, self.algo, self._ws, world)
                 lw, uw, lb, ub = o[0].view(shp_w), o[1].view(shp_w), o[2].view(shp_b), o[3].view(shp_b)
             elif ly[0] == "linear":
                 lw, uw, lb, ub = ops.matmul(lw.reshape(1, 1, size, -1), uw.reshape(1, 1, size, -1),
                                             lb.reshape(1, 1, -1), ub.reshape(1, 1, -1), ly[1], ly[2])
-        if self.comm is not None:
+        if self.comm is not None and world > 1:
             l, u = concretize_sharded(lw.reshape(1, size, -1), uw.reshape(1, size, -1), lb.reshape(1, -1), ub.reshape(1, -1),
                                       p, eps, self.comm, self.algo)
             return l.reshape(-1), u.reshape(-1)
         part_l, part_u = ops.norm_partials(lw.reshape(1, size, -1), uw.reshape(1, size, -1), p)
-        norm_l, norm_u = reduce_partials(part_l, part_u, p, self.group)
+        norm_l, norm_u = (part_l, part_u) if world == 1 else reduce_partials(part_l, part_u, p, self.group)
         if p == 2:
             norm_l, norm_u = norm_l.sqrt(), norm_u.sqrt()
         return lb.reshape(-1) - eps * norm_l.reshape(-1), ub.reshape(-1) + eps * norm_u.reshape(-1)
