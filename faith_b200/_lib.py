@@ -67,6 +67,8 @@ SIGNATURES = {
     "fb_split_heads_f32": [_P] * 4 + [_I] * 6 + [_P],
     "fb_merge_heads_f32": [_P] * 4 + [_I] * 5 + [_P],
     "fb_conv2d_f32": [_P] * 10 + [_I] * 10 + [_P],
+    "fb_conv2d_identity_relax_f32": [_I, _P, _P, _P, _P, _F] + [_P] * 5 + [_L, _L] + [_I] * 9 + [_F, _P, _P],
+    "fb_conv2d_windowed_f32": [_P] * 5 + [_L, _L, _I, _I, _P, _I] + [_I] * 8 + [_P],
     "fb_encoder_workspace_bytes": [ctypes.POINTER(Encoder), _I, _I, _I],
     "fb_encoder_forward_f32": [ctypes.POINTER(Encoder), _P, _I, _I, ctypes.POINTER(_I), _I, _I, _F, _P, _P, _P, _P, _L, _P],
     "fb_encoder_forward_instances_f32": [ctypes.POINTER(Encoder), _P, _I, _I, _P, _P, _I, _I, _P, _P, _P, _P, _L, _P],

@@ -7,6 +7,8 @@
 // (8 x 32, or 16 x 16 for narrow outputs such as the 16 x 16 map of a stride-2 layer) and CO
 // output channels (16 or 32); input channels are staged through shared memory four at a time
 // (centre and radius planes with halo), the weights of the chunk are broadcast from shared memory.
+#include <algorithm>
+#include <cstdint>
 #include "common.cuh"
 
 namespace fb {
@@ -156,15 +158,314 @@ int launch_conv(const float* x_lo, const float* x_up, const float* Wt, const flo
 #undef FB_CONV_ARGS
 }
 
+// ------------------------------------------------------------------------------------------------
+// Convolutions behind an identity input.  When every pixel of an image is perturbed, dim_in = Cin * H * W and the
+// input bound is lw = uw = scale * I: row r of the weight tensors is the image with the single pixel
+// (ci, yi, xi) = unravel(r) set.  Two consequences are used here:
+//  * the first convolution needs no input at all: y_lw[r, co, y, x] is scale * W[co, ci, ky, kx] where the tap
+//    (ky, kx) of output pixel (y, x) falls on (yi, xi), else zero, and the dual norm of output column (co, y, x)
+//    over ALL rows is the norm of the taps of W[co] that fall inside the image -- so the concretised range, the
+//    relaxation that follows and its rescale are computed from W alone and the relaxed rows are written directly;
+//  * further layers keep the rows local: row r is zero outside a small window around its pixel, so a later
+//    convolution only has to compute the outputs whose taps reach into that window and store zeros elsewhere.
+
+// Per output column (co, y, x): slopes and bias terms of the relaxation `op` of conv(identity input) (op < 0: no
+// relaxation).  col_ws: k_l, k_u, then the bias terms are written to y_lb, y_ub in place (they hold the conv of
+// the bias part on entry).
+__global__ void __launch_bounds__(256)
+identity_conv_columns_kernel(int op, const float* __restrict__ Wt, float* __restrict__ y_lb, float* __restrict__ y_ub,
+                             float* __restrict__ k_l, float* __restrict__ k_u, float scale, int Cin, int H, int W,
+                             int Cout, int Kh, int Kw, int stride, int pad, int Ho, int Wo, int p, float eps,
+                             int* __restrict__ violation) {
+  const int64_t n = (int64_t)Cout * Ho * Wo;
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < n; t += (int64_t)gridDim.x * blockDim.x) {
+    const int x = (int)(t % Wo), y = (int)((t / Wo) % Ho), co = (int)(t / ((int64_t)Wo * Ho));
+    float acc = 0.f;
+    for (int ci = 0; ci < Cin; ++ci)
+      for (int ky = 0; ky < Kh; ++ky) {
+        const int iy = y * stride - pad + ky;
+        if (iy < 0 || iy >= H) continue;
+        for (int kx = 0; kx < Kw; ++kx) {
+          const int ix = x * stride - pad + kx;
+          if (ix < 0 || ix >= W) continue;
+          acc = norm_accum(p, acc, fmul(scale, Wt[(((int64_t)co * Cin + ci) * Kh + ky) * Kw + kx]));
+        }
+      }
+    const float nrm = norm_finish(p, acc);
+    const float lbv = y_lb[t], ubv = y_ub[t];
+    if (op < 0) {
+      k_l[t] = 1.f;
+      k_u[t] = 1.f;
+      continue;
+    }
+    const float l = fadd(lbv, fmul(-eps, nrm)), u = fadd(ubv, fmul(eps, nrm));
+    bool bad = false;
+    const ColCoef c = relax_column(op, l, u, lbv, ubv, bad);
+    if (bad && violation != nullptr) *violation = 1;
+    // both lines of the input coincide, so own-side and cross coefficients apply to the same numbers; for a
+    // well-formed column one of each pair is zero and the sum is exact
+    k_l[t] = fadd(c.c_ll, c.c_lu);
+    k_u[t] = fadd(c.c_ul, c.c_uu);
+    y_lb[t] = c.nlb;
+    y_ub[t] = c.nub;
+  }
+}
+
+// The convolutions a row has been through before the one being computed: enough to know, from the row's pixel alone,
+// the window outside of which the row is zero.
+constexpr int kMaxChain = 8;
+struct ConvChain {
+  int n;
+  int kh[kMaxChain], kw[kMaxChain], stride[kMaxChain], pad[kMaxChain];
+};
+
+struct Span { int lo, hi; };   // inclusive; lo > hi: empty
+
+// Outputs (along one axis) of a convolution (k, stride, pad, n_out outputs) that have a tap inside the input span.
+__host__ __device__ inline Span span_after_conv(Span s, int k, int stride, int pad, int n_out) {
+  if (s.lo > s.hi) return s;
+  const int a = s.lo + pad - (k - 1);
+  Span o;
+  o.lo = a > 0 ? (a + stride - 1) / stride : 0;
+  o.hi = (s.hi + pad) / stride;
+  if (o.hi > n_out - 1) o.hi = n_out - 1;
+  return o;
+}
+
+// Window (in the coordinates of the chain's last output) reached by pixel (yi, xi) of the H0 x W0 image.
+__host__ __device__ inline void chain_window(const ConvChain& ch, int H0, int W0, int yi, int xi, Span& wy, Span& wx) {
+  wy.lo = wy.hi = yi;
+  wx.lo = wx.hi = xi;
+  int h = H0, w = W0;
+  for (int i = 0; i < ch.n; ++i) {
+    h = (h + 2 * ch.pad[i] - ch.kh[i]) / ch.stride[i] + 1;
+    w = (w + 2 * ch.pad[i] - ch.kw[i]) / ch.stride[i] + 1;
+    wy = span_after_conv(wy, ch.kh[i], ch.stride[i], ch.pad[i], h);
+    wx = span_after_conv(wx, ch.kw[i], ch.stride[i], ch.pad[i], w);
+  }
+}
+
+__device__ __forceinline__ void store_elems(float* p, const float (&v)[4], int n) {
+  if (n == 4) *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  else p[0] = v[0];
+}
+
+// One block per row r = row_start + blockIdx.x: zeros everywhere, k * scale * W at the (at most Kh * Kw * Cout)
+// positions whose tap falls on the row's pixel.  A thread owns output elements (V in a row of the image at a time:
+// 4 when the width allows 16-byte stores, else 1), so nothing is written twice.
+template <int V>
+__global__ void __launch_bounds__(256)
+identity_conv_rows_kernel(const float* __restrict__ Wt, const float* __restrict__ k_l, const float* __restrict__ k_u,
+                          float* __restrict__ y_lw, float* __restrict__ y_uw, float scale, int64_t row_start, int Cin,
+                          int H, int W, int Cout, int Kh, int Kw, int stride, int pad, int Ho, int Wo) {
+  const int64_t r = row_start + blockIdx.x;
+  const int xi = (int)(r % W), yi = (int)((r / W) % H), ci = (int)(r / ((int64_t)W * H));
+  const unsigned n = (unsigned)Cout * Ho * Wo, uWo = Wo, uHo = Ho;
+  float* zl = y_lw + (int64_t)blockIdx.x * n;
+  float* zu = y_uw + (int64_t)blockIdx.x * n;
+  for (unsigned t = threadIdx.x * V; t < n; t += blockDim.x * V) {
+    const unsigned q = t / uWo, x0 = t - q * uWo, co = q / uHo, y = q - co * uHo;
+    const int ky = yi - ((int)y * stride - pad);
+    float lo[4] = {0.f, 0.f, 0.f, 0.f}, up[4] = {0.f, 0.f, 0.f, 0.f};
+    if (ky >= 0 && ky < Kh) {
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        const int kx = xi - ((int)(x0 + e) * stride - pad);
+        if (kx >= 0 && kx < Kw) {
+          const float tap = fmul(scale, __ldg(Wt + (((int64_t)co * Cin + ci) * Kh + ky) * Kw + kx));
+          lo[e] = fmul(tap, k_l[t + e]);
+          up[e] = fmul(tap, k_u[t + e]);
+        }
+      }
+    }
+    store_elems(zl + t, lo, V);
+    store_elems(zu + t, up, V);
+  }
+}
+
+// Split-sign convolution of rows that are zero outside a window (the window follows from the row's pixel and the chain
+// of convolutions before this one).  One block per row: the window of the input is staged in shared memory as
+// centre and radius, the outputs whose taps reach it are accumulated there in the order of the dense kernel (input
+// channel, then tap row, then tap column; the skipped terms are exact zeros, so the value is the dense kernel's bit
+// for bit), and the row is then streamed out, zeros outside the output window.
+// Shared memory: centre and radius [Cin, win_h, win_w], then lower and upper [Cout, out_h, out_w].
+template <int V>
+__global__ void __launch_bounds__(256)
+conv_window_kernel(const float* __restrict__ x_lo, const float* __restrict__ x_up, const float* __restrict__ Wt,
+                   float* __restrict__ y_lo, float* __restrict__ y_up, int64_t row_start, int H0, int W0,
+                   const ConvChain ch, int Cin, int H, int W, int Cout, int Kh, int Kw, int stride, int pad, int Ho,
+                   int Wo, int win_h, int win_w, int out_h, int out_w) {
+  extern __shared__ float win_smem[];
+  float* s_c = win_smem;
+  float* s_r = s_c + Cin * win_h * win_w;
+  float* s_ol = s_r + Cin * win_h * win_w;
+  float* s_ou = s_ol + Cout * out_h * out_w;
+  const int64_t r = row_start + blockIdx.x;
+  const int xi = (int)(r % W0), yi = (int)((r / W0) % H0);
+  Span wy, wx;
+  chain_window(ch, H0, W0, yi, xi, wy, wx);
+  const Span oy = span_after_conv(wy, Kh, stride, pad, Ho), ox = span_after_conv(wx, Kw, stride, pad, Wo);
+  const bool empty = wy.lo > wy.hi || wx.lo > wx.hi || oy.lo > oy.hi || ox.lo > ox.hi;
+  const int ah = wy.hi - wy.lo + 1, aw = wx.hi - wx.lo + 1, bh = oy.hi - oy.lo + 1, bw = ox.hi - ox.lo + 1;
+  const unsigned n_out = (unsigned)Cout * Ho * Wo;
+  const int64_t n_in = (int64_t)Cin * H * W;
+  const float* il = x_lo + (int64_t)blockIdx.x * n_in;
+  const float* iu = x_up + (int64_t)blockIdx.x * n_in;
+  float* zl = y_lo + (int64_t)blockIdx.x * n_out;
+  float* zu = y_up + (int64_t)blockIdx.x * n_out;
+  if (!empty) {
+    for (int i = threadIdx.x; i < Cin * ah * aw; i += blockDim.x) {
+      const int x = i % aw, y = (i / aw) % ah, c = i / (aw * ah);
+      const int64_t o = ((int64_t)c * H + wy.lo + y) * W + wx.lo + x;
+      const float lo = __ldg(il + o), up = __ldg(iu + o);
+      s_c[(c * win_h + y) * win_w + x] = fmul(fadd(lo, up), 0.5f);
+      s_r[(c * win_h + y) * win_w + x] = fmul(fsub(up, lo), 0.5f);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < Cout * bh * bw; i += blockDim.x) {
+      const int x = i % bw, y = (i / bw) % bh, co = i / (bw * bh);
+      const int iy0 = (oy.lo + y) * stride - pad - wy.lo, ix0 = (ox.lo + x) * stride - pad - wx.lo;  // window coordinates
+      float ac = 0.f, ar = 0.f;
+      for (int c = 0; c < Cin; ++c)
+        for (int ky = 0; ky < Kh; ++ky) {
+          const int wyy = iy0 + ky;
+          if (wyy < 0 || wyy >= ah) continue;
+          for (int kx = 0; kx < Kw; ++kx) {
+            const int wxx = ix0 + kx;
+            if (wxx < 0 || wxx >= aw) continue;
+            const float w = __ldg(Wt + (((int64_t)co * Cin + c) * Kh + ky) * Kw + kx);
+            ac = fmaf(s_c[(c * win_h + wyy) * win_w + wxx], w, ac);
+            ar = fmaf(s_r[(c * win_h + wyy) * win_w + wxx], fabsf(w), ar);
+          }
+        }
+      s_ol[(co * out_h + y) * out_w + x] = fsub(ac, ar);
+      s_ou[(co * out_h + y) * out_w + x] = fadd(ac, ar);
+    }
+    __syncthreads();
+  }
+  const unsigned uWo = Wo, uHo = Ho;
+  for (unsigned t = threadIdx.x * V; t < n_out; t += blockDim.x * V) {
+    const unsigned q = t / uWo, x0 = t - q * uWo, co = q / uHo, y = q - co * uHo;
+    float lo[4] = {0.f, 0.f, 0.f, 0.f}, up[4] = {0.f, 0.f, 0.f, 0.f};
+    if (!empty && (int)y >= oy.lo && (int)y <= oy.hi && (int)x0 + V - 1 >= ox.lo && (int)x0 <= ox.hi) {
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        const int x = (int)x0 + e;
+        if (x >= ox.lo && x <= ox.hi) {
+          const int o = ((int)co * out_h + ((int)y - oy.lo)) * out_w + (x - ox.lo);
+          lo[e] = s_ol[o];
+          up[e] = s_ou[o];
+        }
+      }
+    }
+    store_elems(zl + t, lo, V);
+    store_elems(zu + t, up, V);
+  }
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
 }  // namespace
 }  // namespace fb
+
+extern "C" int fb_conv2d_identity_relax_f32(int op, const float* x_lb, const float* x_ub, const float* Wt,
+                                            const float* bias, float scale, float* y_lw, float* y_uw, float* y_lb,
+                                            float* y_ub, float* col_ws, int64_t rows, int64_t row_start, int Cin, int H,
+                                            int W, int Cout, int Kh, int Kw, int stride, int pad, int p, float eps,
+                                            int* violation, void* stream) {
+  if (!x_lb || !x_ub || !Wt || !y_lw || !y_uw || !y_lb || !y_ub || !col_ws) return FB_ERR_ARG;
+  if (rows < 0 || row_start < 0 || Cin <= 0 || H <= 0 || W <= 0 || Cout <= 0 || Kh <= 0 || Kw <= 0 || stride <= 0 || pad < 0 ||
+      !fb::valid_norm(p) || row_start + rows > (int64_t)Cin * H * W)
+    return FB_ERR_ARG;
+  if (op >= 0 && !((op >= FB_RELU && op <= FB_SQRT))) return FB_ERR_ARG;
+  const int Ho = (H + 2 * pad - Kh) / stride + 1, Wo = (W + 2 * pad - Kw) / stride + 1;
+  if (Ho <= 0 || Wo <= 0) return FB_ERR_SHAPE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t ncol = (int64_t)Cout * Ho * Wo;
+  fb::ProfileScope prof(fb::PK_CONV, 8.0 * (rows + 1) * ncol * Cin * Kh * Kw, 4.0 * (2.0 * (rows + 1) * ncol), stream);
+  // bias part: an ordinary convolution of one image
+  int rc = fb::launch_conv(x_lb, x_ub, Wt, bias, y_lb, y_ub, 1, Cin, H, W, Cout, Kh, Kw, stride, pad, Ho, Wo, st);
+  if (rc != FB_OK) return rc;
+  float* k_l = col_ws;
+  float* k_u = col_ws + ncol;
+  const int64_t want = fb::ceil_div(ncol, 256), cap = (int64_t)fb::device_info().sms * 8;
+  fb::identity_conv_columns_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, st>>>(
+      op, Wt, y_lb, y_ub, k_l, k_u, scale, Cin, H, W, Cout, Kh, Kw, stride, pad, Ho, Wo, p, eps, violation);
+  FB_LAUNCH_OK();
+  if (rows == 0) return FB_OK;
+  if (rows > 0x7fffffff) return FB_ERR_SHAPE;
+  if (ncol > 0x7fffffff) return FB_ERR_SHAPE;
+  if (Wo % 4 == 0 && fb::aligned16(y_lw) && fb::aligned16(y_uw))
+    fb::identity_conv_rows_kernel<4><<<(unsigned)rows, 256, 0, st>>>(Wt, k_l, k_u, y_lw, y_uw, scale, row_start, Cin, H, W,
+                                                                       Cout, Kh, Kw, stride, pad, Ho, Wo);
+  else
+    fb::identity_conv_rows_kernel<1><<<(unsigned)rows, 256, 0, st>>>(Wt, k_l, k_u, y_lw, y_uw, scale, row_start, Cin, H, W,
+                                                                       Cout, Kh, Kw, stride, pad, Ho, Wo);
+  FB_LAUNCH_OK();
+  return FB_OK;
+}
+
+extern "C" int fb_conv2d_windowed_f32(const float* x_lw, const float* x_uw, const float* Wt, float* y_lw, float* y_uw,
+                                      int64_t rows, int64_t row_start, int H0, int W0, const int* chain, int n_chain,
+                                      int Cin, int H, int W, int Cout, int Kh, int Kw, int stride, int pad,
+                                      void* stream) {
+  if (!x_lw || !x_uw || !Wt || !y_lw || !y_uw || (n_chain > 0 && !chain)) return FB_ERR_ARG;
+  if (rows < 0 || row_start < 0 || H0 <= 0 || W0 <= 0 || n_chain < 0 || Cin <= 0 || H <= 0 || W <= 0 || Cout <= 0 || Kh <= 0 ||
+      Kw <= 0 || stride <= 0 || pad < 0)
+    return FB_ERR_ARG;
+  if (n_chain > fb::kMaxChain) return FB_ERR_SHAPE;
+  fb::ConvChain ch;
+  ch.n = n_chain;
+  int h = H0, w = W0;
+  for (int i = 0; i < n_chain; ++i) {
+    ch.kh[i] = chain[4 * i], ch.kw[i] = chain[4 * i + 1], ch.stride[i] = chain[4 * i + 2], ch.pad[i] = chain[4 * i + 3];
+    if (ch.kh[i] <= 0 || ch.kw[i] <= 0 || ch.stride[i] <= 0 || ch.pad[i] < 0) return FB_ERR_ARG;
+    h = (h + 2 * ch.pad[i] - ch.kh[i]) / ch.stride[i] + 1;
+    w = (w + 2 * ch.pad[i] - ch.kw[i]) / ch.stride[i] + 1;
+  }
+  if (h != H || w != W) return FB_ERR_SHAPE;   // the chain must lead from the H0 x W0 image to this layer's input
+  const int Ho = (H + 2 * pad - Kh) / stride + 1, Wo = (W + 2 * pad - Kw) / stride + 1;
+  if (Ho <= 0 || Wo <= 0) return FB_ERR_SHAPE;
+  if (rows == 0) return FB_OK;
+  const double ncol = (double)Cout * Ho * Wo;
+  if (rows > 0x7fffffff || ncol > 0x7fffffff) return FB_ERR_SHAPE;
+  // the largest window any pixel reaches, in and out (the kernel sizes its shared memory by it)
+  int win_h = 1, win_w = 1, out_h = 1, out_w = 1;
+  for (int yi = 0; yi < H0; ++yi) {
+    fb::Span wy, wx;
+    fb::chain_window(ch, H0, W0, yi, 0, wy, wx);
+    const fb::Span oy = fb::span_after_conv(wy, Kh, stride, pad, Ho);
+    win_h = std::max(win_h, wy.hi - wy.lo + 1);
+    out_h = std::max(out_h, oy.hi - oy.lo + 1);
+  }
+  for (int xi = 0; xi < W0; ++xi) {
+    fb::Span wy, wx;
+    fb::chain_window(ch, H0, W0, 0, xi, wy, wx);
+    const fb::Span ox = fb::span_after_conv(wx, Kw, stride, pad, Wo);
+    win_w = std::max(win_w, wx.hi - wx.lo + 1);
+    out_w = std::max(out_w, ox.hi - ox.lo + 1);
+  }
+  const size_t smem = sizeof(float) * 2 * ((size_t)Cin * win_h * win_w + (size_t)Cout * out_h * out_w);
+  if (smem > (size_t)fb::device_info().smem_optin) return FB_ERR_SHAPE;   // windows too large to pay: use fb_conv2d_f32
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool vec = Wo % 4 == 0 && fb::aligned16(y_lw) && fb::aligned16(y_uw);
+  auto kern = vec ? fb::conv_window_kernel<4> : fb::conv_window_kernel<1>;
+  if (smem > 48 * 1024) FB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  fb::ProfileScope prof(fb::PK_CONV, 8.0 * rows * Cout * out_h * out_w * Cin * Kh * Kw,
+                        4.0 * (2.0 * rows * Cin * win_h * win_w + 2.0 * rows * ncol), stream);
+  kern<<<(unsigned)rows, 256, smem, st>>>(x_lw, x_uw, Wt, y_lw, y_uw, row_start, H0, W0, ch, Cin, H, W, Cout, Kh, Kw, stride, pad,
+                                          Ho, Wo, win_h, win_w, out_h, out_w);
+  FB_LAUNCH_OK();
+  return FB_OK;
+}
 
 extern "C" int fb_conv2d_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
                              const float* Wt, const float* bias, float* y_lw, float* y_uw, float* y_lb, float* y_ub,
                              int B, int Di, int Cin, int H, int W, int Cout, int Kh, int Kw, int stride, int pad,
                              void* stream) {
   if (!x_lw || !x_uw || !x_lb || !x_ub || !Wt || !y_lw || !y_uw || !y_lb || !y_ub) return FB_ERR_ARG;
-  if (B < 0 || Di <= 0 || Cin <= 0 || H <= 0 || W <= 0 || Cout <= 0 || Kh <= 0 || Kw <= 0 || stride <= 0 || pad < 0)
+  // (Di == 0: the bias part alone)
+  if (B < 0 || Di < 0 || Cin <= 0 || H <= 0 || W <= 0 || Cout <= 0 || Kh <= 0 || Kw <= 0 || stride <= 0 || pad < 0)
     return FB_ERR_ARG;
   const int Ho = (H + 2 * pad - Kh) / stride + 1, Wo = (W + 2 * pad - Kw) / stride + 1;
   if (Ho <= 0 || Wo <= 0) return FB_ERR_SHAPE;

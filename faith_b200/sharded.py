@@ -14,6 +14,8 @@ library's one-shot exchange over NVLink.  Without one (CPU tests of the host log
 partial norms are reduced through torch.distributed.  One perturbed word only: the whole dim_in axis is one norm
 block here (the CNN of the benchmark perturbs every pixel), and the C entry points reject anything else.
 """
+import ctypes
+
 import torch
 
 from . import _lib, ops
@@ -77,6 +79,55 @@ def concretize_sharded(lw, uw, lb, ub, p, eps, comm, algo=0, part_ws=None):
     return l, u
 
 
+def conv_identity_relax(op, image_lb, image_ub, weight, bias, rows, row_start, stride, pad, p, eps, scale=1.0):
+    """First convolution of an all-pixels-perturbed image and the relaxation after it (op None: convolution only), for
+    the dim_in rows [row_start, row_start + rows): fb_conv2d_identity_relax_f32."""
+    dev = ops._chk(image_lb, image_ub, weight, bias)
+    C, H, W = image_lb.shape[-3:]
+    Co, _, Kh, Kw = weight.shape
+    Ho, Wo = (H + 2 * pad - Kh) // stride + 1, (W + 2 * pad - Kw) // stride + 1
+    y_lw = torch.empty(1, rows, Co, Ho, Wo, device=dev)
+    y_uw = torch.empty_like(y_lw)
+    y_lb = torch.empty(1, Co, Ho, Wo, device=dev)
+    y_ub = torch.empty_like(y_lb)
+    ws = torch.empty(2 * Co * Ho * Wo, device=dev)
+    with torch.cuda.device(dev):
+        check(load().fb_conv2d_identity_relax_f32(-1 if op is None else op, image_lb.data_ptr(), image_ub.data_ptr(),
+                                                  weight.data_ptr(), bias.data_ptr() if bias is not None else None,
+                                                  float(scale), y_lw.data_ptr(), y_uw.data_ptr(), y_lb.data_ptr(),
+                                                  y_ub.data_ptr(), ws.data_ptr(), rows, row_start, C, H, W, Co, Kh, Kw,
+                                                  stride, pad, ops.norm_code(p), float(eps), None, ops._stream()),
+              "fb_conv2d_identity_relax_f32")
+    return y_lw, y_uw, y_lb, y_ub
+
+
+def conv_windowed(x, weight, bias, stride, pad, row_start, H0, W0, chain):
+    """A later convolution of rows that are zero outside the window their pixel reaches through `chain`, the list of
+    (kernel height, kernel width, stride, padding) of the convolutions so far: the weight part through
+    fb_conv2d_windowed_f32, the bias part through the ordinary kernel."""
+    lw, uw, lb, ub = x
+    dev = ops._chk(lw, uw, lb, ub, weight, bias)
+    _, rows, C, H, W = lw.shape
+    Co, _, Kh, Kw = weight.shape
+    Ho, Wo = (H + 2 * pad - Kh) // stride + 1, (W + 2 * pad - Kw) // stride + 1
+    y_lw = torch.empty(1, rows, Co, Ho, Wo, device=dev)
+    y_uw = torch.empty_like(y_lw)
+    y_lb = torch.empty(1, Co, Ho, Wo, device=dev)
+    y_ub = torch.empty_like(y_lb)
+    lib = load()
+    flat = [int(v) for c in chain for v in c]
+    chain_arr = (ctypes.c_int * max(1, len(flat)))(*flat)
+    with torch.cuda.device(dev):
+        check(lib.fb_conv2d_windowed_f32(lw.data_ptr(), uw.data_ptr(), weight.data_ptr(), y_lw.data_ptr(), y_uw.data_ptr(),
+                                         rows, row_start, H0, W0, chain_arr, len(chain), C, H, W, Co, Kh, Kw,
+                                         stride, pad, ops._stream()), "fb_conv2d_windowed_f32")
+        check(lib.fb_conv2d_f32(lw.data_ptr(), uw.data_ptr(), lb.data_ptr(), ub.data_ptr(), weight.data_ptr(),
+                                bias.data_ptr() if bias is not None else None, y_lw.data_ptr(), y_uw.data_ptr(),
+                                y_lb.data_ptr(), y_ub.data_ptr(), 1, 0, C, H, W, Co, Kh, Kw, stride, pad, ops._stream()),
+              "fb_conv2d_f32")
+    return y_lw, y_uw, y_lb, y_ub
+
+
 class CnnVerifier:
     """Forward bound pass of conv -> relu -> conv -> relu -> linear on one image with every pixel
     perturbed (dim_in = C*H*W), the dim_in axis sharded over the ranks of `group`.
@@ -99,21 +150,38 @@ class CnnVerifier:
             else:
                 self.layers.append(ly)
 
-    def forward(self, image, p, eps, rank=0, world=1):
+    def forward(self, image, p, eps, rank=0, world=1, dense=False):
+        """dense=True materialises the identity input and runs every convolution densely (the general kernels; kept
+        for comparison).  Otherwise the structure of the identity input is used: the first convolution and its
+        relaxation are written from the filter alone, later convolutions only compute the window each row can reach."""
         C, H, W = image.shape
         di = C * H * W
         base, rem = divmod(di, world)
         start = rank * base + max(0, rank - (world - rem))
         size = base + (1 if rank >= world - rem else 0)
-        # identity dependence on every pixel: the local rows of eye(di)
-        lw = torch.zeros(size, di, device=self.device)
-        lw[torch.arange(size, device=self.device), start + torch.arange(size, device=self.device)] = 1.0
-        lw = lw.view(1, size, C, H, W)
-        uw = lw.clone()
         lb = image.to(self.device, torch.float32).view(1, C, H, W).contiguous()
         ub = lb.clone()
-        for ly in self.layers:
-            if ly[0] == "conv":
+        layers = list(self.layers)
+        chain = None      # geometry of the convolutions so far, while the rows keep their window structure
+        if dense or not layers or layers[0][0] != "conv":
+            # identity dependence on every pixel: the local rows of eye(di)
+            lw = torch.zeros(size, di, device=self.device)
+            lw[torch.arange(size, device=self.device), start + torch.arange(size, device=self.device)] = 1.0
+            lw = lw.view(1, size, C, H, W)
+            uw = lw.clone()
+        else:
+            ly = layers.pop(0)
+            fuse = bool(layers) and layers[0][0] == "relu"
+            if fuse:
+                layers.pop(0)
+            lw, uw, lb, ub = conv_identity_relax(FB_RELU if fuse else None, lb, ub, ly[1], ly[2], size, start, ly[3], ly[4],
+                                                 p, eps)
+            chain = [(ly[1].shape[-2], ly[1].shape[-1], ly[3], ly[4])]
+        for ly in layers:
+            if ly[0] == "conv" and chain is not None:
+                lw, uw, lb, ub = conv_windowed((lw, uw, lb, ub), ly[1], ly[2], ly[3], ly[4], start, H, W, chain)
+                chain.append((ly[1].shape[-2], ly[1].shape[-1], ly[3], ly[4]))
+            elif ly[0] == "conv":
                 lw, uw, lb, ub = ops.conv2d((lw, uw, lb, ub), ly[1], ly[2], ly[3], ly[4])
             elif ly[0] == "relu":
                 shp_w, shp_b = lw.shape, lb.shape

@@ -356,12 +356,38 @@ int fb_merge_heads_f32(const float* x_w, const float* x_b, float* z_w, float* z_
  * is the batch axis of the convolution.  Replaces the commented-out
  * c_convolution_verification (kernel.cpp:268-295).
  * x_lw,x_uw [B, Di, Cin, H, W]; x_lb,x_ub [B, Cin, H, W]; Wt [Cout, Cin, Kh, Kw]; bias [Cout] or
- * NULL; y_lw,y_uw [B, Di, Cout, Ho, Wo]; y_lb,y_ub [B, Cout, Ho, Wo]. */
+ * NULL; y_lw,y_uw [B, Di, Cout, Ho, Wo]; y_lb,y_ub [B, Cout, Ho, Wo].  Di may be 0 (bias part alone). */
 int fb_conv2d_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
                   const float* Wt, const float* bias,
                   float* y_lw, float* y_uw, float* y_lb, float* y_ub,
                   int B, int Di, int Cin, int H, int W, int Cout, int Kh, int Kw,
                   int stride, int pad, void* stream);
+
+/* Convolutions behind an identity input: every pixel of a [Cin, H, W] image perturbed, dim_in = Cin * H * W, input
+ * bound lw = uw = scale * I, lb / ub = the image (the convention of fb_conv2d_f32 with dim_in as batch axis; the
+ * reference's stub, HandTunedKernels/convolution_verification.cu:228-238, has no such shortcut).
+ *
+ * fb_conv2d_identity_relax_f32: first convolution and the relaxation `op` that follows it (op < 0: convolution
+ * only) for the rows [row_start, row_start + rows) of dim_in (a shard; all of them: 0, Cin*H*W).  Nothing is read
+ * but the filter: row r of the result is scale * W at the taps that fall on pixel r and zero elsewhere, and the
+ * dual norm of every output column over ALL of dim_in is the norm of the filter taps inside the image, so the
+ * concretisation needs no reduction over rows (or ranks).  y_lw, y_uw [rows, Cout, Ho, Wo]; y_lb, y_ub
+ * [Cout, Ho, Wo]; col_ws: 2 * Cout * Ho * Wo floats of scratch.  Equals fb_conv2d_f32 on the materialised identity
+ * followed by fb_relax_f32 up to the summation order of the column norms.
+ *
+ * fb_conv2d_windowed_f32: a later convolution of such rows (weight part only).  Row r stands for pixel
+ * (yi, xi) = ((r / W0) % H0, r % W0) of the original H0 x W0 image and is zero outside the window that pixel reaches
+ * through the convolutions before this one: `chain` is a HOST array of n_chain x 4 ints (kernel height, kernel width,
+ * stride, padding), first convolution first (n_chain <= 8; it must lead from H0 x W0 to this layer's H x W, else
+ * FB_ERR_SHAPE).  Outputs whose taps miss the window are stored as zero, the others equal fb_conv2d_f32's bit for
+ * bit.  FB_ERR_SHAPE when the largest window does not fit in shared memory (use fb_conv2d_f32 then). */
+int fb_conv2d_identity_relax_f32(int op, const float* x_lb, const float* x_ub, const float* Wt, const float* bias,
+                                 float scale, float* y_lw, float* y_uw, float* y_lb, float* y_ub, float* col_ws,
+                                 int64_t rows, int64_t row_start, int Cin, int H, int W, int Cout, int Kh, int Kw,
+                                 int stride, int pad, int p, float eps, int* violation, void* stream);
+int fb_conv2d_windowed_f32(const float* x_lw, const float* x_uw, const float* Wt, float* y_lw, float* y_uw,
+                           int64_t rows, int64_t row_start, int H0, int W0, const int* chain, int n_chain,
+                           int Cin, int H, int W, int Cout, int Kh, int Kw, int stride, int pad, void* stream);
 
 /* ---- whole-model driver: forward bound pass of a BERT-style encoder ---------------------
  * Follows VerifierForward.verify_safety (VerifierForward.py:93-119) for a batch of S

@@ -150,3 +150,37 @@ def test_config5_cnn_full_size_properties():
     x = torch.cat([img.unsqueeze(0), img.unsqueeze(0) + delta])
     y = net(x)
     assert bool((y >= l.reshape(1, -1) - 1e-4).all()) and bool((y <= u.reshape(1, -1) + 1e-4).all())
+
+
+def test_config5_cnn_full_size_against_the_oracle():
+    """C5 at full size against the CPU oracle: the whole pass (both paths of the driver: the structured one and the one
+    that materialises the identity and runs every convolution densely), and the two convolutions on their own at
+    dim_in = 3072, the second one (16 -> 32, stride 2) on the relaxed output of the first."""
+    from faith_b200 import ops
+    from faith_b200.sharded import CnnVerifier
+    layers = O.make_cnn(5)
+    img = torch.rand(3, 32, 32, generator=torch.Generator().manual_seed(5))
+    eps, p = 2.0 / 255, float("inf")
+    ol, ou = O.cnn_forward(layers, img, p, eps)
+    l64, u64 = O.cnn_forward([tuple(t.double() if isinstance(t, torch.Tensor) else t for t in ly) for ly in layers],
+                             img.double(), p, eps)
+    ver = CnnVerifier(layers, DEV)
+    for dense in (False, True):
+        l, u = ver.forward(img, p, eps, dense=dense)
+        helpers.assert_within_noise(l, ol, l64, "l dense=%s" % dense)
+        helpers.assert_within_noise(u, ou, u64, "u dense=%s" % dense)
+    di = 3072
+    eye = torch.eye(di).view(1, di, 3, 32, 32)
+    x0 = O.OBounds(p, eps, eye, img.unsqueeze(0), eye.clone(), img.unsqueeze(0))
+    o1 = O.conv_bounds(x0, layers[0][1], layers[0][2], layers[0][3], layers[0][4])
+    g1 = ops.conv2d((eye.to(DEV), eye.to(DEV), img.unsqueeze(0).to(DEV), img.unsqueeze(0).to(DEV)),
+                    layers[0][1].to(DEV), layers[0][2].to(DEV), layers[0][3], layers[0][4])
+    for a, k in zip(g1, ("lw", "uw", "lb", "ub")):
+        helpers.assert_close(a, getattr(o1, k), "conv1 " + k)
+    r1 = O.tokens_as_conv(O.conv_as_tokens(o1).relu(), *o1.lb.shape[1:])
+    o2 = O.conv_bounds(r1, layers[2][1], layers[2][2], layers[2][3], layers[2][4])
+    g2 = ops.conv2d((r1.lw.to(DEV), r1.uw.to(DEV), r1.lb.to(DEV), r1.ub.to(DEV)), layers[2][1].to(DEV), layers[2][2].to(DEV),
+                    layers[2][3], layers[2][4])
+    for a, k in zip(g2, ("lw", "uw", "lb", "ub")):
+        # K = 144 products of magnitude ~0.05: two fp32 summation orders
+        helpers.assert_close(a, getattr(o2, k), "conv2 " + k, atol=2e-6)

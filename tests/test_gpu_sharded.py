@@ -61,3 +61,85 @@ def test_cnn_pass_matches_oracle():
     x = img.unsqueeze(0) + (torch.rand(256, 3, 8, 8, generator=g) * 2 - 1) * (2.0 / 255)
     y = net(x)
     assert bool((y >= l.cpu() - 1e-5).all()) and bool((y <= u.cpu() + 1e-5).all())
+
+
+@pytest.mark.parametrize("stride,pad,hw", [(1, 1, 8), (2, 1, 9)])
+def test_first_convolution_from_the_filter_alone(stride, pad, hw):
+    """fb_conv2d_identity_relax_f32 (first convolution + relu of an all-pixels-perturbed image, written from the filter
+    alone, for a shard of the rows) against the general kernels on the materialised identity and against the oracle."""
+    from faith_b200 import ops, sharded
+    from faith_b200._lib import FB_RELU
+    g = torch.Generator().manual_seed(31)
+    C, Co, eps = 3, 5, 0.05
+    img = torch.rand(C, hw, hw, generator=g)
+    wt = torch.randn(Co, C, 3, 3, generator=g) * 0.3
+    bias = torch.randn(Co, generator=g) * 0.1
+    di = C * hw * hw
+    eye = torch.eye(di).view(1, di, C, hw, hw)
+    for p in (1.0, 2.0, float("inf")):
+        ob = O.conv_bounds(O.OBounds(p, eps, eye, img.unsqueeze(0), eye.clone(), img.unsqueeze(0)), wt, bias, stride, pad)
+        flat = O.conv_as_tokens(ob)
+        ref = O.tokens_as_conv(flat.relu(), *ob.lb.shape[1:])
+        start, rows = 17, di - 40      # a shard in the middle of dim_in
+        lb = img.unsqueeze(0).to(DEV)
+        got = sharded.conv_identity_relax(FB_RELU, lb, lb.clone(), wt.to(DEV), bias.to(DEV), rows, start, stride, pad, p, eps)
+        helpers.assert_close(got[0][0], ref.lw[0, start:start + rows], "lw p=%s" % p)
+        helpers.assert_close(got[1][0], ref.uw[0, start:start + rows], "uw p=%s" % p)
+        helpers.assert_close(got[2], ref.lb, "lb p=%s" % p)
+        helpers.assert_close(got[3], ref.ub, "ub p=%s" % p)
+        plain = sharded.conv_identity_relax(None, lb, lb.clone(), wt.to(DEV), bias.to(DEV), rows, start, stride, pad, p, eps)
+        helpers.assert_close(plain[0][0], ob.lw[0, start:start + rows], "conv lw")
+        helpers.assert_close(plain[3], ob.ub, "conv ub")
+
+
+@pytest.mark.parametrize("hw,geoms,start,drop", [
+    (10, [(3, 1, 1), (3, 2, 1)], 0, 0),                # the benchmark CNN's geometry; width 5 after: scalar stores
+    (16, [(3, 1, 1), (3, 2, 1), (3, 1, 1)], 0, 0),     # three convolutions; widths 16, 8, 8: 16-byte stores
+    (12, [(3, 2, 1), (5, 1, 2), (3, 2, 0)], 29, 61),   # strided first layer, 5x5 taps, no padding; a shard of dim_in
+    (9, [(2, 3, 0), (3, 1, 1)], 0, 0),                 # stride above the kernel size: some pixels reach nothing
+])
+def test_windowed_convolution_equals_the_dense_kernel_bit_for_bit(hw, geoms, start, drop):
+    """Later convolutions of rows that are zero outside the window of their pixel: the windowed kernel against the dense
+    one on the same rows, layer after layer (geoms: kernel size, stride, padding per convolution)."""
+    from faith_b200 import ops, sharded
+    from faith_b200._lib import FB_RELU
+    g = torch.Generator().manual_seed(32)
+    C, eps = 3, 0.05
+    chans = [C, 6, 7, 5][:len(geoms) + 1]
+    img = torch.rand(C, hw, hw, generator=g)
+    ws = [(torch.randn(chans[i + 1], chans[i], k, k, generator=g) * 0.3).to(DEV) for i, (k, _, _) in enumerate(geoms)]
+    bs = [(torch.randn(chans[i + 1], generator=g) * 0.1).to(DEV) for i in range(len(geoms))]
+    di = C * hw * hw
+    rows = di - start - drop
+    lb = img.unsqueeze(0).to(DEV)
+    k, stride, pad = geoms[0]
+    x = sharded.conv_identity_relax(FB_RELU, lb, lb.clone(), ws[0], bs[0], rows, start, stride, pad, float("inf"), eps)
+    chain = [(k, k, stride, pad)]
+    for (k, stride, pad), w, b in zip(geoms[1:], ws[1:], bs[1:]):
+        dense = ops.conv2d(x, w, b, stride, pad)
+        win = sharded.conv_windowed(x, w, b, stride, pad, start, hw, hw, chain)
+        for got, want, name in zip(win, dense, ("lw", "uw", "lb", "ub")):
+            assert torch.equal(got, want), (name, len(chain))
+        assert float(dense[0].abs().max()) > 0
+        chain.append((k, k, stride, pad))
+        x = win
+
+
+def test_windowed_convolution_rejects_a_chain_that_does_not_lead_to_its_input():
+    from faith_b200 import sharded, FaithError
+    x = tuple(torch.zeros(s, device=DEV) for s in ((1, 4, 2, 6, 6), (1, 4, 2, 6, 6), (1, 2, 6, 6), (1, 2, 6, 6)))
+    w = torch.zeros(3, 2, 3, 3, device=DEV)
+    with pytest.raises(FaithError):
+        sharded.conv_windowed(x, w, None, 1, 1, 0, 6, 6, [(3, 3, 2, 1)])    # 6x6 through stride 2 is 3x3, not 6x6
+
+
+def test_cnn_pass_structured_path_equals_dense_path():
+    from faith_b200.sharded import CnnVerifier
+    layers = O.make_cnn(5, c_in=3, hw=8)
+    img = torch.rand(3, 8, 8, generator=torch.Generator().manual_seed(5))
+    ver = CnnVerifier(layers, DEV)
+    for p in (2.0, float("inf")):
+        l0, u0 = ver.forward(img, p, 2.0 / 255, dense=True)
+        l1, u1 = ver.forward(img, p, 2.0 / 255)
+        helpers.assert_close(l1, l0, "l p=%s" % p)
+        helpers.assert_close(u1, u0, "u p=%s" % p)

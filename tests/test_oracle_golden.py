@@ -64,8 +64,10 @@ def test_bounds_contain_concrete_forward():
     assert float(u[0] - l[0]) < 2.0  # and the bound is finite and of sane width at this eps
 
 
-def test_conv_oracle_agrees_with_im2col_matmul():
-    """Ties the (otherwise unpinned) conv restatement to the pinned matmul: unfold + matmul."""
+@pytest.mark.parametrize("stride,pad,k", [(1, 1, 3), (2, 1, 3), (2, 0, 3), (1, 2, 5)])
+def test_conv_oracle_agrees_with_im2col_matmul(stride, pad, k):
+    """Ties the (otherwise unpinned) conv restatement to the pinned matmul: unfold + matmul, for the strides and
+    paddings of the benchmark CNN (3x3: stride 1 pad 1, stride 2 pad 1) and two more."""
     import torch.nn.functional as F
     g = torch.Generator().manual_seed(502)
     B, Di, C, H, W, Co = 1, 6, 3, 8, 8, 5
@@ -73,17 +75,21 @@ def test_conv_oracle_agrees_with_im2col_matmul():
     uw = torch.rand(B, Di, C, H, W, generator=g) - 0.5
     lb = torch.rand(B, C, H, W, generator=g)
     ub = lb + torch.rand(B, C, H, W, generator=g)
-    wt = torch.randn(Co, C, 3, 3, generator=g) * 0.3
-    o = O.conv_bounds(O.OBounds(2.0, 0.1, lw, lb, uw, ub), wt, None, 1, 1)
+    wt = torch.randn(Co, C, k, k, generator=g) * 0.3
+    o = O.conv_bounds(O.OBounds(2.0, 0.1, lw, lb, uw, ub), wt, None, stride, pad)
+    Ho, Wo = o.lw.shape[-2:]
 
-    def cols(t):  # [N, C, H, W] -> [N, H*W, C*9]
-        return F.unfold(t, 3, padding=1).transpose(1, 2)
+    def cols(t):  # [N, C, H, W] -> [N, Ho*Wo, C*k*k]
+        return F.unfold(t, k, padding=pad, stride=stride).transpose(1, 2)
 
     xw = O.OBounds(2.0, 0.1, cols(lw[0]).transpose(0, 1).unsqueeze(0), cols(lb), cols(uw[0]).transpose(0, 1).unsqueeze(0),
                    cols(ub))
-    m = xw.matmul(wt.reshape(Co, -1))  # lw [1, H*W, Di, Co]
-    helpers.assert_close(m.lw[0].permute(1, 2, 0).reshape(Di, Co, H, W), o.lw[0], "lw", atol=2e-6)
-    helpers.assert_close(m.ub[0].transpose(0, 1).reshape(Co, H, W), o.ub[0], "ub", atol=2e-6)
+    m = xw.matmul(wt.reshape(Co, -1))  # lw [1, Ho*Wo, Di, Co]
+    # two fp32 summation orders of K = C*k*k terms of magnitude ~0.1: absolute part scaled to the summed magnitude
+    helpers.assert_close(m.lw[0].permute(1, 2, 0).reshape(Di, Co, Ho, Wo), o.lw[0], "lw", atol=2e-6)
+    helpers.assert_close(m.uw[0].permute(1, 2, 0).reshape(Di, Co, Ho, Wo), o.uw[0], "uw", atol=2e-6)
+    helpers.assert_close(m.lb[0].transpose(0, 1).reshape(Co, Ho, Wo), o.lb[0], "lb", atol=2e-6)
+    helpers.assert_close(m.ub[0].transpose(0, 1).reshape(Co, Ho, Wo), o.ub[0], "ub", atol=2e-6)
 
 
 def test_oracle_search_loop_matches_the_reference_verifier():
