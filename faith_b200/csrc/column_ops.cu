@@ -7,6 +7,8 @@
 // its 256 threads are (column lanes) x (row groups); the reduction over Di runs down the
 // row groups, then across them by warp shuffles and a small shared-memory tree.
 // Transposed layout [rows, Do, Di] (the reference's pybind layout): one warp per column.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace fb {
@@ -357,6 +359,47 @@ col_norm_partials_native(const float* __restrict__ lw, const float* __restrict__
   }
 }
 
+// The same for a tall operand with few column tiles (the CNN: one image, dim_in = 3072 rows): a cluster of kSplit
+// blocks shares a column tile, each block accumulates a contiguous range of the rows, and block 0 of the cluster
+// combines the kSplit partial results through distributed shared memory, in block order (so the value does not
+// depend on scheduling).
+constexpr int kSplit = 8;
+template <int VEC>
+__global__ void __launch_bounds__(kThreads)
+col_norm_partials_split(const float* __restrict__ lw, const float* __restrict__ uw, float* __restrict__ part_l,
+                        float* __restrict__ part_u, int Di, int Do, int ntiles, int p) {
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  __shared__ __align__(16) float s_red[2 * 8 * kCW];
+  __shared__ float s_part[2 * kCW];
+  const unsigned cr = cluster.block_rank();
+  const int64_t tile = blockIdx.x / kSplit;
+  const int64_t row = tile / ntiles;
+  const int c0 = (int)(tile % ntiles) * kCW;
+  const int tid = threadIdx.x;
+  const int chunk = (Di + kSplit - 1) / kSplit;
+  const int r0 = min(Di, (int)cr * chunk), r1 = min(Di, r0 + chunk);
+  float l, u;
+  const size_t base = (size_t)row * Di * Do + (size_t)r0 * Do;
+  tile_concretize<VEC, false>(lw + base, uw + base, r1 - r0, Do, c0, 1, p, 0.f, nullptr, nullptr, s_red, 0.f, 0.f, l, u, true);
+  if (tid < kCW) {
+    s_part[tid] = l;
+    s_part[kCW + tid] = u;
+  }
+  cluster.sync();
+  if (cr == 0 && tid < kCW && c0 + tid < Do) {
+    float sl = l, su = u;
+    for (unsigned k = 1; k < kSplit; ++k) {
+      const float* rp = cluster.map_shared_rank(s_part, k);
+      sl = norm_combine(p, sl, rp[tid]);
+      su = norm_combine(p, su, rp[kCW + tid]);
+    }
+    part_l[(size_t)row * Do + c0 + tid] = sl;
+    part_u[(size_t)row * Do + c0 + tid] = su;
+  }
+  cluster.sync();   // the other blocks' shared memory stays alive until block 0 has read it
+}
+
 template <int VEC>
 __global__ void __launch_bounds__(kThreads)
 col_relax_apply_native(int op, const float* __restrict__ lw, const float* __restrict__ uw,
@@ -624,6 +667,24 @@ extern "C" int fb_norm_partials_f32(const float* lw, const float* uw, float* par
   ProfileScope prof(PK_RELAX, 4.0 * mw, 4.0 * (2 * mw + 2.0 * rows * Do), stream);
   const size_t smem = sizeof(float) * 2 * 8 * kCW;
   const bool vec = Do % 4 == 0 && aligned16(lw) && aligned16(uw);
+  if (blocks < 2 * (int64_t)device_info().sms && Di_local >= 64 * kSplit) {
+    // few column tiles, many rows: split the rows over a cluster
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(blocks * kSplit));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = kSplit;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    FB_CUDA_OK(cudaLaunchKernelEx(&cfg, vec ? col_norm_partials_split<4> : col_norm_partials_split<1>, lw, uw, part_l, part_u,
+                                  Di_local, Do, ntiles, p));
+    return FB_OK;
+  }
   if (vec) col_norm_partials_native<4><<<(unsigned)blocks, kThreads, smem, (cudaStream_t)stream>>>(lw, uw, part_l, part_u, Di_local, Do, ntiles, p);
   else col_norm_partials_native<1><<<(unsigned)blocks, kThreads, smem, (cudaStream_t)stream>>>(lw, uw, part_l, part_u, Di_local, Do, ntiles, p);
   FB_LAUNCH_OK();

@@ -313,51 +313,72 @@ conv_window_kernel(const float* __restrict__ x_lo, const float* __restrict__ x_u
   const float* iu = x_up + (int64_t)blockIdx.x * n_in;
   float* zl = y_lo + (int64_t)blockIdx.x * n_out;
   float* zu = y_up + (int64_t)blockIdx.x * n_out;
-  if (!empty) {
-    for (int i = threadIdx.x; i < Cin * ah * aw; i += blockDim.x) {
-      const int x = i % aw, y = (i / aw) % ah, c = i / (aw * ah);
-      const int64_t o = ((int64_t)c * H + wy.lo + y) * W + wx.lo + x;
-      const float lo = __ldg(il + o), up = __ldg(iu + o);
-      s_c[(c * win_h + y) * win_w + x] = fmul(fadd(lo, up), 0.5f);
-      s_r[(c * win_h + y) * win_w + x] = fmul(fsub(up, lo), 0.5f);
+  // 1. zeros everywhere outside the output window: these stores depend on nothing and drain while the window is
+  //    computed (a thread owns whole groups of V elements, so nothing is written twice).  The position (y, x0) of a
+  //    thread's group is stepped without divisions: one step is blockDim.x * V elements = dq image rows and dx columns.
+  {
+    const unsigned uWo = Wo, uHo = Ho, step = blockDim.x * V;
+    const unsigned dq = step / uWo, dx = step - dq * uWo, dy = dq % uHo;
+    unsigned t = threadIdx.x * V;
+    unsigned q = t / uWo, x0 = t - q * uWo, y = q % uHo;
+    const float zero[4] = {0.f, 0.f, 0.f, 0.f};
+    for (; t < n_out; t += step) {
+      if (empty || (int)y < oy.lo || (int)y > oy.hi || (int)x0 + V - 1 < ox.lo || (int)x0 > ox.hi) {
+        store_elems(zl + t, zero, V);
+        store_elems(zu + t, zero, V);
+      }
+      x0 += dx;
+      y += dy;
+      if (x0 >= uWo) { x0 -= uWo; ++y; }
+      if (y >= uHo) y -= uHo;
     }
-    __syncthreads();
-    for (int i = threadIdx.x; i < Cout * bh * bw; i += blockDim.x) {
-      const int x = i % bw, y = (i / bw) % bh, co = i / (bw * bh);
-      const int iy0 = (oy.lo + y) * stride - pad - wy.lo, ix0 = (ox.lo + x) * stride - pad - wx.lo;  // window coordinates
-      float ac = 0.f, ar = 0.f;
-      for (int c = 0; c < Cin; ++c)
-        for (int ky = 0; ky < Kh; ++ky) {
-          const int wyy = iy0 + ky;
-          if (wyy < 0 || wyy >= ah) continue;
-          for (int kx = 0; kx < Kw; ++kx) {
-            const int wxx = ix0 + kx;
-            if (wxx < 0 || wxx >= aw) continue;
-            const float w = __ldg(Wt + (((int64_t)co * Cin + c) * Kh + ky) * Kw + kx);
-            ac = fmaf(s_c[(c * win_h + wyy) * win_w + wxx], w, ac);
-            ar = fmaf(s_r[(c * win_h + wyy) * win_w + wxx], fabsf(w), ar);
-          }
-        }
-      s_ol[(co * out_h + y) * out_w + x] = fsub(ac, ar);
-      s_ou[(co * out_h + y) * out_w + x] = fadd(ac, ar);
-    }
-    __syncthreads();
   }
-  const unsigned uWo = Wo, uHo = Ho;
-  for (unsigned t = threadIdx.x * V; t < n_out; t += blockDim.x * V) {
-    const unsigned q = t / uWo, x0 = t - q * uWo, co = q / uHo, y = q - co * uHo;
-    float lo[4] = {0.f, 0.f, 0.f, 0.f}, up[4] = {0.f, 0.f, 0.f, 0.f};
-    if (!empty && (int)y >= oy.lo && (int)y <= oy.hi && (int)x0 + V - 1 >= ox.lo && (int)x0 <= ox.hi) {
-#pragma unroll
-      for (int e = 0; e < V; ++e) {
-        const int x = (int)x0 + e;
-        if (x >= ox.lo && x <= ox.hi) {
-          const int o = ((int)co * out_h + ((int)y - oy.lo)) * out_w + (x - ox.lo);
-          lo[e] = s_ol[o];
-          up[e] = s_ou[o];
+  if (empty) return;
+  // 2. the window of the input, as centre and radius
+  for (int i = threadIdx.x; i < Cin * ah * aw; i += blockDim.x) {
+    const int x = i % aw, y = (i / aw) % ah, c = i / (aw * ah);
+    const int64_t o = ((int64_t)c * H + wy.lo + y) * W + wx.lo + x;
+    const float lo = __ldg(il + o), up = __ldg(iu + o);
+    s_c[(c * win_h + y) * win_w + x] = fmul(fadd(lo, up), 0.5f);
+    s_r[(c * win_h + y) * win_w + x] = fmul(fsub(up, lo), 0.5f);
+  }
+  __syncthreads();
+  // 3. the outputs that reach it (the taps inside the window are a contiguous range per axis)
+  for (int i = threadIdx.x; i < Cout * bh * bw; i += blockDim.x) {
+    const int x = i % bw, y = (i / bw) % bh, co = i / (bw * bh);
+    const int iy0 = (oy.lo + y) * stride - pad - wy.lo, ix0 = (ox.lo + x) * stride - pad - wx.lo;  // window coordinates
+    const int ky0 = max(0, -iy0), ky1 = min(Kh, ah - iy0), kx0 = max(0, -ix0), kx1 = min(Kw, aw - ix0);
+    float ac = 0.f, ar = 0.f;
+    for (int c = 0; c < Cin; ++c) {
+      const float* wp = Wt + ((int64_t)co * Cin + c) * Kh * Kw;
+      const int sb = (c * win_h + iy0) * win_w + ix0;
+      for (int ky = ky0; ky < ky1; ++ky)
+        for (int kx = kx0; kx < kx1; ++kx) {
+          const float w = __ldg(wp + ky * Kw + kx);
+          ac = fmaf(s_c[sb + ky * win_w + kx], w, ac);
+          ar = fmaf(s_r[sb + ky * win_w + kx], fabsf(w), ar);
         }
+    }
+    s_ol[(co * out_h + y) * out_w + x] = fsub(ac, ar);
+    s_ou[(co * out_h + y) * out_w + x] = fadd(ac, ar);
+  }
+  __syncthreads();
+  // 4. the groups of V elements that touch the output window
+  const int g0 = ox.lo / V, ng = ox.hi / V - g0 + 1;
+  for (int i = threadIdx.x; i < Cout * bh * ng; i += blockDim.x) {
+    const int gx = i % ng, y = (i / ng) % bh, co = i / (ng * bh);
+    const int x0 = (g0 + gx) * V;
+    float lo[4] = {0.f, 0.f, 0.f, 0.f}, up[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      const int x = x0 + e;
+      if (x >= ox.lo && x <= ox.hi) {
+        const int o = (co * out_h + y) * out_w + (x - ox.lo);
+        lo[e] = s_ol[o];
+        up[e] = s_ou[o];
       }
     }
+    const int64_t t = ((int64_t)co * Ho + oy.lo + y) * Wo + x0;
     store_elems(zl + t, lo, V);
     store_elems(zu + t, up, V);
   }

@@ -215,48 +215,84 @@ split_sign_gemv_rows(const float* __restrict__ a_lo, const float* __restrict__ a
 }
 
 // Narrow outputs with a long contraction (e.g. the 8192 -> 10 head of the CNN): a block owns eight
-// rows of A (one per warp) and walks K in chunks of 512; the chunk of W is staged in shared memory
-// once per block and read by all eight warps, the rows of A are read with 128-bit loads.
+// rows of A (one per warp) and walks K in chunks of 512.  The chunk of W is staged in shared memory once per block
+// (cp.async into the other of two buffers while the current chunk is computed) and read by all eight warps; the
+// rows of A are read with 128-bit loads, the next chunk's into registers before the current one is used, so that a
+// warp keeps 8 KB of loads in flight.  Dynamic shared memory: 2 * NMAX * 512 floats.
 constexpr int kGemvChunk = 512;
+__device__ __forceinline__ void gemv_cp16(float* dst, const float* src, bool valid) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  const int bytes = valid ? 16 : 0;   // 0: the 16 bytes are zero-filled and nothing is read
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
 template <int NMAX>
 __global__ void __launch_bounds__(kThreads)
 split_sign_gemv_tiled(const float* __restrict__ a_lo, const float* __restrict__ a_up,
                       const float* __restrict__ W, const float* __restrict__ bias,
                       float* __restrict__ c_lo, float* __restrict__ c_up, int64_t M, int N, int K) {
-  __shared__ __align__(16) float sw[NMAX][kGemvChunk];
+  extern __shared__ __align__(16) float gemv_sw[];   // [2][NMAX][kGemvChunk]
+  constexpr int J = kGemvChunk / 128;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t m = (int64_t)blockIdx.x * (kThreads / 32) + warp;
-  float sc[NMAX], sr[NMAX];
-#pragma unroll
-  for (int n = 0; n < NMAX; ++n) { sc[n] = 0.f; sr[n] = 0.f; }
-  for (int k0 = 0; k0 < K; k0 += kGemvChunk) {
+  auto stage_w = [&](int buf, int k0) {
     const int kc = min(kGemvChunk, K - k0);   // multiple of 4
     for (int f = threadIdx.x; f < NMAX * (kGemvChunk / 4); f += kThreads) {
       const int n = f / (kGemvChunk / 4), k4 = (f % (kGemvChunk / 4)) * 4;
-      float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (n < N && k4 < kc) w = *reinterpret_cast<const float4*>(W + (int64_t)n * K + k0 + k4);
-      *reinterpret_cast<float4*>(&sw[n][k4]) = w;
+      const bool ok = n < N && k4 < kc;
+      gemv_cp16(gemv_sw + ((size_t)buf * NMAX + n) * kGemvChunk + k4, ok ? W + (int64_t)n * K + k0 + k4 : W, ok);
     }
-    __syncthreads();
-    if (m < M) {
-      for (int k4 = lane * 4; k4 < kc; k4 += 128) {
-        const float4 lo = *reinterpret_cast<const float4*>(a_lo + m * K + k0 + k4);
-        const float4 up = *reinterpret_cast<const float4*>(a_up + m * K + k0 + k4);
-        const float c[4] = {fmul(fadd(lo.x, up.x), 0.5f), fmul(fadd(lo.y, up.y), 0.5f), fmul(fadd(lo.z, up.z), 0.5f), fmul(fadd(lo.w, up.w), 0.5f)};
-        const float r[4] = {fmul(fsub(up.x, lo.x), 0.5f), fmul(fsub(up.y, lo.y), 0.5f), fmul(fsub(up.z, lo.z), 0.5f), fmul(fsub(up.w, lo.w), 0.5f)};
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  auto load_a = [&](float4 (&lo)[J], float4 (&up)[J], int k0) {
+    const int kc = min(kGemvChunk, K - k0);
 #pragma unroll
-        for (int n = 0; n < NMAX; ++n) {
-          if (n < N) {
-            const float4 w = *reinterpret_cast<const float4*>(&sw[n][k4]);
-            sc[n] = fmaf(c[0], w.x, sc[n]); sr[n] = fmaf(r[0], fabsf(w.x), sr[n]);
-            sc[n] = fmaf(c[1], w.y, sc[n]); sr[n] = fmaf(r[1], fabsf(w.y), sr[n]);
-            sc[n] = fmaf(c[2], w.z, sc[n]); sr[n] = fmaf(r[2], fabsf(w.z), sr[n]);
-            sc[n] = fmaf(c[3], w.w, sc[n]); sr[n] = fmaf(r[3], fabsf(w.w), sr[n]);
-          }
+    for (int j = 0; j < J; ++j) {
+      const int k4 = lane * 4 + j * 128;
+      if (m < M && k0 < K && k4 < kc) {
+        lo[j] = __ldg(reinterpret_cast<const float4*>(a_lo + m * K + k0 + k4));
+        up[j] = __ldg(reinterpret_cast<const float4*>(a_up + m * K + k0 + k4));
+      } else {
+        lo[j] = make_float4(0.f, 0.f, 0.f, 0.f);   // exact zeros: they leave the sums as they are
+        up[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+  };
+  float sc[NMAX], sr[NMAX];
+#pragma unroll
+  for (int n = 0; n < NMAX; ++n) { sc[n] = 0.f; sr[n] = 0.f; }
+  float4 lo[J], up[J], nlo[J], nup[J];
+  stage_w(0, 0);
+  load_a(lo, up, 0);
+  int buf = 0;
+  for (int k0 = 0; k0 < K; k0 += kGemvChunk, buf ^= 1) {
+    const bool more = k0 + kGemvChunk < K;
+    if (more) stage_w(buf ^ 1, k0 + kGemvChunk);
+    load_a(nlo, nup, k0 + kGemvChunk);
+    if (more) asm volatile("cp.async.wait_group 1;" ::: "memory");
+    else asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    const float* sw = gemv_sw + (size_t)buf * NMAX * kGemvChunk;
+#pragma unroll
+    for (int j = 0; j < J; ++j) {
+      const int k4 = lane * 4 + j * 128;
+      const float c[4] = {fmul(fadd(lo[j].x, up[j].x), 0.5f), fmul(fadd(lo[j].y, up[j].y), 0.5f),
+                          fmul(fadd(lo[j].z, up[j].z), 0.5f), fmul(fadd(lo[j].w, up[j].w), 0.5f)};
+      const float r[4] = {fmul(fsub(up[j].x, lo[j].x), 0.5f), fmul(fsub(up[j].y, lo[j].y), 0.5f),
+                          fmul(fsub(up[j].z, lo[j].z), 0.5f), fmul(fsub(up[j].w, lo[j].w), 0.5f)};
+#pragma unroll
+      for (int n = 0; n < NMAX; ++n) {
+        if (n < N) {
+          const float4 w = *reinterpret_cast<const float4*>(sw + n * kGemvChunk + k4);
+          sc[n] = fmaf(c[0], w.x, sc[n]); sr[n] = fmaf(r[0], fabsf(w.x), sr[n]);
+          sc[n] = fmaf(c[1], w.y, sc[n]); sr[n] = fmaf(r[1], fabsf(w.y), sr[n]);
+          sc[n] = fmaf(c[2], w.z, sc[n]); sr[n] = fmaf(r[2], fabsf(w.z), sr[n]);
+          sc[n] = fmaf(c[3], w.w, sc[n]); sr[n] = fmaf(r[3], fabsf(w.w), sr[n]);
         }
       }
     }
-    __syncthreads();
+    __syncthreads();   // everyone is done with this buffer before the chunk after next is staged into it
+#pragma unroll
+    for (int j = 0; j < J; ++j) { lo[j] = nlo[j]; up[j] = nup[j]; }
   }
   if (m >= M) return;
 #pragma unroll
@@ -271,12 +307,58 @@ split_sign_gemv_tiled(const float* __restrict__ a_lo, const float* __restrict__ 
 #pragma unroll
     for (int n = 0; n < NMAX; ++n) {
       if (n < N) {
-        float lo = fsub(sc[n], sr[n]), up = fadd(sc[n], sr[n]);
-        if (bias != nullptr) { lo = fadd(lo, bias[n]); up = fadd(up, bias[n]); }
-        c_lo[m * N + n] = lo;
-        c_up[m * N + n] = up;
+        float lo1 = fsub(sc[n], sr[n]), up1 = fadd(sc[n], sr[n]);
+        if (bias != nullptr) { lo1 = fadd(lo1, bias[n]); up1 = fadd(up1, bias[n]); }
+        c_lo[m * N + n] = lo1;
+        c_up[m * N + n] = up1;
       }
     }
+  }
+}
+
+// A few rows with a long contraction (the bias row of the CNN head, M = 1): a block per row, K interleaved over its
+// threads, partial sums combined first inside each warp, then over the warps in warp order.
+template <int NMAX>
+__global__ void __launch_bounds__(kThreads)
+split_sign_gemv_block(const float* __restrict__ a_lo, const float* __restrict__ a_up, const float* __restrict__ W,
+                      const float* __restrict__ bias, float* __restrict__ c_lo, float* __restrict__ c_up, int N, int K) {
+  __shared__ float s_red[2][kThreads / 32][NMAX];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t m = blockIdx.x;
+  float sc[NMAX], sr[NMAX];
+#pragma unroll
+  for (int n = 0; n < NMAX; ++n) { sc[n] = 0.f; sr[n] = 0.f; }
+#pragma unroll 4
+  for (int k = threadIdx.x; k < K; k += kThreads) {
+    const float lo = __ldg(a_lo + m * K + k), up = __ldg(a_up + m * K + k);
+    const float c = fmul(fadd(lo, up), 0.5f), r = fmul(fsub(up, lo), 0.5f);
+#pragma unroll
+    for (int n = 0; n < NMAX; ++n) {
+      if (n < N) {
+        const float w = __ldg(W + (int64_t)n * K + k);
+        sc[n] = fmaf(c, w, sc[n]);
+        sr[n] = fmaf(r, fabsf(w), sr[n]);
+      }
+    }
+  }
+#pragma unroll
+  for (int n = 0; n < NMAX; ++n) {
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) {
+      sc[n] += __shfl_xor_sync(0xffffffffu, sc[n], s);
+      sr[n] += __shfl_xor_sync(0xffffffffu, sr[n], s);
+    }
+    if (lane == 0) { s_red[0][warp][n] = sc[n]; s_red[1][warp][n] = sr[n]; }
+  }
+  __syncthreads();
+  if (threadIdx.x < N) {
+    const int n = threadIdx.x;
+    float c = s_red[0][0][n], r = s_red[1][0][n];
+    for (int w = 1; w < kThreads / 32; ++w) { c = fadd(c, s_red[0][w][n]); r = fadd(r, s_red[1][w][n]); }
+    float lo = fsub(c, r), up = fadd(c, r);
+    if (bias != nullptr) { lo = fadd(lo, bias[n]); up = fadd(up, bias[n]); }
+    c_lo[m * N + n] = lo;
+    c_up[m * N + n] = up;
   }
 }
 
@@ -286,9 +368,16 @@ split_sign_gemv_tiled(const float* __restrict__ a_lo, const float* __restrict__ 
 int launch_split_sign_ffma(const float* a_lo, const float* a_up, const float* W, const float* bias, float* c_lo,
                            float* c_up, int64_t M, int N, int K, cudaStream_t st, int split_rows, int split_d) {
   if (M == 0 || N == 0) return FB_OK;
+  if (N <= 16 && split_rows == 0 && K >= 2048 && M <= 32) {
+    split_sign_gemv_block<16><<<(unsigned)M, kThreads, 0, st>>>(a_lo, a_up, W, bias, c_lo, c_up, N, K);
+    FB_LAUNCH_OK();
+    return FB_OK;
+  }
   if (N <= 16 && split_rows == 0 && K >= 1024 && K % 4 == 0 && aligned16(a_lo) && aligned16(a_up) && aligned16(W) &&
       ceil_div(M, kThreads / 32) <= 0x7fffffff) {
-    split_sign_gemv_tiled<16><<<(unsigned)ceil_div(M, kThreads / 32), kThreads, 0, st>>>(a_lo, a_up, W, bias, c_lo, c_up, M, N, K);
+    const size_t gemv_smem = sizeof(float) * 2 * 16 * kGemvChunk;
+    FB_CUDA_OK(cudaFuncSetAttribute(split_sign_gemv_tiled<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemv_smem));
+    split_sign_gemv_tiled<16><<<(unsigned)ceil_div(M, kThreads / 32), kThreads, gemv_smem, st>>>(a_lo, a_up, W, bias, c_lo, c_up, M, N, K);
     FB_LAUNCH_OK();
     return FB_OK;
   }

@@ -208,7 +208,11 @@ def test_context_with_values_in_projection_layout_matches_transposed_path():
 # ------------------------------------------------------------------ matmul
 @pytest.mark.parametrize("shape,Dy", [((1, 2, 64, 64), 64), ((1, 16, 64, 64), 128), ((2, 8, 128, 256), 512),
                                       ((1, 3, 24, 20), 7), ((1, 5, 33, 130), 129), ((1, 4, 64, 128), 2),
-                                      ((1, 1, 128, 512), 128)])
+                                      ((1, 1, 128, 512), 128),
+                                      # narrow output, long contraction (the head of the CNN): many rows through the
+                                      # chunked kernel (K a multiple of its 512-chunk, and not), one row (the bias
+                                      # part of every call here) through the block-per-row kernel
+                                      ((1, 1, 96, 4096), 10), ((1, 2, 40, 2308), 16), ((1, 1, 3, 8192), 10)])
 def test_matmul_shapes(shape, Dy):
     import types
     B, L, Di, Do = shape
