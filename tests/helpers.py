@@ -105,3 +105,39 @@ def assert_within_noise(got, ref32, ref64, what, c=8.0, rtol=RTOL, atol=ATOL):
     err = float((got - ref64).abs().max())
     bound = c * noise + atol + rtol * float(ref64.abs().max())
     assert err <= bound, "%s: max|got-ref64|=%.3e exceeds %.1f x fp32 noise %.3e (+tol) = %.3e" % (what, err, c, noise, bound)
+
+
+# worst observed (error against the fp64 run) / (fp32 noise of the reference restatement), per call site; printed
+# in the terminal summary of a GPU run (tests/conftest.py)
+ARBITER_RATIOS = {}
+
+
+def assert_arbitrated(got, ref32, ref64, what, c=4.0, rtol=RTOL, atol=ATOL):
+    """GEMM-shaped operators: two fp32 evaluation orders of a K-term sum differ by more than the per-operator bar
+    where the terms are large or cancel, so the fp64 run of the same algorithm is the arbiter.  Elementwise
+        |got - ref64| <= c * max|ref32 - ref64| + atol + rtol * |ref64|,   c <= 4:
+    the result may stray from the exact value by a few times what the reference's own fp32 evaluation strays, on top
+    of the per-operator bar."""
+    def d(t):
+        t = torch.as_tensor(np.asarray(t)) if not isinstance(t, torch.Tensor) else t.detach().cpu()
+        return t.double()
+    got, ref32, ref64 = d(got), d(ref32), d(ref64)
+    assert got.shape == ref64.shape, "%s: shape %s vs %s" % (what, tuple(got.shape), tuple(ref64.shape))
+    assert bool(torch.isfinite(got).all()), "%s: non-finite values" % what
+    noise = float((ref32 - ref64).abs().max())
+    err = (got - ref64).abs()
+    ratio = float(err.max()) / noise if noise > 0 else (0.0 if float(err.max()) == 0 else float("inf"))
+    ARBITER_RATIOS[what] = max(ARBITER_RATIOS.get(what, 0.0), ratio)
+    bound = c * noise + atol + rtol * ref64.abs()
+    bad = err > bound
+    if bool(bad.any()):
+        i = int(torch.argmax(err - bound))
+        raise AssertionError("%s: %d of %d outside %.0f x fp32 noise %.3e (+ bar); worst |got-ref64|=%.3e at flat index %d "
+                             "(got %.9g ref64 %.9g)" % (what, int(bad.sum()), bad.numel(), c, noise,
+                                                        float(err.flatten()[i]), i, float(got.flatten()[i]),
+                                                        float(ref64.flatten()[i])))
+
+
+def assert_bounds_arbitrated(g, o32, o64, what, c=4.0):
+    for k in ("lw", "uw", "lb", "ub"):
+        assert_arbitrated(getattr(g, k), getattr(o32, k), getattr(o64, k), "%s %s" % (what, k), c=c)

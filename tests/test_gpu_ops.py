@@ -171,9 +171,11 @@ def test_dot_product_tensor_core_shapes_match_fp64_and_repeat():
         Q = torch.einsum("bjmk,bik->bimj", yr, xl.abs())
         zl = torch.einsum("bimk,bjk->bimj", xc, yl) - torch.einsum("bimk,bjk->bimj", xr, yl.abs()) + P - Q
         zu = torch.einsum("bimk,bjk->bimj", xc, yu) + torch.einsum("bimk,bjk->bimj", xr, yu.abs()) + P + Q
-        for got, ref in ((first[0], zl * 0.25), (first[1], zu * 0.25)):
-            err = (got.double() - ref).abs()
-            assert bool((err <= 4e-6 + 1e-5 * ref.abs()).all()), float(err.max())
+        # the same formula evaluated in fp32 by the oracle's dot product gives the noise the fp64 value is the arbiter of
+        o32 = O.OBounds(float("inf"), 0.01, x[0].cpu(), x[2].cpu(), x[1].cpu(), x[3].cpu()).dot_product(
+            O.OBounds(float("inf"), 0.01, y[0].cpu(), y[2].cpu(), y[1].cpu(), y[3].cpu()))
+        helpers.assert_arbitrated(first[0], o32.lw * 0.25, zl * 0.25, "tcgen05 dot product lw")
+        helpers.assert_arbitrated(first[1], o32.uw * 0.25, zu * 0.25, "tcgen05 dot product uw")
 
 
 def test_context_with_values_in_projection_layout_matches_transposed_path():
@@ -225,9 +227,9 @@ def test_matmul_shapes(shape, Dy):
     o = O.OBounds(2.0, 0.5, *t).dense(W, bias)
     g = faith_b200.BoundsLite(2.0, 0.5, *[v.to(DEV) for v in t]).dense(
         types.SimpleNamespace(weight=W.to(DEV), bias=bias.to(DEV)))
-    # fp32 GEMMs with different summation order: error scales with sum_k |a_k w_k|, about
-    # sqrt(K) * |a| |w| ~ 0.3 here, so the absolute part of the bar is 1e-6 per unit of that sum
-    _cmp(g, o, "dense %s->%d" % (shape, Dy), rtol=1e-5, atol=2e-6)
+    # fp32 GEMMs with different summation order: judged against the fp64 run of the same algorithm
+    o64 = O.OBounds(2.0, 0.5, *[v.double() for v in t]).dense(W.double(), bias.double())
+    helpers.assert_bounds_arbitrated(g, o, o64, "dense %s->%d" % (shape, Dy))
 
 
 def test_matmul_tensor_core_stage_reuse_is_race_free():
@@ -321,14 +323,11 @@ def test_dot_product_shapes(B, Lx, Ly, Di, K, p):
     # The K-term sums reach 1e2..1e4 (operand ranges of a few units times K terms) and cancel, so two
     # fp32 evaluation orders (the reference's four separate GEMMs, the kernel's fused centre/radius
     # accumulation) differ by more than the per-operator bar near zeros of the result.  The result is
-    # therefore judged against the fp64 run of the same algorithm: within 4x the fp32 noise of the
-    # reference itself, plus an elementwise bar scaled to the size of the summed terms.
+    # therefore judged, element by element, against the fp64 run of the same algorithm: within 4x the fp32 noise
+    # of the reference itself on top of the per-operator bar.
     d = torch.float64
     o64 = O.OBounds(p, 0.5, *[v.to(d) for v in tx]).dot_product(O.OBounds(p, 0.5, *[v.to(d) for v in ty]))
-    for k in ("lw", "uw", "lb", "ub"):
-        helpers.assert_within_noise(getattr(g, k), getattr(o, k), getattr(o64, k), "dot %s" % k)
-    if p == 2.0:
-        _cmp(g, o, "dot", rtol=1e-5, atol=2e-6 * max(1.0, K / 8))
+    helpers.assert_bounds_arbitrated(g, o, o64, "dot K=%d" % K)
 
 
 def test_context_matches_oracle():
@@ -339,7 +338,8 @@ def test_context_matches_oracle():
     o = O.OBounds(2.0, 0.1, *tp).context(O.OBounds(2.0, 0.1, *tv))
     g = faith_b200.BoundsLite(2.0, 0.1, *[v.to(DEV) for v in tp]).context(
         faith_b200.BoundsLite(2.0, 0.1, *[v.to(DEV) for v in tv]))
-    _cmp(g, o, "context", rtol=1e-5, atol=4e-6)
+    o64 = O.OBounds(2.0, 0.1, *[v.double() for v in tp]).context(O.OBounds(2.0, 0.1, *[v.double() for v in tv]))
+    helpers.assert_bounds_arbitrated(g, o, o64, "context")
 
 
 def test_split_merge_heads_round_trip():
@@ -395,11 +395,11 @@ def test_c_bound_dot_product_qk(B, L, Di, K):
         x[0].transpose(2, 3).contiguous(), x[2].transpose(2, 3).contiguous(),
         y[0].transpose(2, 3).contiguous(), y[2].transpose(2, 3).contiguous(),
         z_lb, z_ub, z_lw, z_uw, B, L, K, Di, 0.5)
-    tol = dict(rtol=1e-5, atol=1e-6 * max(1.0, K / 8))
-    helpers.assert_close(z_lw.transpose(2, 3), o.lw, "qk lw", **tol)
-    helpers.assert_close(z_uw.transpose(2, 3), o.uw, "qk uw", **tol)
-    helpers.assert_close(z_lb, o.lb, "qk lb", **tol)
-    helpers.assert_close(z_ub, o.ub, "qk ub", **tol)
+    o64 = O.OBounds(2.0, 0.5, *[v.double() for v in tx]).dot_product(O.OBounds(2.0, 0.5, *[v.double() for v in ty]))
+    helpers.assert_arbitrated(z_lw.transpose(2, 3), o.lw, o64.lw, "c_bound qk lw")
+    helpers.assert_arbitrated(z_uw.transpose(2, 3), o.uw, o64.uw, "c_bound qk uw")
+    helpers.assert_arbitrated(z_lb, o.lb, o64.lb, "c_bound qk lb")
+    helpers.assert_arbitrated(z_ub, o.ub, o64.ub, "c_bound qk ub")
     # the caller-visible scratch receives the concretised operand ranges
     lx, ux = ox.concretize()
     ly, uy = oy.concretize()
@@ -426,11 +426,11 @@ def test_c_bound_dot_product_v(B, L, Di, Dout):
         x[0].transpose(2, 3).contiguous(), x[2].transpose(2, 3).contiguous(),
         y[0].transpose(2, 3).contiguous(), y[2].transpose(2, 3).contiguous(),
         z_lb, z_ub, z_lw, z_uw, B, L, Dout, Di, 0.5)
-    tol = dict(rtol=1e-5, atol=4e-6)
-    helpers.assert_close(z_lw.transpose(2, 3), o.lw, "v lw", **tol)
-    helpers.assert_close(z_uw.transpose(2, 3), o.uw, "v uw", **tol)
-    helpers.assert_close(z_lb, o.lb, "v lb", **tol)
-    helpers.assert_close(z_ub, o.ub, "v ub", **tol)
+    o64 = O.OBounds(2.0, 0.5, *[v.double() for v in tp]).dot_product(O.OBounds(2.0, 0.5, *[v.double() for v in tv]))
+    helpers.assert_arbitrated(z_lw.transpose(2, 3), o.lw, o64.lw, "c_bound v lw")
+    helpers.assert_arbitrated(z_uw.transpose(2, 3), o.uw, o64.uw, "c_bound v uw")
+    helpers.assert_arbitrated(z_lb, o.lb, o64.lb, "c_bound v lb")
+    helpers.assert_arbitrated(z_ub, o.ub, o64.ub, "c_bound v ub")
 
 
 def test_c_bound_matmul():
@@ -443,7 +443,9 @@ def test_c_bound_matmul():
     y_lw = torch.zeros(B, L, Di, Dy, device=DEV); y_uw = torch.zeros_like(y_lw)
     y_lb = torch.zeros(B, L, Dy, device=DEV); y_ub = torch.zeros_like(y_lb)
     c_bound.c_matmul_verification(lb, ub, lw, uw, W.to(DEV), y_lb, y_ub, y_lw, y_uw, B, L, Di, Do, Dy)
-    helpers.assert_close(y_lw, o.lw, "lw", atol=2e-6); helpers.assert_close(y_ub, o.ub, "ub", atol=2e-6)
+    o64 = O.OBounds(2.0, 0.5, *[v.double() for v in t]).matmul(W.double())
+    for got, k in ((y_lw, "lw"), (y_uw, "uw"), (y_lb, "lb"), (y_ub, "ub")):
+        helpers.assert_arbitrated(got, getattr(o, k), getattr(o64, k), "c_bound matmul " + k)
 
 
 # ------------------------------------------------------------------- conv
@@ -463,11 +465,11 @@ def test_conv_bounds(cfg):
     bias = torch.randn(cfg["Co"], generator=g) * 0.1
     o = O.conv_bounds(O.OBounds(float("inf"), 0.01, lw, lb, uw, ub), wt, bias, cfg["s"], cfg["p"])
     r = ops.conv2d((lw.to(DEV), uw.to(DEV), lb.to(DEV), ub.to(DEV)), wt.to(DEV), bias.to(DEV), cfg["s"], cfg["p"])
-    tol = dict(rtol=1e-5, atol=2e-6)
-    helpers.assert_close(r[0], o.lw, "conv lw", **tol)
-    helpers.assert_close(r[1], o.uw, "conv uw", **tol)
-    helpers.assert_close(r[2], o.lb, "conv lb", **tol)
-    helpers.assert_close(r[3], o.ub, "conv ub", **tol)
+    o64 = O.conv_bounds(O.OBounds(float("inf"), 0.01, lw.double(), lb.double(), uw.double(), ub.double()), wt.double(),
+                        bias.double(), cfg["s"], cfg["p"])
+    what = "conv %dx%d s%d" % (cfg["k"], cfg["k"], cfg["s"])
+    for got, k in zip(r, ("lw", "uw", "lb", "ub")):
+        helpers.assert_arbitrated(got, getattr(o, k), getattr(o64, k), what + " " + k)
 
 
 def test_dot_product_with_merged_head_store():
