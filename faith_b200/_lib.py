@@ -31,6 +31,17 @@ class Encoder(ctypes.Structure):
                 ("pool_w", _P), ("pool_b", _P), ("cls_w", _P), ("cls_b", _P)]
 
 
+class CnnLayer(ctypes.Structure):
+    _fields_ = [("kind", _I), ("weight", _P), ("bias", _P), ("cout", _I), ("kh", _I), ("kw", _I), ("stride", _I),
+                ("pad", _I), ("n_out", _I)]
+
+
+class Cnn(ctypes.Structure):
+    _fields_ = [("n_layers", _I), ("layer", ctypes.POINTER(CnnLayer)), ("cin", _I), ("h", _I), ("w", _I)]
+
+
+FB_CNN_CONV, FB_CNN_RELU, FB_CNN_LINEAR = 0, 1, 2
+
 # name -> argtypes; every function returns int (fb_status) unless listed in _OTHER_RESTYPE
 SIGNATURES = {
     "fb_concretize_f32": [_P] * 6 + [_L, _I, _I, _I, _I, _F, _I, _P],
@@ -69,6 +80,8 @@ SIGNATURES = {
     "fb_conv2d_f32": [_P] * 10 + [_I] * 10 + [_P],
     "fb_conv2d_identity_relax_f32": [_I, _P, _P, _P, _P, _F] + [_P] * 5 + [_L, _L] + [_I] * 9 + [_F, _P, _P],
     "fb_conv2d_windowed_f32": [_P] * 5 + [_L, _L, _I, _I, _P, _I] + [_I] * 8 + [_P],
+    "fb_cnn_workspace_bytes": [ctypes.POINTER(Cnn), _L],
+    "fb_cnn_forward_f32": [ctypes.POINTER(Cnn), _P, _I, _F, _L, _L, _P, _I, _P, _P, _P, _P, _L, _P],
     "fb_encoder_workspace_bytes": [ctypes.POINTER(Encoder), _I, _I, _I],
     "fb_encoder_forward_f32": [ctypes.POINTER(Encoder), _P, _I, _I, ctypes.POINTER(_I), _I, _I, _F, _P, _P, _P, _P, _L, _P],
     "fb_encoder_forward_instances_f32": [ctypes.POINTER(Encoder), _P, _I, _I, _P, _P, _I, _I, _P, _P, _P, _P, _L, _P],
@@ -93,7 +106,7 @@ SIGNATURES = {
     "fb_last_cuda_error": [],
     "fb_version": [],
 }
-_OTHER_RESTYPE = {"fb_comm_last_error": ctypes.c_char_p, "fb_status_string": ctypes.c_char_p, "fb_encoder_workspace_bytes": _L, "fb_launch_count": _L,
+_OTHER_RESTYPE = {"fb_comm_last_error": ctypes.c_char_p, "fb_status_string": ctypes.c_char_p, "fb_encoder_workspace_bytes": _L, "fb_cnn_workspace_bytes": _L, "fb_launch_count": _L,
                    "fb_dot_product_noalloc_max_floats": _L}
 
 _lib = None

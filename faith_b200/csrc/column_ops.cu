@@ -683,6 +683,7 @@ extern "C" int fb_norm_partials_f32(const float* lw, const float* uw, float* par
     cfg.numAttrs = 1;
     FB_CUDA_OK(cudaLaunchKernelEx(&cfg, vec ? col_norm_partials_split<4> : col_norm_partials_split<1>, lw, uw, part_l, part_u,
                                   Di_local, Do, ntiles, p));
+    count_launches(1);
     return FB_OK;
   }
   if (vec) col_norm_partials_native<4><<<(unsigned)blocks, kThreads, smem, (cudaStream_t)stream>>>(lw, uw, part_l, part_u, Di_local, Do, ntiles, p);

@@ -123,6 +123,40 @@ conv_bounds_kernel(const float* __restrict__ x_lo, const float* __restrict__ x_u
   }
 }
 
+// A few images only (the bias part of a bound: one image per batch element): the tiled kernel above would occupy a
+// handful of SMs and run at the latency of its staging loop (51 us for one 16 -> 32 channel image of 32 x 32).  Here a
+// thread owns one output element and accumulates in the same order (input channel, tap row, tap column; taps outside
+// the image are the exact zeros the tiled kernel multiplies), so the value is the tiled kernel's bit for bit.
+__global__ void __launch_bounds__(128)
+conv_bounds_small_kernel(const float* __restrict__ x_lo, const float* __restrict__ x_up, const float* __restrict__ Wt,
+                         const float* __restrict__ bias, float* __restrict__ y_lo, float* __restrict__ y_up, int64_t total,
+                         int Cin, int H, int W, int Cout, int Kh, int Kw, int stride, int pad, int Ho, int Wo) {
+  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= total) return;
+  const int ow = (int)(t % Wo), oh = (int)((t / Wo) % Ho), co = (int)((t / ((int64_t)Wo * Ho)) % Cout);
+  const int64_t n = t / ((int64_t)Wo * Ho * Cout);
+  const int ih0 = oh * stride - pad, iw0 = ow * stride - pad;
+  const int kh0 = max(0, -ih0), kh1 = min(Kh, H - ih0), kw0 = max(0, -iw0), kw1 = min(Kw, W - iw0);
+  const float* il = x_lo + n * (int64_t)Cin * H * W;
+  const float* iu = x_up + n * (int64_t)Cin * H * W;
+  float ac = 0.f, ar = 0.f;
+  for (int c = 0; c < Cin; ++c) {
+    const float* wp = Wt + ((int64_t)co * Cin + c) * Kh * Kw;
+    const int64_t ib = ((int64_t)c * H + ih0) * W + iw0;
+    for (int kh = kh0; kh < kh1; ++kh)
+      for (int kw = kw0; kw < kw1; ++kw) {
+        const float lo = __ldg(il + ib + (int64_t)kh * W + kw), up = __ldg(iu + ib + (int64_t)kh * W + kw);
+        const float w = __ldg(wp + kh * Kw + kw);
+        ac = fmaf(fmul(fadd(lo, up), 0.5f), w, ac);
+        ar = fmaf(fmul(fsub(up, lo), 0.5f), fabsf(w), ar);
+      }
+  }
+  float lo = fsub(ac, ar), up = fadd(ac, ar);
+  if (bias != nullptr) { lo = fadd(lo, bias[co]); up = fadd(up, bias[co]); }
+  y_lo[t] = lo;
+  y_up[t] = up;
+}
+
 template <int TH, int TW, int CO, int KS>
 int launch_conv_t(const float* x_lo, const float* x_up, const float* Wt, const float* bias, float* y_lo, float* y_up,
                   int64_t N, int Cin, int H, int W, int Cout, int Kh, int Kw, int stride, int pad, int Ho, int Wo,
@@ -147,6 +181,18 @@ int launch_conv(const float* x_lo, const float* x_up, const float* Wt, const flo
                 int64_t N, int Cin, int H, int W, int Cout, int Kh, int Kw, int stride, int pad, int Ho, int Wo,
                 cudaStream_t st) {
   if (N == 0) return FB_OK;
+  {
+    // blocks the tiled kernel would launch (its smallest tile: 256 pixels x 16 or 32 channels); fewer than one per
+    // SM and it is latency-bound
+    const int64_t tiled = N * ceil_div(Cout, Cout > 16 ? 32 : 16) * ceil_div((int64_t)Ho * Wo, 256);
+    const int64_t total = N * (int64_t)Cout * Ho * Wo;
+    if (tiled < device_info().sms && ceil_div(total, 128) <= 0x7fffffff) {
+      conv_bounds_small_kernel<<<(unsigned)ceil_div(total, 128), 128, 0, st>>>(x_lo, x_up, Wt, bias, y_lo, y_up, total, Cin, H, W,
+                                                                               Cout, Kh, Kw, stride, pad, Ho, Wo);
+      FB_LAUNCH_OK();
+      return FB_OK;
+    }
+  }
   const bool narrow = Wo <= 16, wide_co = Cout > 16;
 #define FB_CONV_ARGS x_lo, x_up, Wt, bias, y_lo, y_up, N, Cin, H, W, Cout, Kh, Kw, stride, pad, Ho, Wo, st
   if (Kh == 3 && Kw == 3) {

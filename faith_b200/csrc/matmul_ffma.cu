@@ -11,6 +11,8 @@
 // Tiling: 128 x 128 output tile per block, K in steps of 16, 256 threads with an 8 x 8 micro
 // tile and two accumulators (centre, radius) each; global loads of the next K step are issued
 // into registers before the current step is computed (two shared-memory stages).
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace fb {
@@ -316,20 +318,28 @@ split_sign_gemv_tiled(const float* __restrict__ a_lo, const float* __restrict__ 
   }
 }
 
-// A few rows with a long contraction (the bias row of the CNN head, M = 1): a block per row, K interleaved over its
-// threads, partial sums combined first inside each warp, then over the warps in warp order.
+// A few rows with a long contraction (the bias row of the CNN head, M = 1): a cluster of kGemvSplit blocks per row, each
+// taking a contiguous part of K interleaved over its threads; partial sums are combined inside each warp, over the
+// warps in warp order, and over the blocks in block order by block 0 through distributed shared memory.
+constexpr int kGemvSplit = 8;
 template <int NMAX>
 __global__ void __launch_bounds__(kThreads)
 split_sign_gemv_block(const float* __restrict__ a_lo, const float* __restrict__ a_up, const float* __restrict__ W,
                       const float* __restrict__ bias, float* __restrict__ c_lo, float* __restrict__ c_up, int N, int K) {
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
   __shared__ float s_red[2][kThreads / 32][NMAX];
+  __shared__ float s_part[2][NMAX];
+  const unsigned cr = cluster.block_rank();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t m = blockIdx.x;
+  const int64_t m = blockIdx.x / kGemvSplit;
+  const int chunk = (K + kGemvSplit - 1) / kGemvSplit;
+  const int k_begin = min(K, (int)cr * chunk), k_end = min(K, k_begin + chunk);
   float sc[NMAX], sr[NMAX];
 #pragma unroll
   for (int n = 0; n < NMAX; ++n) { sc[n] = 0.f; sr[n] = 0.f; }
 #pragma unroll 4
-  for (int k = threadIdx.x; k < K; k += kThreads) {
+  for (int k = k_begin + threadIdx.x; k < k_end; k += kThreads) {
     const float lo = __ldg(a_lo + m * K + k), up = __ldg(a_up + m * K + k);
     const float c = fmul(fadd(lo, up), 0.5f), r = fmul(fsub(up, lo), 0.5f);
 #pragma unroll
@@ -351,15 +361,28 @@ split_sign_gemv_block(const float* __restrict__ a_lo, const float* __restrict__ 
     if (lane == 0) { s_red[0][warp][n] = sc[n]; s_red[1][warp][n] = sr[n]; }
   }
   __syncthreads();
-  if (threadIdx.x < N) {
+  if (threadIdx.x < NMAX) {
     const int n = threadIdx.x;
     float c = s_red[0][0][n], r = s_red[1][0][n];
     for (int w = 1; w < kThreads / 32; ++w) { c = fadd(c, s_red[0][w][n]); r = fadd(r, s_red[1][w][n]); }
+    s_part[0][n] = c;
+    s_part[1][n] = r;
+  }
+  cluster.sync();
+  if (cr == 0 && threadIdx.x < N) {
+    const int n = threadIdx.x;
+    float c = s_part[0][n], r = s_part[1][n];
+    for (unsigned b = 1; b < kGemvSplit; ++b) {
+      const float* rp = cluster.map_shared_rank(&s_part[0][0], b);
+      c = fadd(c, rp[n]);
+      r = fadd(r, rp[NMAX + n]);
+    }
     float lo = fsub(c, r), up = fadd(c, r);
     if (bias != nullptr) { lo = fadd(lo, bias[n]); up = fadd(up, bias[n]); }
     c_lo[m * N + n] = lo;
     c_up[m * N + n] = up;
   }
+  cluster.sync();   // the other blocks' shared memory stays alive until block 0 has read it
 }
 
 }  // namespace
@@ -369,8 +392,19 @@ int launch_split_sign_ffma(const float* a_lo, const float* a_up, const float* W,
                            float* c_up, int64_t M, int N, int K, cudaStream_t st, int split_rows, int split_d) {
   if (M == 0 || N == 0) return FB_OK;
   if (N <= 16 && split_rows == 0 && K >= 2048 && M <= 32) {
-    split_sign_gemv_block<16><<<(unsigned)M, kThreads, 0, st>>>(a_lo, a_up, W, bias, c_lo, c_up, N, K);
-    FB_LAUNCH_OK();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(M * kGemvSplit));
+    cfg.blockDim = dim3(kThreads);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = kGemvSplit;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    FB_CUDA_OK(cudaLaunchKernelEx(&cfg, split_sign_gemv_block<16>, a_lo, a_up, W, bias, c_lo, c_up, N, K));
+    count_launches(1);
     return FB_OK;
   }
   if (N <= 16 && split_rows == 0 && K >= 1024 && K % 4 == 0 && aligned16(a_lo) && aligned16(a_up) && aligned16(W) &&

@@ -134,6 +134,11 @@ class CnnVerifier:
 
     layers: list of ("conv", weight [Co,Ci,k,k], bias, stride, pad) / ("relu",) / ("linear", W, b).
     Returns the concretised output bounds (l, u), identical on every rank.
+
+    A network that starts with a convolution goes through the C driver (fb_cnn_forward_f32): one call enqueues the
+    whole pass, the structure of the identity input is used (first convolution and its relaxation written from the
+    filter alone, later convolutions windowed).  `forward(dense=True)`, and networks that start otherwise, take the
+    general kernels operator by operator with the identity materialised.
     """
 
     def __init__(self, layers, device, group=None, comm=None, algo=0):
@@ -142,6 +147,7 @@ class CnnVerifier:
         self.comm = comm        # faith_b200.comm.Comm: the all-reduces are enqueued by the library (NCCL or one-shot)
         self.algo = algo
         self._ws = None
+        self._arena = None
         self.layers = []
         for ly in layers:
             if ly[0] in ("conv", "linear"):
@@ -149,16 +155,63 @@ class CnnVerifier:
                                                     if isinstance(t, torch.Tensor) else t for t in ly[1:]))
             else:
                 self.layers.append(ly)
+        # the network as the C driver takes it (host array of layer records; the tensors above keep the weights alive)
+        recs = (_lib.CnnLayer * max(1, len(self.layers)))()
+        for r, ly in zip(recs, self.layers):
+            if ly[0] == "conv":
+                r.kind, r.weight, r.bias = _lib.FB_CNN_CONV, ly[1].data_ptr(), ly[2].data_ptr() if ly[2] is not None else None
+                r.cout, r.kh, r.kw, r.stride, r.pad = ly[1].shape[0], ly[1].shape[2], ly[1].shape[3], ly[3], ly[4]
+            elif ly[0] == "linear":
+                r.kind, r.weight, r.bias = _lib.FB_CNN_LINEAR, ly[1].data_ptr(), ly[2].data_ptr() if ly[2] is not None else None
+                r.n_out = ly[1].shape[0]
+            else:
+                r.kind = _lib.FB_CNN_RELU
+        self._recs = recs
+        self._driver_ok = bool(self.layers) and self.layers[0][0] == "conv"
+
+    def _forward_driver(self, image, p, eps, start, size, world):
+        C, H, W = image.shape
+        lib = load()
+        net = _lib.Cnn(len(self.layers), self._recs, C, H, W)
+        need = lib.fb_cnn_workspace_bytes(ctypes.byref(net), size)
+        if need < 0:
+            raise _lib.FaithError("fb_cnn_workspace_bytes: network not supported by the driver")
+        if self._arena is None or self._arena.numel() < need:
+            self._arena = torch.empty(need, dtype=torch.uint8, device=self.device)
+        img = image.to(self.device, torch.float32, non_blocking=True).contiguous()
+        n_out = self._out_features(C, H, W)
+        l = torch.empty(n_out, device=self.device)
+        u = torch.empty(n_out, device=self.device)
+        violation = torch.zeros(1, dtype=torch.int32, device=self.device)
+        comm = self.comm._h if (self.comm is not None and world > 1) else None
+        with torch.cuda.device(self.device):
+            check(lib.fb_cnn_forward_f32(ctypes.byref(net), img.data_ptr(), ops.norm_code(p), float(eps), start, size, comm,
+                                         self.algo, l.data_ptr(), u.data_ptr(), violation.data_ptr(), self._arena.data_ptr(),
+                                         self._arena.numel(), ops._stream()), "fb_cnn_forward_f32")
+        return l, u
+
+    def _out_features(self, C, H, W):
+        c, h, w = C, H, W
+        feat = c * h * w
+        for ly in self.layers:
+            if ly[0] == "conv":
+                k_h, k_w = ly[1].shape[2], ly[1].shape[3]
+                h, w, c = (h + 2 * ly[4] - k_h) // ly[3] + 1, (w + 2 * ly[4] - k_w) // ly[3] + 1, ly[1].shape[0]
+                feat = c * h * w
+            elif ly[0] == "linear":
+                feat = ly[1].shape[0]
+        return feat
 
     def forward(self, image, p, eps, rank=0, world=1, dense=False):
-        """dense=True materialises the identity input and runs every convolution densely (the general kernels; kept
-        for comparison).  Otherwise the structure of the identity input is used: the first convolution and its
-        relaxation are written from the filter alone, later convolutions only compute the window each row can reach."""
+        """dense=True materialises the identity input and runs every convolution densely, operator by operator (the
+        general kernels; kept for comparison).  Otherwise the C driver runs the pass."""
         C, H, W = image.shape
         di = C * H * W
         base, rem = divmod(di, world)
         start = rank * base + max(0, rank - (world - rem))
         size = base + (1 if rank >= world - rem else 0)
+        if not dense and self._driver_ok and (world == 1 or self.comm is not None):
+            return self._forward_driver(image, p, eps, start, size, world)
         lb = image.to(self.device, torch.float32).view(1, C, H, W).contiguous()
         ub = lb.clone()
         layers = list(self.layers)

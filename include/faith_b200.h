@@ -482,6 +482,35 @@ int fb_concretize_sharded_f32(fb_comm* c, int algo,
                               float* l, float* u, float* part_ws,
                               int64_t rows, int Di_local, int Do, int words, int p, float eps, void* stream);
 
+/* ---- whole-model driver: CNN with every pixel of the image perturbed ----------------------
+ * conv -> [relu] -> (conv | relu)* -> linear -> (relu | linear)*, dim_in = cin * h * w, input bound lw = uw = I,
+ * lb = ub = image [cin, h, w] (device).  Computes the rows [row_start, row_start + rows) of dim_in (a rank's shard, or
+ * 0 and cin*h*w) and writes the concretised range of the last layer, out_l / out_u [features of the last layer]; with a
+ * communicator (world > 1) the dual norms are all-reduced over the ranks by `algo` (fb_allreduce_algo) and every rank
+ * gets the same range, with comm == NULL nothing is exchanged.  One call enqueues the whole pass on `stream`.
+ * The first layer must be a convolution (its output, and the relaxation behind it, are written from the filter alone,
+ * fb_conv2d_identity_relax_f32); later convolutions go through fb_conv2d_windowed_f32.  The reference has no CNN
+ * verifier to mirror (HandTunedKernels/convolution_verification.cu:228-238 is a benchmark stub); layer semantics are
+ * Bounds.matmul / Bounds.relu (Bounds.py:397-413, :921-963) with dim_in as the batch axis of the convolutions.
+ * Weights are device pointers: conv [cout, cin, kh, kw], linear [n_out, features] (nn.Linear layout), bias or NULL. */
+typedef enum fb_cnn_kind { FB_CNN_CONV = 0, FB_CNN_RELU = 1, FB_CNN_LINEAR = 2 } fb_cnn_kind;
+typedef struct fb_cnn_layer {
+  int kind;
+  const float* weight;
+  const float* bias;
+  int cout, kh, kw, stride, pad;   /* FB_CNN_CONV */
+  int n_out;                       /* FB_CNN_LINEAR */
+} fb_cnn_layer;
+typedef struct fb_cnn {
+  int n_layers;
+  const fb_cnn_layer* layer;       /* host array */
+  int cin, h, w;
+} fb_cnn;
+int64_t fb_cnn_workspace_bytes(const fb_cnn* net, int64_t rows);   /* -1: malformed network */
+int fb_cnn_forward_f32(const fb_cnn* net, const float* image, int p, float eps, int64_t row_start, int64_t rows,
+                       fb_comm* comm, int algo, float* out_l, float* out_u, int* violation,
+                       void* workspace, int64_t workspace_bytes, void* stream);
+
 /* ---- measurement hooks (no counterpart in the reference) --------------------------------
  * fb_profile_enable(1) clears the records and makes every outermost operator call bracket its
  * launches with a pair of CUDA events on the caller's stream; fb_profile_read() waits for the

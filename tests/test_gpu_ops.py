@@ -472,6 +472,27 @@ def test_conv_bounds(cfg):
         helpers.assert_arbitrated(got, getattr(o, k), getattr(o64, k), what + " " + k)
 
 
+@pytest.mark.parametrize("C,H,W,Co,k,s,p", [(16, 32, 32, 32, 3, 2, 1), (3, 32, 32, 16, 3, 1, 1), (5, 9, 11, 7, 3, 1, 0),
+                                           (2, 8, 8, 20, 5, 2, 2)])
+def test_conv_of_a_few_images_equals_the_tiled_kernel_bit_for_bit(C, H, W, Co, k, s, p):
+    """One image goes through the thread-per-output kernel, many through the tiled one: same accumulation order, same
+    bits (the image is row 0 of a batch of 600 copies in the second call)."""
+    from faith_b200 import ops
+    g = torch.Generator().manual_seed(503)
+    lo = torch.rand(1, 1, C, H, W, generator=g) - 0.5
+    up = lo + torch.rand(1, 1, C, H, W, generator=g) * 0.3
+    wt = (torch.randn(Co, C, k, k, generator=g) * 0.3).to(DEV)
+    bias = (torch.randn(Co, generator=g) * 0.1).to(DEV)
+    one = ops.conv2d((lo.to(DEV), up.to(DEV), lo[0].to(DEV), up[0].to(DEV)), wt, bias, s, p)
+    n = 600
+    many = ops.conv2d((lo.expand(1, n, C, H, W).contiguous().to(DEV), up.expand(1, n, C, H, W).contiguous().to(DEV),
+                       lo[0].to(DEV), up[0].to(DEV)), wt, bias, s, p)
+    assert torch.equal(one[0][0, 0], many[0][0, 0]) and torch.equal(one[1][0, 0], many[1][0, 0])
+    assert torch.equal(one[0][0, 0], many[0][0, n - 1])
+    # the bias part of both calls is one image (small kernel); without the bias it equals the weight part
+    assert torch.equal(one[2] - bias.view(1, -1, 1, 1), one[0][0]) or float((one[2] - bias.view(1, -1, 1, 1) - one[0][0]).abs().max()) < 1e-6
+
+
 def test_dot_product_with_merged_head_store():
     """fb_dot_product_heads_f32 writes the context head-merged; same values as dot product + merge."""
     from faith_b200 import _lib, ops
