@@ -353,14 +353,19 @@ def per_config_lines(ctx, lib, pipes, pk):
     layers = O.make_cnn(5)
     img = torch.rand(3, 32, 32, generator=torch.Generator().manual_seed(5)).pin_memory()   # 12 KB, copied every pass
     ver = CnnVerifier(layers, dev)
+    # Default route: rows kept as their windows only (fb_cw_*): 7 MB of rows instead of 600 MB; what remains is 14 small
+    # launches, so the figure is launch- and latency-bound and a roofline fraction says little (bytes: the compact rows
+    # written and read by each operator plus the 0.33 MB head weight, 2.3 GFLOP almost all in the head).
     per = ctx.loop_ms(lambda: ver.forward(img, INF, 2.0 / 255), 10)
-    # The default path uses the structure of the identity input (rows are zero outside the window their pixel reaches):
-    # it writes conv1+relu (2 x 201 MB) from the filter alone, reads windows and writes conv2 (2 x 101 MB), reads them
-    # twice and writes them once for the second relaxation, reads them once for the linear layer: 1.41 GB, and 2.3 GFLOP
-    # (almost all of it the 8192 -> 10 head).
-    out.append(roof_entry("C5 CNN pass, one image (conv3-16, relu, conv16-32 s2, relu, linear 8192-10), 1 GPU; identity-input "
-                          "structure used (default path)", per, 2.3e9, 1.41e9, ffma_alg, "ffma", hbm,
-                          {"images_per_s": 1e3 / per}))
+    out.append(roof_entry("C5 CNN pass, one image (conv3-16, relu, conv16-32 s2, relu, linear 8192-10), 1 GPU; compact rows "
+                          "(default route)", per, 2.3e9, 0.06e9, ffma_alg, "ffma", hbm,
+                          {"images_per_s": 1e3 / per, "note": "latency-bound: 14 launches of a few microseconds each"}))
+    # Dense rows, identity-input structure used (first convolution + relu written from the filter alone, windowed second
+    # convolution): 1.41 GB moved.
+    ver_rows = CnnVerifier(layers, dev, compact=False)
+    per_r = ctx.loop_ms(lambda: ver_rows.forward(img, INF, 2.0 / 255), 10)
+    out.append(roof_entry("C5 CNN pass, same image, dense rows with the identity-input structure used", per_r, 2.3e9, 1.41e9,
+                          ffma_alg, "ffma", hbm, {"images_per_s": 1e3 / per_r}))
     per_d = ctx.loop_ms(lambda: ver.forward(img, INF, 2.0 / 255, dense=True), 10)
     out.append(roof_entry("C5 CNN pass, same image, identity materialised and every convolution run by the dense kernel",
                           per_d, 41.9e9, 2.3e9, ffma_alg, "ffma", hbm, {"images_per_s": 1e3 / per_d}))
@@ -407,8 +412,11 @@ def cnn_sharded(ctx, lib, steps):
     if ctx.world > 1:
         comm = Comm.from_process_group(oneshot_floats=1 << 16)
     algos = [("nccl", ALGO_NCCL), ("oneshot", ALGO_ONESHOT)] if comm is not None else [("single", ALGO_NCCL)]
-    for name, algo in algos:
-        ver = CnnVerifier(layers, ctx.dev, comm=comm, algo=algo)
+    # two routes: rows kept as their windows only (the default; so little work per image that sharding it cannot pay),
+    # and dense rows (the formulation of the benchmark description: [3072, C, H, W] tensors sharded along dim_in)
+    runs = [(a + "_dense_rows", algo, False) for a, algo in algos] + [(a + "_compact_rows", algo, True) for a, algo in algos]
+    for name, algo, compact in runs:
+        ver = CnnVerifier(layers, ctx.dev, comm=comm, algo=algo, compact=compact)
         for _ in range(3):
             l, u = ver.forward(img, INF, eps, ctx.rank, ctx.world)
         n0 = lib.fb_launch_count()

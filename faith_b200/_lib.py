@@ -80,8 +80,15 @@ SIGNATURES = {
     "fb_conv2d_f32": [_P] * 10 + [_I] * 10 + [_P],
     "fb_conv2d_identity_relax_f32": [_I, _P, _P, _P, _P, _F] + [_P] * 5 + [_L, _L] + [_I] * 9 + [_F, _P, _P],
     "fb_conv2d_windowed_f32": [_P] * 5 + [_L, _L, _I, _I, _P, _I] + [_I] * 8 + [_P],
+    "fb_cw_extent": [_I, _I, _P, _I, ctypes.POINTER(_I), ctypes.POINTER(_I)],
+    "fb_cw_identity_relax_f32": [_I, _P, _P, _P, _P, _F] + [_P] * 5 + [_L, _L] + [_I] * 9 + [_F, _P, _P],
+    "fb_cw_conv2d_f32": [_P] * 5 + [_L, _L, _I, _I, _P, _I] + [_I] * 8 + [_P],
+    "fb_cw_norm_partials_f32": [_P] * 4 + [_L, _L, _I, _I, _I, _P, _I, _I, _I, _I, _I, _P],
+    "fb_cw_relax_apply_f32": [_I] + [_P] * 11 + [_L, _L, _I, _I, _P, _I, _I, _I, _I, _I, _F, _P, _P],
+    "fb_cw_linear_f32": [_P] * 6 + [_L, _L, _I, _I, _P, _I, _I, _I, _I, _I, _P],
+    "fb_cw_expand_f32": [_P] * 4 + [_L, _L, _I, _I, _P, _I, _I, _I, _I, _P],
     "fb_cnn_workspace_bytes": [ctypes.POINTER(Cnn), _L],
-    "fb_cnn_forward_f32": [ctypes.POINTER(Cnn), _P, _I, _F, _L, _L, _P, _I, _P, _P, _P, _P, _L, _P],
+    "fb_cnn_forward_f32": [ctypes.POINTER(Cnn), _P, _I, _F, _L, _L, _P, _I, _I, _P, _P, _P, _P, _L, _P],
     "fb_encoder_workspace_bytes": [ctypes.POINTER(Encoder), _I, _I, _I],
     "fb_encoder_forward_f32": [ctypes.POINTER(Encoder), _P, _I, _I, ctypes.POINTER(_I), _I, _I, _F, _P, _P, _P, _P, _L, _P],
     "fb_encoder_forward_instances_f32": [ctypes.POINTER(Encoder), _P, _I, _I, _P, _P, _I, _I, _P, _P, _P, _P, _L, _P],

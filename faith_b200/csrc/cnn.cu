@@ -16,13 +16,14 @@ namespace fb {
 namespace {
 
 struct Geometry {
+  int64_t wt;      // elements of the weight of the linear layer that ends the spatial part (transposed copy), or 0
   int64_t f_max;   // widest layer output (features of one row)
   int n_out;       // features of the last layer
   bool ok;
 };
 
 Geometry walk(const fb_cnn* net) {
-  Geometry g = {0, 0, false};
+  Geometry g = {0, 0, 0, false};
   if (!net || net->n_layers <= 0 || !net->layer || net->cin <= 0 || net->h <= 0 || net->w <= 0) return g;
   if (net->layer[0].kind != FB_CNN_CONV) return g;
   int c = net->cin, h = net->h, w = net->w;
@@ -39,6 +40,7 @@ Geometry walk(const fb_cnn* net) {
       feat = (int64_t)c * h * w;
     } else if (ly.kind == FB_CNN_LINEAR) {
       if (!ly.weight || ly.n_out <= 0) return g;
+      if (spatial) g.wt = feat * ly.n_out;
       spatial = false;
       feat = ly.n_out;
     } else if (ly.kind != FB_CNN_RELU) {
@@ -65,14 +67,14 @@ extern "C" int64_t fb_cnn_workspace_bytes(const fb_cnn* net, int64_t rows) {
   const Geometry g = walk(net);
   if (!g.ok || rows < 0) return -1;
   // two bound sets (lw, uw [rows, f_max]; lb, ub [f_max]), the column scratch of the first convolution and the norm
-  // partials (2 * f_max each)
+  // partials (2 * f_max each), the relaxation coefficients of the compact route (4 * f_max)
   const int64_t per_set = 2 * round_up(rows * g.f_max) + 2 * round_up(g.f_max);
-  return 4 * (2 * per_set + 4 * round_up(g.f_max));
+  return 4 * (2 * per_set + 8 * round_up(g.f_max) + round_up(g.wt));
 }
 
 extern "C" int fb_cnn_forward_f32(const fb_cnn* net, const float* image, int p, float eps, int64_t row_start, int64_t rows,
-                                  fb_comm* comm, int algo, float* out_l, float* out_u, int* violation, void* workspace,
-                                  int64_t workspace_bytes, void* stream) {
+                                  fb_comm* comm, int algo, int compact, float* out_l, float* out_u, int* violation,
+                                  void* workspace, int64_t workspace_bytes, void* stream) {
   if (!net || !image || !out_l || !out_u || !workspace) return FB_ERR_ARG;
   const Geometry g = walk(net);
   if (!g.ok) return FB_ERR_SHAPE;
@@ -91,7 +93,9 @@ extern "C" int fb_cnn_forward_f32(const fb_cnn* net, const float* image, int p, 
     set[s].ub = base; base += bsz;
   }
   float* col_ws = base; base += 2 * bsz;
-  float* part_ws = base;
+  float* part_ws = base; base += 2 * bsz;
+  float* coef_ws = base; base += 4 * bsz;
+  float* wt_ws = base;
 
   int c = net->cin, h = net->h, w = net->w;
   int64_t feat = di;
@@ -99,13 +103,14 @@ extern "C" int fb_cnn_forward_f32(const fb_cnn* net, const float* image, int p, 
   int n_chain = 0;
   int cur = 0;
   int i = 0;
+  bool cw = compact != 0;   // rows still kept as their windows (compact route, until the first linear layer)
   {
     // the first convolution (and the relaxation behind it, if any) from the filter alone
     const fb_cnn_layer& ly = net->layer[0];
     const bool fuse = net->n_layers > 1 && net->layer[1].kind == FB_CNN_RELU;
-    int rc = fb_conv2d_identity_relax_f32(fuse ? FB_RELU : -1, image, image, ly.weight, ly.bias, 1.0f, set[0].lw, set[0].uw,
-                                          set[0].lb, set[0].ub, col_ws, rows, row_start, c, h, w, ly.cout, ly.kh, ly.kw,
-                                          ly.stride, ly.pad, p, eps, violation, stream);
+    int rc = (cw ? fb_cw_identity_relax_f32 : fb_conv2d_identity_relax_f32)(
+        fuse ? FB_RELU : -1, image, image, ly.weight, ly.bias, 1.0f, set[0].lw, set[0].uw, set[0].lb, set[0].ub, col_ws, rows,
+        row_start, c, h, w, ly.cout, ly.kh, ly.kw, ly.stride, ly.pad, p, eps, violation, stream);
     if (rc != FB_OK) return rc;
     chain[0] = ly.kh, chain[1] = ly.kw, chain[2] = ly.stride, chain[3] = ly.pad;
     n_chain = 1;
@@ -115,22 +120,46 @@ extern "C" int fb_cnn_forward_f32(const fb_cnn* net, const float* image, int p, 
     feat = (int64_t)c * h * w;
     i = fuse ? 2 : 1;
   }
-  for (; i < net->n_layers; ++i) {
-    const fb_cnn_layer& ly = net->layer[i];
+  // leaves the compact route: dense rows from here on (a layer the compact operators do not cover)
+  auto expand = [&]() -> int {
     const Set& x = set[cur];
     const Set& y = set[cur ^ 1];
+    int rc = fb_cw_expand_f32(x.lw, x.uw, y.lw, y.uw, rows, row_start, net->h, net->w, chain, n_chain, c, h, w, stream);
+    if (rc != FB_OK) return rc;
+    FB_CUDA_OK(cudaMemcpyAsync(y.lb, x.lb, sizeof(float) * feat, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+    FB_CUDA_OK(cudaMemcpyAsync(y.ub, x.ub, sizeof(float) * feat, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+    cur ^= 1;
+    cw = false;
+    return FB_OK;
+  };
+  for (; i < net->n_layers; ++i) {
+    const fb_cnn_layer& ly = net->layer[i];
     int rc = FB_OK;
+    if (cw && ly.kind == FB_CNN_CONV && n_chain + 1 > 8) {
+      rc = expand();
+      if (rc != FB_OK) return rc;
+    }
+    const Set& x = set[cur];
+    const Set& y = set[cur ^ 1];
     if (ly.kind == FB_CNN_CONV) {
       const int ho = (h + 2 * ly.pad - ly.kh) / ly.stride + 1, wo = (w + 2 * ly.pad - ly.kw) / ly.stride + 1;
-      rc = n_chain < 8 ? fb_conv2d_windowed_f32(x.lw, x.uw, ly.weight, y.lw, y.uw, rows, row_start, net->h, net->w, chain,
-                                                n_chain, c, h, w, ly.cout, ly.kh, ly.kw, ly.stride, ly.pad, stream)
-                       : FB_ERR_SHAPE;
-      if (rc == FB_ERR_SHAPE)   // windows too large to pay (or too long a chain): the dense kernel on the same rows
-        rc = fb_conv2d_f32(x.lw, x.uw, x.lb, x.ub, ly.weight, ly.bias, y.lw, y.uw, y.lb, y.ub, 1, (int)rows, c, h, w, ly.cout,
-                           ly.kh, ly.kw, ly.stride, ly.pad, stream);
-      else if (rc == FB_OK)     // bias part: an ordinary convolution of one image
-        rc = fb_conv2d_f32(x.lw, x.uw, x.lb, x.ub, ly.weight, ly.bias, y.lw, y.uw, y.lb, y.ub, 1, 0, c, h, w, ly.cout, ly.kh,
-                           ly.kw, ly.stride, ly.pad, stream);
+      if (cw) {
+        rc = fb_cw_conv2d_f32(x.lw, x.uw, ly.weight, y.lw, y.uw, rows, row_start, net->h, net->w, chain, n_chain, c, h, w, ly.cout,
+                              ly.kh, ly.kw, ly.stride, ly.pad, stream);
+        if (rc == FB_OK)
+          rc = fb_conv2d_f32(x.lb, x.ub, x.lb, x.ub, ly.weight, ly.bias, y.lb, y.ub, y.lb, y.ub, 1, 0, c, h, w, ly.cout, ly.kh,
+                             ly.kw, ly.stride, ly.pad, stream);
+      } else {
+        rc = n_chain < 8 ? fb_conv2d_windowed_f32(x.lw, x.uw, ly.weight, y.lw, y.uw, rows, row_start, net->h, net->w, chain,
+                                                  n_chain, c, h, w, ly.cout, ly.kh, ly.kw, ly.stride, ly.pad, stream)
+                         : FB_ERR_SHAPE;
+        if (rc == FB_ERR_SHAPE)   // windows too large to pay (or too long a chain): the dense kernel on the same rows
+          rc = fb_conv2d_f32(x.lw, x.uw, x.lb, x.ub, ly.weight, ly.bias, y.lw, y.uw, y.lb, y.ub, 1, (int)rows, c, h, w, ly.cout,
+                             ly.kh, ly.kw, ly.stride, ly.pad, stream);
+        else if (rc == FB_OK)     // bias part: an ordinary convolution of one image
+          rc = fb_conv2d_f32(x.lw, x.uw, x.lb, x.ub, ly.weight, ly.bias, y.lw, y.uw, y.lb, y.ub, 1, 0, c, h, w, ly.cout, ly.kh,
+                             ly.kw, ly.stride, ly.pad, stream);
+      }
       if (n_chain < 8) {
         chain[4 * n_chain] = ly.kh, chain[4 * n_chain + 1] = ly.kw, chain[4 * n_chain + 2] = ly.stride;
         chain[4 * n_chain + 3] = ly.pad;
@@ -139,15 +168,38 @@ extern "C" int fb_cnn_forward_f32(const fb_cnn* net, const float* image, int p, 
       h = ho, w = wo, c = ly.cout;
       feat = (int64_t)c * h * w;
     } else if (ly.kind == FB_CNN_RELU) {
-      rc = fb_relax_sharded_f32(comm, algo, FB_RELU, x.lw, x.uw, x.lb, x.ub, y.lw, y.uw, y.lb, y.ub, part_ws, 1, (int)rows,
-                                (int)feat, 1, p, eps, violation, stream);
+      if (cw) {
+        float* part_l = part_ws;
+        float* part_u = part_ws + feat;
+        rc = fb_cw_norm_partials_f32(x.lw, x.uw, part_l, part_u, rows, row_start, net->cin, net->h, net->w, chain, n_chain, c, h, w,
+                                     p, stream);
+        if (rc == FB_OK && comm != nullptr) rc = fb_allreduce_f32(comm, part_ws, 2 * feat, p == FB_P1 ? 1 : 0, algo, stream);
+        if (rc == FB_OK)   // relaxation coefficients in their own scratch
+          rc = fb_cw_relax_apply_f32(FB_RELU, x.lw, x.uw, x.lb, x.ub, part_l, part_u, y.lw, y.uw, y.lb, y.ub, coef_ws, rows,
+                                     row_start, net->h, net->w, chain, n_chain, c, h, w, p, eps, violation, stream);
+      } else {
+        rc = fb_relax_sharded_f32(comm, algo, FB_RELU, x.lw, x.uw, x.lb, x.ub, y.lw, y.uw, y.lb, y.ub, part_ws, 1, (int)rows,
+                                  (int)feat, 1, p, eps, violation, stream);
+      }
     } else {
-      rc = fb_matmul_f32(x.lw, x.uw, x.lb, x.ub, ly.weight, ly.bias, y.lw, y.uw, y.lb, y.ub, 1, (int)rows, (int)feat, ly.n_out,
-                         stream);
+      if (cw) {
+        rc = fb_cw_linear_f32(x.lw, x.uw, ly.weight, y.lw, y.uw, wt_ws, rows, row_start, net->h, net->w, chain, n_chain, c, h, w, ly.n_out,
+                              stream);
+        if (rc == FB_OK)
+          rc = fb_matmul_f32(x.lb, x.ub, x.lb, x.ub, ly.weight, ly.bias, y.lb, y.ub, y.lb, y.ub, 1, 0, (int)feat, ly.n_out, stream);
+        cw = false;
+      } else {
+        rc = fb_matmul_f32(x.lw, x.uw, x.lb, x.ub, ly.weight, ly.bias, y.lw, y.uw, y.lb, y.ub, 1, (int)rows, (int)feat, ly.n_out,
+                           stream);
+      }
       feat = ly.n_out;
     }
     if (rc != FB_OK) return rc;
     cur ^= 1;
+  }
+  if (cw) {   // the network ended on a feature map
+    int rc = expand();
+    if (rc != FB_OK) return rc;
   }
   const Set& z = set[cur];
   return fb_concretize_sharded_f32(comm, algo, z.lw, z.uw, z.lb, z.ub, out_l, out_u, part_ws, 1, (int)rows, (int)feat, 1, p,

@@ -400,6 +400,62 @@ col_norm_partials_split(const float* __restrict__ lw, const float* __restrict__ 
   cluster.sync();   // the other blocks' shared memory stays alive until block 0 has read it
 }
 
+// Few columns, many rows (the final concretisation of the CNN head: [3072, 10]): a column tile of 32 would leave
+// two thirds of the lanes idle and make every load a partial sector.  Here the [Di, Do] slab of a (b, l) row is read
+// as the flat array it is: a cluster of kSplit blocks splits the rows, in a block thread t < S (S = the largest
+// multiple of Do within the block) owns column t % Do and walks the rows t / Do, t / Do + S / Do, ..., so a warp reads
+// consecutive words; the S / Do partial results of a column are added in thread order by one thread per column, the
+// kSplit block results in block order by block 0 through distributed shared memory.
+__global__ void __launch_bounds__(kThreads)
+col_norm_partials_narrow(const float* __restrict__ lw, const float* __restrict__ uw, float* __restrict__ part_l,
+                         float* __restrict__ part_u, int Di, int Do, int p) {
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  __shared__ float s_l[kThreads], s_u[kThreads];
+  __shared__ float s_part[2 * 64];
+  const unsigned cr = cluster.block_rank();
+  const int64_t row = blockIdx.x / kSplit;
+  const int tid = threadIdx.x;
+  const int per = kThreads / Do, S = per * Do;       // rows in flight per step, active threads
+  const int chunk = (Di + kSplit - 1) / kSplit;
+  const int r0 = min(Di, (int)cr * chunk), r1 = min(Di, r0 + chunk);
+  const float* gl = lw + (size_t)row * Di * Do;
+  const float* gu = uw + (size_t)row * Di * Do;
+  float al = 0.f, au = 0.f;
+  if (tid < S) {
+    const int col = tid % Do;
+#pragma unroll 4
+    for (int r = r0 + tid / Do; r < r1; r += per) {
+      al = norm_accum(p, al, __ldg(gl + (size_t)r * Do + col));
+      au = norm_accum(p, au, __ldg(gu + (size_t)r * Do + col));
+    }
+  }
+  s_l[tid] = al;
+  s_u[tid] = au;
+  __syncthreads();
+  if (tid < Do) {
+    float sl = s_l[tid], su = s_u[tid];
+    for (int k = 1; k < per; ++k) {
+      sl = norm_combine(p, sl, s_l[k * Do + tid]);
+      su = norm_combine(p, su, s_u[k * Do + tid]);
+    }
+    s_part[tid] = sl;
+    s_part[64 + tid] = su;
+  }
+  cluster.sync();
+  if (cr == 0 && tid < Do) {
+    float sl = s_part[tid], su = s_part[64 + tid];
+    for (unsigned k = 1; k < kSplit; ++k) {
+      const float* rp = cluster.map_shared_rank(s_part, k);
+      sl = norm_combine(p, sl, rp[tid]);
+      su = norm_combine(p, su, rp[64 + tid]);
+    }
+    part_l[(size_t)row * Do + tid] = sl;
+    part_u[(size_t)row * Do + tid] = su;
+  }
+  cluster.sync();   // the other blocks' shared memory stays alive until block 0 has read it
+}
+
 template <int VEC>
 __global__ void __launch_bounds__(kThreads)
 col_relax_apply_native(int op, const float* __restrict__ lw, const float* __restrict__ uw,
@@ -669,8 +725,9 @@ extern "C" int fb_norm_partials_f32(const float* lw, const float* uw, float* par
   const bool vec = Do % 4 == 0 && aligned16(lw) && aligned16(uw);
   if (blocks < 2 * (int64_t)device_info().sms && Di_local >= 64 * kSplit) {
     // few column tiles, many rows: split the rows over a cluster
+    const bool narrow = Do <= 64 && Do % 32 != 0 && rows * kSplit <= 0x7fffffff;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(blocks * kSplit));
+    cfg.gridDim = dim3((unsigned)((narrow ? rows : blocks) * kSplit));
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = 0;
     cfg.stream = (cudaStream_t)stream;
@@ -681,8 +738,11 @@ extern "C" int fb_norm_partials_f32(const float* lw, const float* uw, float* par
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    FB_CUDA_OK(cudaLaunchKernelEx(&cfg, vec ? col_norm_partials_split<4> : col_norm_partials_split<1>, lw, uw, part_l, part_u,
-                                  Di_local, Do, ntiles, p));
+    if (narrow)
+      FB_CUDA_OK(cudaLaunchKernelEx(&cfg, col_norm_partials_narrow, lw, uw, part_l, part_u, Di_local, Do, p));
+    else
+      FB_CUDA_OK(cudaLaunchKernelEx(&cfg, vec ? col_norm_partials_split<4> : col_norm_partials_split<1>, lw, uw, part_l, part_u,
+                                    Di_local, Do, ntiles, p));
     count_launches(1);
     return FB_OK;
   }

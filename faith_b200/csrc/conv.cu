@@ -10,6 +10,7 @@
 #include <algorithm>
 #include <cstdint>
 #include "common.cuh"
+#include "conv_window.cuh"
 
 namespace fb {
 namespace {
@@ -127,29 +128,57 @@ conv_bounds_kernel(const float* __restrict__ x_lo, const float* __restrict__ x_u
 // handful of SMs and run at the latency of its staging loop (51 us for one 16 -> 32 channel image of 32 x 32).  Here a
 // thread owns one output element and accumulates in the same order (input channel, tap row, tap column; taps outside
 // the image are the exact zeros the tiled kernel multiplies), so the value is the tiled kernel's bit for bit.
+// KS: filter size when it is the same in both directions and known at compile time (3), 0 = from the arguments.  With KS
+// every tap is visited (those outside the image with a zero input: fmaf(0, w, acc) leaves the sum as it is), so the tap
+// loops unroll and the loads of a channel are in flight together.
+template <int KS>
 __global__ void __launch_bounds__(128)
 conv_bounds_small_kernel(const float* __restrict__ x_lo, const float* __restrict__ x_up, const float* __restrict__ Wt,
                          const float* __restrict__ bias, float* __restrict__ y_lo, float* __restrict__ y_up, int64_t total,
-                         int Cin, int H, int W, int Cout, int Kh, int Kw, int stride, int pad, int Ho, int Wo) {
+                         int Cin, int H, int W, int Cout, int Kh_arg, int Kw_arg, int stride, int pad, int Ho, int Wo) {
+  const int Kh = KS ? KS : Kh_arg, Kw = KS ? KS : Kw_arg;
   const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= total) return;
   const int ow = (int)(t % Wo), oh = (int)((t / Wo) % Ho), co = (int)((t / ((int64_t)Wo * Ho)) % Cout);
   const int64_t n = t / ((int64_t)Wo * Ho * Cout);
   const int ih0 = oh * stride - pad, iw0 = ow * stride - pad;
-  const int kh0 = max(0, -ih0), kh1 = min(Kh, H - ih0), kw0 = max(0, -iw0), kw1 = min(Kw, W - iw0);
   const float* il = x_lo + n * (int64_t)Cin * H * W;
   const float* iu = x_up + n * (int64_t)Cin * H * W;
   float ac = 0.f, ar = 0.f;
-  for (int c = 0; c < Cin; ++c) {
-    const float* wp = Wt + ((int64_t)co * Cin + c) * Kh * Kw;
-    const int64_t ib = ((int64_t)c * H + ih0) * W + iw0;
-    for (int kh = kh0; kh < kh1; ++kh)
-      for (int kw = kw0; kw < kw1; ++kw) {
-        const float lo = __ldg(il + ib + (int64_t)kh * W + kw), up = __ldg(iu + ib + (int64_t)kh * W + kw);
-        const float w = __ldg(wp + kh * Kw + kw);
-        ac = fmaf(fmul(fadd(lo, up), 0.5f), w, ac);
-        ar = fmaf(fmul(fsub(up, lo), 0.5f), fabsf(w), ar);
+  if (KS) {
+    for (int c = 0; c < Cin; ++c) {
+      const float* wp = Wt + ((int64_t)co * Cin + c) * KS * KS;
+      float lo[KS ? KS * KS : 1], up[KS ? KS * KS : 1], w[KS ? KS * KS : 1];
+#pragma unroll
+      for (int kh = 0; kh < KS; ++kh)
+#pragma unroll
+        for (int kw = 0; kw < KS; ++kw) {
+          const int ih = ih0 + kh, iw = iw0 + kw;
+          const bool in = ih >= 0 && ih < H && iw >= 0 && iw < W;
+          const int64_t o = ((int64_t)c * H + ih) * W + iw;
+          lo[kh * KS + kw] = in ? __ldg(il + o) : 0.f;
+          up[kh * KS + kw] = in ? __ldg(iu + o) : 0.f;
+          w[kh * KS + kw] = __ldg(wp + kh * KS + kw);
+        }
+#pragma unroll
+      for (int k = 0; k < KS * KS; ++k) {
+        ac = fmaf(fmul(fadd(lo[k], up[k]), 0.5f), w[k], ac);
+        ar = fmaf(fmul(fsub(up[k], lo[k]), 0.5f), fabsf(w[k]), ar);
       }
+    }
+  } else {
+    const int kh0 = max(0, -ih0), kh1 = min(Kh, H - ih0), kw0 = max(0, -iw0), kw1 = min(Kw, W - iw0);
+    for (int c = 0; c < Cin; ++c) {
+      const float* wp = Wt + ((int64_t)co * Cin + c) * Kh * Kw;
+      const int64_t ib = ((int64_t)c * H + ih0) * W + iw0;
+      for (int kh = kh0; kh < kh1; ++kh)
+        for (int kw = kw0; kw < kw1; ++kw) {
+          const float lo = __ldg(il + ib + (int64_t)kh * W + kw), up = __ldg(iu + ib + (int64_t)kh * W + kw);
+          const float w = __ldg(wp + kh * Kw + kw);
+          ac = fmaf(fmul(fadd(lo, up), 0.5f), w, ac);
+          ar = fmaf(fmul(fsub(up, lo), 0.5f), fabsf(w), ar);
+        }
+    }
   }
   float lo = fsub(ac, ar), up = fadd(ac, ar);
   if (bias != nullptr) { lo = fadd(lo, bias[co]); up = fadd(up, bias[co]); }
@@ -187,8 +216,12 @@ int launch_conv(const float* x_lo, const float* x_up, const float* Wt, const flo
     const int64_t tiled = N * ceil_div(Cout, Cout > 16 ? 32 : 16) * ceil_div((int64_t)Ho * Wo, 256);
     const int64_t total = N * (int64_t)Cout * Ho * Wo;
     if (tiled < device_info().sms && ceil_div(total, 128) <= 0x7fffffff) {
-      conv_bounds_small_kernel<<<(unsigned)ceil_div(total, 128), 128, 0, st>>>(x_lo, x_up, Wt, bias, y_lo, y_up, total, Cin, H, W,
-                                                                               Cout, Kh, Kw, stride, pad, Ho, Wo);
+      if (Kh == 3 && Kw == 3)
+        conv_bounds_small_kernel<3><<<(unsigned)ceil_div(total, 128), 128, 0, st>>>(x_lo, x_up, Wt, bias, y_lo, y_up, total, Cin, H,
+                                                                                    W, Cout, Kh, Kw, stride, pad, Ho, Wo);
+      else
+        conv_bounds_small_kernel<0><<<(unsigned)ceil_div(total, 128), 128, 0, st>>>(x_lo, x_up, Wt, bias, y_lo, y_up, total, Cin, H,
+                                                                                    W, Cout, Kh, Kw, stride, pad, Ho, Wo);
       FB_LAUNCH_OK();
       return FB_OK;
     }
@@ -254,40 +287,6 @@ identity_conv_columns_kernel(int op, const float* __restrict__ Wt, float* __rest
     k_u[t] = fadd(c.c_ul, c.c_uu);
     y_lb[t] = c.nlb;
     y_ub[t] = c.nub;
-  }
-}
-
-// The convolutions a row has been through before the one being computed: enough to know, from the row's pixel alone,
-// the window outside of which the row is zero.
-constexpr int kMaxChain = 8;
-struct ConvChain {
-  int n;
-  int kh[kMaxChain], kw[kMaxChain], stride[kMaxChain], pad[kMaxChain];
-};
-
-struct Span { int lo, hi; };   // inclusive; lo > hi: empty
-
-// Outputs (along one axis) of a convolution (k, stride, pad, n_out outputs) that have a tap inside the input span.
-__host__ __device__ inline Span span_after_conv(Span s, int k, int stride, int pad, int n_out) {
-  if (s.lo > s.hi) return s;
-  const int a = s.lo + pad - (k - 1);
-  Span o;
-  o.lo = a > 0 ? (a + stride - 1) / stride : 0;
-  o.hi = (s.hi + pad) / stride;
-  if (o.hi > n_out - 1) o.hi = n_out - 1;
-  return o;
-}
-
-// Window (in the coordinates of the chain's last output) reached by pixel (yi, xi) of the H0 x W0 image.
-__host__ __device__ inline void chain_window(const ConvChain& ch, int H0, int W0, int yi, int xi, Span& wy, Span& wx) {
-  wy.lo = wy.hi = yi;
-  wx.lo = wx.hi = xi;
-  int h = H0, w = W0;
-  for (int i = 0; i < ch.n; ++i) {
-    h = (h + 2 * ch.pad[i] - ch.kh[i]) / ch.stride[i] + 1;
-    w = (w + 2 * ch.pad[i] - ch.kw[i]) / ch.stride[i] + 1;
-    wy = span_after_conv(wy, ch.kh[i], ch.stride[i], ch.pad[i], h);
-    wx = span_after_conv(wx, ch.kw[i], ch.stride[i], ch.pad[i], w);
   }
 }
 
@@ -430,9 +429,19 @@ conv_window_kernel(const float* __restrict__ x_lo, const float* __restrict__ x_u
   }
 }
 
-inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
-
 }  // namespace
+
+int launch_identity_columns(int op, const float* Wt, float* y_lb, float* y_ub, float* k_l, float* k_u, float scale, int Cin,
+                            int H, int W, int Cout, int Kh, int Kw, int stride, int pad, int Ho, int Wo, int p, float eps,
+                            int* violation, cudaStream_t st) {
+  const int64_t ncol = (int64_t)Cout * Ho * Wo;
+  const int64_t want = ceil_div(ncol, 256), cap = (int64_t)device_info().sms * 8;
+  identity_conv_columns_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, st>>>(
+      op, Wt, y_lb, y_ub, k_l, k_u, scale, Cin, H, W, Cout, Kh, Kw, stride, pad, Ho, Wo, p, eps, violation);
+  FB_LAUNCH_OK();
+  return FB_OK;
+}
+
 }  // namespace fb
 
 extern "C" int fb_conv2d_identity_relax_f32(int op, const float* x_lb, const float* x_ub, const float* Wt,
@@ -455,10 +464,9 @@ extern "C" int fb_conv2d_identity_relax_f32(int op, const float* x_lb, const flo
   if (rc != FB_OK) return rc;
   float* k_l = col_ws;
   float* k_u = col_ws + ncol;
-  const int64_t want = fb::ceil_div(ncol, 256), cap = (int64_t)fb::device_info().sms * 8;
-  fb::identity_conv_columns_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, st>>>(
-      op, Wt, y_lb, y_ub, k_l, k_u, scale, Cin, H, W, Cout, Kh, Kw, stride, pad, Ho, Wo, p, eps, violation);
-  FB_LAUNCH_OK();
+  rc = fb::launch_identity_columns(op, Wt, y_lb, y_ub, k_l, k_u, scale, Cin, H, W, Cout, Kh, Kw, stride, pad, Ho, Wo, p, eps,
+                                   violation, st);
+  if (rc != FB_OK) return rc;
   if (rows == 0) return FB_OK;
   if (rows > 0x7fffffff) return FB_ERR_SHAPE;
   if (ncol > 0x7fffffff) return FB_ERR_SHAPE;

@@ -108,7 +108,7 @@ static int matmul_impl(const float* x_lw, const float* x_uw, const float* x_lb, 
                        const float* bias, float* y_lw, float* y_uw, float* y_lb, float* y_ub, int64_t rows, int Di,
                        int Do, int Dy, int L, int heads, void* stream) {
   if (!x_lw || !x_uw || !x_lb || !x_ub || !W || !y_lw || !y_uw || !y_lb || !y_ub) return FB_ERR_ARG;
-  if (rows < 0 || Di <= 0 || Do <= 0 || Dy <= 0) return FB_ERR_ARG;
+  if (rows < 0 || Di < 0 || Do <= 0 || Dy <= 0) return FB_ERR_ARG;   // Di == 0: the bias rows alone
   if (heads > 1 && (L <= 0 || rows % L != 0 || Dy % heads != 0)) return FB_ERR_ARG;
   cudaStream_t st = (cudaStream_t)stream;
   const double M = (double)rows * (Di + 1);

@@ -128,6 +128,110 @@ def conv_windowed(x, weight, bias, stride, pad, row_start, H0, W0, chain):
     return y_lw, y_uw, y_lb, y_ub
 
 
+def _chain_arr(chain):
+    flat = [int(v) for c in chain for v in c]
+    return (ctypes.c_int * max(1, len(flat)))(*flat)
+
+
+def cw_extent(H0, W0, chain):
+    """Largest window (wh, ww) any pixel of an H0 x W0 image reaches through `chain`: the trailing dimensions of a compact
+    tensor (fb_cw_extent)."""
+    wh, ww = ctypes.c_int(0), ctypes.c_int(0)
+    check(load().fb_cw_extent(H0, W0, _chain_arr(chain), len(chain), ctypes.byref(wh), ctypes.byref(ww)), "fb_cw_extent")
+    return wh.value, ww.value
+
+
+def cw_identity_relax(op, image_lb, image_ub, weight, bias, rows, row_start, stride, pad, p, eps, scale=1.0):
+    """conv_identity_relax with compact rows: z_lw, z_uw [rows, Cout, wh, ww] (fb_cw_identity_relax_f32)."""
+    dev = ops._chk(image_lb, image_ub, weight, bias)
+    C, H, W = image_lb.shape[-3:]
+    Co, _, Kh, Kw = weight.shape
+    Ho, Wo = (H + 2 * pad - Kh) // stride + 1, (W + 2 * pad - Kw) // stride + 1
+    wh, ww = cw_extent(H, W, [(Kh, Kw, stride, pad)])
+    z_lw = torch.empty(rows, Co, wh, ww, device=dev)
+    z_uw = torch.empty_like(z_lw)
+    y_lb = torch.empty(1, Co, Ho, Wo, device=dev)
+    y_ub = torch.empty_like(y_lb)
+    ws = torch.empty(2 * Co * Ho * Wo, device=dev)
+    with torch.cuda.device(dev):
+        check(load().fb_cw_identity_relax_f32(-1 if op is None else op, image_lb.data_ptr(), image_ub.data_ptr(),
+                                              weight.data_ptr(), bias.data_ptr() if bias is not None else None, float(scale),
+                                              z_lw.data_ptr(), z_uw.data_ptr(), y_lb.data_ptr(), y_ub.data_ptr(), ws.data_ptr(),
+                                              rows, row_start, C, H, W, Co, Kh, Kw, stride, pad, ops.norm_code(p), float(eps),
+                                              None, ops._stream()), "fb_cw_identity_relax_f32")
+    return z_lw, z_uw, y_lb, y_ub
+
+
+def cw_conv(z_lw, z_uw, weight, stride, pad, row_start, H0, W0, chain, H, W):
+    """Weight part of a later convolution on compact rows (fb_cw_conv2d_f32); `chain` leads to the input [Cin, H, W]."""
+    dev = ops._chk(z_lw, z_uw, weight)
+    rows, C = z_lw.shape[:2]
+    Co, _, Kh, Kw = weight.shape
+    wh, ww = cw_extent(H0, W0, list(chain) + [(Kh, Kw, stride, pad)])
+    y_lw = torch.empty(rows, Co, wh, ww, device=dev)
+    y_uw = torch.empty_like(y_lw)
+    with torch.cuda.device(dev):
+        check(load().fb_cw_conv2d_f32(z_lw.data_ptr(), z_uw.data_ptr(), weight.data_ptr(), y_lw.data_ptr(), y_uw.data_ptr(), rows,
+                                      row_start, H0, W0, _chain_arr(chain), len(chain), C, H, W, Co, Kh, Kw, stride, pad,
+                                      ops._stream()), "fb_cw_conv2d_f32")
+    return y_lw, y_uw
+
+
+def cw_norm_partials(z_lw, z_uw, row_start, Cin0, H0, W0, chain, H, W, p):
+    """Unfinished dual-norm accumulation of every dense column over the rows of a compact tensor (fb_cw_norm_partials_f32)."""
+    dev = ops._chk(z_lw, z_uw)
+    rows, C = z_lw.shape[:2]
+    part_l = torch.empty(C * H * W, device=dev)
+    part_u = torch.empty_like(part_l)
+    with torch.cuda.device(dev):
+        check(load().fb_cw_norm_partials_f32(z_lw.data_ptr(), z_uw.data_ptr(), part_l.data_ptr(), part_u.data_ptr(), rows,
+                                             row_start, Cin0, H0, W0, _chain_arr(chain), len(chain), C, H, W, ops.norm_code(p),
+                                             ops._stream()), "fb_cw_norm_partials_f32")
+    return part_l, part_u
+
+
+def cw_relax_apply(op, z_lw, z_uw, lb, ub, norm_l, norm_u, row_start, H0, W0, chain, H, W, p, eps):
+    """Relaxation of compact rows from given (reduced) norm accumulations (fb_cw_relax_apply_f32)."""
+    dev = ops._chk(z_lw, z_uw, lb, ub, norm_l, norm_u)
+    rows, C = z_lw.shape[:2]
+    o_lw, o_uw, o_lb, o_ub = torch.empty_like(z_lw), torch.empty_like(z_uw), torch.empty_like(lb), torch.empty_like(ub)
+    coef = torch.empty(4 * C * H * W, device=dev)
+    with torch.cuda.device(dev):
+        check(load().fb_cw_relax_apply_f32(op, z_lw.data_ptr(), z_uw.data_ptr(), lb.data_ptr(), ub.data_ptr(), norm_l.data_ptr(),
+                                           norm_u.data_ptr(), o_lw.data_ptr(), o_uw.data_ptr(), o_lb.data_ptr(), o_ub.data_ptr(),
+                                           coef.data_ptr(), rows, row_start, H0, W0, _chain_arr(chain), len(chain), C, H, W,
+                                           ops.norm_code(p), float(eps), None, ops._stream()), "fb_cw_relax_apply_f32")
+    return o_lw, o_uw, o_lb, o_ub
+
+
+def cw_linear(z_lw, z_uw, weight, row_start, H0, W0, chain, H, W):
+    """Weight rows of the linear layer that ends the spatial part, from compact rows: [rows, N] (fb_cw_linear_f32)."""
+    dev = ops._chk(z_lw, z_uw, weight)
+    rows, C = z_lw.shape[:2]
+    N = weight.shape[0]
+    y_lw = torch.empty(rows, N, device=dev)
+    y_uw = torch.empty_like(y_lw)
+    wt_ws = torch.empty(weight.numel(), device=dev)
+    with torch.cuda.device(dev):
+        check(load().fb_cw_linear_f32(z_lw.data_ptr(), z_uw.data_ptr(), weight.data_ptr(), y_lw.data_ptr(), y_uw.data_ptr(),
+                                      wt_ws.data_ptr(), rows,
+                                      row_start, H0, W0, _chain_arr(chain), len(chain), C, H, W, N, ops._stream()),
+              "fb_cw_linear_f32")
+    return y_lw, y_uw
+
+
+def cw_expand(z_lw, z_uw, row_start, H0, W0, chain, H, W):
+    """Dense rows [rows, C, H, W] of a compact tensor (fb_cw_expand_f32)."""
+    dev = ops._chk(z_lw, z_uw)
+    rows, C = z_lw.shape[:2]
+    y_lw = torch.empty(rows, C, H, W, device=dev)
+    y_uw = torch.empty_like(y_lw)
+    with torch.cuda.device(dev):
+        check(load().fb_cw_expand_f32(z_lw.data_ptr(), z_uw.data_ptr(), y_lw.data_ptr(), y_uw.data_ptr(), rows, row_start, H0, W0,
+                                      _chain_arr(chain), len(chain), C, H, W, ops._stream()), "fb_cw_expand_f32")
+    return y_lw, y_uw
+
+
 class CnnVerifier:
     """Forward bound pass of conv -> relu -> conv -> relu -> linear on one image with every pixel
     perturbed (dim_in = C*H*W), the dim_in axis sharded over the ranks of `group`.
@@ -141,8 +245,9 @@ class CnnVerifier:
     general kernels operator by operator with the identity materialised.
     """
 
-    def __init__(self, layers, device, group=None, comm=None, algo=0):
+    def __init__(self, layers, device, group=None, comm=None, algo=0, compact=True):
         self.device = torch.device(device)
+        self.compact = compact  # rows kept as their windows only (fb_cw_*), or dense rows (fb_conv2d_windowed_f32)
         self.group = group
         self.comm = comm        # faith_b200.comm.Comm: the all-reduces are enqueued by the library (NCCL or one-shot)
         self.algo = algo
@@ -186,7 +291,7 @@ class CnnVerifier:
         comm = self.comm._h if (self.comm is not None and world > 1) else None
         with torch.cuda.device(self.device):
             check(lib.fb_cnn_forward_f32(ctypes.byref(net), img.data_ptr(), ops.norm_code(p), float(eps), start, size, comm,
-                                         self.algo, l.data_ptr(), u.data_ptr(), violation.data_ptr(), self._arena.data_ptr(),
+                                         self.algo, 1 if self.compact else 0, l.data_ptr(), u.data_ptr(), violation.data_ptr(), self._arena.data_ptr(),
                                          self._arena.numel(), ops._stream()), "fb_cnn_forward_f32")
         return l, u
 

@@ -356,7 +356,8 @@ int fb_merge_heads_f32(const float* x_w, const float* x_b, float* z_w, float* z_
  * is the batch axis of the convolution.  Replaces the commented-out
  * c_convolution_verification (kernel.cpp:268-295).
  * x_lw,x_uw [B, Di, Cin, H, W]; x_lb,x_ub [B, Cin, H, W]; Wt [Cout, Cin, Kh, Kw]; bias [Cout] or
- * NULL; y_lw,y_uw [B, Di, Cout, Ho, Wo]; y_lb,y_ub [B, Cout, Ho, Wo].  Di may be 0 (bias part alone). */
+ * NULL; y_lw,y_uw [B, Di, Cout, Ho, Wo]; y_lb,y_ub [B, Cout, Ho, Wo].  Di may be 0 (bias part alone; so may it
+ * in fb_matmul_f32). */
 int fb_conv2d_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
                   const float* Wt, const float* bias,
                   float* y_lw, float* y_uw, float* y_lb, float* y_ub,
@@ -482,14 +483,60 @@ int fb_concretize_sharded_f32(fb_comm* c, int algo,
                               float* l, float* u, float* part_ws,
                               int64_t rows, int Di_local, int Do, int words, int p, float eps, void* stream);
 
+/* ---- compact rows for the convolutions behind an identity input ---------------------------
+ * Row r of such a CNN is zero outside the window its pixel reaches (fb_conv2d_windowed_f32 above); here a row is stored
+ * as that window only, z [rows, C, wh, ww] with z[r, c, dy, dx] = row r at (c, y_lo(r) + dy, x_lo(r) + dx) and zeros
+ * where the pixel's own window is smaller than (wh, ww), the largest window over all pixels (fb_cw_extent).  `chain`
+ * (host, n_chain x 4 ints: kernel height, kernel width, stride, padding) always lists the convolutions that lead from
+ * the H0 x W0 image to the tensor in question, whose dense shape is [C, H, W].  For the benchmark CNN a row shrinks
+ * from 16 384 resp. 8 192 values to 144 resp. 288.  No counterpart in the reference.
+ *
+ * fb_cw_identity_relax_f32  first convolution + relaxation (op < 0: none), the compact form of
+ *                           fb_conv2d_identity_relax_f32 (same arguments; z instead of y_lw / y_uw).
+ * fb_cw_conv2d_f32          a later convolution, compact -> compact (weight part; the bias part is fb_conv2d_f32 with
+ *                           Di = 0).  `chain` leads to the input [Cin, H, W]; the output's chain is that plus this layer.
+ *                           Expands to fb_conv2d_f32's values bit for bit.
+ * fb_cw_norm_partials_f32   unfinished dual-norm accumulation of every dense column over the rows of the shard
+ *                           (the counterpart of fb_norm_partials_f32): part_l, part_u [C*H*W]; Cin0 = channels of the
+ *                           original image (dim_in = Cin0 * H0 * W0).  Gathered in row order: deterministic.
+ * fb_cw_relax_apply_f32     relaxation from (all-reduced) norms, the counterpart of fb_relax_with_norms_f32: rescaled
+ *                           compact rows, relaxed bias terms out_lb / out_ub [C*H*W]; coef_ws: 4*C*H*W floats of scratch.
+ * fb_cw_linear_f32          the linear layer that ends the spatial part, weight rows only: Wl [N, C*H*W] (nn.Linear
+ *                           layout) -> y_lw, y_uw [rows, N] dense (bias rows: fb_matmul_f32 with Di = 0); wt_ws: N*C*H*W
+ *                           floats of scratch (the call transposes the weight once so that its reads coalesce).
+ * fb_cw_expand_f32          dense rows [rows, C, H, W] from compact ones. */
+int fb_cw_extent(int H0, int W0, const int* chain, int n_chain, int* wh, int* ww);
+int fb_cw_identity_relax_f32(int op, const float* x_lb, const float* x_ub, const float* Wt, const float* bias,
+                             float scale, float* z_lw, float* z_uw, float* y_lb, float* y_ub, float* col_ws,
+                             int64_t rows, int64_t row_start, int Cin, int H, int W, int Cout, int Kh, int Kw,
+                             int stride, int pad, int p, float eps, int* violation, void* stream);
+int fb_cw_conv2d_f32(const float* x_lw, const float* x_uw, const float* Wt, float* y_lw, float* y_uw,
+                     int64_t rows, int64_t row_start, int H0, int W0, const int* chain, int n_chain,
+                     int Cin, int H, int W, int Cout, int Kh, int Kw, int stride, int pad, void* stream);
+int fb_cw_norm_partials_f32(const float* z_lw, const float* z_uw, float* part_l, float* part_u,
+                            int64_t rows, int64_t row_start, int Cin0, int H0, int W0, const int* chain, int n_chain,
+                            int C, int H, int W, int p, void* stream);
+int fb_cw_relax_apply_f32(int op, const float* z_lw, const float* z_uw, const float* lb, const float* ub,
+                          const float* norm_l, const float* norm_u, float* out_lw, float* out_uw,
+                          float* out_lb, float* out_ub, float* coef_ws, int64_t rows, int64_t row_start,
+                          int H0, int W0, const int* chain, int n_chain, int C, int H, int W,
+                          int p, float eps, int* violation, void* stream);
+int fb_cw_linear_f32(const float* z_lw, const float* z_uw, const float* Wl, float* y_lw, float* y_uw, float* wt_ws,
+                     int64_t rows, int64_t row_start, int H0, int W0, const int* chain, int n_chain,
+                     int C, int H, int W, int N, void* stream);
+int fb_cw_expand_f32(const float* z_lw, const float* z_uw, float* y_lw, float* y_uw,
+                     int64_t rows, int64_t row_start, int H0, int W0, const int* chain, int n_chain,
+                     int C, int H, int W, void* stream);
+
 /* ---- whole-model driver: CNN with every pixel of the image perturbed ----------------------
  * conv -> [relu] -> (conv | relu)* -> linear -> (relu | linear)*, dim_in = cin * h * w, input bound lw = uw = I,
  * lb = ub = image [cin, h, w] (device).  Computes the rows [row_start, row_start + rows) of dim_in (a rank's shard, or
  * 0 and cin*h*w) and writes the concretised range of the last layer, out_l / out_u [features of the last layer]; with a
  * communicator (world > 1) the dual norms are all-reduced over the ranks by `algo` (fb_allreduce_algo) and every rank
  * gets the same range, with comm == NULL nothing is exchanged.  One call enqueues the whole pass on `stream`.
- * The first layer must be a convolution (its output, and the relaxation behind it, are written from the filter alone,
- * fb_conv2d_identity_relax_f32); later convolutions go through fb_conv2d_windowed_f32.  The reference has no CNN
+ * The first layer must be a convolution (its output, and the relaxation behind it, are written from the filter alone).
+ * compact != 0 (the default of the Python layer): rows are kept as their windows only (the fb_cw_* operators above)
+ * until the first linear layer; compact == 0: dense rows, fb_conv2d_identity_relax_f32 and fb_conv2d_windowed_f32.  The reference has no CNN
  * verifier to mirror (HandTunedKernels/convolution_verification.cu:228-238 is a benchmark stub); layer semantics are
  * Bounds.matmul / Bounds.relu (Bounds.py:397-413, :921-963) with dim_in as the batch axis of the convolutions.
  * Weights are device pointers: conv [cout, cin, kh, kw], linear [n_out, features] (nn.Linear layout), bias or NULL. */
@@ -508,7 +555,7 @@ typedef struct fb_cnn {
 } fb_cnn;
 int64_t fb_cnn_workspace_bytes(const fb_cnn* net, int64_t rows);   /* -1: malformed network */
 int fb_cnn_forward_f32(const fb_cnn* net, const float* image, int p, float eps, int64_t row_start, int64_t rows,
-                       fb_comm* comm, int algo, float* out_l, float* out_u, int* violation,
+                       fb_comm* comm, int algo, int compact, float* out_l, float* out_u, int* violation,
                        void* workspace, int64_t workspace_bytes, void* stream);
 
 /* ---- measurement hooks (no counterpart in the reference) --------------------------------

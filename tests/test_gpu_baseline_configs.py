@@ -124,9 +124,11 @@ def test_config3_tanh_linear():
     helpers.assert_bounds_arbitrated(sub(gh), oh, O.OBounds(p, eps, *_dbl(t2), words=4).matmul(W1.double()), "C3 first linear")
     cpu = lambda b, dt=torch.float32: O.OBounds(p, eps, b.lw[:2].cpu().to(dt), b.lb[:2].cpu().to(dt), b.uw[:2].cpu().to(dt),
                                                 b.ub[:2].cpu().to(dt), words=4)
-    # (the tanh relaxation is elementwise, not GEMM-shaped: the per-operator bar, its absolute part doubled for the
-    # 10-step bisection of the tangent point run in two fp32 orders)
-    _cmp(sub(gt), cpu(gh).tanh(), "C3 tanh", atol=2e-6)
+    # The tanh relaxation finds its tangent points by a 10-step bisection on tanhf / coshf values: a last-bit difference
+    # between two libm implementations (the GPU's, the host's, which itself varies with the host's vector unit) moves
+    # a tangent point by one step for a few per cent of the columns here (ranges of several units), a 1e-5-sized jump
+    # in the line that says nothing about either implementation.  The fp64 run of the same algorithm is the arbiter.
+    helpers.assert_bounds_arbitrated(sub(gt), cpu(gh).tanh(), cpu(gh, torch.float64).tanh(), "C3 tanh")
     helpers.assert_bounds_arbitrated(sub(gy), cpu(gt).matmul(W2), cpu(gt, torch.float64).matmul(W2.double()),
                                      "C3 linear after tanh")
 
