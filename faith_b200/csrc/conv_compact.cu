@@ -78,15 +78,18 @@ cw_identity_rows_kernel(const float* __restrict__ Wt, const float* __restrict__ 
 // both the staging stores, whose lanes differ in the tap, and the reads, whose lanes differ in the channel, are free of
 // bank conflicts).
 constexpr int kCwRows = 8;
+// CPT: output channels per work item (4 when Cout is a multiple of 4: the four weights of a tap are one 128-bit read and
+// the input pair is read once for four channels, which halves the instructions per multiply-add; else 1).
+template <int CPT>
 __global__ void __launch_bounds__(256)
 cw_conv_kernel(const float* __restrict__ x_lo, const float* __restrict__ x_up, const float* __restrict__ Wt,
                float* __restrict__ y_lo, float* __restrict__ y_up, int64_t rows, int64_t row_start, int H0, int W0,
                const ConvChain ch, int Cin, int Cout, int Kh, int Kw, int stride, int pad, int Ho, int Wo, int iwh, int iww,
                int owh, int oww) {
-  extern __shared__ __align__(8) float cw_smem[];
-  const int ldw = Cout + 1, ctaps = Cin * Kh * Kw;
+  extern __shared__ __align__(16) float cw_smem[];
+  const int ldw = Cout + (CPT == 4 ? 4 : 1), ctaps = Cin * Kh * Kw;   // padded: staging stores and reads spread over the banks
   const int n_in = Cin * iwh * iww, n_out = Cout * owh * oww, n_w = ctaps * ldw;
-  float* s_w = cw_smem;                                        // [Cin][Kh][Kw][Cout + 1]
+  float* s_w = cw_smem;                                        // [Cin][Kh][Kw][ldw]
   float2* s_x = reinterpret_cast<float2*>(cw_smem + n_w + (n_w & 1));   // [kCwRows][Cin][iwh][iww] (centre, radius)
   __shared__ int s_geo[kCwRows][8];   // wy.lo, wx.lo, ah, aw, oy.lo, ox.lo, bh, bw (bh = 0: nothing to compute)
   const int64_t lr0 = (int64_t)blockIdx.x * kCwRows;
@@ -111,32 +114,43 @@ cw_conv_kernel(const float* __restrict__ x_lo, const float* __restrict__ x_up, c
     gq[4] = oy.lo, gq[5] = ox.lo, gq[6] = empty ? 0 : oy.hi - oy.lo + 1, gq[7] = empty ? 0 : ox.hi - ox.lo + 1;
   }
   __syncthreads();
-  const int taps = Kh * Kw;
-  for (int i = threadIdx.x; i < nr * n_out; i += blockDim.x) {
-    const int co = i % Cout, q = i / Cout;
+  const int taps = Kh * Kw, cgroups = Cout / CPT;
+  for (int i = threadIdx.x; i < nr * owh * oww * cgroups; i += blockDim.x) {
+    const int co = (i % cgroups) * CPT, q = i / cgroups;
     const int x = q % oww, y = (q / oww) % owh, lr = q / (oww * owh);
     const int* gq = s_geo[lr];
-    float lo = 0.f, up = 0.f;
-    if (y < gq[6] && x < gq[7]) {
+    float ac[CPT], ar[CPT];
+#pragma unroll
+    for (int e = 0; e < CPT; ++e) { ac[e] = 0.f; ar[e] = 0.f; }
+    const bool live = y < gq[6] && x < gq[7];
+    if (live) {
       const int iy0 = (gq[4] + y) * stride - pad - gq[0], ix0 = (gq[5] + x) * stride - pad - gq[1];   // window coordinates
       const int ky0 = max(0, -iy0), ky1 = min(Kh, gq[2] - iy0), kx0 = max(0, -ix0), kx1 = min(Kw, gq[3] - ix0);
       const float2* xp = s_x + (lr * Cin * iwh + iy0) * iww + ix0;
       const float* wp = s_w + co;
-      float ac = 0.f, ar = 0.f;
       for (int c = 0; c < Cin; ++c, xp += iwh * iww, wp += taps * ldw)
         for (int ky = ky0; ky < ky1; ++ky)
           for (int kx = kx0; kx < kx1; ++kx) {
-            const float w = wp[(ky * Kw + kx) * ldw];
             const float2 v = xp[ky * iww + kx];
-            ac = fmaf(v.x, w, ac);
-            ar = fmaf(v.y, fabsf(w), ar);
+            if (CPT == 4) {
+              const float4 w = *reinterpret_cast<const float4*>(wp + (ky * Kw + kx) * ldw);
+              ac[0] = fmaf(v.x, w.x, ac[0]); ar[0] = fmaf(v.y, fabsf(w.x), ar[0]);
+              ac[1 % CPT] = fmaf(v.x, w.y, ac[1 % CPT]); ar[1 % CPT] = fmaf(v.y, fabsf(w.y), ar[1 % CPT]);
+              ac[2 % CPT] = fmaf(v.x, w.z, ac[2 % CPT]); ar[2 % CPT] = fmaf(v.y, fabsf(w.z), ar[2 % CPT]);
+              ac[3 % CPT] = fmaf(v.x, w.w, ac[3 % CPT]); ar[3 % CPT] = fmaf(v.y, fabsf(w.w), ar[3 % CPT]);
+            } else {
+              const float w = wp[(ky * Kw + kx) * ldw];
+              ac[0] = fmaf(v.x, w, ac[0]);
+              ar[0] = fmaf(v.y, fabsf(w), ar[0]);
+            }
           }
-      lo = fsub(ac, ar);
-      up = fadd(ac, ar);
     }
-    const int64_t o = (lr0 + lr) * n_out + ((int64_t)co * owh + y) * oww + x;
-    y_lo[o] = lo;
-    y_up[o] = up;
+#pragma unroll
+    for (int e = 0; e < CPT; ++e) {
+      const int64_t o = (lr0 + lr) * n_out + ((int64_t)(co + e) * owh + y) * oww + x;
+      y_lo[o] = live ? fsub(ac[e], ar[e]) : 0.f;
+      y_up[o] = live ? fadd(ac[e], ar[e]) : 0.f;
+    }
   }
 }
 
@@ -448,13 +462,15 @@ extern "C" int fb_cw_conv2d_f32(const float* x_lw, const float* x_uw, const floa
   if (rc != FB_OK) return rc;
   if (rows == 0) return FB_OK;
   if (rows > 0x7fffffff) return FB_ERR_SHAPE;
-  const size_t n_w = (size_t)Cin * Kh * Kw * (Cout + 1);
+  const bool by4 = Cout % 4 == 0;
+  const size_t n_w = (size_t)Cin * Kh * Kw * (Cout + (by4 ? 4 : 1));
   const size_t smem = sizeof(float) * (n_w + (n_w & 1) + 2 * (size_t)kCwRows * Cin * gi.wh * gi.ww);
   if (smem > (size_t)device_info().smem_optin) return FB_ERR_SHAPE;
-  if (smem > 48 * 1024) FB_CUDA_OK(cudaFuncSetAttribute(cw_conv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  auto kern = by4 ? cw_conv_kernel<4> : cw_conv_kernel<1>;
+  if (smem > 48 * 1024) FB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   ProfileScope prof(PK_CONV, 8.0 * rows * Cout * go.wh * go.ww * Cin * Kh * Kw,
                     4.0 * 2.0 * rows * ((double)Cin * gi.wh * gi.ww + (double)Cout * go.wh * go.ww), stream);
-  cw_conv_kernel<<<(unsigned)ceil_div(rows, kCwRows), 256, smem, (cudaStream_t)stream>>>(
+  kern<<<(unsigned)ceil_div(rows, kCwRows), 256, smem, (cudaStream_t)stream>>>(
       x_lw, x_uw, Wt, y_lw, y_uw, rows, row_start, H0, W0, gi.ch, Cin, Cout, Kh, Kw, stride, pad, Ho, Wo, gi.wh, gi.ww, go.wh, go.ww);
   FB_LAUNCH_OK();
   return FB_OK;

@@ -245,8 +245,10 @@ class CnnVerifier:
     general kernels operator by operator with the identity materialised.
     """
 
-    def __init__(self, layers, device, group=None, comm=None, algo=0, compact=True):
+    def __init__(self, layers, device, group=None, comm=None, algo=0, compact=True, graph=True):
         self.device = torch.device(device)
+        self.graph = graph      # single-GPU passes through the driver are replayed from a CUDA graph
+        self._graphs = {}
         self.compact = compact  # rows kept as their windows only (fb_cw_*), or dense rows (fb_conv2d_windowed_f32)
         self.group = group
         self.comm = comm        # faith_b200.comm.Comm: the all-reduces are enqueued by the library (NCCL or one-shot)
@@ -274,8 +276,9 @@ class CnnVerifier:
         self._recs = recs
         self._driver_ok = bool(self.layers) and self.layers[0][0] == "conv"
 
-    def _forward_driver(self, image, p, eps, start, size, world):
-        C, H, W = image.shape
+    def _run_driver(self, img, p, eps, start, size, world):
+        """One fb_cnn_forward_f32 call on the current stream; img [C, H, W] on the device."""
+        C, H, W = img.shape
         lib = load()
         net = _lib.Cnn(len(self.layers), self._recs, C, H, W)
         need = lib.fb_cnn_workspace_bytes(ctypes.byref(net), size)
@@ -283,7 +286,6 @@ class CnnVerifier:
             raise _lib.FaithError("fb_cnn_workspace_bytes: network not supported by the driver")
         if self._arena is None or self._arena.numel() < need:
             self._arena = torch.empty(need, dtype=torch.uint8, device=self.device)
-        img = image.to(self.device, torch.float32, non_blocking=True).contiguous()
         n_out = self._out_features(C, H, W)
         l = torch.empty(n_out, device=self.device)
         u = torch.empty(n_out, device=self.device)
@@ -291,9 +293,34 @@ class CnnVerifier:
         comm = self.comm._h if (self.comm is not None and world > 1) else None
         with torch.cuda.device(self.device):
             check(lib.fb_cnn_forward_f32(ctypes.byref(net), img.data_ptr(), ops.norm_code(p), float(eps), start, size, comm,
-                                         self.algo, 1 if self.compact else 0, l.data_ptr(), u.data_ptr(), violation.data_ptr(), self._arena.data_ptr(),
-                                         self._arena.numel(), ops._stream()), "fb_cnn_forward_f32")
+                                         self.algo, 1 if self.compact else 0, l.data_ptr(), u.data_ptr(), violation.data_ptr(),
+                                         self._arena.data_ptr(), self._arena.numel(), ops._stream()), "fb_cnn_forward_f32")
         return l, u
+
+    def _forward_driver(self, image, p, eps, start, size, world):
+        if not self.graph or world > 1:
+            img = image.to(self.device, torch.float32, non_blocking=True).contiguous()
+            return self._run_driver(img, p, eps, start, size, world)
+        # Single GPU: the pass is a dozen launches of a few microseconds each, which cost more to launch than to run;
+        # they are captured once per (shape, norm, radius) into a CUDA graph that reads the image from a fixed device
+        # buffer and writes the range to fixed outputs.  (Not with a communicator: the one-shot exchange takes its
+        # epoch as a kernel argument, which a replay would repeat.)
+        key = (tuple(image.shape), float(p), float(eps), start, size)
+        ent = self._graphs.get(key)
+        if ent is None:
+            with torch.cuda.device(self.device):
+                static_img = torch.empty(tuple(image.shape), device=self.device)
+                static_img.copy_(image)
+                self._run_driver(static_img, p, eps, start, size, world)      # sizes the arena, warms every launcher
+                torch.cuda.synchronize(self.device)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    l, u = self._run_driver(static_img, p, eps, start, size, world)
+            ent = self._graphs[key] = (g, static_img, l, u)
+        g, static_img, l, u = ent
+        static_img.copy_(image, non_blocking=True)
+        g.replay()
+        return l.clone(), u.clone()
 
     def _out_features(self, C, H, W):
         c, h, w = C, H, W
