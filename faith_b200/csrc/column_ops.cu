@@ -568,10 +568,7 @@ size_t relax_smem_bytes(int Di, bool staged, int tiles) {
 
 template <typename K>
 int ensure_smem(K kernel, size_t bytes) {
-  if (bytes > 48 * 1024) {
-    FB_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
-  }
-  return FB_OK;
+  return ensure_dynamic_smem(kernel, bytes);
 }
 
 int launch_relax(int op, const float* lw, const float* uw, const float* lb, const float* ub,

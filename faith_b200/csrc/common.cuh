@@ -37,6 +37,27 @@ const DeviceInfo& device_info();
 
 void count_launches(int n);
 
+// Hint for the tensor-core GEMM (thread-local, set by the encoder driver around the projections of the first layer):
+// the operand has M rows in blocks of Di per (sentence, position) pair, L positions per sentence, and only the
+// blocks of the perturbed positions are non-zero (the input bound is an identity at those positions and zero
+// elsewhere, VerifierForward.py:127-156).  Positions: `pos` (one set for all sentences) or `inst_pos` (device,
+// [sentences, words]).  The zero-radius GEMM then writes zeros for the other blocks without reading or multiplying.
+struct LiveRows {
+  int L, Di, words;
+  int pos[4];
+  const int* inst_pos;
+  int64_t M;
+};
+void tc_set_live_rows(const LiveRows* lr);   // nullptr clears
+
+// Opts `kernel` in to `bytes` of dynamic shared memory on the current device (nothing to do up to 48 KB, or when it
+// already has that much): FB_OK or FB_ERR_CUDA.
+int ensure_dynamic_smem_impl(const void* func, size_t bytes);
+template <typename K>
+inline int ensure_dynamic_smem(K kernel, size_t bytes) {
+  return ensure_dynamic_smem_impl(reinterpret_cast<const void*>(kernel), bytes);
+}
+
 // Optional per-operator timing (fb_profile_enable): the outermost C-ABI operator call on a thread
 // brackets its launches with a pair of CUDA events on the caller's stream and records the
 // algorithmic work of the call.  Disabled (the default), a scope costs one branch.

@@ -197,8 +197,7 @@ int launch_conv_t(const float* x_lo, const float* x_up, const float* Wt, const f
   const int tiles_h = (int)ceil_div(Ho, TH), tiles_w = (int)ceil_div(Wo, TW), co_chunks = (int)ceil_div(Cout, CO);
   const int64_t blocks = N * co_chunks * tiles_h * tiles_w;
   if (blocks > 0x7fffffff) return FB_ERR_SHAPE;
-  if (smem > 48 * 1024)
-    FB_CUDA_OK(cudaFuncSetAttribute(conv_bounds_kernel<TH, TW, CO, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  if (int rc = ensure_dynamic_smem(conv_bounds_kernel<TH, TW, CO, KS>, smem)) return rc;
   conv_bounds_kernel<TH, TW, CO, KS><<<(unsigned)blocks, kThreads, smem, st>>>(x_lo, x_up, Wt, bias, y_lo, y_up, Cin, H, W, Cout,
                                                                          Kh, Kw, stride, pad, Ho, Wo, tiles_h, tiles_w,
                                                                          co_chunks);
@@ -525,7 +524,7 @@ extern "C" int fb_conv2d_windowed_f32(const float* x_lw, const float* x_uw, cons
   cudaStream_t st = (cudaStream_t)stream;
   const bool vec = Wo % 4 == 0 && fb::aligned16(y_lw) && fb::aligned16(y_uw);
   auto kern = vec ? fb::conv_window_kernel<4> : fb::conv_window_kernel<1>;
-  if (smem > 48 * 1024) FB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  if (int rc = fb::ensure_dynamic_smem(kern, smem)) return rc;
   fb::ProfileScope prof(fb::PK_CONV, 8.0 * rows * Cout * out_h * out_w * Cin * Kh * Kw,
                         4.0 * (2.0 * rows * Cin * win_h * win_w + 2.0 * rows * ncol), stream);
   kern<<<(unsigned)rows, 256, smem, st>>>(x_lw, x_uw, Wt, y_lw, y_uw, row_start, H0, W0, ch, Cin, H, W, Cout, Kh, Kw, stride, pad,

@@ -467,7 +467,7 @@ extern "C" int fb_cw_conv2d_f32(const float* x_lw, const float* x_uw, const floa
   const size_t smem = sizeof(float) * (n_w + (n_w & 1) + 2 * (size_t)kCwRows * Cin * gi.wh * gi.ww);
   if (smem > (size_t)device_info().smem_optin) return FB_ERR_SHAPE;
   auto kern = by4 ? cw_conv_kernel<4> : cw_conv_kernel<1>;
-  if (smem > 48 * 1024) FB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  if (int rc = ensure_dynamic_smem(kern, smem)) return rc;
   ProfileScope prof(PK_CONV, 8.0 * rows * Cout * go.wh * go.ww * Cin * Kh * Kw,
                     4.0 * 2.0 * rows * ((double)Cin * gi.wh * gi.ww + (double)Cout * go.wh * go.ww), stream);
   kern<<<(unsigned)ceil_div(rows, kCwRows), 256, smem, (cudaStream_t)stream>>>(

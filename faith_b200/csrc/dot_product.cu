@@ -454,12 +454,12 @@ static int dot_heads_impl(const float* x_lw, const float* x_uw, const float* x_l
       const int n_kc = (int)ceil_div(K, TK);
       const int64_t n_items = blocks * n_kc;
       const size_t psmem = sizeof(float) * kDotPipeSmemFloats;
-      FB_CUDA_OK(cudaFuncSetAttribute(dot_weight_native_pipelined, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)psmem));
+      if (int rc = ensure_dynamic_smem(dot_weight_native_pipelined, psmem)) return rc;
       const int64_t sms = device_info().sms;
       dot_weight_native_pipelined<<<(unsigned)(blocks < sms ? blocks : sms), kThreads, psmem, st>>>(
           x_lw, x_uw, y_lw, y_uw, x_l, y_l, y_u, z_lw, z_uw, Lx, Ly, Di, K, n_it, n_jt, n_mt, n_kc, n_items, out_scale, merge_heads);
     } else {
-      FB_CUDA_OK(cudaFuncSetAttribute(dot_weight_native<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      if (int rc = ensure_dynamic_smem(dot_weight_native<false>, smem)) return rc;
       dot_weight_native<false><<<(unsigned)blocks, kThreads, smem, st>>>(x_lw, x_uw, y_lw, y_uw, x_l, y_l, y_u, z_lw,
                                                                          z_uw, Lx, Ly, Di, K, n_it, n_jt, n_mt, out_scale);
     }

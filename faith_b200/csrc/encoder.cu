@@ -11,6 +11,8 @@
 
 #include <utility>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace fb {
@@ -23,6 +25,12 @@ namespace {
 struct StatusSinkScope {
   explicit StatusSinkScope(int* status) { tc_set_status_sink(status); }
   ~StatusSinkScope() { tc_set_status_sink(nullptr); }
+};
+
+// Around the projections of the first layer: tells the tensor-core GEMM which row blocks of the layer input are zero.
+struct LiveRowsScope {
+  explicit LiveRowsScope(const LiveRows* lr) { tc_set_live_rows(lr); }
+  ~LiveRowsScope() { tc_set_live_rows(nullptr); }
 };
 
 struct BoundSet {
@@ -277,6 +285,13 @@ static int encoder_forward_impl(const fb_encoder* enc, const float* emb, int S, 
     // so the products that read them fetch every tile from HBM once.
     BoundSet Qh = T2, Kh = T3;
     if (li == 0) { Qh.uw = Qh.lw; Kh.uw = Kh.lw; }
+    // The layer input of the first layer is zero in the weight rows of every position that is not perturbed (identity
+    // rows at the perturbed positions only, and the exact layer norm keeps zero rows zero): the three projections of
+    // this layer need not read or multiply those row blocks.
+    LiveRows live_in = {L, Di, words, {0, 0, 0, 0}, inst_pos, rows * (int64_t)Di};
+    for (int w = 0; positions != nullptr && w < words; ++w) live_in.pos[w] = positions[w];
+    // (FB_ENCODER_NO_ZERO_SKIP in the environment switches this off: the tests compare both ways bit for bit)
+    const LiveRowsScope live_scope(li == 0 && getenv("FB_ENCODER_NO_ZERO_SKIP") == nullptr ? &live_in : nullptr);
     // queries and keys, split into heads: [S*H, L, Di, d].  Where the shapes allow it the projection also
     // returns the concretised range of its result (column norms taken in the GEMM epilogue), which the
     // product below would otherwise compute in a pass of its own over the operand.

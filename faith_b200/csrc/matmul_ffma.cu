@@ -410,7 +410,7 @@ int launch_split_sign_ffma(const float* a_lo, const float* a_up, const float* W,
   if (N <= 16 && split_rows == 0 && K >= 1024 && K % 4 == 0 && aligned16(a_lo) && aligned16(a_up) && aligned16(W) &&
       ceil_div(M, kThreads / 32) <= 0x7fffffff) {
     const size_t gemv_smem = sizeof(float) * 2 * 16 * kGemvChunk;
-    FB_CUDA_OK(cudaFuncSetAttribute(split_sign_gemv_tiled<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemv_smem));
+    if (int rc = ensure_dynamic_smem(split_sign_gemv_tiled<16>, gemv_smem)) return rc;
     split_sign_gemv_tiled<16><<<(unsigned)ceil_div(M, kThreads / 32), kThreads, gemv_smem, st>>>(a_lo, a_up, W, bias, c_lo, c_up, M, N, K);
     FB_LAUNCH_OK();
     return FB_OK;
@@ -429,10 +429,10 @@ int launch_split_sign_ffma(const float* a_lo, const float* a_up, const float* W,
   const size_t smem = sizeof(float) * 2 * kStageFloats;
   const bool vec = K % 4 == 0 && aligned16(a_lo) && aligned16(a_up) && aligned16(W);
   if (vec) {
-    FB_CUDA_OK(cudaFuncSetAttribute(split_sign_gemm_ffma<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (int rc = ensure_dynamic_smem(split_sign_gemm_ffma<true>, smem)) return rc;
     split_sign_gemm_ffma<true><<<dim3((unsigned)gm, gn), kThreads, smem, st>>>(a_lo, a_up, W, bias, c_lo, c_up, M, N, K, split_rows, split_d);
   } else {
-    FB_CUDA_OK(cudaFuncSetAttribute(split_sign_gemm_ffma<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (int rc = ensure_dynamic_smem(split_sign_gemm_ffma<false>, smem)) return rc;
     split_sign_gemm_ffma<false><<<dim3((unsigned)gm, gn), kThreads, smem, st>>>(a_lo, a_up, W, bias, c_lo, c_up, M, N, K, split_rows, split_d);
   }
   FB_LAUNCH_OK();

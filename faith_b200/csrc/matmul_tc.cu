@@ -155,10 +155,24 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
                    int n_tiles_n, int64_t total_tiles, int split_rows, int split_d,
                    const float* __restrict__ coef_l, const float* __restrict__ coef_u, int coef_di,
                    float* __restrict__ norm_lo, float* __restrict__ norm_up, int norm_p,
-                   int* __restrict__ status, uint32_t wait_tries, int skip_it) {
+                   int* __restrict__ status, uint32_t wait_tries, int skip_it, const LiveRows live_rows, int same_out) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  // Row blocks known to be zero (live_rows.L > 0; zero-radius instantiation only): a tile of such a block is not
+  // loaded, converted or multiplied; the issuers only signal "ready" and the epilogue stores zeros (and zero norms).
+  const bool use_live = kPoint && kNorm && !kCoef && !kResid && live_rows.L > 0;
+  auto tile_live = [&](int tile) -> bool {
+    if (!use_live) return true;
+    const int bl = (int)(((int64_t)(tile / n_tiles_n) * BM) / live_rows.Di);
+    const int l = bl % live_rows.L, b = bl / live_rows.L;
+    bool live = false;
+#pragma unroll
+    for (int w = 0; w < 4; ++w)
+      if (w < live_rows.words)
+        live |= (live_rows.inst_pos != nullptr ? __ldg(live_rows.inst_pos + b * live_rows.words + w) : live_rows.pos[w]) == l;
+    return live;
+  };
   // barriers: full[2], raw_empty[2], ops_ready[2], mma_done[2], acc_ready, acc_free; then the TMEM base slot and the abort flag
   const uint32_t bar0 = base + SharedLayout::bars();
   const uint32_t bar_full = bar0 + 0;            // [kRawStages]
@@ -214,6 +228,7 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
     bool ok = true;
     for (int ti = 0; ti < my_tiles && ok; ++ti) {
       const int tile = blockIdx.x + ti * gridDim.x;
+      if (!tile_live(tile)) continue;
       const int m0 = (int)(tile / n_tiles_n) * BM, n0 = (int)(tile % n_tiles_n) * BN;
       for (int kb = 0; kb < nkb; ++kb, ++it) {
         const int rs = (int)(it % kRawStages);
@@ -252,12 +267,14 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
           blo[st][pl][j] = (uint32_t)bdesc0 + ((st * kPlaneStageBytes + pl * kWTileBytes + j * 32) >> 4);
           acol[st][pl][j] = tmem_base + kABase + st * 128 + pl * 32 + j * 8;
         }
+    int lt = 0;   // tiles multiplied so far: the accumulator hand-shake with the epilogue counts these only
     for (int ti = 0; ti < my_tiles && ok; ++ti) {
+      if (!tile_live(blockIdx.x + ti * gridDim.x)) continue;   // a zero row block: nothing to multiply, nothing to signal
       for (int kb = 0; kb < nkb; ++kb, ++it) {
         const int s = (int)(it & 1);
         ok = mbar_wait_warp(bar_ops_ready + 8 * s, (uint32_t)((it >> 1) & 1), wc);
         // the first MMA of a tile overwrites the accumulators: the previous tile must have been read out
-        if (ok && kb == 0 && ti > 0) ok = mbar_wait_warp(bar_acc_free, (uint32_t)((ti - 1) & 1), wc);
+        if (ok && kb == 0 && lt > 0) ok = mbar_wait_warp(bar_acc_free, (uint32_t)((lt - 1) & 1), wc);
         if (!ok) break;
         tc_fence_after();
         if (lane == 0) {
@@ -275,6 +292,7 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
         }
         __syncwarp();
       }
+      ++lt;
     }
   } else if (warp < kFirstConvWarp) {
     // ------------------------------------------------------------------ epilogue (warps 4-11)
@@ -299,14 +317,59 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
       return r;
     };
     const int chalf = (warp - kCtrlWarps) >> 2;   // which 32 of the 64 tile columns (= which output box)
+    bool staging_zero = false;   // the staging buffer holds zeros (left there by a tile of a zero row block)
+    int le = 0;                  // tiles read out of tensor memory so far (the issuers count the same tiles)
     for (int e = 0; e < my_tiles && ok; ++e) {
+      const int etile = blockIdx.x + e * gridDim.x;
+      const bool elive = tile_live(etile);
+      const int my = (etile / n_tiles_n) * BM, nx = (etile % n_tiles_n) * BN;
+      if (!elive) {
+        // A zero row block (kPoint and kNorm only): the result is +0 everywhere and so are its column norms.  The
+        // accumulators play no part (the issuers skip the tile as well); the staging buffer is zeroed once and then
+        // stored from for every such tile in a row, without being touched again, so these tiles cost their stores and
+        // little else.
+        if (!staging_zero) {
+          if (leader) tma_store_wait_read();
+          ok = epi_sync();
+          if (!ok) break;
+          float4* sz = reinterpret_cast<float4*>(base_ptr + SharedLayout::out());
+          for (uint32_t i = threadIdx.x - 32 * kCtrlWarps; i < kOutStageBytes / 16; i += 32 * kEpiWarps)
+            sz[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+          fence_async_smem();
+          ok = epi_sync();
+          if (!ok) break;
+          staging_zero = true;
+        }
+        if (leader) {
+          const uint32_t so = base + SharedLayout::out();
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            int cx = nx + 32 * q, cy = my, cz = 0;
+            if (split_rows > 0) {
+              const int heads = N / split_d;
+              cz = (my / split_rows) * heads + cx / split_d;
+              cy = my % split_rows;
+              cx = cx % split_d;
+            }
+            tma_store_3d(&tm_out_lo, cx, cy, cz, so + q * kOutBoxBytes);
+            // (zero radius and one buffer named as both outputs: the two tiles are the same numbers, stored once)
+            if (!(kPoint && same_out)) tma_store_3d(&tm_out_up, cx, cy, cz, so + (2 + q) * kOutBoxBytes);
+          }
+          tma_store_commit();
+        }
+        if (kNorm) {
+          const int i = (int)threadIdx.x - 32 * kCtrlWarps;   // 0..255: 64 lower and 64 upper norms
+          const int n = nx + (i & 63);
+          if (i < 128 && n < N) (i < 64 ? norm_lo : norm_up)[(int64_t)(my / BM) * N + n] = 0.f;
+        }
+        continue;
+      }
+      staging_zero = false;
       // the staging buffer is free once the previous tile's stores have read it: settle that before
       // the accumulators become ready, so that nothing stands between "ready" and the read-out
       if (leader) tma_store_wait_read();
       ok = epi_sync();
       if (!ok) break;
-      const int etile = blockIdx.x + e * gridDim.x;
-      const int my = (etile / n_tiles_n) * BM, nx = (etile % n_tiles_n) * BN;
       if (kResid && leader) {
         // the staging buffer is free now: fetch the residual tile into it (same boxes as the store below)
         const uint32_t so = base + SharedLayout::out();
@@ -317,8 +380,9 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
           tma_load_3d(so + (2 + q) * kOutBoxBytes, &tm_res_up, nx + 32 * q, my, 0, bar_res);
         }
       }
-      ok = mbar_wait_warp(bar_acc_ready, (uint32_t)(e & 1), wc);
+      ok = mbar_wait_warp(bar_acc_ready, (uint32_t)(le & 1), wc);
       if (!ok) break;
+      ++le;
       tc_fence_after();
       if (kResid) {
         ok = mbar_wait_warp(bar_res, (uint32_t)(e & 1), wc);
@@ -392,7 +456,7 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
             cx = cx % split_d;
           }
           tma_store_3d(&tm_out_lo, cx, cy, cz, so + q * kOutBoxBytes);
-          tma_store_3d(&tm_out_up, cx, cy, cz, so + (2 + q) * kOutBoxBytes);
+          if (!(kPoint && same_out)) tma_store_3d(&tm_out_up, cx, cy, cz, so + (2 + q) * kOutBoxBytes);
         }
         tma_store_commit();
       }
@@ -435,7 +499,13 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     bool ok = true;
     int c_ti = 0, c_kb = g;   // tile and k-block of `it`, kept incrementally (used by the coefficient loads)
-    for (int it = g; it < total_it && ok; it += 2, c_kb += 2) {
+    int conv_it = total_it;   // k-blocks to convert: those of the live tiles
+    if (use_live) {
+      int live_tiles = 0;
+      for (int ti = 0; ti < my_tiles; ++ti) live_tiles += tile_live(blockIdx.x + ti * gridDim.x) ? 1 : 0;
+      conv_it = live_tiles * nkb;
+    }
+    for (int it = g; it < conv_it && ok; it += 2, c_kb += 2) {
       // Column coefficients of a relaxation applied on the fly (coef_l != nullptr): x_lw is read as
       // coef_l[row block, k] * x_lw and x_uw as coef_u[row block, k] * x_uw, the row block being the
       // (b, l) row of the bound (tile row / coef_di; a tile never straddles two row blocks).  The 16
@@ -577,6 +647,7 @@ bool make_out_map(CUtensorMap* map, const float* ptr, uint64_t M, uint64_t N, in
 }
 
 thread_local int* t_status_sink = nullptr;
+thread_local LiveRows t_live_rows = {0, 0, 0, {0, 0, 0, 0}, nullptr, 0};
 uint32_t g_wait_tries = kMaxTries;
 int g_skip_it = -1;
 
@@ -585,6 +656,10 @@ int g_skip_it = -1;
 // The encoder driver registers its status word here around a pass: a tensor-core kernel whose bounded wait
 // expires sets bit 2 of it (besides the flag behind fb_tc_error_flag).
 void tc_set_status_sink(int* status) { t_status_sink = status; }
+void tc_set_live_rows(const LiveRows* lr) {
+  if (lr != nullptr) t_live_rows = *lr;
+  else t_live_rows.L = 0;
+}
 int* tc_status_sink() { return t_status_sink; }
 
 // Head-split store is possible when a 128-row tile stays inside one group and a 32-column box inside one head.
@@ -648,19 +723,25 @@ int launch_split_sign_tc(const float* a_lo, const float* a_up, const float* W, c
   int* status = t_status_sink;
   const uint32_t tries = g_wait_tries;
   const int skip = g_skip_it;
+  // zero row blocks: only for the zero-radius products of the operand the hint was set for (weight rows, no bias)
+  LiveRows no_live = {0, 0, 0, {0, 0, 0, 0}, nullptr, 0};
+  LiveRows live = no_live;
+  if (t_live_rows.L > 0 && t_live_rows.M == M && bias == nullptr && t_live_rows.Di > 0 && t_live_rows.Di % BM == 0 &&
+      t_live_rows.words >= 1 && t_live_rows.words <= 4 && M % ((int64_t)t_live_rows.Di * t_live_rows.L) == 0)
+    live = t_live_rows;
 #define FB_TC_ARGS tm_lo, tm_up, tm_w, tm_out_lo, tm_out_up, tm_res_lo, tm_res_up, bias, M, N, K, gn, total_tiles, split_rows, split_d
   if (coef_l != nullptr && res_lo != nullptr)
-    split_sign_gemm_tc<true, false, true, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, coef_l, coef_u, coef_di, nullptr, nullptr, 0, status, tries, skip);
+    split_sign_gemm_tc<true, false, true, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, coef_l, coef_u, coef_di, nullptr, nullptr, 0, status, tries, skip, no_live, 0);
   else if (coef_l != nullptr)
-    split_sign_gemm_tc<true, false, false, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, coef_l, coef_u, coef_di, nullptr, nullptr, 0, status, tries, skip);
+    split_sign_gemm_tc<true, false, false, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, coef_l, coef_u, coef_di, nullptr, nullptr, 0, status, tries, skip, no_live, 0);
   else if (norm_lo != nullptr && a_lo == a_up)   // one tensor as both lines: zero radius
-    split_sign_gemm_tc<false, true, false, true><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, norm_lo, norm_up, norm_p, status, tries, skip);
+    split_sign_gemm_tc<false, true, false, true><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, norm_lo, norm_up, norm_p, status, tries, skip, live, c_lo == c_up ? 1 : 0);
   else if (norm_lo != nullptr)
-    split_sign_gemm_tc<false, true, false, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, norm_lo, norm_up, norm_p, status, tries, skip);
+    split_sign_gemm_tc<false, true, false, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, norm_lo, norm_up, norm_p, status, tries, skip, no_live, 0);
   else if (res_lo != nullptr)
-    split_sign_gemm_tc<false, false, true, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, nullptr, nullptr, 0, status, tries, skip);
+    split_sign_gemm_tc<false, false, true, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, nullptr, nullptr, 0, status, tries, skip, no_live, 0);
   else
-    split_sign_gemm_tc<false, false, false, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, nullptr, nullptr, 0, status, tries, skip);
+    split_sign_gemm_tc<false, false, false, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, nullptr, nullptr, 0, status, tries, skip, no_live, 0);
 #undef FB_TC_ARGS
   FB_LAUNCH_OK();
   return FB_OK;

@@ -289,8 +289,7 @@ extern "C" int fb_softmax_ranges_f32(const float* lw, const float* uw, const flo
   ProfileScope prof(PK_RELAX, 30.0 * mw, 4.0 * (4 * mw + 4 * mb), stream);
 #define FB_SOFTMAX_LAUNCH(P)                                                                                          \
   do {                                                                                                                \
-    if (smem > 48 * 1024)                                                                                             \
-      FB_CUDA_OK(cudaFuncSetAttribute(softmax_bounds_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    if (int rc_ = ensure_dynamic_smem(softmax_bounds_kernel<P>, smem)) return rc_;                                     \
     softmax_bounds_kernel<P><<<(unsigned)rows, kThreads, smem, (cudaStream_t)stream>>>(                                \
         lw, uw, lb, ub, out_lw, out_uw, out_lb, out_ub, out_l, out_u, Di, Do, words, eps, violation);                  \
   } while (0)

@@ -245,3 +245,33 @@ def test_batched_two_word_search_reproduces_the_reference_radii():
             diff += np.float32(got[0][q]) != np.float32(e)
             assert abs(got[0][q] - float(e)) <= 2.001 * step_floor * max(float(e), warmed), (s, q, got[0][q], float(e))
         assert diff <= 1, "%d of %d radii differ from the reference" % (diff, len(pairs))
+
+
+@pytest.mark.parametrize("words,positions,p", [(1, [1], float("inf")), (2, [3, 30], 2.0)])
+def test_first_layer_projections_skip_zero_row_blocks_bit_for_bit(words, positions, p):
+    """In the first layer only the weight rows of the perturbed positions are non-zero; the tensor-core GEMM is told so
+    and stores zeros for the other row blocks without reading or multiplying them.  The pass must give the same bits
+    as with the shortcut switched off (FB_ENCODER_NO_ZERO_SKIP), for one set of positions and for per-sentence ones."""
+    import os
+    import faith_b200
+    model = O.make_encoder(4)
+    emb = torch.randn(6, 32, 128, generator=torch.Generator().manual_seed(6)).to(DEV)
+    ver = faith_b200.EncoderVerifier(model, DEV)
+    inst = torch.tensor([[(q + 5 * s) % 32 for q in positions] for s in range(6)], dtype=torch.int32, device=DEV)
+    eps_i = torch.full((6,), 1e-3, device=DEV)
+
+    def run():
+        a = ver.forward(emb, positions, p, 1e-3)
+        b = ver.forward_instances(emb, inst, p, eps_i)
+        return [t.clone() for t in (a[0], a[1], b[0], b[1])]
+
+    assert "FB_ENCODER_NO_ZERO_SKIP" not in os.environ
+    fast = run()
+    os.environ["FB_ENCODER_NO_ZERO_SKIP"] = "1"
+    try:
+        plain = run()
+    finally:
+        del os.environ["FB_ENCODER_NO_ZERO_SKIP"]
+    for x, y in zip(fast, plain):
+        assert torch.equal(x, y)
+    assert bool(torch.isfinite(fast[0]).all()) and bool((fast[0] <= fast[1]).all())
