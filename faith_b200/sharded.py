@@ -285,6 +285,7 @@ class CnnVerifier:
         if need < 0:
             raise _lib.FaithError("fb_cnn_workspace_bytes: network not supported by the driver")
         if self._arena is None or self._arena.numel() < need:
+            self._graphs.clear()     # captured passes point into the arena that is about to be replaced
             self._arena = torch.empty(need, dtype=torch.uint8, device=self.device)
         n_out = self._out_features(C, H, W)
         l = torch.empty(n_out, device=self.device)
