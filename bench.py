@@ -127,6 +127,39 @@ def cpu_reference_pass(model, emb, n_sentences, threads):
     return time.perf_counter() - t0
 
 
+def cpu_model():
+    try:
+        with open("/proc/cpuinfo") as f:
+            for ln in f:
+                if ln.startswith("model name"):
+                    return ln.split(":", 1)[1].strip()
+    except OSError:
+        pass
+    return "unknown"
+
+
+def reference_on_gpu(model, emb, dev):
+    """The reference's own PyTorch Bounds and VerifierForward, unchanged, with its tensors on the GPU (what the
+    reference's figures call "pytorch"): one sentence per call, 4 sentences after one warm-up.  A second baseline next
+    to the CPU one; reported, not a target."""
+    if reference_kind() != "reference":
+        return {"unavailable": "reference modules are not staged under oracle/_ref"}
+    try:
+        import reference_loader
+        ver = reference_loader.build_reference_verifier(model, INF, device=str(dev))
+        e = emb[:5].to(dev)
+        reference_loader.reference_encoder_pass(ver, e[0:1], CFG["index"], CFG["eps"])
+        torch.cuda.synchronize(dev)
+        t0 = time.perf_counter()
+        for s in range(1, 5):
+            reference_loader.reference_encoder_pass(ver, e[s:s + 1], CFG["index"], CFG["eps"])
+        torch.cuda.synchronize(dev)
+        return {"value": 4 / (time.perf_counter() - t0), "unit": UNIT,
+                "sample": "4 of the 256 sentences, one sentence per call, the reference's torch operators on this GPU"}
+    except Exception as ex:   # the reference creates some tensors on the CPU; whatever stops it is reported, not hidden
+        return {"unavailable": "%s: %s" % (type(ex).__name__, str(ex)[:200])}
+
+
 def baseline_sample_text(n):
     if reference_kind() == "reference":
         return ("%d of the 256 sentences, one sentence per call through the reference's unchanged VerifierForward "
@@ -155,7 +188,8 @@ def run_reference(args):
         "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD, "sample": sample_txt},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": reference_kind(), "sample": sample_txt},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "cpu_model": cpu_model(), "kind": reference_kind(),
+                         "sample": sample_txt},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -272,6 +306,25 @@ def roof_entry(name, ms, flops, nbytes, pipe_tflops, pipe_name, hbm_gbs, extra=N
 
 
 # ------------------------------------------------------------------------------------- per-configuration lines
+def graph_replay_ms(ctx, fn, replays=200):
+    """Device time per replay of a CUDA graph that captured one call of `fn` (its launches and output allocations)."""
+    fn()
+    torch.cuda.synchronize(ctx.dev)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        keep = fn()   # noqa: F841  (outputs live in the graph's pool)
+    for _ in range(5):
+        g.replay()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(ctx.dev)
+    a.record()
+    for _ in range(replays):
+        g.replay()
+    b.record()
+    torch.cuda.synchronize(ctx.dev)
+    return a.elapsed_time(b) / replays
+
+
 def per_config_lines(ctx, lib, pipes, pk):
     """Benchmark configurations 1-3 and 5 on this GPU: device time of one launch sequence on its own (latency:
     the microsecond-sized problems are below a kernel launch) and the steady state over many independent
@@ -310,6 +363,10 @@ def per_config_lines(ctx, lib, pipes, pk):
     fl, by = c1_work(1)
     out.append(roof_entry("C1 linear 64->128 + relu, one instance [1,16,64,*]", best, fl, by, ffma_alg, "ffma", hbm,
                           {"median_ms": med, "mode": "single launch sequence (2 GEMM launches + 1 relaxation): launch latency"}))
+    graph_ms = graph_replay_ms(ctx, lambda: c1(x1))
+    out.append(roof_entry("C1 one instance, replayed from a CUDA graph", graph_ms, fl, by, ffma_alg, "ffma", hbm,
+                          {"mode": "the same 3 launches captured once and replayed back to back: device-side latency without "
+                                   "the host's launch cost"}))
     nb = 2048
     xb = bounds(nb, 16, 64, 64, 2)
     per = ctx.loop_ms(lambda: c1(xb), 10)
@@ -329,6 +386,9 @@ def per_config_lines(ctx, lib, pipes, pk):
     fl, by = c2_work(4)
     out.append(roof_entry("C2 dot product Q.K^T, one instance [4,32,128,32]", best, fl, by, tf32_alg, "tf32x3", hbm,
                           {"median_ms": med, "mode": "single call (2 concretisations + bias + weight kernel): launch latency"}))
+    graph_ms = graph_replay_ms(ctx, lambda: c2(q, k))
+    out.append(roof_entry("C2 one instance, replayed from a CUDA graph", graph_ms, fl, by, tf32_alg, "tf32x3", hbm,
+                          {"mode": "the same launches captured once and replayed back to back"}))
     nb = 1024
     qb, kb = bounds(4 * nb, 32, 128, 32, 5), bounds(4 * nb, 32, 128, 32, 6)
     per = ctx.loop_ms(lambda: c2(qb, kb), 10)
@@ -643,8 +703,9 @@ def main():
         cpu_reference_pass(model, emb_host, 1, threads)
         n = 8
         secs = cpu_reference_pass(model, emb_host, n, threads)
-        line["cpu_baseline"] = {"value": n / secs, "unit": UNIT, "cores": threads, "kind": reference_kind(),
-                                "sample": baseline_sample_text(n)}
+        line["cpu_baseline"] = {"value": n / secs, "unit": UNIT, "cores": threads, "cpu_model": cpu_model(),
+                                "kind": reference_kind(), "sample": baseline_sample_text(n)}
+        line["reference_torch_gpu"] = reference_on_gpu(model, emb_host, dev)
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
