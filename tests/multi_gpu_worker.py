@@ -1,6 +1,6 @@
 """One rank of the multi-GPU tests (started by tests/test_gpu_multi.py, one process per GPU).
 
-argv: rank world port case.  The process group (gloo) only carries the NCCL id and the verdicts; all data-path
+argv: rank world port case.  The process group (gloo) only carries the NCCL id and the pass or fail of each rank; all data-path
 traffic goes through the library's communicator.  Prints "RANK r OK" when its checks hold."""
 import os
 import sys
