@@ -93,3 +93,63 @@ def test_ctypes_prototypes_match_the_header_parameter_by_parameter():
     protos = declared_prototypes()
     for name, argtypes in _lib.SIGNATURES.items():
         assert [kind(t) for t in argtypes] == protos[name], name
+
+
+def test_cnn_driver_validates_the_network_without_gpu():
+    """fb_cnn_workspace_bytes walks the layer records on the host: a network that does not start with a convolution, a
+    convolution behind a linear layer or a feature map that shrinks to nothing is refused (-1); a well-formed one gets
+    its arena size, which grows with the rows of the shard."""
+    import ctypes
+    from faith_b200 import _lib
+    lib = _lib.load()
+    dummy = ctypes.c_void_p(256)     # never dereferenced on the host
+
+    def net(layers, cin=3, h=8, w=8):
+        recs = (_lib.CnnLayer * len(layers))()
+        for r, ly in zip(recs, layers):
+            r.kind, r.weight, r.bias = ly[0], dummy, None
+            if ly[0] == _lib.FB_CNN_CONV:
+                r.cout, r.kh, r.kw, r.stride, r.pad = ly[1:]
+            elif ly[0] == _lib.FB_CNN_LINEAR:
+                r.n_out = ly[1]
+        return _lib.Cnn(len(layers), recs, cin, h, w), recs
+
+    conv = (_lib.FB_CNN_CONV, 4, 3, 3, 1, 1)
+    good, keep = net([conv, (_lib.FB_CNN_RELU,), (_lib.FB_CNN_CONV, 6, 3, 3, 2, 1), (_lib.FB_CNN_RELU,), (_lib.FB_CNN_LINEAR, 5)])
+    small = lib.fb_cnn_workspace_bytes(ctypes.byref(good), 10)
+    large = lib.fb_cnn_workspace_bytes(ctypes.byref(good), 192)
+    assert 0 < small < large
+    for bad_layers in ([(_lib.FB_CNN_RELU,), conv], [(_lib.FB_CNN_LINEAR, 5)], [conv, (_lib.FB_CNN_LINEAR, 5), conv],
+                       [(_lib.FB_CNN_CONV, 4, 9, 9, 1, 0), (_lib.FB_CNN_CONV, 4, 3, 3, 1, 0)], [(7,)]):
+        bad, keep2 = net(bad_layers)
+        assert lib.fb_cnn_workspace_bytes(ctypes.byref(bad), 10) == -1, bad_layers
+    assert lib.fb_cnn_workspace_bytes(None, 10) == -1
+    # the forward call refuses bad arguments before touching the device
+    assert lib.fb_cnn_forward_f32(None, None, 3, 0.1, 0, 1, None, 0, 1, None, None, None, None, 0, None) == 1
+    out = ctypes.c_void_p(512)
+    assert lib.fb_cnn_forward_f32(ctypes.byref(good), dummy, 3, 0.1, 0, 10 ** 6, None, 0, 1, out, out, None, dummy, 1 << 40,
+                                  None) == 1      # more rows than dim_in
+    assert lib.fb_cnn_forward_f32(ctypes.byref(good), dummy, 3, 0.1, 0, 8, None, 0, 1, out, out, None, dummy, 16, None) == 5  # arena too small
+
+
+def test_compact_window_extent_without_gpu():
+    """fb_cw_extent is host arithmetic: the largest window a pixel reaches through a chain of convolutions."""
+    import ctypes
+    from faith_b200 import _lib
+    lib = _lib.load()
+
+    def extent(h, w, chain):
+        flat = [v for c in chain for v in c]
+        arr = (ctypes.c_int * max(1, len(flat)))(*flat)
+        wh, ww = ctypes.c_int(0), ctypes.c_int(0)
+        rc = lib.fb_cw_extent(h, w, arr, len(chain), ctypes.byref(wh), ctypes.byref(ww))
+        return rc, wh.value, ww.value
+
+    assert extent(32, 32, [(3, 3, 1, 1)]) == (0, 3, 3)
+    assert extent(32, 32, [(3, 3, 1, 1), (3, 3, 2, 1)]) == (0, 3, 3)          # the benchmark CNN
+    assert extent(32, 32, [(3, 3, 1, 1), (3, 3, 1, 1)]) == (0, 5, 5)
+    assert extent(16, 8, [(5, 3, 1, 2)]) == (0, 5, 3)
+    assert extent(9, 9, [(2, 2, 3, 0)]) == (0, 1, 1)
+    assert extent(8, 8, [(3, 3, 0, 1)])[0] == 1                                # stride 0
+    assert extent(4, 4, [(9, 9, 1, 0)])[0] == 2                                # feature map shrinks to nothing
+    assert extent(8, 8, [(3, 3, 1, 1)] * 9)[0] == 2                            # more than eight convolutions
