@@ -71,9 +71,11 @@ constexpr uint32_t kWTileBytes = BN * BK * 4;            // one 64 x 32 fp32 til
 constexpr uint32_t kRawStageBytes = 2 * kTileBytes + kWTileBytes;  // x_lw, x_uw, W
 constexpr uint32_t kPlaneStageBytes = 4 * kWTileBytes;   // W_hi, W_lo, |W|_hi, |W|_lo
 constexpr int kRawStages = 2;                            // TMA runs two k-blocks ahead
+constexpr int kLiveWords = 128;                          // bitmap of the CTA's tiles that are not known to be zero (4096 tiles)
 constexpr uint32_t kOutBoxBytes = BM * 32 * 4;            // one 128-row x 32-column fp32 box of an output tile = 16 KB
 constexpr uint32_t kOutStageBytes = 4 * kOutBoxBytes;    // lower and upper output tile, two boxes each
-constexpr uint32_t kSmemBytes = kRawStages * kRawStageBytes + 2 * kPlaneStageBytes + kOutStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+constexpr uint32_t kSmemBytes = kRawStages * kRawStageBytes + 2 * kPlaneStageBytes + kOutStageBytes + 1024 /*align*/ + 256 /*barriers*/ +
+                                kLiveWords * 4 /*live-tile bitmap*/;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kAccC = 0, kAccR = 64, kCorC = 128, kCorR = 192, kABase = 256;  // TMEM column map
 
@@ -162,10 +164,9 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
   // Row blocks known to be zero (live_rows.L > 0; zero-radius instantiation only): a tile of such a block is not
   // loaded, converted or multiplied; the issuers only signal "ready" and the epilogue stores zeros (and zero norms).
   const bool use_live = kPoint && kNorm && !kCoef && !kResid && live_rows.L > 0;
-  auto tile_live = [&](int tile) -> bool {
-    if (!use_live) return true;
-    const int bl = (int)(((int64_t)(tile / n_tiles_n) * BM) / live_rows.Di);
-    const int l = bl % live_rows.L, b = bl / live_rows.L;
+  auto tile_live_slow = [&](int tile) -> bool {
+    const unsigned bl = ((unsigned)(tile / n_tiles_n) * (unsigned)BM) / (unsigned)live_rows.Di;   // M < 2^31
+    const int l = (int)(bl % (unsigned)live_rows.L), b = (int)(bl / (unsigned)live_rows.L);
     bool live = false;
 #pragma unroll
     for (int w = 0; w < 4; ++w)
@@ -193,6 +194,27 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
   // 64-bit division per k-block cost more instructions than the conversion itself)
   const int my_tiles = (int)((total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x);
   const int total_it = my_tiles * nkb;   // k-blocks this CTA walks, across all its tiles
+
+  // Liveness of this CTA's tiles, worked out once by all threads into a bitmap (every role of every tile asks; the
+  // divisions and the position loads of the direct form, 28 warps x 100+ tiles, cost more than the zero tiles themselves).
+  uint32_t* live_bits = reinterpret_cast<uint32_t*>(base_ptr + SharedLayout::bars() + 256);
+  const bool live_map = use_live && my_tiles <= 32 * kLiveWords;
+  if (live_map) {
+    for (int w = threadIdx.x; w < (my_tiles + 31) / 32; w += blockDim.x) {
+      uint32_t bits = 0;
+      for (int k = 0; k < 32; ++k) {
+        const int ti = w * 32 + k;
+        if (ti < my_tiles && tile_live_slow((int)blockIdx.x + ti * (int)gridDim.x)) bits |= 1u << k;
+      }
+      live_bits[w] = bits;
+    }
+  }
+  // ti: index among this CTA's tiles (tile = blockIdx.x + ti * gridDim.x)
+  auto tile_live = [&](int ti) -> bool {
+    if (!use_live) return true;
+    if (live_map) return (live_bits[ti >> 5] >> (ti & 31)) & 1u;
+    return tile_live_slow((int)blockIdx.x + ti * (int)gridDim.x);
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kRawStages; ++s) {
@@ -228,7 +250,7 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
     bool ok = true;
     for (int ti = 0; ti < my_tiles && ok; ++ti) {
       const int tile = blockIdx.x + ti * gridDim.x;
-      if (!tile_live(tile)) continue;
+      if (!tile_live(ti)) continue;
       const int m0 = (int)(tile / n_tiles_n) * BM, n0 = (int)(tile % n_tiles_n) * BN;
       for (int kb = 0; kb < nkb; ++kb, ++it) {
         const int rs = (int)(it % kRawStages);
@@ -269,7 +291,7 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
         }
     int lt = 0;   // tiles multiplied so far: the accumulator hand-shake with the epilogue counts these only
     for (int ti = 0; ti < my_tiles && ok; ++ti) {
-      if (!tile_live(blockIdx.x + ti * gridDim.x)) continue;   // a zero row block: nothing to multiply, nothing to signal
+      if (!tile_live(ti)) continue;   // a zero row block: nothing to multiply, nothing to signal
       for (int kb = 0; kb < nkb; ++kb, ++it) {
         const int s = (int)(it & 1);
         ok = mbar_wait_warp(bar_ops_ready + 8 * s, (uint32_t)((it >> 1) & 1), wc);
@@ -321,7 +343,7 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
     int le = 0;                  // tiles read out of tensor memory so far (the issuers count the same tiles)
     for (int e = 0; e < my_tiles && ok; ++e) {
       const int etile = blockIdx.x + e * gridDim.x;
-      const bool elive = tile_live(etile);
+      const bool elive = tile_live(e);
       const int my = (etile / n_tiles_n) * BM, nx = (etile % n_tiles_n) * BN;
       if (!elive) {
         // A zero row block (kPoint and kNorm only): the result is +0 everywhere and so are its column norms.  The
@@ -502,7 +524,7 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
     int conv_it = total_it;   // k-blocks to convert: those of the live tiles
     if (use_live) {
       int live_tiles = 0;
-      for (int ti = 0; ti < my_tiles; ++ti) live_tiles += tile_live(blockIdx.x + ti * gridDim.x) ? 1 : 0;
+      for (int ti = 0; ti < my_tiles; ++ti) live_tiles += tile_live(ti) ? 1 : 0;
       conv_it = live_tiles * nkb;
     }
     for (int it = g; it < conv_it && ok; it += 2, c_kb += 2) {
