@@ -306,6 +306,30 @@ def roof_entry(name, ms, flops, nbytes, pipe_tflops, pipe_name, hbm_gbs, extra=N
 
 
 # ------------------------------------------------------------------------------------- per-configuration lines
+def epsilon_search_line(ver, emb_dev):
+    """The reference's search for the largest certified radius (Verifier.py:106-147: per word a probe at max_eps and
+    10 bisection steps, each a full bound pass) on 8 of the benchmark's sentences, every perturbable position: the
+    probes of all (sentence, position) pairs of a round go through one call of the driver."""
+    import faith_b200
+    n_sent, iters, max_eps = 8, 10, 0.02
+    emb = emb_dev[:n_sent].contiguous()
+    labels = torch.zeros(n_sent, dtype=torch.int64, device=emb.device)
+    search = faith_b200.EpsilonSearch(ver, INF, max_eps, iters, max_instances=256)
+    search.run(emb[:1], labels[:1])        # warm-up (arena of the instance driver)
+    search.passes = search.instances = 0
+    torch.cuda.synchronize(emb.device)
+    t0 = time.perf_counter()
+    radii = search.run(emb, labels)
+    torch.cuda.synchronize(emb.device)
+    secs = time.perf_counter() - t0
+    found = [v for d in radii for v in d.values()]
+    return {"sentences": n_sent, "positions_per_sentence": len(radii[0]), "bisection_steps": iters, "max_eps": max_eps,
+            "seconds": secs, "sentences_per_s": n_sent / secs, "bound_passes": search.instances,
+            "bound_passes_per_s": search.instances / secs, "driver_calls": search.passes,
+            "mean_certified_radius": sum(found) / len(found),
+            "note": "the reference makes one verify_safety call per bound pass (cpu_baseline.value of them per second)"}
+
+
 def graph_replay_ms(ctx, fn, replays=200):
     """Device time per replay of a CUDA graph that captured one call of `fn` (its launches and output allocations)."""
     fn()
@@ -620,6 +644,7 @@ def main():
         extras["cnn"] = cnn_sharded(ctx, lib, max(args.steps, 10))
         if rank == 0:
             extras["per_config"] = per_config_lines(ctx, lib, pipes, pk)
+            extras["epsilon_search"] = epsilon_search_line(ver, emb_dev)
         ctx.barrier()
 
     if rank != 0:
