@@ -335,7 +335,7 @@ def graph_replay_ms(ctx, fn, replays=200):
     fn()
     torch.cuda.synchronize(ctx.dev)
     g = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(g):
+    with torch.cuda.graph(g, capture_error_mode="thread_local"):   # other threads (a collective's watchdog) stay free to call CUDA
         keep = fn()   # noqa: F841  (outputs live in the graph's pool)
     for _ in range(5):
         g.replay()

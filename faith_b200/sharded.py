@@ -315,7 +315,7 @@ class CnnVerifier:
                 self._run_driver(static_img, p, eps, start, size, world)      # sizes the arena, warms every launcher
                 torch.cuda.synchronize(self.device)
                 g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g):
+                with torch.cuda.graph(g, capture_error_mode="thread_local"):   # other threads (a collective's watchdog) stay free to call CUDA
                     l, u = self._run_driver(static_img, p, eps, start, size, world)
             ent = self._graphs[key] = (g, static_img, l, u)
         g, static_img, l, u = ent
