@@ -283,6 +283,62 @@ dot_weight_native(const float* __restrict__ x_lw, const float* __restrict__ x_uw
 }
 
 #include "dot_product_pipelined.cuh"
+// Few query rows (Lx <= kFewRows; a last layer run for the first token only has Lx = 1): the tiled kernels would spend 31
+// of the 32 rows of every x tile on padding.  One thread per output element (b, i, m, j), lanes along j, the products
+// accumulated over k in the order of dot_weight_native; y is read once, in its native layout [B, Ly, Di, K] (a thread
+// walks K consecutive values) or as [B, K, Di, Ly] (y_kmajor: the value tensor as the projection writes it; the lanes
+// read consecutive words).
+constexpr int kFewRows = 4;
+__global__ void __launch_bounds__(256)
+dot_weight_rows_kernel(const float* __restrict__ x_lw, const float* __restrict__ x_uw, const float* __restrict__ y_lw,
+                       const float* __restrict__ y_uw, const float* __restrict__ x_l, const float* __restrict__ y_l,
+                       const float* __restrict__ y_u, float* __restrict__ z_lw, float* __restrict__ z_uw, int64_t total,
+                       int Lx, int Ly, int Di, int K, float out_scale, int merge_heads, int y_kmajor) {
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+    const int j = (int)(t % Ly), m = (int)((t / Ly) % Di), i = (int)((t / ((int64_t)Ly * Di)) % Lx);
+    const int64_t b = t / ((int64_t)Ly * Di * Lx);
+    const float* xl = x_lw + ((b * Lx + i) * (int64_t)Di + m) * K;
+    const float* xu = x_uw + ((b * Lx + i) * (int64_t)Di + m) * K;
+    const float* lx = x_l + (b * Lx + i) * (int64_t)K;
+    const float* ly = y_l + (b * Ly + j) * (int64_t)K;
+    const float* uy = y_u + (b * Ly + j) * (int64_t)K;
+    const int64_t y0 = y_kmajor ? (b * K * (int64_t)Di + m) * Ly + j : ((b * Ly + j) * (int64_t)Di + m) * K;
+    const int64_t ys = y_kmajor ? (int64_t)Di * Ly : 1;
+    float l = 0.f, u = 0.f;
+#pragma unroll 4
+    for (int k = 0; k < K; ++k) {
+      const float yl = __ldg(y_lw + y0 + k * ys), yu = __ldg(y_uw + y0 + k * ys);
+      const float a = __ldg(xl + k), c = __ldg(xu + k);
+      const float vly = __ldg(ly + k), vuy = __ldg(uy + k), vlx = __ldg(lx + k);
+      const float lyp = fmaxf(vly, 0.f), lyn = fminf(vly, 0.f), uyp = fmaxf(vuy, 0.f), uyn = fminf(vuy, 0.f);
+      const float lxp = fmaxf(vlx, 0.f), lxn = fminf(vlx, 0.f);
+      l = fmaf(a, lyp, l); l = fmaf(c, lyn, l);
+      l = fmaf(yl, lxp, l); l = fmaf(yu, lxn, l);
+      u = fmaf(c, uyp, u); u = fmaf(a, uyn, u);
+      u = fmaf(yu, lxp, u); u = fmaf(yl, lxn, u);
+    }
+    int64_t o = ((b * Lx + i) * (int64_t)Di + m) * Ly + j;
+    if (merge_heads > 1) {
+      const int64_t sidx = b / merge_heads;
+      const int h = (int)(b % merge_heads);
+      o = ((sidx * Lx + i) * (int64_t)Di + m) * ((int64_t)merge_heads * Ly) + (int64_t)h * Ly + j;
+    }
+    z_lw[o] = fmul(l, out_scale);
+    z_uw[o] = fmul(u, out_scale);
+  }
+}
+
+int launch_dot_weight_rows(const float* x_lw, const float* x_uw, const float* y_lw, const float* y_uw, const float* x_l,
+                           const float* y_l, const float* y_u, float* z_lw, float* z_uw, int B, int Lx, int Ly, int Di, int K,
+                           float out_scale, int merge_heads, int y_kmajor, cudaStream_t st) {
+  const int64_t total = (int64_t)B * Lx * Di * Ly;
+  const int64_t want = ceil_div(total, 256), cap = (int64_t)device_info().sms * 64;
+  dot_weight_rows_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, st>>>(x_lw, x_uw, y_lw, y_uw, x_l, y_l, y_u, z_lw, z_uw, total,
+                                                                             Lx, Ly, Di, K, out_scale, merge_heads, y_kmajor);
+  FB_LAUNCH_OK();
+  return FB_OK;
+}
+
 
 // --------------------------------------------- weight part, transposed layout
 // x [B, Lx, K, Di], y [B, Ly, K, Di] -> z [B, Lx, Ly, Di]   (Di contiguous).
@@ -441,6 +497,8 @@ static int dot_heads_impl(const float* x_lw, const float* x_uw, const float* x_l
     // attention shapes: tensor-core kernel
     return launch_dot_weight_tc(x_lw, x_uw, y_lw, y_uw, x_l, y_l, y_u, z_lw, z_uw, B, Lx, Ly, Di, out_scale, merge_heads, 0, st);
   }
+  if (layout == FB_NATIVE && Lx <= kFewRows)
+    return launch_dot_weight_rows(x_lw, x_uw, y_lw, y_uw, x_l, y_l, y_u, z_lw, z_uw, B, Lx, Ly, Di, K, out_scale, merge_heads, 0, st);
   if (layout == FB_NATIVE) {
     const int n_it = (int)ceil_div(Lx, TI), n_jt = (int)ceil_div(Ly, TJ), n_mt = (int)ceil_div(Di, TM);
     const int64_t blocks = (int64_t)B * n_it * n_jt * n_mt;
@@ -547,9 +605,11 @@ extern "C" int fb_context_given_f32(const float* x_lw, const float* x_uw, const 
   if (!(out_scale > 0.f)) return FB_ERR_ARG;
   if (Di % words != 0 || Di == 1) return FB_ERR_SHAPE;
   if (B == 0) return FB_OK;
-  if (dot_force_cuda_cores() ||
-      !dot_tc_supported(x_lw, x_uw, v_lw, v_uw, x_l, y_l, y_u, z_lw, z_uw, B, Lx, Ly, Di, K, merge_heads))
-    return FB_ERR_SHAPE;
+  const bool tc = !dot_force_cuda_cores() &&
+                  dot_tc_supported(x_lw, x_uw, v_lw, v_uw, x_l, y_l, y_u, z_lw, z_uw, B, Lx, Ly, Di, K, merge_heads);
+  // (a few query rows go through the thread-per-output kernel, which reads the values in this layout as well)
+  const bool rows_kernel = !tc && Lx <= kFewRows && (int64_t)K * Ly <= 4096;
+  if (!tc && !rows_kernel) return FB_ERR_SHAPE;
   cudaStream_t st = (cudaStream_t)stream;
   const double d1 = (double)Di + 1;
   ProfileScope prof(PK_DOT, 16.0 * B * Lx * Ly * d1 * K,
@@ -568,6 +628,8 @@ extern "C" int fb_context_given_f32(const float* x_lw, const float* x_uw, const 
                                                                             Lx, Ly, K, n_it, n_jt, out_scale, merge_heads, 1);
     FB_LAUNCH_OK();
   }
+  if (rows_kernel)
+    return launch_dot_weight_rows(x_lw, x_uw, v_lw, v_uw, x_l, y_l, y_u, z_lw, z_uw, B, Lx, Ly, Di, K, out_scale, merge_heads, 1, st);
   return launch_dot_weight_tc(x_lw, x_uw, v_lw, v_uw, x_l, y_l, y_u, z_lw, z_uw, B, Lx, Ly, Di, out_scale, merge_heads, 1, st);
 }
 

@@ -270,8 +270,95 @@ static int encoder_forward_impl(const fb_encoder* enc, const float* emb, int S, 
     }
   }
   const float inv_sqrt_d = (float)(1.0 / sqrt((double)d));
+  BoundSet first_token = {nullptr, nullptr, nullptr, nullptr};   // [S, 1, Di, D] output of a last layer run for token 0 only
   for (int li = 0; li < enc->layers; ++li) {
     const fb_encoder_layer& ly = enc->layer[li];
+    if (enc->first_token_only != 0 && li == enc->layers - 1 && L > 1 && d % 4 == 0) {
+      // ---- last layer, first token only (the pooler reads nothing else of its output, VerifierForward.py:269-287).
+      // Keys and values at every position; query, attention row, attention output, feed-forward block at position 0.
+      // Plain operator calls throughout: the tensors on the query side are 1/L of the usual size.
+      const BoundSet X = slot[A];
+      char* bump = reinterpret_cast<char*>(slot[B].lw);
+      char* const bump_end = bump + plan.slot_bytes;
+      bool fits = true;
+      auto take = [&](int64_t r, int64_t feat) -> BoundSet {
+        BoundSet b;
+        const int64_t nw = align_up(r * Di * feat * 4, 256), nb = align_up(r * feat * 4, 256);
+        b.lw = reinterpret_cast<float*>(bump); bump += nw;
+        b.uw = reinterpret_cast<float*>(bump); bump += nw;
+        b.lb = reinterpret_cast<float*>(bump); bump += nb;
+        b.ub = reinterpret_cast<float*>(bump); bump += nb;
+        if (bump > bump_end) fits = false;
+        return b;
+      };
+      const int64_t SH = (int64_t)S * H;
+      const BoundSet Xq = take(S, D), Qh = take(S, D), Sc = take(SH, L), Pr = take(SH, L), E1 = take(SH, L), E2 = take(SH, L),
+                     Vt = take(rows, D), Cx = take(S, D), Ao = take(S, D), H3 = take(S, D), Hd = take(S, F), Hr = take(S, F),
+                     F2 = take(S, D), Out = take(S, D);
+      if (fits) {
+        const BoundSet Kh = slot[Dd], Vd = slot[C];
+        // the first token's rows of the layer input
+        FB_CUDA_OK(cudaMemcpy2DAsync(Xq.lw, (size_t)Di * D * 4, X.lw, (size_t)L * Di * D * 4, (size_t)Di * D * 4, S,
+                                     cudaMemcpyDeviceToDevice, st));
+        FB_CUDA_OK(cudaMemcpy2DAsync(Xq.uw, (size_t)Di * D * 4, X.uw, (size_t)L * Di * D * 4, (size_t)Di * D * 4, S,
+                                     cudaMemcpyDeviceToDevice, st));
+        FB_CUDA_OK(cudaMemcpy2DAsync(Xq.lb, (size_t)D * 4, X.lb, (size_t)L * D * 4, (size_t)D * 4, S, cudaMemcpyDeviceToDevice, st));
+        FB_CUDA_OK(cudaMemcpy2DAsync(Xq.ub, (size_t)D * 4, X.ub, (size_t)L * D * 4, (size_t)D * 4, S, cudaMemcpyDeviceToDevice, st));
+        // query of token 0 [S*H, 1, Di, d], keys of every token [S*H, L, Di, d] (with their ranges from the GEMM's
+        // epilogue where the shapes allow it), scores [S*H, 1, Di, L]
+        FB_TRY(fb_matmul_heads_f32(Xq.lw, Xq.uw, Xq.lb, Xq.ub, ly.q_w, ly.q_b, Qh.lw, Qh.uw, Qh.lb, Qh.ub, S, Di, D, D, 1, H, stream));
+        int kgiven = 0;
+        const int krc = fb_matmul_heads_ranges_f32(X.lw, X.uw, X.lb, X.ub, ly.k_w, ly.k_b, Kh.lw, Kh.uw, Kh.lb, Kh.ub, range[2],
+                                                   range[3], norm_ws, rows, Di, D, D, L, H, words, p, eps, stream);
+        if (krc == FB_OK) kgiven = 2;
+        else if (krc == FB_ERR_SHAPE)
+          FB_TRY(fb_matmul_heads_f32(X.lw, X.uw, X.lb, X.ub, ly.k_w, ly.k_b, Kh.lw, Kh.uw, Kh.lb, Kh.ub, rows, Di, D, D, L, H, stream));
+        else return krc;
+        FB_TRY(fb_dot_product_given_f32(Qh.lw, Qh.uw, Qh.lb, Qh.ub, Kh.lw, Kh.uw, Kh.lb, Kh.ub, Sc.lw, Sc.uw, Sc.lb, Sc.ub, range[0],
+                                        range[1], range[2], range[3], S * H, 1, L, Di, d, words, p, eps, inv_sqrt_d, FB_NATIVE, 1,
+                                        kgiven, stream));
+        // probabilities of that row
+        int src = fb_softmax_f32(Sc.lw, Sc.uw, Sc.lb, Sc.ub, Pr.lw, Pr.uw, Pr.lb, Pr.ub, SH, Di, L, words, p, eps, violation, stream);
+        if (src == FB_ERR_SHAPE || src == FB_ERR_ALIGN) {
+          FB_TRY(relax(FB_EXP, Sc, E1, SH, Di, L, words, p, eps, nullptr, stream));
+          FB_TRY(fb_rowsum_f32(E1.lw, E1.uw, E1.lb, E1.ub, Sc.lw, Sc.uw, Sc.lb, Sc.ub, SH, Di, L, stream));
+          FB_TRY(relax(FB_RECIPROCAL, Sc, E2, SH, Di, L, words, p, eps, violation, stream));
+          src = fb_mul_bounds_f32(E1.lw, E1.uw, E1.lb, E1.ub, E2.lw, E2.uw, E2.lb, E2.ub, Pr.lw, Pr.uw, Pr.lb, Pr.ub, SH, Di, L, words,
+                                  p, eps, stream);
+        }
+        if (src != FB_OK) return src;
+        // values of every token, split into heads as the projection writes them [S*H, L, Di, d]; context of token 0,
+        // head-merged [S, 1, Di, D].  (Other shapes: the transposed copy [S*H, d, Di, L] and the general product.)
+        int vgiven = 0;
+        const int vrc = fb_matmul_heads_ranges_f32(X.lw, X.uw, X.lb, X.ub, ly.v_w, ly.v_b, Vd.lw, Vd.uw, Vd.lb, Vd.ub, range[2],
+                                                   range[3], norm_ws, rows, Di, D, D, L, H, words, p, eps, stream);
+        if (vrc == FB_OK) vgiven = 2;
+        else if (vrc == FB_ERR_SHAPE)
+          FB_TRY(fb_matmul_heads_f32(X.lw, X.uw, X.lb, X.ub, ly.v_w, ly.v_b, Vd.lw, Vd.uw, Vd.lb, Vd.ub, rows, Di, D, D, L, H, stream));
+        else return vrc;
+        const int crc = fb_context_given_f32(Pr.lw, Pr.uw, Pr.lb, Pr.ub, Vd.lw, Vd.uw, Vd.lb, Vd.ub, Cx.lw, Cx.uw, Cx.lb, Cx.ub,
+                                             range[0], range[1], range[2], range[3], S * H, 1, d, Di, L, words, p, eps, 1.0f, H,
+                                             vgiven, stream);
+        if (crc == FB_ERR_SHAPE) {
+          FB_TRY(dense(X, ly.v_w, ly.v_b, Vd, rows, Di, D, D, stream));
+          FB_TRY(fb_split_heads_f32(Vd.lw, Vd.lb, Vt.lw, Vt.lb, S, L, Di, H, d, 1, stream));
+          FB_TRY(fb_split_heads_f32(Vd.uw, Vd.ub, Vt.uw, Vt.ub, S, L, Di, H, d, 1, stream));
+          FB_TRY(fb_dot_product_heads_f32(Pr.lw, Pr.uw, Pr.lb, Pr.ub, Vt.lw, Vt.uw, Vt.lb, Vt.ub, Cx.lw, Cx.uw, Cx.lb, Cx.ub, range[0],
+                                          range[1], range[2], range[3], S * H, 1, d, Di, L, words, p, eps, 1.0f, FB_NATIVE, H, stream));
+        } else if (crc != FB_OK) {
+          return crc;
+        }
+        // attention output + residual, layer norm; feed-forward block + residual, layer norm
+        FB_TRY(dense(Cx, ly.ao_w, ly.ao_b, Ao, S, Di, D, D, stream));
+        FB_TRY(norm_residual(enc, Ao, &Xq, ly.ln1_g, ly.ln1_b, H3, S, Di, D, stream));
+        FB_TRY(dense(H3, ly.f1_w, ly.f1_b, Hd, S, Di, D, F, stream));
+        FB_TRY(relax(FB_RELU, Hd, Hr, S, Di, F, words, p, eps, nullptr, stream));
+        FB_TRY(dense(Hr, ly.f2_w, ly.f2_b, F2, S, Di, F, D, stream));
+        FB_TRY(norm_residual(enc, F2, &H3, ly.ln2_g, ly.ln2_b, Out, S, Di, D, stream));
+        first_token = Out;
+        break;
+      }
+    }
     const BoundSet X = slot[A], T3 = slot[Dd];
     BoundSet T1 = slot[B], T2 = slot[C];
     // Xin: the layer input as the products read it.  Before the first relaxation the two lines of the bound
@@ -436,7 +523,17 @@ static int encoder_forward_impl(const fb_encoder* enc, const float* emb, int S, 
     C = A;
     A = newA;
   }
-  {
+  if (first_token.lw != nullptr) {
+    // the last layer was run for the first token only: its output is the pooler's input (it lives in slot B; the two
+    // scratch sets below are taken from slots C and D)
+    const BoundSet &T1 = slot[C], &T2 = slot[Dd];
+    FB_TRY(dense(first_token, enc->pool_w, enc->pool_b, T2, S, Di, D, D, stream));
+    FB_TRY(relax(FB_TANH, T2, T1, S, Di, D, words, p, eps, nullptr, stream));
+    fold_classifier_kernel<<<1, 128, 0, st>>>(enc->cls_w, enc->cls_b, fold_w, fold_b, D);
+    FB_LAUNCH_OK();
+    FB_TRY(dense(T1, fold_w, fold_b, T2, S, Di, D, 1, stream));
+    FB_TRY(fb_concretize_f32(T2.lw, T2.uw, T2.lb, T2.ub, out_l, out_u, S, Di, 1, words, p, eps, FB_NATIVE, stream));
+  } else {
     const BoundSet &X = slot[A], &T1 = slot[B], &T2 = slot[C];
     // first token of every sentence: [S, 1, Di, D]
     FB_CUDA_OK(cudaMemcpy2DAsync(T1.lw, (size_t)Di * D * 4, X.lw, (size_t)L * Di * D * 4, (size_t)Di * D * 4, S,

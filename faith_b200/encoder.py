@@ -16,9 +16,15 @@ class EncoderVerifier:
     `model` is a dict of float32 tensors: emb_ln_g, emb_ln_b, layers (list of dicts with the
     keys of _LAYER_KEYS, nn.Linear layout), pool_w, pool_b, cls_w [2, D], cls_b [2], heads,
     layer_norm ("no_var" or "no").  Weights are copied to `device` once.
+
+    first_token_only: the reference propagates every layer at every position (VerifierForward.py:93-119) although its
+    pooler reads token 0 of the last layer only (:269-287).  With this flag the last layer forms keys and values at every
+    position but the query, the attention row and everything behind them for token 0 alone: the same bounds up to the
+    rounding of other kernel shapes, about a quarter less work for three layers.  Off by default, so that a pass does the
+    work the reference does.
     """
 
-    def __init__(self, model, device):
+    def __init__(self, model, device, first_token_only=False):
         self.device = torch.device(device)
         self.heads = int(model["heads"])
         self.ln = {"no": 0, "no_var": 1}[model["layer_norm"]]
@@ -38,7 +44,8 @@ class EncoderVerifier:
                 setattr(self._layers[i], k, dev(ly[k]))
         self._enc = Encoder(n, self.d_model, self.heads, self.ffn, self.ln, dev(model["emb_ln_g"]),
                             dev(model["emb_ln_b"]), ctypes.cast(self._layers, ctypes.POINTER(EncoderLayer)),
-                            dev(model["pool_w"]), dev(model["pool_b"]), dev(model["cls_w"]), dev(model["cls_b"]))
+                            dev(model["pool_w"]), dev(model["pool_b"]), dev(model["cls_w"]), dev(model["cls_b"]),
+                            1 if first_token_only else 0)
         self._keep = keep
         self._ws = None
 

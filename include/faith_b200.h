@@ -406,6 +406,13 @@ typedef struct fb_encoder {
   const fb_encoder_layer* layer;  /* host array of `layers` entries */
   const float *pool_w, *pool_b;   /* [d_model, d_model], [d_model] */
   const float *cls_w, *cls_b;     /* [2, d_model], [2] */
+  int first_token_only;           /* 0: every layer is propagated at every position, as the reference does
+                                     (VerifierForward.py:93-119); != 0: the last layer is propagated for the first token
+                                     only.  The pooler reads nothing else of it (VerifierForward.py:269-287), so keys
+                                     and values are still formed at every position but the query, the attention row,
+                                     the attention output and the feed-forward block only at position 0.  Same bounds
+                                     up to the rounding of other kernel shapes; about a quarter less work for three
+                                     layers. */
 } fb_encoder;
 
 /* Bytes of scratch fb_encoder_forward_f32 needs for S sentences of length L. */

@@ -275,3 +275,34 @@ def test_first_layer_projections_skip_zero_row_blocks_bit_for_bit(words, positio
     for x, y in zip(fast, plain):
         assert torch.equal(x, y)
     assert bool(torch.isfinite(fast[0]).all()) and bool((fast[0] <= fast[1]).all())
+
+
+@pytest.mark.parametrize("full_size", [False, True])
+def test_last_layer_for_the_first_token_only_gives_the_same_bounds(full_size):
+    """The pooler reads token 0 of the last layer only; with first_token_only the driver forms the rest of that layer for
+    token 0 alone.  Same bounds as the full pass up to the rounding of the other kernel shapes, and within the fp32
+    noise of the fp64 oracle (which propagates every position, as the reference does)."""
+    import faith_b200
+    if full_size:
+        model = O.make_encoder(4)
+        emb = torch.randn(4, 32, 128, generator=torch.Generator().manual_seed(4))
+        positions, p, eps = [1], float("inf"), 1e-3
+    else:
+        c, model, emb = _small()
+        positions, p, eps = [c["index"]], c["p"], c["eps"]
+    full = faith_b200.EncoderVerifier(model, DEV)
+    pruned = faith_b200.EncoderVerifier(model, DEV, first_token_only=True)
+    l0, u0, v0 = full.forward(emb.to(DEV), positions, p, eps)
+    l1, u1, v1 = pruned.forward(emb.to(DEV), positions, p, eps)
+    assert full.check_status(v0) == 0 and pruned.check_status(v1) == 0
+    l32, u32 = O.encoder_forward(model, emb, positions, p, eps)
+    l64, u64 = O.encoder_forward(O.model_to(model, torch.float64), emb.double(), positions, p, eps)
+    helpers.assert_within_noise(l1, l32, l64, "l")
+    helpers.assert_within_noise(u1, u32, u64, "u")
+    width = float((u0 - l0).abs().max())
+    assert float((l1 - l0).abs().max()) <= 1e-4 * max(width, 1.0) and float((u1 - u0).abs().max()) <= 1e-4 * max(width, 1.0)
+    # per-sentence instances take the same route
+    inst = torch.tensor([[positions[0]]] * emb.shape[0], dtype=torch.int32, device=DEV)
+    l2, u2, _ = pruned.forward_instances(emb.to(DEV), inst, p, torch.full((emb.shape[0],), eps, device=DEV))
+    helpers.assert_within_noise(l2, l32, l64, "l instances")
+    helpers.assert_within_noise(u2, u32, u64, "u instances")

@@ -311,7 +311,9 @@ def test_tensor_core_gemm_never_raised_its_error_flag():
 
 # ------------------------------------------------------------- dot product
 @pytest.mark.parametrize("B,Lx,Ly,Di,K", [(1, 2, 2, 64, 16), (4, 32, 32, 128, 32), (2, 8, 8, 64, 64),
-                                          (1, 5, 7, 24, 10), (2, 33, 9, 36, 130), (1, 16, 16, 256, 512)])
+                                          (1, 5, 7, 24, 10), (2, 33, 9, 36, 130), (1, 16, 16, 256, 512),
+                                          # a few query rows: the thread-per-output kernel
+                                          (8, 1, 32, 128, 32), (3, 4, 9, 20, 33), (2, 3, 40, 64, 7)])
 @pytest.mark.parametrize("p", [2.0, float("inf")])
 def test_dot_product_shapes(B, Lx, Ly, Di, K, p):
     import faith_b200
@@ -491,6 +493,33 @@ def test_conv_of_a_few_images_equals_the_tiled_kernel_bit_for_bit(C, H, W, Co, k
     assert torch.equal(one[0][0, 0], many[0][0, n - 1])
     # the bias part of both calls is one image (small kernel); without the bias it equals the weight part
     assert torch.equal(one[2] - bias.view(1, -1, 1, 1), one[0][0]) or float((one[2] - bias.view(1, -1, 1, 1) - one[0][0]).abs().max()) < 1e-6
+
+
+def test_context_of_a_single_query_row_reads_the_values_in_projection_layout():
+    """fb_context_given_f32 with Lx = 1 (a last layer run for the first token only): the thread-per-output kernel with the
+    values as [B, K, Di, Ly] against the dot product with the transposed copy, head-merged store included."""
+    from faith_b200 import ops
+    B, L, Di, d, H = 8, 32, 64, 32, 4
+    g0 = torch.Generator().manual_seed(24)
+
+    def mk(shape_w, shape_b, sc):
+        lw = torch.randn(*shape_w, generator=g0) * sc
+        uw = lw + torch.rand(*shape_w, generator=g0) * 0.05
+        lb = torch.rand(*shape_b, generator=g0)
+        ub = lb + torch.rand(*shape_b, generator=g0) * 0.05
+        return [t.to(DEV) for t in (lw, uw, lb, ub)]
+    x = mk((B, 1, Di, L), (B, 1, L), 0.05)           # probabilities of one query row [B, 1, Di, K]
+    v = mk((B, L, Di, d), (B, L, d), 0.3)            # values [B, K, Di, Ly]
+    vt = [v[0].permute(0, 3, 2, 1).contiguous(), v[1].permute(0, 3, 2, 1).contiguous(),
+          v[2].permute(0, 2, 1).contiguous(), v[3].permute(0, 2, 1).contiguous()]
+    ref = ops.dot_product(x, vt, 2.0, 0.02, 2, 1.0)
+    got = ops.context_kmajor(x, v, 2.0, 0.02, 2, 1.0, 1)
+    for a, b, name in zip(got, ref, ("lw", "uw", "lb", "ub")):
+        helpers.assert_close(a, b.cpu(), "single-row context " + name, rtol=1e-6, atol=1e-7)
+    merged = ops.context_kmajor(x, v, 2.0, 0.02, 2, 1.0, H)
+    m_ref = ops.merge_heads(ref, H)
+    for a, b, name in zip(merged, m_ref, ("lw", "uw", "lb", "ub")):
+        helpers.assert_close(a, b.cpu(), "single-row merged context " + name, rtol=1e-6, atol=1e-7)
 
 
 def test_dot_product_with_merged_head_store():
