@@ -28,7 +28,7 @@ class EncoderLayer(ctypes.Structure):
 class Encoder(ctypes.Structure):
     _fields_ = [("layers", _I), ("d_model", _I), ("heads", _I), ("ffn", _I), ("layer_norm", _I),
                 ("emb_ln_g", _P), ("emb_ln_b", _P), ("layer", ctypes.POINTER(EncoderLayer)),
-                ("pool_w", _P), ("pool_b", _P), ("cls_w", _P), ("cls_b", _P), ("first_token_only", _I)]
+                ("pool_w", _P), ("pool_b", _P), ("cls_w", _P), ("cls_b", _P), ("first_token_only", _I), ("pooling", _I)]
 
 
 class CnnLayer(ctypes.Structure):

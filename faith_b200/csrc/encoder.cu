@@ -11,6 +11,7 @@
 
 #include <utility>
 
+#include <algorithm>
 #include <cstdlib>
 
 #include "common.cuh"
@@ -163,6 +164,23 @@ input_bounds_norm128_kernel(const float* __restrict__ emb, const float* __restri
   }
 }
 
+// Mean over the positions: z[s, r] = (sum_l x[s, l, r]) / L for the inner[-sized] slab r of every sentence (r runs over
+// Di * D weight entries resp. D bias entries); lanes along r, the L terms added in order.
+__global__ void __launch_bounds__(256)
+mean_pool_kernel(const float* __restrict__ x_lo, const float* __restrict__ x_up, float* __restrict__ z_lo,
+                 float* __restrict__ z_up, int64_t total, int64_t inner, int L) {
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t sidx = t / inner, r = t - sidx * inner;
+    const float* pl = x_lo + sidx * L * inner + r;
+    const float* pu = x_up + sidx * L * inner + r;
+    float al = 0.f, au = 0.f;
+#pragma unroll 4
+    for (int l = 0; l < L; ++l) { al = fadd(al, __ldg(pl + (int64_t)l * inner)); au = fadd(au, __ldg(pu + (int64_t)l * inner)); }
+    z_lo[t] = __fdiv_rn(al, (float)L);
+    z_up[t] = __fdiv_rn(au, (float)L);
+  }
+}
+
 // classifier folded to one row: w = cls_w[0] - cls_w[1], b = cls_b[0] - cls_b[1]
 // (VerifierForward.py:289-292)
 __global__ void fold_classifier_kernel(const float* __restrict__ cls_w, const float* __restrict__ cls_b,
@@ -222,6 +240,7 @@ static int encoder_forward_impl(const fb_encoder* enc, const float* emb, int S, 
   if (enc->layers < 0 || enc->heads <= 0 || enc->d_model <= 0 || enc->d_model % enc->heads != 0 || enc->ffn <= 0)
     return FB_ERR_ARG;
   if (enc->layer_norm != 0 && enc->layer_norm != 1) return FB_ERR_ARG;
+  if (enc->pooling != 0 && enc->pooling != 1) return FB_ERR_ARG;
   for (int w = 0; positions != nullptr && w < words; ++w)
     if (positions[w] < 0 || positions[w] >= L) return FB_ERR_ARG;
   if (!aligned16(workspace)) return FB_ERR_ALIGN;
@@ -273,7 +292,7 @@ static int encoder_forward_impl(const fb_encoder* enc, const float* emb, int S, 
   BoundSet first_token = {nullptr, nullptr, nullptr, nullptr};   // [S, 1, Di, D] output of a last layer run for token 0 only
   for (int li = 0; li < enc->layers; ++li) {
     const fb_encoder_layer& ly = enc->layer[li];
-    if (enc->first_token_only != 0 && li == enc->layers - 1 && L > 1 && d % 4 == 0) {
+    if (enc->first_token_only != 0 && enc->pooling == 0 && li == enc->layers - 1 && L > 1 && d % 4 == 0) {
       // ---- last layer, first token only (the pooler reads nothing else of its output, VerifierForward.py:269-287).
       // Keys and values at every position; query, attention row, attention output, feed-forward block at position 0.
       // Plain operator calls throughout: the tensors on the query side are 1/L of the usual size.
@@ -535,6 +554,14 @@ static int encoder_forward_impl(const fb_encoder* enc, const float* emb, int S, 
     FB_TRY(fb_concretize_f32(T2.lw, T2.uw, T2.lb, T2.ub, out_l, out_u, S, Di, 1, words, p, eps, FB_NATIVE, stream));
   } else {
     const BoundSet &X = slot[A], &T1 = slot[B], &T2 = slot[C];
+    if (enc->pooling == 1) {
+      // mean over the positions: [S, 1, Di, D]
+      const int64_t nw = (int64_t)S * Di * D, nb = (int64_t)S * D, cap = (int64_t)device_info().sms * 32;
+      mean_pool_kernel<<<(unsigned)std::min(ceil_div(nw, 256), cap), 256, 0, st>>>(X.lw, X.uw, T1.lw, T1.uw, nw, (int64_t)Di * D, L);
+      FB_LAUNCH_OK();
+      mean_pool_kernel<<<(unsigned)std::min(ceil_div(nb, 256), cap), 256, 0, st>>>(X.lb, X.ub, T1.lb, T1.ub, nb, (int64_t)D, L);
+      FB_LAUNCH_OK();
+    } else {
     // first token of every sentence: [S, 1, Di, D]
     FB_CUDA_OK(cudaMemcpy2DAsync(T1.lw, (size_t)Di * D * 4, X.lw, (size_t)L * Di * D * 4, (size_t)Di * D * 4, S,
                                  cudaMemcpyDeviceToDevice, st));
@@ -544,6 +571,7 @@ static int encoder_forward_impl(const fb_encoder* enc, const float* emb, int S, 
                                  cudaMemcpyDeviceToDevice, st));
     FB_CUDA_OK(cudaMemcpy2DAsync(T1.ub, (size_t)D * 4, X.ub, (size_t)L * D * 4, (size_t)D * 4, S,
                                  cudaMemcpyDeviceToDevice, st));
+    }
     FB_TRY(dense(T1, enc->pool_w, enc->pool_b, T2, S, Di, D, D, stream));
     FB_TRY(relax(FB_TANH, T2, T1, S, Di, D, words, p, eps, nullptr, stream));
     fold_classifier_kernel<<<1, 128, 0, st>>>(enc->cls_w, enc->cls_b, fold_w, fold_b, D);

@@ -15,7 +15,8 @@ class EncoderVerifier:
 
     `model` is a dict of float32 tensors: emb_ln_g, emb_ln_b, layers (list of dicts with the
     keys of _LAYER_KEYS, nn.Linear layout), pool_w, pool_b, cls_w [2, D], cls_b [2], heads,
-    layer_norm ("no_var" or "no").  Weights are copied to `device` once.
+    layer_norm ("no_var" or "no"), optionally pooling ("first": the reference's first-token pooler, the default; "mean":
+    mean over the positions).  Weights are copied to `device` once.
 
     first_token_only: the reference propagates every layer at every position (VerifierForward.py:93-119) although its
     pooler reads token 0 of the last layer only (:269-287).  With this flag the last layer forms keys and values at every
@@ -45,7 +46,7 @@ class EncoderVerifier:
         self._enc = Encoder(n, self.d_model, self.heads, self.ffn, self.ln, dev(model["emb_ln_g"]),
                             dev(model["emb_ln_b"]), ctypes.cast(self._layers, ctypes.POINTER(EncoderLayer)),
                             dev(model["pool_w"]), dev(model["pool_b"]), dev(model["cls_w"]), dev(model["cls_b"]),
-                            1 if first_token_only else 0)
+                            1 if first_token_only else 0, {"first": 0, "mean": 1}[model.get("pooling", "first")])
         self._keep = keep
         self._ws = None
 

@@ -413,6 +413,10 @@ typedef struct fb_encoder {
                                      the attention output and the feed-forward block only at position 0.  Same bounds
                                      up to the rounding of other kernel shapes; about a quarter less work for three
                                      layers. */
+  int pooling;                    /* 0: the reference's pooler, first token -> dense -> tanh (VerifierForward.py:269-287);
+                                     1: mean over the positions -> dense -> tanh (the pooling the benchmark description
+                                     names; no reference implementation, exact for linear bounds: every line is
+                                     averaged with the positive weight 1/L).  With 1, first_token_only is ignored. */
 } fb_encoder;
 
 /* Bytes of scratch fb_encoder_forward_f32 needs for S sentences of length L. */

@@ -548,7 +548,13 @@ def encoder_forward(model, emb, positions, p, eps, trace=None, ibp=False):
         inter = rec("layer%d.intermediate" % i, att.dense(ly["f1_w"], ly["f1_b"]).relu())
         x = inter.dense(ly["f2_w"], ly["f2_b"]).add(att).layer_norm(ly["ln2_g"], ly["ln2_b"], ln)
         rec("layer%d.output" % i, x)
-    first = x.like(x.lw[:, :1], x.lb[:, :1], x.uw[:, :1], x.ub[:, :1])
+    if model.get("pooling", "first") == "mean":
+        # mean over the positions (a fixed 1/L contraction, exact for linear bounds): the pooling the benchmark
+        # description names; the reference itself pools the first token (VerifierForward.py:269-287)
+        first = x.like(x.lw.mean(1, keepdim=True), x.lb.mean(1, keepdim=True), x.uw.mean(1, keepdim=True),
+                       x.ub.mean(1, keepdim=True))
+    else:
+        first = x.like(x.lw[:, :1], x.lb[:, :1], x.uw[:, :1], x.ub[:, :1])
     pooled = rec("pooled", first.dense(model["pool_w"], model["pool_b"]).tanh())
     cw = (model["cls_w"][0] - model["cls_w"][1]).unsqueeze(0)
     cb = (model["cls_b"][0] - model["cls_b"][1]).unsqueeze(0)
@@ -584,7 +590,8 @@ def concrete_forward(model, emb):
         att = norm(F.linear(ctx, ly["ao_w"], ly["ao_b"]) + x, ly["ln1_g"], ly["ln1_b"])
         inter = torch.relu(F.linear(att, ly["f1_w"], ly["f1_b"]))
         x = norm(F.linear(inter, ly["f2_w"], ly["f2_b"]) + att, ly["ln2_g"], ly["ln2_b"])
-    pooled = torch.tanh(F.linear(x[:, 0], model["pool_w"], model["pool_b"]))
+    tok = x.mean(1) if model.get("pooling", "first") == "mean" else x[:, 0]
+    pooled = torch.tanh(F.linear(tok, model["pool_w"], model["pool_b"]))
     logits = F.linear(pooled, model["cls_w"], model["cls_b"])
     return logits[:, 0] - logits[:, 1]
 

@@ -306,3 +306,31 @@ def test_last_layer_for_the_first_token_only_gives_the_same_bounds(full_size):
     l2, u2, _ = pruned.forward_instances(emb.to(DEV), inst, p, torch.full((emb.shape[0],), eps, device=DEV))
     helpers.assert_within_noise(l2, l32, l64, "l instances")
     helpers.assert_within_noise(u2, u32, u64, "u instances")
+
+
+def test_mean_pooling_option():
+    """pooling = "mean" (the pooling the benchmark description names; the reference pools the first token): mean over the
+    positions -> dense -> tanh.  Against the oracle's restatement (no reference implementation exists: unpinned), and
+    10 000 sampled concrete passes of the mean-pooled model inside [l, u]."""
+    import faith_b200
+    c, model, emb = _small()
+    model = dict(model, pooling="mean")
+    ver = faith_b200.EncoderVerifier(model, DEV)
+    l, u, viol = ver.forward(emb.to(DEV), [c["index"]], c["p"], c["eps"])
+    assert ver.check_status(viol) == 0
+    l32, u32 = O.encoder_forward(model, emb, [c["index"]], c["p"], c["eps"])
+    l64, u64 = O.encoder_forward(O.model_to(model, torch.float64), emb.double(), [c["index"]], c["p"], c["eps"])
+    helpers.assert_within_noise(l, l32, l64, "l")
+    helpers.assert_within_noise(u, u32, u64, "u")
+    first = faith_b200.EncoderVerifier(dict(model, pooling="first"), DEV).forward(emb.to(DEV), [c["index"]], c["p"], c["eps"])
+    assert float((first[0] - l).abs().max()) > 1e-4          # it is a different model
+    l, u = l.cpu(), u.cpu()
+    g = torch.Generator().manual_seed(12)
+    n = 10000
+    for s in range(emb.shape[0]):
+        delta = (torch.randint(0, 2, (n, c["d_model"]), generator=g).float() * 2 - 1) * c["eps"]
+        delta[: n // 2] *= torch.rand(n // 2, 1, generator=g)
+        x = emb[s:s + 1].repeat(n, 1, 1)
+        x[:, c["index"], :] += delta
+        y = O.concrete_forward(model, x)
+        assert float(y.min()) >= float(l[s]) - 1e-5 and float(y.max()) <= float(u[s]) + 1e-5
