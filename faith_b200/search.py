@@ -160,3 +160,61 @@ class EpsilonSearch:
             out.append({tuple(q): float(lo[k + j]) for j, q in enumerate(pairs[s])})
             k += len(pairs[s])
         return out, max_eps
+
+
+def result_record(per_sentence, emb, labels, p, tokens=None, seconds=None):
+    """The reference's result file for one run of the search, as a dict ready for json.dumps(indent=4).
+
+    Reference: Verifier.run and Verifier.verify (Transformer_Verification_Code/Verifiers/Verifier.py:40-60, :76-80,
+    :139-147, :197-206).  per_sentence is what run() or run_pairs() returned: one dict {position: eps} or
+    {(i1, i2): eps} per sentence.  Each sentence becomes {"tokens", "label", "bounds": [...], "time"}; a one-word
+    bound is {"position", "eps", "eps_normalized"} with eps held in single precision, as the reference keeps it in a
+    float tensor (:98, :137), and eps_normalized = eps / ||embedding of that position||_p in single precision (:143-146);
+    a two-word bound is {"position": (i1, i2), "eps"} in double precision (:194-200).  "average" is the mean over
+    sentences of the per-sentence mean radius and "minimum" the mean over sentences of the per-sentence smallest radius
+    (:45-47, :52-58).  A sentence with nothing to search has no mean radius (the reference divides by zero there,
+    :206) and is rejected.  tokens: per sentence the list of token strings (default: the position numbers as strings);
+    seconds: per sentence the time the reference would have logged (default: 0.0, the batched search has no
+    per-sentence time)."""
+    emb = emb.detach().float().cpu()
+    labels = [float(v) for v in labels.tolist()] if hasattr(labels, "tolist") else [float(v) for v in labels]
+    N, L, _ = emb.shape
+    if len(per_sentence) != N or len(labels) != N:
+        raise ValueError("result_record: one entry per sentence is needed")
+    examples, sum_avg, sum_min = [], 0.0, 0.0
+    for s, found in enumerate(per_sentence):
+        if not found:
+            raise ValueError("result_record: sentence %d has no searched position" % s)
+        bounds, sum_eps, min_eps = [], 0.0, 1e30
+        for position, eps in found.items():
+            if isinstance(position, tuple):
+                value = float(eps)
+                bounds.append({"position": (int(position[0]), int(position[1])), "eps": value})
+            else:
+                e32 = torch.tensor(float(eps), dtype=torch.float32)
+                norm = torch.norm(emb[s, int(position), :], p=float(p))
+                value = float(e32)
+                bounds.append({"position": int(position), "eps": value, "eps_normalized": float(e32 / norm)})
+            sum_eps += value
+            min_eps = min(min_eps, value)
+        examples.append({
+            "tokens": list(tokens[s]) if tokens is not None else [str(i) for i in range(L)],
+            "label": labels[s],
+            "bounds": bounds,
+            "time": float(seconds[s]) if seconds is not None else 0.0,
+        })
+        sum_avg += sum_eps / len(found)
+        sum_min += min_eps
+    return {"examples": examples, "minimum": sum_min / N, "average": sum_avg / N}
+
+
+def write_result(path, record, log=None):
+    """Writes the record the way the reference does (Verifier.py:59-60: json.dumps(result, indent=4)) and, when log
+    is a callable taking one string, the three summary lines the reference logs (:49-51)."""
+    import json
+    with open(path, "w") as f:
+        f.write(json.dumps(record, indent=4))
+    if log is not None:
+        log("{} valid examples".format(len(record["examples"])))
+        log("Minimum: {:.5f}".format(record["minimum"]))
+        log("Average: {:.5f}".format(record["average"]))
