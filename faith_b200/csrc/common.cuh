@@ -50,6 +50,20 @@ struct LiveRows {
 };
 void tc_set_live_rows(const LiveRows* lr);   // nullptr clears
 
+// The bias terms of a bound riding in the GEMM launch of its weight rows (extra tiles at the end of the grid):
+// operand a_lo / a_up [M, K], the layer bias (may be null), results c_lo / c_up [M, N] stored plain, and the
+// residual res_lo / res_up [M, N] when the weight rows add one.
+struct TcBiasRows {
+  const float* a_lo;
+  const float* a_up;
+  const float* bias;
+  float* c_lo;
+  float* c_up;
+  int64_t M;
+  const float* res_lo;
+  const float* res_up;
+};
+
 // Opts `kernel` in to `bytes` of dynamic shared memory on the current device (nothing to do up to 48 KB, or when it
 // already has that much): FB_OK or FB_ERR_CUDA.
 int ensure_dynamic_smem_impl(const void* func, size_t bytes);

@@ -385,7 +385,7 @@ static int encoder_forward_impl(const fb_encoder* enc, const float* emb, int S, 
     // tensor as both lines selects its zero-radius instantiation.  (X itself keeps both buffers: they serve
     // as scratch later in the layer.)
     BoundSet Xin = X;
-    if (li == 0) Xin.uw = Xin.lw;
+    if (li == 0) { Xin.uw = Xin.lw; Xin.ub = Xin.lb; }   // (the bias terms coincide as well: their rows then ride in the same launch)
     // The projections of such an input have coinciding lines as well: in the first layer Q, K and V are kept
     // once (both line pointers name the lw buffer; the zero-radius GEMM stores the same tile through both),
     // so the products that read them fetch every tile from HBM once.
@@ -402,24 +402,24 @@ static int encoder_forward_impl(const fb_encoder* enc, const float* emb, int S, 
     // returns the concretised range of its result (column norms taken in the GEMM epilogue), which the
     // product below would otherwise compute in a pass of its own over the operand.
     int given = 0;
-    int qrc = fb_matmul_heads_ranges_f32(Xin.lw, Xin.uw, X.lb, X.ub, ly.q_w, ly.q_b, Qh.lw, Qh.uw, T2.lb, T2.ub, range[0],
+    int qrc = fb_matmul_heads_ranges_f32(Xin.lw, Xin.uw, Xin.lb, Xin.ub, ly.q_w, ly.q_b, Qh.lw, Qh.uw, T2.lb, T2.ub, range[0],
                                          range[1], norm_ws, rows, Di, D, D, L, H, words, p, eps, stream);
     if (qrc == FB_OK) {
       given |= 1;
     } else if (qrc == FB_ERR_SHAPE) {
       Qh = T2;
-      FB_TRY(fb_matmul_heads_f32(Xin.lw, Xin.uw, X.lb, X.ub, ly.q_w, ly.q_b, T2.lw, T2.uw, T2.lb, T2.ub, rows, Di, D, D, L, H,
+      FB_TRY(fb_matmul_heads_f32(Xin.lw, Xin.uw, Xin.lb, Xin.ub, ly.q_w, ly.q_b, T2.lw, T2.uw, T2.lb, T2.ub, rows, Di, D, D, L, H,
                                  stream));
     } else {
       return qrc;
     }
-    qrc = fb_matmul_heads_ranges_f32(Xin.lw, Xin.uw, X.lb, X.ub, ly.k_w, ly.k_b, Kh.lw, Kh.uw, T3.lb, T3.ub, range[2], range[3],
+    qrc = fb_matmul_heads_ranges_f32(Xin.lw, Xin.uw, Xin.lb, Xin.ub, ly.k_w, ly.k_b, Kh.lw, Kh.uw, T3.lb, T3.ub, range[2], range[3],
                                      norm_ws, rows, Di, D, D, L, H, words, p, eps, stream);
     if (qrc == FB_OK) {
       given |= 2;
     } else if (qrc == FB_ERR_SHAPE) {
       Kh = T3;
-      FB_TRY(fb_matmul_heads_f32(Xin.lw, Xin.uw, X.lb, X.ub, ly.k_w, ly.k_b, T3.lw, T3.uw, T3.lb, T3.ub, rows, Di, D, D, L, H,
+      FB_TRY(fb_matmul_heads_f32(Xin.lw, Xin.uw, Xin.lb, Xin.ub, ly.k_w, ly.k_b, T3.lw, T3.uw, T3.lb, T3.ub, rows, Di, D, D, L, H,
                                  stream));
     } else {
       return qrc;
@@ -454,13 +454,13 @@ static int encoder_forward_impl(const fb_encoder* enc, const float* emb, int S, 
       int vgiven = pgiven;
       BoundSet Vh = T3;
       if (li == 0) Vh.uw = Vh.lw;
-      const int vrc = fb_matmul_heads_ranges_f32(Xin.lw, Xin.uw, X.lb, X.ub, ly.v_w, ly.v_b, Vh.lw, Vh.uw, T3.lb, T3.ub, range[2],
+      const int vrc = fb_matmul_heads_ranges_f32(Xin.lw, Xin.uw, Xin.lb, Xin.ub, ly.v_w, ly.v_b, Vh.lw, Vh.uw, T3.lb, T3.ub, range[2],
                                                  range[3], norm_ws, rows, Di, D, D, L, H, words, p, eps, stream);
       if (vrc == FB_OK) {
         vgiven |= 2;
       } else if (vrc == FB_ERR_SHAPE) {
         Vh = T3;
-        FB_TRY(fb_matmul_heads_f32(Xin.lw, Xin.uw, X.lb, X.ub, ly.v_w, ly.v_b, T3.lw, T3.uw, T3.lb, T3.ub, rows, Di, D, D, L, H,
+        FB_TRY(fb_matmul_heads_f32(Xin.lw, Xin.uw, Xin.lb, Xin.ub, ly.v_w, ly.v_b, T3.lw, T3.uw, T3.lb, T3.ub, rows, Di, D, D, L, H,
                                    stream));
       } else {
         return vrc;

@@ -12,7 +12,9 @@ int launch_split_sign_tc(const float* a_lo, const float* a_up, const float* W, c
                          float* c_up, int64_t M, int N, int K, cudaStream_t st, int split_rows, int split_d,
                          const float* coef_l = nullptr, const float* coef_u = nullptr, int coef_di = 1,
                          float* norm_lo = nullptr, float* norm_up = nullptr, int norm_p = 0,
-                         const float* res_lo = nullptr, const float* res_up = nullptr);
+                         const float* res_lo = nullptr, const float* res_up = nullptr, const TcBiasRows* br = nullptr);
+bool tc_bias_rows_mergeable(const float* a_lo, const float* a_up, const float* b_lo, const float* b_up, const float* W,
+                            const float* cb_lo, const float* cb_up, int64_t Mb, int N, int K, bool with_norms);
 int launch_split_sign_ffma(const float* a_lo, const float* a_up, const float* W, const float* bias, float* c_lo,
                            float* c_up, int64_t M, int N, int K, cudaStream_t st, int split_rows, int split_d);
 
@@ -114,6 +116,14 @@ static int matmul_impl(const float* x_lw, const float* x_uw, const float* x_lb, 
   const double M = (double)rows * (Di + 1);
   fb::ProfileScope prof(fb::PK_MATMUL, 8.0 * M * Do * Dy, 4.0 * (2 * M * Do + 2 * M * Dy + (double)Do * Dy + Dy), stream);
   const int d = heads > 1 ? Dy / heads : 0;
+  const int64_t Mw = rows * (int64_t)Di;
+  if (heads <= 1 && Di > 0 && fb::use_tensor_cores() && fb::tc_gemm_supported(x_lw, x_uw, W, y_lw, y_uw, Mw, Dy, Do) &&
+      fb::tc_bias_rows_mergeable(x_lw, x_uw, x_lb, x_ub, W, y_lb, y_ub, rows, Dy, Do, false)) {
+    // both parts on the tensor cores: the bias rows are extra tiles of the weight rows' launch
+    const fb::TcBiasRows br = {x_lb, x_ub, bias, y_lb, y_ub, rows, nullptr, nullptr};
+    return fb::launch_split_sign_tc(x_lw, x_uw, W, nullptr, y_lw, y_uw, Mw, Dy, Do, st, 0, 0, nullptr, nullptr, 1, nullptr,
+                                    nullptr, 0, nullptr, nullptr, &br);
+  }
   // weight rows: [rows * Di, Do] -> [rows * Di, Dy]; no bias on the symbolic part
   int rc = fb::split_sign_gemm(x_lw, x_uw, W, nullptr, y_lw, y_uw, rows * (int64_t)Di, Dy, Do, st,
                                heads > 1 ? L * Di : 0, d);
@@ -154,8 +164,11 @@ extern "C" int fb_matmul_coef_f32(const float* x_lw, const float* x_uw, const fl
   cudaStream_t st = (cudaStream_t)stream;
   const double Mt = (double)rows * (Di + 1);
   fb::ProfileScope prof(fb::PK_MATMUL, 8.0 * Mt * Do * Dy, 4.0 * (2 * Mt * Do + 2 * Mt * Dy + (double)Do * Dy + Dy), stream);
-  int rc = fb::launch_split_sign_tc(x_lw, x_uw, W, nullptr, y_lw, y_uw, M, Dy, Do, st, 0, 0, c_l, c_u, Di);
-  if (rc != FB_OK) return rc;
+  const fb::TcBiasRows br = {x_lb, x_ub, bias, y_lb, y_ub, rows, nullptr, nullptr};
+  const bool merged = fb::tc_bias_rows_mergeable(x_lw, x_uw, x_lb, x_ub, W, y_lb, y_ub, rows, Dy, Do, false);
+  int rc = fb::launch_split_sign_tc(x_lw, x_uw, W, nullptr, y_lw, y_uw, M, Dy, Do, st, 0, 0, c_l, c_u, Di, nullptr, nullptr, 0,
+                                    nullptr, nullptr, merged ? &br : nullptr);
+  if (rc != FB_OK || merged) return rc;
   return fb::split_sign_gemm(x_lb, x_ub, W, bias, y_lb, y_ub, rows, Dy, Do, st);
 }
 
@@ -184,17 +197,25 @@ extern "C" int fb_matmul_heads_ranges_f32(const float* x_lw, const float* x_uw, 
   fb::ProfileScope prof(fb::PK_MATMUL, 8.0 * Mt * Do * Dy, 4.0 * (2 * Mt * Do + 2 * Mt * Dy + (double)Do * Dy + Dy), stream);
   float* norm_lo = norm_ws;
   float* norm_up = norm_ws + rows * words * Dy;
-  int rc = fb::launch_split_sign_tc(x_lw, x_uw, W, nullptr, y_lw, y_uw, M, Dy, Do, st, heads > 1 ? L * Di : 0,
-                                    heads > 1 ? d : 0, nullptr, nullptr, 1, norm_lo, norm_up, p);
-  if (rc != FB_OK) return rc;
   // Bias rows.  A head-split store of [rows, Dy] does not fit the tensor-core kernel's output boxes (L rows per
   // group), and the CUDA-core kernel has too few tiles to fill the machine at this size: with heads > 1 the
-  // tensor-core kernel writes them unsplit into the scratch and the range kernel splits them on the way.
+  // tensor-core kernel writes them unsplit into the scratch and the range kernel splits them on the way.  Where
+  // the shapes allow, they are extra tiles of the weight rows' launch.
   float* plain_lb = nullptr;
   float* plain_ub = nullptr;
-  if (heads > 1 && fb::tc_gemm_supported(x_lb, x_ub, W, norm_ws, norm_ws, rows, Dy, Do)) {
-    plain_lb = norm_ws + 2 * rows * words * Dy;
-    plain_ub = plain_lb + rows * Dy;
+  float* const b_lo = heads > 1 ? norm_ws + 2 * rows * words * Dy : y_lb;
+  float* const b_up = heads > 1 ? b_lo + rows * Dy : y_ub;
+  const bool merged = fb::tc_bias_rows_mergeable(x_lw, x_uw, x_lb, x_ub, W, b_lo, b_up, rows, Dy, Do, true);
+  const fb::TcBiasRows br = {x_lb, x_ub, bias, b_lo, b_up, rows, nullptr, nullptr};
+  int rc = fb::launch_split_sign_tc(x_lw, x_uw, W, nullptr, y_lw, y_uw, M, Dy, Do, st, heads > 1 ? L * Di : 0,
+                                    heads > 1 ? d : 0, nullptr, nullptr, 1, norm_lo, norm_up, p, nullptr, nullptr,
+                                    merged ? &br : nullptr);
+  if (rc != FB_OK) return rc;
+  if (merged) {
+    if (heads > 1) { plain_lb = b_lo; plain_ub = b_up; }
+  } else if (heads > 1 && fb::tc_gemm_supported(x_lb, x_ub, W, norm_ws, norm_ws, rows, Dy, Do)) {
+    plain_lb = b_lo;
+    plain_ub = b_up;
     rc = fb::launch_split_sign_tc(x_lb, x_ub, W, bias, plain_lb, plain_ub, rows, Dy, Do, st, 0, 0);
   } else {
     rc = fb::split_sign_gemm(x_lb, x_ub, W, bias, y_lb, y_ub, rows, Dy, Do, st, heads > 1 ? L : 0, heads > 1 ? d : 0);
@@ -243,9 +264,11 @@ extern "C" int fb_matmul_residual_f32(const float* x_lw, const float* x_uw, cons
   cudaStream_t st = (cudaStream_t)stream;
   const double Mt = (double)rows * (Di + 1);
   fb::ProfileScope prof(fb::PK_MATMUL, 8.0 * Mt * Do * Dy, 4.0 * (2 * Mt * Do + 4 * Mt * Dy + (double)Do * Dy + Dy), stream);
+  const fb::TcBiasRows br = {x_lb, x_ub, bias, y_lb, y_ub, rows, r_lb, r_ub};
+  const bool merged = fb::tc_bias_rows_mergeable(x_lw, x_uw, x_lb, x_ub, W, y_lb, y_ub, rows, Dy, Do, false);
   int rc = fb::launch_split_sign_tc(x_lw, x_uw, W, nullptr, y_lw, y_uw, M, Dy, Do, st, 0, 0, c_l, c_u, Di, nullptr, nullptr, 0,
-                                    r_lw, r_uw);
-  if (rc != FB_OK) return rc;
+                                    r_lw, r_uw, merged ? &br : nullptr);
+  if (rc != FB_OK || merged) return rc;
   return fb::launch_split_sign_tc(x_lb, x_ub, W, bias, y_lb, y_ub, rows, Dy, Do, st, 0, 0, nullptr, nullptr, 1, nullptr,
                                   nullptr, 0, r_lb, r_ub);
 }

@@ -48,6 +48,7 @@
 // tensor memory and returns.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -145,6 +146,11 @@ struct SharedLayout {
 // x_uw is not loaded, no radius planes are written, the radius products are not issued and the epilogue reads
 // two accumulators; the results equal those of the general kernel bit for bit.
 //
+// Bias rows in the same grid: tiles main_tiles .. total_tiles-1 belong to a second operand (the bias terms
+// x_lb, x_ub [rows, K] of the bound whose weight rows are the first operand): the same W, maps of their own
+// (tm_b_*, tm_bout_*, tm_bres_*), the layer bias bias_b added, plain store, no slopes and no column norms.  Every tile is
+// computed exactly as a launch of its own would compute it.  main_tiles == total_tiles: no such tiles.
+//
 // status: device word of the caller (may be null); bit 2 is set when a bounded wait of this launch expired.
 // wait_tries: bound of every mbarrier wait in tries of ~20 us.  skip_it >= 0 makes the producer of CTA 0 leave
 // out the loads of that k-block: the self-test of the give-up path (fb_tc_selftest_timeout), never set otherwise.
@@ -153,7 +159,11 @@ __global__ void __launch_bounds__(kThreads, 1)
 split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_constant__ CUtensorMap tm_up,
                    const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_out_lo,
                    const __grid_constant__ CUtensorMap tm_out_up, const __grid_constant__ CUtensorMap tm_res_lo,
-                   const __grid_constant__ CUtensorMap tm_res_up, const float* __restrict__ bias, int64_t M, int N, int K,
+                   const __grid_constant__ CUtensorMap tm_res_up, const __grid_constant__ CUtensorMap tm_b_lo,
+                   const __grid_constant__ CUtensorMap tm_b_up, const __grid_constant__ CUtensorMap tm_bout_lo,
+                   const __grid_constant__ CUtensorMap tm_bout_up, const __grid_constant__ CUtensorMap tm_bres_lo,
+                   const __grid_constant__ CUtensorMap tm_bres_up, const float* __restrict__ bias,
+                   const float* __restrict__ bias_b, int main_tiles, int same_out_b, int64_t M, int N, int K,
                    int n_tiles_n, int64_t total_tiles, int split_rows, int split_d,
                    const float* __restrict__ coef_l, const float* __restrict__ coef_u, int coef_di,
                    float* __restrict__ norm_lo, float* __restrict__ norm_up, int norm_p,
@@ -165,6 +175,7 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
   // loaded, converted or multiplied; the issuers only signal "ready" and the epilogue stores zeros (and zero norms).
   const bool use_live = kPoint && kNorm && !kCoef && !kResid && live_rows.L > 0;
   auto tile_live_slow = [&](int tile) -> bool {
+    if (tile >= main_tiles) return true;   // bias rows are never known to be zero
     const unsigned bl = ((unsigned)(tile / n_tiles_n) * (unsigned)BM) / (unsigned)live_rows.Di;   // M < 2^31
     const int l = (int)(bl % (unsigned)live_rows.L), b = (int)(bl / (unsigned)live_rows.L);
     bool live = false;
@@ -251,7 +262,11 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
     for (int ti = 0; ti < my_tiles && ok; ++ti) {
       const int tile = blockIdx.x + ti * gridDim.x;
       if (!tile_live(ti)) continue;
-      const int m0 = (int)(tile / n_tiles_n) * BM, n0 = (int)(tile % n_tiles_n) * BN;
+      const bool bseg = tile >= main_tiles;            // a tile of the bias rows
+      const int stile = bseg ? tile - main_tiles : tile;
+      const int m0 = (int)(stile / n_tiles_n) * BM, n0 = (int)(stile % n_tiles_n) * BN;
+      const CUtensorMap* const map_lo = bseg ? &tm_b_lo : &tm_lo;
+      const CUtensorMap* const map_up = bseg ? &tm_b_up : &tm_up;
       for (int kb = 0; kb < nkb; ++kb, ++it) {
         const int rs = (int)(it % kRawStages);
         const uint32_t full = bar_full + 8 * rs;
@@ -260,8 +275,8 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
         if (lane == 0 && !(blockIdx.x == 0 && it == skip_it)) {
           mbar_arrive_expect_tx(full, kPoint ? kRawStageBytes - kTileBytes : kRawStageBytes);
           const uint32_t dst = base + SharedLayout::raw(rs);
-          tma_load_2d(dst, &tm_lo, kb * BK, m0, full);
-          if (!kPoint) tma_load_2d(dst + kTileBytes, &tm_up, kb * BK, m0, full);
+          tma_load_2d(dst, map_lo, kb * BK, m0, full);
+          if (!kPoint) tma_load_2d(dst + kTileBytes, map_up, kb * BK, m0, full);
           tma_load_2d(dst + 2 * kTileBytes, &tm_w, kb * BK, n0, full);
         }
         __syncwarp();
@@ -344,7 +359,14 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
     for (int e = 0; e < my_tiles && ok; ++e) {
       const int etile = blockIdx.x + e * gridDim.x;
       const bool elive = tile_live(e);
-      const int my = (etile / n_tiles_n) * BM, nx = (etile % n_tiles_n) * BN;
+      const bool bseg = etile >= main_tiles;           // a tile of the bias rows: maps and bias of its own, plain store, no norms
+      const int stile = bseg ? etile - main_tiles : etile;
+      const int my = (stile / n_tiles_n) * BM, nx = (stile % n_tiles_n) * BN;
+      const float* const tbias = bseg ? bias_b : bias;
+      const CUtensorMap* const map_out_lo = bseg ? &tm_bout_lo : &tm_out_lo;
+      const CUtensorMap* const map_out_up = bseg ? &tm_bout_up : &tm_out_up;
+      const int t_split_rows = bseg ? 0 : split_rows;
+      const bool t_same_out = (bseg ? same_out_b : same_out) != 0;
       if (!elive) {
         // A zero row block (kPoint and kNorm only): the result is +0 everywhere and so are its column norms.  The
         // accumulators play no part (the issuers skip the tile as well); the staging buffer is zeroed once and then
@@ -367,15 +389,15 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
 #pragma unroll
           for (int q = 0; q < 2; ++q) {
             int cx = nx + 32 * q, cy = my, cz = 0;
-            if (split_rows > 0) {
+            if (t_split_rows > 0) {
               const int heads = N / split_d;
-              cz = (my / split_rows) * heads + cx / split_d;
-              cy = my % split_rows;
+              cz = (my / t_split_rows) * heads + cx / split_d;
+              cy = my % t_split_rows;
               cx = cx % split_d;
             }
-            tma_store_3d(&tm_out_lo, cx, cy, cz, so + q * kOutBoxBytes);
+            tma_store_3d(map_out_lo, cx, cy, cz, so + q * kOutBoxBytes);
             // (zero radius and one buffer named as both outputs: the two tiles are the same numbers, stored once)
-            if (!(kPoint && same_out)) tma_store_3d(&tm_out_up, cx, cy, cz, so + (2 + q) * kOutBoxBytes);
+            if (!(kPoint && t_same_out)) tma_store_3d(map_out_up, cx, cy, cz, so + (2 + q) * kOutBoxBytes);
           }
           tma_store_commit();
         }
@@ -398,8 +420,8 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
         mbar_arrive_expect_tx(bar_res, kOutStageBytes);
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
-          tma_load_3d(so + q * kOutBoxBytes, &tm_res_lo, nx + 32 * q, my, 0, bar_res);
-          tma_load_3d(so + (2 + q) * kOutBoxBytes, &tm_res_up, nx + 32 * q, my, 0, bar_res);
+          tma_load_3d(so + q * kOutBoxBytes, bseg ? &tm_bres_lo : &tm_res_lo, nx + 32 * q, my, 0, bar_res);
+          tma_load_3d(so + (2 + q) * kOutBoxBytes, bseg ? &tm_bres_up : &tm_res_up, nx + 32 * q, my, 0, bar_res);
         }
       }
       ok = mbar_wait_warp(bar_acc_ready, (uint32_t)(le & 1), wc);
@@ -442,9 +464,9 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
               lo[i] = fsub(yc, yr);
               up[i] = fadd(yc, yr);
             }
-            if (bias != nullptr) {
+            if (tbias != nullptr) {
               const int n = nx + ncol + q * 4 + i;
-              const float bv = n < N ? bias[n] : 0.f;
+              const float bv = n < N ? tbias[n] : 0.f;
               lo[i] = fadd(lo[i], bv);
               up[i] = fadd(up[i], bv);
             }
@@ -471,18 +493,18 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
           int cx = nx + 32 * q, cy = my, cz = 0;
-          if (split_rows > 0) {
+          if (t_split_rows > 0) {
             const int heads = N / split_d;
-            cz = (my / split_rows) * heads + cx / split_d;
-            cy = my % split_rows;
+            cz = (my / t_split_rows) * heads + cx / split_d;
+            cy = my % t_split_rows;
             cx = cx % split_d;
           }
-          tma_store_3d(&tm_out_lo, cx, cy, cz, so + q * kOutBoxBytes);
-          if (!(kPoint && same_out)) tma_store_3d(&tm_out_up, cx, cy, cz, so + (2 + q) * kOutBoxBytes);
+          tma_store_3d(map_out_lo, cx, cy, cz, so + q * kOutBoxBytes);
+          if (!(kPoint && t_same_out)) tma_store_3d(map_out_up, cx, cy, cz, so + (2 + q) * kOutBoxBytes);
         }
         tma_store_commit();
       }
-      if (kNorm) {
+      if (kNorm && !bseg) {
         // Column norms of the staged tile.  Warp w reads 16 columns of box w / 2 (lower q0, lower q1, upper q0,
         // upper q1): lanes 0-15 the rows with bit 2 clear, lanes 16-31 those with bit 2 set, which the
         // swizzle puts into the other half of the banks.  The next tile overwrites the staging buffer
@@ -537,13 +559,19 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
       if (kCoef) {
         while (c_kb >= nkb) { c_kb -= nkb; ++c_ti; }
         const int tile = blockIdx.x + c_ti * gridDim.x;
-        const int64_t rb = ((int64_t)(tile / n_tiles_n) * BM) / coef_di;
-        const float* pl = coef_l + rb * K + c_kb * BK + half * 16;
-        const float* pu = coef_u + rb * K + c_kb * BK + half * 16;
+        if (tile >= main_tiles) {
+          // bias rows carry no slopes (the relaxed bias terms are given as they are): a factor of one is exact
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          kl[q] = __ldg(reinterpret_cast<const float4*>(pl) + q);
-          ku[q] = __ldg(reinterpret_cast<const float4*>(pu) + q);
+          for (int q = 0; q < 4; ++q) kl[q] = ku[q] = make_float4(1.f, 1.f, 1.f, 1.f);
+        } else {
+          const int64_t rb = ((int64_t)(tile / n_tiles_n) * BM) / coef_di;
+          const float* pl = coef_l + rb * K + c_kb * BK + half * 16;
+          const float* pu = coef_u + rb * K + c_kb * BK + half * 16;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            kl[q] = __ldg(reinterpret_cast<const float4*>(pl) + q);
+            ku[q] = __ldg(reinterpret_cast<const float4*>(pu) + q);
+          }
         }
       }
       ok = mbar_wait_warp(bar_full + 8 * g, (uint32_t)((it >> 1) & 1), wc);
@@ -684,6 +712,20 @@ void tc_set_live_rows(const LiveRows* lr) {
 }
 int* tc_status_sink() { return t_status_sink; }
 
+// Whether the bias rows [Mb, K] of a bound can ride in the grid of its weight rows: tensor-core shapes, and the
+// same choice of zero radius on both sides when the weight rows take the zero-radius instantiation.
+// FB_TC_SEPARATE_BIAS_ROWS=1 keeps them in a launch of their own (for comparisons).
+bool tc_bias_rows_mergeable(const float* a_lo, const float* a_up, const float* b_lo, const float* b_up, const float* W,
+                            const float* cb_lo, const float* cb_up, int64_t Mb, int N, int K, bool with_norms) {
+  const char* e = std::getenv("FB_TC_SEPARATE_BIAS_ROWS");   // read per call, so that a test can compare the two forms
+  const bool separate = e != nullptr && e[0] == '1';
+  if (separate || Mb < 256 || Mb >= (1ll << 31)) return false;   // below 256 rows the bias terms take the CUDA-core kernel
+  if (!aligned16(b_lo) || !aligned16(b_up) || !aligned16(cb_lo) || !aligned16(cb_up) || !aligned16(W)) return false;
+  if (N < 32 || N % 4 != 0 || K < 8 || K % 4 != 0) return false;
+  if (with_norms && (a_lo == a_up) != (b_lo == b_up)) return false;
+  return true;
+}
+
 // Head-split store is possible when a 128-row tile stays inside one group and a 32-column box inside one head.
 bool tc_split_supported(int64_t M, int N, int split_rows, int split_d) {
   return split_rows > 0 && split_d > 0 && split_rows % BM == 0 && M % split_rows == 0 && split_d % 32 == 0 &&
@@ -701,7 +743,12 @@ bool tc_gemm_supported(const float* a_lo, const float* a_up, const float* W, con
 int launch_split_sign_tc(const float* a_lo, const float* a_up, const float* W, const float* bias, float* c_lo,
                          float* c_up, int64_t M, int N, int K, cudaStream_t st, int split_rows, int split_d,
                          const float* coef_l, const float* coef_u, int coef_di, float* norm_lo, float* norm_up,
-                         int norm_p, const float* res_lo, const float* res_up) {
+                         int norm_p, const float* res_lo, const float* res_up, const TcBiasRows* br) {
+  // Bias rows in the same grid (br != nullptr): they must take the same instantiation as the weight rows (zero
+  // radius or not, residual or not); the caller checks tc_bias_rows_mergeable first.
+  if (br != nullptr && ((br->res_lo != nullptr) != (res_lo != nullptr) || (br->res_lo != nullptr) != (br->res_up != nullptr) ||
+                        ((br->a_lo == br->a_up) != (a_lo == a_up) && norm_lo != nullptr) || br->M <= 0))
+    return FB_ERR_ARG;
   if (norm_lo != nullptr && (coef_l != nullptr || norm_up == nullptr || M % BM != 0)) return FB_ERR_ARG;
   if (res_lo != nullptr && (res_up == nullptr || norm_lo != nullptr || split_rows > 0 || !aligned16(res_lo) || !aligned16(res_up)))
     return FB_ERR_ARG;
@@ -719,7 +766,26 @@ int launch_split_sign_tc(const float* a_lo, const float* a_up, const float* W, c
     return FB_ERR_CUDA;
   const int64_t gm = ceil_div(M, BM);
   const int gn = (int)ceil_div(N, BN);
-  const int64_t total_tiles = gm * gn;
+  const int64_t main_tiles = gm * gn;
+  // the maps of the bias rows are only read for tiles beyond main_tiles; without such tiles they are copies
+  CUtensorMap tm_b_lo = tm_lo, tm_b_up = tm_up, tm_bout_lo = tm_out_lo, tm_bout_up = tm_out_up, tm_bres_lo = tm_res_lo,
+              tm_bres_up = tm_res_up;
+  int64_t total_tiles = main_tiles;
+  if (br != nullptr) {
+    if (!make_map(&tm_b_lo, br->a_lo, (uint64_t)br->M, (uint64_t)K, BM) || !make_map(&tm_b_up, br->a_up, (uint64_t)br->M, (uint64_t)K, BM) ||
+        !make_out_map(&tm_bout_lo, br->c_lo, (uint64_t)br->M, (uint64_t)N, 0, 0) ||
+        !make_out_map(&tm_bout_up, br->c_up, (uint64_t)br->M, (uint64_t)N, 0, 0))
+      return FB_ERR_CUDA;
+    tm_bres_lo = tm_bout_lo;
+    tm_bres_up = tm_bout_up;
+    if (br->res_lo != nullptr && (!make_out_map(&tm_bres_lo, br->res_lo, (uint64_t)br->M, (uint64_t)N, 0, 0) ||
+                                  !make_out_map(&tm_bres_up, br->res_up, (uint64_t)br->M, (uint64_t)N, 0, 0)))
+      return FB_ERR_CUDA;
+    total_tiles += ceil_div(br->M, BM) * gn;
+    if (total_tiles * ((K + BK - 1) / BK) >= (1ll << 31)) return FB_ERR_SHAPE;
+  }
+  const float* bias_b = br != nullptr ? br->bias : nullptr;
+  const int same_b = (br != nullptr && br->c_lo == br->c_up) ? 1 : 0;
   static std::once_flag attr_once[64];
   int dev = 0;
   FB_CUDA_OK(cudaGetDevice(&dev));
@@ -751,7 +817,8 @@ int launch_split_sign_tc(const float* a_lo, const float* a_up, const float* W, c
   if (t_live_rows.L > 0 && t_live_rows.M == M && bias == nullptr && t_live_rows.Di > 0 && t_live_rows.Di % BM == 0 &&
       t_live_rows.words >= 1 && t_live_rows.words <= 4 && M % ((int64_t)t_live_rows.Di * t_live_rows.L) == 0)
     live = t_live_rows;
-#define FB_TC_ARGS tm_lo, tm_up, tm_w, tm_out_lo, tm_out_up, tm_res_lo, tm_res_up, bias, M, N, K, gn, total_tiles, split_rows, split_d
+#define FB_TC_ARGS tm_lo, tm_up, tm_w, tm_out_lo, tm_out_up, tm_res_lo, tm_res_up, tm_b_lo, tm_b_up, tm_bout_lo, tm_bout_up, tm_bres_lo, \
+                   tm_bres_up, bias, bias_b, (int)main_tiles, same_b, M, N, K, gn, total_tiles, split_rows, split_d
   if (coef_l != nullptr && res_lo != nullptr)
     split_sign_gemm_tc<true, false, true, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, coef_l, coef_u, coef_di, nullptr, nullptr, 0, status, tries, skip, no_live, 0);
   else if (coef_l != nullptr)
@@ -894,7 +961,7 @@ extern "C" int fb_tc_selftest_timeout(const float* x_lw, const float* x_uw, cons
   int* const saved_sink = fb::t_status_sink;
   fb::t_status_sink = status;
   rc = fb::launch_split_sign_tc(x_lw, x_uw, W, nullptr, y_lw, y_uw, M, N, K, (cudaStream_t)stream, 0, 0, nullptr, nullptr, 1,
-                                nullptr, nullptr, 0, nullptr, nullptr);
+                                nullptr, nullptr, 0, nullptr, nullptr, nullptr);
   fb::t_status_sink = saved_sink;
   fb::g_wait_tries = fb::kMaxTries;
   fb::g_skip_it = -1;

@@ -854,3 +854,48 @@ def test_interval_mode_matches_the_reference_on_the_gpu(name):
     got = run_gpu_op(c)
     for k in ("lw", "uw", "lb", "ub"):
         helpers.assert_close(got[k], getattr(ref, k), "%s/%s vs the reference on the GPU" % (name, k))
+
+
+@pytest.mark.parametrize("S", [8, 9])
+def test_bias_rows_in_the_grid_of_the_weight_rows_bit_for_bit(S, monkeypatch):
+    """The bias terms of a bound ride as extra tiles in the tensor-core launch of its weight rows (plain product,
+    product with ranges, with slopes, with the residual; zero radius or not).  Every tile is computed as a launch of
+    its own computes it: results equal those with FB_TC_SEPARATE_BIAS_ROWS=1 bit for bit, also with a last tile of
+    the bias rows that is cut short (S = 9: 288 rows)."""
+    from faith_b200 import ops, _lib
+    L, Di, D, F, H, eps, p = 32, 128, 128, 256, 4, 0.05, float("inf")
+    t = [v.to(DEV) for v in cases.rand_bounds(911, S, L, Di, D, -0.4, 0.6)]
+    lw, lb, uw, ub = t
+    r = [v.to(DEV) for v in cases.rand_bounds(912, S, L, Di, F)]
+    res = (r[0], r[2], r[1], r[3])
+    g = torch.Generator().manual_seed(15)
+    W = (torch.randn(F, D, generator=g) / math.sqrt(D)).to(DEV)
+    Wq = (torch.randn(D, D, generator=g) / math.sqrt(D)).to(DEV)
+    bias = (torch.randn(F, generator=g) * 0.1).to(DEV)
+    bq = (torch.randn(D, generator=g) * 0.1).to(DEV)
+    c_l, c_u, nlb, nub = ops.relax_coef(_lib.FB_RELU, lw, uw, lb, ub, p, eps, 1)
+
+    def run_all():
+        out = []
+        out += ops.matmul(lw, uw, lb, ub, W, bias)
+        out += ops.matmul(lw, uw, lb, ub, W, None)
+        out += ops.matmul_heads_ranges(lw, uw, lb, ub, Wq, bq, H, p, eps, 1)
+        out += ops.matmul_heads_ranges(lw, lw, lb, lb, Wq, bq, H, 2.0, eps, 1)     # zero radius on both parts
+        out += ops.matmul_heads_ranges(lw, lw, lb, ub, Wq, bq, H, p, eps, 1)       # zero radius on one: not merged
+        out += ops.matmul_heads_ranges(lw, uw, lb, ub, Wq, bq, 1, p, eps, 1)       # one head: bias rows stored in place
+        out += ops.matmul_coef(lw, uw, nlb, nub, c_l, c_u, W, bias)
+        out += ops.matmul_residual(lw, uw, lb, ub, W, bias, res)
+        out += ops.matmul_residual(lw, uw, nlb, nub, W, bias, res, c_l, c_u)
+        torch.cuda.synchronize()
+        return out
+    monkeypatch.setenv("FB_TC_SEPARATE_BIAS_ROWS", "1")
+    separate = run_all()
+    monkeypatch.delenv("FB_TC_SEPARATE_BIAS_ROWS")
+    merged = run_all()
+    assert len(merged) == len(separate)
+    for k, (a, b) in enumerate(zip(merged, separate)):
+        assert torch.equal(a, b), k
+    for _ in range(3):
+        for k, (a, b) in enumerate(zip(run_all(), merged)):
+            assert torch.equal(a, b), k
+    assert _lib.load().fb_tc_check() == 0
