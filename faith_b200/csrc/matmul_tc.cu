@@ -555,22 +555,22 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
       // (b, l) row of the bound (tile row / coef_di; a tile never straddles two row blocks).  The 16
       // values per side are the same for every thread of the CTA; they are fetched first so that their
       // latency hides behind the wait and the shared-memory loads.
-      float4 kl[4], ku[4];
+      ulonglong2 kl[4], ku[4];   // pairs of fp32 slopes
       if (kCoef) {
         while (c_kb >= nkb) { c_kb -= nkb; ++c_ti; }
         const int tile = blockIdx.x + c_ti * gridDim.x;
         if (tile >= main_tiles) {
           // bias rows carry no slopes (the relaxed bias terms are given as they are): a factor of one is exact
 #pragma unroll
-          for (int q = 0; q < 4; ++q) kl[q] = ku[q] = make_float4(1.f, 1.f, 1.f, 1.f);
+          for (int q = 0; q < 4; ++q) kl[q] = ku[q] = make_ulonglong2(kOne2, kOne2);
         } else {
           const int64_t rb = ((int64_t)(tile / n_tiles_n) * BM) / coef_di;
           const float* pl = coef_l + rb * K + c_kb * BK + half * 16;
           const float* pu = coef_u + rb * K + c_kb * BK + half * 16;
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            kl[q] = __ldg(reinterpret_cast<const float4*>(pl) + q);
-            ku[q] = __ldg(reinterpret_cast<const float4*>(pu) + q);
+            kl[q] = __ldg(reinterpret_cast<const ulonglong2*>(pl) + q);
+            ku[q] = __ldg(reinterpret_cast<const ulonglong2*>(pu) + q);
           }
         }
       }
@@ -579,53 +579,52 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
       const uint8_t* raw = base_ptr + SharedLayout::raw(g);
       // W tile: 64 rows x 8 chunks; this thread converts two adjacent chunks of one row
       const int wrow = gt >> 2, wchunk = (gt & 3) * 2;
-      float c[16], r[16];
-      uint32_t whi[8], wlo[8];
+      // The arithmetic below runs on pairs of fp32 values (fma / mul / sub .f32x2: one instruction for two
+      // round-to-nearest results, bit for bit those of the scalar forms): the converters are bound by the number of
+      // instructions they issue, not by the fp32 pipe.  c2[i], r2[i]: elements 2i, 2i+1 of this thread's 16 centres / radii.
+      uint64_t c2[8], r2[8], w2[4];
       {
-        float4 vl[4], vu[4], vw[2];
+        ulonglong2 vl[4], vu[4], vw[2];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const uint32_t off = swz(row, half * 4 + q);
-          vl[q] = *reinterpret_cast<const float4*>(raw + off);
-          vu[q] = kPoint ? vl[q] : *reinterpret_cast<const float4*>(raw + kTileBytes + off);
+          vl[q] = *reinterpret_cast<const ulonglong2*>(raw + off);
+          vu[q] = kPoint ? vl[q] : *reinterpret_cast<const ulonglong2*>(raw + kTileBytes + off);
         }
 #pragma unroll
-        for (int q = 0; q < 2; ++q) vw[q] = *reinterpret_cast<const float4*>(raw + 2 * kTileBytes + swz(wrow, wchunk + q));
+        for (int q = 0; q < 2; ++q) vw[q] = *reinterpret_cast<const ulonglong2*>(raw + 2 * kTileBytes + swz(wrow, wchunk + q));
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          float l4[4] = {vl[q].x, vl[q].y, vl[q].z, vl[q].w};
-          float u4[4] = {vu[q].x, vu[q].y, vu[q].z, vu[q].w};
+          uint64_t l2[2] = {vl[q].x, vl[q].y}, u2[2] = {vu[q].x, vu[q].y};
           if (kCoef) {   // one rounded product per side, as the rescale pass of the relaxation kernels
-            l4[0] = fmul(kl[q].x, l4[0]); l4[1] = fmul(kl[q].y, l4[1]); l4[2] = fmul(kl[q].z, l4[2]); l4[3] = fmul(kl[q].w, l4[3]);
-            u4[0] = fmul(ku[q].x, u4[0]); u4[1] = fmul(ku[q].y, u4[1]); u4[2] = fmul(ku[q].z, u4[2]); u4[3] = fmul(ku[q].w, u4[3]);
+            l2[0] = mul2(kl[q].x, l2[0]); l2[1] = mul2(kl[q].y, l2[1]);
+            u2[0] = mul2(ku[q].x, u2[0]); u2[1] = mul2(ku[q].y, u2[1]);
           }
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
+          for (int i = 0; i < 2; ++i) {
             // centre (l + u) / 2 and radius (u - l) / 2, each rounded once
-            const float hu = fmul(u4[i], 0.5f);
-            c[q * 4 + i] = __fmaf_rn(l4[i], 0.5f, hu);
-            r[q * 4 + i] = __fmaf_rn(l4[i], -0.5f, hu);
+            const uint64_t hu = mul2(u2[i], kHalf2);
+            c2[q * 2 + i] = fma2(l2[i], kHalf2, hu);
+            r2[q * 2 + i] = fma2(l2[i], kMinusHalf2, hu);
           }
         }
-#pragma unroll
-        for (int q = 0; q < 2; ++q) {
-          const float w4[4] = {vw[q].x, vw[q].y, vw[q].z, vw[q].w};
-#pragma unroll
-          for (int i = 0; i < 4; ++i) split_tf32(w4[i], whi[q * 4 + i], wlo[q * 4 + i]);
-        }
+        w2[0] = vw[0].x; w2[1] = vw[0].y; w2[2] = vw[1].x; w2[3] = vw[1].y;
       }
+      uint64_t whi2[4], wlo2[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) split_tf32_pair(w2[i], whi2[i], wlo2[i]);
       // The raw stage goes back to the TMA producer only when every value loaded from it has been
       // used: a shared-memory load completes asynchronously and the hardware only waits for it at
       // the first instruction that reads its result.  (With the arrive placed directly behind the
       // loads, k-block it+2 was seen overwriting rows of k-block it that were still being read.)
       // The empty asm statements keep the arithmetic above from being moved below the arrive.
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        if (kPoint) asm volatile("" : "+f"(c[i]));
-        else asm volatile("" : "+f"(c[i]), "+f"(r[i]));
+      for (int i = 0; i < 8; ++i) {
+        if (kPoint) asm volatile("" : "+l"(c2[i]));
+        else asm volatile("" : "+l"(c2[i]), "+l"(r2[i]));
       }
 #pragma unroll
-      for (int i = 0; i < 8; ++i) asm volatile("" : "+r"(whi[i]), "+r"(wlo[i]));
+      for (int i = 0; i < 4; ++i) asm volatile("" : "+l"(whi2[i]), "+l"(wlo2[i]));
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_raw_empty + 8 * g);
       if (it >= 2) {
@@ -637,12 +636,22 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
         const uint32_t a_cols = tmem_base + lane_addr + kABase + (uint32_t)g * 128u + (uint32_t)half * 16u;
         uint32_t hi[16], lo[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) split_tf32(c[i], hi[i], lo[i]);
+        for (int i = 0; i < 8; ++i) {
+          uint64_t h2, l2;
+          split_tf32_pair(c2[i], h2, l2);
+          hi[2 * i] = (uint32_t)h2; hi[2 * i + 1] = (uint32_t)(h2 >> 32);
+          lo[2 * i] = (uint32_t)l2; lo[2 * i + 1] = (uint32_t)(l2 >> 32);
+        }
         tmem_st16(a_cols + 0, hi);
         tmem_st16(a_cols + 32, lo);
         if (!kPoint) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) split_tf32(r[i], hi[i], lo[i]);
+          for (int i = 0; i < 8; ++i) {
+            uint64_t h2, l2;
+            split_tf32_pair(r2[i], h2, l2);
+            hi[2 * i] = (uint32_t)h2; hi[2 * i + 1] = (uint32_t)(h2 >> 32);
+            lo[2 * i] = (uint32_t)l2; lo[2 * i + 1] = (uint32_t)(l2 >> 32);
+          }
           tmem_st16(a_cols + 64, hi);
           tmem_st16(a_cols + 96, lo);
         }
@@ -651,12 +660,12 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
         for (int q = 0; q < 2; ++q) {
           const uint32_t off = swz(wrow, wchunk + q);
           // |w| = sgn(w) * (hi + lo); hi and lo both carry the sign of w (lo may be zero)
-          const uint32_t m = 0x7fffffffu;
-          *reinterpret_cast<uint4*>(pl + 0 * kWTileBytes + off) = make_uint4(whi[q * 4], whi[q * 4 + 1], whi[q * 4 + 2], whi[q * 4 + 3]);
-          *reinterpret_cast<uint4*>(pl + 1 * kWTileBytes + off) = make_uint4(wlo[q * 4], wlo[q * 4 + 1], wlo[q * 4 + 2], wlo[q * 4 + 3]);
+          const uint64_t m = 0x7fffffff7fffffffull;
+          *reinterpret_cast<ulonglong2*>(pl + 0 * kWTileBytes + off) = make_ulonglong2(whi2[2 * q], whi2[2 * q + 1]);
+          *reinterpret_cast<ulonglong2*>(pl + 1 * kWTileBytes + off) = make_ulonglong2(wlo2[2 * q], wlo2[2 * q + 1]);
           if (!kPoint) {
-            *reinterpret_cast<uint4*>(pl + 2 * kWTileBytes + off) = make_uint4(whi[q * 4] & m, whi[q * 4 + 1] & m, whi[q * 4 + 2] & m, whi[q * 4 + 3] & m);
-            *reinterpret_cast<uint4*>(pl + 3 * kWTileBytes + off) = make_uint4(wlo[q * 4] & m, wlo[q * 4 + 1] & m, wlo[q * 4 + 2] & m, wlo[q * 4 + 3] & m);
+            *reinterpret_cast<ulonglong2*>(pl + 2 * kWTileBytes + off) = make_ulonglong2(whi2[2 * q] & m, whi2[2 * q + 1] & m);
+            *reinterpret_cast<ulonglong2*>(pl + 3 * kWTileBytes + off) = make_ulonglong2(wlo2[2 * q] & m, wlo2[2 * q + 1] & m);
           }
         }
       }

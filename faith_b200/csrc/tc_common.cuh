@@ -205,6 +205,32 @@ __device__ __forceinline__ void split_tf32(float v, uint32_t& hi, uint32_t& lo) 
   lo = __float_as_uint(fsub(v, __uint_as_float(hi)));
 }
 
+// Two fp32 values in one 64-bit register (element 0 in the low half) and the packed arithmetic of sm_100: each
+// half is rounded to nearest exactly as the scalar instruction rounds it.
+constexpr uint64_t kHalf2 = 0x3f0000003f000000ull;        // {0.5f, 0.5f}
+constexpr uint64_t kMinusHalf2 = 0xbf000000bf000000ull;   // {-0.5f, -0.5f}
+constexpr uint64_t kOne2 = 0x3f8000003f800000ull;         // {1.0f, 1.0f}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+// split_tf32 of both halves
+__device__ __forceinline__ void split_tf32_pair(uint64_t v, uint64_t& hi, uint64_t& lo) {
+  hi = v & 0xffffe000ffffe000ull;
+  lo = sub2(v, hi);
+}
+
 // Byte offset of (row, 16-byte chunk) inside a 128-row x 128-byte tile with the 128-byte swizzle
 // (chunk index XOR row mod 8); tiles are 1024-byte aligned.
 __device__ __forceinline__ uint32_t swz(int row, int chunk) { return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4)); }
