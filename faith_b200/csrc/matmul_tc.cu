@@ -450,36 +450,39 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
           if (lane == 0) mbar_arrive(bar_acc_free);
         }
         uint8_t* so = base_ptr + SharedLayout::out() + (uint32_t)(cq >> 2) * kOutBoxBytes;
+        // (pairs of fp32 values per instruction, as in the converters; the order of the additions is that of the
+        // scalar form: (y_c -/+ y_r) + bias + residual, each rounded to nearest)
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
-          float lo[4], up[4];
+          uint64_t lo2[2], up2[2];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float yc = fadd(__uint_as_float(t0[q * 4 + i]), __uint_as_float(t1[q * 4 + i]));
+          for (int i = 0; i < 2; ++i) {
+            const int k = q * 4 + 2 * i;
+            const uint64_t yc = add2(pack2(t0[k], t0[k + 1]), pack2(t1[k], t1[k + 1]));
             if (kPoint) {
-              lo[i] = yc;
-              up[i] = yc;
+              lo2[i] = yc;
+              up2[i] = yc;
             } else {
-              const float yr = fadd(__uint_as_float(t2[q * 4 + i]), __uint_as_float(t3[q * 4 + i]));
-              lo[i] = fsub(yc, yr);
-              up[i] = fadd(yc, yr);
+              const uint64_t yr = add2(pack2(t2[k], t2[k + 1]), pack2(t3[k], t3[k + 1]));
+              lo2[i] = sub2(yc, yr);
+              up2[i] = add2(yc, yr);
             }
             if (tbias != nullptr) {
-              const int n = nx + ncol + q * 4 + i;
-              const float bv = n < N ? tbias[n] : 0.f;
-              lo[i] = fadd(lo[i], bv);
-              up[i] = fadd(up[i], bv);
+              const int n = nx + ncol + k;   // even, and N is a multiple of four: n and n + 1 are inside or outside together
+              const uint64_t bv = n < N ? pack2(__float_as_uint(tbias[n]), __float_as_uint(tbias[n + 1])) : 0ull;
+              lo2[i] = add2(lo2[i], bv);
+              up2[i] = add2(up2[i], bv);
             }
           }
           const uint32_t off = swz(row, (cq & 3) * 2 + q);
           if (kResid) {
-            const float4 rl = *reinterpret_cast<const float4*>(so + off);
-            const float4 ru = *reinterpret_cast<const float4*>(so + 2 * kOutBoxBytes + off);
-            lo[0] = fadd(lo[0], rl.x); lo[1] = fadd(lo[1], rl.y); lo[2] = fadd(lo[2], rl.z); lo[3] = fadd(lo[3], rl.w);
-            up[0] = fadd(up[0], ru.x); up[1] = fadd(up[1], ru.y); up[2] = fadd(up[2], ru.z); up[3] = fadd(up[3], ru.w);
+            const ulonglong2 rl = *reinterpret_cast<const ulonglong2*>(so + off);
+            const ulonglong2 ru = *reinterpret_cast<const ulonglong2*>(so + 2 * kOutBoxBytes + off);
+            lo2[0] = add2(lo2[0], rl.x); lo2[1] = add2(lo2[1], rl.y);
+            up2[0] = add2(up2[0], ru.x); up2[1] = add2(up2[1], ru.y);
           }
-          *reinterpret_cast<float4*>(so + off) = make_float4(lo[0], lo[1], lo[2], lo[3]);
-          *reinterpret_cast<float4*>(so + 2 * kOutBoxBytes + off) = make_float4(up[0], up[1], up[2], up[3]);
+          *reinterpret_cast<ulonglong2*>(so + off) = make_ulonglong2(lo2[0], lo2[1]);
+          *reinterpret_cast<ulonglong2*>(so + 2 * kOutBoxBytes + off) = make_ulonglong2(up2[0], up2[1]);
         }
       }
       fence_async_smem();

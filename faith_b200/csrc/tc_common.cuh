@@ -225,6 +225,16 @@ __device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b) {
   asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
 }
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t pack2(uint32_t e0, uint32_t e1) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(e0), "r"(e1));
+  return d;
+}
 // split_tf32 of both halves
 __device__ __forceinline__ void split_tf32_pair(uint64_t v, uint64_t& hi, uint64_t& lo) {
   hi = v & 0xffffe000ffffe000ull;
