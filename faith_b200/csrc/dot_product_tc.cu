@@ -235,11 +235,14 @@ dot_weight_tc(const __grid_constant__ CUtensorMap tm_xl, const __grid_constant__
           tmem_ld16(tmem_base + lane_addr + kDtQ + 16 * h, tq);
           tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float pv = __uint_as_float(tp[i]), qv = __uint_as_float(tq[i]);
+          for (int i = 0; i < 16; i += 2) {
+            const uint64_t pv = pack2(tp[i], tp[i + 1]), qv = pack2(tq[i], tq[i + 1]);
+            const uint64_t d = sub2(pv, qv), a = add2(pv, qv);
             const int r = (16 * h + i) * 4 + m;
-            T[r * kDtTStride + j] = fsub(pv, qv);
-            T[128 * kDtTStride + r * kDtTStride + j] = fadd(pv, qv);
+            T[r * kDtTStride + j] = __uint_as_float((uint32_t)d);
+            T[(r + 4) * kDtTStride + j] = __uint_as_float((uint32_t)(d >> 32));
+            T[128 * kDtTStride + r * kDtTStride + j] = __uint_as_float((uint32_t)a);
+            T[128 * kDtTStride + (r + 4) * kDtTStride + j] = __uint_as_float((uint32_t)(a >> 32));
           }
         }
       }
@@ -250,7 +253,8 @@ dot_weight_tc(const __grid_constant__ CUtensorMap tm_xl, const __grid_constant__
       // written only after every thread has read its row of the buffer.
 #pragma unroll
       for (int side = 0; side < 2; ++side) {
-        float z[32];
+        uint64_t z2[16];
+        const uint64_t scale2 = pack2(__float_as_uint(out_scale), __float_as_uint(out_scale));
         const float* Ts = T + side * 128 * kDtTStride + row * kDtTStride;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -266,14 +270,14 @@ dot_weight_tc(const __grid_constant__ CUtensorMap tm_xl, const __grid_constant__
           }
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            const float4 tv = *reinterpret_cast<const float4*>(Ts + 16 * h + 4 * q);
-            const float t4[4] = {tv.x, tv.y, tv.z, tv.w};
+            const ulonglong2 tv = *reinterpret_cast<const ulonglong2*>(Ts + 16 * h + 4 * q);
+            const uint64_t t2[2] = {tv.x, tv.y};
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int i = 4 * q + e;
-              const float cv = __uint_as_float(cc[i]), rv = __uint_as_float(rr[i]);
-              const float xv = side == 0 ? fsub(cv, rv) : fadd(cv, rv);
-              z[16 * h + i] = fmul(fadd(xv, t4[e]), out_scale);
+            for (int e = 0; e < 2; ++e) {
+              const int i = 4 * q + 2 * e;
+              const uint64_t cv = pack2(cc[i], cc[i + 1]), rv = pack2(rr[i], rr[i + 1]);
+              const uint64_t xv = side == 0 ? sub2(cv, rv) : add2(cv, rv);
+              z2[(16 * h + i) >> 1] = mul2(add2(xv, t2[e]), scale2);
             }
           }
         }
@@ -282,7 +286,7 @@ dot_weight_tc(const __grid_constant__ CUtensorMap tm_xl, const __grid_constant__
         uint8_t* so = base_ptr + kDtOffT + side * kDtTBytes;
 #pragma unroll
         for (int q = 0; q < 8; ++q)
-          *reinterpret_cast<float4*>(so + swz(row, q)) = make_float4(z[4 * q], z[4 * q + 1], z[4 * q + 2], z[4 * q + 3]);
+          *reinterpret_cast<ulonglong2*>(so + swz(row, q)) = make_ulonglong2(z2[2 * q], z2[2 * q + 1]);
       }
       if (!ok) break;
       fence_async_smem();
@@ -313,32 +317,35 @@ dot_weight_tc(const __grid_constant__ CUtensorMap tm_xl, const __grid_constant__
       const uint8_t* raw = base_ptr + s * kDtRawStage;
       const uint8_t* tl = raw + (grp == 0 ? kDtRawXl : kDtRawYl);
       const uint8_t* tu = raw + (grp == 0 ? kDtRawXu : kDtRawYu);
-      float c[16], r[16];
+      // (arithmetic on pairs of fp32 values, fma / mul / sub .f32x2: each half rounded as the scalar instruction rounds it)
+      uint64_t c2[8], r2[8];
       if (grp == 1 && y_kmajor) {
         // y given as [b, k, m, j] (the value tensor as the projection writes it): the tile is
         // [k][m][j]; this thread's row (j, m) is gathered element by element
         const int j = row >> 2, m = row & 3;
 #pragma unroll
-        for (int kk = 0; kk < 16; ++kk) {
+        for (int kk = 0; kk < 16; kk += 2) {
           const int k = half * 16 + kk;
-          const uint32_t off = swz(k * 4 + m, j >> 2) + (uint32_t)(j & 3) * 4u;
-          const float lo = *reinterpret_cast<const float*>(tl + off), up = *reinterpret_cast<const float*>(tu + off);
-          const float hu = fmul(up, 0.5f);
-          c[kk] = __fmaf_rn(lo, 0.5f, hu);
-          r[kk] = __fmaf_rn(lo, -0.5f, hu);
+          const uint32_t off0 = swz(k * 4 + m, j >> 2) + (uint32_t)(j & 3) * 4u;
+          const uint32_t off1 = swz((k + 1) * 4 + m, j >> 2) + (uint32_t)(j & 3) * 4u;
+          const uint64_t lo = pack2(*reinterpret_cast<const uint32_t*>(tl + off0), *reinterpret_cast<const uint32_t*>(tl + off1));
+          const uint64_t up = pack2(*reinterpret_cast<const uint32_t*>(tu + off0), *reinterpret_cast<const uint32_t*>(tu + off1));
+          const uint64_t hu = mul2(up, kHalf2);
+          c2[kk >> 1] = fma2(lo, kHalf2, hu);
+          r2[kk >> 1] = fma2(lo, kMinusHalf2, hu);
         }
       } else {
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const uint32_t off = swz(row, half * 4 + q);
-          const float4 vl = *reinterpret_cast<const float4*>(tl + off);
-          const float4 vu = *reinterpret_cast<const float4*>(tu + off);
-          const float l4[4] = {vl.x, vl.y, vl.z, vl.w}, u4[4] = {vu.x, vu.y, vu.z, vu.w};
+          const ulonglong2 vl = *reinterpret_cast<const ulonglong2*>(tl + off);
+          const ulonglong2 vu = *reinterpret_cast<const ulonglong2*>(tu + off);
+          const uint64_t l2[2] = {vl.x, vl.y}, u2[2] = {vu.x, vu.y};
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float hu = fmul(u4[i], 0.5f);
-            c[q * 4 + i] = __fmaf_rn(l4[i], 0.5f, hu);
-            r[q * 4 + i] = __fmaf_rn(l4[i], -0.5f, hu);
+          for (int i = 0; i < 2; ++i) {
+            const uint64_t hu = mul2(u2[i], kHalf2);
+            c2[q * 2 + i] = fma2(l2[i], kHalf2, hu);
+            r2[q * 2 + i] = fma2(l2[i], kMinusHalf2, hu);
           }
         }
       }
@@ -353,15 +360,19 @@ dot_weight_tc(const __grid_constant__ CUtensorMap tm_xl, const __grid_constant__
         const int id = gt * nch + q;
         roff[q] = swz(id >> 3, id & 7);
         if (q < nch) {
-          const float4 v = *reinterpret_cast<const float4*>(rsrc + roff[q]);
-          const float v4[4] = {v.x, v.y, v.z, v.w};
+          const ulonglong2 v = *reinterpret_cast<const ulonglong2*>(rsrc + roff[q]);
+          const uint64_t v2[2] = {v.x, v.y};
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint32_t hi, lo;
-            split_tf32(v4[i], hi, lo);
-            blo[q * 4 + i] = lo;
-            bah[q * 4 + i] = hi & 0x7fffffffu;    // |v| = sgn(v) (hi + lo); hi and lo carry the sign of v
-            bal[q * 4 + i] = lo & 0x7fffffffu;
+          for (int i = 0; i < 2; ++i) {
+            uint64_t hi, lo;
+            split_tf32_pair(v2[i], hi, lo);
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const uint32_t h = (uint32_t)(hi >> (32 * e)), l = (uint32_t)(lo >> (32 * e));
+              blo[q * 4 + 2 * i + e] = l;
+              bah[q * 4 + 2 * i + e] = h & 0x7fffffffu;    // |v| = sgn(v) (hi + lo); hi and lo carry the sign of v
+              bal[q * 4 + 2 * i + e] = l & 0x7fffffffu;
+            }
           }
         } else {
 #pragma unroll
@@ -372,7 +383,7 @@ dot_weight_tc(const __grid_constant__ CUtensorMap tm_xl, const __grid_constant__
       // (a shared-memory load completes asynchronously); the empty asm statements keep the arithmetic
       // above from being moved below the arrive.
 #pragma unroll
-      for (int i = 0; i < 16; ++i) asm volatile("" : "+f"(c[i]), "+f"(r[i]));
+      for (int i = 0; i < 8; ++i) asm volatile("" : "+l"(c2[i]), "+l"(r2[i]));
 #pragma unroll
       for (int i = 0; i < 8; ++i) asm volatile("" : "+r"(blo[i]), "+r"(bah[i]), "+r"(bal[i]));
       __syncwarp();
@@ -387,11 +398,21 @@ dot_weight_tc(const __grid_constant__ CUtensorMap tm_xl, const __grid_constant__
         const uint32_t a_cols = tmem_base + lane_addr + kDtA + (uint32_t)grp * 128u + (uint32_t)half * 16u;
         uint32_t hi[16], lo[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) split_tf32(c[i], hi[i], lo[i]);
+        for (int i = 0; i < 8; ++i) {
+          uint64_t h2, l2;
+          split_tf32_pair(c2[i], h2, l2);
+          hi[2 * i] = (uint32_t)h2; hi[2 * i + 1] = (uint32_t)(h2 >> 32);
+          lo[2 * i] = (uint32_t)l2; lo[2 * i + 1] = (uint32_t)(l2 >> 32);
+        }
         tmem_st16(a_cols + 0, hi);
         tmem_st16(a_cols + 32, lo);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) split_tf32(r[i], hi[i], lo[i]);
+        for (int i = 0; i < 8; ++i) {
+          uint64_t h2, l2;
+          split_tf32_pair(r2[i], h2, l2);
+          hi[2 * i] = (uint32_t)h2; hi[2 * i + 1] = (uint32_t)(h2 >> 32);
+          lo[2 * i] = (uint32_t)l2; lo[2 * i + 1] = (uint32_t)(l2 >> 32);
+        }
         tmem_st16(a_cols + 64, hi);
         tmem_st16(a_cols + 96, lo);
         uint8_t* pl = base_ptr + kDtOffPlanes;
