@@ -899,3 +899,34 @@ def test_bias_rows_in_the_grid_of_the_weight_rows_bit_for_bit(S, monkeypatch):
         for k, (a, b) in enumerate(zip(run_all(), merged)):
             assert torch.equal(a, b), k
     assert _lib.load().fb_tc_check() == 0
+
+
+def test_bias_rows_in_the_grid_with_a_ragged_last_tile_of_weight_rows(monkeypatch):
+    """Weight rows that do not fill their last 128-row tile (288 x 50 rows = 112.5 tiles): the bias rows start at a
+    tile of their own behind it; plain product and product with residual, merged and separate launches bit for bit,
+    and both against the fp64 statement of the split-sign product."""
+    from faith_b200 import ops
+    S, L, Di, D, F = 9, 32, 50, 64, 96
+    lw, lb, uw, ub = [v.to(DEV) for v in cases.rand_bounds(921, S, L, Di, D, -0.4, 0.6)]
+    r = [v.to(DEV) for v in cases.rand_bounds(922, S, L, Di, F)]
+    res = (r[0], r[2], r[1], r[3])
+    g = torch.Generator().manual_seed(16)
+    W = (torch.randn(F, D, generator=g) / math.sqrt(D)).to(DEV)
+    bias = (torch.randn(F, generator=g) * 0.1).to(DEV)
+
+    def run_all():
+        out = list(ops.matmul(lw, uw, lb, ub, W, bias)) + list(ops.matmul_residual(lw, uw, lb, ub, W, bias, res))
+        torch.cuda.synchronize()
+        return out
+    monkeypatch.setenv("FB_TC_SEPARATE_BIAS_ROWS", "1")
+    separate = run_all()
+    monkeypatch.delenv("FB_TC_SEPARATE_BIAS_ROWS")
+    merged = run_all()
+    for k, (a, b) in enumerate(zip(merged, separate)):
+        assert torch.equal(a, b), k
+    Wp, Wn = W.double().clamp(min=0).t(), W.double().clamp(max=0).t()
+    ref = [lw.double() @ Wp + uw.double() @ Wn, uw.double() @ Wp + lw.double() @ Wn,
+           lb.double() @ Wp + ub.double() @ Wn + bias.double(), ub.double() @ Wp + lb.double() @ Wn + bias.double()]
+    for k in range(4):
+        assert float((merged[k].double() - ref[k]).abs().max()) < 2e-5, k
+        assert float((merged[4 + k].double() - ref[k] - res[k].double()).abs().max()) < 2e-5, k
