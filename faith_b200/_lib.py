@@ -55,6 +55,7 @@ SIGNATURES = {
     "fb_dot_product_f32": [_P] * 16 + [_I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P],
     "fb_matmul_heads_f32": [_P] * 10 + [_L, _I, _I, _I, _I, _I, _P],
     "fb_matmul_residual_f32": [_P] * 16 + [_L, _I, _I, _I, _P],
+    "fb_matmul_residual_ln_f32": [_P] * 20 + [_L, _I, _I, _I, _P],
     "fb_matmul_heads_ranges_f32": [_P] * 13 + [_L, _I, _I, _I, _I, _I, _I, _I, _F, _P],
     "fb_relax_coef_f32": [_I] + [_P] * 8 + [_L, _I, _I, _I, _I, _F, _P, _P],
     "fb_relax_coef_given_f32": [_I] + [_P] * 8 + [_L, _I, _P, _P],

@@ -64,6 +64,18 @@ struct TcBiasRows {
   const float* res_up;
 };
 
+// Layer norm (mode no_var) applied by the epilogue of a product with residual: gain and shift [N], the weight itself
+// (its column means give the row means of the product), the row sums of the residual as its producer left them and
+// those of the result for the next consumer: [2 lines][4 partial sums][rs_stride rows], weight rows first, then bias rows.
+struct TcLnArgs {
+  const float* gamma;
+  const float* beta;
+  const float* w_raw;
+  const float* rs_in;
+  float* rs_out;
+  int64_t rs_stride;
+};
+
 // Opts `kernel` in to `bytes` of dynamic shared memory on the current device (nothing to do up to 48 KB, or when it
 // already has that much): FB_OK or FB_ERR_CUDA.
 int ensure_dynamic_smem_impl(const void* func, size_t bytes);

@@ -12,7 +12,8 @@ int launch_split_sign_tc(const float* a_lo, const float* a_up, const float* W, c
                          float* c_up, int64_t M, int N, int K, cudaStream_t st, int split_rows, int split_d,
                          const float* coef_l = nullptr, const float* coef_u = nullptr, int coef_di = 1,
                          float* norm_lo = nullptr, float* norm_up = nullptr, int norm_p = 0,
-                         const float* res_lo = nullptr, const float* res_up = nullptr, const TcBiasRows* br = nullptr);
+                         const float* res_lo = nullptr, const float* res_up = nullptr, const TcBiasRows* br = nullptr,
+                         const TcLnArgs* ln = nullptr);
 bool tc_bias_rows_mergeable(const float* a_lo, const float* a_up, const float* b_lo, const float* b_up, const float* W,
                             const float* cb_lo, const float* cb_up, int64_t Mb, int N, int K, bool with_norms);
 int launch_split_sign_ffma(const float* a_lo, const float* a_up, const float* W, const float* bias, float* c_lo,
@@ -271,4 +272,45 @@ extern "C" int fb_matmul_residual_f32(const float* x_lw, const float* x_uw, cons
   if (rc != FB_OK || merged) return rc;
   return fb::launch_split_sign_tc(x_lb, x_ub, W, bias, y_lb, y_ub, rows, Dy, Do, st, 0, 0, nullptr, nullptr, 1, nullptr,
                                   nullptr, 0, r_lb, r_ub);
+}
+
+// fb_matmul_residual_f32 followed by the layer norm of the encoder blocks (mode no_var, Bounds.layer_norm,
+// Bounds.py:1111-1131), applied by the GEMM epilogue before the store: z = layer_norm(matmul(x, W) + bias + r).  The
+// row means the norm needs are not taken from the result (a tile holds half of a row): those of the product come
+// from the operand and the column means of W, those of the residual from r_rowsum, which the producer of r left
+// behind, and z_rowsum receives those of z for the next product that takes z as its residual.  Row sums:
+// [2 lines][4 partial sums][rows * (Di + 1)] floats, weight rows first, then the bias rows; a reader adds the four
+// partial sums of a line in order (a producer that has whole rows writes the sum into the first and zeros into the
+// others).  The means are rounded in a different order than fb_layernorm_novar_f32 rounds them, so the result equals
+// the separate operators to rounding, not bit for bit.  Dy == 128, Do a multiple of 64 up to 512, Di a multiple of
+// 128 / gcd and tensor-core shapes with at least 256 bias rows only; otherwise FB_ERR_SHAPE and nothing is launched.
+extern "C" int fb_matmul_residual_ln_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+                                         const float* c_l, const float* c_u, const float* W, const float* bias,
+                                         const float* r_lw, const float* r_uw, const float* r_lb, const float* r_ub,
+                                         const float* r_rowsum, const float* gamma, const float* beta,
+                                         float* z_lw, float* z_uw, float* z_lb, float* z_ub, float* z_rowsum,
+                                         int64_t rows, int Di, int Do, int Dy, void* stream) {
+  if (!x_lw || !x_uw || !x_lb || !x_ub || !W || !r_lw || !r_uw || !r_lb || !r_ub || !r_rowsum || !gamma || !beta || !z_lw ||
+      !z_uw || !z_lb || !z_ub || !z_rowsum)
+    return FB_ERR_ARG;
+  if ((c_l == nullptr) != (c_u == nullptr)) return FB_ERR_ARG;
+  if (rows < 0 || Di <= 0 || Do <= 0 || Dy <= 0) return FB_ERR_ARG;
+  if (z_lw == r_lw || z_lw == r_uw || z_uw == r_lw || z_uw == r_uw || z_lb == r_lb || z_lb == r_ub || z_ub == r_lb ||
+      z_ub == r_ub || z_rowsum == r_rowsum)
+    return FB_ERR_ARG;
+  const int64_t M = rows * (int64_t)Di;
+  if (!fb::use_tensor_cores() || Dy != 128 || Do % 64 != 0 || Do > 512 || M % 128 != 0 ||
+      !fb::tc_gemm_supported(x_lw, x_uw, W, z_lw, z_uw, M, Dy, Do) ||
+      !fb::tc_bias_rows_mergeable(x_lw, x_uw, x_lb, x_ub, W, z_lb, z_ub, rows, Dy, Do, false) || !fb::aligned16(r_lw) ||
+      !fb::aligned16(r_uw) || !fb::aligned16(r_lb) || !fb::aligned16(r_ub))
+    return FB_ERR_SHAPE;
+  if (c_l != nullptr && (Di % 128 != 0 || !fb::aligned16(c_l) || !fb::aligned16(c_u))) return FB_ERR_SHAPE;
+  if (rows == 0) return FB_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const double Mt = (double)rows * (Di + 1);
+  fb::ProfileScope prof(fb::PK_MATMUL, 8.0 * Mt * Do * Dy, 4.0 * (2 * Mt * Do + 4 * Mt * Dy + (double)Do * Dy + Dy), stream);
+  const fb::TcBiasRows br = {x_lb, x_ub, bias, z_lb, z_ub, rows, r_lb, r_ub};
+  const fb::TcLnArgs ln = {gamma, beta, W, r_rowsum, z_rowsum, M + rows};
+  return fb::launch_split_sign_tc(x_lw, x_uw, W, nullptr, z_lw, z_uw, M, Dy, Do, st, 0, 0, c_l, c_u, Di, nullptr, nullptr, 0,
+                                  r_lw, r_uw, &br, &ln);
 }

@@ -78,6 +78,12 @@ constexpr uint32_t kOutStageBytes = 4 * kOutBoxBytes;    // lower and upper outp
 constexpr uint32_t kSmemBytes = kRawStages * kRawStageBytes + 2 * kPlaneStageBytes + kOutStageBytes + 1024 /*align*/ + 256 /*barriers*/ +
                                 kLiveWords * 4 /*live-tile bitmap*/;
 constexpr uint32_t kTmemCols = 512;
+// Extra shared memory of the instantiations that apply the layer norm in the epilogue (kLN), behind the live-tile bitmap:
+// column means of W and |W| [512 + 512], gain split by sign [128 + 128], shift [128], mean of the layer bias [4], and the
+// row means handed from the converters to the epilogue, [2 tiles][4 partial sums][128 rows] x (centre, radius).
+constexpr uint32_t kLnOffWbar = 0, kLnOffAbar = 2048, kLnOffGp = 4096, kLnOffGn = 4608, kLnOffBeta = 5120, kLnOffBiasMean = 5632,
+                   kLnOffMu = 5648, kLnSmemBytes = 5648 + 2 * 4 * 128 * 8;
+constexpr int kLnMaxK = 512, kLnN = 128;
 constexpr uint32_t kAccC = 0, kAccR = 64, kCorC = 128, kCorR = 192, kABase = 256;  // TMEM column map
 
 
@@ -151,10 +157,19 @@ struct SharedLayout {
 // (tm_b_*, tm_bout_*, tm_bres_*), the layer bias bias_b added, plain store, no slopes and no column norms.  Every tile is
 // computed exactly as a launch of its own would compute it.  main_tiles == total_tiles: no such tiles.
 //
+// kLN (with kResid, N = 128, bias rows in the same grid): the layer norm that follows the product (mode no_var,
+// Bounds.py:1111-1131: lw - mean(uw), uw - mean(lw) over the features, then the gain with its sign split, the shift
+// on the bias rows) is applied before the store.  A tile holds 64 of the 128 features of a row, so the row means
+// come from elsewhere: the mean over n of (x W^T)[r, n] is x[r, :] . mean_n W[n, :], which the converters accumulate from
+// the centres and radii they hold anyway (column means of W and |W| in shared memory; four partial sums per row, added
+// by the epilogue in a fixed order); the row sums of the residual were left behind by whoever wrote it (ln_args.rs_in:
+// [2 lines][4 partial sums][rows of the bound, weight rows first]), and this launch leaves those of its own result in
+// ln_args.rs_out for the next one.
+//
 // status: device word of the caller (may be null); bit 2 is set when a bounded wait of this launch expired.
 // wait_tries: bound of every mbarrier wait in tries of ~20 us.  skip_it >= 0 makes the producer of CTA 0 leave
 // out the loads of that k-block: the self-test of the give-up path (fb_tc_selftest_timeout), never set otherwise.
-template <bool kCoef, bool kNorm, bool kResid, bool kPoint>
+template <bool kCoef, bool kNorm, bool kResid, bool kPoint, bool kLN>
 __global__ void __launch_bounds__(kThreads, 1)
 split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_constant__ CUtensorMap tm_up,
                    const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_out_lo,
@@ -167,7 +182,8 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
                    int n_tiles_n, int64_t total_tiles, int split_rows, int split_d,
                    const float* __restrict__ coef_l, const float* __restrict__ coef_u, int coef_di,
                    float* __restrict__ norm_lo, float* __restrict__ norm_up, int norm_p,
-                   int* __restrict__ status, uint32_t wait_tries, int skip_it, const LiveRows live_rows, int same_out) {
+                   int* __restrict__ status, uint32_t wait_tries, int skip_it, const LiveRows live_rows, int same_out,
+                   const TcLnArgs ln_args, int64_t Mb) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -195,6 +211,7 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
   const uint32_t bar_acc_free = bar0 + 104;
   const uint32_t bar_conv = bar0 + 128;          // rendezvous of the converter warps in the epilogue (bounded, unlike bar.sync)
   const uint32_t bar_res = bar0 + 136;           // residual tile has landed in the staging buffer (kResid)
+  const uint32_t bar_mu = bar0 + 144;            // [2] row means of a tile are in shared memory (kLN)
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + SharedLayout::bars() + 112);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(base_ptr + SharedLayout::bars() + 120);
 
@@ -240,8 +257,37 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
     mbar_init(bar_acc_free, kEpiWarps);
     mbar_init(bar_conv, kEpiWarps);
     mbar_init(bar_res, 1);
+    mbar_init(bar_mu, kConvWarps);
+    mbar_init(bar_mu + 8, kConvWarps);
     *cta_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  float* const ln_smem = reinterpret_cast<float*>(base_ptr + SharedLayout::bars() + 256 + kLiveWords * 4);
+  if (kLN) {
+    // column means of W and |W| (terms added in the order of n), the gain split by sign as the layer-norm kernel splits it
+    const float inv_n = 1.0f / (float)N;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) {
+      float sw = 0.f, sa = 0.f;
+      for (int n = 0; n < N; ++n) {
+        const float w = __ldg(ln_args.w_raw + (size_t)n * K + k);
+        sw = fmaf(w, inv_n, sw);
+        sa = fmaf(fabsf(w), inv_n, sa);
+      }
+      ln_smem[kLnOffWbar / 4 + k] = sw;
+      ln_smem[kLnOffAbar / 4 + k] = sa;
+    }
+    for (int n = threadIdx.x; n < N; n += blockDim.x) {
+      const float gv = __ldg(ln_args.gamma + n);
+      const float gpv = gv > 0.f ? gv : 0.f;
+      ln_smem[kLnOffGp / 4 + n] = gpv;
+      ln_smem[kLnOffGn / 4 + n] = fsub(gv, gpv);
+      ln_smem[kLnOffBeta / 4 + n] = __ldg(ln_args.beta + n);
+    }
+    if (threadIdx.x == 0) {
+      float sb = 0.f;
+      for (int n = 0; n < N && bias_b != nullptr; ++n) sb = fmaf(__ldg(bias_b + n), inv_n, sb);
+      ln_smem[kLnOffBiasMean / 4] = sb;
+    }
   }
   if (warp == 1) {  // one warp allocates all of tensor memory for this CTA
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
@@ -432,6 +478,35 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
         ok = mbar_wait_warp(bar_res, (uint32_t)(e & 1), wc);
         if (!ok) break;
       }
+      // kLN: the means over all 128 features of this thread's row of y_lw and of y_uw (product + bias + residual)
+      uint64_t mlo2 = 0, mup2 = 0, sl2 = 0, su2 = 0;   // the means as pairs; running sums of the normalised row
+      int64_t grow = 0;                                // row of the bound: weight rows first, then the bias rows
+      bool rvalid = false;
+      if (kLN) {
+        ok = mbar_wait_warp(bar_mu + 8 * (e & 1), (uint32_t)((e >> 1) & 1), wc);
+        if (!ok) break;
+        const float2* mu = reinterpret_cast<const float2*>(ln_smem + kLnOffMu / 4) + ((e & 1) * 4) * 128 + row;
+        const float2 p0 = mu[0], p1 = mu[128], p2 = mu[256], p3 = mu[384];
+        const float mc = fadd(fadd(fadd(p0.x, p1.x), p2.x), p3.x), mr = fadd(fadd(fadd(p0.y, p1.y), p2.y), p3.y);
+        grow = (bseg ? M : 0) + my + row;
+        rvalid = my + row < (bseg ? Mb : M);
+        float rl = 0.f, ru = 0.f;
+        if (rvalid) {
+#pragma unroll
+          for (int sl = 0; sl < 4; ++sl) {
+            rl = fadd(rl, __ldg(ln_args.rs_in + (int64_t)sl * ln_args.rs_stride + grow));
+            ru = fadd(ru, __ldg(ln_args.rs_in + (int64_t)(4 + sl) * ln_args.rs_stride + grow));
+          }
+        }
+        const float inv_n = 1.0f / (float)N;
+        float mlo = fadd(fsub(mc, mr), fmul(rl, inv_n)), mup = fadd(fadd(mc, mr), fmul(ru, inv_n));
+        if (bseg) {
+          mlo = fadd(mlo, ln_smem[kLnOffBiasMean / 4]);
+          mup = fadd(mup, ln_smem[kLnOffBiasMean / 4]);
+        }
+        mlo2 = pack2(__float_as_uint(mlo), __float_as_uint(mlo));
+        mup2 = pack2(__float_as_uint(mup), __float_as_uint(mup));
+      }
 #pragma unroll
       for (int cq = 4 * chalf; cq < 4 * chalf + 4; ++cq) {
         const int ncol = cq * 8;
@@ -481,9 +556,36 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
             lo2[0] = add2(lo2[0], rl.x); lo2[1] = add2(lo2[1], rl.y);
             up2[0] = add2(up2[0], ru.x); up2[1] = add2(up2[1], ru.y);
           }
+          if (kLN) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              const int n = nx + ncol + q * 4 + 2 * i;
+              const uint64_t gp2 = *reinterpret_cast<const uint64_t*>(ln_smem + kLnOffGp / 4 + n);
+              const uint64_t gn2 = *reinterpret_cast<const uint64_t*>(ln_smem + kLnOffGn / 4 + n);
+              const uint64_t dl = sub2(lo2[i], mup2), du = sub2(up2[i], mlo2);   // each line minus the mean of the other
+              uint64_t zl = add2(mul2(dl, gp2), mul2(du, gn2)), zu = add2(mul2(dl, gn2), mul2(du, gp2));
+              if (bseg) {
+                const uint64_t b2 = *reinterpret_cast<const uint64_t*>(ln_smem + kLnOffBeta / 4 + n);
+                zl = add2(zl, b2);
+                zu = add2(zu, b2);
+              }
+              sl2 = add2(sl2, zl);
+              su2 = add2(su2, zu);
+              lo2[i] = zl;
+              up2[i] = zu;
+            }
+          }
           *reinterpret_cast<ulonglong2*>(so + off) = make_ulonglong2(lo2[0], lo2[1]);
           *reinterpret_cast<ulonglong2*>(so + 2 * kOutBoxBytes + off) = make_ulonglong2(up2[0], up2[1]);
         }
+      }
+      if (kLN && rvalid) {
+        // sums of this thread's row over the 32 columns it handled: partial sum (n tile, column half) of the result's row
+        const int sl = (nx / BN) * 2 + chalf;
+        ln_args.rs_out[(int64_t)sl * ln_args.rs_stride + grow] =
+            fadd(__uint_as_float((uint32_t)sl2), __uint_as_float((uint32_t)(sl2 >> 32)));
+        ln_args.rs_out[(int64_t)(4 + sl) * ln_args.rs_stride + grow] =
+            fadd(__uint_as_float((uint32_t)su2), __uint_as_float((uint32_t)(su2 >> 32)));
       }
       fence_async_smem();
       ok = epi_sync();
@@ -545,7 +647,8 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
     const int row = quarter * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     bool ok = true;
-    int c_ti = 0, c_kb = g;   // tile and k-block of `it`, kept incrementally (used by the coefficient loads)
+    int c_ti = 0, c_kb = g;   // tile and k-block of `it`, kept incrementally (used by the coefficient loads and by kLN)
+    uint64_t mc2 = 0, mr2 = 0;   // kLN: partial row means of the product, centre and radius part (pairs)
     int conv_it = total_it;   // k-blocks to convert: those of the live tiles
     if (use_live) {
       int live_tiles = 0;
@@ -559,6 +662,9 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
       // values per side are the same for every thread of the CTA; they are fetched first so that their
       // latency hides behind the wait and the shared-memory loads.
       ulonglong2 kl[4], ku[4];   // pairs of fp32 slopes
+      if (kLN && !kCoef) {
+        while (c_kb >= nkb) { c_kb -= nkb; ++c_ti; }
+      }
       if (kCoef) {
         while (c_kb >= nkb) { c_kb -= nkb; ++c_ti; }
         const int tile = blockIdx.x + c_ti * gridDim.x;
@@ -630,10 +736,36 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
       for (int i = 0; i < 4; ++i) asm volatile("" : "+l"(whi2[i]), "+l"(wlo2[i]));
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_raw_empty + 8 * g);
+      if (kLN) {
+        // this thread's share of the row means of the product: its 16 centres and radii against the column means of
+        // W and |W| (nkb is even here, so the group sees nkb / 2 k-blocks of every tile, the last one at nkb - 2 + g)
+        const ulonglong2* wq = reinterpret_cast<const ulonglong2*>(ln_smem + kLnOffWbar / 4 + c_kb * BK + half * 16);
+        const ulonglong2* aq = reinterpret_cast<const ulonglong2*>(ln_smem + kLnOffAbar / 4 + c_kb * BK + half * 16);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const ulonglong2 w = wq[q], a = aq[q];
+          mc2 = fma2(c2[2 * q], w.x, mc2);
+          mc2 = fma2(c2[2 * q + 1], w.y, mc2);
+          mr2 = fma2(r2[2 * q], a.x, mr2);
+          mr2 = fma2(r2[2 * q + 1], a.y, mr2);
+        }
+      }
       if (it >= 2) {
         ok = mbar_wait_warp(bar_mma_done + 8 * g, (uint32_t)(((it >> 1) - 1) & 1), wc);
         if (!ok) break;
         tc_fence_after();
+      }
+      if (kLN && c_kb >= nkb - 2) {
+        // Last k-block of the tile for this group: hand the partial row means to the epilogue.  Only now: the MMAs of
+        // this group's previous k-block have retired, so the tile before this one has been read out of tensor memory,
+        // which the epilogue does after it has read that tile's means; the buffer of the tile two back is free.
+        float2* mu = reinterpret_cast<float2*>(ln_smem + kLnOffMu / 4) + (((c_ti & 1) * 4 + g * 2 + half) * 128 + row);
+        *mu = make_float2(fadd(__uint_as_float((uint32_t)mc2), __uint_as_float((uint32_t)(mc2 >> 32))),
+                          fadd(__uint_as_float((uint32_t)mr2), __uint_as_float((uint32_t)(mr2 >> 32))));
+        mc2 = 0;
+        mr2 = 0;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_mu + 8 * (c_ti & 1));
       }
       {
         const uint32_t a_cols = tmem_base + lane_addr + kABase + (uint32_t)g * 128u + (uint32_t)half * 16u;
@@ -755,11 +887,15 @@ bool tc_gemm_supported(const float* a_lo, const float* a_up, const float* W, con
 int launch_split_sign_tc(const float* a_lo, const float* a_up, const float* W, const float* bias, float* c_lo,
                          float* c_up, int64_t M, int N, int K, cudaStream_t st, int split_rows, int split_d,
                          const float* coef_l, const float* coef_u, int coef_di, float* norm_lo, float* norm_up,
-                         int norm_p, const float* res_lo, const float* res_up, const TcBiasRows* br) {
+                         int norm_p, const float* res_lo, const float* res_up, const TcBiasRows* br, const TcLnArgs* ln) {
   // Bias rows in the same grid (br != nullptr): they must take the same instantiation as the weight rows (zero
   // radius or not, residual or not); the caller checks tc_bias_rows_mergeable first.
   if (br != nullptr && ((br->res_lo != nullptr) != (res_lo != nullptr) || (br->res_lo != nullptr) != (br->res_up != nullptr) ||
                         ((br->a_lo == br->a_up) != (a_lo == a_up) && norm_lo != nullptr) || br->M <= 0))
+    return FB_ERR_ARG;
+  if (ln != nullptr && (br == nullptr || res_lo == nullptr || N != kLnN || K % (2 * BK) != 0 || K > kLnMaxK || M % BM != 0 ||
+                        ln->gamma == nullptr || ln->beta == nullptr || ln->rs_in == nullptr || ln->rs_out == nullptr ||
+                        ln->rs_stride < M + br->M))
     return FB_ERR_ARG;
   if (norm_lo != nullptr && (coef_l != nullptr || norm_up == nullptr || M % BM != 0)) return FB_ERR_ARG;
   if (res_lo != nullptr && (res_up == nullptr || norm_lo != nullptr || split_rows > 0 || !aligned16(res_lo) || !aligned16(res_up)))
@@ -804,17 +940,22 @@ int launch_split_sign_tc(const float* a_lo, const float* a_up, const float* W, c
   cudaError_t attr_err = cudaSuccess;
   std::call_once(attr_once[dev & 63], [&]() {
     const int bytes = (int)kSmemBytes;
-    attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<false, false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<false, false, false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     if (attr_err == cudaSuccess)
-      attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<true, false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+      attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<true, false, false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     if (attr_err == cudaSuccess)
-      attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<false, true, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+      attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<false, true, false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     if (attr_err == cudaSuccess)
-      attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<false, false, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+      attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<false, false, true, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     if (attr_err == cudaSuccess)
-      attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<true, false, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+      attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<true, false, true, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     if (attr_err == cudaSuccess)
-      attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<false, true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+      attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<false, true, false, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    const int ln_bytes = (int)(kSmemBytes + kLnSmemBytes);
+    if (attr_err == cudaSuccess)
+      attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<false, false, true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, ln_bytes);
+    if (attr_err == cudaSuccess)
+      attr_err = cudaFuncSetAttribute(split_sign_gemm_tc<true, false, true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, ln_bytes);
   });
   FB_CUDA_OK(attr_err);
   // persistent: one CTA per SM (tensor memory and shared memory allow exactly one)
@@ -829,21 +970,33 @@ int launch_split_sign_tc(const float* a_lo, const float* a_up, const float* W, c
   if (t_live_rows.L > 0 && t_live_rows.M == M && bias == nullptr && t_live_rows.Di > 0 && t_live_rows.Di % BM == 0 &&
       t_live_rows.words >= 1 && t_live_rows.words <= 4 && M % ((int64_t)t_live_rows.Di * t_live_rows.L) == 0)
     live = t_live_rows;
+  TcLnArgs ln_args = {nullptr, nullptr, nullptr, nullptr, nullptr, 0};
+  if (ln != nullptr) {
+    ln_args = *ln;
+    ln_args.w_raw = W;
+  }
+  const int64_t Mb = br != nullptr ? br->M : 0;
+#define FB_TC_TAIL ln_args, Mb
 #define FB_TC_ARGS tm_lo, tm_up, tm_w, tm_out_lo, tm_out_up, tm_res_lo, tm_res_up, tm_b_lo, tm_b_up, tm_bout_lo, tm_bout_up, tm_bres_lo, \
                    tm_bres_up, bias, bias_b, (int)main_tiles, same_b, M, N, K, gn, total_tiles, split_rows, split_d
-  if (coef_l != nullptr && res_lo != nullptr)
-    split_sign_gemm_tc<true, false, true, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, coef_l, coef_u, coef_di, nullptr, nullptr, 0, status, tries, skip, no_live, 0);
+  if (ln != nullptr && coef_l != nullptr)
+    split_sign_gemm_tc<true, false, true, false, true><<<grid, kThreads, kSmemBytes + kLnSmemBytes, st>>>(FB_TC_ARGS, coef_l, coef_u, coef_di, nullptr, nullptr, 0, status, tries, skip, no_live, 0, FB_TC_TAIL);
+  else if (ln != nullptr)
+    split_sign_gemm_tc<false, false, true, false, true><<<grid, kThreads, kSmemBytes + kLnSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, nullptr, nullptr, 0, status, tries, skip, no_live, 0, FB_TC_TAIL);
+  else if (coef_l != nullptr && res_lo != nullptr)
+    split_sign_gemm_tc<true, false, true, false, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, coef_l, coef_u, coef_di, nullptr, nullptr, 0, status, tries, skip, no_live, 0, FB_TC_TAIL);
   else if (coef_l != nullptr)
-    split_sign_gemm_tc<true, false, false, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, coef_l, coef_u, coef_di, nullptr, nullptr, 0, status, tries, skip, no_live, 0);
+    split_sign_gemm_tc<true, false, false, false, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, coef_l, coef_u, coef_di, nullptr, nullptr, 0, status, tries, skip, no_live, 0, FB_TC_TAIL);
   else if (norm_lo != nullptr && a_lo == a_up)   // one tensor as both lines: zero radius
-    split_sign_gemm_tc<false, true, false, true><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, norm_lo, norm_up, norm_p, status, tries, skip, live, c_lo == c_up ? 1 : 0);
+    split_sign_gemm_tc<false, true, false, true, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, norm_lo, norm_up, norm_p, status, tries, skip, live, c_lo == c_up ? 1 : 0, FB_TC_TAIL);
   else if (norm_lo != nullptr)
-    split_sign_gemm_tc<false, true, false, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, norm_lo, norm_up, norm_p, status, tries, skip, no_live, 0);
+    split_sign_gemm_tc<false, true, false, false, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, norm_lo, norm_up, norm_p, status, tries, skip, no_live, 0, FB_TC_TAIL);
   else if (res_lo != nullptr)
-    split_sign_gemm_tc<false, false, true, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, nullptr, nullptr, 0, status, tries, skip, no_live, 0);
+    split_sign_gemm_tc<false, false, true, false, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, nullptr, nullptr, 0, status, tries, skip, no_live, 0, FB_TC_TAIL);
   else
-    split_sign_gemm_tc<false, false, false, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, nullptr, nullptr, 0, status, tries, skip, no_live, 0);
+    split_sign_gemm_tc<false, false, false, false, false><<<grid, kThreads, kSmemBytes, st>>>(FB_TC_ARGS, nullptr, nullptr, 1, nullptr, nullptr, 0, status, tries, skip, no_live, 0, FB_TC_TAIL);
 #undef FB_TC_ARGS
+#undef FB_TC_TAIL
   FB_LAUNCH_OK();
   return FB_OK;
 }
@@ -973,7 +1126,7 @@ extern "C" int fb_tc_selftest_timeout(const float* x_lw, const float* x_uw, cons
   int* const saved_sink = fb::t_status_sink;
   fb::t_status_sink = status;
   rc = fb::launch_split_sign_tc(x_lw, x_uw, W, nullptr, y_lw, y_uw, M, N, K, (cudaStream_t)stream, 0, 0, nullptr, nullptr, 1,
-                                nullptr, nullptr, 0, nullptr, nullptr, nullptr);
+                                nullptr, nullptr, 0, nullptr, nullptr, nullptr, nullptr);
   fb::t_status_sink = saved_sink;
   fb::g_wait_tries = fb::kMaxTries;
   fb::g_skip_it = -1;

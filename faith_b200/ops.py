@@ -125,6 +125,36 @@ def matmul_residual(lw, uw, lb, ub, W, bias, residual, c_l=None, c_u=None):
     return y_lw, y_uw, y_lb, y_ub
 
 
+def row_sums(lw, uw, lb, ub):
+    """Row sums of a bound in the form fb_matmul_residual_ln_f32 reads: [2 lines, 4 partial sums, rows * (Di + 1)], the
+    whole sum in the first partial sum (weight rows first, then the bias rows)."""
+    D = lw.shape[-1]
+    out = torch.zeros(2, 4, lw.numel() // D + lb.numel() // D, device=lw.device, dtype=torch.float32)
+    out[0, 0] = torch.cat([lw.reshape(-1, D).sum(-1), lb.reshape(-1, D).sum(-1)])
+    out[1, 0] = torch.cat([uw.reshape(-1, D).sum(-1), ub.reshape(-1, D).sum(-1)])
+    return out
+
+
+def matmul_residual_ln(lw, uw, lb, ub, W, bias, residual, residual_rowsum, gamma, beta, c_l=None, c_u=None):
+    """layer_norm(matmul(x, W) + bias + residual), mode no_var, in one launch.  Returns (z_lw, z_uw, z_lb, z_ub,
+    z_rowsum); residual_rowsum / z_rowsum as row_sums() lays them out."""
+    dev = _chk(lw, uw, lb, ub, W, bias, *residual, residual_rowsum, gamma, beta)
+    rows = lb.numel() // lb.shape[-1]
+    Di, Do = lw.shape[-2], lw.shape[-1]
+    Dy = W.shape[0]
+    z_lw = torch.empty(lw.shape[:-1] + (Dy,), device=dev, dtype=torch.float32)
+    z_uw = torch.empty_like(z_lw)
+    z_lb = torch.empty(lb.shape[:-1] + (Dy,), device=dev, dtype=torch.float32)
+    z_ub = torch.empty_like(z_lb)
+    z_rs = torch.empty(2, 4, rows * (Di + 1), device=dev, dtype=torch.float32)
+    with torch.cuda.device(dev):
+        check(load().fb_matmul_residual_ln_f32(_p(lw), _p(uw), _p(lb), _p(ub), _p(c_l), _p(c_u), _p(W), _p(bias),
+                                               *[_p(t) for t in residual], _p(residual_rowsum), _p(gamma), _p(beta),
+                                               _p(z_lw), _p(z_uw), _p(z_lb), _p(z_ub), _p(z_rs), rows, Di, Do, Dy, _stream()),
+              "fb_matmul_residual_ln_f32")
+    return z_lw, z_uw, z_lb, z_ub, z_rs
+
+
 def relax_coef_given(op, lb, ub, l, u, violation=None):
     """relax_coef for a bound whose concretised range (l, u) is already known: no pass over lw / uw."""
     dev = _chk(lb, ub, l, u)

@@ -166,6 +166,20 @@ int fb_matmul_residual_f32(const float* x_lw, const float* x_uw, const float* x_
                            float* y_lw, float* y_uw, float* y_lb, float* y_ub,
                            int64_t rows, int Di, int Do, int Dy, void* stream);
 
+/* fb_matmul_residual_f32 followed by the layer norm of the encoder blocks (mode no_var, Bounds.py:1111-1131), applied
+ * by the GEMM epilogue: z = layer_norm(matmul(x, W) + bias + r).  r_rowsum: row sums of the residual as its producer
+ * left them, z_rowsum: those of z for the next consumer; each [2 lines][4 partial sums][rows * (Di + 1)] floats (weight
+ * rows first, then the bias rows; a reader adds the four partial sums in order).  Equals the separate operators to
+ * rounding (the row means are rounded in another order).  Dy == 128, Do % 64 == 0, Do <= 512, rows * Di % 128 == 0,
+ * rows >= 256; otherwise FB_ERR_SHAPE and nothing is launched.  Replaces Bounds.matmul + Bounds.add +
+ * Bounds.layer_norm (Bounds.py:397-413, :383-395, :1111-1131). */
+int fb_matmul_residual_ln_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+                              const float* c_l, const float* c_u, const float* W, const float* bias,
+                              const float* r_lw, const float* r_uw, const float* r_lb, const float* r_ub,
+                              const float* r_rowsum, const float* gamma, const float* beta,
+                              float* z_lw, float* z_uw, float* z_lb, float* z_ub, float* z_rowsum,
+                              int64_t rows, int Di, int Do, int Dy, void* stream);
+
 /* The tensor-core kernels behind fb_matmul_f32 and fb_dot_product_f32 bound every wait inside the kernel; if a
  * wait ever expires, the kernel raises a device-side flag, frees its tensor memory and returns, leaving its
  * outputs partly written.  fb_tc_error_flag synchronises the device, returns the flag in *flag (0 = never

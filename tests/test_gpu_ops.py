@@ -930,3 +930,65 @@ def test_bias_rows_in_the_grid_with_a_ragged_last_tile_of_weight_rows(monkeypatc
     for k in range(4):
         assert float((merged[k].double() - ref[k]).abs().max()) < 2e-5, k
         assert float((merged[4 + k].double() - ref[k] - res[k].double()).abs().max()) < 2e-5, k
+
+
+@pytest.mark.parametrize("with_slopes,Do", [(False, 128), (True, 512), (False, 64)])
+def test_layer_norm_applied_by_the_epilogue_of_the_product(with_slopes, Do):
+    """fb_matmul_residual_ln_f32 against fb_matmul_residual_f32 followed by fb_layernorm_novar_f32: same bounds to
+    rounding (the row means are rounded in another order, so the bar is the fp64 arbiter's, not bit identity), the
+    row sums it leaves behind are those of its result, a second product chained on them works, and ten launches
+    give identical bits."""
+    from faith_b200 import ops, _lib
+    S, L, Di, Dy, eps, p = 9, 32, 128, 128, 0.05, float("inf")
+    t = cases.rand_bounds(931, S, L, Di, Do, -0.4, 0.6)
+    r = cases.rand_bounds(932, S, L, Di, Dy)
+    g0 = torch.Generator().manual_seed(17)
+    W = (torch.randn(Dy, Do, generator=g0) / math.sqrt(Do)).to(DEV)
+    bias = (torch.randn(Dy, generator=g0) * 0.1).to(DEV)
+    gamma = (torch.randn(Dy, generator=g0)).to(DEV)       # both signs
+    beta = (torch.randn(Dy, generator=g0) * 0.1).to(DEV)
+    lw, lb, uw, ub = [v.to(DEV) for v in t]
+    res = tuple(v.to(DEV) for v in (r[0], r[2], r[1], r[3]))
+    rs = ops.row_sums(*res)
+    if with_slopes:
+        c_l, c_u, nlb, nub = ops.relax_coef(_lib.FB_RELU, lw, uw, lb, ub, p, eps, 1)
+        x = (lw, uw, nlb, nub)
+        extra = (c_l, c_u)
+    else:
+        x = (lw, uw, lb, ub)
+        extra = ()
+    y = ops.matmul_residual(*x, W, bias, res, *extra)
+    want = ops.layernorm_novar(y, gamma, beta)
+    got = ops.matmul_residual_ln(*x, W, bias, res, rs, gamma, beta, *extra)
+    # fp64 statement of the whole chain from the inputs: split-sign product, bias, residual, norm
+    xl, xu = (x[0] * extra[0].unsqueeze(-2), x[1] * extra[1].unsqueeze(-2)) if with_slopes else (x[0], x[1])
+    Wp, Wn = W.double().clamp(min=0).t(), W.double().clamp(max=0).t()
+    y64 = [xl.double() @ Wp + xu.double() @ Wn + res[0].double(), xu.double() @ Wp + xl.double() @ Wn + res[1].double(),
+           x[2].double() @ Wp + x[3].double() @ Wn + bias.double() + res[2].double(),
+           x[3].double() @ Wp + x[2].double() @ Wn + bias.double() + res[3].double()]
+    g64, b64 = gamma.double(), beta.double()
+    gp, gn = g64.clamp(min=0), g64.clamp(max=0)
+    cl = [y64[0] - y64[1].mean(-1, keepdim=True), y64[2] - y64[3].mean(-1, keepdim=True)]
+    cu = [y64[1] - y64[0].mean(-1, keepdim=True), y64[3] - y64[2].mean(-1, keepdim=True)]
+    ref64 = [cl[0] * gp + cu[0] * gn, cu[0] * gp + cl[0] * gn, cl[1] * gp + cu[1] * gn + b64, cu[1] * gp + cl[1] * gn + b64]
+    for k, name in enumerate(("lw", "uw", "lb", "ub")):
+        helpers.assert_arbitrated(got[k], want[k], ref64[k], "layer norm in the epilogue, " + name)
+    sums = ops.row_sums(*got[:4])
+    assert torch.allclose(got[4].sum(1), sums.sum(1), rtol=1e-5, atol=2e-4)
+    # chained: the result as the residual of the next product, with the row sums this launch left behind
+    nxt_want = ops.layernorm_novar(ops.matmul_residual(lw[..., :128].contiguous(), uw[..., :128].contiguous(),
+                                                       lb[..., :128].contiguous(), ub[..., :128].contiguous(),
+                                                       W[:, :128].contiguous(), bias, want), gamma, beta) if Do >= 128 else None
+    if nxt_want is not None:
+        nxt = ops.matmul_residual_ln(lw[..., :128].contiguous(), uw[..., :128].contiguous(), lb[..., :128].contiguous(),
+                                     ub[..., :128].contiguous(), W[:, :128].contiguous(), bias, got[:4], got[4], gamma, beta)
+        for k in range(4):
+            helpers.assert_close(nxt[k], nxt_want[k], "chained %d" % k, atol=2e-4, rtol=1e-4)
+    for _ in range(9):
+        again = ops.matmul_residual_ln(*x, W, bias, res, rs, gamma, beta, *extra)
+        for a, b in zip(again, got):
+            assert torch.equal(a, b)
+    assert _lib.load().fb_tc_check() == 0
+    with pytest.raises(_lib.FaithError):   # 64 output features: not a shape of the fused kernel
+        ops.matmul_residual_ln(*x, W[:64].contiguous(), bias[:64].contiguous(), tuple(v[..., :64].contiguous() for v in res),
+                               rs, gamma[:64].contiguous(), beta[:64].contiguous(), *extra)
