@@ -76,6 +76,11 @@ struct TcLnArgs {
   int64_t rs_stride;
 };
 
+int layernorm_novar_rowsum(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub, const float* r_lw,
+                           const float* r_uw, const float* r_lb, const float* r_ub, const float* gamma, const float* beta,
+                           float* z_lw, float* z_uw, float* z_lb, float* z_ub, int64_t rows, int Di, int Do, float* rowsum,
+                           void* stream);
+
 // Opts `kernel` in to `bytes` of dynamic shared memory on the current device (nothing to do up to 48 KB, or when it
 // already has that much): FB_OK or FB_ERR_CUDA.
 int ensure_dynamic_smem_impl(const void* func, size_t bytes);

@@ -153,7 +153,7 @@ layernorm_novar_row128_kernel(const float* __restrict__ x_lw, const float* __res
                               const float* __restrict__ r_lb, const float* __restrict__ r_ub,
                               const float* __restrict__ gamma, const float* __restrict__ beta,
                               float* __restrict__ z_lw, float* __restrict__ z_uw, float* __restrict__ z_lb,
-                              float* __restrict__ z_ub, int64_t n_w, int64_t n_b) {
+                              float* __restrict__ z_ub, int64_t n_w, int64_t n_b, float* __restrict__ rowsum) {
   constexpr int Do = 128;
   const int lane = threadIdx.x & 31;
   const int64_t warps = (int64_t)gridDim.x * (kThreads / 32);
@@ -197,6 +197,17 @@ layernorm_novar_row128_kernel(const float* __restrict__ x_lw, const float* __res
     }
     reinterpret_cast<float4*>(q.z_l)[lane] = make_float4(ol[0], ol[1], ol[2], ol[3]);
     reinterpret_cast<float4*>(q.z_u)[lane] = make_float4(ou[0], ou[1], ou[2], ou[3]);
+    if (rowsum != nullptr) {
+      // row sums of the result, for a product that takes it as its residual and applies the next layer norm in its
+      // epilogue: [2 lines][4 partial sums][n_w + n_b], the whole sum in the first partial sum of each line
+      float sl = fadd(fadd(ol[0], ol[1]), fadd(ol[2], ol[3])), su = fadd(fadd(ou[0], ou[1]), fadd(ou[2], ou[3]));
+#pragma unroll
+      for (int s = 16; s > 0; s >>= 1) {
+        sl += __shfl_xor_sync(0xffffffffu, sl, s);
+        su += __shfl_xor_sync(0xffffffffu, su, s);
+      }
+      if (lane < 8) rowsum[(int64_t)lane * (n_w + n_b) + row] = lane == 0 ? sl : lane == 4 ? su : 0.f;
+    }
   }
 }
 
@@ -377,11 +388,12 @@ extern "C" int fb_rowsum_f32(const float* x_lw, const float* x_uw, const float* 
   return FB_OK;
 }
 
-extern "C" int fb_layernorm_novar_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+// fb_layernorm_novar_f32 that can also leave the row sums of its result behind (rowsum, may be null).
+int fb::layernorm_novar_rowsum(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
                                       const float* r_lw, const float* r_uw, const float* r_lb, const float* r_ub,
                                       const float* gamma, const float* beta,
                                       float* z_lw, float* z_uw, float* z_lb, float* z_ub,
-                                      int64_t rows, int Di, int Do, void* stream) {
+                                      int64_t rows, int Di, int Do, float* rowsum, void* stream) {
   FB_REQUIRE(x_lw && x_uw && x_lb && x_ub && gamma && beta && z_lw && z_uw && z_lb && z_ub, FB_ERR_ARG);
   const bool any_r = r_lw || r_uw || r_lb || r_ub, all_r = r_lw && r_uw && r_lb && r_ub;
   FB_REQUIRE(any_r == all_r, FB_ERR_ARG);
@@ -394,19 +406,29 @@ extern "C" int fb_layernorm_novar_f32(const float* x_lw, const float* x_uw, cons
                       aligned16(z_lw) && aligned16(z_uw) && aligned16(z_lb) && aligned16(z_ub) && aligned16(gamma) &&
                       aligned16(beta) &&
                       (!r_lw || (aligned16(r_lw) && aligned16(r_uw) && aligned16(r_lb) && aligned16(r_ub)));
+  if (rowsum != nullptr && !row128) return FB_ERR_SHAPE;   // row sums come from the 128-feature kernel only
   const unsigned blocks = stream_blocks((n_w + n_b) * 32);
   cudaStream_t st = (cudaStream_t)stream;
   if (row128 && r_lw)
     layernorm_novar_row128_kernel<true><<<blocks, kThreads, 0, st>>>(x_lw, x_uw, x_lb, x_ub, r_lw, r_uw, r_lb, r_ub, gamma,
-                                                                      beta, z_lw, z_uw, z_lb, z_ub, n_w, n_b);
+                                                                      beta, z_lw, z_uw, z_lb, z_ub, n_w, n_b, rowsum);
   else if (row128)
     layernorm_novar_row128_kernel<false><<<blocks, kThreads, 0, st>>>(x_lw, x_uw, x_lb, x_ub, r_lw, r_uw, r_lb, r_ub, gamma,
-                                                                       beta, z_lw, z_uw, z_lb, z_ub, n_w, n_b);
+                                                                       beta, z_lw, z_uw, z_lb, z_ub, n_w, n_b, rowsum);
   else
     layernorm_novar_kernel<<<blocks, kThreads, 0, st>>>(x_lw, x_uw, x_lb, x_ub, r_lw, r_uw, r_lb, r_ub, gamma, beta, z_lw,
                                                         z_uw, z_lb, z_ub, n_w, n_b, Do);
   FB_LAUNCH_OK();
   return FB_OK;
+}
+
+extern "C" int fb_layernorm_novar_f32(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub,
+                                      const float* r_lw, const float* r_uw, const float* r_lb, const float* r_ub,
+                                      const float* gamma, const float* beta,
+                                      float* z_lw, float* z_uw, float* z_lb, float* z_ub,
+                                      int64_t rows, int Di, int Do, void* stream) {
+  return fb::layernorm_novar_rowsum(x_lw, x_uw, x_lb, x_ub, r_lw, r_uw, r_lb, r_ub, gamma, beta, z_lw, z_uw, z_lb, z_ub, rows, Di,
+                                    Do, nullptr, stream);
 }
 
 extern "C" int fb_split_heads_f32(const float* x_w, const float* x_b, float* z_w, float* z_b,

@@ -46,6 +46,7 @@ struct Plan {
   int64_t range_floats;      // one operand-range scratch tensor of the dot product
   int64_t small_bytes;       // folded classifier weight + bias
   int64_t norm_floats;       // column norms that the projection GEMMs hand to the range kernel (lower + upper)
+  int64_t rowsum_floats;     // row sums of the layer input for the layer norm in a GEMM epilogue: [2 lines][4 partial sums][rows * (Di + 1)]
   int64_t total;
 };
 
@@ -61,7 +62,9 @@ Plan make_plan(const fb_encoder* e, int S, int L, int words) {
   p.range_floats = (int64_t)S * H * (L > d ? L : d) * (L > d ? L : d);
   p.small_bytes = align_up((D + 1) * 4, 256);
   p.norm_floats = 2 * (int64_t)S * L * (words + 1) * (D > F ? D : F);
-  p.total = 4 * p.slot_bytes + 4 * align_up(p.range_floats * 4, 256) + p.small_bytes + align_up(p.norm_floats * 4, 256);
+  p.rowsum_floats = 8 * (int64_t)S * L * (Di + 1);
+  p.total = 4 * p.slot_bytes + 4 * align_up(p.range_floats * 4, 256) + p.small_bytes + align_up(p.norm_floats * 4, 256) +
+            align_up(p.rowsum_floats * 4, 256);
   return p;
 }
 
@@ -115,7 +118,7 @@ __global__ void __launch_bounds__(256)
 input_bounds_norm128_kernel(const float* __restrict__ emb, const float* __restrict__ gamma, const float* __restrict__ beta,
                             float* __restrict__ lw, float* __restrict__ uw, float* __restrict__ lb, float* __restrict__ ub,
                             int64_t n_w_rows, int64_t n_b_rows, int L, int words, Positions pos,
-                            const int* __restrict__ inst_pos, const float* __restrict__ inst_eps) {
+                            const int* __restrict__ inst_pos, const float* __restrict__ inst_eps, float* __restrict__ rowsum) {
   constexpr int D = 128;
   const int lane = threadIdx.x & 31;
   const int64_t warps = (int64_t)gridDim.x * 8;
@@ -161,6 +164,18 @@ input_bounds_norm128_kernel(const float* __restrict__ emb, const float* __restri
     float* zu = is_bias ? ub + (row - n_w_rows) * D : uw + row * D;
     reinterpret_cast<float4*>(zl)[lane] = make_float4(ol[0], ol[1], ol[2], ol[3]);
     reinterpret_cast<float4*>(zu)[lane] = make_float4(ou[0], ou[1], ou[2], ou[3]);
+    if (rowsum != nullptr) {
+      // row sums of the result for a product that applies the next layer norm in its epilogue: the whole sum in the
+      // first of the four partial sums of each line, zeros in the others
+      float sl = fadd(fadd(ol[0], ol[1]), fadd(ol[2], ol[3])), su = fadd(fadd(ou[0], ou[1]), fadd(ou[2], ou[3]));
+#pragma unroll
+      for (int s = 16; s > 0; s >>= 1) {
+        sl += __shfl_xor_sync(0xffffffffu, sl, s);
+        su += __shfl_xor_sync(0xffffffffu, su, s);
+      }
+      const int64_t stride = n_w_rows + n_b_rows;
+      if (lane < 8) rowsum[(int64_t)lane * stride + row] = lane == 0 ? sl : lane == 4 ? su : 0.f;
+    }
   }
 }
 
@@ -260,6 +275,14 @@ static int encoder_forward_impl(const fb_encoder* enc, const float* emb, int S, 
   float* fold_b = fold_w + D;
   float* norm_ws = reinterpret_cast<float*>(base + 4 * plan.slot_bytes + 4 * align_up(plan.range_floats * 4, 256) +
                                             plan.small_bytes);
+  // row sums of the layer input, for the layer norm applied in the epilogue of the attention output product
+  float* rs_in = norm_ws + align_up(plan.norm_floats * 4, 256) / 4;
+  // The first layer norm of a block is applied by the epilogue of the attention output product where the shapes allow it
+  // (128 features, at least 256 rows): the row sums of the residual (the layer input) are left behind by the kernel
+  // that wrote it.  FB_ENCODER_SEPARATE_LN in the environment keeps the norm as a launch of its own (the results
+  // differ in the rounding of the row means).  The second norm stays a launch of its own: behind a product with
+  // K = 512 the converters' share of the row means costs more than the norm (2.66 against 1.98 + 0.34 ms).
+  bool fuse_ln = enc->layer_norm == 1 && D == 128 && rows >= 256 && enc->layers > 0 && getenv("FB_ENCODER_SEPARATE_LN") == nullptr;
 
   FB_CUDA_OK(cudaMemsetAsync(violation, 0, sizeof(int), st));
   const StatusSinkScope sink(violation);
@@ -277,9 +300,10 @@ static int encoder_forward_impl(const fb_encoder* enc, const float* emb, int S, 
       // (without encoder layers the pooler reads both buffers, so both are written)
       input_bounds_norm128_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, st>>>(
           emb, enc->emb_ln_g, enc->emb_ln_b, slot[A].lw, enc->layers == 0 ? slot[A].uw : slot[A].lw, slot[A].lb, slot[A].ub,
-          n_w_rows, n_b_rows, L, words, pos, inst_pos, inst_eps);
+          n_w_rows, n_b_rows, L, words, pos, inst_pos, inst_eps, fuse_ln ? rs_in : nullptr);
       FB_LAUNCH_OK();
     } else {
+      fuse_ln = false;   // (the row sums of the layer input come from the fused input kernel)
       const int64_t n_w = rows * Di * D, n_b = rows * D;
       const int64_t want = ceil_div(n_w, 256), cap = (int64_t)device_info().sms * 16;
       input_bounds_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, st>>>(emb, slot[B].lw, slot[B].uw, slot[B].lb,
@@ -490,9 +514,21 @@ static int encoder_forward_impl(const fb_encoder* enc, const float* emb, int S, 
     }
     // attention output: dense, + residual, layer norm -> T3
     // (the residual is added by the GEMM epilogue where the shapes allow it: the layer norm then reads one bound)
-    const int arc = fb_matmul_residual_f32(T2.lw, T2.uw, T2.lb, T2.ub, nullptr, nullptr, ly.ao_w, ly.ao_b, Xin.lw, Xin.uw, X.lb,
-                                           X.ub, T1.lw, T1.uw, T1.lb, T1.ub, rows, Di, D, D, stream);
-    if (arc == FB_OK) {
+    int arc = FB_ERR_SHAPE;
+    bool ln1_done = false;
+    if (fuse_ln) {
+      arc = fb_matmul_residual_ln_f32(T2.lw, T2.uw, T2.lb, T2.ub, nullptr, nullptr, ly.ao_w, ly.ao_b, Xin.lw, Xin.uw, X.lb, X.ub,
+                                      rs_in, ly.ln1_g, ly.ln1_b, T3.lw, T3.uw, T3.lb, T3.ub, nullptr, rows, Di, D, D, stream);
+      if (arc == FB_OK) ln1_done = true;
+      else if (arc == FB_ERR_SHAPE) fuse_ln = false;   // from here on the norms are launches of their own
+      else return arc;
+    }
+    if (!ln1_done)
+      arc = fb_matmul_residual_f32(T2.lw, T2.uw, T2.lb, T2.ub, nullptr, nullptr, ly.ao_w, ly.ao_b, Xin.lw, Xin.uw, X.lb, X.ub, T1.lw,
+                                   T1.uw, T1.lb, T1.ub, rows, Di, D, D, stream);
+    if (ln1_done) {
+      // (T3 holds the normalised output of the attention block)
+    } else if (arc == FB_OK) {
       FB_TRY(norm_residual(enc, T1, nullptr, ly.ln1_g, ly.ln1_b, T3, rows, Di, D, stream));
     } else if (arc == FB_ERR_SHAPE) {
       FB_TRY(dense(T2, ly.ao_w, ly.ao_b, T1, rows, Di, D, D, stream));
@@ -526,7 +562,21 @@ static int encoder_forward_impl(const fb_encoder* enc, const float* emb, int S, 
     }
     if (frc == FB_OK) {
       const BoundSet Y = {T2.lw, T2.uw, X.lb, X.ub};
-      FB_TRY(norm_residual(enc, Y, residual_added ? nullptr : &T3, ly.ln2_g, ly.ln2_b, T1, rows, Di, D, stream));
+      if (fuse_ln) {
+        // (the norm also leaves the row sums of the layer output behind, for the next layer's attention output product)
+        const BoundSet* r2 = residual_added ? nullptr : &T3;
+        const int lrc = layernorm_novar_rowsum(Y.lw, Y.uw, Y.lb, Y.ub, r2 ? r2->lw : nullptr, r2 ? r2->uw : nullptr,
+                                               r2 ? r2->lb : nullptr, r2 ? r2->ub : nullptr, ly.ln2_g, ly.ln2_b, T1.lw, T1.uw, T1.lb,
+                                               T1.ub, rows, Di, D, rs_in, stream);
+        if (lrc == FB_ERR_SHAPE) {
+          fuse_ln = false;
+          FB_TRY(norm_residual(enc, Y, r2, ly.ln2_g, ly.ln2_b, T1, rows, Di, D, stream));
+        } else if (lrc != FB_OK) {
+          return lrc;
+        }
+      } else {
+        FB_TRY(norm_residual(enc, Y, residual_added ? nullptr : &T3, ly.ln2_g, ly.ln2_b, T1, rows, Di, D, stream));
+      }
       // the layer output (slot B) becomes the next layer's input
       const int newA = B;
       B = A;
@@ -537,6 +587,7 @@ static int encoder_forward_impl(const fb_encoder* enc, const float* emb, int S, 
     FB_TRY(relax(FB_RELU, T1, T2, rows, Di, F, words, p, eps, nullptr, stream));
     FB_TRY(dense(T2, ly.f2_w, ly.f2_b, T1, rows, Di, F, D, stream));
     FB_TRY(norm_residual(enc, T1, &T3, ly.ln2_g, ly.ln2_b, T2, rows, Di, D, stream));
+    fuse_ln = false;
     // the layer output becomes the next layer's input
     const int newA = C;
     C = A;

@@ -278,7 +278,7 @@ extern "C" int fb_matmul_residual_f32(const float* x_lw, const float* x_uw, cons
 // Bounds.py:1111-1131), applied by the GEMM epilogue before the store: z = layer_norm(matmul(x, W) + bias + r).  The
 // row means the norm needs are not taken from the result (a tile holds half of a row): those of the product come
 // from the operand and the column means of W, those of the residual from r_rowsum, which the producer of r left
-// behind, and z_rowsum receives those of z for the next product that takes z as its residual.  Row sums:
+// behind, and z_rowsum (may be NULL) receives those of z for the next product that takes z as its residual.  Row sums:
 // [2 lines][4 partial sums][rows * (Di + 1)] floats, weight rows first, then the bias rows; a reader adds the four
 // partial sums of a line in order (a producer that has whole rows writes the sum into the first and zeros into the
 // others).  The means are rounded in a different order than fb_layernorm_novar_f32 rounds them, so the result equals
@@ -291,7 +291,7 @@ extern "C" int fb_matmul_residual_ln_f32(const float* x_lw, const float* x_uw, c
                                          float* z_lw, float* z_uw, float* z_lb, float* z_ub, float* z_rowsum,
                                          int64_t rows, int Di, int Do, int Dy, void* stream) {
   if (!x_lw || !x_uw || !x_lb || !x_ub || !W || !r_lw || !r_uw || !r_lb || !r_ub || !r_rowsum || !gamma || !beta || !z_lw ||
-      !z_uw || !z_lb || !z_ub || !z_rowsum)
+      !z_uw || !z_lb || !z_ub)
     return FB_ERR_ARG;
   if ((c_l == nullptr) != (c_u == nullptr)) return FB_ERR_ARG;
   if (rows < 0 || Di <= 0 || Do <= 0 || Dy <= 0) return FB_ERR_ARG;

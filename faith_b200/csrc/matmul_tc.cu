@@ -579,7 +579,7 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
           *reinterpret_cast<ulonglong2*>(so + 2 * kOutBoxBytes + off) = make_ulonglong2(up2[0], up2[1]);
         }
       }
-      if (kLN && rvalid) {
+      if (kLN && rvalid && ln_args.rs_out != nullptr) {
         // sums of this thread's row over the 32 columns it handled: partial sum (n tile, column half) of the result's row
         const int sl = (nx / BN) * 2 + chalf;
         ln_args.rs_out[(int64_t)sl * ln_args.rs_stride + grow] =
@@ -894,7 +894,7 @@ int launch_split_sign_tc(const float* a_lo, const float* a_up, const float* W, c
                         ((br->a_lo == br->a_up) != (a_lo == a_up) && norm_lo != nullptr) || br->M <= 0))
     return FB_ERR_ARG;
   if (ln != nullptr && (br == nullptr || res_lo == nullptr || N != kLnN || K % (2 * BK) != 0 || K > kLnMaxK || M % BM != 0 ||
-                        ln->gamma == nullptr || ln->beta == nullptr || ln->rs_in == nullptr || ln->rs_out == nullptr ||
+                        ln->gamma == nullptr || ln->beta == nullptr || ln->rs_in == nullptr ||
                         ln->rs_stride < M + br->M))
     return FB_ERR_ARG;
   if (norm_lo != nullptr && (coef_l != nullptr || norm_up == nullptr || M % BM != 0)) return FB_ERR_ARG;

@@ -168,7 +168,7 @@ int fb_matmul_residual_f32(const float* x_lw, const float* x_uw, const float* x_
 
 /* fb_matmul_residual_f32 followed by the layer norm of the encoder blocks (mode no_var, Bounds.py:1111-1131), applied
  * by the GEMM epilogue: z = layer_norm(matmul(x, W) + bias + r).  r_rowsum: row sums of the residual as its producer
- * left them, z_rowsum: those of z for the next consumer; each [2 lines][4 partial sums][rows * (Di + 1)] floats (weight
+ * left them, z_rowsum (may be NULL): those of z for the next consumer; each [2 lines][4 partial sums][rows * (Di + 1)] floats (weight
  * rows first, then the bias rows; a reader adds the four partial sums in order).  Equals the separate operators to
  * rounding (the row means are rounded in another order).  Dy == 128, Do % 64 == 0, Do <= 512, rows * Di % 128 == 0,
  * rows >= 256; otherwise FB_ERR_SHAPE and nothing is launched.  Replaces Bounds.matmul + Bounds.add +

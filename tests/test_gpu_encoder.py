@@ -334,3 +334,48 @@ def test_mean_pooling_option():
         x[:, c["index"], :] += delta
         y = O.concrete_forward(model, x)
         assert float(y.min()) >= float(l[s]) - 1e-5 and float(y.max()) <= float(u[s]) + 1e-5
+
+
+@pytest.mark.parametrize("words,positions,p,S", [(1, [1], float("inf"), 8), (2, [3, 30], 2.0, 8), (1, [2], float("inf"), 4)])
+def test_layer_norms_applied_in_gemm_epilogues_give_the_same_bounds(words, positions, p, S):
+    """With 128 features the first layer norm of every block is applied by the epilogue of the attention output product
+    (row means of the product from the operand and the weight's column means, of the residual from the row sums its
+    producer left behind).  FB_ENCODER_SEPARATE_LN=1 keeps the norm as a launch of its own; both routes stay within
+    the noise budget of the fp64 oracle, the fused one is deterministic, and fewer than 256 rows (S = 4) take the
+    separate launch either way."""
+    import os
+    import faith_b200
+    from faith_b200 import _lib
+    model = O.make_encoder(4)
+    emb = torch.randn(S, 32, 128, generator=torch.Generator().manual_seed(8)).to(DEV)
+    ver = faith_b200.EncoderVerifier(model, DEV)
+    lib = _lib.load()
+
+    def run():
+        n0 = lib.fb_launch_count()
+        a = ver.forward(emb, positions, p, 1e-3)
+        torch.cuda.synchronize()
+        return [t.clone() for t in a[:2]], lib.fb_launch_count() - n0
+
+    assert "FB_ENCODER_SEPARATE_LN" not in os.environ
+    fused, n_fused = run()
+    os.environ["FB_ENCODER_SEPARATE_LN"] = "1"
+    try:
+        separate, n_separate = run()
+    finally:
+        del os.environ["FB_ENCODER_SEPARATE_LN"]
+    layers = len(model["layers"])
+    assert n_separate - n_fused == (layers if S * 32 >= 256 else 0)
+    # Two fp32 evaluation orders of this pass differ by what the later layers make of their rounding (the oracle's own
+    # fp32 run strays from its fp64 run by about 1e-2 of a bound here), so both routes are held against the fp64 oracle
+    # with the noise budget of the other driver tests, on the first two sentences.
+    l32, u32 = O.encoder_forward(model, emb[:2].cpu(), positions, p, 1e-3)
+    l64, u64 = O.encoder_forward(O.model_to(model, torch.float64), emb[:2].cpu().double(), positions, p, 1e-3)
+    for route, name in ((fused, "norm in the epilogue"), (separate, "norm as a launch")):
+        assert bool(torch.isfinite(route[0]).all()) and bool(torch.isfinite(route[1]).all())
+        helpers.assert_within_noise(route[0][:2], l32, l64, "lower, " + name)
+        helpers.assert_within_noise(route[1][:2], u32, u64, "upper, " + name)
+    again, _ = run()
+    for x, y in zip(again, fused):
+        assert torch.equal(x, y)
+    assert lib.fb_tc_check() == 0
