@@ -76,6 +76,8 @@ struct TcLnArgs {
   int64_t rs_stride;
 };
 
+// fb_layernorm_novar_f32 that can also leave the row sums of its result behind (rowsum, may be null; 128 features
+// only): [2 lines][4 partial sums][rows * (Di + 1)], of which it writes the first partial sum of each line.
 int layernorm_novar_rowsum(const float* x_lw, const float* x_uw, const float* x_lb, const float* x_ub, const float* r_lw,
                            const float* r_uw, const float* r_lb, const float* r_ub, const float* gamma, const float* beta,
                            float* z_lw, float* z_uw, float* z_lb, float* z_ub, int64_t rows, int Di, int Do, float* rowsum,

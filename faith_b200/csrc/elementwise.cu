@@ -199,14 +199,18 @@ layernorm_novar_row128_kernel(const float* __restrict__ x_lw, const float* __res
     reinterpret_cast<float4*>(q.z_u)[lane] = make_float4(ou[0], ou[1], ou[2], ou[3]);
     if (rowsum != nullptr) {
       // row sums of the result, for a product that takes it as its residual and applies the next layer norm in its
-      // epilogue: [2 lines][4 partial sums][n_w + n_b], the whole sum in the first partial sum of each line
+      // epilogue: [2 lines][4 partial sums][n_w + n_b], the whole sum in the first partial sum of each line (the other
+      // three are not written: the caller keeps them zero)
       float sl = fadd(fadd(ol[0], ol[1]), fadd(ol[2], ol[3])), su = fadd(fadd(ou[0], ou[1]), fadd(ou[2], ou[3]));
 #pragma unroll
       for (int s = 16; s > 0; s >>= 1) {
         sl += __shfl_xor_sync(0xffffffffu, sl, s);
         su += __shfl_xor_sync(0xffffffffu, su, s);
       }
-      if (lane < 8) rowsum[(int64_t)lane * (n_w + n_b) + row] = lane == 0 ? sl : lane == 4 ? su : 0.f;
+      if (lane == 0) {   // (the other three partial sums of each line stay zero: the caller cleared them)
+        rowsum[row] = sl;
+        rowsum[4 * (n_w + n_b) + row] = su;
+      }
     }
   }
 }

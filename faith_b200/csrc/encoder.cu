@@ -166,7 +166,7 @@ input_bounds_norm128_kernel(const float* __restrict__ emb, const float* __restri
     reinterpret_cast<float4*>(zu)[lane] = make_float4(ou[0], ou[1], ou[2], ou[3]);
     if (rowsum != nullptr) {
       // row sums of the result for a product that applies the next layer norm in its epilogue: the whole sum in the
-      // first of the four partial sums of each line, zeros in the others
+      // first of the four partial sums of each line (the others were cleared at the start of the pass)
       float sl = fadd(fadd(ol[0], ol[1]), fadd(ol[2], ol[3])), su = fadd(fadd(ou[0], ou[1]), fadd(ou[2], ou[3]));
 #pragma unroll
       for (int s = 16; s > 0; s >>= 1) {
@@ -174,7 +174,10 @@ input_bounds_norm128_kernel(const float* __restrict__ emb, const float* __restri
         su += __shfl_xor_sync(0xffffffffu, su, s);
       }
       const int64_t stride = n_w_rows + n_b_rows;
-      if (lane < 8) rowsum[(int64_t)lane * stride + row] = lane == 0 ? sl : lane == 4 ? su : 0.f;
+      if (lane == 0) {
+        rowsum[row] = sl;
+        rowsum[4 * stride + row] = su;
+      }
     }
   }
 }
@@ -286,6 +289,8 @@ static int encoder_forward_impl(const fb_encoder* enc, const float* emb, int S, 
 
   FB_CUDA_OK(cudaMemsetAsync(violation, 0, sizeof(int), st));
   const StatusSinkScope sink(violation);
+  // (the producers of the row sums write the first of the four partial sums of a line; the rest stays zero)
+  if (fuse_ln) FB_CUDA_OK(cudaMemsetAsync(rs_in, 0, (size_t)plan.rowsum_floats * 4, st));
 
   // slot roles rotate; names follow the walk-through in the file header
   int A = 0, B = 1, C = 2, Dd = 3;
