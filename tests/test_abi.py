@@ -37,6 +37,12 @@ def test_argument_validation_without_gpu():
     assert lib.fb_relax_f32(0, None, None, None, None, None, None, None, None, 1, 4, 4, 1, 2, 0.1, 0, None, None) == 1
     assert lib.fb_concretize_f32(1, 1, 1, 1, 1, 1, 1, 4, 4, 1, 7, 0.1, 0, None) == 1  # unknown norm
     assert lib.fb_concretize_f32(1, 1, 1, 1, 1, 1, 1, 6, 4, 4, 2, 0.1, 0, None) == 2  # Di % words != 0
+    # product + residual + layer norm: missing row sums of the residual, slopes given for one line only, result aliasing
+    # the residual
+    P = [256 * (k + 1) for k in range(20)]   # never dereferenced
+    assert lib.fb_matmul_residual_ln_f32(*P[:12], None, *P[13:], 256, 128, 128, 128, None) == 1
+    assert lib.fb_matmul_residual_ln_f32(*P[:4], P[4], None, *P[6:], 256, 128, 128, 128, None) == 1
+    assert lib.fb_matmul_residual_ln_f32(*P[:15], P[8], *P[16:], 256, 128, 128, 128, None) == 1
 
 
 def test_ops_refuse_cpu_tensors():
