@@ -126,3 +126,42 @@ def test_oracle_two_word_search_matches_the_reference_verifier():
     assert sorted(got) == pairs
     diff = [q for q, e in zip(pairs, g["s0/pair_eps"]) if np.float32(got[q]) != np.float32(e)]
     assert len(diff) <= 1, diff
+
+
+def test_layer_norm_after_a_product_from_the_weight_column_means():
+    """The identity behind the layer norm applied in a GEMM epilogue (fb_matmul_residual_ln_f32), in double precision on
+    the oracle: for y = matmul(x, W) + bias + r the feature mean of a row of y_lw is x's centre row times the column
+    means of W minus x's radius row times the column means of |W|, plus the mean of the bias (bias rows), plus the row
+    sum of r over the number of features; with those means, (y_lw - mean(y_uw)) gamma+ + (y_uw - mean(y_lw)) gamma-
+    (+ beta on the bias rows) is Bounds.layer_norm in mode no_var (Bounds.py:1111-1131)."""
+    g = torch.Generator().manual_seed(41)
+    B, L, Di, K, N = 2, 3, 5, 12, 8
+    dt = torch.float64
+    lw = torch.randn(B, L, Di, K, generator=g, dtype=dt)
+    uw = lw + torch.rand(B, L, Di, K, generator=g, dtype=dt) * torch.randn(B, L, Di, K, generator=g, dtype=dt).sign()
+    lb = torch.randn(B, L, K, generator=g, dtype=dt)
+    ub = lb + torch.rand(B, L, K, generator=g, dtype=dt)
+    x = O.OBounds(2.0, 0.01, lw, lb, uw, ub)
+    r = O.OBounds(2.0, 0.01, torch.randn(B, L, Di, N, generator=g, dtype=dt), torch.randn(B, L, N, generator=g, dtype=dt),
+                 torch.randn(B, L, Di, N, generator=g, dtype=dt), torch.randn(B, L, N, generator=g, dtype=dt))
+    W = torch.randn(N, K, generator=g, dtype=dt)
+    bias, gamma, beta = (torch.randn(N, generator=g, dtype=dt) for _ in range(3))
+    y = x.matmul(W).add(bias).add(r)
+    want = y.layer_norm(gamma, beta, "no_var")
+
+    wbar, abar = W.mean(0), W.abs().mean(0)
+    gp, gn = gamma.clamp(min=0), gamma.clamp(max=0)
+
+    def fused(lo, up, r_lo, r_up, y_lo, y_up, with_bias):
+        c, rad = (lo + up) / 2, (up - lo) / 2
+        extra = bias.mean() if with_bias else 0.0
+        mean_lo = c @ wbar - rad @ abar + r_lo.sum(-1) / N + extra
+        mean_up = c @ wbar + rad @ abar + r_up.sum(-1) / N + extra
+        dl, du = y_lo - mean_up.unsqueeze(-1), y_up - mean_lo.unsqueeze(-1)
+        shift = beta if with_bias else 0.0
+        return dl * gp + du * gn + shift, du * gp + dl * gn + shift
+
+    z_lw, z_uw = fused(x.lw, x.uw, r.lw, r.uw, y.lw, y.uw, False)
+    z_lb, z_ub = fused(x.lb, x.ub, r.lb, r.ub, y.lb, y.ub, True)
+    for got, ref in ((z_lw, want.lw), (z_uw, want.uw), (z_lb, want.lb), (z_ub, want.ub)):
+        assert float((got - ref).abs().max()) < 1e-12
