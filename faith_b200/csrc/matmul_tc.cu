@@ -264,17 +264,38 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
   }
   float* const ln_smem = reinterpret_cast<float*>(base_ptr + SharedLayout::bars() + 256 + kLiveWords * 4);
   if (kLN) {
-    // column means of W and |W| (terms added in the order of n), the gain split by sign as the layer-norm kernel splits it
+    // column means of W and |W|, the gain split by sign as the layer-norm kernel splits it.  The rows of W are dealt
+    // out to as many threads per group of four columns as the block has (a single thread per column walks 128 rows one
+    // load after the other: 40 us); the partial sums go through the output staging buffer, which is idle until the first
+    // tile is done, and are added in a fixed order.
     const float inv_n = 1.0f / (float)N;
-    for (int k = threadIdx.x; k < K; k += blockDim.x) {
-      float sw = 0.f, sa = 0.f;
-      for (int n = 0; n < N; ++n) {
-        const float w = __ldg(ln_args.w_raw + (size_t)n * K + k);
-        sw = fmaf(w, inv_n, sw);
-        sa = fmaf(fabsf(w), inv_n, sa);
+    {
+      float* scratch = reinterpret_cast<float*>(base_ptr + SharedLayout::out());
+      const int groups = K >> 2;
+      int parts = (int)blockDim.x / groups;
+      if (parts > N) parts = N;
+      const int gidx = (int)threadIdx.x % groups, part = (int)threadIdx.x / groups;
+      if (part < parts) {
+        float4 sw = make_float4(0.f, 0.f, 0.f, 0.f), sa = sw;
+        for (int n = part; n < N; n += parts) {
+          const float4 w = __ldg(reinterpret_cast<const float4*>(ln_args.w_raw + (size_t)n * K) + gidx);
+          sw.x = fmaf(w.x, inv_n, sw.x); sw.y = fmaf(w.y, inv_n, sw.y); sw.z = fmaf(w.z, inv_n, sw.z); sw.w = fmaf(w.w, inv_n, sw.w);
+          sa.x = fmaf(fabsf(w.x), inv_n, sa.x); sa.y = fmaf(fabsf(w.y), inv_n, sa.y);
+          sa.z = fmaf(fabsf(w.z), inv_n, sa.z); sa.w = fmaf(fabsf(w.w), inv_n, sa.w);
+        }
+        reinterpret_cast<float4*>(scratch + (size_t)(2 * part) * K)[gidx] = sw;
+        reinterpret_cast<float4*>(scratch + (size_t)(2 * part + 1) * K)[gidx] = sa;
       }
-      ln_smem[kLnOffWbar / 4 + k] = sw;
-      ln_smem[kLnOffAbar / 4 + k] = sa;
+      __syncthreads();
+      for (int k = threadIdx.x; k < K; k += blockDim.x) {
+        float a = 0.f, b = 0.f;
+        for (int q = 0; q < parts; ++q) {
+          a = fadd(a, scratch[(size_t)(2 * q) * K + k]);
+          b = fadd(b, scratch[(size_t)(2 * q + 1) * K + k]);
+        }
+        ln_smem[kLnOffWbar / 4 + k] = a;
+        ln_smem[kLnOffAbar / 4 + k] = b;
+      }
     }
     for (int n = threadIdx.x; n < N; n += blockDim.x) {
       const float gv = __ldg(ln_args.gamma + n);
@@ -470,6 +491,21 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
           tma_load_3d(so + (2 + q) * kOutBoxBytes, bseg ? &tm_bres_up : &tm_res_up, nx + 32 * q, my, 0, bar_res);
         }
       }
+      // kLN: the row sums of the residual do not depend on the accumulators: their loads go out before the wait
+      int64_t grow = 0;                                // row of the bound: weight rows first, then the bias rows
+      bool rvalid = false;
+      float rsl[4] = {0.f, 0.f, 0.f, 0.f}, rsu[4] = {0.f, 0.f, 0.f, 0.f};
+      if (kLN) {
+        grow = (bseg ? M : 0) + my + row;
+        rvalid = my + row < (bseg ? Mb : M);
+        if (rvalid) {
+#pragma unroll
+          for (int sl = 0; sl < 4; ++sl) {
+            rsl[sl] = __ldg(ln_args.rs_in + (int64_t)sl * ln_args.rs_stride + grow);
+            rsu[sl] = __ldg(ln_args.rs_in + (int64_t)(4 + sl) * ln_args.rs_stride + grow);
+          }
+        }
+      }
       ok = mbar_wait_warp(bar_acc_ready, (uint32_t)(le & 1), wc);
       if (!ok) break;
       ++le;
@@ -480,24 +516,14 @@ split_sign_gemm_tc(const __grid_constant__ CUtensorMap tm_lo, const __grid_const
       }
       // kLN: the means over all 128 features of this thread's row of y_lw and of y_uw (product + bias + residual)
       uint64_t mlo2 = 0, mup2 = 0, sl2 = 0, su2 = 0;   // the means as pairs; running sums of the normalised row
-      int64_t grow = 0;                                // row of the bound: weight rows first, then the bias rows
-      bool rvalid = false;
       if (kLN) {
         ok = mbar_wait_warp(bar_mu + 8 * (e & 1), (uint32_t)((e >> 1) & 1), wc);
         if (!ok) break;
         const float2* mu = reinterpret_cast<const float2*>(ln_smem + kLnOffMu / 4) + ((e & 1) * 4) * 128 + row;
         const float2 p0 = mu[0], p1 = mu[128], p2 = mu[256], p3 = mu[384];
         const float mc = fadd(fadd(fadd(p0.x, p1.x), p2.x), p3.x), mr = fadd(fadd(fadd(p0.y, p1.y), p2.y), p3.y);
-        grow = (bseg ? M : 0) + my + row;
-        rvalid = my + row < (bseg ? Mb : M);
-        float rl = 0.f, ru = 0.f;
-        if (rvalid) {
-#pragma unroll
-          for (int sl = 0; sl < 4; ++sl) {
-            rl = fadd(rl, __ldg(ln_args.rs_in + (int64_t)sl * ln_args.rs_stride + grow));
-            ru = fadd(ru, __ldg(ln_args.rs_in + (int64_t)(4 + sl) * ln_args.rs_stride + grow));
-          }
-        }
+        const float rl = fadd(fadd(fadd(fadd(0.f, rsl[0]), rsl[1]), rsl[2]), rsl[3]);
+        const float ru = fadd(fadd(fadd(fadd(0.f, rsu[0]), rsu[1]), rsu[2]), rsu[3]);
         const float inv_n = 1.0f / (float)N;
         float mlo = fadd(fsub(mc, mr), fmul(rl, inv_n)), mup = fadd(fadd(mc, mr), fmul(ru, inv_n));
         if (bseg) {
