@@ -159,3 +159,32 @@ def test_compact_window_extent_without_gpu():
     assert extent(8, 8, [(3, 3, 0, 1)])[0] == 1                                # stride 0
     assert extent(4, 4, [(9, 9, 1, 0)])[0] == 2                                # feature map shrinks to nothing
     assert extent(8, 8, [(3, 3, 1, 1)] * 9)[0] == 2                            # more than eight convolutions
+
+
+def test_encoder_arena_size_without_gpu():
+    """fb_encoder_workspace_bytes is host arithmetic: four bound slots sized for the widest tensor of a block, the range
+    scratch of the dot products, the column-norm scratch and the row sums of the layer input; it grows with the
+    sentences, and a width that the heads do not divide is refused."""
+    import ctypes
+    from faith_b200 import _lib
+    lib = _lib.load()
+
+    def enc(d_model=128, heads=4, ffn=512, layers=3):
+        e = _lib.Encoder()
+        e.layers, e.d_model, e.heads, e.ffn, e.layer_norm = layers, d_model, heads, ffn, 1
+        return e
+
+    def up(v):
+        return (v + 255) // 256 * 256
+    S, L, words = 256, 32, 1
+    D, F, H = 128, 512, 4
+    Di = words * D
+    got = lib.fb_encoder_workspace_bytes(ctypes.byref(enc()), S, L, words)
+    slot = 2 * up(S * L * Di * F * 4) + 2 * up(S * L * F * 4)
+    want = (4 * slot + 4 * up(S * H * L * L * 4) + up((D + 1) * 4) + up(2 * S * L * (words + 1) * F * 4) +
+            up(8 * S * L * (Di + 1) * 4))
+    assert got == want
+    assert lib.fb_encoder_workspace_bytes(ctypes.byref(enc()), 8, L, words) < got
+    assert lib.fb_encoder_workspace_bytes(ctypes.byref(enc()), S, L, 2) > got
+    assert lib.fb_encoder_workspace_bytes(ctypes.byref(enc(d_model=130)), S, L, words) == -1
+    assert lib.fb_encoder_workspace_bytes(None, S, L, words) == -1
