@@ -9,5 +9,5 @@ Host-side mirror of the reference's operator interface over libfaith_b200.so:
 from . import c_bound, ops  # noqa: F401
 from .bounds import Bounds, BoundsLite  # noqa: F401
 from .encoder import EncoderVerifier  # noqa: F401
-from .search import EpsilonSearch, result_record, write_result  # noqa: F401
+from .search import EpsilonSearch, result_record, run_and_record, write_result  # noqa: F401
 from ._lib import FaithError, load  # noqa: F401

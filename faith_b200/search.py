@@ -162,6 +162,31 @@ class EpsilonSearch:
         return out, max_eps
 
 
+def run_and_record(search, emb, labels, tokens=None, perturbed_words=1, path=None, log=None):
+    """The reference's Verifier.run (Verifiers/Verifier.py:36-60) on a batch of sentences: search every perturbable
+    position (one word) or pair of positions (two words) of every sentence, word pieces skipped where the tokens are
+    given (:109-110, :159-163), and return the reference's result record; with `path` the record is also written as the
+    reference writes it, with `log` (a callable taking one string) its summary lines are logged.  search: an
+    EpsilonSearch; emb [N, L, D] and labels [N] on the verifier's device."""
+    N, L, _ = emb.shape
+    positions = [perturbable_positions(L, tokens[s] if tokens is not None else None) for s in range(N)]
+    if perturbed_words == 1:
+        found = search.run(emb, labels, positions)
+    elif perturbed_words == 2:
+        pairs = [[(a, b) for k, a in enumerate(pp) for b in pp[k + 1:]] for pp in positions]
+        found, _ = search.run_pairs(emb, labels, pairs)
+    else:
+        raise NotImplementedError("perturbed_words = %r (the reference supports 1 and 2, Verifier.py:203-204)" % (perturbed_words,))
+    record = result_record(found, emb, labels, search.p, tokens)
+    if path is not None:
+        write_result(path, record, log)
+    elif log is not None:
+        log("{} valid examples".format(len(record["examples"])))
+        log("Minimum: {:.5f}".format(record["minimum"]))
+        log("Average: {:.5f}".format(record["average"]))
+    return record
+
+
 def result_record(per_sentence, emb, labels, p, tokens=None, seconds=None):
     """The reference's result file for one run of the search, as a dict ready for json.dumps(indent=4).
 

@@ -167,3 +167,31 @@ def test_result_record_two_words_and_empty_sentence():
         assert "no searched position" in str(e)
     else:
         raise AssertionError("an empty sentence must be rejected")
+
+
+def test_run_and_record_mirrors_the_reference_run(tmp_path):
+    """One word: word pieces are skipped, every other position is searched, the record has the reference's layout and is
+    written with its summary lines; two words: every pair of the remaining positions; three words are refused as the
+    reference refuses them."""
+    from faith_b200.search import run_and_record
+    emb, labels, thr = _inputs(N=2, L=7)
+    tokens = [["[CLS]", "a", "b", "##c", "d", "e", "[SEP]"], ["[CLS]", "f", "g", "h", "i", "j", "[SEP]"]]
+    search = EpsilonSearch(FakeVerifier(thr), p=2, max_eps=0.1, num_verify_iters=6, max_instances=64)
+    lines = []
+    rec = run_and_record(search, emb, labels, tokens, 1, tmp_path / "res.json", lines.append)
+    assert [b["position"] for b in rec["examples"][0]["bounds"]] == [1, 4, 5]     # 2 precedes a word piece, 3 is one
+    assert [b["position"] for b in rec["examples"][1]["bounds"]] == [1, 2, 3, 4, 5]
+    want = _reference_one_word(thr[0], 7, 0.1, 6)
+    for b in rec["examples"][0]["bounds"]:
+        assert b["eps"] == float(torch.tensor(want[b["position"]], dtype=torch.float32))
+    assert rec["examples"][0]["tokens"] == tokens[0]
+    assert json.loads((tmp_path / "res.json").read_text()) == rec
+    assert lines[0] == "2 valid examples" and lines[1].startswith("Minimum: ") and lines[2].startswith("Average: ")
+    pairs = run_and_record(EpsilonSearch(FakeVerifier(thr), 2, 0.5, 4), emb[:1], labels[:1], tokens[:1], 2)
+    assert [tuple(b["position"]) for b in pairs["examples"][0]["bounds"]] == [(1, 4), (1, 5), (4, 5)]
+    try:
+        run_and_record(search, emb, labels, tokens, 3)
+    except NotImplementedError:
+        pass
+    else:
+        raise AssertionError("three perturbed words must be refused")
