@@ -379,3 +379,34 @@ def test_layer_norms_applied_in_gemm_epilogues_give_the_same_bounds(words, posit
     for x, y in zip(again, fused):
         assert torch.equal(x, y)
     assert lib.fb_tc_check() == 0
+
+
+def test_run_and_record_gives_the_reference_result_file(tmp_path):
+    """run_and_record on the real driver: the record's radii are those of the batched search (which the test above holds
+    against the reference's own run), held in single precision with eps_normalized = eps / ||embedding||_p, the
+    summary follows from them, and the file on disk is the record as the reference writes it."""
+    import json
+    import faith_b200
+    from faith_b200.search import EpsilonSearch, run_and_record
+    c = sc = cases.SEARCH_CASE
+    model = O.make_encoder(c["seed"], c["layers"], c["d_model"], c["heads"], c["ffn"], c["std"])
+    emb = cases.encoder_inputs(c).to(DEV)
+    labels = torch.as_tensor(helpers.load_golden("search.npz")["labels"])
+    ver = faith_b200.EncoderVerifier(model, DEV)
+    plain = EpsilonSearch(ver, c["p"], sc["max_eps"], sc["iters"], max_instances=8).run(emb, labels)
+    lines = []
+    rec = run_and_record(EpsilonSearch(ver, c["p"], sc["max_eps"], sc["iters"], max_instances=8), emb, labels, None, 1,
+                         tmp_path / "res.json", lines.append)
+    assert len(rec["examples"]) == c["B"] and len(lines) == 3
+    mins, avgs = [], []
+    for s, ex in enumerate(rec["examples"]):
+        assert [b["position"] for b in ex["bounds"]] == sorted(plain[s])
+        for b in ex["bounds"]:
+            e32 = torch.tensor(plain[s][b["position"]], dtype=torch.float32)
+            assert b["eps"] == float(e32)
+            assert b["eps_normalized"] == float(e32 / torch.norm(emb[s, b["position"]].cpu(), p=float(c["p"])))
+        eps = [b["eps"] for b in ex["bounds"]]
+        mins.append(min(eps))
+        avgs.append(sum(eps) / len(eps))
+    assert abs(rec["minimum"] - sum(mins) / len(mins)) < 1e-12 and abs(rec["average"] - sum(avgs) / len(avgs)) < 1e-12
+    assert json.loads((tmp_path / "res.json").read_text()) == rec
